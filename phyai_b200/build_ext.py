@@ -1,0 +1,146 @@
+"""In-tree build of the native extensions for sm_100a.
+
+``python -m phyai_b200.build_ext`` compiles every ``csrc/*.cu`` with
+``nvcc -gencode arch=compute_100a,code=sm_100a -lineinfo`` (cross-compiles without a
+GPU), the pybind/torch binding unit with the host compiler, and links them into
+``phyai_b200/_C*.so`` next to the Python sources. Objects are cached under
+``build/`` keyed by a hash of the source, its headers and the flags, so an
+unchanged file is not recompiled.
+"""
+
+from __future__ import annotations
+
+import hashlib
+import os
+import subprocess
+import sys
+import sysconfig
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+CSRC = ROOT / "csrc"
+BUILD = ROOT.parent / "build"
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo"]
+
+
+def _hash(paths: list[Path], flags: list[str]) -> str:
+    h = hashlib.sha256()
+    for p in sorted(paths):
+        h.update(p.name.encode())
+        h.update(p.read_bytes())
+    h.update(" ".join(flags).encode())
+    return h.hexdigest()[:16]
+
+
+def _run(cmd: list[str]) -> None:
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)
+        raise RuntimeError(f"build step failed: {cmd[0]} {cmd[-1]}")
+
+
+def _torch_paths() -> tuple[list[str], list[str]]:
+    import torch  # noqa: F401
+    from torch.utils import cpp_extension as ce
+
+    return ce.include_paths(), ce.library_paths()
+
+
+def ext_suffix() -> str:
+    return sysconfig.get_config_var("EXT_SUFFIX") or ".so"
+
+
+def build_core(verbose: bool = False) -> Path:
+    """Build ``phyai_b200/_C`` (CUDA kernels + torch bindings)."""
+    BUILD.mkdir(exist_ok=True)
+    headers = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
+    inc, libdirs = _torch_paths()
+    pyinc = sysconfig.get_paths()["include"]
+    import pybind11
+
+    common_inc = [f"-I{CSRC}", f"-I{pyinc}", f"-I{pybind11.get_include()}"]
+    cu_flags = ARCH_FLAGS + ["-O3", "-std=c++17", "--use_fast_math", "-Xcompiler", "-fPIC",
+                             "--expt-relaxed-constexpr"] + common_inc
+    if verbose:
+        cu_flags += ["-Xptxas", "-v"]
+    cxx_flags = ["-O2", "-std=c++17", "-fPIC", "-DTORCH_EXTENSION_NAME=_C",
+                 "-DTORCH_API_INCLUDE_EXTENSION_H", "-D_GLIBCXX_USE_CXX11_ABI=1",
+                 "-I/usr/local/cuda/include"] + common_inc + [f"-I{p}" for p in inc]
+
+    jobs: list[tuple[list[str], Path]] = []
+    objs: list[Path] = []
+    for src in sorted(CSRC.glob("*.cu")):
+        if src.name.startswith("radix") or src.name.startswith("standalone_"):
+            continue
+        tag = _hash([src] + headers, cu_flags)
+        obj = BUILD / f"{src.stem}.{tag}.o"
+        objs.append(obj)
+        if not obj.exists():
+            jobs.append(([NVCC, *cu_flags, "-c", str(src), "-o", str(obj)], obj))
+    bsrc = CSRC / "bindings.cpp"
+    tag = _hash([bsrc] + headers, cxx_flags)
+    bobj = BUILD / f"bindings.{tag}.o"
+    objs.append(bobj)
+    if not bobj.exists():
+        jobs.append((["g++", *cxx_flags, "-c", str(bsrc), "-o", str(bobj)], bobj))
+
+    with ThreadPoolExecutor(max_workers=max(1, min(8, len(jobs) or 1))) as ex:
+        list(ex.map(lambda j: _run(j[0]), jobs))
+
+    out = ROOT / f"_C{ext_suffix()}"
+    link_tag = _hash(objs, ["link"])
+    stamp = BUILD / f"_C.{link_tag}.stamp"
+    if not out.exists() or not stamp.exists():
+        libs = ["-lc10", "-ltorch", "-ltorch_cpu", "-ltorch_python", "-lc10_cuda", "-ltorch_cuda"]
+        cmd = [NVCC, "-shared", *ARCH_FLAGS, "-o", str(out), *map(str, objs),
+               *[f"-L{p}" for p in libdirs], *libs,
+               *[f"-Xlinker=-rpath={p}" for p in libdirs]]
+        _run(cmd)
+        stamp.write_text("ok")
+    return out
+
+
+def build_radix(verbose: bool = False) -> Path | None:
+    """Build ``phyai_b200/_radix`` (host-only C++ prefix cache, pybind11)."""
+    src_dir = CSRC / "radix_cache"
+    if not src_dir.exists():
+        return None
+    BUILD.mkdir(exist_ok=True)
+    import pybind11
+
+    srcs = sorted(src_dir.glob("*.cpp"))
+    hdrs = sorted(src_dir.glob("*.h"))
+    pyinc = sysconfig.get_paths()["include"]
+    flags = ["-O2", "-std=c++20", "-fPIC", "-pthread", f"-I{src_dir}", f"-I{pyinc}",
+             f"-I{pybind11.get_include()}"]
+    objs, jobs = [], []
+    for s in srcs:
+        tag = _hash([s] + hdrs, flags)
+        o = BUILD / f"radix_{s.stem}.{tag}.o"
+        objs.append(o)
+        if not o.exists():
+            jobs.append(["g++", *flags, "-c", str(s), "-o", str(o)])
+    with ThreadPoolExecutor(max_workers=8) as ex:
+        list(ex.map(_run, jobs))
+    out = ROOT / f"_radix{ext_suffix()}"
+    link_tag = _hash(objs, ["link-radix"])
+    stamp = BUILD / f"_radix.{link_tag}.stamp"
+    if not out.exists() or not stamp.exists():
+        _run(["g++", "-shared", "-pthread", "-o", str(out), *map(str, objs)])
+        stamp.write_text("ok")
+    return out
+
+
+def build_all(verbose: bool = False) -> list[Path]:
+    outs = [build_core(verbose)]
+    r = build_radix(verbose)
+    if r is not None:
+        outs.append(r)
+    return outs
+
+
+if __name__ == "__main__":
+    for p in build_all("-v" in sys.argv):
+        print("built", p)

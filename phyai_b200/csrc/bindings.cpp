@@ -1,0 +1,264 @@
+// Python bindings: torch tensors in, raw pointers + the current CUDA stream out.
+// No allocation happens here; callers own every buffer (so the calls are safe to
+// capture in a CUDA graph).
+#include <ATen/cuda/CUDAContext.h>
+#include <torch/extension.h>
+
+#include "attention.cuh"
+#include "comm.cuh"
+#include "gemm.cuh"
+#include "ops.cuh"
+
+namespace {
+
+using at::Tensor;
+using OptT = c10::optional<Tensor>;
+
+inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+inline void check(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) {
+    // a launch error leaves a sticky "last error"; clear it so later calls report their own
+    cudaGetLastError();
+    TORCH_CHECK(false, what, ": ", cudaGetErrorString(e));
+  }
+}
+inline const __nv_bfloat16* bf(const OptT& t) {
+  if (!t.has_value() || !t->defined()) return nullptr;
+  TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kBFloat16, "expected a CUDA bf16 tensor");
+  return reinterpret_cast<const __nv_bfloat16*>(t->data_ptr());
+}
+inline const __nv_bfloat16* bf(const Tensor& t) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16, "expected a CUDA bf16 tensor");
+  return reinterpret_cast<const __nv_bfloat16*>(t.data_ptr());
+}
+inline __nv_bfloat16* bfm(const Tensor& t) { return const_cast<__nv_bfloat16*>(bf(t)); }
+inline const float* f32(const OptT& t) {
+  if (!t.has_value() || !t->defined()) return nullptr;
+  TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat, "expected a CUDA fp32 tensor");
+  return reinterpret_cast<const float*>(t->data_ptr());
+}
+inline const int* i32(const OptT& t) {
+  if (!t.has_value() || !t->defined()) return nullptr;
+  TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kInt, "expected a CUDA int32 tensor");
+  return reinterpret_cast<const int*>(t->data_ptr());
+}
+inline const long long* i64(const OptT& t) {
+  if (!t.has_value() || !t->defined()) return nullptr;
+  TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kLong, "expected a CUDA int64 tensor");
+  return reinterpret_cast<const long long*>(t->data_ptr());
+}
+
+void gemm(const Tensor& x, const Tensor& w, Tensor& out, const OptT& bias, const OptT& residual,
+          int64_t res_mod, const OptT& col_gate, const OptT& row_scale, const OptT& sumsq,
+          int64_t act, bool glu, const OptT& a_scale, const OptT& w_scale, int64_t force_bn,
+          int64_t force_swap, int64_t force_splits) {
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2, "gemm: 2-D tensors expected");
+  TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1 && out.stride(1) == 1, "gemm: rows must be contiguous");
+  TORCH_CHECK(x.size(1) == w.size(1), "gemm: K mismatch");
+  const bool fp8 = x.scalar_type() == at::kFloat8_e4m3fn;
+  TORCH_CHECK(fp8 || x.scalar_type() == at::kBFloat16, "gemm: x must be bf16 or float8_e4m3fn");
+  TORCH_CHECK(w.scalar_type() == x.scalar_type(), "gemm: x and w dtypes differ");
+  pb::GemmArgs a;
+  a.x = x.data_ptr(); a.w = w.data_ptr(); a.out = out.data_ptr();
+  a.M = int(x.size(0)); a.N = int(w.size(0)); a.K = int(x.size(1));
+  a.ldx = int(x.stride(0)); a.ldw = int(w.stride(0)); a.ldo = int(out.stride(0));
+  TORCH_CHECK(out.size(0) == a.M && out.size(1) == (glu ? a.N / 2 : a.N), "gemm: out shape");
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 || out.scalar_type() == at::kFloat, "gemm: out dtype");
+  a.out_fp32 = out.scalar_type() == at::kFloat;
+  a.bias = bf(bias);
+  if (residual.has_value() && residual->defined()) {
+    TORCH_CHECK(residual->dim() == 2 && residual->stride(1) == 1, "gemm: residual layout");
+    a.residual = bf(residual);
+    a.ldr = int(residual->stride(0));
+    a.res_mod = int(res_mod);
+  }
+  a.col_gate = bf(col_gate);
+  a.row_scale = f32(row_scale);
+  a.sumsq = const_cast<float*>(f32(sumsq));
+  a.act = int(act); a.glu = glu ? 1 : 0; a.fp8 = fp8 ? 1 : 0;
+  a.a_scale = f32(a_scale); a.w_scale = f32(w_scale);
+  TORCH_CHECK(!fp8 || (a.a_scale && a.w_scale), "gemm: fp8 needs a_scale [M] and w_scale [N]");
+  a.force_bn = int(force_bn); a.force_swap = int(force_swap); a.force_splits = int(force_splits);
+  check(pb::gemm_launch(a, cur_stream()), "gemm_launch");
+}
+
+void attention(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& out,
+               const Tensor& q_start, const Tensor& q_len, const Tensor& kv_indptr,
+               const Tensor& kv_len, const OptT& kv_indices, int64_t max_q_len, bool causal,
+               int64_t splits, double sm_scale) {
+  // q/out: [tokens, Hq, D]; k/v: [rows, Hkv, D]; innermost dim contiguous
+  TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3 && out.dim() == 3, "attention: 3-D tensors");
+  TORCH_CHECK(q.stride(2) == 1 && k.stride(2) == 1 && v.stride(2) == 1 && out.stride(2) == 1,
+              "attention: head_dim must be contiguous");
+  TORCH_CHECK(k.stride(0) == v.stride(0) && k.stride(1) == v.stride(1), "attention: k/v strides differ");
+  pb::AttnParams p;
+  p.q = bf(q); p.k = bf(k); p.v = bf(v); p.out = bfm(out);
+  p.q_start = i32(q_start); p.q_len = i32(q_len); p.kv_indptr = i32(kv_indptr); p.kv_len = i32(kv_len);
+  p.kv_indices = i32(kv_indices);
+  p.q_tok_stride = q.stride(0); p.q_head_stride = q.stride(1);
+  p.kv_row_stride = k.stride(0); p.kv_head_stride = k.stride(1);
+  p.o_tok_stride = out.stride(0); p.o_head_stride = out.stride(1);
+  p.batch = int(q_len.numel());
+  p.num_kv_heads = int(k.size(1));
+  TORCH_CHECK(q.size(1) % k.size(1) == 0, "attention: Hq must be a multiple of Hkv");
+  p.group = int(q.size(1) / k.size(1));
+  p.head_dim = int(q.size(2));
+  p.max_q_len = int(max_q_len);
+  p.causal = causal ? 1 : 0;
+  p.splits = int(splits);
+  p.sm_scale = float(sm_scale);
+  check(pb::attn_launch(p, cur_stream()), "attn_launch");
+}
+
+void norm(const Tensor& x, const OptT& y, int64_t mode, const OptT& weight, const OptT& bias,
+          const OptT& mod, int64_t group, const OptT& residual, const OptT& sumsq, double eps,
+          const OptT& y8, const OptT& y8_scale, int64_t y8_block) {
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1, "norm: x must be 2-D with contiguous rows");
+  pb::NormArgs a;
+  a.x = bf(x); a.rows = int(x.size(0)); a.D = int(x.size(1)); a.ldx = int(x.stride(0));
+  if (y.has_value() && y->defined()) {
+    TORCH_CHECK(y->dim() == 2 && y->stride(1) == 1 && y->size(0) == x.size(0) && y->size(1) == x.size(1), "norm: y shape");
+    a.y = bfm(*y); a.ldy = int(y->stride(0));
+  }
+  a.weight = bf(weight); a.bias = bf(bias); a.mod = bf(mod);
+  a.group = int(group); a.mode = int(mode); a.eps = float(eps);
+  if (residual.has_value() && residual->defined()) {
+    a.residual = bfm(*residual); a.ldr = int(residual->stride(0));
+  }
+  a.sumsq = f32(sumsq);
+  if (y8.has_value() && y8->defined()) {
+    TORCH_CHECK(y8->is_contiguous(), "norm: y8 must be contiguous");
+    a.y8 = reinterpret_cast<uint8_t*>(y8->data_ptr());
+    a.y8_scale = const_cast<float*>(f32(y8_scale));
+    a.y8_block = int(y8_block);
+  }
+  if (a.mode == pb::kNormLayer) TORCH_CHECK(a.weight && a.bias, "layernorm needs weight and bias");
+  if (a.mode == pb::kNormRms || a.mode == pb::kNormGemmaRms) TORCH_CHECK(a.weight, "rmsnorm needs weight");
+  if (a.mode == pb::kNormAdaRms) TORCH_CHECK(a.mod && a.group > 0, "adarmsnorm needs modulation");
+  check(pb::norm_launch(a, cur_stream()), "norm_launch");
+}
+
+void rope_kv(const Tensor& qkv, int64_t Hq, int64_t Hkv, int64_t D, const OptT& pos,
+             const OptT& cos_sin, int64_t rot_dim, const OptT& q_norm_w, const OptT& k_norm_w,
+             double norm_eps, Tensor& q_out, const OptT& k_pool, const OptT& v_pool,
+             const OptT& slots, int64_t slot_base) {
+  TORCH_CHECK(qkv.dim() == 2 && qkv.stride(1) == 1, "rope_kv: qkv layout");
+  TORCH_CHECK(qkv.size(1) == (Hq + 2 * Hkv) * D, "rope_kv: qkv width");
+  pb::RopeKvArgs a;
+  a.qkv = bf(qkv); a.M = int(qkv.size(0)); a.ld = int(qkv.stride(0));
+  a.Hq = int(Hq); a.Hkv = int(Hkv); a.D = int(D);
+  a.pos = i32(pos); a.cos_sin = f32(cos_sin); a.rot_dim = int(rot_dim);
+  a.q_norm_w = bf(q_norm_w); a.k_norm_w = bf(k_norm_w); a.norm_eps = float(norm_eps);
+  TORCH_CHECK(q_out.dim() == 2 && q_out.stride(1) == 1, "rope_kv: q_out layout");
+  a.q_out = bfm(q_out); a.ldq = int(q_out.stride(0));
+  if (k_pool.has_value() && k_pool->defined()) {
+    TORCH_CHECK(v_pool.has_value() && k_pool->stride(0) == v_pool->stride(0), "rope_kv: pools");
+    a.k_pool = bfm(*k_pool); a.v_pool = bfm(*v_pool);
+    a.pool_row_stride = k_pool->stride(0);
+  }
+  a.slots = i64(slots); a.slot_base = slot_base;
+  check(pb::rope_kv_launch(a, cur_stream()), "rope_kv_launch");
+}
+
+void embedding(const Tensor& ids, const Tensor& table, int64_t lo, int64_t hi, double scale,
+               Tensor& out, const OptT& dst_rows) {
+  TORCH_CHECK(ids.is_contiguous() && table.is_contiguous() && out.stride(-1) == 1, "embedding: layout");
+  check(pb::embedding_launch(i64(OptT(ids)), int(ids.numel()), bf(table), int(table.size(1)), lo,
+                             hi, float(scale), bfm(out), int(out.stride(0)), i32(dst_rows),
+                             cur_stream()),
+        "embedding_launch");
+}
+
+void im2col(const Tensor& pix, int64_t patch, Tensor& out) {
+  TORCH_CHECK(pix.dim() == 4 && pix.is_contiguous() && out.is_contiguous(), "im2col: layout");
+  check(pb::im2col_launch(bf(pix), int(pix.size(0)), int(pix.size(1)), int(pix.size(2)),
+                          int(pix.size(3)), int(patch), bfm(out), int(out.size(1)), cur_stream()),
+        "im2col_launch");
+}
+
+void gated_act(const Tensor& x, Tensor& y, int64_t act, bool interleaved) {
+  TORCH_CHECK(x.is_contiguous() && y.is_contiguous() && x.size(-1) == 2 * y.size(-1), "gated_act: layout");
+  const int I = int(y.size(-1));
+  check(pb::gated_act_launch(bf(x), bfm(y), int(y.numel() / I), I, int(act), interleaved ? 1 : 0,
+                             cur_stream()),
+        "gated_act_launch");
+}
+
+void unary(const Tensor& x, Tensor& y, int64_t act) {
+  TORCH_CHECK(x.is_contiguous() && y.is_contiguous() && x.numel() == y.numel(), "unary: layout");
+  check(pb::unary_launch(bf(x), bfm(y), x.numel(), int(act), cur_stream()), "unary_launch");
+}
+
+void axpy(Tensor& x, const Tensor& v, double dt) {
+  TORCH_CHECK(x.is_contiguous() && v.is_contiguous() && x.numel() == v.numel(), "axpy: layout");
+  TORCH_CHECK(x.scalar_type() == at::kFloat || x.scalar_type() == at::kBFloat16, "axpy: x dtype");
+  check(pb::axpy_launch(x.data_ptr(), x.scalar_type() == at::kFloat, bf(v), float(dt), x.numel(),
+                        cur_stream()),
+        "axpy_launch");
+}
+
+void cfg_combine(const Tensor& cond, const Tensor& uncond, double g, const OptT& out,
+                 const OptT& x_fp32, double dt) {
+  TORCH_CHECK(cond.is_contiguous() && uncond.is_contiguous() && cond.numel() == uncond.numel(), "cfg_combine: layout");
+  __nv_bfloat16* o = (out.has_value() && out->defined()) ? bfm(*out) : nullptr;
+  check(pb::cfg_combine_launch(bf(cond), bf(uncond), float(g), o,
+                               const_cast<float*>(f32(x_fp32)), float(dt), cond.numel(),
+                               cur_stream()),
+        "cfg_combine_launch");
+}
+
+void scatter_rows(const Tensor& src, Tensor& dst, const OptT& rows) {
+  TORCH_CHECK(src.dim() == 2 && dst.dim() == 2 && src.stride(1) == 1 && dst.stride(1) == 1, "scatter_rows: layout");
+  check(pb::scatter_rows_launch(bf(src), int(src.size(0)), int(src.size(1)), int(src.stride(0)),
+                                bfm(dst), int(dst.stride(0)), i32(rows), cur_stream()),
+        "scatter_rows_launch");
+}
+
+void quant_fp8(const Tensor& x, Tensor& y, Tensor& scale, int64_t block) {
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && y.is_contiguous(), "quant_fp8: layout");
+  check(pb::quant_fp8_launch(bf(x), int(x.size(0)), int(x.size(1)), int(x.stride(0)),
+                             reinterpret_cast<uint8_t*>(y.data_ptr()),
+                             const_cast<float*>(f32(OptT(scale))), int(block), cur_stream()),
+        "quant_fp8_launch");
+}
+
+}  // namespace
+
+void register_comm(pybind11::module_& m);
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  namespace py = pybind11;
+  m.def("gemm", &gemm, py::arg("x"), py::arg("w"), py::arg("out"), py::arg("bias") = py::none(),
+        py::arg("residual") = py::none(), py::arg("res_mod") = 0, py::arg("col_gate") = py::none(),
+        py::arg("row_scale") = py::none(), py::arg("sumsq") = py::none(), py::arg("act") = 0,
+        py::arg("glu") = false, py::arg("a_scale") = py::none(), py::arg("w_scale") = py::none(),
+        py::arg("force_bn") = 0, py::arg("force_swap") = -1, py::arg("force_splits") = 0);
+  m.def("attention", &attention, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"),
+        py::arg("q_start"), py::arg("q_len"), py::arg("kv_indptr"), py::arg("kv_len"),
+        py::arg("kv_indices") = py::none(), py::arg("max_q_len"), py::arg("causal") = false,
+        py::arg("splits") = 1, py::arg("sm_scale") = 1.0);
+  m.def("norm", &norm, py::arg("x"), py::arg("y"), py::arg("mode"), py::arg("weight") = py::none(),
+        py::arg("bias") = py::none(), py::arg("mod") = py::none(), py::arg("group") = 1,
+        py::arg("residual") = py::none(), py::arg("sumsq") = py::none(), py::arg("eps") = 1e-6,
+        py::arg("y8") = py::none(), py::arg("y8_scale") = py::none(), py::arg("y8_block") = 0);
+  m.def("rope_kv", &rope_kv, py::arg("qkv"), py::arg("Hq"), py::arg("Hkv"), py::arg("D"),
+        py::arg("pos") = py::none(), py::arg("cos_sin") = py::none(), py::arg("rot_dim") = 0,
+        py::arg("q_norm_w") = py::none(), py::arg("k_norm_w") = py::none(),
+        py::arg("norm_eps") = 1e-6, py::arg("q_out"), py::arg("k_pool") = py::none(),
+        py::arg("v_pool") = py::none(), py::arg("slots") = py::none(), py::arg("slot_base") = 0);
+  m.def("embedding", &embedding, py::arg("ids"), py::arg("table"), py::arg("lo"), py::arg("hi"),
+        py::arg("scale"), py::arg("out"), py::arg("dst_rows") = py::none());
+  m.def("im2col", &im2col);
+  m.def("gated_act", &gated_act);
+  m.def("unary", &unary);
+  m.def("axpy", &axpy);
+  m.def("cfg_combine", &cfg_combine, py::arg("cond"), py::arg("uncond"), py::arg("g"),
+        py::arg("out") = py::none(), py::arg("x_fp32") = py::none(), py::arg("dt") = 0.0);
+  m.def("scatter_rows", &scatter_rows, py::arg("src"), py::arg("dst"), py::arg("rows") = py::none());
+  m.def("quant_fp8", &quant_fp8);
+  m.def("kernel_status", [] { return pb::read_and_clear_kernel_status(); });
+  m.def("launch_counter", [] { return pb::launch_counter(); });
+  m.def("reset_launch_counter", [] { pb::reset_launch_counter(); });
+  register_comm(m);
+}

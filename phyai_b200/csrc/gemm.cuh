@@ -1,0 +1,60 @@
+// Host-visible declarations for the tcgen05 GEMM family (see gemm.cu).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace pb {
+
+enum GemmAct : int { kActNone = 0, kActGeluTanh = 1, kActSilu = 2, kActGeluErf = 3 };
+
+// out[M, N'] = epilogue( X[M, K] @ W[N, K]^T ), bf16 (or e4m3) operands, fp32 accumulate.
+//
+// Epilogue, in this order, on the fp32 accumulator acc[m, n]:
+//   acc *= row_scale[m]                 (row_scale != null; e.g. a fused RMS 1/rms)
+//   acc *= a_scale[m] * w_scale[n]      (per-row / per-channel dequant scales, fp8 only)
+//   acc += bias[n]                      (bias != null)
+//   acc  = act(acc)                     (act != none, glu == 0)
+//   glu: y[m, n/2] = act(acc[m, 2j]) * acc[m, 2j+1]   (weight rows interleaved gate/up)
+//   acc *= col_gate[n]                  (col_gate != null; row-broadcast gate vector)
+//   acc *= row_gate... (unused)
+//   acc += residual[m % res_mod, n]     (residual != null)
+//   sumsq[m] += sum_n acc^2             (sumsq != null; fp32 atomics; feeds a fused RMSNorm)
+//   store bf16 (or fp32 when out_fp32)
+struct GemmArgs {
+  const void* x = nullptr;   // [M, K], row stride ldx elements
+  const void* w = nullptr;   // [N, K], row stride ldw elements
+  void* out = nullptr;       // [M, N or N/2], row stride ldo elements
+  int M = 0, N = 0, K = 0;
+  int ldx = 0, ldw = 0, ldo = 0;
+  const __nv_bfloat16* bias = nullptr;      // [N]
+  const __nv_bfloat16* residual = nullptr;  // [res_rows, ldr]
+  int ldr = 0;
+  int res_mod = 0;                          // 0: residual row = m
+  const __nv_bfloat16* col_gate = nullptr;  // [N]
+  const float* row_scale = nullptr;         // [M]
+  float* sumsq = nullptr;                   // [M]
+  int act = kActNone;
+  int glu = 0;
+  int out_fp32 = 0;
+  int fp8 = 0;                              // operands are e4m3, K counted in elements
+  const float* a_scale = nullptr;           // fp8: [M] or [M, K/128] (block)
+  const float* w_scale = nullptr;           // fp8: [N] or [N/128, K/128] (block)
+  int block_scaled = 0;                     // fp8: 128x128 weight blocks, 1x128 act blocks
+  int force_bn = 0, force_swap = -1, force_splits = 0;  // tuning overrides (0/-1 = auto)
+};
+
+// Launches on `stream`. Returns cudaSuccess or the launch error; argument
+// problems (alignment, unsupported shape) return cudaErrorInvalidValue.
+cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream);
+
+// Device-global status word shared by the kernels of this library (0 = ok).
+int* kernel_status_ptr();
+int read_and_clear_kernel_status();
+
+// How many kernels of this library were launched since the last reset.
+uint64_t launch_counter();
+void reset_launch_counter();
+void bump_launch_counter(uint64_t n = 1);
+
+}  // namespace pb

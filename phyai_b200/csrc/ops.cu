@@ -1,0 +1,515 @@
+// Memory-bound kernels for sm_100a: every one is a single pass over its rows with
+// 16-byte vector accesses and fp32 arithmetic. They cover what the reference runs
+// through Triton / FlashInfer / ATen:
+//   norms            phyai-kernel/phyai_kernel/triton/{rms_norm,layer_norm,ada_rms_norm}.py
+//   RoPE + KV write  phyai/src/phyai/layers/rotary_embedding.py:520-578,
+//                    phyai/src/phyai/cache/kv_cache_pool.py:139-182 (two index_put_)
+//   masked embedding phyai-kernel/phyai_kernel/triton/masked_embedding.py:35-77
+//   gated act        phyai/src/phyai/layers/mlp/dense_mlp.py:87-108
+//   Euler / CFG      phyai/src/phyai/models/pi05/model_runner_pi05.py:735-737,
+//                    phyai/src/phyai/models/cosmos3/scheduler_wn_cosmos3.py:228
+#include "ops.cuh"
+
+#include <cuda_fp8.h>
+
+#include "gemm.cuh"
+#include "ptx.cuh"
+
+namespace pb {
+
+namespace {
+
+struct alignas(16) BF8 {
+  __nv_bfloat162 v[4];
+};
+
+__device__ __forceinline__ void unpack8(const BF8& b, float (&f)[8]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __bfloat162float(b.v[i].x);
+    f[2 * i + 1] = __bfloat162float(b.v[i].y);
+  }
+}
+__device__ __forceinline__ BF8 pack8(const float (&f)[8]) {
+  BF8 b;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) b.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return b;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// Block-wide sum; red must hold 32 floats. Every thread gets the result.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  const int nw = (blockDim.x + 31) >> 5;
+  float t = lane < nw ? red[lane] : 0.f;
+  return warp_sum(t);
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  const int nw = (blockDim.x + 31) >> 5;
+  float t = lane < nw ? red[lane] : -INFINITY;
+  return warp_max(t);
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------- norms
+template <int MODE>
+__global__ void norm_kernel(NormArgs a) {
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const int nv = a.D >> 3;
+  pdl_wait();
+  const BF8* xr = reinterpret_cast<const BF8*>(a.x + size_t(row) * a.ldx);
+  BF8* rr = a.residual ? reinterpret_cast<BF8*>(a.residual + size_t(row) * a.ldr) : nullptr;
+  BF8* yr = reinterpret_cast<BF8*>(a.y + size_t(row) * a.ldy);
+
+  // pass 1: (optional residual add, written back) + moments
+  float s1 = 0.f, s2 = 0.f;
+  for (int v = threadIdx.x; v < nv; v += blockDim.x) {
+    float f[8];
+    unpack8(xr[v], f);
+    if (rr) {
+      float g[8];
+      unpack8(rr[v], g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] += g[i];
+      BF8 h = pack8(f);
+      rr[v] = h;
+      unpack8(h, f);  // the norm sees the rounded sum, as a separate add kernel would produce
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { s1 += f[i]; s2 += f[i] * f[i]; }
+  }
+  float mean = 0.f, rstd;
+  if (MODE == kNormLayer) {
+    s1 = block_sum(s1, red);
+    s2 = block_sum(s2, red);
+    mean = s1 / a.D;
+    const float var = fmaxf(s2 / a.D - mean * mean, 0.f);
+    rstd = rsqrtf(var + a.eps);
+  } else {
+    if (a.sumsq && !rr) s2 = a.sumsq[row]; else s2 = block_sum(s2, red);
+    rstd = rsqrtf(s2 / a.D + a.eps);
+  }
+  const BF8* src = rr ? rr : xr;
+  const BF8* wv = a.weight ? reinterpret_cast<const BF8*>(a.weight) : nullptr;
+  const BF8* bv = a.bias ? reinterpret_cast<const BF8*>(a.bias) : nullptr;
+  const BF8* mv = nullptr;
+  if (MODE == kNormAdaRms) mv = reinterpret_cast<const BF8*>(a.mod + size_t(row / a.group) * 3 * a.D);
+
+  float amax = 0.f;
+  for (int v = threadIdx.x; v < nv; v += blockDim.x) {
+    float f[8], o[8];
+    unpack8(src[v], f);
+    if (MODE == kNormLayer) {
+      float w[8], b[8];
+      unpack8(wv[v], w);
+      unpack8(bv[v], b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = (f[i] - mean) * rstd * w[i] + b[i];
+    } else if (MODE == kNormAdaRms) {
+      float sc[8], sh[8];
+      unpack8(mv[v], sc);
+      unpack8(mv[nv + v], sh);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = f[i] * rstd * (1.f + sc[i]) + sh[i];
+    } else if (MODE == kNormRmsNoWeight) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = f[i] * rstd;
+    } else {
+      float w[8];
+      unpack8(wv[v], w);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        o[i] = f[i] * rstd * (MODE == kNormGemmaRms ? 1.f + w[i] : w[i]);
+    }
+    if (a.y) yr[v] = pack8(o);
+    if (a.y8) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(o[i]));
+    }
+  }
+  if (a.y8) {
+    // second sweep for the fp8 copy: per-row scale, or one scale per 128 columns
+    if (a.y8_block == 0) {
+      amax = block_max(amax, red);
+      const float sc = fmaxf(amax, 1e-12f) / 448.f;
+      if (threadIdx.x == 0) a.y8_scale[row] = sc;
+      const float inv = 1.f / sc;
+      for (int v = threadIdx.x; v < nv; v += blockDim.x) {
+        float o[8];
+        unpack8(yr[v], o);
+        uint8_t q[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          q[i] = __nv_cvt_float_to_fp8(o[i] * inv, __NV_SATFINITE, __NV_E4M3);
+        *reinterpret_cast<uint2*>(a.y8 + size_t(row) * a.D + v * 8) =
+            *reinterpret_cast<uint2*>(q);
+      }
+    } else {
+      // 16 consecutive threads own one 128-column block
+      __syncthreads();
+      const int nb = a.D >> 7;
+      for (int v0 = 0; v0 < nv; v0 += blockDim.x) {
+        const int v = v0 + threadIdx.x;
+        float o[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (v < nv) unpack8(yr[v], o);
+        float m = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(o[i]));
+#pragma unroll
+        for (int off = 8; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+        const float sc = fmaxf(m, 1e-12f) / 448.f;
+        if (v < nv) {
+          if ((v & 15) == 0) a.y8_scale[size_t(row) * nb + (v >> 4)] = sc;
+          const float inv = 1.f / sc;
+          uint8_t q[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            q[i] = __nv_cvt_float_to_fp8(o[i] * inv, __NV_SATFINITE, __NV_E4M3);
+          *reinterpret_cast<uint2*>(a.y8 + size_t(row) * a.D + v * 8) =
+              *reinterpret_cast<uint2*>(q);
+        }
+      }
+    }
+  }
+  pdl_launch_dependents();
+}
+
+cudaError_t norm_launch(const NormArgs& a, cudaStream_t s) {
+  if (a.rows <= 0) return cudaSuccess;
+  if (a.D % 8 || a.ldx % 8 || a.ldy % 8 || (a.residual && a.ldr % 8)) return cudaErrorInvalidValue;
+  if (a.y8 && a.y8_block && (a.D % 128)) return cudaErrorInvalidValue;
+  if (a.y8 && !a.y) return cudaErrorInvalidValue;
+  int threads = ((a.D / 8) + 31) / 32 * 32;
+  if (threads > 1024) threads = 1024;
+  if (threads < 32) threads = 32;
+  bump_launch_counter();
+  switch (a.mode) {
+    case kNormRms: norm_kernel<kNormRms><<<a.rows, threads, 0, s>>>(a); break;
+    case kNormGemmaRms: norm_kernel<kNormGemmaRms><<<a.rows, threads, 0, s>>>(a); break;
+    case kNormLayer: norm_kernel<kNormLayer><<<a.rows, threads, 0, s>>>(a); break;
+    case kNormAdaRms: norm_kernel<kNormAdaRms><<<a.rows, threads, 0, s>>>(a); break;
+    case kNormRmsNoWeight: norm_kernel<kNormRmsNoWeight><<<a.rows, threads, 0, s>>>(a); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------- RoPE + KV scatter
+// One warp per (token, head). Heads [0,Hq) are queries (normed, rotated, written to
+// q_out), [Hq,Hq+Hkv) keys (normed, rotated, scattered to k_pool), the rest values.
+__global__ void rope_kv_kernel(RopeKvArgs a) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long wid = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const int H = a.Hq + 2 * a.Hkv;
+  pdl_wait();
+  if (wid >= (long long)a.M * H) return;
+  const int tok = int(wid / H), h = int(wid % H);
+  const int D = a.D, half_rot = (a.rot_dim > 0 ? a.rot_dim : D) >> 1;
+  const __nv_bfloat16* src = a.qkv + size_t(tok) * a.ld + size_t(h) * D;
+  const bool is_q = h < a.Hq, is_k = !is_q && h < a.Hq + a.Hkv;
+  __nv_bfloat16* dst;
+  if (is_q) {
+    dst = a.q_out + size_t(tok) * a.ldq + size_t(h) * D;
+  } else {
+    const long long slot = a.slots ? a.slots[tok] : a.slot_base + tok;
+    __nv_bfloat16* pool = is_k ? a.k_pool : a.v_pool;
+    if (pool == nullptr) return;
+    const int hk = is_k ? h - a.Hq : h - a.Hq - a.Hkv;
+    dst = pool + size_t(slot) * a.pool_row_stride + size_t(hk) * D;
+  }
+  if (!is_q && !is_k) {
+    for (int i = lane * 8; i < D; i += 256)
+      *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(src + i);
+    return;
+  }
+  const __nv_bfloat16* nw = is_q ? a.q_norm_w : a.k_norm_w;
+  float rstd = 1.f;
+  if (nw) {
+    float ss = 0.f;
+    for (int i = lane; i < D; i += 32) {
+      const float v = __bfloat162float(src[i]);
+      ss += v * v;
+    }
+    ss = warp_sum(ss);
+    rstd = rsqrtf(ss / D + a.norm_eps);
+  }
+  const float* cs = nullptr;
+  if (a.cos_sin) cs = a.cos_sin + size_t(a.pos ? a.pos[tok] : tok) * (2 * half_rot);
+  for (int i = lane; i < (D >> 1); i += 32) {
+    // pair (i, i + half_rot) inside the rotated span; dims past rot_dim pass through
+    if (i < half_rot) {
+      float x1 = __bfloat162float(src[i]), x2 = __bfloat162float(src[i + half_rot]);
+      if (nw) {
+        // norm output is rounded to bf16 before the rotation, as separate kernels would
+        x1 = __bfloat162float(__float2bfloat16(x1 * rstd * __bfloat162float(nw[i])));
+        x2 = __bfloat162float(__float2bfloat16(x2 * rstd * __bfloat162float(nw[i + half_rot])));
+      }
+      float c = 1.f, s = 0.f;
+      if (cs) { c = cs[i]; s = cs[half_rot + i]; }
+      dst[i] = __float2bfloat16(x1 * c - x2 * s);
+      dst[i + half_rot] = __float2bfloat16(x2 * c + x1 * s);
+    }
+  }
+  for (int i = 2 * half_rot + lane; i < D; i += 32) {
+    float x = __bfloat162float(src[i]);
+    if (nw) x = x * rstd * __bfloat162float(nw[i]);
+    dst[i] = __float2bfloat16(x);
+  }
+}
+
+cudaError_t rope_kv_launch(const RopeKvArgs& a, cudaStream_t s) {
+  if (a.M <= 0) return cudaSuccess;
+  if (a.D % 8 || a.ld % 8) return cudaErrorInvalidValue;
+  const long long warps = (long long)a.M * (a.Hq + 2 * a.Hkv);
+  const int wpb = 8;
+  bump_launch_counter();
+  rope_kv_kernel<<<unsigned((warps + wpb - 1) / wpb), wpb * 32, 0, s>>>(a);
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ embedding
+__global__ void embedding_kernel(const long long* ids, int n, const __nv_bfloat16* table, int D,
+                                 long long lo, long long hi, float scale, __nv_bfloat16* out,
+                                 int ldo, const int* dst_rows) {
+  const int m = blockIdx.x;
+  pdl_wait();
+  const long long id = ids[m];
+  const bool in = id >= lo && id < hi;
+  const int row = dst_rows ? dst_rows[m] : m;
+  if (row < 0) return;
+  BF8* o = reinterpret_cast<BF8*>(out + size_t(row) * ldo);
+  const BF8* t = reinterpret_cast<const BF8*>(table + size_t(in ? id - lo : 0) * D);
+  for (int v = threadIdx.x; v < (D >> 3); v += blockDim.x) {
+    float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (in) {
+      unpack8(t[v], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] *= scale;
+    }
+    o[v] = pack8(f);
+  }
+}
+cudaError_t embedding_launch(const long long* ids, int n, const __nv_bfloat16* table, int D,
+                             long long lo, long long hi, float scale, __nv_bfloat16* out, int ldo,
+                             const int* dst_rows, cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  if (D % 8 || ldo % 8) return cudaErrorInvalidValue;
+  bump_launch_counter();
+  embedding_kernel<<<n, 128, 0, s>>>(ids, n, table, D, lo, hi, scale, out, ldo, dst_rows);
+  return cudaGetLastError();
+}
+
+// --------------------------------------------------------------------- im2col
+__global__ void im2col_kernel(const __nv_bfloat16* pix, int C, int H, int W, int p,
+                              __nv_bfloat16* out, int kpad) {
+  const int gw = W / p, gh = H / p;
+  const int patch = blockIdx.x;             // over n_img * gh * gw
+  const int img = patch / (gh * gw), rem = patch % (gh * gw);
+  const int py0 = (rem / gw) * p, px0 = (rem % gw) * p;
+  const int kreal = C * p * p;
+  pdl_wait();
+  for (int k = threadIdx.x; k < kpad; k += blockDim.x) {
+    __nv_bfloat16 v = __float2bfloat16(0.f);
+    if (k < kreal) {
+      const int c = k / (p * p), r = k % (p * p);
+      const int y = py0 + r / p, x = px0 + r % p;
+      v = pix[((size_t(img) * C + c) * H + y) * W + x];
+    }
+    out[size_t(patch) * kpad + k] = v;
+  }
+}
+cudaError_t im2col_launch(const __nv_bfloat16* pix, int n_img, int C, int H, int W, int p,
+                          __nv_bfloat16* out, int kpad, cudaStream_t s) {
+  if (H % p || W % p || kpad < C * p * p) return cudaErrorInvalidValue;
+  bump_launch_counter();
+  im2col_kernel<<<n_img * (H / p) * (W / p), 256, 0, s>>>(pix, C, H, W, p, out, kpad);
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ gated act
+__device__ __forceinline__ float act_f(float v, int act) {
+  switch (act) {
+    case kActGeluTanh: return gelu_tanh_f(v);
+    case kActSilu: return silu_f(v);
+    case kActGeluErf: return gelu_erf_f(v);
+    default: return v;
+  }
+}
+__global__ void gated_act_kernel(const __nv_bfloat16* x, __nv_bfloat16* y, int M, int I, int act,
+                                 int interleaved) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_wait();
+  if (idx >= (long long)M * I) return;
+  const int m = int(idx / I), j = int(idx % I);
+  const __nv_bfloat16* r = x + size_t(m) * 2 * I;
+  const float g = __bfloat162float(interleaved ? r[2 * j] : r[j]);
+  const float u = __bfloat162float(interleaved ? r[2 * j + 1] : r[I + j]);
+  y[size_t(m) * I + j] = __float2bfloat16(act_f(g, act) * u);
+}
+cudaError_t gated_act_launch(const __nv_bfloat16* x, __nv_bfloat16* y, int M, int I, int act,
+                             int interleaved, cudaStream_t s) {
+  const long long n = (long long)M * I;
+  if (n <= 0) return cudaSuccess;
+  bump_launch_counter();
+  gated_act_kernel<<<unsigned((n + 255) / 256), 256, 0, s>>>(x, y, M, I, act, interleaved);
+  return cudaGetLastError();
+}
+
+__global__ void unary_kernel(const __nv_bfloat16* x, __nv_bfloat16* y, long long n, int act) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_wait();
+  if (i < n) y[i] = __float2bfloat16(act_f(__bfloat162float(x[i]), act));
+}
+cudaError_t unary_launch(const __nv_bfloat16* x, __nv_bfloat16* y, long long n, int act,
+                         cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  bump_launch_counter();
+  unary_kernel<<<unsigned((n + 255) / 256), 256, 0, s>>>(x, y, n, act);
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------ sampler updates
+__global__ void axpy_kernel(void* x, int x_fp32, const __nv_bfloat16* v, float dt, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_wait();
+  if (i >= n) return;
+  if (x_fp32) {
+    float* xf = reinterpret_cast<float*>(x);
+    xf[i] += dt * __bfloat162float(v[i]);
+  } else {
+    __nv_bfloat16* xb = reinterpret_cast<__nv_bfloat16*>(x);
+    xb[i] = __float2bfloat16(__bfloat162float(xb[i]) + dt * __bfloat162float(v[i]));
+  }
+}
+cudaError_t axpy_launch(void* x, int x_fp32, const __nv_bfloat16* v, float dt, long long n,
+                        cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  bump_launch_counter();
+  axpy_kernel<<<unsigned((n + 255) / 256), 256, 0, s>>>(x, x_fp32, v, dt, n);
+  return cudaGetLastError();
+}
+
+__global__ void cfg_combine_kernel(const __nv_bfloat16* c, const __nv_bfloat16* u, float g,
+                                   __nv_bfloat16* out, float* x, float dt, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_wait();
+  if (i >= n) return;
+  const float vc = __bfloat162float(c[i]), vu = __bfloat162float(u[i]);
+  const float v = vu + g * (vc - vu);
+  if (out) out[i] = __float2bfloat16(v);
+  if (x) x[i] += dt * v;
+}
+cudaError_t cfg_combine_launch(const __nv_bfloat16* cond, const __nv_bfloat16* uncond, float g,
+                               __nv_bfloat16* out, float* x_fp32, float dt, long long n,
+                               cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  bump_launch_counter();
+  cfg_combine_kernel<<<unsigned((n + 255) / 256), 256, 0, s>>>(cond, uncond, g, out, x_fp32, dt, n);
+  return cudaGetLastError();
+}
+
+// --------------------------------------------------------------- row scatter
+__global__ void scatter_rows_kernel(const __nv_bfloat16* src, int D, int lds, __nv_bfloat16* dst,
+                                    int ldd, const int* rows) {
+  const int i = blockIdx.x;
+  pdl_wait();
+  const int r = rows ? rows[i] : i;
+  if (r < 0) return;
+  const uint4* s4 = reinterpret_cast<const uint4*>(src + size_t(i) * lds);
+  uint4* d4 = reinterpret_cast<uint4*>(dst + size_t(r) * ldd);
+  for (int v = threadIdx.x; v < (D >> 3); v += blockDim.x) d4[v] = s4[v];
+}
+cudaError_t scatter_rows_launch(const __nv_bfloat16* src, int n, int D, int lds,
+                                __nv_bfloat16* dst, int ldd, const int* rows, cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  if (D % 8 || lds % 8 || ldd % 8) return cudaErrorInvalidValue;
+  bump_launch_counter();
+  scatter_rows_kernel<<<n, 128, 0, s>>>(src, D, lds, dst, ldd, rows);
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ fp8 quant
+__global__ void quant_fp8_kernel(const __nv_bfloat16* x, int D, int ldx, uint8_t* y, float* scale,
+                                 int block) {
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const int nv = D >> 3;
+  pdl_wait();
+  const BF8* xr = reinterpret_cast<const BF8*>(x + size_t(row) * ldx);
+  if (block == 0) {
+    float amax = 0.f;
+    for (int v = threadIdx.x; v < nv; v += blockDim.x) {
+      float f[8];
+      unpack8(xr[v], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+    }
+    amax = block_max(amax, red);
+    const float sc = fmaxf(amax, 1e-12f) / 448.f;
+    if (threadIdx.x == 0) scale[row] = sc;
+    const float inv = 1.f / sc;
+    for (int v = threadIdx.x; v < nv; v += blockDim.x) {
+      float f[8];
+      unpack8(xr[v], f);
+      uint8_t q[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) q[i] = __nv_cvt_float_to_fp8(f[i] * inv, __NV_SATFINITE, __NV_E4M3);
+      *reinterpret_cast<uint2*>(y + size_t(row) * D + v * 8) = *reinterpret_cast<uint2*>(q);
+    }
+  } else {
+    const int nb = D >> 7;
+    for (int v0 = 0; v0 < nv; v0 += blockDim.x) {
+      const int v = v0 + threadIdx.x;
+      float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      if (v < nv) unpack8(xr[v], f);
+      float m = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(f[i]));
+#pragma unroll
+      for (int off = 8; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+      const float sc = fmaxf(m, 1e-12f) / 448.f;
+      if (v < nv) {
+        if ((v & 15) == 0) scale[size_t(row) * nb + (v >> 4)] = sc;
+        const float inv = 1.f / sc;
+        uint8_t q[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q[i] = __nv_cvt_float_to_fp8(f[i] * inv, __NV_SATFINITE, __NV_E4M3);
+        *reinterpret_cast<uint2*>(y + size_t(row) * D + v * 8) = *reinterpret_cast<uint2*>(q);
+      }
+    }
+  }
+}
+cudaError_t quant_fp8_launch(const __nv_bfloat16* x, int rows, int D, int ldx, uint8_t* y,
+                             float* scale, int block, cudaStream_t s) {
+  if (rows <= 0) return cudaSuccess;
+  if (D % 8 || ldx % 8 || (block && D % 128)) return cudaErrorInvalidValue;
+  int threads = ((D / 8) + 31) / 32 * 32;
+  if (threads > 1024) threads = 1024;
+  bump_launch_counter();
+  quant_fp8_kernel<<<rows, threads, 0, s>>>(x, D, ldx, y, scale, block);
+  return cudaGetLastError();
+}
+
+}  // namespace pb

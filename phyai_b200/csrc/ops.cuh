@@ -1,0 +1,85 @@
+// Host-visible declarations for the memory-bound kernels (ops.cu): norms, RoPE +
+// KV scatter, embedding, patch extraction, gated activations, sampler updates,
+// fp8 activation quantisation.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace pb {
+
+enum NormMode : int { kNormRms = 0, kNormGemmaRms = 1, kNormLayer = 2, kNormAdaRms = 3, kNormRmsNoWeight = 4 };
+
+struct NormArgs {
+  const __nv_bfloat16* x = nullptr;     // [rows, D] row stride ldx
+  __nv_bfloat16* y = nullptr;           // [rows, D] row stride ldy
+  const __nv_bfloat16* weight = nullptr;  // [D] (rms / layer gamma)
+  const __nv_bfloat16* bias = nullptr;    // [D] (layer beta)
+  const __nv_bfloat16* mod = nullptr;     // AdaRMS: [rows/group, 3D] = scale | shift | gate
+  __nv_bfloat16* residual = nullptr;    // optional, in place: residual += x; y = norm(residual)
+  const float* sumsq = nullptr;         // optional: precomputed sum of squares per row
+  int rows = 0, D = 0, ldx = 0, ldy = 0, ldr = 0;
+  int group = 1;                        // AdaRMS: rows sharing one modulation row
+  int mode = kNormRms;
+  float eps = 1e-6f;
+  // optional fp8 output: y8 = e4m3(y / s) with s per row (block = 0) or per 128 columns
+  uint8_t* y8 = nullptr;
+  float* y8_scale = nullptr;
+  int y8_block = 0;
+};
+cudaError_t norm_launch(const NormArgs& a, cudaStream_t s);
+
+struct RopeKvArgs {
+  const __nv_bfloat16* qkv = nullptr;   // [M, ld]: q heads | k heads | v heads, each D wide
+  int M = 0, ld = 0, Hq = 0, Hkv = 0, D = 0;
+  const int* pos = nullptr;             // [M] row of cos_sin per token (null: row = token)
+  const float* cos_sin = nullptr;       // [rows, D]: cos(D/2) | sin(D/2); null = no rotation
+  int rot_dim = 0;                      // rotate the first rot_dim dims (0 = D)
+  const __nv_bfloat16* q_norm_w = nullptr;  // optional per-head RMSNorm weights [D]
+  const __nv_bfloat16* k_norm_w = nullptr;
+  float norm_eps = 1e-6f;
+  __nv_bfloat16* q_out = nullptr;       // [M, Hq*D], row stride ldq
+  int ldq = 0;
+  __nv_bfloat16* k_pool = nullptr;      // [slots, Hkv, D]
+  __nv_bfloat16* v_pool = nullptr;
+  long long pool_row_stride = 0;
+  const long long* slots = nullptr;     // [M] pool row per token (null: row = slot_base + token)
+  long long slot_base = 0;
+};
+cudaError_t rope_kv_launch(const RopeKvArgs& a, cudaStream_t s);
+
+// out[dst_row(m), :] = (lo <= id < hi) ? table[id - lo, :] * scale : 0
+cudaError_t embedding_launch(const long long* ids, int n_ids, const __nv_bfloat16* table, int D,
+                             long long lo, long long hi, float scale, __nv_bfloat16* out, int ldo,
+                             const int* dst_rows, cudaStream_t s);
+
+// pixels [n_img, C, H, W] -> patches [n_img * (H/p) * (W/p), kpad], k = (c, py, px), zero tail
+cudaError_t im2col_launch(const __nv_bfloat16* pix, int n_img, int C, int H, int W, int p,
+                          __nv_bfloat16* out, int kpad, cudaStream_t s);
+
+// y[m, j] = act(x[m, j]) * x[m, I + j]   (x: [M, 2I], split halves; interleaved = pairs)
+cudaError_t gated_act_launch(const __nv_bfloat16* x, __nv_bfloat16* y, int M, int I, int act,
+                             int interleaved, cudaStream_t s);
+
+// x += dt * v (elementwise; x fp32 or bf16, v bf16)
+cudaError_t axpy_launch(void* x, int x_fp32, const __nv_bfloat16* v, float dt, long long n,
+                        cudaStream_t s);
+
+// out = uncond + g * (cond - uncond); optional fused Euler step x += dt * out
+cudaError_t cfg_combine_launch(const __nv_bfloat16* cond, const __nv_bfloat16* uncond, float g,
+                               __nv_bfloat16* out, float* x_fp32, float dt, long long n,
+                               cudaStream_t s);
+
+// dst[rows[i], :] = src[i, :]   (row scatter of 16-byte aligned rows)
+cudaError_t scatter_rows_launch(const __nv_bfloat16* src, int n, int D, int lds,
+                                __nv_bfloat16* dst, int ldd, const int* rows, cudaStream_t s);
+
+// e4m3 quantisation: per row (block = 0) or per 1 x 128 block; scale = amax / 448
+cudaError_t quant_fp8_launch(const __nv_bfloat16* x, int rows, int D, int ldx, uint8_t* y,
+                             float* scale, int block, cudaStream_t s);
+
+// gelu / silu / snake elementwise
+cudaError_t unary_launch(const __nv_bfloat16* x, __nv_bfloat16* y, long long n, int act,
+                         cudaStream_t s);
+
+}  // namespace pb

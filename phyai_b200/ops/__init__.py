@@ -1,0 +1,197 @@
+"""Python face of the sm_100a kernels in ``phyai_b200/csrc``.
+
+Every function here launches exactly one hand-written CUDA kernel on the current
+stream and allocates nothing unless the caller leaves ``out=None``. The module
+refuses to work without the compiled extension: there is no eager fallback on a
+GPU, so a missing build fails loudly instead of silently running PyTorch ops.
+``phyai_b200.ops.ref`` holds plain PyTorch fp32 restatements of the same ops,
+used by the tests and by the CPU execution path.
+"""
+
+from __future__ import annotations
+
+import importlib
+from typing import Optional
+
+import torch
+
+from . import ref  # noqa: F401
+
+ACT = {"none": 0, None: 0, "gelu_tanh": 1, "gelu_pytorch_tanh": 1, "silu": 2, "swish": 2,
+       "gelu": 3, "gelu_erf": 3}
+NORM = {"rms": 0, "gemma_rms": 1, "layer": 2, "ada_rms": 3, "rms_noweight": 4}
+
+_ext = None
+
+
+def ext():
+    """The compiled extension module; raises with build instructions if absent."""
+    global _ext
+    if _ext is None:
+        try:
+            _ext = importlib.import_module("phyai_b200._C")
+        except ImportError as e:  # pragma: no cover - exercised only on a broken install
+            raise RuntimeError(
+                "phyai_b200._C is not built; run `python -m phyai_b200.build_ext` "
+                "(needs nvcc with sm_100a support)."
+            ) from e
+    return _ext
+
+
+def available() -> bool:
+    """True when the extension is importable and a CUDA device is visible."""
+    if not torch.cuda.is_available():
+        return False
+    try:
+        ext()
+    except RuntimeError:
+        return False
+    return True
+
+
+def kernel_status() -> int:
+    """Read and clear the device status word (0 = no kernel gave up on a wait)."""
+    return ext().kernel_status()
+
+
+def launch_counter() -> int:
+    return ext().launch_counter()
+
+
+def reset_launch_counter() -> None:
+    ext().reset_launch_counter()
+
+
+def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *,
+         bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+         res_mod: int = 0, col_gate: Optional[torch.Tensor] = None,
+         row_scale: Optional[torch.Tensor] = None, sumsq: Optional[torch.Tensor] = None,
+         act: str | None = "none", glu: bool = False, out_dtype: torch.dtype = torch.bfloat16,
+         a_scale: Optional[torch.Tensor] = None, w_scale: Optional[torch.Tensor] = None,
+         force_bn: int = 0, force_swap: int = -1, force_splits: int = 0) -> torch.Tensor:
+    """``out = epilogue(x @ w.T)`` on tcgen05 tensor cores (see ``csrc/gemm.cuh``).
+
+    ``x`` is ``(M, K)``, ``w`` is ``(N, K)`` (the ``nn.Linear`` layout), both bf16 or
+    both float8_e4m3fn (then ``a_scale`` (M,) and ``w_scale`` (N,) dequantise). With
+    ``glu=True`` the rows of ``w`` interleave gate and up (row ``2j`` = gate ``j``,
+    row ``2j+1`` = up ``j``) and the output has ``N/2`` columns.
+    """
+    M, N = x.shape[0], w.shape[0]
+    if out is None:
+        out = torch.empty((M, N // 2 if glu else N), dtype=out_dtype, device=x.device)
+    ext().gemm(x, w, out, bias, residual, res_mod, col_gate, row_scale, sumsq, ACT[act], glu,
+               a_scale, w_scale, force_bn, force_swap, force_splits)
+    return out
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[torch.Tensor],
+              q_start: torch.Tensor, q_len: torch.Tensor, kv_indptr: torch.Tensor,
+              kv_len: torch.Tensor, *, kv_indices: Optional[torch.Tensor] = None,
+              max_q_len: int, causal: bool = False, splits: int = 1,
+              sm_scale: Optional[float] = None) -> torch.Tensor:
+    """Ragged / paged attention (see ``csrc/attention.cuh``).
+
+    ``q`` ``(tokens, Hq, D)``; ``k``/``v`` ``(rows, Hkv, D)`` pools; sequence ``b`` owns
+    query tokens ``q_start[b] + [0, q_len[b])`` and KV entries ``kv_indptr[b] +
+    [0, kv_len[b])``, mapped to pool rows through ``kv_indices`` when given.
+    """
+    if out is None:
+        out = torch.empty_like(q)
+    if sm_scale is None:
+        sm_scale = q.shape[-1] ** -0.5
+    ext().attention(q, k, v, out, q_start, q_len, kv_indptr, kv_len, kv_indices, max_q_len,
+                    causal, splits, sm_scale)
+    return out
+
+
+def norm(x: torch.Tensor, mode: str, *, weight: Optional[torch.Tensor] = None,
+         bias: Optional[torch.Tensor] = None, mod: Optional[torch.Tensor] = None,
+         group: int = 1, residual: Optional[torch.Tensor] = None,
+         sumsq: Optional[torch.Tensor] = None, eps: float = 1e-6,
+         out: Optional[torch.Tensor] = None, y8: Optional[torch.Tensor] = None,
+         y8_scale: Optional[torch.Tensor] = None, y8_block: int = 0) -> torch.Tensor:
+    """Row norms: ``rms`` / ``gemma_rms`` ((1+w)) / ``layer`` / ``ada_rms``.
+
+    With ``residual`` the kernel first does ``residual += x`` in place and norms the
+    sum. ``ada_rms`` reads ``mod`` rows ``(scale | shift | gate)`` shared by ``group``
+    consecutive rows. ``y8`` additionally emits an e4m3 copy with scales.
+    """
+    if out is None:
+        out = torch.empty_like(x)
+    ext().norm(x, out, NORM[mode], weight, bias, mod, group, residual, sumsq, eps, y8, y8_scale,
+               y8_block)
+    return out
+
+
+def rope_kv(qkv: torch.Tensor, Hq: int, Hkv: int, D: int, q_out: torch.Tensor, *,
+            pos: Optional[torch.Tensor] = None, cos_sin: Optional[torch.Tensor] = None,
+            rot_dim: int = 0, q_norm_w: Optional[torch.Tensor] = None,
+            k_norm_w: Optional[torch.Tensor] = None, norm_eps: float = 1e-6,
+            k_pool: Optional[torch.Tensor] = None, v_pool: Optional[torch.Tensor] = None,
+            slots: Optional[torch.Tensor] = None, slot_base: int = 0) -> torch.Tensor:
+    """Split fused qkv rows, optional per-head RMSNorm, rotate q/k, scatter k/v to the pool."""
+    ext().rope_kv(qkv, Hq, Hkv, D, pos, cos_sin, rot_dim, q_norm_w, k_norm_w, norm_eps, q_out,
+                  k_pool, v_pool, slots, slot_base)
+    return q_out
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, *, lo: int = 0,
+              hi: Optional[int] = None, scale: float = 1.0,
+              dst_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Masked (vocab-range) embedding lookup with scale; rows can be scattered."""
+    if hi is None:
+        hi = lo + table.shape[0]
+    ext().embedding(ids, table, lo, hi, scale, out, dst_rows)
+    return out
+
+
+def im2col(pix: torch.Tensor, patch: int, out: torch.Tensor) -> torch.Tensor:
+    ext().im2col(pix, patch, out)
+    return out
+
+
+def gated_act(x: torch.Tensor, act: str, *, interleaved: bool = False,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    if out is None:
+        out = torch.empty(*x.shape[:-1], x.shape[-1] // 2, dtype=x.dtype, device=x.device)
+    ext().gated_act(x, out, ACT[act], interleaved)
+    return out
+
+
+def unary(x: torch.Tensor, act: str, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    if out is None:
+        out = torch.empty_like(x)
+    ext().unary(x, out, ACT[act])
+    return out
+
+
+def axpy(x: torch.Tensor, v: torch.Tensor, dt: float) -> torch.Tensor:
+    """In place ``x += dt * v`` (the Euler flow-matching update)."""
+    ext().axpy(x, v, dt)
+    return x
+
+
+def cfg_combine(cond: torch.Tensor, uncond: torch.Tensor, g: float, *,
+                out: Optional[torch.Tensor] = None, x_fp32: Optional[torch.Tensor] = None,
+                dt: float = 0.0) -> Optional[torch.Tensor]:
+    """``uncond + g (cond - uncond)``, optionally fused with ``x += dt * v``."""
+    if out is None and x_fp32 is None:
+        out = torch.empty_like(cond)
+    ext().cfg_combine(cond, uncond, g, out, x_fp32, dt)
+    return out
+
+
+def scatter_rows(src: torch.Tensor, dst: torch.Tensor,
+                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    ext().scatter_rows(src, dst, rows)
+    return dst
+
+
+def quant_fp8(x: torch.Tensor, block: int = 0):
+    """e4m3 quantisation of bf16 rows: per-row scales, or per 1x128 block (block=128)."""
+    y = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
+    n = x.shape[1] // 128 if block else 1
+    scale = torch.empty((x.shape[0], n) if block else (x.shape[0],), dtype=torch.float32,
+                        device=x.device)
+    ext().quant_fp8(x, y, scale, block)
+    return y, scale
