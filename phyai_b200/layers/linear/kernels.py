@@ -1,0 +1,198 @@
+"""Linear kernel providers, registry and per-shape dispatcher.
+
+A kernel declares the spec ids it can run, the minimum SM it needs and whether it
+is CUDA-graph capturable. The registry prefers kernels per ``(spec_id, regime)``
+where the regime is ``"decode"`` for M <= 4 and ``"prefill"`` otherwise; the
+dispatcher caches the choice per M bucket. SM support is checked when a kernel is
+selected, not when a layer is built, so a config can be constructed anywhere.
+
+Reference: phyai/src/phyai/layers/linear/{backend,registry,dispatch,__init__}.py and
+backends/{flashinfer,torch}.py. The CUDA provider here is this repository's tcgen05
+GEMM (``phyai_b200.ops.gemm``) instead of FlashInfer / cuBLAS.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Iterable, Protocol
+
+import torch
+import torch.nn.functional as F
+
+from ... import ops
+from ...engine_config import get_engine_config
+from ...utils.cuda import sm_arch
+from ..quant.scheme import Granularity
+
+
+@dataclass(frozen=True)
+class KernelProbe:
+    spec_id: str
+    M: int
+    N: int
+    K: int
+    in_dtype: torch.dtype
+    out_dtype: torch.dtype
+    device_type: str = "cuda"
+    capturing: bool = False
+
+    @property
+    def regime(self) -> str:
+        return "decode" if self.M <= 4 else "prefill"
+
+
+class LinearKernel(Protocol):
+    name: str
+    specs: frozenset[str]
+    min_sm: int
+    device_types: frozenset[str]
+
+    def supports_capture(self) -> bool: ...
+
+    def apply(self, layer, x: torch.Tensor, bias: torch.Tensor | None) -> torch.Tensor: ...
+
+
+class TorchKernel:
+    """Plain PyTorch: ``F.linear`` for bf16/fp16/fp32, dequantise + matmul for quantised specs."""
+
+    name = "torch"
+    specs = frozenset({"bf16", "fp16", "fp8_per_tensor", "fp8_per_channel", "fp8_block_128_128", "nvfp4_block_16"})
+    min_sm = 0
+    device_types = frozenset({"cpu", "cuda"})
+
+    def supports_capture(self) -> bool:
+        return True
+
+    def apply(self, layer, x, bias):
+        if layer.spec.spec_id in ("bf16", "fp16"):
+            return F.linear(x, layer.weight, bias)
+        return layer.spec.reference_apply(layer, x, bias)
+
+
+class B200Kernel:
+    """tcgen05 GEMM with fused bias; fp8 specs quantise the activation with the CUDA quant kernel."""
+
+    name = "b200"
+    specs = frozenset({"bf16", "fp8_per_tensor", "fp8_per_channel", "fp8_block_128_128"})
+    min_sm = 100
+    device_types = frozenset({"cuda"})
+
+    def supports_capture(self) -> bool:
+        return True
+
+    def apply(self, layer, x, bias):
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        spec = layer.spec
+        if spec.spec_id == "bf16":
+            if x2.dtype != torch.bfloat16 or x2.shape[1] % 8 or layer.weight.shape[0] % 8:
+                return F.linear(x, layer.weight, bias)
+            y = ops.gemm(x2, layer.weight, bias=bias)
+        elif spec.granularity is Granularity.BLOCK:
+            from ...ops import fp8_block
+
+            q, s = ops.quant_fp8(x2.to(torch.bfloat16), 128)
+            y = fp8_block.gemm_fp8_block(q, s, layer.weight, layer.weight_scale, bias=bias)
+        else:
+            q, s = ops.quant_fp8(x2.to(torch.bfloat16), 0)
+            ws = layer.weight_scale
+            if ws.numel() == 1:
+                ws = ws.expand(layer.weight.shape[0]).contiguous()
+            y = ops.gemm(q, layer.weight, a_scale=s, w_scale=ws, bias=bias)
+        return y.reshape(*lead, -1)
+
+
+class Registry:
+    def __init__(self) -> None:
+        self._kernels: list[LinearKernel] = []
+        self._prefer: dict[tuple[str, str], list[str]] = {}
+
+    def register(self, kernel: LinearKernel, *, prefer_for: Iterable[tuple[str, str]] = ()) -> None:
+        if any(k.name == kernel.name for k in self._kernels):
+            raise ValueError(f"linear kernel {kernel.name!r} already registered")
+        self._kernels.append(kernel)
+        for key in prefer_for:
+            self._prefer.setdefault(key, []).append(kernel.name)
+
+    def names(self) -> list[str]:
+        return [k.name for k in self._kernels]
+
+    def candidates(self, probe: KernelProbe, sm: int) -> list[LinearKernel]:
+        ok = [k for k in self._kernels
+              if probe.spec_id in k.specs and probe.device_type in k.device_types
+              and (probe.device_type != "cuda" or sm >= k.min_sm)
+              and (not probe.capturing or k.supports_capture())]
+        pref = self._prefer.get((probe.spec_id, probe.regime), [])
+        ok.sort(key=lambda k: pref.index(k.name) if k.name in pref else len(pref))
+        return ok
+
+    def validate(self) -> None:
+        if not self._kernels:
+            raise RuntimeError("no linear kernel registered")
+
+    def supported_specs_for_sm(self, sm: int, device_type: str = "cuda") -> set[str]:
+        out: set[str] = set()
+        for k in self._kernels:
+            if device_type in k.device_types and (device_type != "cuda" or sm >= k.min_sm):
+                out |= set(k.specs)
+        return out
+
+
+class Dispatcher:
+    def __init__(self, registry: Registry, forced: str | None = None) -> None:
+        self.registry = registry
+        self.forced = forced
+        self._cache: dict[tuple, LinearKernel] = {}
+
+    def select(self, *, spec_id: str, M: int, N: int, K: int, in_dtype: torch.dtype, out_dtype: torch.dtype,
+               device_type: str = "cuda", capturing: bool = False) -> LinearKernel:
+        key = (spec_id, max(M, 1).bit_length(), N, K, in_dtype, out_dtype, device_type, capturing)
+        hit = self._cache.get(key)
+        if hit is not None:
+            return hit
+        probe = KernelProbe(spec_id, M, N, K, in_dtype, out_dtype, device_type, capturing)
+        sm = sm_arch() if device_type == "cuda" else 0
+        cands = self.registry.candidates(probe, sm)
+        if self.forced is not None:
+            cands = [k for k in cands if k.name == self.forced]
+        if not cands:
+            raise RuntimeError(
+                f"no linear kernel for spec {spec_id!r} on {device_type} sm_{sm} (M={M}, N={N}, K={K}, "
+                f"regime={probe.regime}, forced={self.forced!r}); registered: {self.registry.names()}")
+        self._cache[key] = cands[0]
+        return cands[0]
+
+
+_DISPATCHER: Dispatcher | None = None
+
+
+def init(force: str | None = None) -> Dispatcher:
+    """Register the kernels for this process and install the dispatcher."""
+    global _DISPATCHER
+    cfg = get_engine_config()
+    reg = Registry()
+    b200_pref = [(s, r) for s in B200Kernel.specs for r in ("decode", "prefill")]
+    reg.register(B200Kernel(), prefer_for=b200_pref)
+    reg.register(TorchKernel())
+    reg.validate()
+    forced = force or cfg.runtime.force_linear_kernel or (
+        cfg.backends.linear if cfg.backends.linear not in (None, "auto") else None)
+    _DISPATCHER = Dispatcher(reg, forced)
+    return _DISPATCHER
+
+
+def get_linear_dispatcher() -> Dispatcher:
+    if _DISPATCHER is None:
+        return init()
+    return _DISPATCHER
+
+
+def _reset_for_test() -> None:
+    global _DISPATCHER
+    _DISPATCHER = None
+
+
+__all__ = ["KernelProbe", "LinearKernel", "TorchKernel", "B200Kernel", "Registry", "Dispatcher", "init",
+           "get_linear_dispatcher"]

@@ -1,0 +1,278 @@
+"""Static execution plan of Pi0.5 on B200: preallocated buffers + a fixed kernel sequence.
+
+A request is three stages, each a straight line of this repository's sm_100a kernels
+(no per-op Python dispatch, no allocation), so the whole request is captured as one
+CUDA graph per prompt-length bucket:
+
+* ``vision``  all cameras of all robots in one batch (the reference runs one robot at a
+  time, phyai/src/phyai/models/pi05/scheduler_ws1_pi05.py:449-462);
+* ``prefix``  18 Gemma blocks over [image | prompt] rows; K/V go straight from the RoPE
+  kernel into the paged pool; the last block stops after its K/V write because nothing
+  reads its output (the reference computes it, scheduler_ws1_pi05.py:505-511);
+* ``expert``  the 10-step Euler loop, 8 kernels per block: AdaRMSNorm, qkv GEMM,
+  RoPE+KV write, joint attention (KV split over a cluster), o-proj GEMM with gated
+  residual epilogue, AdaRMSNorm, gate-up GEMM with GeGLU epilogue, down GEMM with gated
+  residual epilogue (the reference needs ~13, modeling_pi05.py:801-835).
+
+KV pool layout: robot ``b`` owns slots ``1 + b*(P+C) + [0, P)`` for its prefix rows and the
+next ``C`` for its action tokens (``P`` = max prefix rows, ``C`` = chunk). Slot 0 is unused
+padding. Prefix attention reads a contiguous range; joint attention reads through an
+index list that skips the unused tail of the prefix slab.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ... import ops
+from ...cache import KVCachePool
+from .modeling_pi05 import PI05Model
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+@dataclass
+class PI05Layout:
+    """Host-side description of one request shape."""
+
+    batch: int
+    lang_lens: tuple[int, ...]
+    lang_bucket: int
+
+
+class PI05Plan:
+    def __init__(self, model: PI05Model, *, max_batch_size: int = 1, num_images: int = 3,
+                 device: torch.device | str = "cuda") -> None:
+        cfg = model.config
+        self.model, self.cfg = model, cfg
+        self.device = torch.device(device)
+        self.B, self.n_img = max_batch_size, num_images
+        dt = torch.bfloat16
+        if model.params_dtype != dt or model.vision.compute_dtype != dt:
+            raise ValueError("PI05Plan runs bf16 weights; use the eager path for other dtypes")
+        v, t, e = cfg.vision, cfg.text, cfg.expert
+        self.img_tokens = v.num_patches * num_images
+        self.P = self.img_tokens + cfg.tokenizer_max_length          # max prefix rows per robot
+        self.C = cfg.chunk_size
+        self.slab = self.P + self.C
+        dev = self.device
+        B = self.B
+
+        def buf(*shape, dtype=dt):
+            return torch.zeros(*shape, dtype=dtype, device=dev)
+
+        # ---------------- weights prepared for the kernels
+        kp = _round_up(v.num_channels * v.patch_size ** 2, 8)
+        self.patch_k = kp
+        w = model.vision.patch_weight.reshape(v.hidden_size, -1)
+        self.patch_w = torch.zeros(v.hidden_size, kp, dtype=dt, device=dev)
+        self.patch_w[:, : w.shape[1]].copy_(w)
+        self.cos_sin = model.rope.cos_sin_cache.to(dev, torch.float32).contiguous()
+
+        # ---------------- vision buffers
+        Mv = B * self.img_tokens
+        self.Mv = Mv
+        self.pixels = buf(B * num_images, v.num_channels, v.image_size, v.image_size)
+        self.v_cols = buf(Mv, kp)
+        self.v_h = buf(Mv, v.hidden_size)
+        self.v_x = buf(Mv, v.hidden_size)
+        self.v_qkv = buf(Mv, 3 * v.hidden_size)
+        self.v_attn = buf(Mv, v.hidden_size)
+        self.v_mlp = buf(Mv, v.intermediate_size)
+        n_seq = B * num_images
+        ar = torch.arange(n_seq, dtype=torch.int32, device=dev)
+        self.v_qstart = ar * v.num_patches
+        self.v_qlen = torch.full((n_seq,), v.num_patches, dtype=torch.int32, device=dev)
+
+        # ---------------- prefix buffers (sized for the largest bucket)
+        Mp = B * self.P
+        H = t.hidden_size
+        qkv_w = (t.num_attention_heads + 2 * t.num_key_value_heads) * t.head_dim
+        self.p_h = buf(Mp, H)
+        self.p_x = buf(Mp, H)
+        self.p_qkv = buf(Mp, qkv_w)
+        self.p_q = buf(Mp, t.num_attention_heads * t.head_dim)
+        self.p_attn = buf(Mp, t.num_attention_heads * t.head_dim)
+        self.p_act = buf(Mp, t.intermediate_size)
+        self.input_ids = torch.zeros(B, cfg.tokenizer_max_length, dtype=torch.int64, device=dev)
+        self.pool = KVCachePool(cfg.num_layers, 1 + B * self.slab, t.num_key_value_heads, t.head_dim, dtype=dt, device=dev)
+        # per-bucket metadata (filled by set_layout)
+        self.p_pos = torch.zeros(Mp, dtype=torch.int32, device=dev)
+        self.p_slots = torch.zeros(Mp, dtype=torch.int64, device=dev)
+        self.p_qstart = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.p_qlen = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.p_kvptr = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.p_kvlen = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.lang_rows = torch.full((B * cfg.tokenizer_max_length,), -1, dtype=torch.int32, device=dev)
+
+        # ---------------- expert buffers
+        Me = B * self.C
+        He = e.hidden_size
+        self.Me = Me
+        self.x_t = buf(Me, cfg.max_action_dim)
+        self.noise = buf(B, self.C, cfg.max_action_dim)
+        self.e_h = buf(Me, He)
+        self.e_x = buf(Me, He)
+        self.e_qkv = buf(Me, qkv_w)
+        self.e_q = buf(Me, t.num_attention_heads * t.head_dim)
+        self.e_attn = buf(Me, t.num_attention_heads * t.head_dim)
+        self.e_act = buf(Me, e.intermediate_size)
+        self.e_v = buf(Me, cfg.max_action_dim)
+        self.e_pos = torch.zeros(Me, dtype=torch.int32, device=dev)
+        self.e_slots = torch.zeros(Me, dtype=torch.int64, device=dev)
+        self.e_qstart = torch.arange(B, dtype=torch.int32, device=dev) * self.C
+        self.e_qlen = torch.full((B,), self.C, dtype=torch.int32, device=dev)
+        self.e_kvptr = torch.arange(B, dtype=torch.int32, device=dev) * self.slab
+        self.e_kvlen = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.e_kvidx = torch.zeros(B * self.slab, dtype=torch.int32, device=dev)
+        self.out = buf(B, self.C, cfg.max_action_dim)
+        self.mod_in: list[torch.Tensor] = []
+        self.mod_post: list[torch.Tensor] = []
+        self.mod_final: torch.Tensor | None = None
+        self.dt = -1.0 / cfg.num_inference_steps
+        self.expert_splits = 8
+        self._layout_key = None
+
+    # ------------------------------------------------------------------ setup
+    @torch.no_grad()
+    def build_modulation_tables(self) -> None:
+        """AdaRMS (scale|shift|gate) rows for every norm and Euler step; call after weights are loaded."""
+        cfg = self.cfg
+        N = cfg.num_inference_steps
+        ts = 1.0 + torch.arange(N, dtype=torch.float32, device=self.device) * self.dt
+        conds = self.model.heads.embed_time(ts).contiguous()
+        stack = self.model.expert_stack
+        self.mod_in = [l.input_layernorm.project_modulation(conds) for l in stack.layers]
+        self.mod_post = [l.post_attention_layernorm.project_modulation(conds) for l in stack.layers]
+        self.mod_final = stack.norm.project_modulation(conds)
+
+    def set_layout(self, layout: PI05Layout) -> bool:
+        """Write the metadata of a request shape into the static buffers. Returns True if it changed."""
+        key = (layout.batch, layout.lang_lens, layout.lang_bucket)
+        if key == self._layout_key:
+            return False
+        cfg, B, dev = self.cfg, self.B, self.device
+        n_per = self.img_tokens + layout.lang_bucket
+        real = [self.img_tokens + l for l in layout.lang_lens] + [0] * (B - layout.batch)
+        base = [1 + b * self.slab for b in range(B)]
+        j = torch.arange(n_per, dtype=torch.int64)
+        pos = j.repeat(B)
+        slots = torch.cat([base[b] + j for b in range(B)])
+        Mp = B * n_per
+        self.p_pos[:Mp].copy_(pos.to(torch.int32))
+        self.p_slots[:Mp].copy_(slots)
+        self.p_qstart.copy_(torch.arange(B, dtype=torch.int32) * n_per)
+        self.p_qlen.fill_(n_per)
+        self.p_kvptr.copy_(torch.tensor(base, dtype=torch.int32))
+        self.p_kvlen.copy_(torch.tensor(real, dtype=torch.int32))
+        L = cfg.tokenizer_max_length
+        rows = torch.full((B, L), -1, dtype=torch.int32)
+        for b in range(B):
+            rows[b, : layout.lang_bucket] = b * n_per + self.img_tokens + torch.arange(layout.lang_bucket, dtype=torch.int32)
+        self.lang_rows.copy_(rows.flatten())
+        c = torch.arange(self.C, dtype=torch.int64)
+        self.e_pos.copy_(torch.cat([real[b] + c for b in range(B)]).to(torch.int32))
+        self.e_slots.copy_(torch.cat([base[b] + self.P + c for b in range(B)]))
+        self.e_kvlen.copy_(torch.tensor([r + self.C for r in real], dtype=torch.int32))
+        idx = torch.zeros(B, self.slab, dtype=torch.int32)
+        for b in range(B):
+            r = real[b]
+            idx[b, :r] = base[b] + torch.arange(r, dtype=torch.int32)
+            idx[b, r:r + self.C] = base[b] + self.P + torch.arange(self.C, dtype=torch.int32)
+        self.e_kvidx.copy_(idx.flatten())
+        self._layout_key = key
+        return True
+
+    # ----------------------------------------------------------------- stages
+    def vision(self) -> None:
+        cfg, v, m = self.cfg, self.cfg.vision, self.model.vision
+        ops.im2col(self.pixels, v.patch_size, self.v_cols)
+        ops.gemm(self.v_cols, self.patch_w, self.v_h, bias=m.patch_bias, residual=m.position_embedding,
+                 res_mod=v.num_patches)
+        H, hd, nh = v.hidden_size, v.head_dim, v.num_attention_heads
+        q3 = self.v_qkv[:, :H].unflatten(1, (nh, hd))
+        k3 = self.v_qkv[:, H:2 * H].unflatten(1, (nh, hd))
+        v3 = self.v_qkv[:, 2 * H:].unflatten(1, (nh, hd))
+        a3 = self.v_attn.unflatten(1, (nh, hd))
+        for blk in m.blocks:
+            ops.norm(self.v_h, "layer", weight=blk.ln1.weight, bias=blk.ln1.bias, eps=v.layer_norm_eps, out=self.v_x)
+            ops.gemm(self.v_x, blk.qkv.weight, self.v_qkv, bias=blk.qkv.bias)
+            ops.attention(q3, k3, v3, a3, self.v_qstart, self.v_qlen, self.v_qstart, self.v_qlen,
+                          max_q_len=v.num_patches, sm_scale=hd ** -0.5)
+            ops.gemm(self.v_attn, blk.out.weight, self.v_h, bias=blk.out.bias, residual=self.v_h)
+            ops.norm(self.v_h, "layer", weight=blk.ln2.weight, bias=blk.ln2.bias, eps=v.layer_norm_eps, out=self.v_x)
+            ops.gemm(self.v_x, blk.fc1.weight, self.v_mlp, bias=blk.fc1.bias, act="gelu_tanh")
+            ops.gemm(self.v_mlp, blk.fc2.weight, self.v_h, bias=blk.fc2.bias, residual=self.v_h)
+        ops.norm(self.v_h, "layer", weight=m.post_layernorm.weight, bias=m.post_layernorm.bias,
+                 eps=v.layer_norm_eps, out=self.v_x)
+
+    def prefix(self, lang_bucket: int) -> None:
+        cfg, t, lm = self.cfg, self.cfg.text, self.model.paligemma_lm
+        n_per = self.img_tokens + lang_bucket
+        Mp = self.B * n_per
+        h, x = self.p_h[:Mp], self.p_x[:Mp]
+        # image rows: projector output lands directly in the packed prefix rows of each robot
+        proj = self.model.vision.projector
+        for b in range(self.B):
+            ops.gemm(self.v_x[b * self.img_tokens:(b + 1) * self.img_tokens], proj.weight,
+                     h[b * n_per: b * n_per + self.img_tokens], bias=proj.bias)
+        ops.embedding(self.input_ids.view(-1), lm.embed_tokens, h, scale=lm.embed_scale, dst_rows=self.lang_rows)
+        Hq, Hkv, D = t.num_attention_heads, t.num_key_value_heads, t.head_dim
+        qkv, q, attn, act = self.p_qkv[:Mp], self.p_q[:Mp], self.p_attn[:Mp], self.p_act[:Mp]
+        q3, a3 = q.unflatten(1, (Hq, D)), attn.unflatten(1, (Hq, D))
+        last = len(lm.layers) - 1
+        for li, layer in enumerate(lm.layers):
+            kpool, vpool = self.pool.layer(li)
+            ops.norm(h, "gemma_rms", weight=layer.input_layernorm.weight, eps=t.rms_norm_eps, out=x)
+            ops.gemm(x, layer.attn.qkv.weight, qkv)
+            ops.rope_kv(qkv, Hq, Hkv, D, q, pos=self.p_pos[:Mp], cos_sin=self.cos_sin, k_pool=kpool, v_pool=vpool,
+                        slots=self.p_slots[:Mp])
+            if li == last:
+                break  # only this block's K/V are consumed downstream
+            ops.attention(q3, kpool, vpool, a3, self.p_qstart, self.p_qlen, self.p_kvptr, self.p_kvlen,
+                          max_q_len=n_per, sm_scale=D ** -0.5)
+            ops.gemm(attn, layer.attn.o.weight, h, residual=h)
+            ops.norm(h, "gemma_rms", weight=layer.post_attention_layernorm.weight, eps=t.rms_norm_eps, out=x)
+            ops.gemm(x, layer.mlp.gate_up.weight, act, act="gelu_tanh", glu=True)
+            ops.gemm(act, layer.mlp.down.weight, h, residual=h)
+
+    def expert(self) -> None:
+        cfg, e, t = self.cfg, self.cfg.expert, self.cfg.text
+        heads, stack = self.model.heads, self.model.expert_stack
+        Hq, Hkv, D, He, Me = t.num_attention_heads, t.num_key_value_heads, t.head_dim, e.hidden_size, self.Me
+        h, x = self.e_h, self.e_x
+        q3, a3 = self.e_q.unflatten(1, (Hq, D)), self.e_attn.unflatten(1, (Hq, D))
+        self.x_t.copy_(self.noise.view(Me, -1))
+        for i in range(cfg.num_inference_steps):
+            ops.gemm(self.x_t, heads.action_in_proj.weight, h, bias=heads.action_in_proj.bias)
+            for li, layer in enumerate(stack.layers):
+                kpool, vpool = self.pool.layer(li)
+                m_in, m_post = self.mod_in[li][i:i + 1], self.mod_post[li][i:i + 1]
+                ops.norm(h, "ada_rms", mod=m_in, group=Me, eps=e.rms_norm_eps, out=x)
+                ops.gemm(x, layer.attn.qkv.weight, self.e_qkv)
+                ops.rope_kv(self.e_qkv, Hq, Hkv, D, self.e_q, pos=self.e_pos, cos_sin=self.cos_sin, k_pool=kpool,
+                            v_pool=vpool, slots=self.e_slots)
+                ops.attention(q3, kpool, vpool, a3, self.e_qstart, self.e_qlen, self.e_kvptr, self.e_kvlen,
+                              kv_indices=self.e_kvidx, max_q_len=self.C, splits=self.expert_splits, sm_scale=D ** -0.5)
+                ops.gemm(self.e_attn, layer.attn.o.weight, h, residual=h, col_gate=m_in[0, 2 * He:])
+                ops.norm(h, "ada_rms", mod=m_post, group=Me, eps=e.rms_norm_eps, out=x)
+                ops.gemm(x, layer.mlp.gate_up.weight, self.e_act, act="gelu_tanh", glu=True)
+                ops.gemm(self.e_act, layer.mlp.down.weight, h, residual=h, col_gate=m_post[0, 2 * He:])
+            ops.norm(h, "ada_rms", mod=self.mod_final[i:i + 1], group=Me, eps=e.rms_norm_eps, out=x)
+            ops.gemm(x, heads.action_out_proj.weight, self.e_v, bias=heads.action_out_proj.bias)
+            ops.axpy(self.x_t, self.e_v, self.dt)
+        self.out.view(Me, -1).copy_(self.x_t)
+
+    def run(self, lang_bucket: int) -> torch.Tensor:
+        """The whole request; inputs are ``pixels``, ``input_ids``, ``noise``; result in ``out``."""
+        self.vision()
+        self.prefix(lang_bucket)
+        self.expert()
+        return self.out
+
+
+__all__ = ["PI05Plan", "PI05Layout"]

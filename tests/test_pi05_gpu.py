@@ -1,0 +1,54 @@
+"""Pi0.5 on a GPU: the CUDA execution plan against the eager fp32-softmax oracle."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _mid_config():
+    from phyai_b200.models.pi05.configuration_pi05 import (GemmaExpertConfig, PaliGemmaTextConfig, PI05Config,
+                                                           SiglipVisionConfig)
+
+    return PI05Config(
+        vision=SiglipVisionConfig(hidden_size=144, num_hidden_layers=2, num_attention_heads=2, intermediate_size=304,
+                                  image_size=56, patch_size=14, projection_dim=256),
+        text=PaliGemmaTextConfig(hidden_size=256, num_hidden_layers=3, num_attention_heads=8, num_key_value_heads=1,
+                                 head_dim=256, intermediate_size=512, vocab_size=1024),
+        expert=GemmaExpertConfig(hidden_size=128, num_hidden_layers=3, num_attention_heads=8, num_key_value_heads=1,
+                                 head_dim=256, intermediate_size=256, adarms_cond_dim=128),
+        chunk_size=50, max_action_dim=32, num_inference_steps=4, tokenizer_max_length=48)
+
+
+@pytest.mark.parametrize("batch,graph", [(1, True), (2, True), (2, False)])
+def test_plan_matches_eager(batch, graph):
+    from phyai_b200 import ops
+    from phyai_b200.engine import Engine, EngineArgs
+    from phyai_b200.engine_config import DeviceConfig, EngineConfig, RuntimeConfig
+    from phyai_b200.models.pi05.main_pi05 import PI05Args
+    from phyai_b200.models.pi05.scheduler_ws1_pi05 import PI05Request
+
+    cfg = _mid_config()
+    eng = Engine(EngineArgs("pi05", PI05Args(config=cfg, max_batch_size=2, inputs_image_shape=[[56, 56, 3]] * 2),
+                            EngineConfig(device=DeviceConfig("cuda:0", torch.bfloat16),
+                                         runtime=RuntimeConfig(use_cuda_graph=graph))))
+    g = torch.Generator().manual_seed(batch)
+    lens = torch.tensor([40, 7][:batch])
+    req = PI05Request((torch.rand(batch, 2, 3, 56, 56, generator=g) * 2 - 1).bfloat16().cuda(),
+                      torch.randint(0, 1024, (batch, 48), generator=g).cuda(), lens.cuda(),
+                      torch.randn(batch, 50, 32, generator=g).bfloat16().cuda())
+    out = eng.step(req)
+    out_again = eng.step(req)
+    torch.cuda.synchronize()
+    assert ops.kernel_status() == 0
+    ref = eng.entry.model.sample_actions(req.pixel_values, req.input_ids, lens, req.noise)
+    rel = (out.float() - ref.float()).abs().max() / ref.float().abs().max()
+    assert torch.equal(out, out_again)
+    assert rel < 5e-2, rel
+    # a different prompt length re-plans the metadata without re-capturing anything it should not
+    req2 = PI05Request(req.pixel_values, req.input_ids, torch.tensor([12, 30][:batch]).cuda(), req.noise)
+    out2 = eng.step(req2)
+    ref2 = eng.entry.model.sample_actions(req2.pixel_values, req2.input_ids, req2.lang_lens.cpu(), req2.noise)
+    rel2 = (out2.float() - ref2.float()).abs().max() / ref2.float().abs().max()
+    assert rel2 < 5e-2, rel2
+    eng.close()
