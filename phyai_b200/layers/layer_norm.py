@@ -12,7 +12,7 @@ import torch
 import torch.nn as nn
 
 from .. import ops
-from ..engine_config import resolve_engine_defaults
+from ..engine_config import get_engine_config, resolve_engine_defaults
 from ..ops import ref
 from .linear import ReplicatedLinear
 
@@ -28,6 +28,7 @@ class RMSNorm(nn.Module):
                  dtype: torch.dtype | None = None, device=None, prefix: str = "") -> None:
         super().__init__()
         dtype, _, backend = resolve_engine_defaults(dtype, None, backend)
+        device = device if device is not None else get_engine_config().device.target
         self.hidden_size, self.variance_epsilon, self.backend, self.prefix = hidden_size, eps, backend, prefix
         init = torch.zeros if self.gemma else torch.ones
         self.weight = nn.Parameter(init(hidden_size, dtype=dtype, device=device), requires_grad=False)
@@ -58,6 +59,7 @@ class LayerNorm(nn.Module):
                  dtype: torch.dtype | None = None, device=None, prefix: str = "") -> None:
         super().__init__()
         dtype, _, backend = resolve_engine_defaults(dtype, None, backend)
+        device = device if device is not None else get_engine_config().device.target
         self.hidden_size, self.eps, self.backend, self.prefix = hidden_size, eps, backend, prefix
         self.weight = nn.Parameter(torch.ones(hidden_size, dtype=dtype, device=device), requires_grad=False)
         self.bias = nn.Parameter(torch.zeros(hidden_size, dtype=dtype, device=device), requires_grad=False)

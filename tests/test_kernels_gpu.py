@@ -1,0 +1,238 @@
+"""Numerics of the sm_100a kernels against plain PyTorch fp32 restatements of the same ops."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+TOL = 2e-2  # bf16 outputs
+
+
+def relerr(a, b):
+    a, b = a.float(), b.float()
+    return float((a - b).abs().max() / (b.abs().max() + 1e-6))
+
+
+def _status_ok():
+    from phyai_b200 import ops
+
+    torch.cuda.synchronize()
+    assert ops.kernel_status() == 0
+
+
+GEMM_CASES = [
+    dict(M=128, N=128, K=64, force_swap=0, force_bn=128, force_splits=1),
+    dict(M=256, N=256, K=512, force_swap=0),
+    dict(M=968, N=2560, K=2048),
+    dict(M=968, N=4096, K=2048, glu=True, act="gelu_tanh"),
+    dict(M=968, N=2048, K=2048, residual=True, force_bn=128),
+    dict(M=768, N=4304, K=1152, bias=True, act="gelu_tanh"),
+    dict(M=768, N=1152, K=4304, bias=True, residual=True),
+    dict(M=768, N=1152, K=592, bias=True, residual=True, res_mod=256),
+    dict(M=50, N=2560, K=1024),
+    dict(M=50, N=1024, K=2048, residual=True, col_gate=True),
+    dict(M=50, N=8192, K=1024, glu=True, act="gelu_tanh"),
+    dict(M=50, N=1024, K=4096, residual=True, col_gate=True, force_splits=4),
+    dict(M=50, N=32, K=1024, bias=True),
+    dict(M=50, N=1024, K=32, bias=True),
+    dict(M=1, N=1024, K=1024, bias=True, act="silu"),
+    dict(M=200, N=1024, K=1024, row_scale=True),
+    dict(M=400, N=2048, K=1024, glu=True, act="silu"),
+    dict(M=300, N=512, K=1024, force_swap=0, force_bn=64),
+    dict(M=300, N=512, K=1024, force_swap=0, force_bn=32, out_fp32=True),
+]
+
+
+@pytest.mark.parametrize("case", GEMM_CASES, ids=lambda c: "-".join(f"{k}{v}" for k, v in c.items()))
+def test_gemm(case):
+    from phyai_b200 import ops
+    from phyai_b200.ops import ref
+
+    c = dict(case)
+    M, N, K = c.pop("M"), c.pop("N"), c.pop("K")
+    g = torch.Generator(device=DEV).manual_seed(M + N + K)
+    x = (torch.randn(M, K, device=DEV, generator=g) * 0.5).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).bfloat16()
+    glu, act = c.pop("glu", False), c.pop("act", "none")
+    No = N // 2 if glu else N
+    kw = {}
+    if c.pop("bias", False):
+        kw["bias"] = torch.randn(N, device=DEV, generator=g).bfloat16()
+    res_mod = c.pop("res_mod", 0)
+    if c.pop("residual", False):
+        kw["residual"] = torch.randn(res_mod or M, No, device=DEV, generator=g).bfloat16()
+        kw["res_mod"] = res_mod
+    if c.pop("col_gate", False):
+        kw["col_gate"] = torch.randn(No, device=DEV, generator=g).bfloat16()
+    if c.pop("row_scale", False):
+        kw["row_scale"] = torch.rand(M, device=DEV, generator=g) + 0.5
+    odt = torch.float32 if c.pop("out_fp32", False) else torch.bfloat16
+    out = ops.gemm(x, w, act=act, glu=glu, out_dtype=odt, **kw, **c)
+    _status_ok()
+    exp = ref.gemm(x, w, act=act, glu=glu, out_dtype=odt, **kw)
+    assert relerr(out, exp) < TOL
+
+
+def test_gemm_sumsq_and_determinism():
+    from phyai_b200 import ops
+
+    for M in (50, 968):
+        x = (torch.randn(M, 2048, device=DEV) * 0.5).bfloat16()
+        w = (torch.randn(1024, 2048, device=DEV) * 0.05).bfloat16()
+        ss = torch.zeros(M, device=DEV)
+        o = ops.gemm(x, w, sumsq=ss)
+        o2 = ops.gemm(x, w)
+        _status_ok()
+        assert relerr(ss, o.float().pow(2).sum(-1)) < 1e-4
+        assert torch.equal(o, o2)
+
+
+def test_gemm_rejects_misaligned():
+    from phyai_b200 import ops
+
+    x = torch.randn(16, 68, device=DEV).bfloat16()   # row stride 136 B: not a multiple of 16
+    w = torch.randn(64, 68, device=DEV).bfloat16()
+    with pytest.raises(RuntimeError):
+        ops.gemm(x, w)
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("M", [200, 968])
+def test_gemm_fp8_rowwise(M):
+    from phyai_b200 import ops
+    from phyai_b200.ops import ref
+
+    x = torch.randn(M, 2048, device=DEV).bfloat16()
+    w = (torch.randn(1024, 2048, device=DEV) * 0.05).bfloat16()
+    x8, xs = ops.quant_fp8(x)
+    w8, ws = ops.quant_fp8(w)
+    o = ops.gemm(x8, w8, a_scale=xs, w_scale=ws)
+    _status_ok()
+    assert relerr(o, ref.gemm(x8.float(), w8.float(), a_scale=xs, w_scale=ws)) < TOL
+    assert relerr(o, ref.gemm(x, w)) < 8e-2     # quantisation error itself
+
+
+ATTN_CASES = [
+    dict(B=3, ql=256, kl=256, Hq=16, Hkv=16, D=72),
+    dict(B=1, ql=968, kl=968, Hq=8, Hkv=1, D=256, paged=True),
+    dict(B=1, ql=50, kl=1018, Hq=8, Hkv=1, D=256, paged=True, splits=8),
+    dict(B=2, ql=50, kl=834, Hq=8, Hkv=1, D=256, paged=True, splits=2),
+    dict(B=2, ql=100, kl=100, Hq=8, Hkv=2, D=128, causal=True),
+    dict(B=1, ql=333, kl=500, Hq=4, Hkv=4, D=128, causal=True, splits=2),
+    dict(B=1, ql=10, kl=26, Hq=4, Hkv=1, D=32, paged=True),
+    dict(B=2, ql=64, kl=0, Hq=2, Hkv=2, D=64),
+]
+
+
+@pytest.mark.parametrize("case", ATTN_CASES, ids=lambda c: "-".join(f"{k}{v}" for k, v in c.items()))
+def test_attention(case):
+    from phyai_b200 import ops
+    from phyai_b200.ops import ref
+
+    B, ql, kl, Hq, Hkv, D = (case[k] for k in ("B", "ql", "kl", "Hq", "Hkv", "D"))
+    causal, paged, splits = case.get("causal", False), case.get("paged", False), case.get("splits", 1)
+    q = torch.randn(B * ql, Hq, D, device=DEV).bfloat16()
+    R = B * kl + 7
+    k = torch.randn(R, Hkv, D, device=DEV).bfloat16()
+    v = torch.randn(R, Hkv, D, device=DEV).bfloat16()
+    ar = torch.arange(B, device=DEV, dtype=torch.int32)
+    q_start, q_len = ar * ql, torch.full((B,), ql, device=DEV, dtype=torch.int32)
+    kv_ptr, kv_len = ar * kl, torch.full((B,), kl, device=DEV, dtype=torch.int32)
+    idx = torch.randperm(R, device=DEV)[: B * kl].int() if paged else None
+    o = ops.attention(q, k, v, None, q_start, q_len, kv_ptr, kv_len, kv_indices=idx, max_q_len=ql, causal=causal,
+                      splits=splits)
+    _status_ok()
+    e = ref.attention(q, k, v, q_start.cpu(), q_len.cpu(), kv_ptr.cpu(), kv_len.cpu(), kv_indices=idx, causal=causal)
+    assert relerr(o, e) < TOL if kl else float(o.abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("rows,D", [(50, 1024), (968, 2048), (768, 1152), (7, 4096), (3, 12288)])
+def test_norms(rows, D):
+    from phyai_b200 import ops
+    from phyai_b200.ops import ref
+
+    x = torch.randn(rows, D, device=DEV).bfloat16()
+    w = (torch.randn(D, device=DEV) * 0.1).bfloat16()
+    b = (torch.randn(D, device=DEV) * 0.1).bfloat16()
+    assert relerr(ops.norm(x, "rms", weight=w), ref.rms_norm(x, w)) < TOL
+    assert relerr(ops.norm(x, "gemma_rms", weight=w), ref.rms_norm(x, w, gemma=True)) < TOL
+    assert relerr(ops.norm(x, "layer", weight=w, bias=b), ref.layer_norm(x, w, b)) < TOL
+    mod = (torch.randn(1, 3 * D, device=DEV) * 0.2).bfloat16()
+    assert relerr(ops.norm(x, "ada_rms", mod=mod, group=rows), ref.ada_rms_norm(x, mod)[0]) < TOL
+    modr = (torch.randn(rows, 3 * D, device=DEV) * 0.2).bfloat16()
+    assert relerr(ops.norm(x, "ada_rms", mod=modr, group=1), ref.ada_rms_norm(x, modr)[0]) < TOL
+    r = torch.randn(rows, D, device=DEV).bfloat16()
+    r2 = r.clone()
+    y = ops.norm(x, "gemma_rms", weight=w, residual=r2)
+    h = (x.float() + r.float()).bfloat16()
+    assert relerr(r2, h) < 1e-2 and relerr(y, ref.rms_norm(h, w, gemma=True)) < TOL
+    _status_ok()
+
+
+def test_norm_fp8_outputs():
+    from phyai_b200 import ops
+    from phyai_b200.ops import ref
+
+    x = torch.randn(64, 1024, device=DEV).bfloat16()
+    w = torch.ones(1024, device=DEV).bfloat16()
+    for blk in (0, 128):
+        y8 = torch.empty(64, 1024, device=DEV, dtype=torch.float8_e4m3fn)
+        sc = torch.empty((64, 8) if blk else (64,), device=DEV)
+        y = ops.norm(x, "rms", weight=w, y8=y8, y8_scale=sc, y8_block=blk)
+        q, s = ref.quant_fp8(y, blk)
+        assert relerr(sc, s) < 1e-5 and relerr(y8.float(), q.float()) < 0.07
+
+
+def test_rope_kv_and_small_ops():
+    from phyai_b200 import ops
+    from phyai_b200.ops import ref
+
+    M, Hq, Hkv, D = 60, 8, 1, 256
+    qkv = torch.randn(M, (Hq + 2 * Hkv) * D, device=DEV).bfloat16()
+    pos = torch.arange(5, 5 + M, device=DEV, dtype=torch.int32)
+    table = ref.rope_cos_sin(torch.arange(0, 128, device=DEV), D)
+    kp = torch.zeros(100, Hkv, D, device=DEV, dtype=torch.bfloat16)
+    vp = torch.zeros_like(kp)
+    slots = torch.randperm(100, device=DEV)[:M].long()
+    qo = torch.empty(M, Hq * D, device=DEV, dtype=torch.bfloat16)
+    ops.rope_kv(qkv, Hq, Hkv, D, qo, pos=pos, cos_sin=table, k_pool=kp, v_pool=vp, slots=slots)
+    q3 = qkv[:, : Hq * D].reshape(M, Hq, D)
+    k3 = qkv[:, Hq * D:(Hq + Hkv) * D].reshape(M, Hkv, D)
+    v3 = qkv[:, (Hq + Hkv) * D:].reshape(M, Hkv, D)
+    cs = table[pos.long()]
+    assert relerr(qo.reshape(M, Hq, D), ref.apply_rope(q3, cs)) < 1e-2
+    assert relerr(kp[slots], ref.apply_rope(k3, cs)) < 1e-2 and torch.equal(vp[slots], v3)
+    # per-head RMSNorm before the rotation (Cosmos3 qk-norm)
+    nw = (torch.rand(D, device=DEV) + 0.5).bfloat16()
+    ops.rope_kv(qkv, Hq, Hkv, D, qo, pos=pos, cos_sin=table, q_norm_w=nw, k_norm_w=nw, k_pool=kp, v_pool=vp, slots=slots)
+    assert relerr(qo.reshape(M, Hq, D), ref.apply_rope(ref.rms_norm(q3, nw), cs)) < TOL
+
+    ids = torch.randint(0, 1000, (37,), device=DEV)
+    tab = torch.randn(600, 256, device=DEV).bfloat16()
+    o = torch.zeros(37, 256, device=DEV, dtype=torch.bfloat16)
+    ops.embedding(ids, tab, o, lo=100, hi=700, scale=3.0)
+    assert relerr(o, ref.embedding(ids, tab, 100, 700, 3.0)) < 1e-2
+    pix = torch.rand(3, 3, 224, 224, device=DEV).bfloat16()
+    oc = torch.empty(768, 592, device=DEV, dtype=torch.bfloat16)
+    ops.im2col(pix, 14, oc)
+    assert torch.equal(oc, ref.im2col(pix, 14, 592))
+    x = torch.randn(33, 512, device=DEV).bfloat16()
+    for inter in (False, True):
+        assert relerr(ops.gated_act(x, "silu", interleaved=inter), ref.gated_act(x, "silu", inter)) < TOL
+    c, u = torch.randn(1000, device=DEV).bfloat16(), torch.randn(1000, device=DEV).bfloat16()
+    assert relerr(ops.cfg_combine(c, u, 7.0), ref.cfg_combine(c, u, 7.0)) < TOL
+    xs = torch.randn(1000, device=DEV)
+    xe = xs + (-0.1) * ref.cfg_combine(c, u, 3.0).float()
+    ops.cfg_combine(c, u, 3.0, x_fp32=xs, dt=-0.1)
+    assert relerr(xs, xe) < 1e-2
+    xb = torch.randn(640, device=DEV).bfloat16()
+    vb = torch.randn(640, device=DEV).bfloat16()
+    e = (xb.float() + 0.25 * vb.float())
+    ops.axpy(xb, vb, 0.25)
+    assert relerr(xb, e) < 1e-2
+    for blk in (0, 128):
+        xq = torch.randn(64, 1024, device=DEV).bfloat16()
+        y, sc = ops.quant_fp8(xq, blk)
+        ye, se = ref.quant_fp8(xq, blk)
+        assert relerr(sc, se) < 1e-5 and relerr(y.float(), ye.float()) < 0.07
+    _status_ok()
