@@ -62,7 +62,9 @@ def build_core(verbose: bool = False) -> Path:
 
     common_inc = [f"-I{CSRC}", f"-I{pyinc}", f"-I{pybind11.get_include()}"]
     cu_flags = ARCH_FLAGS + ["-O3", "-std=c++17", "--use_fast_math", "-Xcompiler", "-fPIC",
-                             "--expt-relaxed-constexpr"] + common_inc
+                             "--expt-relaxed-constexpr", "-DTORCH_EXTENSION_NAME=_C",
+                             "-DTORCH_API_INCLUDE_EXTENSION_H", "-D_GLIBCXX_USE_CXX11_ABI=1"] + common_inc + [
+                                 f"-I{p}" for p in inc]
     if verbose:
         cu_flags += ["-Xptxas", "-v"]
     cxx_flags = ["-O2", "-std=c++17", "-fPIC", "-DTORCH_EXTENSION_NAME=_C",

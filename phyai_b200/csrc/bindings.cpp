@@ -52,7 +52,7 @@ inline const long long* i64(const OptT& t) {
 void gemm(const Tensor& x, const Tensor& w, Tensor& out, const OptT& bias, const OptT& residual,
           int64_t res_mod, const OptT& col_gate, const OptT& row_scale, const OptT& sumsq,
           int64_t act, bool glu, const OptT& a_scale, const OptT& w_scale, int64_t force_bn,
-          int64_t force_swap, int64_t force_splits) {
+          int64_t force_swap, int64_t force_splits, const OptT& trace) {
   TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2, "gemm: 2-D tensors expected");
   TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1 && out.stride(1) == 1, "gemm: rows must be contiguous");
   TORCH_CHECK(x.size(1) == w.size(1), "gemm: K mismatch");
@@ -80,6 +80,10 @@ void gemm(const Tensor& x, const Tensor& w, Tensor& out, const OptT& bias, const
   a.a_scale = f32(a_scale); a.w_scale = f32(w_scale);
   TORCH_CHECK(!fp8 || (a.a_scale && a.w_scale), "gemm: fp8 needs a_scale [M] and w_scale [N]");
   a.force_bn = int(force_bn); a.force_swap = int(force_swap); a.force_splits = int(force_splits);
+  if (trace.has_value() && trace->defined()) {
+    TORCH_CHECK(trace->is_cuda() && trace->scalar_type() == at::kLong && trace->is_contiguous(), "gemm: trace must be a CUDA int64 tensor");
+    a.trace = reinterpret_cast<unsigned long long*>(trace->data_ptr());
+  }
   check(pb::gemm_launch(a, cur_stream()), "gemm_launch");
 }
 
@@ -233,7 +237,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("residual") = py::none(), py::arg("res_mod") = 0, py::arg("col_gate") = py::none(),
         py::arg("row_scale") = py::none(), py::arg("sumsq") = py::none(), py::arg("act") = 0,
         py::arg("glu") = false, py::arg("a_scale") = py::none(), py::arg("w_scale") = py::none(),
-        py::arg("force_bn") = 0, py::arg("force_swap") = -1, py::arg("force_splits") = 0);
+        py::arg("force_bn") = 0, py::arg("force_swap") = -1, py::arg("force_splits") = 0,
+        py::arg("trace") = py::none());
   m.def("attention", &attention, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"),
         py::arg("q_start"), py::arg("q_len"), py::arg("kv_indptr"), py::arg("kv_len"),
         py::arg("kv_indices") = py::none(), py::arg("max_q_len"), py::arg("causal") = false,

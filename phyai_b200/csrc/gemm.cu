@@ -90,7 +90,8 @@ constexpr int kRowBytes = 128;     // one swizzle-128B row: 64 bf16 or 128 e4m3
 template <int BN, bool SWAP, bool FP8>
 __global__ void __launch_bounds__(kThreads)
 gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
-            EpiParams ep, int total_kb, int kb_per_split, int stages, int* status) {
+            EpiParams ep, int total_kb, int kb_per_split, int stages, int* status,
+            unsigned long long* trace) {
   constexpr int BK = FP8 ? 128 : 64;                 // elements per k-block
   constexpr int P_BYTES = kTileP * kRowBytes;        // 16 KB
   constexpr int Q_BYTES = BN * kRowBytes;
@@ -110,6 +111,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
   __shared__ int err_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // optional phase timestamps (ns): 8 slots per CTA, written by one thread of the phase
+  unsigned long long* tr = trace ? trace + 8 * (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z))
+                                 : nullptr;
+  if (tr && threadIdx.x == 0) tr[0] = globaltimer_ns();
   const int p_tile = blockIdx.x, q_tile = blockIdx.y, split = blockIdx.z;
   const int nsplit = gridDim.z;
   const int kb0 = split * kb_per_split;
@@ -136,6 +141,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
   const uint32_t tmem_base = tmem_base_s;
 
   pdl_wait();  // inputs written by the previous kernel in the stream are visible from here
+  if (tr && threadIdx.x == 0) tr[1] = globaltimer_ns();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -181,6 +187,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
       __syncwarp();
     }
     if (lane == 0 && ok) umma_commit(&acc_bar);
+    if (tr && lane == 0) tr[2] = globaltimer_ns();
     __syncwarp();
   } else {
     // ----------------------------------------- TMEM -> shared staging (4 warps)
@@ -190,6 +197,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
       if (lane == 0) { err_s = kStatusTimeoutAcc; }
     } else {
       tc_fence_after();
+      if (tr && threadIdx.x == 64) tr[3] = globaltimer_ns();
       const int i = quad * 32 + lane;  // row of the P operand inside the tile
       constexpr int CH = BN >= 32 ? 32 : 16;
 #pragma unroll 1
@@ -215,6 +223,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
 
   __syncthreads();
   if (nsplit > 1) cluster_sync_all();
+  if (tr && threadIdx.x == 0) tr[4] = globaltimer_ns();
   const int err = err_s;
 
   if (err == 0) {
@@ -332,8 +341,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
     while (globaltimer_ns() - t0 < 2000000ull) { __nanosleep(1000); }
   }
 
+  if (tr && threadIdx.x == 0) tr[5] = globaltimer_ns();
   pdl_launch_dependents();
   if (nsplit > 1) cluster_sync_all();  // peers may still be reading this CTA's staging tile
+  if (tr && threadIdx.x == 0) tr[6] = globaltimer_ns();
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
@@ -410,7 +421,7 @@ static bool make_tmap(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t
 template <int BN, bool SWAP, bool FP8>
 static cudaError_t launch_inst(const CUtensorMap& tmP, const CUtensorMap& tmQ, const EpiParams& ep,
                                dim3 grid, int total_kb, int kbps, int stages, size_t smem,
-                               cudaStream_t stream) {
+                               cudaStream_t stream, unsigned long long* trace) {
   auto kern = gemm_kernel<BN, SWAP, FP8>;
   static bool attr_done = false;
   if (!attr_done) {
@@ -437,19 +448,19 @@ static cudaError_t launch_inst(const CUtensorMap& tmP, const CUtensorMap& tmQ, c
   cfg.numAttrs = na;
   int* status = kernel_status_ptr();
   bump_launch_counter();
-  return cudaLaunchKernelEx(&cfg, kern, tmP, tmQ, ep, total_kb, kbps, stages, status);
+  return cudaLaunchKernelEx(&cfg, kern, tmP, tmQ, ep, total_kb, kbps, stages, status, trace);
 }
 
 template <bool SWAP, bool FP8>
 static cudaError_t launch_bn(int bn, const CUtensorMap& tmP, const CUtensorMap& tmQ,
                              const EpiParams& ep, dim3 grid, int total_kb, int kbps, int stages,
-                             size_t smem, cudaStream_t st) {
+                             size_t smem, cudaStream_t st, unsigned long long* tr) {
   switch (bn) {
-    case 16: return launch_inst<16, SWAP, FP8>(tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, st);
-    case 32: return launch_inst<32, SWAP, FP8>(tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, st);
-    case 64: return launch_inst<64, SWAP, FP8>(tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, st);
-    case 128: return launch_inst<128, SWAP, FP8>(tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, st);
-    case 256: return launch_inst<256, SWAP, FP8>(tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, st);
+    case 16: return launch_inst<16, SWAP, FP8>(tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, st, tr);
+    case 32: return launch_inst<32, SWAP, FP8>(tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, st, tr);
+    case 64: return launch_inst<64, SWAP, FP8>(tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, st, tr);
+    case 128: return launch_inst<128, SWAP, FP8>(tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, st, tr);
+    case 256: return launch_inst<256, SWAP, FP8>(tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, st, tr);
     default: return cudaErrorInvalidValue;
   }
 }
@@ -540,11 +551,11 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
 
   dim3 grid(p_tiles, q_tiles, splits);
   if (swap) {
-    return a.fp8 ? launch_bn<true, true>(bn, tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, stream)
-                 : launch_bn<true, false>(bn, tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, stream);
+    return a.fp8 ? launch_bn<true, true>(bn, tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, stream, a.trace)
+                 : launch_bn<true, false>(bn, tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, stream, a.trace);
   }
-  return a.fp8 ? launch_bn<false, true>(bn, tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, stream)
-               : launch_bn<false, false>(bn, tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, stream);
+  return a.fp8 ? launch_bn<false, true>(bn, tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, stream, a.trace)
+               : launch_bn<false, false>(bn, tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, stream, a.trace);
 }
 
 }  // namespace pb

@@ -42,6 +42,7 @@ struct GemmArgs {
   const float* w_scale = nullptr;           // fp8: [N] or [N/128, K/128] (block)
   int block_scaled = 0;                     // fp8: 128x128 weight blocks, 1x128 act blocks
   int force_bn = 0, force_swap = -1, force_splits = 0;  // tuning overrides (0/-1 = auto)
+  unsigned long long* trace = nullptr;  // optional: 8 globaltimer stamps per CTA (debugging)
 };
 
 // Launches on `stream`. Returns cudaSuccess or the launch error; argument

@@ -68,7 +68,8 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *
          row_scale: Optional[torch.Tensor] = None, sumsq: Optional[torch.Tensor] = None,
          act: str | None = "none", glu: bool = False, out_dtype: torch.dtype = torch.bfloat16,
          a_scale: Optional[torch.Tensor] = None, w_scale: Optional[torch.Tensor] = None,
-         force_bn: int = 0, force_swap: int = -1, force_splits: int = 0) -> torch.Tensor:
+         force_bn: int = 0, force_swap: int = -1, force_splits: int = 0,
+         trace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out = epilogue(x @ w.T)`` on tcgen05 tensor cores (see ``csrc/gemm.cuh``).
 
     ``x`` is ``(M, K)``, ``w`` is ``(N, K)`` (the ``nn.Linear`` layout), both bf16 or
@@ -80,7 +81,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *
     if out is None:
         out = torch.empty((M, N // 2 if glu else N), dtype=out_dtype, device=x.device)
     ext().gemm(x, w, out, bias, residual, res_mod, col_gate, row_scale, sumsq, ACT[act], glu,
-               a_scale, w_scale, force_bn, force_swap, force_splits)
+               a_scale, w_scale, force_bn, force_swap, force_splits, trace)
     return out
 
 
