@@ -20,6 +20,7 @@
 #include "attention.cuh"
 
 #include "gemm.cuh"
+#include "launch.cuh"
 #include "ptx.cuh"
 
 namespace pb {
@@ -104,6 +105,7 @@ attn_kernel(AttnParams p) {
   const int row0 = blockIdx.x * kBM;
   const bool cta_live = row0 < rows_total;   // uniform across the cluster (same x, b)
 
+  pdl_launch_dependents();
   pdl_wait();
 
   float o_acc[ONB][4];
@@ -335,7 +337,6 @@ attn_kernel(AttnParams p) {
       *reinterpret_cast<uint2*>(dst) = raw;
     }
   }
-  pdl_launch_dependents();
   if (nsplit > 1) cluster_sync_all();
 }
 
@@ -351,24 +352,8 @@ static cudaError_t attn_launch_dp(const AttnParams& p, cudaStream_t stream) {
     attr_done = true;
   }
   const int max_rows = p.max_q_len * p.group;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((max_rows + kBM - 1) / kBM, p.num_kv_heads, p.batch * p.splits);
-  cfg.blockDim = dim3(kAttnThreads, 1, 1);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attrs[1];
-  int na = 0;
-  if (p.splits > 1) {
-    attrs[na].id = cudaLaunchAttributeClusterDimension;
-    attrs[na].val.clusterDim.x = 1;
-    attrs[na].val.clusterDim.y = 1;
-    attrs[na].val.clusterDim.z = p.splits;
-    ++na;
-  }
-  cfg.attrs = attrs;
-  cfg.numAttrs = na;
-  bump_launch_counter();
-  return cudaLaunchKernelEx(&cfg, kern, p);
+  return launch_kernel(kern, dim3((max_rows + kBM - 1) / kBM, p.num_kv_heads, p.batch * p.splits),
+                       dim3(kAttnThreads), smem, stream, p.splits, p);
 }
 
 cudaError_t attn_launch(const AttnParams& p, cudaStream_t stream) {

@@ -26,6 +26,7 @@ struct AttnParams {
   float sm_scale = 1.0f;
 };
 
-cudaError_t attn_launch(const AttnParams& p, cudaStream_t stream);
+cudaError_t attn_launch(const AttnParams& p, cudaStream_t stream);     // mma.sync path
+cudaError_t attn_tc_launch(const AttnParams& p, cudaStream_t stream);  // tcgen05 path
 
 }  // namespace pb

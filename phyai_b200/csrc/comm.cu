@@ -29,6 +29,10 @@
 
 #include "comm_device.cuh"
 #include "gemm.cuh"
+#include "launch.cuh"
+
+#define PB_LAUNCH(kern, grid, block, stream, ...) \
+  throw_on(pb::launch_kernel(kern, dim3(grid), dim3(block), 0, stream, 1, __VA_ARGS__), #kern)
 
 namespace py = pybind11;
 
@@ -40,6 +44,7 @@ __global__ void reduce_norm_kernel(ReduceNormArgs a, ChannelSig* local_sig, int 
   __shared__ float red[32];
   __shared__ int ok_s;
   ChannelSig* sig = local_sig + channel;
+  pdl_launch_dependents();
   pdl_wait();
   const unsigned int e = ld_relaxed_sys(&sig->epoch);
   const int parity = int(e & 1u);
@@ -58,13 +63,13 @@ __global__ void reduce_norm_kernel(ReduceNormArgs a, ChannelSig* local_sig, int 
     }
   }
   channel_finish(sig, parity, gridDim.x);
-  pdl_launch_dependents();
 }
 
 // Copies this rank's partial [M, N] (row stride ldx) into slots[parity][rank] of every peer.
 __global__ void push_partial_kernel(const __nv_bfloat16* x, int M, int N, int ldx, PeerPtrs data,
                                     long long slots_off, long long slot_stride, int ld, int world,
                                     int rank, PeerPtrs sig, ChannelSig* local_sig, int channel) {
+  pdl_launch_dependents();
   pdl_wait();
   const unsigned int e = ld_relaxed_sys(&(local_sig + channel)->epoch);
   const int parity = int(e & 1u);
@@ -82,7 +87,6 @@ __global__ void push_partial_kernel(const __nv_bfloat16* x, int M, int N, int ld
   }
   __syncthreads();
   if (threadIdx.x == 0) channel_signal_all(sig, channel, parity, world);
-  pdl_launch_dependents();
 }
 
 // CFG pair exchange. `mine` is this branch's prediction (n bf16). Both ranks of the pair
@@ -93,6 +97,7 @@ __global__ void cfg_exchange_kernel(const __nv_bfloat16* mine, long long n, Peer
                                     ChannelSig* local_sig, int channel, int* status) {
   __shared__ int ok_s;
   ChannelSig* ls = local_sig + channel;
+  pdl_launch_dependents();
   pdl_wait();
   const unsigned int e = ld_relaxed_sys(&ls->epoch);
   const int parity = int(e & 1u);
@@ -141,7 +146,6 @@ __global__ void cfg_exchange_kernel(const __nv_bfloat16* mine, long long n, Peer
     }
   }
   channel_finish(ls, parity, gridDim.x);
-  pdl_launch_dependents();
 }
 
 // Consumer half of the row all-gather: every rank pushed its shard into
@@ -153,6 +157,7 @@ __global__ void gather_consume_kernel(const __nv_bfloat16* slots, long long slot
                                       int* status) {
   __shared__ int ok_s;
   ChannelSig* ls = local_sig + channel;
+  pdl_launch_dependents();
   pdl_wait();
   const unsigned int e = ld_relaxed_sys(&ls->epoch);
   const int parity = int(e & 1u);
@@ -176,7 +181,6 @@ __global__ void gather_consume_kernel(const __nv_bfloat16* slots, long long slot
     }
   }
   channel_finish(ls, parity, gridDim.x);
-  pdl_launch_dependents();
 }
 
 __global__ void flag_wait_probe_kernel(const unsigned int* flag, unsigned int want,
@@ -266,8 +270,7 @@ void reduce_norm(const std::vector<uintptr_t>& data_ptrs, int64_t rank, int64_t 
   int threads = int(((N / 8) + 31) / 32 * 32);
   threads = threads > 512 ? 512 : (threads < 64 ? 64 : threads);
   int grid = int(M < max_ctas ? M : max_ctas);
-  pb::bump_launch_counter();
-  pb::reduce_norm_kernel<<<grid, threads, 0, cur_stream()>>>(a, sig, int(channel), unsigned(expect),
+  PB_LAUNCH(pb::reduce_norm_kernel, grid, threads, cur_stream(), a, sig, int(channel), unsigned(expect),
                                                              pb::kernel_status_ptr());
   throw_on(cudaGetLastError(), "reduce_norm_kernel");
 }
@@ -281,8 +284,7 @@ int64_t push_partial(const Tensor& x, const std::vector<uintptr_t>& data_ptrs, i
   int grid = int((total + 255) / 256);
   grid = grid > 64 ? 64 : (grid < 1 ? 1 : grid);
   auto* sig = reinterpret_cast<pb::ChannelSig*>(data_ptrs[rank] + sig_off_bytes);
-  pb::bump_launch_counter();
-  pb::push_partial_kernel<<<grid, 256, 0, cur_stream()>>>(
+  PB_LAUNCH(pb::push_partial_kernel, grid, 256, cur_stream(), 
       bfp(OptT(x)), int(x.size(0)), int(x.size(1)), int(x.stride(0)), to_ptrs(data_ptrs), slots_off_elems,
       slot_stride, int(ld), world, int(rank), to_ptrs(data_ptrs, sig_off_bytes), sig, int(channel));
   throw_on(cudaGetLastError(), "push_partial_kernel");
@@ -303,8 +305,7 @@ void cfg_exchange(const Tensor& mine, const std::vector<uintptr_t>& data_ptrs, i
     xp = reinterpret_cast<float*>(x_fp32->data_ptr());
   }
   __nv_bfloat16* op = (out.has_value() && out->defined()) ? const_cast<__nv_bfloat16*>(bfp(out)) : nullptr;
-  pb::bump_launch_counter();
-  pb::cfg_exchange_kernel<<<grid, 256, 0, cur_stream()>>>(
+  PB_LAUNCH(pb::cfg_exchange_kernel, grid, 256, cur_stream(), 
       bfp(OptT(mine)), n, to_ptrs(data_ptrs), buf_off_elems, int(my_pos), int(partner_pos), is_cond ? 1 : 0,
       float(g), op, xp, float(dt), to_ptrs(data_ptrs, sig_off_bytes), sig, int(channel), pb::kernel_status_ptr());
   throw_on(cudaGetLastError(), "cfg_exchange_kernel");
@@ -319,8 +320,7 @@ void gather_consume(const std::vector<uintptr_t>& data_ptrs, int64_t rank, int64
   int grid = int((total + 255) / 256);
   grid = grid > 128 ? 128 : (grid < 1 ? 1 : grid);
   auto* sig = reinterpret_cast<pb::ChannelSig*>(data_ptrs[rank] + sig_off_bytes);
-  pb::bump_launch_counter();
-  pb::gather_consume_kernel<<<grid, 256, 0, cur_stream()>>>(
+  PB_LAUNCH(pb::gather_consume_kernel, grid, 256, cur_stream(), 
       reinterpret_cast<const __nv_bfloat16*>(data_ptrs[rank]) + slots_off_elems, slot_stride, int(rows), int(N),
       int(ld), world, const_cast<__nv_bfloat16*>(bfp(OptT(out))), int(out.stride(0)), sig, int(channel),
       unsigned(expect), pb::kernel_status_ptr());
@@ -329,8 +329,7 @@ void gather_consume(const std::vector<uintptr_t>& data_ptrs, int64_t rank, int64
 
 void flag_wait_probe(const Tensor& flag, int64_t want, double timeout_s) {
   TORCH_CHECK(flag.is_cuda() && flag.scalar_type() == at::kInt, "flag_wait_probe: int32 CUDA tensor");
-  pb::bump_launch_counter();
-  pb::flag_wait_probe_kernel<<<1, 32, 0, cur_stream()>>>(
+  PB_LAUNCH(pb::flag_wait_probe_kernel, 1, 32, cur_stream(), 
       reinterpret_cast<const unsigned int*>(flag.data_ptr()), unsigned(want),
       (unsigned long long)(timeout_s * 1e9), pb::kernel_status_ptr());
   throw_on(cudaGetLastError(), "flag_wait_probe_kernel");

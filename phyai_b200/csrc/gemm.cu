@@ -23,9 +23,12 @@
 #include "gemm.cuh"
 
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
+#include "gemm_epilogue.cuh"
+#include "launch.cuh"
 #include "ptx.cuh"
 
 namespace pb {
@@ -56,31 +59,10 @@ int read_and_clear_kernel_status() {
 }
 uint64_t launch_counter() { return g_launches.load(); }
 void reset_launch_counter() { g_launches.store(0); }
-void bump_launch_counter(uint64_t n) { g_launches.fetch_add(n); }
-
-// ------------------------------------------------------------------ epilogue
-struct EpiParams {
-  void* out;
-  int ldo, M, N;
-  const __nv_bfloat16* bias;
-  const __nv_bfloat16* residual;
-  int ldr, res_mod;
-  const __nv_bfloat16* col_gate;
-  const float* row_scale;
-  float* sumsq;
-  const float* a_scale;
-  const float* w_scale;
-  int act, glu, out_fp32;
-};
-
-__device__ __forceinline__ float apply_act(float v, int act) {
-  switch (act) {
-    case kActGeluTanh: return gelu_tanh_f(v);
-    case kActSilu: return silu_f(v);
-    case kActGeluErf: return gelu_erf_f(v);
-    default: return v;
-  }
-}
+void bump_launch_counter(unsigned long long n) { g_launches.fetch_add(n); }
+static std::atomic<bool> g_pdl{false};
+bool pdl_enabled() { return g_pdl.load(); }
+void set_pdl_enabled(bool on) { g_pdl.store(on); }
 
 constexpr int kThreads = 192;
 constexpr int kMaxStages = 8;
@@ -112,7 +94,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // optional phase timestamps (ns): 8 slots per CTA, written by one thread of the phase
-  unsigned long long* tr = trace ? trace + 8 * (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z))
+  unsigned long long* tr = trace ? trace + 32 * (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z))
                                  : nullptr;
   if (tr && threadIdx.x == 0) tr[0] = globaltimer_ns();
   const int p_tile = blockIdx.x, q_tile = blockIdx.y, split = blockIdx.z;
@@ -140,12 +122,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
 
-  pdl_wait();  // inputs written by the previous kernel in the stream are visible from here
+  pdl_launch_dependents();
+  if (warp != 0) pdl_wait();  // everything but the weight prefetch below depends on earlier kernels
   if (tr && threadIdx.x == 0) tr[1] = globaltimer_ns();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    for (int kb = 0; kb < nkb; ++kb) {
+    // Weights never depend on a predecessor kernel: their first tiles are requested
+    // before the dependency wait, the activation tiles of the same stages right after it.
+    const CUtensorMap* tmW = SWAP ? &tmP : &tmQ;
+    const CUtensorMap* tmX = SWAP ? &tmQ : &tmP;
+    const int w_row = SWAP ? p_tile * kTileP : q_tile * BN;
+    const int x_row = SWAP ? q_tile * BN : p_tile * kTileP;
+    constexpr int W_OFF = SWAP ? 0 : P_BYTES, X_OFF = SWAP ? P_BYTES : 0;
+    const int pre = min(nkb, stages);
+    if (lane == 0) {
+      for (int kb = 0; kb < pre; ++kb) {
+        mbar_expect_tx(&full_bar[kb], STAGE_BYTES);
+        tma_load_2d(smem + kb * STAGE_BYTES + W_OFF, tmW, &full_bar[kb], (kb0 + kb) * BK, w_row);
+      }
+    }
+    pdl_wait();
+    if (lane == 0) {
+      for (int kb = 0; kb < pre; ++kb)
+        tma_load_2d(smem + kb * STAGE_BYTES + X_OFF, tmX, &full_bar[kb], (kb0 + kb) * BK, x_row);
+    }
+    __syncwarp();
+    for (int kb = pre; kb < nkb; ++kb) {
       const int s = kb % stages;
       const uint32_t ph = (kb / stages) & 1;
       if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
@@ -155,8 +158,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
       if (lane == 0) {
         uint8_t* sp = smem + s * STAGE_BYTES;
         mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-        tma_load_2d(sp, &tmP, &full_bar[s], (kb0 + kb) * BK, p_tile * kTileP);
-        tma_load_2d(sp + P_BYTES, &tmQ, &full_bar[s], (kb0 + kb) * BK, q_tile * BN);
+        tma_load_2d(sp + W_OFF, tmW, &full_bar[s], (kb0 + kb) * BK, w_row);
+        tma_load_2d(sp + X_OFF, tmX, &full_bar[s], (kb0 + kb) * BK, x_row);
       }
       __syncwarp();
     }
@@ -231,109 +234,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
     const int m0 = SWAP ? q_tile * BN : p_tile * kTileP;
     const int n0 = SWAP ? p_tile * kTileP : q_tile * BN;
     const int rows_per_cta = TM / nsplit;
-    const int r0 = split * rows_per_cta;
-    constexpr int G = TN / 4;  // float4 groups per row
-    const uint32_t stg_addr = smem_u32(smem);
-    const float* stg = reinterpret_cast<const float*>(smem);
-    for (int g = threadIdx.x; g < rows_per_cta * G; g += kThreads) {
-      const int row = r0 + g / G;
-      const int c4 = (g % G) * 4;
-      const int m = m0 + row, n = n0 + c4;
-      const bool live = (m < ep.M) && (n < ep.N);
-      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (live) {
-        if (nsplit == 1) {
-          a = *reinterpret_cast<const float4*>(stg + row * LDS + c4);
-        } else {
-          const uint32_t off = stg_addr + uint32_t(row * LDS + c4) * 4u;
-          for (int r = 0; r < nsplit; ++r) {
-            float4 v = ld_dsmem_f4(map_to_cta(off, r));
-            a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
-          }
-        }
-        float v[4] = {a.x, a.y, a.z, a.w};
-        if (ep.row_scale) {
-          const float s = ep.row_scale[m];
-#pragma unroll
-          for (int t = 0; t < 4; ++t) v[t] *= s;
-        }
-        if (ep.a_scale) {
-          const float sa = ep.a_scale[m];
-#pragma unroll
-          for (int t = 0; t < 4; ++t) v[t] *= sa * ep.w_scale[n + t];
-        }
-        if (ep.bias) {
-#pragma unroll
-          for (int t = 0; t < 4; ++t) v[t] += __bfloat162float(ep.bias[n + t]);
-        }
-        if (ep.glu) {
-          float y[2] = {apply_act(v[0], ep.act) * v[1], apply_act(v[2], ep.act) * v[3]};
-          const int no = n >> 1;
-          if (ep.col_gate) {
-            y[0] *= __bfloat162float(ep.col_gate[no]);
-            y[1] *= __bfloat162float(ep.col_gate[no + 1]);
-          }
-          if (ep.residual) {
-            const int rr = ep.res_mod > 0 ? (m % ep.res_mod) : m;
-            y[0] += __bfloat162float(ep.residual[size_t(rr) * ep.ldr + no]);
-            y[1] += __bfloat162float(ep.residual[size_t(rr) * ep.ldr + no + 1]);
-          }
-          if (ep.out_fp32) {
-            float* o = reinterpret_cast<float*>(ep.out) + size_t(m) * ep.ldo + no;
-            *reinterpret_cast<float2*>(o) = make_float2(y[0], y[1]);
-          } else {
-            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(ep.out) + size_t(m) * ep.ldo + no;
-            *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(y[0], y[1]);
-          }
-          a = make_float4(y[0], y[1], 0.f, 0.f);
-        } else {
-          if (ep.act != kActNone) {
-#pragma unroll
-            for (int t = 0; t < 4; ++t) v[t] = apply_act(v[t], ep.act);
-          }
-          if (ep.col_gate) {
-#pragma unroll
-            for (int t = 0; t < 4; ++t) v[t] *= __bfloat162float(ep.col_gate[n + t]);
-          }
-          if (ep.residual) {
-            const int rr = ep.res_mod > 0 ? (m % ep.res_mod) : m;
-            const __nv_bfloat16* rp = ep.residual + size_t(rr) * ep.ldr + n;
-            const uint2 raw = *reinterpret_cast<const uint2*>(rp);
-            const __nv_bfloat162 r01 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-            const __nv_bfloat162 r23 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-            v[0] += __bfloat162float(r01.x); v[1] += __bfloat162float(r01.y);
-            v[2] += __bfloat162float(r23.x); v[3] += __bfloat162float(r23.y);
-          }
-          if (ep.out_fp32) {
-            float* o = reinterpret_cast<float*>(ep.out) + size_t(m) * ep.ldo + n;
-            *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
-          } else {
-            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(ep.out) + size_t(m) * ep.ldo + n;
-            __nv_bfloat162 o01 = __floats2bfloat162_rn(v[0], v[1]);
-            __nv_bfloat162 o23 = __floats2bfloat162_rn(v[2], v[3]);
-            uint2 raw;
-            raw.x = *reinterpret_cast<uint32_t*>(&o01);
-            raw.y = *reinterpret_cast<uint32_t*>(&o23);
-            *reinterpret_cast<uint2*>(o) = raw;
-            // the norm that consumes this sees the rounded values
-            v[0] = __bfloat162float(o01.x); v[1] = __bfloat162float(o01.y);
-            v[2] = __bfloat162float(o23.x); v[3] = __bfloat162float(o23.y);
-          }
-          a = make_float4(v[0], v[1], v[2], v[3]);
-        }
-      }
-      if (ep.sumsq) {
-        float ss = live ? (a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w) : 0.f;
-        if constexpr (G % 32 == 0) {
-          // one warp covers 32 consecutive groups of one row
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-          if (lane == 0 && m < ep.M) atomicAdd(ep.sumsq + m, ss);
-        } else {
-          if (live) atomicAdd(ep.sumsq + m, ss);
-        }
-      }
-    }
+    epilogue_pass<TN>(ep, reinterpret_cast<const float*>(smem), smem_u32(smem), LDS, m0, n0,
+                      split * rows_per_cta, rows_per_cta, nsplit, warp, lane, kThreads / 32);
   } else if (threadIdx.x == 0) {
     if (status) atomicCAS(status, 0, err);
     // let copies that are still in flight land before the block goes away
@@ -342,7 +244,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
   }
 
   if (tr && threadIdx.x == 0) tr[5] = globaltimer_ns();
-  pdl_launch_dependents();
   if (nsplit > 1) cluster_sync_all();  // peers may still be reading this CTA's staging tile
   if (tr && threadIdx.x == 0) tr[6] = globaltimer_ns();
   tc_fence_before();
@@ -430,25 +331,8 @@ static cudaError_t launch_inst(const CUtensorMap& tmP, const CUtensorMap& tmQ, c
     if (e != cudaSuccess) return e;
     attr_done = true;
   }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = dim3(kThreads, 1, 1);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attrs[1];
-  int na = 0;
-  if (grid.z > 1) {
-    attrs[na].id = cudaLaunchAttributeClusterDimension;
-    attrs[na].val.clusterDim.x = 1;
-    attrs[na].val.clusterDim.y = 1;
-    attrs[na].val.clusterDim.z = grid.z;
-    ++na;
-  }
-  cfg.attrs = attrs;
-  cfg.numAttrs = na;
-  int* status = kernel_status_ptr();
-  bump_launch_counter();
-  return cudaLaunchKernelEx(&cfg, kern, tmP, tmQ, ep, total_kb, kbps, stages, status, trace);
+  return launch_kernel(kern, grid, dim3(kThreads), smem, stream, int(grid.z), tmP, tmQ, ep, total_kb, kbps,
+                       stages, kernel_status_ptr(), trace);
 }
 
 template <bool SWAP, bool FP8>
@@ -484,6 +368,11 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   if ((reinterpret_cast<uintptr_t>(a.x) & 15) || (reinterpret_cast<uintptr_t>(a.w) & 15) ||
       (size_t(a.ldx) * eb) % 16 || (size_t(a.ldw) * eb) % 16 || (a.N % 8) ||
       (reinterpret_cast<uintptr_t>(a.out) & 15) || (a.ldo % 4))
+    return cudaErrorInvalidValue;
+  // the epilogue reads bias / gate / residual as 8-byte vectors, scales as 16-byte vectors
+  if ((reinterpret_cast<uintptr_t>(a.bias) & 7) || (reinterpret_cast<uintptr_t>(a.col_gate) & 7) ||
+      (reinterpret_cast<uintptr_t>(a.residual) & 7) || (a.residual && (a.ldr % 4)) ||
+      (reinterpret_cast<uintptr_t>(a.w_scale) & 15))
     return cudaErrorInvalidValue;
   if (a.block_scaled) return cudaErrorInvalidValue;  // handled by gemm_fp8_block_launch
 

@@ -56,6 +56,6 @@ int read_and_clear_kernel_status();
 // How many kernels of this library were launched since the last reset.
 uint64_t launch_counter();
 void reset_launch_counter();
-void bump_launch_counter(uint64_t n = 1);
+void bump_launch_counter(unsigned long long n = 1);
 
 }  // namespace pb

@@ -13,7 +13,14 @@
 #include <cuda_fp8.h>
 
 #include "gemm.cuh"
+#include "launch.cuh"
 #include "ptx.cuh"
+
+#define PB_LAUNCH(kern, grid, block, stream, ...)                                           \
+  do {                                                                                    \
+    cudaError_t e__ = launch_kernel(kern, dim3(grid), dim3(block), 0, stream, 1, __VA_ARGS__); \
+    if (e__ != cudaSuccess) return e__;                                                   \
+  } while (0)
 
 namespace pb {
 
@@ -77,6 +84,7 @@ __global__ void norm_kernel(NormArgs a) {
   __shared__ float red[32];
   const int row = blockIdx.x;
   const int nv = a.D >> 3;
+  pdl_launch_dependents();
   pdl_wait();
   const BF8* xr = reinterpret_cast<const BF8*>(a.x + size_t(row) * a.ldx);
   BF8* rr = a.residual ? reinterpret_cast<BF8*>(a.residual + size_t(row) * a.ldr) : nullptr;
@@ -192,7 +200,6 @@ __global__ void norm_kernel(NormArgs a) {
       }
     }
   }
-  pdl_launch_dependents();
 }
 
 cudaError_t norm_launch(const NormArgs& a, cudaStream_t s) {
@@ -203,13 +210,12 @@ cudaError_t norm_launch(const NormArgs& a, cudaStream_t s) {
   int threads = ((a.D / 8) + 31) / 32 * 32;
   if (threads > 1024) threads = 1024;
   if (threads < 32) threads = 32;
-  bump_launch_counter();
   switch (a.mode) {
-    case kNormRms: norm_kernel<kNormRms><<<a.rows, threads, 0, s>>>(a); break;
-    case kNormGemmaRms: norm_kernel<kNormGemmaRms><<<a.rows, threads, 0, s>>>(a); break;
-    case kNormLayer: norm_kernel<kNormLayer><<<a.rows, threads, 0, s>>>(a); break;
-    case kNormAdaRms: norm_kernel<kNormAdaRms><<<a.rows, threads, 0, s>>>(a); break;
-    case kNormRmsNoWeight: norm_kernel<kNormRmsNoWeight><<<a.rows, threads, 0, s>>>(a); break;
+    case kNormRms: PB_LAUNCH(norm_kernel<kNormRms>, a.rows, threads, s, a); break;
+    case kNormGemmaRms: PB_LAUNCH(norm_kernel<kNormGemmaRms>, a.rows, threads, s, a); break;
+    case kNormLayer: PB_LAUNCH(norm_kernel<kNormLayer>, a.rows, threads, s, a); break;
+    case kNormAdaRms: PB_LAUNCH(norm_kernel<kNormAdaRms>, a.rows, threads, s, a); break;
+    case kNormRmsNoWeight: PB_LAUNCH(norm_kernel<kNormRmsNoWeight>, a.rows, threads, s, a); break;
     default: return cudaErrorInvalidValue;
   }
   return cudaGetLastError();
@@ -223,6 +229,7 @@ __global__ void rope_kv_kernel(RopeKvArgs a) {
   const int lane = threadIdx.x & 31;
   const long long wid = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
   const int H = a.Hq + 2 * a.Hkv;
+  pdl_launch_dependents();
   pdl_wait();
   if (wid >= (long long)a.M * H) return;
   const int tok = int(wid / H), h = int(wid % H);
@@ -284,8 +291,7 @@ cudaError_t rope_kv_launch(const RopeKvArgs& a, cudaStream_t s) {
   if (a.D % 8 || a.ld % 8) return cudaErrorInvalidValue;
   const long long warps = (long long)a.M * (a.Hq + 2 * a.Hkv);
   const int wpb = 8;
-  bump_launch_counter();
-  rope_kv_kernel<<<unsigned((warps + wpb - 1) / wpb), wpb * 32, 0, s>>>(a);
+  PB_LAUNCH(rope_kv_kernel, unsigned((warps + wpb - 1) / wpb), wpb * 32, s, a);
   return cudaGetLastError();
 }
 
@@ -294,6 +300,7 @@ __global__ void embedding_kernel(const long long* ids, int n, const __nv_bfloat1
                                  long long lo, long long hi, float scale, __nv_bfloat16* out,
                                  int ldo, const int* dst_rows) {
   const int m = blockIdx.x;
+  pdl_launch_dependents();
   pdl_wait();
   const long long id = ids[m];
   const bool in = id >= lo && id < hi;
@@ -316,8 +323,7 @@ cudaError_t embedding_launch(const long long* ids, int n, const __nv_bfloat16* t
                              const int* dst_rows, cudaStream_t s) {
   if (n <= 0) return cudaSuccess;
   if (D % 8 || ldo % 8) return cudaErrorInvalidValue;
-  bump_launch_counter();
-  embedding_kernel<<<n, 128, 0, s>>>(ids, n, table, D, lo, hi, scale, out, ldo, dst_rows);
+  PB_LAUNCH(embedding_kernel, n, 128, s, ids, n, table, D, lo, hi, scale, out, ldo, dst_rows);
   return cudaGetLastError();
 }
 
@@ -329,6 +335,7 @@ __global__ void im2col_kernel(const __nv_bfloat16* pix, int C, int H, int W, int
   const int img = patch / (gh * gw), rem = patch % (gh * gw);
   const int py0 = (rem / gw) * p, px0 = (rem % gw) * p;
   const int kreal = C * p * p;
+  pdl_launch_dependents();
   pdl_wait();
   for (int k = threadIdx.x; k < kpad; k += blockDim.x) {
     __nv_bfloat16 v = __float2bfloat16(0.f);
@@ -343,8 +350,7 @@ __global__ void im2col_kernel(const __nv_bfloat16* pix, int C, int H, int W, int
 cudaError_t im2col_launch(const __nv_bfloat16* pix, int n_img, int C, int H, int W, int p,
                           __nv_bfloat16* out, int kpad, cudaStream_t s) {
   if (H % p || W % p || kpad < C * p * p) return cudaErrorInvalidValue;
-  bump_launch_counter();
-  im2col_kernel<<<n_img * (H / p) * (W / p), 256, 0, s>>>(pix, C, H, W, p, out, kpad);
+  PB_LAUNCH(im2col_kernel, n_img * (H / p) * (W / p), 256, s, pix, C, H, W, p, out, kpad);
   return cudaGetLastError();
 }
 
@@ -360,6 +366,7 @@ __device__ __forceinline__ float act_f(float v, int act) {
 __global__ void gated_act_kernel(const __nv_bfloat16* x, __nv_bfloat16* y, int M, int I, int act,
                                  int interleaved) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_launch_dependents();
   pdl_wait();
   if (idx >= (long long)M * I) return;
   const int m = int(idx / I), j = int(idx % I);
@@ -372,27 +379,27 @@ cudaError_t gated_act_launch(const __nv_bfloat16* x, __nv_bfloat16* y, int M, in
                              int interleaved, cudaStream_t s) {
   const long long n = (long long)M * I;
   if (n <= 0) return cudaSuccess;
-  bump_launch_counter();
-  gated_act_kernel<<<unsigned((n + 255) / 256), 256, 0, s>>>(x, y, M, I, act, interleaved);
+  PB_LAUNCH(gated_act_kernel, unsigned((n + 255) / 256), 256, s, x, y, M, I, act, interleaved);
   return cudaGetLastError();
 }
 
 __global__ void unary_kernel(const __nv_bfloat16* x, __nv_bfloat16* y, long long n, int act) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_launch_dependents();
   pdl_wait();
   if (i < n) y[i] = __float2bfloat16(act_f(__bfloat162float(x[i]), act));
 }
 cudaError_t unary_launch(const __nv_bfloat16* x, __nv_bfloat16* y, long long n, int act,
                          cudaStream_t s) {
   if (n <= 0) return cudaSuccess;
-  bump_launch_counter();
-  unary_kernel<<<unsigned((n + 255) / 256), 256, 0, s>>>(x, y, n, act);
+  PB_LAUNCH(unary_kernel, unsigned((n + 255) / 256), 256, s, x, y, n, act);
   return cudaGetLastError();
 }
 
 // ------------------------------------------------------------ sampler updates
 __global__ void axpy_kernel(void* x, int x_fp32, const __nv_bfloat16* v, float dt, long long n) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_launch_dependents();
   pdl_wait();
   if (i >= n) return;
   if (x_fp32) {
@@ -406,14 +413,14 @@ __global__ void axpy_kernel(void* x, int x_fp32, const __nv_bfloat16* v, float d
 cudaError_t axpy_launch(void* x, int x_fp32, const __nv_bfloat16* v, float dt, long long n,
                         cudaStream_t s) {
   if (n <= 0) return cudaSuccess;
-  bump_launch_counter();
-  axpy_kernel<<<unsigned((n + 255) / 256), 256, 0, s>>>(x, x_fp32, v, dt, n);
+  PB_LAUNCH(axpy_kernel, unsigned((n + 255) / 256), 256, s, x, x_fp32, v, dt, n);
   return cudaGetLastError();
 }
 
 __global__ void cfg_combine_kernel(const __nv_bfloat16* c, const __nv_bfloat16* u, float g,
                                    __nv_bfloat16* out, float* x, float dt, long long n) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_launch_dependents();
   pdl_wait();
   if (i >= n) return;
   const float vc = __bfloat162float(c[i]), vu = __bfloat162float(u[i]);
@@ -425,8 +432,7 @@ cudaError_t cfg_combine_launch(const __nv_bfloat16* cond, const __nv_bfloat16* u
                                __nv_bfloat16* out, float* x_fp32, float dt, long long n,
                                cudaStream_t s) {
   if (n <= 0) return cudaSuccess;
-  bump_launch_counter();
-  cfg_combine_kernel<<<unsigned((n + 255) / 256), 256, 0, s>>>(cond, uncond, g, out, x_fp32, dt, n);
+  PB_LAUNCH(cfg_combine_kernel, unsigned((n + 255) / 256), 256, s, cond, uncond, g, out, x_fp32, dt, n);
   return cudaGetLastError();
 }
 
@@ -434,6 +440,7 @@ cudaError_t cfg_combine_launch(const __nv_bfloat16* cond, const __nv_bfloat16* u
 __global__ void scatter_rows_kernel(const __nv_bfloat16* src, int D, int lds, __nv_bfloat16* dst,
                                     int ldd, const int* rows) {
   const int i = blockIdx.x;
+  pdl_launch_dependents();
   pdl_wait();
   const int r = rows ? rows[i] : i;
   if (r < 0) return;
@@ -445,8 +452,7 @@ cudaError_t scatter_rows_launch(const __nv_bfloat16* src, int n, int D, int lds,
                                 __nv_bfloat16* dst, int ldd, const int* rows, cudaStream_t s) {
   if (n <= 0) return cudaSuccess;
   if (D % 8 || lds % 8 || ldd % 8) return cudaErrorInvalidValue;
-  bump_launch_counter();
-  scatter_rows_kernel<<<n, 128, 0, s>>>(src, D, lds, dst, ldd, rows);
+  PB_LAUNCH(scatter_rows_kernel, n, 128, s, src, D, lds, dst, ldd, rows);
   return cudaGetLastError();
 }
 
@@ -456,6 +462,7 @@ __global__ void quant_fp8_kernel(const __nv_bfloat16* x, int D, int ldx, uint8_t
   __shared__ float red[32];
   const int row = blockIdx.x;
   const int nv = D >> 3;
+  pdl_launch_dependents();
   pdl_wait();
   const BF8* xr = reinterpret_cast<const BF8*>(x + size_t(row) * ldx);
   if (block == 0) {
@@ -507,8 +514,7 @@ cudaError_t quant_fp8_launch(const __nv_bfloat16* x, int rows, int D, int ldx, u
   if (D % 8 || ldx % 8 || (block && D % 128)) return cudaErrorInvalidValue;
   int threads = ((D / 8) + 31) / 32 * 32;
   if (threads > 1024) threads = 1024;
-  bump_launch_counter();
-  quant_fp8_kernel<<<rows, threads, 0, s>>>(x, D, ldx, y, scale, block);
+  PB_LAUNCH(quant_fp8_kernel, rows, threads, s, x, D, ldx, y, scale, block);
   return cudaGetLastError();
 }
 

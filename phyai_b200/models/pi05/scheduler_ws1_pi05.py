@@ -59,6 +59,11 @@ class PI05WS1Scheduler(Scheduler):
     def setup(self) -> None:
         if not self.use_plan:
             return
+        import os
+
+        from ... import ops
+
+        ops.set_pdl(os.environ.get("PHYAI_PDL", "1") not in ("0", "false", "off"))
         self.plan = PI05Plan(self.model, max_batch_size=self.max_batch_size, num_images=self.num_images,
                              device=self.device)
         self.plan.build_modulation_tables()

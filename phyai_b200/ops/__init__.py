@@ -22,6 +22,7 @@ ACT = {"none": 0, None: 0, "gelu_tanh": 1, "gelu_pytorch_tanh": 1, "silu": 2, "s
 NORM = {"rms": 0, "gemma_rms": 1, "layer": 2, "ada_rms": 3, "rms_noweight": 4}
 
 _ext = None
+ATTN_IMPL = __import__("os").environ.get("PHYAI_ATTN_IMPL", "tc")
 
 
 def ext():
@@ -62,6 +63,16 @@ def reset_launch_counter() -> None:
     ext().reset_launch_counter()
 
 
+def set_pdl(on: bool) -> None:
+    """Launch the library's kernels with programmatic dependent launch: a kernel's set-up
+    and weight prefetch overlap the tail of its predecessor (also inside captured graphs)."""
+    ext().set_pdl(bool(on))
+
+
+def pdl_enabled() -> bool:
+    return ext().pdl_enabled()
+
+
 def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *,
          bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
          res_mod: int = 0, col_gate: Optional[torch.Tensor] = None,
@@ -89,19 +100,22 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[t
               q_start: torch.Tensor, q_len: torch.Tensor, kv_indptr: torch.Tensor,
               kv_len: torch.Tensor, *, kv_indices: Optional[torch.Tensor] = None,
               max_q_len: int, causal: bool = False, splits: int = 1,
-              sm_scale: Optional[float] = None) -> torch.Tensor:
+              sm_scale: Optional[float] = None, impl: Optional[str] = None) -> torch.Tensor:
     """Ragged / paged attention (see ``csrc/attention.cuh``).
 
     ``q`` ``(tokens, Hq, D)``; ``k``/``v`` ``(rows, Hkv, D)`` pools; sequence ``b`` owns
     query tokens ``q_start[b] + [0, q_len[b])`` and KV entries ``kv_indptr[b] +
     [0, kv_len[b])``, mapped to pool rows through ``kv_indices`` when given.
+    ``impl``: ``"tc"`` (tcgen05 + tensor memory, the default) or ``"mma"`` (mma.sync).
     """
+    if impl is None:
+        impl = ATTN_IMPL
     if out is None:
         out = torch.empty_like(q)
     if sm_scale is None:
         sm_scale = q.shape[-1] ** -0.5
     ext().attention(q, k, v, out, q_start, q_len, kv_indptr, kv_len, kv_indices, max_q_len,
-                    causal, splits, sm_scale)
+                    causal, splits, sm_scale, impl == "tc")
     return out
 
 

@@ -121,11 +121,15 @@ ATTN_CASES = [
     dict(B=1, ql=333, kl=500, Hq=4, Hkv=4, D=128, causal=True, splits=2),
     dict(B=1, ql=10, kl=26, Hq=4, Hkv=1, D=32, paged=True),
     dict(B=2, ql=64, kl=0, Hq=2, Hkv=2, D=64),
+    dict(B=1, ql=300, kl=1500, Hq=4, Hkv=2, D=128),
+    dict(B=1, ql=700, kl=700, Hq=2, Hkv=1, D=256, causal=True),
+    dict(B=2, ql=200, kl=900, Hq=8, Hkv=8, D=64, splits=4),
 ]
 
 
+@pytest.mark.parametrize("impl", ["tc", "mma"])
 @pytest.mark.parametrize("case", ATTN_CASES, ids=lambda c: "-".join(f"{k}{v}" for k, v in c.items()))
-def test_attention(case):
+def test_attention(case, impl):
     from phyai_b200 import ops
     from phyai_b200.ops import ref
 
@@ -140,7 +144,7 @@ def test_attention(case):
     kv_ptr, kv_len = ar * kl, torch.full((B,), kl, device=DEV, dtype=torch.int32)
     idx = torch.randperm(R, device=DEV)[: B * kl].int() if paged else None
     o = ops.attention(q, k, v, None, q_start, q_len, kv_ptr, kv_len, kv_indices=idx, max_q_len=ql, causal=causal,
-                      splits=splits)
+                      splits=splits, impl=impl)
     _status_ok()
     e = ref.attention(q, k, v, q_start.cpu(), q_len.cpu(), kv_ptr.cpu(), kv_len.cpu(), kv_indices=idx, causal=causal)
     assert relerr(o, e) < TOL if kl else float(o.abs().max()) == 0.0
@@ -180,7 +184,7 @@ def test_norm_fp8_outputs():
         sc = torch.empty((64, 8) if blk else (64,), device=DEV)
         y = ops.norm(x, "rms", weight=w, y8=y8, y8_scale=sc, y8_block=blk)
         q, s = ref.quant_fp8(y, blk)
-        assert relerr(sc, s) < 1e-5 and relerr(y8.float(), q.float()) < 0.07
+        assert relerr(sc, s) < 1e-5 and relerr(y8.float(), q.float()) < 0.08
 
 
 def test_rope_kv_and_small_ops():
@@ -234,5 +238,5 @@ def test_rope_kv_and_small_ops():
         xq = torch.randn(64, 1024, device=DEV).bfloat16()
         y, sc = ops.quant_fp8(xq, blk)
         ye, se = ref.quant_fp8(xq, blk)
-        assert relerr(sc, se) < 1e-5 and relerr(y.float(), ye.float()) < 0.07
+        assert relerr(sc, se) < 1e-5 and relerr(y.float(), ye.float()) < 0.08
     _status_ok()
