@@ -22,13 +22,15 @@
 #include "launch.cuh"
 #include "ptx.cuh"
 
+#include <cstring>
+
 namespace pb {
 
 namespace {
 
 constexpr int kTQ = 128;         // query rows per CTA = UMMA M
 constexpr int kTK = 128;         // KV entries per chunk = UMMA N of S, K of PV
-constexpr int kTcThreads = 160;  // warps 0-3: softmax / epilogue, warp 4: MMA issue + TMEM
+constexpr int kTcThreads = 256;  // warps 0-3: softmax, warp 4: MMA issue + TMEM, all 8: loads / merge
 constexpr int kBlkBytes = 128 * 128;  // one [128 rows x 128 B] swizzled block
 
 __device__ __forceinline__ void cp16(uint32_t dst, const void* src, bool valid) {
@@ -49,7 +51,9 @@ __device__ __forceinline__ uint32_t sw_off(int r, int c) {
 
 template <int DB>  // head dim padded to 64 * DB
 __global__ void __launch_bounds__(kTcThreads)
-attn_tc_kernel(AttnParams p, int* status) {
+attn_tc_kernel(AttnParams p, int* status, const __grid_constant__ CUtensorMap tmQ,
+               const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+               int use_tma) {
   constexpr int DP = 64 * DB;
   constexpr int CH = DP / 8;                  // 16-byte chunks per Q/K/V row
   constexpr int Q_BYTES = DB * kBlkBytes;     // also K and V chunk bytes
@@ -61,12 +65,15 @@ attn_tc_kernel(AttnParams p, int* status) {
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
   const uint32_t sQ = smem_u32(smem), sK = sQ + Q_BYTES, sV = sK + Q_BYTES, sP = sV + Q_BYTES;
-  __shared__ __align__(8) uint64_t bar_s, bar_o;
+  __shared__ __align__(8) uint64_t bar_s, bar_o, bar_k, bar_v;
   __shared__ uint32_t tmem_base_s;
   __shared__ int err_s;
   __shared__ float m_s[kTQ], l_s[kTQ];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  unsigned long long* tr = p.trace ? p.trace + 16 * (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)) : nullptr;
+#define PB_STAMP(i) do { if (tr && tid == 0) tr[i] = globaltimer_ns(); } while (0)
+  PB_STAMP(0);
   const int nsplit = p.splits;
   const int b = blockIdx.z / nsplit, split = blockIdx.z % nsplit;
   const int kvh = blockIdx.y, G = p.group;
@@ -77,6 +84,8 @@ attn_tc_kernel(AttnParams p, int* status) {
   if (tid == 0) {
     mbar_init(&bar_s, 1);
     mbar_init(&bar_o, 1);
+    mbar_init(&bar_k, 1);
+    mbar_init(&bar_v, 1);
     err_s = 0;
     mbar_fence_init();
   }
@@ -90,6 +99,7 @@ attn_tc_kernel(AttnParams p, int* status) {
   const uint32_t tmem = tmem_base_s;
   pdl_launch_dependents();
   pdl_wait();
+  PB_STAMP(1);
 
   float m_run = -INFINITY, l_run = 0.f;       // softmax threads: tid = row in tile
   const int my_tok = (row0 + tid) / G;
@@ -128,10 +138,34 @@ attn_tc_kernel(AttnParams p, int* status) {
       cp_commit();
     };
 
+    // TMA path (dense q, contiguous KV): one thread issues DB box loads per operand; the
+    // boxes are (64 d) x (G heads) x (128/G tokens) for Q and (64 d) x 1 x 128 rows for K/V,
+    // columns past head_dim and rows past the tensor are zero-filled by the hardware.
+    auto tma_q_k = [&](int chunk, bool with_q) {
+      if (tid == 0) {
+        mbar_expect_tx(&bar_k, uint32_t((with_q ? 2 : 1) * Q_BYTES));
+        for (int blk = 0; blk < DB; ++blk) {
+          if (with_q) tma_load_3d(sQ + blk * kBlkBytes, &tmQ, &bar_k, blk * 64, kvh * G, q_start + row0 / G);
+          tma_load_3d(sK + blk * kBlkBytes, &tmK, &bar_k, blk * 64, kvh, kv_base + chunk * kTK);
+        }
+      }
+    };
+    auto tma_v = [&](int chunk) {
+      if (tid == 0) {
+        mbar_expect_tx(&bar_v, uint32_t(Q_BYTES));
+        for (int blk = 0; blk < DB; ++blk)
+          tma_load_3d(sV + blk * kBlkBytes, &tmV, &bar_v, blk * 64, kvh, kv_base + chunk * kTK);
+      }
+    };
     if (c_begin < c_end) {
-      load_rows(sQ, p.q, 0, true);
-      load_rows(sK, p.k, c_begin, false);
-      load_rows(sV, p.v, c_begin, false);
+      if (use_tma) {
+        tma_q_k(c_begin, true);
+        tma_v(c_begin);
+      } else {
+        load_rows(sQ, p.q, 0, true);
+        load_rows(sK, p.k, c_begin, false);
+        load_rows(sV, p.v, c_begin, false);
+      }
     }
     const float scale_log2 = p.sm_scale * 1.4426950408889634f;
     const uint32_t idesc_s = make_idesc_f16(kTQ, kTK, 1);
@@ -141,9 +175,17 @@ attn_tc_kernel(AttnParams p, int* status) {
     for (int ch = c_begin; ch < c_end; ++ch) {
       const uint32_t ph = uint32_t(n_done & 1);
       // ---- operands of this chunk are in shared memory
-      cp_wait_all();
-      fence_proxy_async_smem();
+      if (use_tma) {
+        if (warp == 4) {
+          if (!mbar_wait(&bar_k, ph)) err_s = kStatusTimeoutFull;
+          if (!mbar_wait(&bar_v, ph)) err_s = kStatusTimeoutFull;
+        }
+      } else {
+        cp_wait_all();
+        fence_proxy_async_smem();
+      }
       __syncthreads();
+      if (ch == c_begin) PB_STAMP(2);
       if (err_s) break;
       // ---- S = Q K^T
       if (warp == 4) {
@@ -222,9 +264,12 @@ attn_tc_kernel(AttnParams p, int* status) {
         tc_fence_before();
       }
       __syncthreads();
+      if (ch == c_begin) PB_STAMP(3);
       if (err_s) break;
       // K is free: start fetching the next chunk's K while P V runs
-      if (ch + 1 < c_end) load_rows(sK, p.k, ch + 1, false);
+      if (ch + 1 < c_end) {
+        if (use_tma) tma_q_k(ch + 1, false); else load_rows(sK, p.k, ch + 1, false);
+      }
       // ---- O += P V
       if (warp == 4) {
         tc_fence_after();
@@ -242,94 +287,141 @@ attn_tc_kernel(AttnParams p, int* status) {
       if (!mbar_wait(&bar_o, ph)) err_s = kStatusTimeoutAcc;   // P, V (and S) are free again
       tc_fence_after();
       __syncthreads();
+      if (ch == c_begin) PB_STAMP(4);
       if (err_s) break;
-      if (ch + 1 < c_end) load_rows(sV, p.v, ch + 1, false);
+      if (ch + 1 < c_end) {
+        if (use_tma) tma_v(ch + 1); else load_rows(sV, p.v, ch + 1, false);
+      }
       ++n_done;
     }
     cp_wait_all();
   }
   __syncthreads();
+  PB_STAMP(5);
   const int err = err_s;
 
-  // ---------------- stage (O, m, l) in shared memory for the merge
-  float* so = reinterpret_cast<float*>(smem);   // Q/K/V/P are dead: reuse as [128][LDO] fp32
-  if (cta_live && !err && warp < 4) {
-    const uint32_t lane_addr = tmem + (uint32_t((warp & 3) * 32) << 16);
+  // ---------------- write-out
+  const uint32_t so_addr = smem_u32(smem), m_addr = smem_u32(m_s), l_addr = smem_u32(l_s);
+  if (nsplit == 1) {
+    // No split: the thread that owns a row normalises it straight out of tensor memory.
+    if (cta_live && !err && warp < 4) {
+      const int row = row0 + tid;
+      const bool live_row = row < rows_total;
+      const uint32_t lane_addr = tmem + (uint32_t((warp & 3) * 32) << 16);
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      __nv_bfloat16* dst = p.out;
+      if (live_row) dst += size_t(q_start + row / G) * p.o_tok_stride + size_t(kvh * G + row % G) * p.o_head_stride;
 #pragma unroll 1
-    for (int c = 0; c < DP; c += 32) {
-      uint32_t r[32];
-      if (n_done > 0) {
-        tc_fence_after();
-        tmem_ld_32x32(lane_addr + O_COL + c, r);
-        tmem_ld_wait();
-      } else {
+      for (int c = 0; c < DP; c += 32) {
+        uint32_t r[32];
+        if (n_done > 0) {
+          tc_fence_after();
+          tmem_ld_32x32(lane_addr + O_COL + c, r);
+          tmem_ld_wait();
+        } else {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) r[j] = 0u;
-      }
-      float4* dst = reinterpret_cast<float4*>(so + tid * LDO + c);
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+        if (live_row) {
 #pragma unroll
-      for (int t = 0; t < 8; ++t)
-        dst[t] = make_float4(__uint_as_float(r[4 * t]), __uint_as_float(r[4 * t + 1]),
-                             __uint_as_float(r[4 * t + 2]), __uint_as_float(r[4 * t + 3]));
-    }
-    m_s[tid] = m_run;
-    l_s[tid] = l_run;
-    tc_fence_before();
-  }
-  __syncthreads();
-  if (nsplit > 1) cluster_sync_all();
-
-  // ---------------- merge the splits and write this CTA's rows
-  if (cta_live && !err) {
-    const int rpc = kTQ / nsplit;
-    const uint32_t so_addr = smem_u32(smem), m_addr = smem_u32(m_s), l_addr = smem_u32(l_s);
-    constexpr int G4 = DP / 4;
-    for (int g = tid; g < rpc * G4; g += kTcThreads) {
-      const int r = split * rpc + g / G4, c = (g % G4) * 4;
-      const int row = row0 + r;
-      if (row >= rows_total || c >= p.head_dim) continue;
-      float mv[8], lv[8];
-      float4 ov[8];
-      float mmax = -INFINITY;
+          for (int t = 0; t < 4; ++t) {
+            if (c + 8 * t < p.head_dim) {
+              uint4 o;
+              __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-      for (int s2 = 0; s2 < 8; ++s2) {
-        if (s2 < nsplit) {
-          if (nsplit == 1) {
-            mv[s2] = m_s[r]; lv[s2] = l_s[r];
-            ov[s2] = *reinterpret_cast<const float4*>(so + r * LDO + c);
-          } else {
-            mv[s2] = ld_dsmem_f1(map_to_cta(m_addr + r * 4, s2));
-            lv[s2] = ld_dsmem_f1(map_to_cta(l_addr + r * 4, s2));
-            ov[s2] = ld_dsmem_f4(map_to_cta(so_addr + uint32_t(r * LDO + c) * 4u, s2));
+              for (int e = 0; e < 4; ++e)
+                o2[e] = __floats2bfloat162_rn(__uint_as_float(r[8 * t + 2 * e]) * inv,
+                                              __uint_as_float(r[8 * t + 2 * e + 1]) * inv);
+              *reinterpret_cast<uint4*>(dst + c + 8 * t) = o;
+            }
           }
-          mmax = fmaxf(mmax, mv[s2]);
         }
       }
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      float lsum = 0.f;
-      if (mmax != -INFINITY) {
+      tc_fence_before();
+    }
+    PB_STAMP(8);
+  } else {
+    // Split KV: stage this CTA's partial (O, m, l) in its own shared memory, then every CTA
+    // finishes 128/S rows by pulling the S partial rows through distributed shared memory.
+    // One warp per row, lanes along the columns (coalesced remote reads, all S of them in
+    // flight together), row-invariant work (weights, output pointer) done once per row.
+    float* so = reinterpret_cast<float*>(smem);
+    if (cta_live && !err && warp < 4) {
+      const uint32_t lane_addr = tmem + (uint32_t((warp & 3) * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < DP; c += 32) {
+        uint32_t r[32];
+        if (n_done > 0) {
+          tc_fence_after();
+          tmem_ld_32x32(lane_addr + O_COL + c, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+        float4* dst = reinterpret_cast<float4*>(so + tid * LDO + c);
+#pragma unroll
+        for (int t = 0; t < 8; ++t)
+          dst[t] = make_float4(__uint_as_float(r[4 * t]), __uint_as_float(r[4 * t + 1]),
+                               __uint_as_float(r[4 * t + 2]), __uint_as_float(r[4 * t + 3]));
+      }
+      m_s[tid] = m_run;
+      l_s[tid] = l_run;
+      tc_fence_before();
+    }
+    __syncthreads();
+    PB_STAMP(7);
+    cluster_sync_all();
+    PB_STAMP(8);
+    if (cta_live && !err) {
+      const int rpc = kTQ / nsplit;
+      for (int lr = warp; lr < rpc; lr += kTcThreads / 32) {
+        const int r = split * rpc + lr;
+        const int row = row0 + r;
+        if (row >= rows_total) continue;
+        float mv[8], wv[8];
+        float mmax = -INFINITY, lsum = 0.f;
+#pragma unroll
+        for (int s2 = 0; s2 < 8; ++s2)
+          if (s2 < nsplit) { mv[s2] = ld_dsmem_f1(map_to_cta(m_addr + r * 4, s2)); mmax = fmaxf(mmax, mv[s2]); }
 #pragma unroll
         for (int s2 = 0; s2 < 8; ++s2) {
-          if (s2 < nsplit) {
-            const float w = exp2f(mv[s2] - mmax);
-            lsum += lv[s2] * w;
-            acc.x += ov[s2].x * w; acc.y += ov[s2].y * w; acc.z += ov[s2].z * w; acc.w += ov[s2].w * w;
+          wv[s2] = 0.f;
+          if (s2 < nsplit && mmax != -INFINITY) {
+            wv[s2] = exp2f(mv[s2] - mmax);
+            lsum += ld_dsmem_f1(map_to_cta(l_addr + r * 4, s2)) * wv[s2];
           }
         }
+        const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+        __nv_bfloat16* dst = p.out + size_t(q_start + row / G) * p.o_tok_stride +
+                             size_t(kvh * G + row % G) * p.o_head_stride;
+#pragma unroll
+        for (int c = lane * 4; c < DP; c += 128) {
+          if (c >= p.head_dim) continue;
+          float4 ov[8];
+#pragma unroll
+          for (int s2 = 0; s2 < 8; ++s2)
+            if (s2 < nsplit) ov[s2] = ld_dsmem_f4(map_to_cta(so_addr + uint32_t(r * LDO + c) * 4u, s2));
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int s2 = 0; s2 < 8; ++s2)
+            if (s2 < nsplit) {
+              acc.x += ov[s2].x * wv[s2]; acc.y += ov[s2].y * wv[s2];
+              acc.z += ov[s2].z * wv[s2]; acc.w += ov[s2].w * wv[s2];
+            }
+          const __nv_bfloat162 o01 = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+          const __nv_bfloat162 o23 = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+          uint2 raw;
+          raw.x = *reinterpret_cast<const uint32_t*>(&o01);
+          raw.y = *reinterpret_cast<const uint32_t*>(&o23);
+          *reinterpret_cast<uint2*>(dst + c) = raw;
+        }
       }
-      const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-      __nv_bfloat16* dst = p.out + size_t(q_start + row / G) * p.o_tok_stride +
-                           size_t(kvh * G + row % G) * p.o_head_stride + c;
-      const __nv_bfloat162 o01 = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
-      const __nv_bfloat162 o23 = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
-      uint2 raw;
-      raw.x = *reinterpret_cast<const uint32_t*>(&o01);
-      raw.y = *reinterpret_cast<const uint32_t*>(&o23);
-      *reinterpret_cast<uint2*>(dst) = raw;
     }
   }
+  PB_STAMP(9);
   if (err && tid == 0 && status) atomicCAS(status, 0, err);
-  if (nsplit > 1) cluster_sync_all();
+  if (nsplit > 1) cluster_sync_all();  // peers may still be reading this CTA's partial rows
   tc_fence_before();
   __syncthreads();
   if (warp == 4) tmem_dealloc(tmem, TMEM_COLS);
@@ -345,9 +437,24 @@ static cudaError_t attn_tc_launch_db(const AttnParams& p, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
     attr_done = true;
   }
+  // TMA needs dense, 16-byte aligned operands and a group size that tiles 128 rows
+  CUtensorMap tq, tk, tv;
+  memset(&tq, 0, sizeof(tq)); memset(&tk, 0, sizeof(tk)); memset(&tv, 0, sizeof(tv));
+  int use_tma = 0;
+  const auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  if (!p.kv_indices && p.q_rows > 0 && p.kv_rows > 0 && (kTQ % p.group) == 0 && al16(p.q) && al16(p.k) &&
+      al16(p.v)) {
+    const int Hq = p.num_kv_heads * p.group;
+    use_tma = make_tmap_3d_bf16(&tq, p.q, p.head_dim, Hq, p.q_rows, p.q_head_stride, p.q_tok_stride,
+                                p.group, kTQ / p.group) &&
+              make_tmap_3d_bf16(&tk, p.k, p.head_dim, p.num_kv_heads, p.kv_rows, p.kv_head_stride,
+                                p.kv_row_stride, 1, kTK) &&
+              make_tmap_3d_bf16(&tv, p.v, p.head_dim, p.num_kv_heads, p.kv_rows, p.kv_head_stride,
+                                p.kv_row_stride, 1, kTK);
+  }
   const int max_rows = p.max_q_len * p.group;
   return launch_kernel(kern, dim3((max_rows + kTQ - 1) / kTQ, p.num_kv_heads, p.batch * p.splits),
-                       dim3(kTcThreads), smem, stream, p.splits, p, kernel_status_ptr());
+                       dim3(kTcThreads), smem, stream, p.splits, p, kernel_status_ptr(), tq, tk, tv, use_tma);
 }
 
 cudaError_t attn_tc_launch(const AttnParams& p, cudaStream_t stream) {

@@ -26,6 +26,7 @@
 #include <cstdlib>
 #include <mutex>
 #include <unordered_map>
+#include <vector>
 
 #include "gemm_epilogue.cuh"
 #include "launch.cuh"
@@ -315,6 +316,38 @@ static bool make_tmap(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t
   std::lock_guard<std::mutex> g(mu);
   if (cache.size() > 65536) cache.clear();
   cache.emplace(key, *out);
+  return true;
+}
+
+// 3-D bf16 view (d, head, row): extents {D, H, R}, byte strides {head_stride, row_stride};
+// box = 64 elements x box_h heads x box_r rows, 128-byte swizzle, zero fill outside.
+bool make_tmap_3d_bf16(CUtensorMap* out, const void* ptr, uint64_t D, uint64_t H, uint64_t R,
+                       uint64_t head_stride_elems, uint64_t row_stride_elems, uint32_t box_h,
+                       uint32_t box_r) {
+  struct K3 { const void* p; uint64_t d, h, r, hs, rs; uint32_t bh, br; };
+  static std::mutex mu;
+  static std::vector<std::pair<K3, CUtensorMap>> cache;
+  {
+    std::lock_guard<std::mutex> g(mu);
+    for (auto& e : cache) {
+      const K3& k = e.first;
+      if (k.p == ptr && k.d == D && k.h == H && k.r == R && k.hs == head_stride_elems &&
+          k.rs == row_stride_elems && k.bh == box_h && k.br == box_r) { *out = e.second; return true; }
+    }
+  }
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return false;
+  cuuint64_t dims[3] = {D, H, R};
+  cuuint64_t strides[2] = {head_stride_elems * 2, row_stride_elems * 2};
+  cuuint32_t box[3] = {64, box_h, box_r};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  std::lock_guard<std::mutex> g(mu);
+  if (cache.size() > 4096) cache.clear();
+  cache.push_back({K3{ptr, D, H, R, head_stride_elems, row_stride_elems, box_h, box_r}, *out});
   return true;
 }
 

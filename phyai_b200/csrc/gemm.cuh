@@ -1,5 +1,6 @@
 // Host-visible declarations for the tcgen05 GEMM family (see gemm.cu).
 #pragma once
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -48,6 +49,11 @@ struct GemmArgs {
 // Launches on `stream`. Returns cudaSuccess or the launch error; argument
 // problems (alignment, unsupported shape) return cudaErrorInvalidValue.
 cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream);
+
+// 3-D bf16 tensor map (d, head, row) for the attention kernels (see gemm.cu).
+bool make_tmap_3d_bf16(CUtensorMap* out, const void* ptr, uint64_t D, uint64_t H, uint64_t R,
+                       uint64_t head_stride_elems, uint64_t row_stride_elems, uint32_t box_h,
+                       uint32_t box_r);
 
 // Device-global status word shared by the kernels of this library (0 = ok).
 int* kernel_status_ptr();

@@ -150,10 +150,13 @@ __global__ void norm_kernel(NormArgs a) {
       for (int i = 0; i < 8; ++i)
         o[i] = f[i] * rstd * (MODE == kNormGemmaRms ? 1.f + w[i] : w[i]);
     }
-    if (a.y) yr[v] = pack8(o);
+    const BF8 packed = pack8(o);
+    if (a.y) yr[v] = packed;
     if (a.y8) {
+      float q8[8];
+      unpack8(packed, q8);  // the fp8 copy quantises the rounded bf16 values
 #pragma unroll
-      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(o[i]));
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(q8[i]));
     }
   }
   if (a.y8) {

@@ -14,10 +14,11 @@ CUDA graph per prompt-length bucket:
   residual epilogue, AdaRMSNorm, gate-up GEMM with GeGLU epilogue, down GEMM with gated
   residual epilogue (the reference needs ~13, modeling_pi05.py:801-835).
 
-KV pool layout: robot ``b`` owns slots ``1 + b*(P+C) + [0, P)`` for its prefix rows and the
-next ``C`` for its action tokens (``P`` = max prefix rows, ``C`` = chunk). Slot 0 is unused
-padding. Prefix attention reads a contiguous range; joint attention reads through an
-index list that skips the unused tail of the prefix slab.
+KV pool layout: robot ``b`` owns the slab of slots ``1 + b*(P+C) + [0, P+C)`` (``P`` = max
+prefix rows, ``C`` = chunk; slot 0 is unused padding). Its real prefix rows fill the start of
+the slab and its action tokens are written directly behind them, so both the prefix
+attention and the joint attention read one contiguous slot range and the attention kernel
+can fetch K/V tiles with TMA instead of per-row gathers.
 """
 
 from __future__ import annotations
@@ -126,15 +127,15 @@ class PI05Plan:
         self.e_slots = torch.zeros(Me, dtype=torch.int64, device=dev)
         self.e_qstart = torch.arange(B, dtype=torch.int32, device=dev) * self.C
         self.e_qlen = torch.full((B,), self.C, dtype=torch.int32, device=dev)
-        self.e_kvptr = torch.arange(B, dtype=torch.int32, device=dev) * self.slab
+        self.e_kvptr = torch.tensor([1 + b * self.slab for b in range(B)], dtype=torch.int32, device=dev)
         self.e_kvlen = torch.zeros(B, dtype=torch.int32, device=dev)
-        self.e_kvidx = torch.zeros(B * self.slab, dtype=torch.int32, device=dev)
         self.out = buf(B, self.C, cfg.max_action_dim)
         self.mod_in: list[torch.Tensor] = []
         self.mod_post: list[torch.Tensor] = []
         self.mod_final: torch.Tensor | None = None
         self.dt = -1.0 / cfg.num_inference_steps
         self.expert_splits = 8
+        self.prefix_splits = 2 if B == 1 else 1
         self._layout_key = None
 
     # ------------------------------------------------------------------ setup
@@ -176,14 +177,8 @@ class PI05Plan:
         self.lang_rows.copy_(rows.flatten())
         c = torch.arange(self.C, dtype=torch.int64)
         self.e_pos.copy_(torch.cat([real[b] + c for b in range(B)]).to(torch.int32))
-        self.e_slots.copy_(torch.cat([base[b] + self.P + c for b in range(B)]))
+        self.e_slots.copy_(torch.cat([base[b] + real[b] + c for b in range(B)]))
         self.e_kvlen.copy_(torch.tensor([r + self.C for r in real], dtype=torch.int32))
-        idx = torch.zeros(B, self.slab, dtype=torch.int32)
-        for b in range(B):
-            r = real[b]
-            idx[b, :r] = base[b] + torch.arange(r, dtype=torch.int32)
-            idx[b, r:r + self.C] = base[b] + self.P + torch.arange(self.C, dtype=torch.int32)
-        self.e_kvidx.copy_(idx.flatten())
         self._layout_key = key
         return True
 
@@ -234,7 +229,7 @@ class PI05Plan:
             if li == last:
                 break  # only this block's K/V are consumed downstream
             ops.attention(q3, kpool, vpool, a3, self.p_qstart, self.p_qlen, self.p_kvptr, self.p_kvlen,
-                          max_q_len=n_per, sm_scale=D ** -0.5)
+                          max_q_len=n_per, splits=self.prefix_splits, sm_scale=D ** -0.5)
             ops.gemm(attn, layer.attn.o.weight, h, residual=h)
             ops.norm(h, "gemma_rms", weight=layer.post_attention_layernorm.weight, eps=t.rms_norm_eps, out=x)
             ops.gemm(x, layer.mlp.gate_up.weight, act, act="gelu_tanh", glu=True)
@@ -257,7 +252,7 @@ class PI05Plan:
                 ops.rope_kv(self.e_qkv, Hq, Hkv, D, self.e_q, pos=self.e_pos, cos_sin=self.cos_sin, k_pool=kpool,
                             v_pool=vpool, slots=self.e_slots)
                 ops.attention(q3, kpool, vpool, a3, self.e_qstart, self.e_qlen, self.e_kvptr, self.e_kvlen,
-                              kv_indices=self.e_kvidx, max_q_len=self.C, splits=self.expert_splits, sm_scale=D ** -0.5)
+                              max_q_len=self.C, splits=self.expert_splits, sm_scale=D ** -0.5)
                 ops.gemm(self.e_attn, layer.attn.o.weight, h, residual=h, col_gate=m_in[0, 2 * He:])
                 ops.norm(h, "ada_rms", mod=m_post, group=Me, eps=e.rms_norm_eps, out=x)
                 ops.gemm(x, layer.mlp.gate_up.weight, self.e_act, act="gelu_tanh", glu=True)

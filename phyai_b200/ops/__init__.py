@@ -100,7 +100,8 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[t
               q_start: torch.Tensor, q_len: torch.Tensor, kv_indptr: torch.Tensor,
               kv_len: torch.Tensor, *, kv_indices: Optional[torch.Tensor] = None,
               max_q_len: int, causal: bool = False, splits: int = 1,
-              sm_scale: Optional[float] = None, impl: Optional[str] = None) -> torch.Tensor:
+              sm_scale: Optional[float] = None, impl: Optional[str] = None,
+              trace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Ragged / paged attention (see ``csrc/attention.cuh``).
 
     ``q`` ``(tokens, Hq, D)``; ``k``/``v`` ``(rows, Hkv, D)`` pools; sequence ``b`` owns
@@ -115,7 +116,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[t
     if sm_scale is None:
         sm_scale = q.shape[-1] ** -0.5
     ext().attention(q, k, v, out, q_start, q_len, kv_indptr, kv_len, kv_indices, max_q_len,
-                    causal, splits, sm_scale, impl == "tc")
+                    causal, splits, sm_scale, impl == "tc", trace)
     return out
 
 
