@@ -74,7 +74,7 @@ def build_index(model: torch.nn.Module) -> tuple[dict[str, tuple[torch.nn.Parame
             if k in index and index[k][0] is not p:
                 raise ValueError(f"checkpoint key {k!r} is claimed by both {index[k][2]!r} and {name!r}")
             index[k] = (p, sid, name)
-            if getattr(p, "optional", False):
+            if getattr(p, "optional", False) or getattr(p, "hf_alternatives", False):
                 optional.add(k)
     return index, optional
 
