@@ -1,0 +1,102 @@
+"""Static execution plan of Pi0 on B200 (vision and prefix stages are Pi0.5's).
+
+Expert stage: one pass for the state token of every robot (its K/V land in the slot right
+behind the robot's real prefix rows), then the 10-step Euler loop over the action tokens,
+whose K/V follow the state slot, so every attention call reads one contiguous slot range.
+The ``cat(action_emb, time_emb) -> Linear(2H, H)`` of the reference is evaluated as
+``W_a (W_in x + b_in) + (W_t time_emb + b)``: the two input projections are folded into one
+``(H, action_dim)`` weight at set-up and the time half becomes a per-step bias row.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ... import ops
+from ..pi05.plan_pi05 import PI05Layout, PI05Plan
+from .modeling_pi0 import PI0Model
+
+
+class PI0Plan(PI05Plan):
+    suffix_extra = 1
+
+    def __init__(self, model: PI0Model, *, max_batch_size: int = 1, num_images: int = 3, device="cuda") -> None:
+        super().__init__(model, max_batch_size=max_batch_size, num_images=num_images, device=device)
+        cfg, dev, B = self.cfg, self.device, self.B
+        He = cfg.expert.hidden_size
+        bf = torch.bfloat16
+        self.state = torch.zeros(B, cfg.max_state_dim, dtype=bf, device=dev)
+        self.s_h = torch.zeros(B, He, dtype=bf, device=dev)
+        self.s_x = torch.zeros(B, He, dtype=bf, device=dev)
+        self.s_qkv = torch.zeros(B, self.e_qkv.shape[1], dtype=bf, device=dev)
+        self.s_q = torch.zeros(B, self.e_q.shape[1], dtype=bf, device=dev)
+        self.s_attn = torch.zeros(B, self.e_q.shape[1], dtype=bf, device=dev)
+        self.s_act = torch.zeros(B, cfg.expert.intermediate_size, dtype=bf, device=dev)
+        self.s_pos = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.s_slots = torch.zeros(B, dtype=torch.int64, device=dev)
+        self.s_qstart = torch.arange(B, dtype=torch.int32, device=dev)
+        self.s_qlen = torch.ones(B, dtype=torch.int32, device=dev)
+        self.s_kvlen = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.e_t = torch.zeros(self.Me, He, dtype=bf, device=dev)
+        self.w_fold: torch.Tensor | None = None
+        self.time_bias: torch.Tensor | None = None
+
+    @torch.no_grad()
+    def build_modulation_tables(self) -> None:
+        """Fold the action/time input projections (call after weights are loaded)."""
+        cfg, heads = self.cfg, self.model.heads
+        H, N = cfg.expert.hidden_size, cfg.num_inference_steps
+        w = heads.action_time_mlp_in.weight.float()
+        wa, wt = w[:, :H], w[:, H:]
+        self.w_fold = (wa @ heads.action_in_proj.weight.float()).to(torch.bfloat16).contiguous()
+        ts = 1.0 + torch.arange(N, dtype=torch.float32, device=self.device) * self.dt
+        te = heads.time_embedding(ts).to(torch.bfloat16).float()
+        bias = te @ wt.t() + heads.action_time_mlp_in.bias.float() + wa @ heads.action_in_proj.bias.float()
+        self.time_bias = bias.to(torch.bfloat16).contiguous()
+
+    def set_layout(self, layout: PI05Layout) -> bool:
+        changed = super().set_layout(layout)
+        if changed:
+            real, base = self._real, self._base
+            self.s_pos.copy_(torch.tensor(real, dtype=torch.int32))
+            self.s_slots.copy_(torch.tensor([b + r for b, r in zip(base, real)], dtype=torch.int64))
+            self.s_kvlen.copy_(torch.tensor([r + 1 for r in real], dtype=torch.int32))
+        return changed
+
+    def _block(self, layer, li, h, x, qkv, q, attn, act, pos, slots, qstart, qlen, kvlen, max_q, splits) -> None:
+        t, e = self.cfg.text, self.cfg.expert
+        Hq, Hkv, D = t.num_attention_heads, t.num_key_value_heads, t.head_dim
+        kpool, vpool = self.pool.layer(li)
+        ops.norm(h, "gemma_rms", weight=layer.input_layernorm.weight, eps=e.rms_norm_eps, out=x)
+        ops.gemm(x, layer.attn.qkv.weight, qkv)
+        ops.rope_kv(qkv, Hq, Hkv, D, q, pos=pos, cos_sin=self.cos_sin, k_pool=kpool, v_pool=vpool, slots=slots)
+        ops.attention(q.unflatten(1, (Hq, D)), kpool, vpool, attn.unflatten(1, (Hq, D)), qstart, qlen, self.e_kvptr,
+                      kvlen, max_q_len=max_q, splits=splits, sm_scale=D ** -0.5)
+        ops.gemm(attn, layer.attn.o.weight, h, residual=h)
+        ops.norm(h, "gemma_rms", weight=layer.post_attention_layernorm.weight, eps=e.rms_norm_eps, out=x)
+        ops.gemm(x, layer.mlp.gate_up.weight, act, act="gelu_tanh", glu=True)
+        ops.gemm(act, layer.mlp.down.weight, h, residual=h)
+
+    def expert(self) -> None:
+        cfg, heads, stack = self.cfg, self.model.heads, self.model.expert_stack
+        Me = self.Me
+        # ---- state token, once per request
+        ops.gemm(self.state, heads.state_proj.weight, self.s_h, bias=heads.state_proj.bias)
+        for li, layer in enumerate(stack.layers):
+            self._block(layer, li, self.s_h, self.s_x, self.s_qkv, self.s_q, self.s_attn, self.s_act, self.s_pos,
+                        self.s_slots, self.s_qstart, self.s_qlen, self.s_kvlen, 1, self.expert_splits)
+        # ---- Euler loop over the action tokens
+        self.x_t.copy_(self.noise.view(Me, -1))
+        for i in range(cfg.num_inference_steps):
+            ops.gemm(self.x_t, self.w_fold, self.e_t, bias=self.time_bias[i], act="silu")
+            ops.gemm(self.e_t, heads.action_time_mlp_out.weight, self.e_h, bias=heads.action_time_mlp_out.bias)
+            for li, layer in enumerate(stack.layers):
+                self._block(layer, li, self.e_h, self.e_x, self.e_qkv, self.e_q, self.e_attn, self.e_act, self.e_pos,
+                            self.e_slots, self.e_qstart, self.e_qlen, self.e_kvlen, self.C, self.expert_splits)
+            ops.norm(self.e_h, "gemma_rms", weight=stack.norm.weight, eps=cfg.expert.rms_norm_eps, out=self.e_x)
+            ops.gemm(self.e_x, heads.action_out_proj.weight, self.e_v, bias=heads.action_out_proj.bias)
+            ops.axpy(self.x_t, self.e_v, self.dt)
+        self.out.view(Me, -1).copy_(self.x_t)
+
+
+__all__ = ["PI0Plan"]

@@ -46,6 +46,9 @@ class PI05Layout:
 
 
 class PI05Plan:
+    #: suffix tokens in front of the action tokens (Pi0 puts one state token there)
+    suffix_extra = 0
+
     def __init__(self, model: PI05Model, *, max_batch_size: int = 1, num_images: int = 3,
                  device: torch.device | str = "cuda") -> None:
         cfg = model.config
@@ -59,7 +62,7 @@ class PI05Plan:
         self.img_tokens = v.num_patches * num_images
         self.P = self.img_tokens + cfg.tokenizer_max_length          # max prefix rows per robot
         self.C = cfg.chunk_size
-        self.slab = self.P + self.C
+        self.slab = self.P + self.suffix_extra + self.C
         dev = self.device
         B = self.B
 
@@ -176,9 +179,11 @@ class PI05Plan:
             rows[b, : layout.lang_bucket] = b * n_per + self.img_tokens + torch.arange(layout.lang_bucket, dtype=torch.int32)
         self.lang_rows.copy_(rows.flatten())
         c = torch.arange(self.C, dtype=torch.int64)
-        self.e_pos.copy_(torch.cat([real[b] + c for b in range(B)]).to(torch.int32))
-        self.e_slots.copy_(torch.cat([base[b] + real[b] + c for b in range(B)]))
-        self.e_kvlen.copy_(torch.tensor([r + self.C for r in real], dtype=torch.int32))
+        x = self.suffix_extra
+        self.e_pos.copy_(torch.cat([real[b] + x + c for b in range(B)]).to(torch.int32))
+        self.e_slots.copy_(torch.cat([base[b] + real[b] + x + c for b in range(B)]))
+        self.e_kvlen.copy_(torch.tensor([r + x + self.C for r in real], dtype=torch.int32))
+        self._real, self._base = real, base
         self._layout_key = key
         return True
 

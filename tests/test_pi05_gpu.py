@@ -52,3 +52,35 @@ def test_plan_matches_eager(batch, graph):
     rel2 = (out2.float() - ref2.float()).abs().max() / ref2.float().abs().max()
     assert rel2 < 5e-2, rel2
     eng.close()
+
+
+@pytest.mark.parametrize("batch", [1, 2])
+def test_pi0_plan_matches_eager(batch):
+    from phyai_b200 import ops
+    from phyai_b200.engine import Engine, EngineArgs
+    from phyai_b200.engine_config import DeviceConfig, EngineConfig, RuntimeConfig
+    from phyai_b200.models.pi0.configuration_pi0 import PI0Config
+    from phyai_b200.models.pi0.main_pi0 import PI0Args
+    from phyai_b200.models.pi0.scheduler_ws1_pi0 import PI0Request
+    from phyai_b200.models.pi05.configuration_pi05 import GemmaExpertConfig
+
+    c5 = _mid_config()
+    cfg = PI0Config(vision=c5.vision, text=c5.text,
+                    expert=GemmaExpertConfig(hidden_size=128, num_hidden_layers=3, num_attention_heads=8, num_key_value_heads=1,
+                                             head_dim=256, intermediate_size=256, use_adarms=False, adarms_cond_dim=128),
+                    chunk_size=50, max_state_dim=32, max_action_dim=32, num_inference_steps=4, tokenizer_max_length=48)
+    eng = Engine(EngineArgs("pi0", PI0Args(config=cfg, max_batch_size=2, inputs_image_shape=[[56, 56, 3]] * 2),
+                            EngineConfig(device=DeviceConfig("cuda:0", torch.bfloat16), runtime=RuntimeConfig(use_cuda_graph=True))))
+    g = torch.Generator().manual_seed(10 + batch)
+    lens = torch.tensor([33, 9][:batch])
+    req = PI0Request((torch.rand(batch, 2, 3, 56, 56, generator=g) * 2 - 1).bfloat16().cuda(),
+                     torch.randint(0, 1024, (batch, 48), generator=g).cuda(), lens.cuda(),
+                     torch.randn(batch, 32, generator=g).bfloat16().cuda(), torch.randn(batch, 50, 32, generator=g).bfloat16().cuda())
+    out = eng.step(req)
+    out2 = eng.step(req)
+    torch.cuda.synchronize()
+    assert ops.kernel_status() == 0 and torch.equal(out, out2)
+    ref = eng.entry.model.sample_actions(req.pixel_values, req.input_ids, lens, req.state, req.noise)
+    rel = (out.float() - ref.float()).abs().max() / ref.float().abs().max()
+    assert rel < 5e-2, rel
+    eng.close()
