@@ -1,0 +1,184 @@
+"""Cosmos3 on CPU: sampler, VAE stream equivalence, sound decoder, schedulers and plugins (tiny geometries)."""
+
+import math
+
+import pytest
+import torch
+
+from phyai_b200.models.cosmos3 import (Cosmos3ActionRequest, Cosmos3AVAESoundConfig, Cosmos3T2VRequest, Cosmos3WanVAEConfig,
+                                       UniPCMultistepSampler, pixel_to_latent_shape, tiny_cosmos3_config)
+from phyai_b200.models.cosmos3.avae_sound import Cosmos3AVAESoundDecoder
+from phyai_b200.models.cosmos3.vae_wan import (Cosmos3WanVAE, feather_1d, fold_patches, pool_down, spread_up, tile_grid, tile_span,
+                                               unfold_patches)
+
+
+def CPU_ENGINE():
+    from phyai_b200 import DeviceConfig, EngineConfig, RuntimeConfig
+
+    return EngineConfig(device=DeviceConfig("cpu", torch.float32), runtime=RuntimeConfig(use_cuda_graph=False))
+
+
+def tiny_vae(seed=0):
+    cfg = Cosmos3WanVAEConfig(z_dim=4, decoder_base_dim=8, base_dim=8, dim_mult=(1, 2, 2, 2), num_res_blocks=1,
+                              latents_mean=tuple(0.1 * i for i in range(4)), latents_std=tuple(1.0 + 0.1 * i for i in range(4)))
+    vae = Cosmos3WanVAE(cfg, device="cpu", dtype=torch.float32).eval()
+    g = torch.Generator().manual_seed(seed)
+    for p in vae.parameters():
+        p.data.copy_(torch.randn(p.shape, generator=g) * (0.3 if p.dim() > 1 else 0.1) + (1.0 if "gamma" in str(p.shape) else 0.0))
+    return vae
+
+
+# ---------------------------------------------------------------- sampler
+@pytest.mark.parametrize("karras", [True, False])
+def test_unipc_exact_on_linear_trajectory(karras):
+    """For x_t = (1 - s) x0 + s e the flow velocity e - x0 is constant, and the solver must land on x0."""
+    torch.manual_seed(0)
+    x0, e = torch.randn(2, 3, 5), torch.randn(2, 3, 5)
+    s = UniPCMultistepSampler(flow_shift=3.0, use_karras_sigmas=karras)
+    s.set_timesteps(8)
+    s0 = float(s.sigmas[0])
+    x = (1 - s0) * x0 + s0 * e
+    for t in s.timesteps:
+        x = s.step(e - x0, t, x)
+    assert torch.allclose(x, x0, atol=1e-4)
+
+
+def test_unipc_timesteps_descend_and_reset():
+    s = UniPCMultistepSampler(flow_shift=10.0, use_karras_sigmas=False)
+    s.set_timesteps(12)
+    ts = [float(t) for t in s.timesteps]
+    assert len(ts) == 12 and all(a > b for a, b in zip(ts, ts[1:]))
+    x = torch.ones(3)
+    s.step(torch.zeros(3), s.timesteps[0], x)
+    assert s.step_index == 1
+    s.set_timesteps(12)
+    assert s.step_index in (None, 0)
+
+
+# ---------------------------------------------------------------- VAE
+def test_patch_fold_round_trip_and_shortcuts():
+    x = torch.randn(2, 3, 5, 8, 12)
+    assert torch.equal(unfold_patches(fold_patches(x, 2), 2), x)
+    y = torch.randn(1, 8, 3, 4, 4)
+    up = spread_up(y, 4, 2, 2, drop_first=True)
+    assert up.shape == (1, 4, 5, 8, 8)
+    # every output channel group copies consecutive input channels; mean-pooling a spread tensor recovers a channel average
+    down = pool_down(torch.randn(1, 4, 5, 8, 8), 8, 2, 2)
+    assert down.shape == (1, 8, 3, 4, 4)
+
+
+def test_vae_shapes_and_stream_equivalence():
+    vae = tiny_vae()
+    lat = torch.randn(1, 4, 4, 3, 2)
+    whole = vae.decode(lat)
+    assert whole.shape == (1, 3, 13, 48, 32)
+    for chunk in (1, 2, 3):
+        assert torch.allclose(vae.decode(lat, frames_per_chunk=chunk), whole, atol=1e-5), chunk
+    pix = torch.rand(1, 3, 9, 32, 32) * 2 - 1
+    z = vae.encode(pix)
+    assert z.shape == (1, 4, 3, 2, 2)
+    assert torch.allclose(vae.encode(pix, frames_per_chunk=4), z, atol=1e-5)
+    with pytest.raises(ValueError):
+        vae.encode(torch.zeros(1, 3, 8, 32, 32))
+
+
+def test_vae_is_causal_in_time():
+    vae = tiny_vae(1)
+    lat = torch.randn(1, 4, 3, 2, 2)
+    full = vae.decode(lat)
+    assert torch.allclose(vae.decode(lat[:, :, :2]), full[:, :, :5], atol=1e-5)
+
+
+def test_tile_helpers():
+    assert tile_grid(4) == (2, 2) and tile_grid(8) == (2, 4) and tile_grid(2) == (1, 2) and tile_grid(7) == (1, 7)
+    spans = [tile_span(45, 4, i, 2) for i in range(4)]
+    assert spans[0][0] == 0 and spans[-1][1] == 45
+    assert all(a[1] - 4 == b[0] for a, b in zip(spans, spans[1:]))  # neighbours overlap by 2 * halo
+    w = feather_1d(10, 3, "cpu", torch.float32)
+    assert w[0] == pytest.approx(0.25) and w[4] == 1 and torch.equal(w, w.flip(0))
+
+
+def test_vae_key_names_match_diffusers_layout():
+    names = {n for n, _ in tiny_vae().named_parameters()}
+    for k in ("decoder.conv_in.weight", "decoder.mid_block.attentions.0.to_qkv.weight", "decoder.mid_block.resnets.1.norm2.gamma",
+              "decoder.up_blocks.0.upsampler.time_conv.bias", "decoder.up_blocks.2.upsampler.resample.1.weight",
+              "decoder.up_blocks.1.resnets.0.conv_shortcut.weight" if False else "decoder.up_blocks.3.resnets.1.conv2.weight",
+              "encoder.down_blocks.1.downsampler.time_conv.weight", "encoder.down_blocks.0.downsampler.resample.1.bias",
+              "quant_conv.weight", "post_quant_conv.bias", "encoder.norm_out.gamma"):
+        hf = {h for n, p in tiny_vae().named_parameters() for h in getattr(p, "hf_keys", {})}
+        assert k in hf, k
+    assert len(names) == len({h for n, p in tiny_vae().named_parameters() for h in p.hf_keys})
+
+
+# ---------------------------------------------------------------- sound
+def test_avae_hop_and_range():
+    cfg = Cosmos3AVAESoundConfig(dec_dim=4, latent_ch=6, audio_channels=2, dec_strides=(2, 3), dec_c_mults=(1, 2))
+    dec = Cosmos3AVAESoundDecoder(cfg, dtype=torch.float32, device="cpu")
+    g = torch.Generator().manual_seed(0)
+    for p in dec.parameters():
+        p.data.copy_(torch.randn(p.shape, generator=g) * 0.2)
+    wav = dec.decode(torch.randn(1, 6, 7))
+    assert dec.hop_size == 6 and wav.shape == (1, 2, 42) and wav.abs().max() <= 1
+
+
+# ---------------------------------------------------------------- schedulers through the engine
+def _prompts(B=1, L=5, vocab=256):
+    ids = torch.randint(0, vocab, (B, L))
+    mask = torch.ones(B, L, dtype=torch.long)
+    return ids, mask
+
+
+def test_pixel_to_latent_shape():
+    assert pixel_to_latent_shape(93, 720, 1280) == (24, 45, 80)
+
+
+def test_t2v_plugin_latents_cfg_and_conditioning():
+    from phyai_b200.engine import Engine, EngineArgs
+    from phyai_b200.engine_config import EngineConfig
+    from phyai_b200.models.cosmos3.main_cosmos3 import Cosmos3Args
+
+    cfg = tiny_cosmos3_config(sound_gen=True)
+    eng = Engine(EngineArgs("cosmos3", Cosmos3Args(config=cfg, load_vae=False, load_sound=False), CPU_ENGINE()))
+    ids, mask = _prompts()
+    nids, nmask = _prompts()
+    cond = torch.randn(1, 4, 3, 4, 6)
+    req = Cosmos3T2VRequest(ids, mask, nids, nmask, video_shape=(3, 4, 6), num_inference_steps=3, guidance_scale=2.0,
+                            cond_latents=cond, cond_frame_indexes=(0,))
+    out = eng.step(req)
+    assert out.shape == (1, 4, 3, 4, 6) and torch.isfinite(out).all()
+    assert torch.equal(out[:, :, 0], cond[:, :, 0])
+    again = eng.step(req)
+    assert torch.equal(out, again)  # seeded noise, fresh solver per request
+    snd = eng.step(Cosmos3T2VRequest(ids, mask, nids, nmask, video_shape=(2, 4, 6), num_inference_steps=2, guidance_scale=1.0,
+                                     sound_frames=5, sound_dim=8))
+    assert snd["video"].shape == (1, 4, 2, 4, 6) and snd["sound"].shape == (1, 8, 5)
+    eng.close()
+
+
+@pytest.mark.parametrize("mode", ["policy", "forward_dynamics", "inverse_dynamics"])
+def test_policy_plugin_modes(mode):
+    from phyai_b200.engine import Engine, EngineArgs
+    from phyai_b200.engine_config import EngineConfig
+    from phyai_b200.models.cosmos3.main_cosmos3_policy import Cosmos3PolicyArgs
+
+    cfg = tiny_cosmos3_config(action_gen=True)
+    eng = Engine(EngineArgs("cosmos3_policy", Cosmos3PolicyArgs(config=cfg), CPU_ENGINE()))
+    ids, mask = _prompts()
+    cond_v = torch.randn(1, 4, 2, 4, 6)
+    cond_a = torch.randn(1, 3, 8)
+    req = Cosmos3ActionRequest(ids, mask, ids, mask, video_shape=(2, 4, 6), mode=mode, domain_id=1, action_chunk=3,
+                               raw_action_dim=5, action_dim=8, cond_video_latents=cond_v, cond_action=cond_a,
+                               num_inference_steps=3)
+    act = eng.step(req)
+    assert act.shape == (1, 3, 5) and torch.isfinite(act).all()
+    full = eng.entry.scheduler.step(req)
+    if mode == "forward_dynamics":
+        assert torch.equal(full["action"], cond_a[:, :, :5])
+        assert torch.equal(full["video"][:, :, 0], cond_v[:, :, 0]) and not torch.equal(full["video"][:, :, 1], cond_v[:, :, 1])
+    elif mode == "inverse_dynamics":
+        assert torch.equal(full["video"], cond_v)
+    else:
+        assert torch.equal(full["video"][:, :, 0], cond_v[:, :, 0])
+    with pytest.raises(ValueError):
+        eng.entry.scheduler.step(Cosmos3ActionRequest(ids, mask, ids, mask, (2, 4, 6), "dream", 0, 3, 5, 8))
+    eng.close()
