@@ -4,6 +4,8 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <torch/extension.h>
 
+#include <cstring>
+
 #include "attention.cuh"
 #include "comm.cuh"
 #include "gemm.cuh"
@@ -53,7 +55,8 @@ inline const long long* i64(const OptT& t) {
 void gemm(const Tensor& x, const Tensor& w, Tensor& out, const OptT& bias, const OptT& residual,
           int64_t res_mod, const OptT& col_gate, const OptT& row_scale, const OptT& sumsq,
           int64_t act, bool glu, const OptT& a_scale, const OptT& w_scale, int64_t force_bn,
-          int64_t force_swap, int64_t force_splits, const OptT& trace) {
+          int64_t force_swap, int64_t force_splits, const OptT& trace, int64_t wait_sig_ptr,
+          int64_t wait_channel, int64_t wait_expect) {
   TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2, "gemm: 2-D tensors expected");
   TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1 && out.stride(1) == 1, "gemm: rows must be contiguous");
   TORCH_CHECK(x.size(1) == w.size(1), "gemm: K mismatch");
@@ -84,6 +87,15 @@ void gemm(const Tensor& x, const Tensor& w, Tensor& out, const OptT& bias, const
   if (trace.has_value() && trace->defined()) {
     TORCH_CHECK(trace->is_cuda() && trace->scalar_type() == at::kLong && trace->is_contiguous(), "gemm: trace must be a CUDA int64 tensor");
     a.trace = reinterpret_cast<unsigned long long*>(trace->data_ptr());
+  }
+  pb::PushParams pp;
+  if (wait_channel >= 0) {
+    // x was written by peer GPUs: the kernel waits for wait_expect arrivals on the channel first
+    memset(&pp, 0, sizeof(pp));
+    pp.local_sig = reinterpret_cast<const void*>(static_cast<uintptr_t>(wait_sig_ptr));
+    pp.wait_channel = int(wait_channel);
+    pp.wait_expect = unsigned(wait_expect);
+    a.push = &pp;
   }
   check(pb::gemm_launch(a, cur_stream()), "gemm_launch");
 }
@@ -242,7 +254,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("row_scale") = py::none(), py::arg("sumsq") = py::none(), py::arg("act") = 0,
         py::arg("glu") = false, py::arg("a_scale") = py::none(), py::arg("w_scale") = py::none(),
         py::arg("force_bn") = 0, py::arg("force_swap") = -1, py::arg("force_splits") = 0,
-        py::arg("trace") = py::none());
+        py::arg("trace") = py::none(), py::arg("wait_sig_ptr") = 0, py::arg("wait_channel") = -1,
+        py::arg("wait_expect") = 0);
   m.def("attention", &attention, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"),
         py::arg("q_start"), py::arg("q_len"), py::arg("kv_indptr"), py::arg("kv_len"),
         py::arg("kv_indices") = py::none(), py::arg("max_q_len"), py::arg("causal") = false,

@@ -40,7 +40,7 @@ namespace pb {
 
 // ------------------------------------------------------------------ kernels
 __global__ void reduce_norm_kernel(ReduceNormArgs a, ChannelSig* local_sig, int channel,
-                                   unsigned int expect_per_call, int* status) {
+                                   unsigned int expect_per_call, PeerPtrs sig_peers, int* status) {
   __shared__ float red[32];
   __shared__ int ok_s;
   ChannelSig* sig = local_sig + channel;
@@ -57,9 +57,17 @@ __global__ void reduce_norm_kernel(ReduceNormArgs a, ChannelSig* local_sig, int 
   if (ok_s) {
     ReduceNormArgs b = a;
     b.slots = a.slots + size_t(parity) * a.world * a.slot_stride;
-    for (int row = blockIdx.x; row < a.M; row += gridDim.x) {
+    for (int row = a.row0 + blockIdx.x; row < a.row0 + a.nrows; row += gridDim.x) {
       reduce_norm_row(b, row, red);
       __syncthreads();
+    }
+  }
+  if (a.y_world > 0) {
+    // the gathered rows of this CTA are on their way: one arrival per CTA on every rank
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned int ye = ld_relaxed_sys(&(local_sig + a.y_channel)->epoch);
+      channel_signal_all(sig_peers, a.y_channel, int(ye & 1u), a.y_world);
     }
   }
   channel_finish(sig, parity, gridDim.x);
@@ -176,8 +184,9 @@ __global__ void gather_consume_kernel(const __nv_bfloat16* slots, long long slot
       const int v = int(i % nv);
       const long long rr = i / nv;
       const int row = int(rr % rows), r = int(rr / rows);
-      *reinterpret_cast<uint4*>(out + (size_t(r) * rows + row) * ldo + v * 8) =
-          *reinterpret_cast<const uint4*>(base + size_t(r) * slot_stride + size_t(row) * ld + v * 8);
+      if (out)
+        *reinterpret_cast<uint4*>(out + (size_t(r) * rows + row) * ldo + v * 8) =
+            *reinterpret_cast<const uint4*>(base + size_t(r) * slot_stride + size_t(row) * ld + v * 8);
     }
   }
   channel_finish(ls, parity, gridDim.x);
@@ -246,11 +255,16 @@ pb::PeerPtrs to_ptrs(const std::vector<uintptr_t>& v, int64_t byte_off = 0) {
 }
 
 // Sums the world partials pushed for this channel, adds residual (* gate), norms.
-void reduce_norm(const std::vector<uintptr_t>& data_ptrs, int64_t rank, int64_t slots_off_elems,
+// With rows_per_rank > 0 only this rank's rows are reduced (the producer scattered them) and
+// residual / h_out / y are indexed by global row. With y_gather_off >= 0 the normalised rows
+// go to that element offset of every rank's slab and y_channel is signalled; the return
+// value is then the number of arrivals a consumer of the gathered matrix waits for.
+int64_t reduce_norm(const std::vector<uintptr_t>& data_ptrs, int64_t rank, int64_t slots_off_elems,
                  int64_t slot_stride, int64_t M, int64_t N, int64_t ld, int64_t sig_off_bytes,
                  int64_t channel, int64_t expect, const OptT& residual, const OptT& col_gate,
                  const OptT& bias, const OptT& h_out, const OptT& y, int64_t norm_mode,
-                 const OptT& weight, const OptT& mod, double eps, int64_t max_ctas) {
+                 const OptT& weight, const OptT& mod, double eps, int64_t max_ctas,
+                 int64_t rows_per_rank, int64_t y_gather_off, int64_t y_ld, int64_t y_channel) {
   pb::ReduceNormArgs a;
   const int world = int(data_ptrs.size());
   a.slots = reinterpret_cast<const __nv_bfloat16*>(data_ptrs[rank]) + slots_off_elems;
@@ -266,13 +280,27 @@ void reduce_norm(const std::vector<uintptr_t>& data_ptrs, int64_t rank, int64_t 
   a.y = nullptr; a.ldy = 0;
   if (y.has_value() && y->defined()) { a.y = const_cast<__nv_bfloat16*>(bfp(y)); a.ldy = int(y->stride(0)); }
   a.norm_mode = int(norm_mode); a.weight = bfp(weight); a.mod = bfp(mod); a.eps = float(eps);
+  a.row0 = 0; a.nrows = int(M); a.slot_row0 = 0;
+  if (rows_per_rank > 0) {
+    a.row0 = int(rank * rows_per_rank);
+    a.slot_row0 = a.row0;
+    a.nrows = int(std::max<int64_t>(0, std::min<int64_t>(rows_per_rank, M - a.row0)));
+  }
+  a.y_world = 0; a.y_off = 0; a.y_channel = 0;
+  a.y_dst = to_ptrs(data_ptrs);
+  if (y_gather_off >= 0) {
+    TORCH_CHECK(y_ld % 8 == 0 && y_gather_off % 8 == 0, "reduce_norm: gathered rows must be 16-byte aligned");
+    a.y_world = world; a.y_off = y_gather_off; a.ldy = int(y_ld); a.y_channel = int(y_channel);
+  }
   auto* sig = reinterpret_cast<pb::ChannelSig*>(data_ptrs[rank] + sig_off_bytes);
   int threads = int(((N / 8) + 31) / 32 * 32);
   threads = threads > 512 ? 512 : (threads < 64 ? 64 : threads);
-  int grid = int(M < max_ctas ? M : max_ctas);
+  int grid = int(a.nrows < max_ctas ? a.nrows : max_ctas);
+  if (grid < 1) grid = 1;
   PB_LAUNCH(pb::reduce_norm_kernel, grid, threads, cur_stream(), a, sig, int(channel), unsigned(expect),
-                                                             pb::kernel_status_ptr());
+            to_ptrs(data_ptrs, sig_off_bytes), pb::kernel_status_ptr());
   throw_on(cudaGetLastError(), "reduce_norm_kernel");
+  return int64_t(grid) * world;
 }
 
 int64_t push_partial(const Tensor& x, const std::vector<uintptr_t>& data_ptrs, int64_t rank,
@@ -289,6 +317,36 @@ int64_t push_partial(const Tensor& x, const std::vector<uintptr_t>& data_ptrs, i
       slot_stride, int(ld), world, int(rank), to_ptrs(data_ptrs, sig_off_bytes), sig, int(channel));
   throw_on(cudaGetLastError(), "push_partial_kernel");
   return int64_t(grid) * world;  // arrivals each rank will see per call
+}
+
+// Row-parallel product pushed straight from the GEMM epilogue into every rank's slots.
+// Returns the number of arrivals each rank's consumer must wait for on this call.
+int64_t gemm_push(const Tensor& x, const Tensor& w, const std::vector<uintptr_t>& data_ptrs, int64_t rank,
+                  int64_t slots_off_elems, int64_t slot_stride, int64_t ld, int64_t sig_off_bytes,
+                  int64_t channel, int64_t rows_per_rank, int64_t force_bn, int64_t force_swap,
+                  int64_t force_splits) {
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1, "gemm_push: layout");
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16, "gemm_push: bf16 operands");
+  TORCH_CHECK(x.size(1) == w.size(1), "gemm_push: K mismatch");
+  pb::PushParams pp;
+  pp.data = to_ptrs(data_ptrs);
+  pp.sig = to_ptrs(data_ptrs, sig_off_bytes);
+  pp.local_sig = reinterpret_cast<const void*>(data_ptrs[rank] + sig_off_bytes);
+  pp.slots_off = slots_off_elems; pp.slot_stride = slot_stride; pp.ld = int(ld);
+  pp.world = int(data_ptrs.size()); pp.rank = int(rank); pp.channel = int(channel);
+  pp.rows_per_rank = int(rows_per_rank); pp.wait_channel = -1; pp.wait_expect = 0;
+  pb::GemmArgs a;
+  a.x = x.data_ptr(); a.w = w.data_ptr(); a.out = nullptr;
+  a.M = int(x.size(0)); a.N = int(w.size(0)); a.K = int(x.size(1));
+  a.ldx = int(x.stride(0)); a.ldw = int(w.stride(0)); a.ldo = int(ld);
+  TORCH_CHECK((rows_per_rank > 0 ? rows_per_rank : int64_t(a.M)) * ld <= slot_stride && a.N <= ld,
+              "gemm_push: product does not fit a slot");
+  TORCH_CHECK(rows_per_rank == 0 || rows_per_rank * pp.world >= a.M, "gemm_push: rows_per_rank too small");
+  a.force_bn = int(force_bn); a.force_swap = int(force_swap); a.force_splits = int(force_splits);
+  a.push = &pp;
+  int ctas = 0;
+  throw_on(pb::gemm_launch(a, cur_stream(), &ctas), "gemm_launch (push)");
+  return int64_t(ctas) * pp.world;
 }
 
 void cfg_exchange(const Tensor& mine, const std::vector<uintptr_t>& data_ptrs, int64_t my_pos,
@@ -312,17 +370,19 @@ void cfg_exchange(const Tensor& mine, const std::vector<uintptr_t>& data_ptrs, i
 }
 
 void gather_consume(const std::vector<uintptr_t>& data_ptrs, int64_t rank, int64_t slots_off_elems,
-                    int64_t slot_stride, int64_t rows, int64_t N, int64_t ld, Tensor& out,
+                    int64_t slot_stride, int64_t rows, int64_t N, int64_t ld, const OptT& out,
                     int64_t sig_off_bytes, int64_t channel, int64_t expect) {
-  TORCH_CHECK(out.dim() == 2 && out.stride(1) == 1 && N % 8 == 0, "gather_consume: layout");
+  const bool copy = out.has_value() && out->defined();
+  TORCH_CHECK(N % 8 == 0 && (!copy || (out->dim() == 2 && out->stride(1) == 1)), "gather_consume: layout");
   const int world = int(data_ptrs.size());
   const long long total = (long long)world * rows * (N / 8);
   int grid = int((total + 255) / 256);
   grid = grid > 128 ? 128 : (grid < 1 ? 1 : grid);
+  if (!copy) grid = 1;  // wait only: the gathered rows are read in place by the next kernel
   auto* sig = reinterpret_cast<pb::ChannelSig*>(data_ptrs[rank] + sig_off_bytes);
   PB_LAUNCH(pb::gather_consume_kernel, grid, 256, cur_stream(), 
       reinterpret_cast<const __nv_bfloat16*>(data_ptrs[rank]) + slots_off_elems, slot_stride, int(rows), int(N),
-      int(ld), world, const_cast<__nv_bfloat16*>(bfp(OptT(out))), int(out.stride(0)), sig, int(channel),
+      int(ld), world, copy ? const_cast<__nv_bfloat16*>(bfp(out)) : nullptr, copy ? int(out->stride(0)) : 0, sig, int(channel),
       unsigned(expect), pb::kernel_status_ptr());
   throw_on(cudaGetLastError(), "gather_consume_kernel");
 }
@@ -344,6 +404,7 @@ void register_comm(py::module_& m) {
   m.def("ipc_free", &ipc_free);
   m.def("reduce_norm", &reduce_norm);
   m.def("push_partial", &push_partial);
+  m.def("gemm_push", &gemm_push);
   m.def("cfg_exchange", &cfg_exchange);
   m.def("gather_consume", &gather_consume);
   m.def("flag_wait_probe", &flag_wait_probe);

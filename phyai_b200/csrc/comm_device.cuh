@@ -91,6 +91,13 @@ struct ReduceNormArgs {
   const __nv_bfloat16* weight;  // rms / gemma weight
   const __nv_bfloat16* mod;     // AdaRMS row (scale | shift | gate), shared by all rows
   float eps;
+  int row0, nrows;              // rows this rank reduces ([0, M) unless the producer scattered)
+  int slot_row0;                // global row stored at slot row 0 (row0 when scattered, else 0)
+  // all-gather of the normalised rows: y_world > 0 stores each y row at element offset
+  // y_off + row * ldy of EVERY rank's slab instead of `y`, then signals y_channel
+  PeerPtrs y_dst;
+  long long y_off;
+  int y_world, y_channel;
 };
 
 // One CTA reduces row `row`: h = residual + (sum_r slot_r + bias) * gate, y = norm(h).
@@ -104,7 +111,7 @@ __device__ __forceinline__ void reduce_norm_row(const ReduceNormArgs& a, int row
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int r = 0; r < a.world; ++r) {
       const uint4 raw = *reinterpret_cast<const uint4*>(a.slots + size_t(r) * a.slot_stride +
-                                                        size_t(row) * a.ld + v * 8);
+                                                        size_t(row - a.slot_row0) * a.ld + v * 8);
       const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -139,7 +146,7 @@ __device__ __forceinline__ void reduce_norm_row(const ReduceNormArgs& a, int row
     }
     if (hrow) *reinterpret_cast<uint4*>(hrow + v * 8) = out;
   }
-  if (a.y == nullptr || a.norm_mode < 0 || hrow == nullptr) return;
+  if ((a.y == nullptr && a.y_world == 0) || hrow == nullptr) return;
   // block-wide sum of squares
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
@@ -151,7 +158,7 @@ __device__ __forceinline__ void reduce_norm_row(const ReduceNormArgs& a, int row
   float t = lane < nw ? red[lane] : 0.f;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-  const float rstd = rsqrtf(t / a.N + a.eps);
+  const float rstd = a.norm_mode < 0 ? 1.f : rsqrtf(t / a.N + a.eps);
   __syncthreads();  // h row written by this CTA is re-read below
   for (int v = threadIdx.x; v < nv; v += blockDim.x) {
     const uint4 raw = *reinterpret_cast<const uint4*>(hrow + v * 8);
@@ -174,7 +181,13 @@ __device__ __forceinline__ void reduce_norm_row(const ReduceNormArgs& a, int row
       }
       o2[i] = __floats2bfloat162_rn(x0, x1);
     }
-    *reinterpret_cast<uint4*>(a.y + size_t(row) * a.ldy + v * 8) = out;
+    if (a.y_world > 0) {
+      const size_t off = size_t(a.y_off) + size_t(row) * a.ldy + v * 8;
+      for (int r = 0; r < a.y_world; ++r)
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.y_dst.p[r]) + off) = out;
+    } else {
+      *reinterpret_cast<uint4*>(a.y + size_t(row) * a.ldy + v * 8) = out;
+    }
   }
 }
 

@@ -24,10 +24,12 @@
 
 #include <atomic>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <unordered_map>
 #include <vector>
 
+#include "comm_device.cuh"
 #include "gemm_epilogue.cuh"
 #include "launch.cuh"
 #include "ptx.cuh"
@@ -73,8 +75,8 @@ constexpr int kRowBytes = 128;     // one swizzle-128B row: 64 bf16 or 128 e4m3
 template <int BN, bool SWAP, bool FP8>
 __global__ void __launch_bounds__(kThreads)
 gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
-            EpiParams ep, int total_kb, int kb_per_split, int stages, int* status,
-            unsigned long long* trace) {
+            EpiParams ep, const __grid_constant__ PushParams push, int total_kb, int kb_per_split,
+            int stages, int* status, unsigned long long* trace) {
   constexpr int BK = FP8 ? 128 : 64;                 // elements per k-block
   constexpr int P_BYTES = kTileP * kRowBytes;        // 16 KB
   constexpr int Q_BYTES = BN * kRowBytes;
@@ -144,6 +146,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
       }
     }
     pdl_wait();
+    if (push.wait_channel >= 0) {
+      // the activations were stored by peer GPUs: wait for their arrivals, then order the
+      // TMA (async proxy) reads after the acquire
+      if (lane == 0) {
+        const ChannelSig* ws = reinterpret_cast<const ChannelSig*>(push.local_sig) + push.wait_channel;
+        const int wp = int(ld_relaxed_sys(&ws->epoch) & 1u);
+        if (!wait_counter_ge(&ws->arrive[wp], push.wait_expect)) err_s = kStatusTimeoutPeer;
+        asm volatile("fence.proxy.async;" ::: "memory");
+      }
+      __syncwarp();
+    }
     if (lane == 0) {
       for (int kb = 0; kb < pre; ++kb)
         tma_load_2d(smem + kb * STAGE_BYTES + X_OFF, tmX, &full_bar[kb], (kb0 + kb) * BK, x_row);
@@ -235,8 +248,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
     const int m0 = SWAP ? q_tile * BN : p_tile * kTileP;
     const int n0 = SWAP ? p_tile * kTileP : q_tile * BN;
     const int rows_per_cta = TM / nsplit;
-    epilogue_pass<TN>(ep, reinterpret_cast<const float*>(smem), smem_u32(smem), LDS, m0, n0,
-                      split * rows_per_cta, rows_per_cta, nsplit, warp, lane, kThreads / 32);
+    if (push.world > 0) {
+      const ChannelSig* ls = reinterpret_cast<const ChannelSig*>(push.local_sig) + push.channel;
+      const int parity = int(ld_relaxed_sys(&ls->epoch) & 1u);
+      epilogue_push<TN>(push, parity, ep.M, ep.N, smem_u32(smem), reinterpret_cast<const float*>(smem), LDS,
+                        m0, n0, split * rows_per_cta, rows_per_cta, nsplit, warp, lane, kThreads / 32);
+      __syncthreads();
+      if (threadIdx.x == 0) channel_signal_all(push.sig, push.channel, parity, push.world);
+    } else {
+      epilogue_pass<TN>(ep, reinterpret_cast<const float*>(smem), smem_u32(smem), LDS, m0, n0,
+                        split * rows_per_cta, rows_per_cta, nsplit, warp, lane, kThreads / 32);
+    }
   } else if (threadIdx.x == 0) {
     if (status) atomicCAS(status, 0, err);
     // let copies that are still in flight land before the block goes away
@@ -250,6 +272,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (push.wait_channel >= 0) {
+    ChannelSig* ws = const_cast<ChannelSig*>(reinterpret_cast<const ChannelSig*>(push.local_sig)) + push.wait_channel;
+    const int wp = int(ld_relaxed_sys(&ws->epoch) & 1u);  // unchanged until every CTA took its ticket
+    channel_finish(ws, wp, gridDim.x * gridDim.y * gridDim.z);
+  }
 }
 
 // ------------------------------------------------------------ host: TMA maps
@@ -354,7 +381,7 @@ bool make_tmap_3d_bf16(CUtensorMap* out, const void* ptr, uint64_t D, uint64_t H
 // ---------------------------------------------------------------- host: launch
 template <int BN, bool SWAP, bool FP8>
 static cudaError_t launch_inst(const CUtensorMap& tmP, const CUtensorMap& tmQ, const EpiParams& ep,
-                               dim3 grid, int total_kb, int kbps, int stages, size_t smem,
+                               const PushParams& push, dim3 grid, int total_kb, int kbps, int stages, size_t smem,
                                cudaStream_t stream, unsigned long long* trace) {
   auto kern = gemm_kernel<BN, SWAP, FP8>;
   static bool attr_done = false;
@@ -364,20 +391,21 @@ static cudaError_t launch_inst(const CUtensorMap& tmP, const CUtensorMap& tmQ, c
     if (e != cudaSuccess) return e;
     attr_done = true;
   }
-  return launch_kernel(kern, grid, dim3(kThreads), smem, stream, int(grid.z), tmP, tmQ, ep, total_kb, kbps,
-                       stages, kernel_status_ptr(), trace);
+  return launch_kernel(kern, grid, dim3(kThreads), smem, stream, int(grid.z), tmP, tmQ, ep, push, total_kb,
+                       kbps, stages, kernel_status_ptr(), trace);
 }
 
 template <bool SWAP, bool FP8>
 static cudaError_t launch_bn(int bn, const CUtensorMap& tmP, const CUtensorMap& tmQ,
-                             const EpiParams& ep, dim3 grid, int total_kb, int kbps, int stages,
-                             size_t smem, cudaStream_t st, unsigned long long* tr) {
+                             const EpiParams& ep, const PushParams& push, dim3 grid, int total_kb,
+                             int kbps, int stages, size_t smem, cudaStream_t st,
+                             unsigned long long* tr) {
   switch (bn) {
-    case 16: return launch_inst<16, SWAP, FP8>(tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, st, tr);
-    case 32: return launch_inst<32, SWAP, FP8>(tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, st, tr);
-    case 64: return launch_inst<64, SWAP, FP8>(tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, st, tr);
-    case 128: return launch_inst<128, SWAP, FP8>(tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, st, tr);
-    case 256: return launch_inst<256, SWAP, FP8>(tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, st, tr);
+    case 16: return launch_inst<16, SWAP, FP8>(tmP, tmQ, ep, push, grid, total_kb, kbps, stages, smem, st, tr);
+    case 32: return launch_inst<32, SWAP, FP8>(tmP, tmQ, ep, push, grid, total_kb, kbps, stages, smem, st, tr);
+    case 64: return launch_inst<64, SWAP, FP8>(tmP, tmQ, ep, push, grid, total_kb, kbps, stages, smem, st, tr);
+    case 128: return launch_inst<128, SWAP, FP8>(tmP, tmQ, ep, push, grid, total_kb, kbps, stages, smem, st, tr);
+    case 256: return launch_inst<256, SWAP, FP8>(tmP, tmQ, ep, push, grid, total_kb, kbps, stages, smem, st, tr);
     default: return cudaErrorInvalidValue;
   }
 }
@@ -393,7 +421,7 @@ static int num_sms() {
   return n;
 }
 
-cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
+cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream, int* n_ctas) {
   const int eb = a.fp8 ? 1 : 2;
   const int BK = a.fp8 ? 128 : 64;
   if (a.M <= 0 || a.N <= 0 || a.K <= 0) return cudaErrorInvalidValue;
@@ -471,13 +499,28 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   ep.a_scale = a.a_scale; ep.w_scale = a.w_scale;
   ep.act = a.act; ep.glu = a.glu; ep.out_fp32 = a.out_fp32;
 
-  dim3 grid(p_tiles, q_tiles, splits);
-  if (swap) {
-    return a.fp8 ? launch_bn<true, true>(bn, tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, stream, a.trace)
-                 : launch_bn<true, false>(bn, tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, stream, a.trace);
+  PushParams push;
+  memset(&push, 0, sizeof(push));
+  push.wait_channel = -1;
+  if (a.push) {
+    // the consumer adds bias / residual / norm; a push-mode product is the bare partial sum
+    if (a.push->world < 0 || a.push->world > kMaxRanks ||
+        (a.push->world > 0 && (a.glu || a.act || a.bias || a.residual || a.col_gate || a.row_scale ||
+                               a.sumsq || a.fp8 || (a.push->ld % 4))))
+      return cudaErrorInvalidValue;
+    if (a.push->world > 0 && a.push->rows_per_rank > 0 &&
+        (a.M + a.push->rows_per_rank - 1) / a.push->rows_per_rank > a.push->world)
+      return cudaErrorInvalidValue;
+    push = *a.push;
   }
-  return a.fp8 ? launch_bn<false, true>(bn, tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, stream, a.trace)
-               : launch_bn<false, false>(bn, tmP, tmQ, ep, grid, total_kb, kbps, stages, smem, stream, a.trace);
+  dim3 grid(p_tiles, q_tiles, splits);
+  if (n_ctas) *n_ctas = p_tiles * q_tiles * splits;
+  if (swap) {
+    return a.fp8 ? launch_bn<true, true>(bn, tmP, tmQ, ep, push, grid, total_kb, kbps, stages, smem, stream, a.trace)
+                 : launch_bn<true, false>(bn, tmP, tmQ, ep, push, grid, total_kb, kbps, stages, smem, stream, a.trace);
+  }
+  return a.fp8 ? launch_bn<false, true>(bn, tmP, tmQ, ep, push, grid, total_kb, kbps, stages, smem, stream, a.trace)
+               : launch_bn<false, false>(bn, tmP, tmQ, ep, push, grid, total_kb, kbps, stages, smem, stream, a.trace);
 }
 
 }  // namespace pb

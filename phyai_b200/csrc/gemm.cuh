@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "comm.cuh"
+
 namespace pb {
 
 enum GemmAct : int { kActNone = 0, kActGeluTanh = 1, kActSilu = 2, kActGeluErf = 3 };
@@ -44,11 +46,16 @@ struct GemmArgs {
   int block_scaled = 0;                     // fp8: 128x128 weight blocks, 1x128 act blocks
   int force_bn = 0, force_swap = -1, force_splits = 0;  // tuning overrides (0/-1 = auto)
   unsigned long long* trace = nullptr;  // optional: 8 globaltimer stamps per CTA (debugging)
+  // Push mode (row-parallel linear fused with its all-reduce): the raw bf16 product goes to
+  // every rank's slots instead of `out`; bias/act/residual belong to the consumer kernel.
+  const PushParams* push = nullptr;
 };
 
 // Launches on `stream`. Returns cudaSuccess or the launch error; argument
 // problems (alignment, unsupported shape) return cudaErrorInvalidValue.
-cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream);
+// `n_ctas`, when given, receives the number of CTAs launched (what a push-mode consumer
+// multiplies by the world size to know how many arrivals to expect).
+cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream, int* n_ctas = nullptr);
 
 // 3-D bf16 tensor map (d, head, row) for the attention kernels (see gemm.cu).
 bool make_tmap_3d_bf16(CUtensorMap* out, const void* ptr, uint64_t D, uint64_t H, uint64_t R,

@@ -8,6 +8,7 @@
 // summed through distributed shared memory (all S loads are issued before the first
 // add, so their latencies overlap).
 #pragma once
+#include "comm.cuh"
 #include "ptx.cuh"
 
 namespace pb {
@@ -183,6 +184,54 @@ __device__ __forceinline__ void epilogue_pass_t(const EpiParams& ep, const float
             if (lane == 0) atomicAdd(ep.sumsq + m, ss);
           }
         }
+      }
+    }
+  }
+}
+
+// Push-mode store pass: the (cluster-reduced) accumulator rows of this CTA, rounded to
+// bf16, go to slots[parity][rank] of every rank over NVLink with plain 8-byte stores (a
+// warp writes 256 contiguous bytes of one row per destination). The caller signals the
+// channel once every thread of the CTA is past this function.
+template <int TN>
+__device__ __forceinline__ void epilogue_push(const PushParams& pp, int parity, int M, int N,
+                                              uint32_t stg_addr, const float* stg, int lds, int m0,
+                                              int n0, int r0, int rows, int nsplit, int warp,
+                                              int lane, int nwarps) {
+  const int row_end = min(r0 + rows, M - m0);
+  const size_t slot = size_t(pp.slots_off) + (size_t(parity) * pp.world + pp.rank) * size_t(pp.slot_stride);
+#pragma unroll
+  for (int c = lane * 4; c < TN; c += 128) {
+    const int n = n0 + c;
+    if (n >= N) continue;
+    for (int rr = r0 + warp; rr < row_end; rr += nwarps) {
+      float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f;
+      if (nsplit == 1) {
+        const float4 a = *reinterpret_cast<const float4*>(stg + rr * lds + c);
+        v0 = a.x; v1 = a.y; v2 = a.z; v3 = a.w;
+      } else {
+        const uint32_t off = stg_addr + uint32_t(rr * lds + c) * 4u;
+        float4 part[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          if (r < nsplit) part[r] = ld_dsmem_f4(map_to_cta(off, r));
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          if (r < nsplit) { v0 += part[r].x; v1 += part[r].y; v2 += part[r].z; v3 += part[r].w; }
+      }
+      const __nv_bfloat162 o01 = __floats2bfloat162_rn(v0, v1), o23 = __floats2bfloat162_rn(v2, v3);
+      uint2 raw;
+      raw.x = *reinterpret_cast<const uint32_t*>(&o01);
+      raw.y = *reinterpret_cast<const uint32_t*>(&o23);
+      const size_t off = slot + size_t(m0 + rr) * pp.ld + n;
+      if (pp.rows_per_rank > 0) {
+        // scattered: the owner's slot holds only its own rows, counted from its first row
+        const int r = (m0 + rr) / pp.rows_per_rank;
+        const size_t offs = slot + size_t(m0 + rr - r * pp.rows_per_rank) * pp.ld + n;
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(pp.data.p[r]) + offs) = raw;
+      } else {
+        for (int r = 0; r < pp.world; ++r)
+          *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(pp.data.p[r]) + off) = raw;
       }
     }
   }

@@ -106,6 +106,8 @@ class envs:
     PHYAI_NCCL_SO_PATH = EnvField("PHYAI_NCCL_SO_PATH", None, str)
     PHYAI_COMM_TIMEOUT_S = EnvField("PHYAI_COMM_TIMEOUT_S", 60.0, float)
     PHYAI_HEARTBEAT_S = EnvField("PHYAI_HEARTBEAT_S", 0.0, float)
+    PHYAI_PEER_COMM = EnvField("PHYAI_PEER_COMM", True, parse_bool)    # fused peer-memory collectives (0: NCCL only)
+    PHYAI_PEER_HEAP_MB = EnvField("PHYAI_PEER_HEAP_MB", 0, int)          # symmetric heap size override
     # debug / tensor dump
     PHYAI_DEBUG_TENSOR_DUMP_DIR = EnvField("PHYAI_DEBUG_TENSOR_DUMP_DIR", None, str)
     PHYAI_DEBUG_TENSOR_DUMP_FILTER = EnvField("PHYAI_DEBUG_TENSOR_DUMP_FILTER", None, parse_regex_list)

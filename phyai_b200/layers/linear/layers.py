@@ -146,6 +146,7 @@ class ColumnParallelLinear(LinearBase):
     def __init__(self, in_features: int, out_features: int, *, axis: str = "tp", sp_axis: str | None = None,
                  gather_output: bool = False, mesh=None, _defer: bool = False, **kw) -> None:
         super().__init__(in_features, out_features, **kw)
+        mesh = mesh if mesh is not None else pstate.default_mesh()
         self.axis, self.sp_axis, self.gather_output, self.mesh = axis, sp_axis, gather_output, mesh
         self.tp_rank, self.tp_size = _axis_info(axis, mesh)
         if out_features % self.tp_size:
@@ -225,6 +226,7 @@ class QKVParallelLinear(ColumnParallelLinear):
                  hf_legs: Sequence[str] | None = None, **kw) -> None:
         kvh = total_num_kv_heads if total_num_kv_heads is not None else total_num_heads
         axis, mesh = kw.get("axis", "tp"), kw.get("mesh")
+        mesh = mesh if mesh is not None else pstate.default_mesh()
         _, tp = _axis_info(axis, mesh)
         if total_num_heads % tp:
             raise ValueError(f"num_heads={total_num_heads} is not divisible by {axis} size {tp}")
@@ -270,6 +272,7 @@ class RowParallelLinear(LinearBase):
     def __init__(self, in_features: int, out_features: int, *, axis: str = "tp", sp_axis: str | None = None,
                  input_is_parallel: bool = True, reduce_results: bool = True, mesh=None, **kw) -> None:
         super().__init__(in_features, out_features, **kw)
+        mesh = mesh if mesh is not None else pstate.default_mesh()
         self.axis, self.sp_axis, self.mesh = axis, sp_axis, mesh
         self.input_is_parallel, self.reduce_results = input_is_parallel, reduce_results
         self.tp_rank, self.tp_size = _axis_info(axis, mesh)

@@ -44,7 +44,7 @@ class VocabParallelEmbedding(nn.Module):
         super().__init__()
         cfg = get_engine_config()
         m = mesh if mesh is not None else pstate.default_mesh()
-        self.axis, self.mesh = axis, mesh
+        self.axis, self.mesh = axis, m
         self.tp_rank = m.axis_local_rank(axis) if m is not None else 0
         self.tp_size = m.axis_size(axis) if m is not None else 1
         self.num_embeddings, self.embedding_dim = num_embeddings, embedding_dim

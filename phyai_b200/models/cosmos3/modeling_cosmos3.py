@@ -225,6 +225,31 @@ class Cosmos3GenDecoderLayer(nn.Module):
             ops.gemm(ws.act, self.mlp.down_proj.weight, h, residual=h)
         return h
 
+    def forward_fused_tp(self, h: torch.Tensor, y_in: torch.Tensor, wait, kv_buf, s_text: int, cos_sin: torch.Tensor,
+                         ws: "GenWorkspace", next_norm_weight: torch.Tensor):
+        """Tensor-parallel layer over peer memory. ``y_in`` is this layer's already normalised input (a
+        gathered matrix other ranks may still be writing: ``wait`` makes the first GEMM wait for it);
+        the residual ``h`` is kept only for the rows this rank owns. Each row-parallel product leaves
+        its GEMM through the epilogue into the row owners' slots; the owner sums, adds the residual,
+        applies the NEXT norm and stores the rows into every rank's gathered matrix, which the next
+        GEMM waits on. Returns the ticket of the layer's output (normalised with ``next_norm_weight``)."""
+        ca, cfg = self.cross_attention, self.cfg
+        S = ws.S
+        Hq, Hkv, D = ca.num_local_heads, ca.num_local_kv_heads, ca.head_dim
+        kbuf, vbuf = kv_buf
+        st = ws.stream
+        scatter = h.shape[0] >= 1024
+        ops.gemm(y_in, ca.qkv_proj.weight, ws.qkv, wait=wait)
+        ops.rope_kv(ws.qkv, Hq, Hkv, D, ws.q, cos_sin=cos_sin, q_norm_w=ca.norm_q.weight, k_norm_w=ca.norm_k.weight,
+                    norm_eps=cfg.rms_norm_eps, k_pool=kbuf, v_pool=vbuf, slots=ws.slots)
+        ops.attention(ws.q.unflatten(1, (Hq, D)), kbuf, vbuf, ws.attn.unflatten(1, (Hq, D)), ws.q_start, ws.q_len,
+                      ws.kv_ptr, ws.kv_len, max_q_len=S, sm_scale=D ** -0.5)
+        t1 = st.linear_reduce(ws.attn, ca.to_out.weight, scatter=scatter, residual=h, norm="rms",
+                              weight=self.post_attention_layernorm.weight, eps=cfg.rms_norm_eps, gather=True)
+        ops.gemm(t1.y, self.mlp.gate_up_proj.weight, ws.act, act=self.mlp.activation, glu=True, wait=t1.wait)
+        return st.linear_reduce(ws.act, self.mlp.down_proj.weight, scatter=scatter, residual=h, norm="rms",
+                                weight=next_norm_weight, eps=cfg.rms_norm_eps, gather=True)
+
 
 @dataclass
 class GenWorkspace:
@@ -243,6 +268,7 @@ class GenWorkspace:
     q_len: torch.Tensor
     kv_ptr: torch.Tensor
     kv_len: torch.Tensor
+    stream: object | None = None   # PeerStream of the tensor-parallel group (None: single rank or NCCL fallback)
 
 
 class Cosmos3LanguageModel(nn.Module):

@@ -11,7 +11,10 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ... import ops
+from ... import parallel as P
 from ...engine_config import get_engine_config, resolve_engine_defaults
+from ...env import envs
 from ...layers.layer_norm import RMSNorm
 from ...layers.linear import ReplicatedLinear
 from .configuration_cosmos3 import Cosmos3Config
@@ -48,6 +51,7 @@ class Cosmos3Transformer(nn.Module):
             self.audio_modality_embed.hf_keys = {"audio_modality_embed": None}
         self.use_fused = (torch.device(device).type == "cuda" and dtype == torch.bfloat16
                           and get_engine_config().resolved_backend("attn") == "b200")
+        self.use_peer = envs.PHYAI_PEER_COMM.get()   # tensor-parallel GEN layers over peer memory (else NCCL all-reduce)
 
     @torch.no_grad()
     def init_random(self, seed: int = 0, std: float = 0.02) -> "Cosmos3Transformer":
@@ -158,6 +162,15 @@ class Cosmos3Transformer(nn.Module):
         ws = GenWorkspace(B, S, z(B * S, cfg.hidden_size), z(B * S, (Hq + 2 * Hkv) * D), z(B * S, Hq * D), z(B * S, Hq * D),
                           z(B * S, self.gen_layers[0].mlp.down_proj.input_size_per_partition), z(B * S, cfg.hidden_size),
                           slots.long(), ar * S, torch.full_like(ar, S), ar * tot, torch.full_like(ar, tot))
+        tp = self.gen_layers[0].mlp.down_proj.tp_size
+        if tp > 1 and self.use_peer:
+            from ...parallel.symm import PeerGroup
+
+            rows, H = B * S, cfg.hidden_size
+            per = -(-rows // tp) if rows >= 1024 else rows
+            need = 2 * tp * per * H * 2 + rows * H * 2 + (64 << 20)
+            pg = PeerGroup.for_axis(P.default_mesh(), self.gen_layers[0].mlp.down_proj.axis, heap_bytes=max(need, 1 << 30))
+            ws.stream = pg.stream(f"cosmos3.gen:{rows}", per, H, gather_rows=rows, gather_cols=H)
         bufs = []
         for k_und, v_und in cond.cached_kv:
             kb = torch.zeros(B * tot, Hkv, D, dtype=bf, device=device)
@@ -195,18 +208,31 @@ class Cosmos3Transformer(nn.Module):
             s = s + self.audio_modality_embed.to(hv.dtype)
             hg = torch.cat([hg, s + self._gate_timestep(te, sound_noisy_mask, 1)], dim=1)
         B, S, H = hg.shape
+        normed = False
         if self.use_fused and hg.is_cuda:
             ws, bufs = self._fused_state(condition, B, S, hg.device)
             s_text = condition.cached_kv[0][0].shape[1]
             cs = condition.freqs_gen.reshape(B * S, -1)
             x = hg.reshape(B * S, H).contiguous()
-            for layer, kv in zip(self.gen_layers, bufs):
-                x = layer.forward_fused(x, kv, s_text, cs, ws)
-            hg = x.reshape(B, S, H)
+            if ws.stream is not None:
+                # sequence-parallel residual: every layer hands the next one its already normalised input
+                y, wait = ops.norm(x, "rms", weight=self.gen_layers[0].input_layernorm.weight, eps=cfg.rms_norm_eps, out=ws.x), None
+                n = len(self.gen_layers)
+                for i, (layer, kv) in enumerate(zip(self.gen_layers, bufs)):
+                    nxt = self.gen_layers[i + 1].input_layernorm.weight if i + 1 < n else self.norm_moe_gen.weight
+                    tk = layer.forward_fused_tp(x, y, wait, kv, s_text, cs, ws, nxt)
+                    y, wait = tk.y, tk.wait
+                hg = ws.stream.wait_gather(tk).reshape(B, S, H)
+                normed = True
+            else:
+                for layer, kv in zip(self.gen_layers, bufs):
+                    x = layer.forward_fused(x, kv, s_text, cs, ws)
+                hg = x.reshape(B, S, H)
         else:
             for layer, (k_und, v_und) in zip(self.gen_layers, condition.cached_kv):
                 hg = layer(hg, k_und, v_und, condition.freqs_gen)
-        hg = self.norm_moe_gen(hg)
+        if not normed:
+            hg = self.norm_moe_gen(hg)
         vo, _ = self.proj_out(hg[:, :s_video])
         video_vel = self.unpatchify(vo, t, h, w)
         if action_latents is not None:

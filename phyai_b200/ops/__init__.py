@@ -80,8 +80,12 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *
          act: str | None = "none", glu: bool = False, out_dtype: torch.dtype = torch.bfloat16,
          a_scale: Optional[torch.Tensor] = None, w_scale: Optional[torch.Tensor] = None,
          force_bn: int = 0, force_swap: int = -1, force_splits: int = 0,
-         trace: Optional[torch.Tensor] = None) -> torch.Tensor:
+         trace: Optional[torch.Tensor] = None, wait: Optional[tuple[int, int, int]] = None) -> torch.Tensor:
     """``out = epilogue(x @ w.T)`` on tcgen05 tensor cores (see ``csrc/gemm.cuh``).
+
+    ``wait=(signal_array_ptr, channel, arrivals)``: ``x`` lives in symmetric memory and is being
+    written by peer GPUs; the kernel waits for that many arrivals on the channel before it loads
+    ``x`` and closes the channel's call when it is done (all-gather fused into the GEMM).
 
     ``x`` is ``(M, K)``, ``w`` is ``(N, K)`` (the ``nn.Linear`` layout), both bf16 or
     both float8_e4m3fn (then ``a_scale`` (M,) and ``w_scale`` (N,) dequantise). With
@@ -92,7 +96,8 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *
     if out is None:
         out = torch.empty((M, N // 2 if glu else N), dtype=out_dtype, device=x.device)
     ext().gemm(x, w, out, bias, residual, res_mod, col_gate, row_scale, sumsq, ACT[act], glu,
-               a_scale, w_scale, force_bn, force_swap, force_splits, trace)
+               a_scale, w_scale, force_bn, force_swap, force_splits, trace,
+               *((0, -1, 0) if wait is None else wait))
     return out
 
 

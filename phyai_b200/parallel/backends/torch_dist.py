@@ -107,6 +107,19 @@ class GlooBackend(_TorchDistBackend):
     device_type = "cpu"
     capturable = False
 
+    def execute(self, call: Call, *tensors: torch.Tensor, **kw: Any):
+        if call.op is Op.ALL_TO_ALL:
+            # gloo has no all-to-all: gather everything and keep the pieces addressed to this rank
+            x = tensors[0]
+            group, n = call.mesh.axis_group(call.axis), call.mesh.axis_size(call.axis)
+            sd, cd = kw.get("split_dim", 0), kw.get("concat_dim", 0)
+            mine = torch.stack([p.contiguous() for p in x.chunk(n, dim=sd)])
+            everyone = [torch.empty_like(mine) for _ in range(n)]
+            dist.all_gather(everyone, mine, group=group)
+            r = dist.get_rank(group)
+            return torch.cat([e[r] for e in everyone], dim=cd)
+        return super().execute(call, *tensors, **kw)
+
     def _all_gather_into(self, out, x, group, n):
         parts = list(out.chunk(n, dim=0))
         dist.all_gather(parts, x, group=group)

@@ -34,6 +34,15 @@ def _axis_pos(axis: str | None, mesh) -> tuple[int, int]:
     return mesh.axis_local_rank(axis), mesh.axis_size(axis)
 
 
+def _pin(mesh):
+    """The mesh a loader works on is the one active when its layer was built, not when weights arrive."""
+    if mesh is not None:
+        return mesh
+    from ..parallel import state
+
+    return state.default_mesh()
+
+
 def _copy(param: torch.nn.Parameter, src: torch.Tensor, dst_view: torch.Tensor | None = None) -> None:
     dst = param.data if dst_view is None else dst_view
     if dst.shape != src.shape:
@@ -49,6 +58,8 @@ def replicated() -> Loader:
 
 def sharded(dim: int, axis: str | None = "tp", mesh=None, *, replicate: int = 1) -> Loader:
     """Slice ``dim`` into ``size/replicate`` parts; ``replicate`` consecutive ranks share a part."""
+    mesh = _pin(mesh)
+
     def load(param, tensor, shard_id=None):
         r, n = _axis_pos(axis, mesh)
         parts = max(n // max(replicate, 1), 1)
@@ -72,6 +83,7 @@ def fused(fuse_dim: int, legs: Mapping[object, tuple[int, int]] | Sequence[tuple
     """
     table = dict(legs) if isinstance(legs, Mapping) else {k: (o, s) for k, o, s in legs}
     order = list(table.keys())
+    mesh = _pin(mesh)
 
     def load(param, tensor, shard_id=None):
         if shard_id not in table:
@@ -98,6 +110,8 @@ def fused(fuse_dim: int, legs: Mapping[object, tuple[int, int]] | Sequence[tuple
 
 def vocab(padded_size: int, axis: str | None = "tp", mesh=None) -> Loader:
     """Rows ``[r*per, (r+1)*per)`` of the padded vocabulary; rows past the real vocab are zero."""
+    mesh = _pin(mesh)
+
     def load(param, tensor, shard_id=None):
         r, n = _axis_pos(axis, mesh)
         per = padded_size // n

@@ -1,0 +1,113 @@
+"""Child of test_dist_cpu.py: one gloo rank. Checks the collective vocabulary, tensor-parallel Cosmos3
+against a single-rank model with the same checkpoint, and CFG-parallel guidance against sequential."""
+
+import os
+import sys
+import tempfile
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+
+def main() -> int:
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    mode = sys.argv[1]
+    dist.init_process_group("gloo")
+    from phyai_b200 import parallel as P
+    from phyai_b200.engine_config import DeviceConfig, EngineConfig, RuntimeConfig, init_engine_config
+    from phyai_b200.layers import linear as L
+    from phyai_b200.parallel.mesh import Mesh
+
+    init_engine_config(EngineConfig(device=DeviceConfig("cpu", torch.float32), runtime=RuntimeConfig(use_cuda_graph=False)))
+    fails: list[str] = []
+
+    def check(name, got, want, tol=1e-5):
+        err = (got.float() - want.float()).abs().max().item()
+        if not err <= tol * max(1.0, want.float().abs().max().item()):
+            fails.append(f"{name}: err {err:.3g}")
+
+    if mode == "collectives":
+        mesh = P.init((world,), ("tp",), device="cpu")
+        x = torch.arange(6, dtype=torch.float32).reshape(2, 3) + rank
+        check("all_reduce", P.all_reduce(x, "tp"), sum(torch.arange(6.).reshape(2, 3) + r for r in range(world)))
+        check("all_reduce.max", P.all_reduce(x, "tp", reduce="max"), torch.arange(6.).reshape(2, 3) + world - 1)
+        ag = P.all_gather(x, "tp", dim=1)
+        check("all_gather", ag, torch.cat([torch.arange(6.).reshape(2, 3) + r for r in range(world)], 1))
+        rs = P.reduce_scatter(torch.ones(2 * world, 3) * (rank + 1), "tp", dim=0)
+        check("reduce_scatter", rs, torch.ones(2, 3) * sum(range(1, world + 1)))
+        a2a = P.all_to_all(torch.arange(world * 2.).reshape(world * 2, 1) + 100 * rank, "tp", split_dim=0, concat_dim=0)
+        want = torch.cat([torch.arange(2.).reshape(2, 1) + 2 * rank + 100 * r for r in range(world)])
+        check("all_to_all", a2a, want)
+        check("broadcast", P.broadcast(torch.full((3,), float(rank)), "tp", src=1), torch.full((3,), 1.0))
+        if rank == 0:
+            P.send(torch.tensor([7.0]), 1, "tp")
+        elif rank == 1:
+            check("recv", P.recv(torch.zeros(1), 0, "tp"), torch.tensor([7.0]))
+        P.barrier("tp")
+        assert mesh.axis_size("tp") == world and mesh.axis_size("dp") == 1
+    elif mode == "cosmos3_tp":
+        from phyai_b200.models.cosmos3 import Cosmos3Transformer, tiny_cosmos3_config
+        from phyai_b200.weights import load_pretrained, synthetic_state_dict, write_checkpoint
+
+        P.init((world,), ("tp",), device="cpu")
+        L.init()
+        P.register_mesh("single", Mesh((1,), ("tp",), rank=0, build_groups=False, device_type="cpu"))
+        mc = tiny_cosmos3_config(action_gen=True)
+        with P.use_mesh("single"):
+            single = Cosmos3Transformer(mc, params_dtype=torch.float32, device="cpu").eval()
+        tp_model = Cosmos3Transformer(mc, params_dtype=torch.float32, device="cpu").eval()
+        ckpt = Path(tempfile.gettempdir()) / f"phyai_b200_dist_worker_{os.environ['MASTER_PORT']}"
+        if rank == 0:
+            write_checkpoint(ckpt, synthetic_state_dict(single, seed=3, std=0.2))
+        dist.barrier()
+        load_pretrained(single, ckpt, strict=False)
+        load_pretrained(tp_model, ckpt, strict=False)
+        g = torch.Generator().manual_seed(0)
+        ids = torch.randint(0, 256, (2, 6), generator=g)
+        mask = torch.ones(2, 6, dtype=torch.long)
+        vs = (2, 4, 6)
+        lat, act = torch.randn(2, 4, *vs, generator=g), torch.randn(2, 3, 8, generator=g)
+        t = torch.tensor([300.0, 300.0])
+        dom = torch.tensor([1, 2])
+        with P.use_mesh("single"):
+            want = single(lat, t, single.encode_condition(ids, mask, vs, 24.0, action_len=3), action_latents=act, action_domain_id=dom)
+        got = tp_model(lat, t, tp_model.encode_condition(ids, mask, vs, 24.0, action_len=3), action_latents=act, action_domain_id=dom)
+        check("video", got[0], want[0], 1e-4)
+        check("action", got[1], want[1], 1e-4)
+    elif mode == "cosmos3_cfg":
+        from phyai_b200.models.cosmos3 import Cosmos3T2VRequest, Cosmos3T2VScheduler, Cosmos3Transformer, tiny_cosmos3_config
+
+        mesh = P.init((world, 1), ("cfg", "tp"), device="cpu")
+        L.init()
+        tr = Cosmos3Transformer(tiny_cosmos3_config(), params_dtype=torch.float32, device="cpu").eval().init_random(1, std=0.2)
+        g = torch.Generator().manual_seed(0)
+        ids, nids = torch.randint(0, 256, (1, 6), generator=g), torch.randint(0, 256, (1, 6), generator=g)
+        mask = torch.ones(1, 6, dtype=torch.long)
+        req = Cosmos3T2VRequest(ids, mask, nids, mask, video_shape=(2, 4, 6), num_inference_steps=3, guidance_scale=4.0)
+        par = Cosmos3T2VScheduler(tr, device="cpu")
+        par.setup()
+        assert par.cfg_size == world and par.cfg_rank == rank
+        got = par.step(req)
+        P.register_mesh("single", Mesh((1, 1), ("cfg", "tp"), rank=0, build_groups=False, device_type="cpu"))
+        with P.use_mesh("single"):
+            seq = Cosmos3T2VScheduler(tr, device="cpu")
+            seq.setup()
+            assert seq.cfg_size == 1
+            want = seq.step(req)
+        check("cfg-parallel", got, want, 1e-4)
+    else:
+        raise SystemExit(f"unknown mode {mode}")
+
+    ok = torch.tensor([0 if fails else 1])
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    for f in fails:
+        print(f"[rank {rank}] FAIL {f}", flush=True)
+    if rank == 0:
+        print("DIST_OK" if ok.item() == 1 else "DIST_FAILED", flush=True)
+    dist.destroy_process_group()
+    return 0 if ok.item() == 1 else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

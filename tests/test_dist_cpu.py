@@ -1,0 +1,19 @@
+"""Multi-process checks on CPU (gloo, two ranks): collectives, tensor-parallel Cosmos3, CFG-parallel guidance."""
+
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+@pytest.mark.parametrize("mode,port", [("collectives", 29711), ("cosmos3_tp", 29712), ("cosmos3_cfg", 29713)])
+def test_two_ranks(mode, port):
+    env = dict(os.environ, PYTHONPATH=f"{ROOT}:{os.environ.get('PYTHONPATH', '')}", OMP_NUM_THREADS="2")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), str(ROOT / "tests" / "dist_worker_cpu.py"), mode]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "DIST_OK" in r.stdout, (r.stdout + r.stderr)[-4000:]
