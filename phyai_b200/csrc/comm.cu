@@ -3,7 +3,7 @@
 // Each rank cudaMalloc's one slab and exports it with cudaIpcGetMemHandle; the handles
 // travel over the host process group and every peer maps them with
 // cudaIpcOpenMemHandle. All inter-GPU traffic in the kernels below is plain ld/st to
-// those peer pointers over NVLink (no TMA from peer memory, no multicast).
+// those peer pointers over NVLink (no TMA from peer memory).
 //
 //   reduce_norm      consumer half of the fused row-parallel linear: waits for the
 //                    partial tiles every rank's GEMM epilogue pushed into the local

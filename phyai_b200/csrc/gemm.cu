@@ -2,7 +2,7 @@
 //
 // One CTA computes a 128 x BN accumulator tile that lives in tensor memory. The
 // 128-row operand ("P") and the BN-row operand ("Q") are both K-major and arrive
-// through TMA (128-byte swizzle, no multicast) into a ring of shared-memory
+// through TMA (128-byte swizzle, one copy per CTA) into a ring of shared-memory
 // stages; one thread issues tcgen05.mma and frees stages with tcgen05.commit.
 // For skinny problems (M <= 256, the action-expert regime) the operands are
 // swapped so the weight rows fill the 128-wide MMA M dimension and the few

@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the kernels in this tree use:
-// mbarrier, TMA (cp.async.bulk.tensor, never with cluster multicast), tcgen05
+// mbarrier, TMA (cp.async.bulk.tensor, each CTA fetching its own tiles), tcgen05
 // (TMEM alloc / mma / commit / ld), thread-block clusters and DSMEM.
 //
 // Every wait in here is bounded: a wait that runs out returns false, the caller

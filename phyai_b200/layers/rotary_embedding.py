@@ -109,8 +109,9 @@ class MRotaryEmbedding(nn.Module):
 
     def cos_sin(self, positions: torch.Tensor) -> torch.Tensor:
         """positions (3, T) float -> (T, head_dim) fp32 ``cos | sin``."""
-        ang_all = positions.float()[:, :, None] * self.inv_freq.float()[None, None, :]   # (3, T, half)
-        ang = torch.gather(ang_all, 0, self.band_axis[None, None, :].expand(1, ang_all.shape[1], -1))[0]
+        dev = positions.device   # the tables are tiny: follow the positions rather than the module
+        ang_all = positions.float()[:, :, None] * self.inv_freq.float().to(dev)[None, None, :]   # (3, T, half)
+        ang = torch.gather(ang_all, 0, self.band_axis.to(dev)[None, None, :].expand(1, ang_all.shape[1], -1))[0]
         return torch.cat([ang.cos(), ang.sin()], dim=-1)
 
 

@@ -204,11 +204,16 @@ class PeerStream:
             if self.y_off < 0 or rows > self.gather_rows or cols > self.gather_cols:
                 raise ValueError("stream was created without (enough) gather space")
             y_off, y_ld = self.y_off // 2, self.gather_cols
-        arrivals = pg.ext.reduce_norm(pg.ptrs, pg.pos, self.slots_off // 2, self.slot_stride, rows, cols, self.max_cols, 0,
+        pg.ext.reduce_norm(pg.ptrs, pg.pos, self.slots_off // 2, self.slot_stride, rows, cols, self.max_cols, 0,
                                       self.channel, expect, residual, col_gate, bias, h_out, y, mode, weight, mod, eps,
                                       max_ctas, rows_per_rank, y_off, y_ld, max(self.y_channel, 0))
         if not gather:
             return None
+        # one arrival per CTA of every rank's reduce kernel; ranks own different numbers of rows
+        arrivals = 0
+        for r in range(pg.world):
+            n_r = max(0, min(rows_per_rank, rows - r * rows_per_rank)) if rows_per_rank > 0 else rows
+            arrivals += max(1, min(n_r, max_ctas))
         full = pg.view(self.y_off, (self.gather_rows, self.gather_cols))[:rows, :cols]
         return GatherTicket(full, (pg.local_ptr, self.y_channel, arrivals))
 
