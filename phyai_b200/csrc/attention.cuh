@@ -30,5 +30,8 @@ struct AttnParams {
 
 cudaError_t attn_launch(const AttnParams& p, cudaStream_t stream);     // mma.sync path
 cudaError_t attn_tc_launch(const AttnParams& p, cudaStream_t stream);  // tcgen05 path
+// tcgen05 two-tile pipelined path: dense q, contiguous K/V, head_dim <= 128, no KV split
+cudaError_t attn_pp_launch(const AttnParams& p, cudaStream_t stream);
+bool attn_pp_supported(const AttnParams& p);
 
 }  // namespace pb

@@ -55,11 +55,15 @@ class Cosmos3Transformer(nn.Module):
 
     @torch.no_grad()
     def init_random(self, seed: int = 0, std: float = 0.02) -> "Cosmos3Transformer":
-        g = torch.Generator().manual_seed(seed)
+        on_gpu = next(self.parameters()).is_cuda   # billions of values: draw them where they live
+        g = torch.Generator(device=next(self.parameters()).device if on_gpu else "cpu").manual_seed(seed)
         for name, p in self.named_parameters():
             if p.dim() == 1 and ("norm" in name) and "bias" not in name:
                 continue
-            p.copy_((torch.randn(p.shape, generator=g) * std).to(p.dtype))
+            if on_gpu:
+                p.copy_(torch.randn(p.shape, generator=g, device=p.device, dtype=torch.float32).mul_(std).to(p.dtype))
+            else:
+                p.copy_((torch.randn(p.shape, generator=g) * std).to(p.dtype))
         return self
 
     # ---------------------------------------------------------------- patches

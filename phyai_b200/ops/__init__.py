@@ -112,16 +112,22 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[t
     ``q`` ``(tokens, Hq, D)``; ``k``/``v`` ``(rows, Hkv, D)`` pools; sequence ``b`` owns
     query tokens ``q_start[b] + [0, q_len[b])`` and KV entries ``kv_indptr[b] +
     [0, kv_len[b])``, mapped to pool rows through ``kv_indices`` when given.
-    ``impl``: ``"tc"`` (tcgen05 + tensor memory, the default) or ``"mma"`` (mma.sync).
+    ``impl``: ``"tc"`` (tcgen05 + tensor memory, one query tile per CTA: the latency variant),
+    ``"pp"`` (tcgen05, two query tiles per CTA in ping-pong with P kept in tensor memory: the
+    throughput variant for long dense sequences, head_dim <= 128) or ``"mma"`` (mma.sync). By
+    default long unpaged calls take ``"pp"`` and everything else ``"tc"``.
     """
     if impl is None:
         impl = ATTN_IMPL
+        if (impl == "tc" and max_q_len >= 512 and kv_indices is None and splits == 1 and q.shape[-1] <= 128
+                and q.shape[-1] % 8 == 0):
+            impl = "pp"
     if out is None:
         out = torch.empty_like(q)
     if sm_scale is None:
         sm_scale = q.shape[-1] ** -0.5
     ext().attention(q, k, v, out, q_start, q_len, kv_indptr, kv_len, kv_indices, max_q_len,
-                    causal, splits, sm_scale, impl == "tc", trace)
+                    causal, splits, sm_scale, {"mma": 0, "tc": 1, "pp": 2}[impl], trace)
     return out
 
 

@@ -150,6 +150,40 @@ def test_attention(case, impl):
     assert relerr(o, e) < TOL if kl else float(o.abs().max()) == 0.0
 
 
+PP_CASES = [
+    dict(B=1, ql=256, kl=256, Hq=2, Hkv=2, D=128),
+    dict(B=1, ql=700, kl=1000, Hq=5, Hkv=1, D=128),
+    dict(B=2, ql=300, kl=515, Hq=4, Hkv=2, D=64),
+    dict(B=1, ql=640, kl=640, Hq=2, Hkv=1, D=128, causal=True),
+    dict(B=2, ql=130, kl=900, Hq=2, Hkv=2, D=72, causal=True),
+    dict(B=1, ql=1500, kl=2100, Hq=3, Hkv=1, D=128, big=True),
+]
+
+
+@pytest.mark.parametrize("case", PP_CASES, ids=lambda c: "-".join(f"{k}{v}" for k, v in c.items()))
+def test_attention_pipelined(case):
+    """Two-tile ping-pong kernel (P in tensor memory, lazy max) against the fp32 reference."""
+    from phyai_b200 import ops
+    from phyai_b200.ops import ref
+
+    B, ql, kl, Hq, Hkv, D = (case[k] for k in ("B", "ql", "kl", "Hq", "Hkv", "D"))
+    causal = case.get("causal", False)
+    scale = 3.0 if case.get("big") else 1.0     # large logits move the running maximum a lot
+    q = (torch.randn(B * ql, Hq, D, device=DEV) * scale).bfloat16()
+    R = B * kl + 5
+    k = torch.randn(R, Hkv, D, device=DEV).bfloat16()
+    v = torch.randn(R, Hkv, D, device=DEV).bfloat16()
+    ar = torch.arange(B, device=DEV, dtype=torch.int32)
+    q_start, q_len = ar * ql, torch.full((B,), ql, device=DEV, dtype=torch.int32)
+    kv_ptr, kv_len = ar * kl, torch.full((B,), kl, device=DEV, dtype=torch.int32)
+    o = ops.attention(q, k, v, None, q_start, q_len, kv_ptr, kv_len, max_q_len=ql, causal=causal, impl="pp")
+    o2 = ops.attention(q, k, v, None, q_start, q_len, kv_ptr, kv_len, max_q_len=ql, causal=causal, impl="pp")
+    _status_ok()
+    e = ref.attention(q, k, v, q_start.cpu(), q_len.cpu(), kv_ptr.cpu(), kv_len.cpu(), causal=causal)
+    assert relerr(o, e) < TOL
+    assert torch.equal(o, o2)
+
+
 @pytest.mark.parametrize("rows,D", [(50, 1024), (968, 2048), (768, 1152), (7, 4096), (3, 12288)])
 def test_norms(rows, D):
     from phyai_b200 import ops
