@@ -25,6 +25,7 @@
 #include <atomic>
 #include <cstdlib>
 #include <cstring>
+#include <type_traits>
 #include <mutex>
 #include <unordered_map>
 #include <vector>
@@ -72,11 +73,15 @@ constexpr int kMaxStages = 8;
 constexpr int kTileP = 128;        // rows of the 128-row operand = UMMA M
 constexpr int kRowBytes = 128;     // one swizzle-128B row: 64 bf16 or 128 e4m3
 
-template <int BN, bool SWAP, bool FP8>
+// COMM selects the variant that talks to peer GPUs (push / scatter epilogue, wait before the
+// activation loads). The plain variant does not even carry the parameter block, which keeps
+// the launch descriptor of the thousands of ordinary GEMMs in a captured step small.
+struct NoComm { int wait_channel, world; };
+template <int BN, bool SWAP, bool FP8, bool COMM>
 __global__ void __launch_bounds__(kThreads)
 gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
-            EpiParams ep, const __grid_constant__ PushParams push, int total_kb, int kb_per_split,
-            int stages, int* status, unsigned long long* trace) {
+            EpiParams ep, const __grid_constant__ std::conditional_t<COMM, PushParams, NoComm> push,
+            int total_kb, int kb_per_split, int stages, int* status, unsigned long long* trace) {
   constexpr int BK = FP8 ? 128 : 64;                 // elements per k-block
   constexpr int P_BYTES = kTileP * kRowBytes;        // 16 KB
   constexpr int Q_BYTES = BN * kRowBytes;
@@ -146,7 +151,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
       }
     }
     pdl_wait();
-    if (push.wait_channel >= 0) {
+    if constexpr (COMM) if (push.wait_channel >= 0) {
       // the activations were stored by peer GPUs: wait for their arrivals, then order the
       // TMA (async proxy) reads after the acquire
       if (lane == 0) {
@@ -248,14 +253,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
     const int m0 = SWAP ? q_tile * BN : p_tile * kTileP;
     const int n0 = SWAP ? p_tile * kTileP : q_tile * BN;
     const int rows_per_cta = TM / nsplit;
-    if (push.world > 0) {
+    bool pushed = false;
+    if constexpr (COMM) if (push.world > 0) {
+      pushed = true;
       const ChannelSig* ls = reinterpret_cast<const ChannelSig*>(push.local_sig) + push.channel;
       const int parity = int(ld_relaxed_sys(&ls->epoch) & 1u);
       epilogue_push<TN>(push, parity, ep.M, ep.N, smem_u32(smem), reinterpret_cast<const float*>(smem), LDS,
                         m0, n0, split * rows_per_cta, rows_per_cta, nsplit, warp, lane, kThreads / 32);
       __syncthreads();
       if (threadIdx.x == 0) channel_signal_all(push.sig, push.channel, parity, push.world);
-    } else {
+    }
+    if (!pushed) {
       epilogue_pass<TN>(ep, reinterpret_cast<const float*>(smem), smem_u32(smem), LDS, m0, n0,
                         split * rows_per_cta, rows_per_cta, nsplit, warp, lane, kThreads / 32);
     }
@@ -272,7 +280,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
-  if (push.wait_channel >= 0) {
+  if constexpr (COMM) if (push.wait_channel >= 0) {
     ChannelSig* ws = const_cast<ChannelSig*>(reinterpret_cast<const ChannelSig*>(push.local_sig)) + push.wait_channel;
     const int wp = int(ld_relaxed_sys(&ws->epoch) & 1u);  // unchanged until every CTA took its ticket
     channel_finish(ws, wp, gridDim.x * gridDim.y * gridDim.z);
@@ -383,15 +391,26 @@ template <int BN, bool SWAP, bool FP8>
 static cudaError_t launch_inst(const CUtensorMap& tmP, const CUtensorMap& tmQ, const EpiParams& ep,
                                const PushParams& push, dim3 grid, int total_kb, int kbps, int stages, size_t smem,
                                cudaStream_t stream, unsigned long long* trace) {
-  auto kern = gemm_kernel<BN, SWAP, FP8>;
+  if (push.world > 0 || push.wait_channel >= 0) {
+    auto kern = gemm_kernel<BN, SWAP, FP8, true>;
+    static bool attr_done = false;
+    if (!attr_done) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      if (e != cudaSuccess) return e;
+      attr_done = true;
+    }
+    return launch_kernel(kern, grid, dim3(kThreads), smem, stream, int(grid.z), tmP, tmQ, ep, push, total_kb,
+                         kbps, stages, kernel_status_ptr(), trace);
+  }
+  auto kern = gemm_kernel<BN, SWAP, FP8, false>;
   static bool attr_done = false;
   if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         200 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return e;
     attr_done = true;
   }
-  return launch_kernel(kern, grid, dim3(kThreads), smem, stream, int(grid.z), tmP, tmQ, ep, push, total_kb,
+  NoComm none{-1, 0};
+  return launch_kernel(kern, grid, dim3(kThreads), smem, stream, int(grid.z), tmP, tmQ, ep, none, total_kb,
                        kbps, stages, kernel_status_ptr(), trace);
 }
 
