@@ -100,6 +100,28 @@ void gemm(const Tensor& x, const Tensor& w, Tensor& out, const OptT& bias, const
   check(pb::gemm_launch(a, cur_stream()), "gemm_launch");
 }
 
+void gemm_fp8_block(const Tensor& x, const Tensor& w, Tensor& out, const Tensor& a_scale, const Tensor& w_scale,
+                    const OptT& bias, const OptT& residual, const OptT& col_gate, int64_t act, bool glu) {
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2, "gemm_fp8_block: 2-D tensors expected");
+  TORCH_CHECK(x.scalar_type() == at::kFloat8_e4m3fn && w.scalar_type() == at::kFloat8_e4m3fn, "gemm_fp8_block: e4m3 operands");
+  TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1 && out.stride(1) == 1 && x.size(1) == w.size(1), "gemm_fp8_block: layout");
+  pb::GemmArgs a;
+  a.x = x.data_ptr(); a.w = w.data_ptr(); a.out = out.data_ptr();
+  a.M = int(x.size(0)); a.N = int(w.size(0)); a.K = int(x.size(1));
+  a.ldx = int(x.stride(0)); a.ldw = int(w.stride(0)); a.ldo = int(out.stride(0));
+  const int64_t kb = a.K / 128;
+  TORCH_CHECK(a.K % 128 == 0, "gemm_fp8_block: K must be a multiple of 128");
+  TORCH_CHECK(a_scale.is_contiguous() && a_scale.numel() == int64_t(a.M) * kb, "gemm_fp8_block: a_scale must be [M, K/128]");
+  TORCH_CHECK(w_scale.is_contiguous() && w_scale.numel() == int64_t((a.N + 127) / 128) * kb, "gemm_fp8_block: w_scale must be [ceil(N/128), K/128]");
+  TORCH_CHECK(out.size(0) == a.M && out.size(1) == (glu ? a.N / 2 : a.N), "gemm_fp8_block: out shape");
+  a.out_fp32 = out.scalar_type() == at::kFloat;
+  a.a_scale = f32(OptT(a_scale)); a.w_scale = f32(OptT(w_scale));
+  a.bias = bf(bias); a.col_gate = bf(col_gate);
+  if (residual.has_value() && residual->defined()) { a.residual = bf(residual); a.ldr = int(residual->stride(0)); }
+  a.act = int(act); a.glu = glu ? 1 : 0; a.fp8 = 1; a.block_scaled = 1;
+  check(pb::gemm_fp8_block_launch(a, cur_stream()), "gemm_fp8_block_launch");
+}
+
 void attention(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& out,
                const Tensor& q_start, const Tensor& q_len, const Tensor& kv_indptr,
                const Tensor& kv_len, const OptT& kv_indices, int64_t max_q_len, bool causal,
@@ -258,6 +280,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("force_bn") = 0, py::arg("force_swap") = -1, py::arg("force_splits") = 0,
         py::arg("trace") = py::none(), py::arg("wait_sig_ptr") = 0, py::arg("wait_channel") = -1,
         py::arg("wait_expect") = 0);
+  m.def("gemm_fp8_block", &gemm_fp8_block, py::arg("x"), py::arg("w"), py::arg("out"), py::arg("a_scale"), py::arg("w_scale"),
+        py::arg("bias") = py::none(), py::arg("residual") = py::none(), py::arg("col_gate") = py::none(), py::arg("act") = 0,
+        py::arg("glu") = false);
   m.def("attention", &attention, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"),
         py::arg("q_start"), py::arg("q_len"), py::arg("kv_indptr"), py::arg("kv_len"),
         py::arg("kv_indices") = py::none(), py::arg("max_q_len"), py::arg("causal") = false,

@@ -326,8 +326,8 @@ struct TmapKeyHash {
 };
 
 // 2-D K-major operand [rows, cols] with row stride ld (elements), box = 128 bytes x box_rows.
-static bool make_tmap(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
-                      uint32_t box_rows, uint32_t elem_bytes) {
+bool make_tmap_2d(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
+                  uint32_t box_rows, uint32_t elem_bytes) {
   static std::mutex mu;
   static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
   TmapKey key{ptr, rows, cols, ld, box_rows, elem_bytes};
@@ -508,8 +508,8 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream, int* n_ctas) {
   const void* p_ptr = swap ? a.w : a.x;
   const void* q_ptr = swap ? a.x : a.w;
   const int p_ld = swap ? a.ldw : a.ldx, q_ld = swap ? a.ldx : a.ldw;
-  if (!make_tmap(&tmP, p_ptr, p_rows, a.K, p_ld, kTileP, eb)) return cudaErrorInvalidValue;
-  if (!make_tmap(&tmQ, q_ptr, q_rows, a.K, q_ld, bn, eb)) return cudaErrorInvalidValue;
+  if (!make_tmap_2d(&tmP, p_ptr, p_rows, a.K, p_ld, kTileP, eb)) return cudaErrorInvalidValue;
+  if (!make_tmap_2d(&tmQ, q_ptr, q_rows, a.K, q_ld, bn, eb)) return cudaErrorInvalidValue;
 
   EpiParams ep;
   ep.out = a.out; ep.ldo = a.ldo; ep.M = a.M; ep.N = a.N;

@@ -57,6 +57,16 @@ struct GemmArgs {
 // multiplies by the world size to know how many arrivals to expect).
 cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream, int* n_ctas = nullptr);
 
+// 2-D K-major operand map: [rows, cols] with row stride ld (elements), box = 128 bytes x box_rows,
+// 128-byte swizzle (elem_bytes 2 = bf16, 1 = 8-bit).
+bool make_tmap_2d(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
+                  uint32_t box_rows, uint32_t elem_bytes);
+
+// Block-scaled fp8 GEMM (gemm_fp8_block.cu): e4m3 operands, fp32 scales per 1x128 activation block
+// (a_scale [M, K/128]) and per 128x128 weight block (w_scale [ceil(N/128), K/128]); epilogue fields
+// of GemmArgs as for gemm_launch (bias, act, glu, col_gate, residual, out_fp32).
+cudaError_t gemm_fp8_block_launch(const GemmArgs& a, cudaStream_t stream);
+
 // 3-D bf16 tensor map (d, head, row) for the attention kernels (see gemm.cu).
 bool make_tmap_3d_bf16(CUtensorMap* out, const void* ptr, uint64_t D, uint64_t H, uint64_t R,
                        uint64_t head_stride_elems, uint64_t row_stride_elems, uint32_t box_h,

@@ -274,3 +274,23 @@ def test_rope_kv_and_small_ops():
         ye, se = ref.quant_fp8(xq, blk)
         assert relerr(sc, se) < 1e-5 and relerr(y.float(), ye.float()) < 0.08
     _status_ok()
+
+
+@pytest.mark.parametrize("M,N,K,bias", [(300, 512, 1024, True), (50, 1024, 2048, False), (7, 256, 512, True), (968, 2048, 2048, False),
+                                       (129, 392, 384, True)])
+def test_gemm_fp8_block_scaled(M, N, K, bias):
+    """128x128 weight blocks, 1x128 activation blocks, against the dequantise-then-multiply fp32 restatement."""
+    from phyai_b200 import ops
+    from phyai_b200.ops import fp8_block
+
+    x = (torch.randn(M, K, device=DEV) * torch.logspace(-1, 1, K // 128, device=DEV).repeat_interleave(128)).bfloat16()
+    w = torch.randn(N, K, device=DEV) * 0.05 * torch.logspace(-1, 1, -(-N // 128), device=DEV).repeat_interleave(128)[:N, None]
+    b = torch.randn(N, device=DEV).bfloat16() if bias else None
+    w8, ws = fp8_block.quantize_weight_block(w)
+    x8, xs = ops.quant_fp8(x, 128)
+    y = fp8_block.gemm_fp8_block(x8, xs, w8, ws, bias=b)
+    _status_ok()
+    e = fp8_block.ref_gemm_fp8_block(x8, xs, w8, ws, bias=b)
+    assert relerr(y, e) < TOL
+    full = x.float() @ w.t() + (b.float() if bias else 0)
+    assert relerr(y, full) < 0.08          # quantisation error itself
