@@ -96,6 +96,35 @@ def main() -> int:
             assert seq.cfg_size == 1
             want = seq.step(req)
         check("cfg-parallel", got, want, 1e-4)
+    elif mode == "pi05_tp":
+        from phyai_b200.models.pi05.configuration_pi05 import tiny_pi05_config
+        from phyai_b200.models.pi05.main_pi05_tp import PI05TPScheduler
+        from phyai_b200.models.pi05.modeling_pi05 import PI05Model
+        from phyai_b200.models.pi05.scheduler_ws1_pi05 import PI05Request
+        from phyai_b200.weights import load_pretrained, synthetic_state_dict, write_checkpoint
+
+        P.init((world,), ("tp",), device="cpu")
+        L.init()
+        P.register_mesh("single", Mesh((1,), ("tp",), rank=0, build_groups=False, device_type="cpu"))
+        cfg = tiny_pi05_config()
+        with P.use_mesh("single"):
+            single = PI05Model(cfg, device="cpu").eval()
+        tp_model = PI05Model(cfg, device="cpu").eval()
+        ckpt = Path(tempfile.gettempdir()) / f"phyai_b200_dist_worker_{os.environ['MASTER_PORT']}"
+        if rank == 0:
+            write_checkpoint(ckpt, synthetic_state_dict(single, seed=7, std=0.1))
+        dist.barrier()
+        load_pretrained(single, ckpt, strict=False)
+        load_pretrained(tp_model, ckpt, strict=False)
+        g = torch.Generator().manual_seed(0)
+        req = PI05Request(torch.rand(2, 2, 3, 56, 56, generator=g) * 2 - 1, torch.randint(0, 1024, (2, 16), generator=g),
+                          torch.tensor([16, 9]), torch.randn(2, 10, 8, generator=g))
+        with P.use_mesh("single"):
+            want = single.sample_actions(req.pixel_values, req.input_ids, req.lang_lens, req.noise)
+        sch = PI05TPScheduler(tp_model, max_batch_size=2, num_images=2, device="cpu")
+        sch.setup()
+        assert sch.tp_size == world
+        check("pi05 tp", sch.step(req), want, 2e-4)
     else:
         raise SystemExit(f"unknown mode {mode}")
 
