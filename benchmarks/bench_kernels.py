@@ -39,6 +39,8 @@ def bench(fn, n=10, warm=3):
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--set", default="all", choices=("gemm", "attention", "norm", "all"))
+    ap.add_argument("--only", default=None, help="run a single named shape (for profiler captures)")
+    ap.add_argument("--no-baselines", action="store_true", help="skip the library kernels (keeps a profiler capture small)")
     ap.add_argument("--peaks", default=str(Path(__file__).resolve().parents[1] / "MEASURED_PEAKS.json"))
     a = ap.parse_args()
     import torch
@@ -55,30 +57,37 @@ def main() -> None:
                   "pi05.expert.qkv": (50, 1024, 2560), "pi05.expert.gate_up": (50, 1024, 8192), "cosmos3.qkv": (7040, 5120, 7168),
                   "cosmos3.gate_up": (7040, 5120, 27648), "cosmos3.down": (7040, 13824, 5120)}
         for name, (M, K, N) in shapes.items():
+            if a.only and name != a.only:
+                continue
             x, w = torch.randn(M, K, device=dev, dtype=bf) * 0.1, torch.randn(N, K, device=dev, dtype=bf) * 0.1
             out = torch.empty(M, N, device=dev, dtype=bf)
-            t_o, t_c = bench(lambda: ops.gemm(x, w, out)), bench(lambda: torch.matmul(x, w.t()))
+            t_o = bench(lambda: ops.gemm(x, w, out))
+            t_c = float("nan") if a.no_baselines else bench(lambda: torch.matmul(x, w.t()))
             tf = 2 * M * N * K / t_o / 1e9
             rows.append(dict(kernel="gemm", shape=name, ours_ms=round(t_o, 4), cublas_ms=round(t_c, 4), tflops=round(tf, 1),
                              frac_of_measured_bf16=round(tf / peaks["bf16_tflops"], 3)))
     if a.set in ("attention", "all"):
         for name, (S, T, hq, hkv, D) in {"cosmos3.gen": (7040, 512, 40, 8, 128), "cosmos3.gen.tp4": (7040, 512, 10, 2, 128)}.items():
+            if a.only and name != a.only:
+                continue
             q = torch.randn(S, hq, D, device=dev, dtype=bf)
             k, v = torch.randn(S + T, hkv, D, device=dev, dtype=bf), torch.randn(S + T, hkv, D, device=dev, dtype=bf)
             o, z = torch.empty_like(q), torch.zeros(1, dtype=torch.int32, device=dev)
             ql, kl = torch.full((1,), S, dtype=torch.int32, device=dev), torch.full((1,), S + T, dtype=torch.int32, device=dev)
             t_o = bench(lambda: ops.attention(q, k, v, o, z, ql, z, kl, max_q_len=S))
             qq, kk, vv = (t.transpose(0, 1)[None] for t in (q, k, v))
-            t_s = bench(lambda: torch.nn.functional.scaled_dot_product_attention(qq, kk, vv, enable_gqa=True))
+            t_s = float("nan") if a.no_baselines else bench(lambda: torch.nn.functional.scaled_dot_product_attention(qq, kk, vv, enable_gqa=True))
             tf = 4 * S * (S + T) * D * hq / t_o / 1e9
             rows.append(dict(kernel="attention", shape=name, ours_ms=round(t_o, 4), sdpa_ms=round(t_s, 4), tflops=round(tf, 1),
                              frac_of_measured_bf16=round(tf / peaks["bf16_tflops"], 3)))
     if a.set in ("norm", "all"):
         for name, (R, D) in {"rms.7040x5120": (7040, 5120), "rms.65536x4096": (65536, 4096)}.items():
+            if a.only and name != a.only:
+                continue
             x, w = torch.randn(R, D, device=dev, dtype=bf), torch.ones(D, device=dev, dtype=bf)
             y = torch.empty_like(x)
             t_o = bench(lambda: ops.norm(x, "rms", weight=w, out=y))
-            t_e = bench(lambda: (x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6)).to(bf) * w)
+            t_e = float("nan") if a.no_baselines else bench(lambda: (x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6)).to(bf) * w)
             gbs = 2 * R * D * 2 / t_o / 1e6
             rows.append(dict(kernel="rms_norm", shape=name, ours_ms=round(t_o, 4), eager_ms=round(t_e, 4), gbs=round(gbs, 1),
                              frac_of_measured_hbm=round(gbs / peaks["hbm_gbs"], 3)))
