@@ -105,7 +105,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
   unsigned long long* tr = trace ? trace + 32 * (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z))
                                  : nullptr;
   if (tr && threadIdx.x == 0) tr[0] = globaltimer_ns();
-  const int p_tile = blockIdx.x, q_tile = blockIdx.y, split = blockIdx.z;
+  // Tile order: the hardware hands out blockIdx.x fastest. Walking all P tiles of one Q tile
+  // before the next Q tile makes every wave of CTAs re-read the whole P operand; instead the
+  // linear block index sweeps groups of kGroupQ Q-tiles with P-tiles inside, so the ~148 tiles
+  // in flight form a compact block of the output and both operands are reused out of L2.
+  constexpr int kGroupQ = 8;
+  int p_tile, q_tile;
+  {
+    const int P = gridDim.x, Q = gridDim.y;
+    const int lin = blockIdx.x + P * blockIdx.y;
+    const int g = lin / (kGroupQ * P);
+    const int q0 = g * kGroupQ;
+    const int gq = min(kGroupQ, Q - q0);
+    const int r = lin - g * kGroupQ * P;
+    q_tile = q0 + r % gq;
+    p_tile = r / gq;
+  }
+  const int split = blockIdx.z;
   const int nsplit = gridDim.z;
   const int kb0 = split * kb_per_split;
   const int nkb = min(kb_per_split, total_kb - kb0);
