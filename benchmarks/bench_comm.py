@@ -23,11 +23,29 @@ import torch.distributed as dist  # noqa: E402
 NVLINK_GBS = 770.0
 
 
-def timed(fn, n=20, warm=5):
+def timed(fn, n=20, warm=5, graph=False):
+    """Mean device time of ``fn``. ``graph=True`` captures it once and times replays, which is how the serving paths
+    run these kernels (no Python or launch overhead between them)."""
     for _ in range(warm):
         fn()
     torch.cuda.synchronize()
     dist.barrier()
+    if graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            fn()
+            side.synchronize()
+            with torch.cuda.graph(g, stream=side):
+                fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        eager, fn = fn, g.replay
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(n):
@@ -85,13 +103,21 @@ def main() -> None:
             ops.gemm(y, w2, z)
 
         t_f, t_b, t_c = timed(fused), timed(baseline), timed(compute_only)
+        try:
+            g_f, g_b = timed(fused, graph=True), timed(baseline, graph=True)
+        except Exception as e:      # a collective that cannot be captured on this stack
+            g_f = g_b = float("nan")
+            if rank == 0:
+                print(f"# graph timing unavailable for {name}: {type(e).__name__}: {e}", flush=True)
         flops = 2.0 * M * N * K + 2.0 * M * N2 * N
         # per GPU over NVLink: scatter sends (w-1)/w of its partial and gathers (w-1)/w of the normed rows; one-shot sends w-1 partials
         link_bytes = (2.0 * (world - 1) / world * M * N * 2) if scatter else ((world - 1) * M * N * 2.0 + (world - 1) * M * N * 2.0)
         roof_ms = max(flops / (peaks["bf16_tflops"] * 1e9), link_bytes / (NVLINK_GBS * 1e6))
         rows_out.append(dict(shape=name, world=world, mode="scatter+gather" if scatter else "one-shot", fused_ms=round(t_f, 4),
-                             nccl_composition_ms=round(t_b, 4), compute_only_ms=round(t_c, 4), roofline_ms=round(roof_ms, 4),
-                             frac_of_roofline=round(roof_ms / t_f, 3), speedup_vs_nccl=round(t_b / t_f, 3)))
+                             nccl_composition_ms=round(t_b, 4), compute_only_ms=round(t_c, 4), graph_fused_ms=round(g_f, 4),
+                             graph_nccl_composition_ms=round(g_b, 4), roofline_ms=round(roof_ms, 4),
+                             frac_of_roofline=round(roof_ms / min(t_f, g_f if g_f == g_f else t_f), 3),
+                             speedup_vs_nccl=round(t_b / t_f, 3), graph_speedup_vs_nccl=round(g_b / g_f, 3) if g_f == g_f else None))
     if world == 2:
         for name, n in (("cfg.cosmos3.super_latent", 16 * 8 * 44 * 80), ("cfg.cosmos3.720p_latent", 48 * 24 * 45 * 80)):
             v = torch.randn(n, device=dev, dtype=bf)

@@ -471,6 +471,14 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream, int* n_ctas) {
       (reinterpret_cast<uintptr_t>(a.w_scale) & 15))
     return cudaErrorInvalidValue;
   if (a.block_scaled) return cudaErrorInvalidValue;  // handled by gemm_fp8_block_launch
+  if (gemm_persist_eligible(a)) {
+    if (a.push && (a.push->world < 0 || a.push->world > kMaxRanks ||
+                   (a.push->world > 0 && (a.glu || a.act || a.bias || a.residual || a.col_gate)) ||
+                   (a.push->world > 0 && a.push->rows_per_rank > 0 &&
+                    (a.M + a.push->rows_per_rank - 1) / a.push->rows_per_rank > a.push->world)))
+      return cudaErrorInvalidValue;
+    return gemm_persist_launch(a, stream, n_ctas);
+  }
 
   bool swap = a.M <= 256;
   if (a.force_swap == 0) swap = false;

@@ -67,6 +67,10 @@ bool make_tmap_2d(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t col
 // of GemmArgs as for gemm_launch (bias, act, glu, col_gate, residual, out_fp32).
 cudaError_t gemm_fp8_block_launch(const GemmArgs& a, cudaStream_t stream);
 
+// Persistent variant for large bf16 problems (gemm_persist.cu); gemm_launch routes eligible calls to it.
+bool gemm_persist_eligible(const GemmArgs& a);
+cudaError_t gemm_persist_launch(const GemmArgs& a, cudaStream_t stream, int* n_ctas = nullptr);
+
 // 3-D bf16 tensor map (d, head, row) for the attention kernels (see gemm.cu).
 bool make_tmap_3d_bf16(CUtensorMap* out, const void* ptr, uint64_t D, uint64_t H, uint64_t R,
                        uint64_t head_stride_elems, uint64_t row_stride_elems, uint32_t box_h,

@@ -205,11 +205,81 @@ __global__ void norm_kernel(NormArgs a) {
   }
 }
 
+// Many-row variant: one WARP per row, eight rows per CTA, no shared memory and no block barrier.
+// The block-per-row kernel above is shaped for a handful of rows (latency); with thousands of
+// rows its barrier and shared-memory reduction dominate, while here a warp streams its row with
+// 512-byte coalesced accesses, reduces with shuffles and re-reads the row (an L1 / L2 hit) for
+// the second pass. RMS family only (no LayerNorm moments, no fp8 copy, no precomputed sums).
+template <int MODE>
+__global__ void norm_rows_kernel(NormArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  pdl_launch_dependents();
+  pdl_wait();
+  if (row >= a.rows) return;
+  const int nv = a.D >> 3;
+  const BF8* xr = reinterpret_cast<const BF8*>(a.x + size_t(row) * a.ldx);
+  BF8* rr = a.residual ? reinterpret_cast<BF8*>(a.residual + size_t(row) * a.ldr) : nullptr;
+  BF8* yr = reinterpret_cast<BF8*>(a.y + size_t(row) * a.ldy);
+  float s2 = 0.f;
+  for (int v = lane; v < nv; v += 32) {
+    float f[8];
+    unpack8(xr[v], f);
+    if (rr) {
+      float g[8];
+      unpack8(rr[v], g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] += g[i];
+      const BF8 h = pack8(f);
+      rr[v] = h;
+      unpack8(h, f);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s2 += f[i] * f[i];
+  }
+  s2 = warp_sum(s2);
+  const float rstd = rsqrtf(s2 / a.D + a.eps);
+  const BF8* src = rr ? rr : xr;
+  const BF8* wv = a.weight ? reinterpret_cast<const BF8*>(a.weight) : nullptr;
+  const BF8* mv = MODE == kNormAdaRms ? reinterpret_cast<const BF8*>(a.mod + size_t(row / a.group) * 3 * a.D) : nullptr;
+  for (int v = lane; v < nv; v += 32) {
+    float f[8], o[8];
+    unpack8(src[v], f);
+    if (MODE == kNormAdaRms) {
+      float sc[8], sh[8];
+      unpack8(mv[v], sc);
+      unpack8(mv[nv + v], sh);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = f[i] * rstd * (1.f + sc[i]) + sh[i];
+    } else if (MODE == kNormRmsNoWeight) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = f[i] * rstd;
+    } else {
+      float w[8];
+      unpack8(wv[v], w);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = f[i] * rstd * (MODE == kNormGemmaRms ? 1.f + w[i] : w[i]);
+    }
+    yr[v] = pack8(o);
+  }
+}
+
 cudaError_t norm_launch(const NormArgs& a, cudaStream_t s) {
   if (a.rows <= 0) return cudaSuccess;
   if (a.D % 8 || a.ldx % 8 || a.ldy % 8 || (a.residual && a.ldr % 8)) return cudaErrorInvalidValue;
   if (a.y8 && a.y8_block && (a.D % 128)) return cudaErrorInvalidValue;
   if (a.y8 && !a.y) return cudaErrorInvalidValue;
+  if (a.rows >= 1024 && a.mode != kNormLayer && !a.y8 && !a.sumsq && a.y && a.D <= 16384) {
+    const int grid = (a.rows + 7) / 8;
+    switch (a.mode) {
+      case kNormRms: PB_LAUNCH(norm_rows_kernel<kNormRms>, grid, 256, s, a); break;
+      case kNormGemmaRms: PB_LAUNCH(norm_rows_kernel<kNormGemmaRms>, grid, 256, s, a); break;
+      case kNormAdaRms: PB_LAUNCH(norm_rows_kernel<kNormAdaRms>, grid, 256, s, a); break;
+      case kNormRmsNoWeight: PB_LAUNCH(norm_rows_kernel<kNormRmsNoWeight>, grid, 256, s, a); break;
+      default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+  }
   int threads = ((a.D / 8) + 31) / 32 * 32;
   if (threads > 1024) threads = 1024;
   if (threads < 32) threads = 32;

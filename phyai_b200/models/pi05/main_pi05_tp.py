@@ -10,7 +10,7 @@ a TP step adds 2 x 36 reductions per denoise step), so this entry exists for che
 not fit one GPU and for parity with TP-capable layers.
 
 The reference has TP-capable Pi0.5 layers and no scheduler that drives them
-(phyai/src/phyai/models/pi05/modeling_pi05.py:388-1008, SURVEY of its schedulers: ws1 and DP only).
+(phyai/src/phyai/models/pi05/modeling_pi05.py:388-1008; its schedulers are scheduler_ws1_pi05.py and scheduler_wn_pi05.py, single GPU and data parallel).
 """
 
 from __future__ import annotations

@@ -85,6 +85,32 @@ def main() -> int:
         check(f"scatter.y[{it}]", ticket.y, y_ref, 0.05)
         check(f"scatter.gemm[{it}]", z, y_ref.to(torch.bfloat16).float() @ w2.float().t(), 0.05)
 
+    # ---- 3b. the same chain at a size that takes the persistent GEMM (scatter epilogue and waiting loads inside it)
+    M, K, N, N2 = 2304, 512, 4096, 4096
+    stb = pg.stream("big", -(-M // world), N, gather_rows=M, gather_cols=N)
+    for it in range(2):
+        x, _ = rnd(M, K, scale=0.5)
+        w, _ = rnd(N, K, scale=0.1)
+        res, _ = rnd(M, N, per_rank=False)
+        wn, _ = rnd(N, per_rank=False, scale=0.1)
+        w2, _ = rnd(N2, N, per_rank=False, scale=0.05)
+        h = res.clone()
+        ticket = stb.linear_reduce(x, w, scatter=True, residual=h, norm="rms", weight=wn, eps=1e-6, gather=True)
+        z = ops.gemm(ticket.y, w2, wait=ticket.wait, act="silu", glu=True)
+        part = nccl_sum(x.float() @ w.float().t())
+        hb = (res.float() + part).to(torch.bfloat16).float()
+        y_ref = (hb * torch.rsqrt(hb.pow(2).mean(-1, keepdim=True) + 1e-6) * wn.float()).to(torch.bfloat16).float()
+        check(f"persist.y[{it}]", ticket.y, y_ref, 0.05)
+        zz = y_ref @ w2.float().t()
+        check(f"persist.gemm[{it}]", z, torch.nn.functional.silu(zz[:, 0::2]) * zz[:, 1::2], 0.06)
+    # one-shot push through the persistent kernel as well
+    x, _ = rnd(640, 512, scale=0.5)
+    w, _ = rnd(4096, 512, scale=0.1)
+    sto = pg.stream("big1", 640, 4096)
+    out = torch.empty(640, 4096, device=dev, dtype=torch.bfloat16)
+    sto.linear_reduce(x, w, h_out=out)
+    check("persist.one_shot", out, nccl_sum(x.float() @ w.float().t()), 0.03)
+
     # ---- 4. gather of row shards
     x, full = rnd(33, 256)
     got = stl.all_gather_rows(x)

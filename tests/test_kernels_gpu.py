@@ -294,3 +294,23 @@ def test_gemm_fp8_block_scaled(M, N, K, bias):
     assert relerr(y, e) < TOL
     full = x.float() @ w.t() + (b.float() if bias else 0)
     assert relerr(y, full) < 0.08          # quantisation error itself
+
+
+@pytest.mark.parametrize("rows,D", [(1024, 1024), (7040, 5120), (3001, 2048)])
+def test_norms_many_rows(rows, D):
+    """Row counts that take the warp-per-row kernel."""
+    from phyai_b200 import ops
+    from phyai_b200.ops import ref
+
+    x = torch.randn(rows, D, device=DEV).bfloat16()
+    w = (torch.randn(D, device=DEV) * 0.1).bfloat16()
+    assert relerr(ops.norm(x, "rms", weight=w), ref.rms_norm(x, w)) < TOL
+    assert relerr(ops.norm(x, "gemma_rms", weight=w), ref.rms_norm(x, w, gemma=True)) < TOL
+    modr = (torch.randn(rows // 7 + 1, 3 * D, device=DEV) * 0.2).bfloat16()
+    assert relerr(ops.norm(x, "ada_rms", mod=modr, group=7), ref.ada_rms_norm(x, modr.repeat_interleave(7, 0)[:rows])[0]) < TOL
+    r = torch.randn(rows, D, device=DEV).bfloat16()
+    r2 = r.clone()
+    y = ops.norm(x, "rms", weight=w, residual=r2)
+    h = (x.float() + r.float()).bfloat16()
+    assert relerr(r2, h) < 1e-2 and relerr(y, ref.rms_norm(h, w)) < TOL
+    _status_ok()
