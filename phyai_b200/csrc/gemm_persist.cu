@@ -304,6 +304,11 @@ bool gemm_persist_eligible(const GemmArgs& a) {
   }
   // fewer tiles than SMs: the one-tile-per-CTA kernel splits K over a cluster and fills the chip better
   if (((a.M + kPM - 1) / kPM) * ((a.N + kPN - 1) / kPN) < sms) return false;
+  if (a.push && (a.push->world > 0 || a.push->wait_channel >= 0)) {
+    // peer variants of this kernel: PHYAI_GEMM_PERSIST_COMM=0 keeps them on the one-tile-per-CTA kernel
+    static const bool comm_on = [] { const char* e = getenv("PHYAI_GEMM_PERSIST_COMM"); return !(e && e[0] == '0'); }();
+    if (!comm_on) return false;
+  }
   if (a.push && a.push->world > 0 && (a.push->ld % 8 || a.push->slots_off % 8 || a.push->slot_stride % 8)) return false;
   return a.M >= 512 && a.N >= 2048 && a.K >= 256 && !a.fp8 && !a.out_fp32 && !a.row_scale && !a.sumsq && !a.a_scale &&
          !a.w_scale && !a.trace && a.force_bn == 0 && a.force_swap == -1 && a.force_splits == 0 &&

@@ -12,6 +12,7 @@ import abc
 import dataclasses
 import importlib
 import logging
+import time
 from dataclasses import dataclass, field
 from typing import Any, ClassVar
 
@@ -22,6 +23,7 @@ from .engine_config import EngineConfig, init_engine_config
 from .layers import linear as L
 from .utils.cuda import init_cublas, init_cuda
 from .utils.logging import this_rank_log
+from .utils.metrics import metrics
 
 logger = logging.getLogger(__name__)
 
@@ -117,6 +119,7 @@ class Engine:
         if not isinstance(args.plugin_args, entry_cls.args_cls):
             raise TypeError(f"plugin {args.plugin!r} expects {entry_cls.args_cls.__name__}, "
                             f"got {type(args.plugin_args).__name__}")
+        self.plugin_name = args.plugin
         self.entry: Entry = entry_cls()
         self.entry.setup(args.plugin_args)
         if cfg.runtime.debug_tensor_dump_dir:
@@ -130,9 +133,13 @@ class Engine:
     def step(self, request: Any) -> Any:
         if self._closed:
             raise RuntimeError("Engine.step after close()")
+        t0 = time.perf_counter()
         out = self.entry.step(request)
         if self._dumper is not None:
             self._dumper.flush()
+        m = metrics()
+        m.inc(f"engine.steps.{self.plugin_name}")
+        m.observe(f"engine.step_host_ms.{self.plugin_name}", (time.perf_counter() - t0) * 1e3)   # host side: launch + any sync the plugin does
         return out
 
     def close(self) -> None:

@@ -106,6 +106,7 @@ class envs:
     PHYAI_NCCL_SO_PATH = EnvField("PHYAI_NCCL_SO_PATH", None, str)
     PHYAI_COMM_TIMEOUT_S = EnvField("PHYAI_COMM_TIMEOUT_S", 60.0, float)
     PHYAI_HEARTBEAT_S = EnvField("PHYAI_HEARTBEAT_S", 0.0, float)
+    PHYAI_USE_PYNCCL = EnvField("PHYAI_USE_PYNCCL", False, parse_bool)   # register the ctypes NCCL backend ahead of torch's
     PHYAI_PEER_COMM = EnvField("PHYAI_PEER_COMM", True, parse_bool)    # fused peer-memory collectives (0: NCCL only)
     PHYAI_PEER_HEAP_MB = EnvField("PHYAI_PEER_HEAP_MB", 0, int)          # symmetric heap size override
     # debug / tensor dump

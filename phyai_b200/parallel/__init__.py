@@ -21,6 +21,7 @@ from typing import Sequence
 import torch
 
 from . import state
+from ..env import envs
 from .backend import Backend, Call, Mode, Op, Topology
 from .dispatch import Dispatcher
 from .dist import destroy_dist, init_dist
@@ -36,7 +37,8 @@ AXES = ("dp", "cfg", "ep", "sp", "cp", "tp")
 
 
 def init(layout: Sequence[int] = (1,), mesh_dim_names: Sequence[str] = ("tp",), *, device: str = "cuda",
-         backend: str | None = None, name: str = "model", enable_peer: bool = True) -> Mesh:
+         backend: str | None = None, name: str = "model", enable_peer: bool = True, enable_pynccl: bool | None = None,
+         pynccl_axes: Sequence[str] | None = None, pynccl_library_path: str | None = None) -> Mesh:
     """Create and register the mesh ``name`` and install the dispatcher.
 
     ``layout`` gives the size of every axis in ``mesh_dim_names`` (outermost first).
@@ -73,6 +75,16 @@ def init(layout: Sequence[int] = (1,), mesh_dim_names: Sequence[str] = ("tp",), 
                     import logging
 
                     logging.getLogger(__name__).warning("peer-memory backend unavailable: %s", e)
+            if enable_pynccl if enable_pynccl is not None else envs.PHYAI_USE_PYNCCL.get():
+                # NCCL through ctypes: one communicator per axis, ops enqueue on the current stream
+                try:
+                    from .backends.pynccl import PyNcclBackend
+
+                    registry.register(PyNcclBackend(mesh, list(pynccl_axes) if pynccl_axes is not None else None, pynccl_library_path))
+                except Exception as e:
+                    import logging
+
+                    logging.getLogger(__name__).warning("pynccl backend unavailable: %s", e)
             registry.register(NcclBackend())
             registry.register(GlooBackend())
         elif kind == "gloo":
