@@ -65,6 +65,7 @@ _BUILTIN_PLUGINS = {
     "pi05_wn": "phyai_b200.models.pi05.main_pi05_wn",
     "pi05_tp": "phyai_b200.models.pi05.main_pi05_tp",
     "pi0": "phyai_b200.models.pi0.main_pi0",
+    "pi0_wn": "phyai_b200.models.pi0.main_pi0_wn",
     "cosmos3": "phyai_b200.models.cosmos3.main_cosmos3",
     "cosmos3_wn": "phyai_b200.models.cosmos3.main_cosmos3_wn",
     "cosmos3_policy": "phyai_b200.models.cosmos3.main_cosmos3_policy",

@@ -73,7 +73,7 @@ class PI0Entry(Entry):
         self.model: PI0Model | None = None
         self.scheduler: PI0WS1Scheduler | None = None
 
-    def setup(self, args: PI0Args) -> None:  # type: ignore[override]
+    def build_local(self, args: PI0Args, max_batch_size: int) -> PI0WS1Scheduler:
         eng = get_engine_config()
         config = args.config or (load_config(args.checkpoint_dir, PI0Config) if args.checkpoint_dir else PI0Config())
         with use_quant_plan(load_quant_plan(args.checkpoint_dir)):
@@ -83,8 +83,11 @@ class PI0Entry(Entry):
         elif args.random_init_seed is not None:
             self.model.init_random(args.random_init_seed)
         n_img = resolve_num_images(args.inputs_image_shape, config.vision.num_channels)
-        self.scheduler = PI0WS1Scheduler(self.model, max_batch_size=args.max_batch_size, num_images=n_img,
-                                         device=eng.device.target, use_cuda_graph=eng.runtime.use_cuda_graph)
+        return PI0WS1Scheduler(self.model, max_batch_size=max_batch_size, num_images=n_img,
+                               device=eng.device.target, use_cuda_graph=eng.runtime.use_cuda_graph)
+
+    def setup(self, args: PI0Args) -> None:  # type: ignore[override]
+        self.scheduler = self.build_local(args, args.max_batch_size)
         self.scheduler.setup()
 
     def step(self, request: PI0Request) -> torch.Tensor:  # type: ignore[override]

@@ -44,11 +44,22 @@ class PI05WNScheduler(Scheduler):
                                f"world_size={self.mesh.world_size}")
         self.local.setup()
 
+    # ---- what travels: subclasses for other request types override these three
     def _shapes(self):
+        """Per-rank shard shapes and dtypes (None = the parameter dtype), in the order of ``_pack``."""
         cfg, pr = self.cfg, self.per_rank_B
         v = cfg.vision
-        return ((pr, self.num_images, v.num_channels, v.image_size, v.image_size), (pr, cfg.tokenizer_max_length),
-                (pr,), (pr, cfg.chunk_size, cfg.max_action_dim))
+        return [((pr, self.num_images, v.num_channels, v.image_size, v.image_size), None), ((pr, cfg.tokenizer_max_length), torch.int64),
+                ((pr,), torch.int64), ((pr, cfg.chunk_size, cfg.max_action_dim), None)]
+
+    def _pack(self, request, real_B: int) -> list[torch.Tensor]:
+        dev, dt = self.device, self.dtype
+        nz = request.noise.to(dev, dt) if request.noise is not None else torch.randn(
+            real_B, self.cfg.chunk_size, self.cfg.max_action_dim, device=dev, dtype=dt)
+        return [request.pixel_values.to(dev, dt), request.input_ids.to(dev, torch.int64), request.lang_lens.to(dev, torch.int64), nz]
+
+    def _unpack(self, tensors: list[torch.Tensor]):
+        return PI05Request(*tensors)
 
     @torch.no_grad()
     def step(self, request: PI05Request | None) -> torch.Tensor:
@@ -72,28 +83,21 @@ class PI05WNScheduler(Scheduler):
         if int(head[0]) != 1:
             raise err if err is not None else RuntimeError("rank 0 rejected the request")
         real_B = int(head[1])
-        px_s, ids_s, len_s, nz_s = self._shapes()
         if R == 0:
             total = N * pr
-            px = _pad_rows(request.pixel_values.to(dev, dt), total)
-            ids = _pad_rows(request.input_ids.to(dev, torch.int64), total)
-            lens = _pad_rows(request.lang_lens.to(dev, torch.int64), total)
-            nz = request.noise.to(dev, dt) if request.noise is not None else torch.randn(
-                real_B, *nz_s[1:], device=dev, dtype=dt)
-            nz = _pad_rows(nz, total)
+            full = [_pad_rows(t, total) for t in self._pack(request, real_B)]
             ops_ = []
             for r in range(1, N):
-                for t in (px, ids, lens, nz):
+                for t in full:
                     ops_.append(dist.P2POp(dist.isend, t[r * pr:(r + 1) * pr].contiguous(), ranks[r], group))
             for w in dist.batch_isend_irecv(ops_):
                 w.wait()
-            shard = PI05Request(px[:pr], ids[:pr], lens[:pr], nz[:pr])
+            shard = self._unpack([t[:pr] for t in full])
         else:
-            bufs = [torch.empty(px_s, dtype=dt, device=dev), torch.empty(ids_s, dtype=torch.int64, device=dev),
-                    torch.empty(len_s, dtype=torch.int64, device=dev), torch.empty(nz_s, dtype=dt, device=dev)]
+            bufs = [torch.empty(shape, dtype=dt if kind is None else kind, device=dev) for shape, kind in self._shapes()]
             for w in dist.batch_isend_irecv([dist.P2POp(dist.irecv, b, ranks[0], group) for b in bufs]):
                 w.wait()
-            shard = PI05Request(*bufs)
+            shard = self._unpack(bufs)
         # rows past real_B are padding: give them an empty prompt so they cost the smallest bucket
         local = self.local.step(shard)
         gathered = P.all_gather(local.contiguous(), axis="dp", dim=0, mesh=self.mesh)

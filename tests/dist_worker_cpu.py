@@ -125,6 +125,61 @@ def main() -> int:
         sch.setup()
         assert sch.tp_size == world
         check("pi05 tp", sch.step(req), want, 2e-4)
+    elif mode in ("pi05_dp", "pi0_dp"):
+        from phyai_b200.engine import Engine, EngineArgs
+        from phyai_b200.engine_config import ParallelConfig
+
+        ec = EngineConfig(device=DeviceConfig("cpu", torch.float32), runtime=RuntimeConfig(use_cuda_graph=False),
+                          parallel=ParallelConfig(world_size=world, dp_size=world))
+        single_ec = EngineConfig(device=DeviceConfig("cpu", torch.float32), runtime=RuntimeConfig(use_cuda_graph=False))
+        g = torch.Generator().manual_seed(0)
+        B = 2 * world - 1                                # last rank gets a padded row
+        px, ids, lens = torch.rand(B, 2, 3, 56, 56, generator=g) * 2 - 1, torch.randint(0, 1024, (B, 16), generator=g), torch.randint(1, 17, (B,), generator=g)
+        noise = torch.randn(B, 10, 8, generator=g)
+        shape = [[56, 56, 3]] * 2
+        if mode == "pi05_dp":
+            from phyai_b200.models.pi05.configuration_pi05 import tiny_pi05_config
+            from phyai_b200.models.pi05.main_pi05 import PI05Args
+            from phyai_b200.models.pi05.main_pi05_wn import PI05WNArgs
+            from phyai_b200.models.pi05.scheduler_ws1_pi05 import PI05Request
+
+            kw = dict(config=tiny_pi05_config(), inputs_image_shape=shape, random_init_seed=3)
+            req = PI05Request(px, ids, lens, noise)
+            eng = Engine(EngineArgs("pi05_wn", PI05WNArgs(max_batch_size=2 * world, **kw), ec))
+            ref_args = ("pi05", PI05Args(max_batch_size=B, **kw))
+        else:
+            from phyai_b200.models.pi0.configuration_pi0 import tiny_pi0_config
+            from phyai_b200.models.pi0.main_pi0 import PI0Args
+            from phyai_b200.models.pi0.main_pi0_wn import PI0WNArgs
+            from phyai_b200.models.pi0.scheduler_ws1_pi0 import PI0Request
+
+            kw = dict(config=tiny_pi0_config(), inputs_image_shape=shape, random_init_seed=3)
+            req = PI0Request(px, ids, lens, torch.randn(B, 8, generator=g), noise)
+            eng = Engine(EngineArgs("pi0_wn", PI0WNArgs(max_batch_size=2 * world, **kw), ec))
+            ref_args = ("pi0", PI0Args(max_batch_size=B, **kw))
+        out = eng.step(req if rank == 0 else None)
+        if rank == 0:
+            assert out.shape[0] == B
+            # the same request through the single-process plugin (same seed -> same weights)
+            P.register_mesh("single", Mesh((1,), ("tp",), rank=0, build_groups=False, device_type="cpu"))
+            from phyai_b200.models.pi05.modeling_pi05 import PI05Model  # noqa: F401  (import side effects only)
+            with P.use_mesh("single"):
+                model = eng.entry.model
+                if mode == "pi05_dp":
+                    want = model.sample_actions(px, ids, lens, noise)
+                else:
+                    want = model.sample_actions(px, ids, lens, req.state, noise)
+            check(mode, out, want, 2e-4)
+        # an oversize batch must raise on every rank instead of leaving peers in a receive
+        big = None
+        if rank == 0:
+            big = type(req)(*[torch.cat([t] * 3) if isinstance(t, torch.Tensor) else t for t in (getattr(req, f) for f in req.__dataclass_fields__)])
+        try:
+            eng.step(big)
+            fails.append("oversize batch was accepted")
+        except (ValueError, RuntimeError):
+            pass
+        eng.entry.scheduler.local.close()
     else:
         raise SystemExit(f"unknown mode {mode}")
 
