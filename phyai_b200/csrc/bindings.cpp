@@ -56,7 +56,7 @@ void gemm(const Tensor& x, const Tensor& w, Tensor& out, const OptT& bias, const
           int64_t res_mod, const OptT& col_gate, const OptT& row_scale, const OptT& sumsq,
           int64_t act, bool glu, const OptT& a_scale, const OptT& w_scale, int64_t force_bn,
           int64_t force_swap, int64_t force_splits, const OptT& trace, int64_t wait_sig_ptr,
-          int64_t wait_channel, int64_t wait_expect) {
+          int64_t wait_channel, int64_t wait_expect, int64_t row_rms_dim, double row_rms_eps) {
   TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2, "gemm: 2-D tensors expected");
   TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1 && out.stride(1) == 1, "gemm: rows must be contiguous");
   TORCH_CHECK(x.size(1) == w.size(1), "gemm: K mismatch");
@@ -79,6 +79,7 @@ void gemm(const Tensor& x, const Tensor& w, Tensor& out, const OptT& bias, const
   }
   a.col_gate = bf(col_gate);
   a.row_scale = f32(row_scale);
+  a.row_rms_dim = int(row_rms_dim); a.row_rms_eps = float(row_rms_eps);
   a.sumsq = const_cast<float*>(f32(sumsq));
   a.act = int(act); a.glu = glu ? 1 : 0; a.fp8 = fp8 ? 1 : 0;
   a.a_scale = f32(a_scale); a.w_scale = f32(w_scale);
@@ -186,7 +187,7 @@ void norm(const Tensor& x, const OptT& y, int64_t mode, const OptT& weight, cons
 void rope_kv(const Tensor& qkv, int64_t Hq, int64_t Hkv, int64_t D, const OptT& pos,
              const OptT& cos_sin, int64_t rot_dim, const OptT& q_norm_w, const OptT& k_norm_w,
              double norm_eps, Tensor& q_out, const OptT& k_pool, const OptT& v_pool,
-             const OptT& slots, int64_t slot_base) {
+             const OptT& slots, int64_t slot_base, const OptT& zero) {
   TORCH_CHECK(qkv.dim() == 2 && qkv.stride(1) == 1, "rope_kv: qkv layout");
   TORCH_CHECK(qkv.size(1) == (Hq + 2 * Hkv) * D, "rope_kv: qkv width");
   pb::RopeKvArgs a;
@@ -202,6 +203,10 @@ void rope_kv(const Tensor& qkv, int64_t Hq, int64_t Hkv, int64_t D, const OptT& 
     a.pool_row_stride = k_pool->stride(0);
   }
   a.slots = i64(slots); a.slot_base = slot_base;
+  if (zero.has_value() && zero->defined()) {
+    TORCH_CHECK(zero->is_contiguous(), "rope_kv: zero must be contiguous");
+    a.zero = const_cast<float*>(f32(zero)); a.zero_n = int(zero->numel());
+  }
   check(pb::rope_kv_launch(a, cur_stream()), "rope_kv_launch");
 }
 
@@ -279,7 +284,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("glu") = false, py::arg("a_scale") = py::none(), py::arg("w_scale") = py::none(),
         py::arg("force_bn") = 0, py::arg("force_swap") = -1, py::arg("force_splits") = 0,
         py::arg("trace") = py::none(), py::arg("wait_sig_ptr") = 0, py::arg("wait_channel") = -1,
-        py::arg("wait_expect") = 0);
+        py::arg("wait_expect") = 0, py::arg("row_rms_dim") = 0, py::arg("row_rms_eps") = 0.0);
   m.def("gemm_fp8_block", &gemm_fp8_block, py::arg("x"), py::arg("w"), py::arg("out"), py::arg("a_scale"), py::arg("w_scale"),
         py::arg("bias") = py::none(), py::arg("residual") = py::none(), py::arg("col_gate") = py::none(), py::arg("act") = 0,
         py::arg("glu") = false);
@@ -295,7 +300,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("pos") = py::none(), py::arg("cos_sin") = py::none(), py::arg("rot_dim") = 0,
         py::arg("q_norm_w") = py::none(), py::arg("k_norm_w") = py::none(),
         py::arg("norm_eps") = 1e-6, py::arg("q_out"), py::arg("k_pool") = py::none(),
-        py::arg("v_pool") = py::none(), py::arg("slots") = py::none(), py::arg("slot_base") = 0);
+        py::arg("v_pool") = py::none(), py::arg("slots") = py::none(), py::arg("slot_base") = 0,
+        py::arg("zero") = py::none());
   m.def("embedding", &embedding, py::arg("ids"), py::arg("table"), py::arg("lo"), py::arg("hi"),
         py::arg("scale"), py::arg("out"), py::arg("dst_rows") = py::none());
   m.def("im2col", &im2col);

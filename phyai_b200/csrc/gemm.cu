@@ -541,6 +541,7 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream, int* n_ctas) {
   ep.col_gate = a.col_gate; ep.row_scale = a.row_scale; ep.sumsq = a.sumsq;
   ep.a_scale = a.a_scale; ep.w_scale = a.w_scale;
   ep.act = a.act; ep.glu = a.glu; ep.out_fp32 = a.out_fp32;
+  ep.rs_inv_dim = a.row_rms_dim > 0 ? 1.f / float(a.row_rms_dim) : 0.f; ep.rs_eps = a.row_rms_eps;
 
   PushParams push;
   memset(&push, 0, sizeof(push));

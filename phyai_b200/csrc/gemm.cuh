@@ -14,7 +14,9 @@ enum GemmAct : int { kActNone = 0, kActGeluTanh = 1, kActSilu = 2, kActGeluErf =
 // out[M, N'] = epilogue( X[M, K] @ W[N, K]^T ), bf16 (or e4m3) operands, fp32 accumulate.
 //
 // Epilogue, in this order, on the fp32 accumulator acc[m, n]:
-//   acc *= row_scale[m]                 (row_scale != null; e.g. a fused RMS 1/rms)
+//   acc *= row_scale[m]                 (row_scale != null; e.g. a fused RMS 1/rms; with row_rms_dim > 0
+//                                        row_scale[m] is a sum of squares and the factor is
+//                                        rsqrt(row_scale[m] / row_rms_dim + row_rms_eps))
 //   acc *= a_scale[m] * w_scale[n]      (per-row / per-channel dequant scales, fp8 only)
 //   acc += bias[n]                      (bias != null)
 //   acc  = act(acc)                     (act != none, glu == 0)
@@ -36,6 +38,8 @@ struct GemmArgs {
   int res_mod = 0;                          // 0: residual row = m
   const __nv_bfloat16* col_gate = nullptr;  // [N]
   const float* row_scale = nullptr;         // [M]
+  int row_rms_dim = 0;                      // > 0: row_scale is the sum of squares of a row of that width
+  float row_rms_eps = 0.f;
   float* sumsq = nullptr;                   // [M]
   int act = kActNone;
   int glu = 0;

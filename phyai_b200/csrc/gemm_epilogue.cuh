@@ -25,6 +25,7 @@ struct EpiParams {
   const float* a_scale;
   const float* w_scale;
   int act, glu, out_fp32;
+  float rs_inv_dim = 0.f, rs_eps = 0.f;   // > 0: row_scale holds a sum of squares, scale = rsqrt(ss * inv_dim + eps)
 };
 
 __device__ __forceinline__ float epi_act(float v, int act) {
@@ -117,7 +118,10 @@ __device__ __forceinline__ void epilogue_pass_t(const EpiParams& ep, const float
         const __nv_bfloat16* res_row = nullptr;
         if constexpr (AUX) {
           float rscale = 1.f;
-          if (ep.row_scale) rscale = ep.row_scale[m];
+          if (ep.row_scale) {
+            rscale = ep.row_scale[m];
+            if (ep.rs_inv_dim > 0.f) rscale = rsqrtf(rscale * ep.rs_inv_dim + ep.rs_eps);
+          }
           if (ep.a_scale) rscale *= ep.a_scale[m];
 #pragma unroll
           for (int t = 0; t < 4; ++t) x[t] = x[t] * (rscale * ws4[t]) + bias4[t];

@@ -24,6 +24,7 @@
 #include "comm_device.cuh"
 #include "gemm.cuh"
 #include "gemm_epilogue.cuh"
+#include "gemm_row_epilogue.cuh"
 #include "launch.cuh"
 #include "ptx.cuh"
 
@@ -34,22 +35,6 @@ constexpr int kPThreads = 192;
 constexpr int kPStages = 4;
 constexpr int kPM = 128, kPN = 256, kPBK = 64;
 constexpr int kPStageBytes = (kPM + kPN) * 128;   // 48 KB
-constexpr int kPGroupQ = 8;
-
-__device__ __forceinline__ void tile_coords(int t, int P, int Q, int& p, int& q) {
-  const int g = t / (kPGroupQ * P);
-  const int q0 = g * kPGroupQ;
-  const int gq = min(kPGroupQ, Q - q0);
-  const int r = t - g * kPGroupQ * P;
-  q = q0 + r % gq;
-  p = r / gq;
-}
-
-__device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float (&f)[8]) {
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) { f[2 * i] = __bfloat162float(h[i].x); f[2 * i + 1] = __bfloat162float(h[i].y); }
-}
 }  // namespace
 
 // COMM: the variant that talks to peer GPUs. `push.world > 0`: the bare bf16 product goes to the slots of
@@ -101,7 +86,7 @@ gemm_persist_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
     int it = 0;
     for (int t = blockIdx.x; t < n_tiles && !err_s; t += gridDim.x) {
       int p, q;
-      tile_coords(t, p_tiles, q_tiles, p, q);
+      grouped_tile_coords(t, p_tiles, q_tiles, p, q);
       for (int kb = 0; kb < total_kb; ++kb, ++it) {
         const int s = it % kPStages;
         if (it >= kPStages && !mbar_wait(&empty_bar[s], uint32_t((it / kPStages) & 1) ^ 1)) { err_s = kStatusTimeoutEmpty; break; }
@@ -150,7 +135,7 @@ gemm_persist_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
       push_parity = int(ld_relaxed_sys(&(reinterpret_cast<const ChannelSig*>(push.local_sig) + push.channel)->epoch) & 1u);
     for (int t = blockIdx.x; t < n_tiles && !err_s; t += gridDim.x, ++ti) {
       int p, q;
-      tile_coords(t, p_tiles, q_tiles, p, q);
+      grouped_tile_coords(t, p_tiles, q_tiles, p, q);
       const int buf = ti & 1;
       if (!mbar_wait(&tfull[buf], uint32_t((ti >> 1) & 1))) { err_s = kStatusTimeoutAcc; break; }
       tc_fence_after();
@@ -187,57 +172,7 @@ gemm_persist_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
             }
             continue;
           }
-          if (ep.bias) {
-            float b[8];
-            unpack_bf16x8(*reinterpret_cast<const uint4*>(ep.bias + n), b);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) x[j] += b[j];
-          }
-          if constexpr (GLU) {
-            float y[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) y[j] = epi_act_c<ACT>(x[2 * j]) * x[2 * j + 1];
-            const int no = n >> 1;
-            if (ep.col_gate) {
-              const uint2 gr = *reinterpret_cast<const uint2*>(ep.col_gate + no);
-              const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gr);
-              y[0] *= __bfloat162float(g2[0].x); y[1] *= __bfloat162float(g2[0].y);
-              y[2] *= __bfloat162float(g2[1].x); y[3] *= __bfloat162float(g2[1].y);
-            }
-            if (res_row) {
-              const uint2 rr = *reinterpret_cast<const uint2*>(res_row + no);
-              const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rr);
-              y[0] += __bfloat162float(r2[0].x); y[1] += __bfloat162float(r2[0].y);
-              y[2] += __bfloat162float(r2[1].x); y[3] += __bfloat162float(r2[1].y);
-            }
-            const __nv_bfloat162 o0 = __floats2bfloat162_rn(y[0], y[1]), o1 = __floats2bfloat162_rn(y[2], y[3]);
-            uint2 o;
-            o.x = *reinterpret_cast<const uint32_t*>(&o0);
-            o.y = *reinterpret_cast<const uint32_t*>(&o1);
-            *reinterpret_cast<uint2*>(out_row + no) = o;
-          } else {
-            if constexpr (ACT != 0) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) x[j] = epi_act_c<ACT>(x[j]);
-            }
-            if (ep.col_gate) {
-              float gt[8];
-              unpack_bf16x8(*reinterpret_cast<const uint4*>(ep.col_gate + n), gt);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) x[j] *= gt[j];
-            }
-            if (res_row) {
-              float rs[8];
-              unpack_bf16x8(*reinterpret_cast<const uint4*>(res_row + n), rs);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) x[j] += rs[j];
-            }
-            uint4 o;
-            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]);
-            *reinterpret_cast<uint4*>(out_row + n) = o;
-          }
+          row_epilogue_8<ACT, GLU>(ep, x, n, res_row, out_row);
         }
       }
       tc_fence_before();

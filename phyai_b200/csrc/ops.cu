@@ -304,6 +304,10 @@ __global__ void rope_kv_kernel(RopeKvArgs a) {
   const int H = a.Hq + 2 * a.Hkv;
   pdl_launch_dependents();
   pdl_wait();
+  if (a.zero) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.zero_n; i += (long long)gridDim.x * blockDim.x)
+      a.zero[i] = 0.f;
+  }
   if (wid >= (long long)a.M * H) return;
   const int tok = int(wid / H), h = int(wid % H);
   const int D = a.D, half_rot = (a.rot_dim > 0 ? a.rot_dim : D) >> 1;

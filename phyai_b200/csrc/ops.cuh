@@ -45,6 +45,8 @@ struct RopeKvArgs {
   long long pool_row_stride = 0;
   const long long* slots = nullptr;     // [M] pool row per token (null: row = slot_base + token)
   long long slot_base = 0;
+  float* zero = nullptr;                // optional fp32 scratch cleared by this launch (e.g. the sum-of-squares
+  int zero_n = 0;                       // accumulators a later GEMM epilogue adds into)
 };
 cudaError_t rope_kv_launch(const RopeKvArgs& a, cudaStream_t s);
 

@@ -53,6 +53,19 @@ class PI0Plan(PI05Plan):
         te = heads.time_embedding(ts).to(torch.bfloat16).float()
         bias = te @ wt.t() + heads.action_time_mlp_in.bias.float() + wa @ heads.action_in_proj.bias.float()
         self.time_bias = bias.to(torch.bfloat16).contiguous()
+        if self.fold_norms:
+            # Gemma RMSNorm weights (1 + w) folded into the weights that consume the normed rows; the
+            # per-row 1/rms is applied in that GEMM's epilogue from sums of squares accumulated by the
+            # epilogue of the GEMM that wrote the rows (the first block of a pass keeps its norm kernel).
+            def fold(w, norm_w):
+                return (w.float() * (1.0 + norm_w.float())[None, :]).to(torch.bfloat16).contiguous()
+
+            stack = self.model.expert_stack
+            self.fold_qkv = [fold(l.attn.qkv.weight, l.input_layernorm.weight) for l in stack.layers]
+            self.fold_gate_up = [fold(l.mlp.gate_up.weight, l.post_attention_layernorm.weight) for l in stack.layers]
+            self.fold_out = fold(heads.action_out_proj.weight, stack.norm.weight)
+            self.e_ss = torch.zeros(2, self.Me, dtype=torch.float32, device=self.device)
+            self.s_ss = torch.zeros(2, self.B, dtype=torch.float32, device=self.device)
 
     def set_layout(self, layout: PI05Layout) -> bool:
         changed = super().set_layout(layout)
@@ -63,10 +76,26 @@ class PI0Plan(PI05Plan):
             self.s_kvlen.copy_(torch.tensor([r + 1 for r in real], dtype=torch.int32))
         return changed
 
-    def _block(self, layer, li, h, x, qkv, q, attn, act, pos, slots, qstart, qlen, kvlen, max_q, splits) -> None:
+    def _block(self, layer, li, h, x, qkv, q, attn, act, pos, slots, qstart, qlen, kvlen, max_q, splits,
+               ss=None) -> None:
         t, e = self.cfg.text, self.cfg.expert
         Hq, Hkv, D = t.num_attention_heads, t.num_key_value_heads, t.head_dim
         kpool, vpool = self.pool.layer(li)
+        if ss is not None:
+            rms = (e.hidden_size, e.rms_norm_eps)
+            if li == 0:
+                ops.norm(h, "gemma_rms", weight=layer.input_layernorm.weight, eps=e.rms_norm_eps, out=x)
+                ops.gemm(x, layer.attn.qkv.weight, qkv)
+            else:
+                ops.gemm(h, self.fold_qkv[li], qkv, row_scale=ss[0], row_rms=rms)
+            ops.rope_kv(qkv, Hq, Hkv, D, q, pos=pos, cos_sin=self.cos_sin, k_pool=kpool, v_pool=vpool, slots=slots,
+                        zero=ss)
+            ops.attention(q.unflatten(1, (Hq, D)), kpool, vpool, attn.unflatten(1, (Hq, D)), qstart, qlen,
+                          self.e_kvptr, kvlen, max_q_len=max_q, splits=splits, sm_scale=D ** -0.5)
+            ops.gemm(attn, layer.attn.o.weight, h, residual=h, sumsq=ss[1])
+            ops.gemm(h, self.fold_gate_up[li], act, row_scale=ss[1], row_rms=rms, act="gelu_tanh", glu=True)
+            ops.gemm(act, layer.mlp.down.weight, h, residual=h, sumsq=ss[0])
+            return
         ops.norm(h, "gemma_rms", weight=layer.input_layernorm.weight, eps=e.rms_norm_eps, out=x)
         ops.gemm(x, layer.attn.qkv.weight, qkv)
         ops.rope_kv(qkv, Hq, Hkv, D, q, pos=pos, cos_sin=self.cos_sin, k_pool=kpool, v_pool=vpool, slots=slots)
@@ -79,12 +108,13 @@ class PI0Plan(PI05Plan):
 
     def expert(self) -> None:
         cfg, heads, stack = self.cfg, self.model.heads, self.model.expert_stack
-        Me = self.Me
+        Me, fold = self.Me, self.fold_norms
         # ---- state token, once per request
         ops.gemm(self.state, heads.state_proj.weight, self.s_h, bias=heads.state_proj.bias)
         for li, layer in enumerate(stack.layers):
             self._block(layer, li, self.s_h, self.s_x, self.s_qkv, self.s_q, self.s_attn, self.s_act, self.s_pos,
-                        self.s_slots, self.s_qstart, self.s_qlen, self.s_kvlen, 1, self.expert_splits)
+                        self.s_slots, self.s_qstart, self.s_qlen, self.s_kvlen, 1, self.expert_splits,
+                        ss=self.s_ss if fold else None)
         # ---- Euler loop over the action tokens
         self.x_t.copy_(self.noise.view(Me, -1))
         for i in range(cfg.num_inference_steps):
@@ -92,9 +122,14 @@ class PI0Plan(PI05Plan):
             ops.gemm(self.e_t, heads.action_time_mlp_out.weight, self.e_h, bias=heads.action_time_mlp_out.bias)
             for li, layer in enumerate(stack.layers):
                 self._block(layer, li, self.e_h, self.e_x, self.e_qkv, self.e_q, self.e_attn, self.e_act, self.e_pos,
-                            self.e_slots, self.e_qstart, self.e_qlen, self.e_kvlen, self.C, self.expert_splits)
-            ops.norm(self.e_h, "gemma_rms", weight=stack.norm.weight, eps=cfg.expert.rms_norm_eps, out=self.e_x)
-            ops.gemm(self.e_x, heads.action_out_proj.weight, self.e_v, bias=heads.action_out_proj.bias)
+                            self.e_slots, self.e_qstart, self.e_qlen, self.e_kvlen, self.C, self.expert_splits,
+                            ss=self.e_ss if fold else None)
+            if fold:
+                ops.gemm(self.e_h, self.fold_out, self.e_v, bias=heads.action_out_proj.bias, row_scale=self.e_ss[0],
+                         row_rms=(cfg.expert.hidden_size, cfg.expert.rms_norm_eps))
+            else:
+                ops.norm(self.e_h, "gemma_rms", weight=stack.norm.weight, eps=cfg.expert.rms_norm_eps, out=self.e_x)
+                ops.gemm(self.e_x, heads.action_out_proj.weight, self.e_v, bias=heads.action_out_proj.bias)
             ops.axpy(self.x_t, self.e_v, self.dt)
         self.out.view(Me, -1).copy_(self.x_t)
 

@@ -48,6 +48,8 @@ class PI05Layout:
 class PI05Plan:
     #: suffix tokens in front of the action tokens (Pi0 puts one state token there)
     suffix_extra = 0
+    #: fold the expert's AdaRMS norms into the neighbouring GEMMs (one weight copy per Euler step)
+    fold_norms = True
 
     def __init__(self, model: PI05Model, *, max_batch_size: int = 1, num_images: int = 3,
                  device: torch.device | str = "cuda") -> None:
@@ -153,6 +155,36 @@ class PI05Plan:
         self.mod_in = [l.input_layernorm.project_modulation(conds) for l in stack.layers]
         self.mod_post = [l.post_attention_layernorm.project_modulation(conds) for l in stack.layers]
         self.mod_final = stack.norm.project_modulation(conds)
+        if self.fold_norms:
+            self._fold_modulation(stack)
+
+    def _fold_modulation(self, stack) -> None:
+        """Per Euler step, fold each AdaRMS (1 + scale) into the weight that consumes the normed rows
+        and (shift @ W^T) into a bias, so that ``norm(h) @ W^T`` becomes one GEMM on the raw rows with
+        a per-row ``rsqrt(mean(h^2) + eps)`` factor in its epilogue. The row sums of squares come from
+        the epilogue of the GEMM that wrote ``h``. Costs one weight copy per step (a few GB)."""
+        He = self.cfg.expert.hidden_size
+        dt = torch.bfloat16
+
+        def fold(w: torch.Tensor, mod: torch.Tensor, bias: torch.Tensor | None = None):
+            scale, shift = mod[:, :He].float(), mod[:, He:2 * He].float()
+            wf = w.float()
+            folded = torch.empty(mod.shape[0], *w.shape, dtype=dt, device=w.device)
+            for i in range(mod.shape[0]):                       # one step at a time: bounded fp32 scratch
+                folded[i] = (wf * (1.0 + scale[i])[None, :]).to(dt)
+            b = shift @ wf.T
+            if bias is not None:
+                b = b + bias.float()[None, :]
+            return folded, b.to(dt).contiguous()
+
+        self.fold_qkv, self.fold_gate_up = [], []
+        for li, layer in enumerate(stack.layers):
+            # the first block of a step keeps its norm kernel: nothing upstream accumulates its sums
+            self.fold_qkv.append(fold(layer.attn.qkv.weight, self.mod_in[li]) if li > 0 else None)
+            self.fold_gate_up.append(fold(layer.mlp.gate_up.weight, self.mod_post[li]))
+        heads = self.model.heads
+        self.fold_out = fold(heads.action_out_proj.weight, self.mod_final, heads.action_out_proj.bias)
+        self.e_ss = torch.zeros(2, self.Me, dtype=torch.float32, device=self.device)
 
     def set_layout(self, layout: PI05Layout) -> bool:
         """Write the metadata of a request shape into the static buffers. Returns True if it changed."""
@@ -247,6 +279,8 @@ class PI05Plan:
         h, x = self.e_h, self.e_x
         q3, a3 = self.e_q.unflatten(1, (Hq, D)), self.e_attn.unflatten(1, (Hq, D))
         self.x_t.copy_(self.noise.view(Me, -1))
+        if self.fold_norms:
+            return self._expert_folded()
         for i in range(cfg.num_inference_steps):
             ops.gemm(self.x_t, heads.action_in_proj.weight, h, bias=heads.action_in_proj.bias)
             for li, layer in enumerate(stack.layers):
@@ -264,6 +298,40 @@ class PI05Plan:
                 ops.gemm(self.e_act, layer.mlp.down.weight, h, residual=h, col_gate=m_post[0, 2 * He:])
             ops.norm(h, "ada_rms", mod=self.mod_final[i:i + 1], group=Me, eps=e.rms_norm_eps, out=x)
             ops.gemm(x, heads.action_out_proj.weight, self.e_v, bias=heads.action_out_proj.bias)
+            ops.axpy(self.x_t, self.e_v, self.dt)
+        self.out.view(Me, -1).copy_(self.x_t)
+
+    def _expert_folded(self) -> None:
+        """Six launches per block: the two AdaRMS kernels live in the epilogues around them."""
+        cfg, e, t = self.cfg, self.cfg.expert, self.cfg.text
+        heads, stack = self.model.heads, self.model.expert_stack
+        Hq, Hkv, D, He, Me = t.num_attention_heads, t.num_key_value_heads, t.head_dim, e.hidden_size, self.Me
+        h, x = self.e_h, self.e_x
+        q3, a3 = self.e_q.unflatten(1, (Hq, D)), self.e_attn.unflatten(1, (Hq, D))
+        ss_in, ss_post = self.e_ss[0], self.e_ss[1]
+        rms = (He, e.rms_norm_eps)
+        for i in range(cfg.num_inference_steps):
+            ops.gemm(self.x_t, heads.action_in_proj.weight, h, bias=heads.action_in_proj.bias)
+            for li, layer in enumerate(stack.layers):
+                kpool, vpool = self.pool.layer(li)
+                m_in, m_post = self.mod_in[li][i:i + 1], self.mod_post[li][i:i + 1]
+                if li == 0:
+                    ops.norm(h, "ada_rms", mod=m_in, group=Me, eps=e.rms_norm_eps, out=x)
+                    ops.gemm(x, layer.attn.qkv.weight, self.e_qkv)
+                else:
+                    w, b = self.fold_qkv[li]
+                    ops.gemm(h, w[i], self.e_qkv, bias=b[i], row_scale=ss_in, row_rms=rms)
+                # both accumulators are idle here: ss_in was consumed above, ss_post by the previous block
+                ops.rope_kv(self.e_qkv, Hq, Hkv, D, self.e_q, pos=self.e_pos, cos_sin=self.cos_sin, k_pool=kpool,
+                            v_pool=vpool, slots=self.e_slots, zero=self.e_ss)
+                ops.attention(q3, kpool, vpool, a3, self.e_qstart, self.e_qlen, self.e_kvptr, self.e_kvlen,
+                              max_q_len=self.C, splits=self.expert_splits, sm_scale=D ** -0.5)
+                ops.gemm(self.e_attn, layer.attn.o.weight, h, residual=h, col_gate=m_in[0, 2 * He:], sumsq=ss_post)
+                w, b = self.fold_gate_up[li]
+                ops.gemm(h, w[i], self.e_act, bias=b[i], row_scale=ss_post, row_rms=rms, act="gelu_tanh", glu=True)
+                ops.gemm(self.e_act, layer.mlp.down.weight, h, residual=h, col_gate=m_post[0, 2 * He:], sumsq=ss_in)
+            w, b = self.fold_out
+            ops.gemm(h, w[i], self.e_v, bias=b[i], row_scale=ss_in, row_rms=rms)
             ops.axpy(self.x_t, self.e_v, self.dt)
         self.out.view(Me, -1).copy_(self.x_t)
 

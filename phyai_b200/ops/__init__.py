@@ -80,12 +80,17 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *
          act: str | None = "none", glu: bool = False, out_dtype: torch.dtype = torch.bfloat16,
          a_scale: Optional[torch.Tensor] = None, w_scale: Optional[torch.Tensor] = None,
          force_bn: int = 0, force_swap: int = -1, force_splits: int = 0,
-         trace: Optional[torch.Tensor] = None, wait: Optional[tuple[int, int, int]] = None) -> torch.Tensor:
+         trace: Optional[torch.Tensor] = None, wait: Optional[tuple[int, int, int]] = None,
+         row_rms: Optional[tuple[int, float]] = None) -> torch.Tensor:
     """``out = epilogue(x @ w.T)`` on tcgen05 tensor cores (see ``csrc/gemm.cuh``).
 
     ``wait=(signal_array_ptr, channel, arrivals)``: ``x`` lives in symmetric memory and is being
     written by peer GPUs; the kernel waits for that many arrivals on the channel before it loads
     ``x`` and closes the channel's call when it is done (all-gather fused into the GEMM).
+
+    ``row_rms=(dim, eps)``: ``row_scale`` holds the sum of squares of each row of the un-normed
+    activation (what another GEMM's ``sumsq`` accumulated) and the epilogue multiplies by
+    ``rsqrt(row_scale / dim + eps)``: an RMSNorm whose weight was folded into ``w``.
 
     ``x`` is ``(M, K)``, ``w`` is ``(N, K)`` (the ``nn.Linear`` layout), both bf16 or
     both float8_e4m3fn (then ``a_scale`` (M,) and ``w_scale`` (N,) dequantise). With
@@ -97,7 +102,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *
         out = torch.empty((M, N // 2 if glu else N), dtype=out_dtype, device=x.device)
     ext().gemm(x, w, out, bias, residual, res_mod, col_gate, row_scale, sumsq, ACT[act], glu,
                a_scale, w_scale, force_bn, force_swap, force_splits, trace,
-               *((0, -1, 0) if wait is None else wait))
+               *((0, -1, 0) if wait is None else wait), *((0, 0.0) if row_rms is None else row_rms))
     return out
 
 
@@ -155,10 +160,13 @@ def rope_kv(qkv: torch.Tensor, Hq: int, Hkv: int, D: int, q_out: torch.Tensor, *
             rot_dim: int = 0, q_norm_w: Optional[torch.Tensor] = None,
             k_norm_w: Optional[torch.Tensor] = None, norm_eps: float = 1e-6,
             k_pool: Optional[torch.Tensor] = None, v_pool: Optional[torch.Tensor] = None,
-            slots: Optional[torch.Tensor] = None, slot_base: int = 0) -> torch.Tensor:
-    """Split fused qkv rows, optional per-head RMSNorm, rotate q/k, scatter k/v to the pool."""
+            slots: Optional[torch.Tensor] = None, slot_base: int = 0,
+            zero: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Split fused qkv rows, optional per-head RMSNorm, rotate q/k, scatter k/v to the pool.
+
+    ``zero``: an fp32 scratch tensor the launch also clears (sum-of-squares accumulators)."""
     ext().rope_kv(qkv, Hq, Hkv, D, pos, cos_sin, rot_dim, q_norm_w, k_norm_w, norm_eps, q_out,
-                  k_pool, v_pool, slots, slot_base)
+                  k_pool, v_pool, slots, slot_base, zero)
     return q_out
 
 

@@ -87,6 +87,35 @@ def test_gemm_sumsq_and_determinism():
         assert torch.equal(o, o2)
 
 
+@pytest.mark.parametrize("M,glu", [(50, False), (50, True), (1, False), (300, True)])
+def test_gemm_folded_rms_norm(M, glu):
+    """norm(h) @ W^T as one GEMM: (1 + scale) folded into W, shift @ W^T as a bias, 1/rms in the epilogue."""
+    from phyai_b200 import ops
+
+    K, N, eps = 1024, 2048, 1e-6
+    g = torch.Generator(device="cpu").manual_seed(M)
+    h0 = (torch.randn(M, K, generator=g) * 2).bfloat16().to(DEV)
+    wo = (torch.randn(K, K, generator=g) * 0.03).bfloat16().to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16().to(DEV)
+    scale, shift = (torch.randn(K, generator=g) * 0.3).to(DEV), (torch.randn(K, generator=g) * 0.3).to(DEV)
+    ss = torch.full((2, M), 7.0, device=DEV)                       # dirty: the rope launch clears it
+    qkv, q = torch.zeros(M, 3 * 64, device=DEV).bfloat16(), torch.zeros(M, 64, device=DEV).bfloat16()
+    ops.rope_kv(qkv, 1, 1, 64, q, zero=ss)
+    assert float(ss.abs().max()) == 0.0
+    h = ops.gemm(h0, wo, residual=h0, sumsq=ss[1])                 # producer: h and its row sums of squares
+    w_fold = (w.float() * (1 + scale)[None, :]).bfloat16()
+    bias = (shift @ w.float().T).bfloat16()
+    act = "gelu_tanh" if glu else "none"
+    out = ops.gemm(h, w_fold, bias=bias, row_scale=ss[1], row_rms=(K, eps), act=act, glu=glu)
+    _status_ok()
+    hf = h.float()
+    x = hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + eps) * (1 + scale) + shift
+    y = x @ w.float().T
+    if glu:
+        y = torch.nn.functional.gelu(y[:, 0::2], approximate="tanh") * y[:, 1::2]
+    assert relerr(out, y) < 2e-2, relerr(out, y)
+
+
 def test_gemm_rejects_misaligned():
     from phyai_b200 import ops
 

@@ -72,6 +72,13 @@ def test_pi0_plan_matches_eager(batch):
     eng = Engine(EngineArgs("pi0", PI0Args(config=cfg, max_batch_size=2, inputs_image_shape=[[56, 56, 3]] * 2),
                             EngineConfig(device=DeviceConfig("cuda:0", torch.bfloat16), runtime=RuntimeConfig(use_cuda_graph=True))))
     g = torch.Generator().manual_seed(10 + batch)
+    # random init leaves the RMSNorm weights at identity: perturb them so that folding them into the
+    # neighbouring GEMM weights is visible, then rebuild the plan's prepared weights
+    with torch.no_grad():
+        for name, p in eng.entry.model.expert_stack.named_parameters():
+            if p.dim() == 1 and "norm" in name:
+                p.copy_((torch.randn(p.shape, generator=g) * 0.2).to(p))
+    eng.entry.scheduler.plan.build_modulation_tables()
     lens = torch.tensor([33, 9][:batch])
     req = PI0Request((torch.rand(batch, 2, 3, 56, 56, generator=g) * 2 - 1).bfloat16().cuda(),
                      torch.randint(0, 1024, (batch, 48), generator=g).cuda(), lens.cuda(),
