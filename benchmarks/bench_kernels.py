@@ -41,6 +41,7 @@ def main() -> None:
     ap.add_argument("--set", default="all", choices=("gemm", "attention", "norm", "all"))
     ap.add_argument("--only", default=None, help="run a single named shape (for profiler captures)")
     ap.add_argument("--no-baselines", action="store_true", help="skip the library kernels (keeps a profiler capture small)")
+    ap.add_argument("--gemm-2cta", action="store_true", help="also time the CTA-pair (cta_group::2) GEMM kernel")
     ap.add_argument("--peaks", default=str(Path(__file__).resolve().parents[1] / "MEASURED_PEAKS.json"))
     a = ap.parse_args()
     import torch
@@ -66,6 +67,11 @@ def main() -> None:
             tf = 2 * M * N * K / t_o / 1e9
             rows.append(dict(kernel="gemm", shape=name, ours_ms=round(t_o, 4), cublas_ms=round(t_c, 4), tflops=round(tf, 1),
                              frac_of_measured_bf16=round(tf / peaks["bf16_tflops"], 3)))
+            if a.gemm_2cta and M >= 512:
+                ops.set_gemm_2cta(True)
+                t_2 = bench(lambda: ops.gemm(x, w, out))
+                ops.set_gemm_2cta(None)
+                rows[-1].update(cta_pair_ms=round(t_2, 4), cta_pair_tflops=round(2 * M * N * K / t_2 / 1e9, 1))
     if a.set in ("attention", "all"):
         for name, (S, T, hq, hkv, D) in {"cosmos3.gen": (7040, 512, 40, 8, 128), "cosmos3.gen.tp4": (7040, 512, 10, 2, 128)}.items():
             if a.only and name != a.only:

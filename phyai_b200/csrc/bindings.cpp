@@ -56,7 +56,8 @@ void gemm(const Tensor& x, const Tensor& w, Tensor& out, const OptT& bias, const
           int64_t res_mod, const OptT& col_gate, const OptT& row_scale, const OptT& sumsq,
           int64_t act, bool glu, const OptT& a_scale, const OptT& w_scale, int64_t force_bn,
           int64_t force_swap, int64_t force_splits, const OptT& trace, int64_t wait_sig_ptr,
-          int64_t wait_channel, int64_t wait_expect, int64_t row_rms_dim, double row_rms_eps) {
+          int64_t wait_channel, int64_t wait_expect, int64_t row_rms_dim, double row_rms_eps,
+          const OptT& rope, const OptT& zero) {
   TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2, "gemm: 2-D tensors expected");
   TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1 && out.stride(1) == 1, "gemm: rows must be contiguous");
   TORCH_CHECK(x.size(1) == w.size(1), "gemm: K mismatch");
@@ -80,6 +81,16 @@ void gemm(const Tensor& x, const Tensor& w, Tensor& out, const OptT& bias, const
   a.col_gate = bf(col_gate);
   a.row_scale = f32(row_scale);
   a.row_rms_dim = int(row_rms_dim); a.row_rms_eps = float(row_rms_eps);
+  if (rope.has_value() && rope->defined()) {
+    TORCH_CHECK(rope->is_cuda() && rope->scalar_type() == at::kByte && rope->is_contiguous() &&
+                rope->numel() == int64_t(sizeof(pb::RopeEpi)), "gemm: rope must come from rope_epilogue_desc");
+    TORCH_CHECK(a.N % 4 == 0, "gemm: rope epilogue needs N % 4 == 0");
+    a.rope = reinterpret_cast<const pb::RopeEpi*>(rope->data_ptr());
+  }
+  if (zero.has_value() && zero->defined()) {
+    TORCH_CHECK(zero->is_contiguous(), "gemm: zero must be contiguous");
+    a.zero = const_cast<float*>(f32(zero)); a.zero_n = int(zero->numel());
+  }
   a.sumsq = const_cast<float*>(f32(sumsq));
   a.act = int(act); a.glu = glu ? 1 : 0; a.fp8 = fp8 ? 1 : 0;
   a.a_scale = f32(a_scale); a.w_scale = f32(w_scale);
@@ -184,6 +195,29 @@ void norm(const Tensor& x, const OptT& y, int64_t mode, const OptT& weight, cons
   check(pb::norm_launch(a, cur_stream()), "norm_launch");
 }
 
+// Device-resident descriptor for the GEMM's rotate-and-scatter epilogue (see pb::RopeEpi). The caller
+// keeps the returned tensor and every tensor named here alive for as long as launches use it.
+Tensor rope_epilogue_desc(const Tensor& q_out, const Tensor& k_pool, const Tensor& v_pool, const Tensor& cos_sin,
+                          const Tensor& pos, const Tensor& slots, int64_t Hq, int64_t Hkv, int64_t D) {
+  TORCH_CHECK(q_out.dim() == 2 && q_out.stride(1) == 1 && q_out.size(1) == Hq * D, "rope_epilogue_desc: q_out layout");
+  TORCH_CHECK(k_pool.stride(0) == v_pool.stride(0) && k_pool.stride(0) >= Hkv * D, "rope_epilogue_desc: pools");
+  TORCH_CHECK(D % 8 == 0 && cos_sin.size(-1) == D && cos_sin.is_contiguous(), "rope_epilogue_desc: cos_sin must be [positions, D]");
+  pb::RopeEpi r;
+  memset(&r, 0, sizeof(r));
+  r.q_out = bfm(q_out);
+  r.k_pool = bfm(k_pool);
+  r.v_pool = bfm(v_pool);
+  r.cos_sin = f32(cos_sin);
+  r.pos = i32(pos);
+  r.slots = i64(slots);
+  TORCH_CHECK(r.pos && r.slots, "rope_epilogue_desc: pos (int32) and slots (int64) are required");
+  r.pool_stride = k_pool.stride(0);
+  r.ldq = int(q_out.stride(0)); r.Hq = int(Hq); r.Hkv = int(Hkv); r.D = int(D);
+  Tensor host = at::empty({int64_t(sizeof(r))}, at::TensorOptions().dtype(at::kByte));
+  memcpy(host.data_ptr(), &r, sizeof(r));
+  return host.to(q_out.device());
+}
+
 void rope_kv(const Tensor& qkv, int64_t Hq, int64_t Hkv, int64_t D, const OptT& pos,
              const OptT& cos_sin, int64_t rot_dim, const OptT& q_norm_w, const OptT& k_norm_w,
              double norm_eps, Tensor& q_out, const OptT& k_pool, const OptT& v_pool,
@@ -284,7 +318,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("glu") = false, py::arg("a_scale") = py::none(), py::arg("w_scale") = py::none(),
         py::arg("force_bn") = 0, py::arg("force_swap") = -1, py::arg("force_splits") = 0,
         py::arg("trace") = py::none(), py::arg("wait_sig_ptr") = 0, py::arg("wait_channel") = -1,
-        py::arg("wait_expect") = 0, py::arg("row_rms_dim") = 0, py::arg("row_rms_eps") = 0.0);
+        py::arg("wait_expect") = 0, py::arg("row_rms_dim") = 0, py::arg("row_rms_eps") = 0.0,
+        py::arg("rope") = py::none(), py::arg("zero") = py::none());
+  m.def("rope_epilogue_desc", &rope_epilogue_desc, py::arg("q_out"), py::arg("k_pool"), py::arg("v_pool"),
+        py::arg("cos_sin"), py::arg("pos"), py::arg("slots"), py::arg("Hq"), py::arg("Hkv"), py::arg("D"));
   m.def("gemm_fp8_block", &gemm_fp8_block, py::arg("x"), py::arg("w"), py::arg("out"), py::arg("a_scale"), py::arg("w_scale"),
         py::arg("bias") = py::none(), py::arg("residual") = py::none(), py::arg("col_gate") = py::none(), py::arg("act") = 0,
         py::arg("glu") = false);
@@ -316,6 +353,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("launch_counter", [] { return pb::launch_counter(); });
   m.def("reset_launch_counter", [] { pb::reset_launch_counter(); });
   m.def("set_pdl", [](bool on) { pb::set_pdl_enabled(on); });
+  m.def("set_gemm_2cta", [](int64_t mode) { pb::set_gemm_2cta(int(mode)); });
   m.def("pdl_enabled", [] { return pb::pdl_enabled(); });
   register_comm(m);
 }

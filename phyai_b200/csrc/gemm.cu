@@ -264,6 +264,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
   if (tr && threadIdx.x == 0) tr[4] = globaltimer_ns();
   const int err = err_s;
 
+  if (ep.zero && blockIdx.x + blockIdx.y + blockIdx.z == 0) {
+    // predecessors have completed (every thread is past its dependency wait), successors still wait on this grid
+    for (int i = threadIdx.x; i < ep.zero_n; i += kThreads) ep.zero[i] = 0.f;
+  }
   if (err == 0) {
     // ------------------------- reduce over the cluster + epilogue + store
     const int m0 = SWAP ? q_tile * BN : p_tile * kTileP;
@@ -471,6 +475,7 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream, int* n_ctas) {
       (reinterpret_cast<uintptr_t>(a.w_scale) & 15))
     return cudaErrorInvalidValue;
   if (a.block_scaled) return cudaErrorInvalidValue;  // handled by gemm_fp8_block_launch
+  if (gemm_2cta_eligible(a)) return gemm_2cta_launch(a, stream);
   if (gemm_persist_eligible(a)) {
     if (a.push && (a.push->world < 0 || a.push->world > kMaxRanks ||
                    (a.push->world > 0 && (a.glu || a.act || a.bias || a.residual || a.col_gate)) ||
@@ -542,6 +547,8 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream, int* n_ctas) {
   ep.a_scale = a.a_scale; ep.w_scale = a.w_scale;
   ep.act = a.act; ep.glu = a.glu; ep.out_fp32 = a.out_fp32;
   ep.rs_inv_dim = a.row_rms_dim > 0 ? 1.f / float(a.row_rms_dim) : 0.f; ep.rs_eps = a.row_rms_eps;
+  ep.rope = a.rope; ep.zero = a.zero; ep.zero_n = a.zero_n;
+  if (a.rope && (a.glu || a.act || a.residual || a.col_gate || a.sumsq || a.fp8 || a.out_fp32)) return cudaErrorInvalidValue;
 
   PushParams push;
   memset(&push, 0, sizeof(push));

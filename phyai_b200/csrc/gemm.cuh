@@ -26,6 +26,21 @@ enum GemmAct : int { kActNone = 0, kActGeluTanh = 1, kActSilu = 2, kActGeluErf =
 //   acc += residual[m % res_mod, n]     (residual != null)
 //   sumsq[m] += sum_n acc^2             (sumsq != null; fp32 atomics; feeds a fused RMSNorm)
 //   store bf16 (or fp32 when out_fp32)
+// Destination of a fused-QKV projection whose epilogue rotates q / k and scatters k / v to the KV
+// pool (lives in device memory; the kernel gets a pointer). The weight rows of every q and k head
+// are permuted so that output column 2i of a head is dimension i and column 2i + 1 is dimension
+// i + D/2: a rotation pair sits in adjacent accumulator columns. v heads keep their order.
+struct RopeEpi {
+  __nv_bfloat16* q_out;        // [M, Hq * D], row stride ldq
+  __nv_bfloat16* k_pool;       // [slots, Hkv * D], row stride pool_stride
+  __nv_bfloat16* v_pool;
+  const float* cos_sin;        // [positions, D]: cos(D/2) | sin(D/2)
+  const int* pos;              // [M] table row per token
+  const long long* slots;      // [M] pool row per token
+  long long pool_stride;
+  int ldq, Hq, Hkv, D;
+};
+
 struct GemmArgs {
   const void* x = nullptr;   // [M, K], row stride ldx elements
   const void* w = nullptr;   // [N, K], row stride ldw elements
@@ -38,6 +53,9 @@ struct GemmArgs {
   int res_mod = 0;                          // 0: residual row = m
   const __nv_bfloat16* col_gate = nullptr;  // [N]
   const float* row_scale = nullptr;         // [M]
+  const RopeEpi* rope = nullptr;     // device pointer: rotate q / k and scatter k / v instead of storing `out`
+  float* zero = nullptr;                    // fp32 scratch this launch clears (not the one it accumulates into)
+  int zero_n = 0;
   int row_rms_dim = 0;                      // > 0: row_scale is the sum of squares of a row of that width
   float row_rms_eps = 0.f;
   float* sumsq = nullptr;                   // [M]
@@ -74,6 +92,11 @@ cudaError_t gemm_fp8_block_launch(const GemmArgs& a, cudaStream_t stream);
 // Persistent variant for large bf16 problems (gemm_persist.cu); gemm_launch routes eligible calls to it.
 bool gemm_persist_eligible(const GemmArgs& a);
 cudaError_t gemm_persist_launch(const GemmArgs& a, cudaStream_t stream, int* n_ctas = nullptr);
+
+// CTA-pair variant (gemm_2cta.cu): 256 x 256 tiles on two SMs with tcgen05.mma.cta_group::2.
+bool gemm_2cta_eligible(const GemmArgs& a);
+cudaError_t gemm_2cta_launch(const GemmArgs& a, cudaStream_t stream);
+void set_gemm_2cta(int mode);   // 1 on, 0 off, -1 follow the PHYAI_GEMM_2CTA variable
 
 // 3-D bf16 tensor map (d, head, row) for the attention kernels (see gemm.cu).
 bool make_tmap_3d_bf16(CUtensorMap* out, const void* ptr, uint64_t D, uint64_t H, uint64_t R,

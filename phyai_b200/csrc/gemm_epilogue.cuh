@@ -9,6 +9,7 @@
 // add, so their latencies overlap).
 #pragma once
 #include "comm.cuh"
+#include "gemm.cuh"
 #include "ptx.cuh"
 
 namespace pb {
@@ -26,6 +27,9 @@ struct EpiParams {
   const float* w_scale;
   int act, glu, out_fp32;
   float rs_inv_dim = 0.f, rs_eps = 0.f;   // > 0: row_scale holds a sum of squares, scale = rsqrt(ss * inv_dim + eps)
+  const RopeEpi* rope = nullptr;          // non-null: rotate + scatter instead of storing to `out`
+  float* zero = nullptr;                  // optional fp32 scratch cleared by the first CTA (sum-of-squares
+  int zero_n = 0;                         // accumulators that a later launch adds into)
 };
 
 __device__ __forceinline__ float epi_act(float v, int act) {
@@ -241,6 +245,69 @@ __device__ __forceinline__ void epilogue_push(const PushParams& pp, int parity, 
   }
 }
 
+// Fused-QKV store pass (see RopeEpi): row scale and bias as in the generic pass, then q / k pairs
+// are rotated in fp32 and written to their two half-head positions, v columns are copied.
+template <int TN>
+__device__ __forceinline__ void epilogue_rope(const EpiParams& ep, const float* stg, uint32_t stg_addr,
+                                              int lds, int m0, int n0, int r0, int rows, int nsplit,
+                                              int warp, int lane, int nwarps) {
+  const RopeEpi rp = *ep.rope;
+  const int row_end = min(r0 + rows, ep.M - m0);
+  const int half = rp.D >> 1;
+#pragma unroll
+  for (int c = lane * 4; c < TN; c += 128) {
+    const int n = n0 + c;
+    if (n >= ep.N) continue;
+    float bias4[4] = {0.f, 0.f, 0.f, 0.f};
+    if (ep.bias) ld_bf16x4(ep.bias + n, bias4);
+    const int head = n / rp.D, within = n - head * rp.D;
+    const bool is_q = head < rp.Hq, is_k = !is_q && head < rp.Hq + rp.Hkv;
+    const int i0 = within >> 1;                       // dims i0, i0 + 1 and their partners i0 + half, i0 + 1 + half
+    for (int rr = r0 + warp; rr < row_end; rr += nwarps) {
+      float x[4] = {0.f, 0.f, 0.f, 0.f};
+      if (nsplit == 1) {
+        const float4 a = *reinterpret_cast<const float4*>(stg + rr * lds + c);
+        x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+      } else {
+        const uint32_t off = stg_addr + uint32_t(rr * lds + c) * 4u;
+        float4 part[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          if (r < nsplit) part[r] = ld_dsmem_f4(map_to_cta(off, r));
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          if (r < nsplit) { x[0] += part[r].x; x[1] += part[r].y; x[2] += part[r].z; x[3] += part[r].w; }
+      }
+      const int m = m0 + rr;
+      float rscale = 1.f;
+      if (ep.row_scale) {
+        rscale = ep.row_scale[m];
+        if (ep.rs_inv_dim > 0.f) rscale = rsqrtf(rscale * ep.rs_inv_dim + ep.rs_eps);
+      }
+#pragma unroll
+      for (int t = 0; t < 4; ++t) x[t] = x[t] * rscale + bias4[t];
+      if (!is_q && !is_k) {
+        __nv_bfloat16* dst = rp.v_pool + size_t(rp.slots[m]) * rp.pool_stride + size_t(head - rp.Hq - rp.Hkv) * rp.D + within;
+        const __nv_bfloat162 o01 = __floats2bfloat162_rn(x[0], x[1]), o23 = __floats2bfloat162_rn(x[2], x[3]);
+        uint2 raw;
+        raw.x = *reinterpret_cast<const uint32_t*>(&o01);
+        raw.y = *reinterpret_cast<const uint32_t*>(&o23);
+        *reinterpret_cast<uint2*>(dst) = raw;
+        continue;
+      }
+      const float* cs = rp.cos_sin + size_t(rp.pos[m]) * rp.D;
+      const float2 cc = *reinterpret_cast<const float2*>(cs + i0), sn = *reinterpret_cast<const float2*>(cs + half + i0);
+      // the projection is rounded to bf16 before the rotation, as the separate kernels would see it
+      const float a0 = __bfloat162float(__float2bfloat16(x[0])), b0 = __bfloat162float(__float2bfloat16(x[1]));
+      const float a1 = __bfloat162float(__float2bfloat16(x[2])), b1 = __bfloat162float(__float2bfloat16(x[3]));
+      __nv_bfloat16* dst = is_q ? rp.q_out + size_t(m) * rp.ldq + size_t(head) * rp.D
+                                : rp.k_pool + size_t(rp.slots[m]) * rp.pool_stride + size_t(head - rp.Hq) * rp.D;
+      *reinterpret_cast<__nv_bfloat162*>(dst + i0) = __floats2bfloat162_rn(a0 * cc.x - b0 * sn.x, a1 * cc.y - b1 * sn.y);
+      *reinterpret_cast<__nv_bfloat162*>(dst + half + i0) = __floats2bfloat162_rn(b0 * cc.x + a0 * sn.x, b1 * cc.y + a1 * sn.y);
+    }
+  }
+}
+
 template <int TN>
 __device__ __forceinline__ void epilogue_pass(const EpiParams& ep, const float* stg,
                                               uint32_t stg_addr, int lds, int m0, int n0, int r0,
@@ -251,6 +318,10 @@ __device__ __forceinline__ void epilogue_pass(const EpiParams& ep, const float* 
     if (aux) epilogue_pass_t<TN, A, G, true>(ep, stg, stg_addr, lds, m0, n0, r0, rows, nsplit, warp, lane, nwarps); \
     else epilogue_pass_t<TN, A, G, false>(ep, stg, stg_addr, lds, m0, n0, r0, rows, nsplit, warp, lane, nwarps);    \
   } while (0)
+  if (ep.rope) {
+    epilogue_rope<TN>(ep, stg, stg_addr, lds, m0, n0, r0, rows, nsplit, warp, lane, nwarps);
+    return;
+  }
   const bool aux = ep.bias || ep.residual || ep.col_gate || ep.row_scale || ep.sumsq || ep.a_scale ||
                    ep.w_scale || ep.out_fp32;
   if (ep.glu) {

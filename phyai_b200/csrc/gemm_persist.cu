@@ -245,7 +245,7 @@ bool gemm_persist_eligible(const GemmArgs& a) {
     if (!comm_on) return false;
   }
   if (a.push && a.push->world > 0 && (a.push->ld % 8 || a.push->slots_off % 8 || a.push->slot_stride % 8)) return false;
-  return a.M >= 512 && a.N >= 2048 && a.K >= 256 && !a.fp8 && !a.out_fp32 && !a.row_scale && !a.sumsq && !a.a_scale &&
+  return a.M >= 512 && a.N >= 2048 && a.K >= 256 && !a.fp8 && !a.out_fp32 && !a.row_scale && !a.sumsq && !a.rope && !a.zero && !a.a_scale &&
          !a.w_scale && !a.trace && a.force_bn == 0 && a.force_swap == -1 && a.force_splits == 0 &&
          (reinterpret_cast<uintptr_t>(a.bias) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.col_gate) & 15) == 0 &&
          (reinterpret_cast<uintptr_t>(a.residual) & 15) == 0 && (!a.residual || a.ldr % 8 == 0) && a.ldo % 8 == 0;

@@ -264,21 +264,106 @@ __global__ void norm_rows_kernel(NormArgs a) {
   }
 }
 
+// Register-resident variant of the above for rows of at most 256 * NVL elements: a lane issues all of
+// its 16-byte loads of the row back to back (NVL independent loads in flight per lane, the whole row
+// per warp) before the first use, keeps the row in registers across the reduction and writes the
+// result from there: one read and one write of the row, and enough bytes in flight per SM to cover
+// the DRAM latency with a single wave of warps.
+template <int MODE, int NVL>
+__global__ void __launch_bounds__(256) norm_rows_reg_kernel(NormArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  pdl_launch_dependents();
+  pdl_wait();
+  if (row >= a.rows) return;
+  const int nv = a.D >> 3;
+  const BF8* xr = reinterpret_cast<const BF8*>(a.x + size_t(row) * a.ldx);
+  BF8* rr = a.residual ? reinterpret_cast<BF8*>(a.residual + size_t(row) * a.ldr) : nullptr;
+  BF8* yr = reinterpret_cast<BF8*>(a.y + size_t(row) * a.ldy);
+  BF8 xv[NVL];
+#pragma unroll
+  for (int j = 0; j < NVL; ++j) {
+    const int v = lane + 32 * j;
+    if (v < nv) xv[j] = xr[v];
+  }
+  if (rr) {
+#pragma unroll
+    for (int j = 0; j < NVL; ++j) {
+      const int v = lane + 32 * j;
+      if (v < nv) {
+        float f[8], g[8];
+        unpack8(xv[j], f);
+        unpack8(rr[v], g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] += g[i];
+        xv[j] = pack8(f);        // the norm sees the rounded sum, as a separate add kernel would produce
+        rr[v] = xv[j];
+      }
+    }
+  }
+  float s2 = 0.f;
+#pragma unroll
+  for (int j = 0; j < NVL; ++j) {
+    if (lane + 32 * j < nv) {
+      float f[8];
+      unpack8(xv[j], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s2 += f[i] * f[i];
+    }
+  }
+  s2 = warp_sum(s2);
+  const float rstd = rsqrtf(s2 / a.D + a.eps);
+  const BF8* wv = a.weight ? reinterpret_cast<const BF8*>(a.weight) : nullptr;
+  const BF8* mv = MODE == kNormAdaRms ? reinterpret_cast<const BF8*>(a.mod + size_t(row / a.group) * 3 * a.D) : nullptr;
+#pragma unroll
+  for (int j = 0; j < NVL; ++j) {
+    const int v = lane + 32 * j;
+    if (v < nv) {
+      float f[8], o[8];
+      unpack8(xv[j], f);
+      if (MODE == kNormAdaRms) {
+        float sc[8], sh[8];
+        unpack8(mv[v], sc);
+        unpack8(mv[nv + v], sh);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = f[i] * rstd * (1.f + sc[i]) + sh[i];
+      } else if (MODE == kNormRmsNoWeight) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = f[i] * rstd;
+      } else {
+        float w[8];
+        unpack8(wv[v], w);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = f[i] * rstd * (MODE == kNormGemmaRms ? 1.f + w[i] : w[i]);
+      }
+      yr[v] = pack8(o);
+    }
+  }
+}
+
+template <int MODE>
+static cudaError_t launch_norm_rows(const NormArgs& a, cudaStream_t s) {
+  const int grid = (a.rows + 7) / 8;
+  if (a.D <= 2048) PB_LAUNCH((norm_rows_reg_kernel<MODE, 8>), grid, 256, s, a);
+  else if (a.D <= 4096) PB_LAUNCH((norm_rows_reg_kernel<MODE, 16>), grid, 256, s, a);
+  else if (a.D <= 6144) PB_LAUNCH((norm_rows_reg_kernel<MODE, 24>), grid, 256, s, a);
+  else PB_LAUNCH(norm_rows_kernel<MODE>, grid, 256, s, a);
+  return cudaGetLastError();
+}
+
 cudaError_t norm_launch(const NormArgs& a, cudaStream_t s) {
   if (a.rows <= 0) return cudaSuccess;
   if (a.D % 8 || a.ldx % 8 || a.ldy % 8 || (a.residual && a.ldr % 8)) return cudaErrorInvalidValue;
   if (a.y8 && a.y8_block && (a.D % 128)) return cudaErrorInvalidValue;
   if (a.y8 && !a.y) return cudaErrorInvalidValue;
   if (a.rows >= 1024 && a.mode != kNormLayer && !a.y8 && !a.sumsq && a.y && a.D <= 16384) {
-    const int grid = (a.rows + 7) / 8;
     switch (a.mode) {
-      case kNormRms: PB_LAUNCH(norm_rows_kernel<kNormRms>, grid, 256, s, a); break;
-      case kNormGemmaRms: PB_LAUNCH(norm_rows_kernel<kNormGemmaRms>, grid, 256, s, a); break;
-      case kNormAdaRms: PB_LAUNCH(norm_rows_kernel<kNormAdaRms>, grid, 256, s, a); break;
-      case kNormRmsNoWeight: PB_LAUNCH(norm_rows_kernel<kNormRmsNoWeight>, grid, 256, s, a); break;
+      case kNormRms: return launch_norm_rows<kNormRms>(a, s);
+      case kNormGemmaRms: return launch_norm_rows<kNormGemmaRms>(a, s);
+      case kNormAdaRms: return launch_norm_rows<kNormAdaRms>(a, s);
+      case kNormRmsNoWeight: return launch_norm_rows<kNormRmsNoWeight>(a, s);
       default: return cudaErrorInvalidValue;
     }
-    return cudaGetLastError();
   }
   int threads = ((a.D / 8) + 31) / 32 * 32;
   if (threads > 1024) threads = 1024;

@@ -61,7 +61,14 @@ class PI0Plan(PI05Plan):
                 return (w.float() * (1.0 + norm_w.float())[None, :]).to(torch.bfloat16).contiguous()
 
             stack = self.model.expert_stack
-            self.fold_qkv = [fold(l.attn.qkv.weight, l.input_layernorm.weight) for l in stack.layers]
+            t = cfg.text
+            Hq, Hkv, D = t.num_attention_heads, t.num_key_value_heads, t.head_dim
+            # QKV rows reordered for the rotating epilogue; block 0 keeps its norm kernel and the plain weight
+            self.fold_qkv = [ops.permute_rope_rows(fold(l.attn.qkv.weight, l.input_layernorm.weight) if li > 0
+                                                   else l.attn.qkv.weight, Hq, Hkv, D)
+                             for li, l in enumerate(stack.layers)]
+            self.e_rope = self._rope_descs(self.e_q, self.e_pos, self.e_slots)
+            self.s_rope = self._rope_descs(self.s_q, self.s_pos, self.s_slots)
             self.fold_gate_up = [fold(l.mlp.gate_up.weight, l.post_attention_layernorm.weight) for l in stack.layers]
             self.fold_out = fold(heads.action_out_proj.weight, stack.norm.weight)
             self.e_ss = torch.zeros(2, self.Me, dtype=torch.float32, device=self.device)
@@ -77,7 +84,7 @@ class PI0Plan(PI05Plan):
         return changed
 
     def _block(self, layer, li, h, x, qkv, q, attn, act, pos, slots, qstart, qlen, kvlen, max_q, splits,
-               ss=None) -> None:
+               ss=None, rope=None) -> None:
         t, e = self.cfg.text, self.cfg.expert
         Hq, Hkv, D = t.num_attention_heads, t.num_key_value_heads, t.head_dim
         kpool, vpool = self.pool.layer(li)
@@ -85,16 +92,15 @@ class PI0Plan(PI05Plan):
             rms = (e.hidden_size, e.rms_norm_eps)
             if li == 0:
                 ops.norm(h, "gemma_rms", weight=layer.input_layernorm.weight, eps=e.rms_norm_eps, out=x)
-                ops.gemm(x, layer.attn.qkv.weight, qkv)
+                ops.gemm(x, self.fold_qkv[li], qkv, rope=rope[li])
             else:
-                ops.gemm(h, self.fold_qkv[li], qkv, row_scale=ss[0], row_rms=rms)
-            ops.rope_kv(qkv, Hq, Hkv, D, q, pos=pos, cos_sin=self.cos_sin, k_pool=kpool, v_pool=vpool, slots=slots,
-                        zero=ss)
+                ops.gemm(h, self.fold_qkv[li], qkv, row_scale=ss[0], row_rms=rms, rope=rope[li])
             ops.attention(q.unflatten(1, (Hq, D)), kpool, vpool, attn.unflatten(1, (Hq, D)), qstart, qlen,
                           self.e_kvptr, kvlen, max_q_len=max_q, splits=splits, sm_scale=D ** -0.5)
-            ops.gemm(attn, layer.attn.o.weight, h, residual=h, sumsq=ss[1])
+            # each accumulating GEMM clears the other accumulator, which is idle at that point
+            ops.gemm(attn, layer.attn.o.weight, h, residual=h, sumsq=ss[1], zero=ss[0])
             ops.gemm(h, self.fold_gate_up[li], act, row_scale=ss[1], row_rms=rms, act="gelu_tanh", glu=True)
-            ops.gemm(act, layer.mlp.down.weight, h, residual=h, sumsq=ss[0])
+            ops.gemm(act, layer.mlp.down.weight, h, residual=h, sumsq=ss[0], zero=ss[1])
             return
         ops.norm(h, "gemma_rms", weight=layer.input_layernorm.weight, eps=e.rms_norm_eps, out=x)
         ops.gemm(x, layer.attn.qkv.weight, qkv)
@@ -114,7 +120,7 @@ class PI0Plan(PI05Plan):
         for li, layer in enumerate(stack.layers):
             self._block(layer, li, self.s_h, self.s_x, self.s_qkv, self.s_q, self.s_attn, self.s_act, self.s_pos,
                         self.s_slots, self.s_qstart, self.s_qlen, self.s_kvlen, 1, self.expert_splits,
-                        ss=self.s_ss if fold else None)
+                        ss=self.s_ss if fold else None, rope=self.s_rope if fold else None)
         # ---- Euler loop over the action tokens
         self.x_t.copy_(self.noise.view(Me, -1))
         for i in range(cfg.num_inference_steps):
@@ -123,7 +129,7 @@ class PI0Plan(PI05Plan):
             for li, layer in enumerate(stack.layers):
                 self._block(layer, li, self.e_h, self.e_x, self.e_qkv, self.e_q, self.e_attn, self.e_act, self.e_pos,
                             self.e_slots, self.e_qstart, self.e_qlen, self.e_kvlen, self.C, self.expert_splits,
-                            ss=self.e_ss if fold else None)
+                            ss=self.e_ss if fold else None, rope=self.e_rope if fold else None)
             if fold:
                 ops.gemm(self.e_h, self.fold_out, self.e_v, bias=heads.action_out_proj.bias, row_scale=self.e_ss[0],
                          row_rms=(cfg.expert.hidden_size, cfg.expert.rms_norm_eps))

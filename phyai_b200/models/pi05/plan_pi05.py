@@ -177,14 +177,25 @@ class PI05Plan:
                 b = b + bias.float()[None, :]
             return folded, b.to(dt).contiguous()
 
+        t = self.cfg.text
+        Hq, Hkv, D = t.num_attention_heads, t.num_key_value_heads, t.head_dim
         self.fold_qkv, self.fold_gate_up = [], []
         for li, layer in enumerate(stack.layers):
-            # the first block of a step keeps its norm kernel: nothing upstream accumulates its sums
-            self.fold_qkv.append(fold(layer.attn.qkv.weight, self.mod_in[li]) if li > 0 else None)
+            # q / k head rows reordered for the rotating epilogue of the QKV GEMM. The first block of a
+            # step keeps its norm kernel (nothing upstream accumulates its sums): plain weight, no bias.
+            wq = ops.permute_rope_rows(layer.attn.qkv.weight, Hq, Hkv, D)
+            self.fold_qkv.append(fold(wq, self.mod_in[li]) if li > 0 else (wq, None))
             self.fold_gate_up.append(fold(layer.mlp.gate_up.weight, self.mod_post[li]))
+        self.rope_desc = self._rope_descs(self.e_q, self.e_pos, self.e_slots)
         heads = self.model.heads
         self.fold_out = fold(heads.action_out_proj.weight, self.mod_final, heads.action_out_proj.bias)
         self.e_ss = torch.zeros(2, self.Me, dtype=torch.float32, device=self.device)
+
+    def _rope_descs(self, q_out: torch.Tensor, pos: torch.Tensor, slots: torch.Tensor) -> list[torch.Tensor]:
+        """One rotate-and-scatter destination per layer (its K/V pool) for the QKV GEMM epilogue."""
+        t = self.cfg.text
+        return [ops.rope_epilogue_desc(q_out, *self.pool.layer(li), self.cos_sin, pos, slots, t.num_attention_heads,
+                                       t.num_key_value_heads, t.head_dim) for li in range(self.cfg.num_layers)]
 
     def set_layout(self, layout: PI05Layout) -> bool:
         """Write the metadata of a request shape into the static buffers. Returns True if it changed."""
@@ -302,7 +313,8 @@ class PI05Plan:
         self.out.view(Me, -1).copy_(self.x_t)
 
     def _expert_folded(self) -> None:
-        """Six launches per block: the two AdaRMS kernels live in the epilogues around them."""
+        """Five launches per block: the two AdaRMS kernels live in the GEMM epilogues around them, rotary
+        embedding and the K/V scatter in the epilogue of the QKV GEMM."""
         cfg, e, t = self.cfg, self.cfg.expert, self.cfg.text
         heads, stack = self.model.heads, self.model.expert_stack
         Hq, Hkv, D, He, Me = t.num_attention_heads, t.num_key_value_heads, t.head_dim, e.hidden_size, self.Me
@@ -315,21 +327,22 @@ class PI05Plan:
             for li, layer in enumerate(stack.layers):
                 kpool, vpool = self.pool.layer(li)
                 m_in, m_post = self.mod_in[li][i:i + 1], self.mod_post[li][i:i + 1]
+                # the QKV epilogue rotates q / k and writes k / v into this block's pool rows
+                w, b = self.fold_qkv[li]
                 if li == 0:
                     ops.norm(h, "ada_rms", mod=m_in, group=Me, eps=e.rms_norm_eps, out=x)
-                    ops.gemm(x, layer.attn.qkv.weight, self.e_qkv)
+                    ops.gemm(x, w, self.e_qkv, rope=self.rope_desc[li])
                 else:
-                    w, b = self.fold_qkv[li]
-                    ops.gemm(h, w[i], self.e_qkv, bias=b[i], row_scale=ss_in, row_rms=rms)
-                # both accumulators are idle here: ss_in was consumed above, ss_post by the previous block
-                ops.rope_kv(self.e_qkv, Hq, Hkv, D, self.e_q, pos=self.e_pos, cos_sin=self.cos_sin, k_pool=kpool,
-                            v_pool=vpool, slots=self.e_slots, zero=self.e_ss)
+                    ops.gemm(h, w[i], self.e_qkv, bias=b[i], row_scale=ss_in, row_rms=rms, rope=self.rope_desc[li])
                 ops.attention(q3, kpool, vpool, a3, self.e_qstart, self.e_qlen, self.e_kvptr, self.e_kvlen,
                               max_q_len=self.C, splits=self.expert_splits, sm_scale=D ** -0.5)
-                ops.gemm(self.e_attn, layer.attn.o.weight, h, residual=h, col_gate=m_in[0, 2 * He:], sumsq=ss_post)
+                # each accumulating GEMM clears the other accumulator, which is idle at that point
+                ops.gemm(self.e_attn, layer.attn.o.weight, h, residual=h, col_gate=m_in[0, 2 * He:], sumsq=ss_post,
+                         zero=ss_in)
                 w, b = self.fold_gate_up[li]
                 ops.gemm(h, w[i], self.e_act, bias=b[i], row_scale=ss_post, row_rms=rms, act="gelu_tanh", glu=True)
-                ops.gemm(self.e_act, layer.mlp.down.weight, h, residual=h, col_gate=m_post[0, 2 * He:], sumsq=ss_in)
+                ops.gemm(self.e_act, layer.mlp.down.weight, h, residual=h, col_gate=m_post[0, 2 * He:], sumsq=ss_in,
+                         zero=ss_post)
             w, b = self.fold_out
             ops.gemm(h, w[i], self.e_v, bias=b[i], row_scale=ss_in, row_rms=rms)
             ops.axpy(self.x_t, self.e_v, self.dt)

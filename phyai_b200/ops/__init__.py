@@ -69,6 +69,12 @@ def set_pdl(on: bool) -> None:
     ext().set_pdl(bool(on))
 
 
+def set_gemm_2cta(mode: int | bool | None) -> None:
+    """Route large plain bf16 GEMMs to the CTA-pair kernel (``tcgen05.mma.cta_group::2``, 256 x 256
+    tiles on two SMs): ``True`` / ``False``, or ``None`` to follow ``PHYAI_GEMM_2CTA``."""
+    ext().set_gemm_2cta(-1 if mode is None else int(bool(mode)))
+
+
 def pdl_enabled() -> bool:
     return ext().pdl_enabled()
 
@@ -81,7 +87,8 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *
          a_scale: Optional[torch.Tensor] = None, w_scale: Optional[torch.Tensor] = None,
          force_bn: int = 0, force_swap: int = -1, force_splits: int = 0,
          trace: Optional[torch.Tensor] = None, wait: Optional[tuple[int, int, int]] = None,
-         row_rms: Optional[tuple[int, float]] = None) -> torch.Tensor:
+         row_rms: Optional[tuple[int, float]] = None, rope: Optional[torch.Tensor] = None,
+         zero: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out = epilogue(x @ w.T)`` on tcgen05 tensor cores (see ``csrc/gemm.cuh``).
 
     ``wait=(signal_array_ptr, channel, arrivals)``: ``x`` lives in symmetric memory and is being
@@ -91,6 +98,11 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *
     ``row_rms=(dim, eps)``: ``row_scale`` holds the sum of squares of each row of the un-normed
     activation (what another GEMM's ``sumsq`` accumulated) and the epilogue multiplies by
     ``rsqrt(row_scale / dim + eps)``: an RMSNorm whose weight was folded into ``w``.
+
+    ``rope``: a descriptor from :func:`rope_epilogue_desc`; ``w`` is a fused QKV weight whose q / k head
+    rows were permuted with :func:`permute_rope_rows`, and instead of storing ``out`` (untouched) the
+    epilogue rotates q and k and writes q to its buffer and k / v to their KV-pool rows.
+    ``zero``: an fp32 scratch tensor this launch clears (never one it reads or accumulates into).
 
     ``x`` is ``(M, K)``, ``w`` is ``(N, K)`` (the ``nn.Linear`` layout), both bf16 or
     both float8_e4m3fn (then ``a_scale`` (M,) and ``w_scale`` (N,) dequantise). With
@@ -102,8 +114,25 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *
         out = torch.empty((M, N // 2 if glu else N), dtype=out_dtype, device=x.device)
     ext().gemm(x, w, out, bias, residual, res_mod, col_gate, row_scale, sumsq, ACT[act], glu,
                a_scale, w_scale, force_bn, force_swap, force_splits, trace,
-               *((0, -1, 0) if wait is None else wait), *((0, 0.0) if row_rms is None else row_rms))
+               *((0, -1, 0) if wait is None else wait), *((0, 0.0) if row_rms is None else row_rms), rope, zero)
     return out
+
+
+def rope_epilogue_desc(q_out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, cos_sin: torch.Tensor,
+                       pos: torch.Tensor, slots: torch.Tensor, Hq: int, Hkv: int, D: int) -> torch.Tensor:
+    """Device descriptor for ``gemm(..., rope=...)``: where rotated q, k and v of a fused QKV projection go.
+
+    Keep the descriptor and the tensors it names alive while launches (or captured graphs) use it."""
+    return ext().rope_epilogue_desc(q_out, k_pool, v_pool, cos_sin, pos, slots, Hq, Hkv, D)
+
+
+def permute_rope_rows(w: torch.Tensor, Hq: int, Hkv: int, D: int) -> torch.Tensor:
+    """Reorder the output rows (dim 0) of a fused QKV weight or bias for the rotating epilogue: inside every
+    q and k head, row ``2i`` is dimension ``i`` and row ``2i + 1`` is dimension ``i + D/2``; v rows stay."""
+    half = D // 2
+    idx = torch.arange(D).view(2, half).t().reshape(-1)              # 0, half, 1, half + 1, ...
+    rows = torch.cat([h * D + idx for h in range(Hq + Hkv)] + [torch.arange((Hq + Hkv) * D, (Hq + 2 * Hkv) * D)])
+    return w.index_select(0, rows.to(w.device)).contiguous()
 
 
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[torch.Tensor],

@@ -116,6 +116,37 @@ def test_gemm_folded_rms_norm(M, glu):
     assert relerr(out, y) < 2e-2, relerr(out, y)
 
 
+@pytest.mark.parametrize("M,N,K,act,glu,res", [(7040, 5120, 5120, "none", False, True), (1300, 4096, 1024, "silu", True, False),
+                                               (2048, 2560, 320, "gelu_tanh", False, False)])
+def test_gemm_cta_pair(M, N, K, act, glu, res):
+    """The cta_group::2 kernel (256 x 256 tiles on CTA pairs) against the fp32 reference and the default kernel."""
+    from phyai_b200 import ops
+
+    g = torch.Generator(device="cpu").manual_seed(N)
+    x = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16().to(DEV)
+    bias = torch.randn(N, generator=g).bfloat16().to(DEV)
+    r = torch.randn(M, N // 2 if glu else N, generator=g).bfloat16().to(DEV) if res else None
+    base = ops.gemm(x, w, bias=bias, residual=r, act=act, glu=glu)
+    ops.set_gemm_2cta(True)
+    try:
+        out = ops.gemm(x, w, bias=bias, residual=r, act=act, glu=glu)
+        torch.cuda.synchronize()
+    finally:
+        ops.set_gemm_2cta(None)
+    _status_ok()
+    y = x.float() @ w.float().T + bias.float()
+    if glu:
+        f = torch.nn.functional.silu if act == "silu" else (lambda t: torch.nn.functional.gelu(t, approximate="tanh"))
+        y = f(y[:, 0::2]) * y[:, 1::2]
+    elif act == "gelu_tanh":
+        y = torch.nn.functional.gelu(y, approximate="tanh")
+    if res:
+        y = y + r.float()
+    assert relerr(out, y) < 2e-2, relerr(out, y)
+    assert relerr(out, base) < 1e-2
+
+
 def test_gemm_rejects_misaligned():
     from phyai_b200 import ops
 
@@ -250,6 +281,46 @@ def test_norm_fp8_outputs():
         assert relerr(sc, s) < 1e-5 and relerr(y8.float(), q.float()) < 0.08
 
 
+@pytest.mark.parametrize("M,K", [(50, 1024), (1, 1024), (968, 2048)])
+def test_gemm_rope_epilogue(M, K):
+    """QKV projection whose epilogue rotates q / k and scatters k / v == GEMM followed by the rope kernel."""
+    from phyai_b200 import ops
+    from phyai_b200.ops import ref
+
+    Hq, Hkv, D = 8, 1, 256
+    N = (Hq + 2 * Hkv) * D
+    g = torch.Generator(device="cpu").manual_seed(M + K)
+    x = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16().to(DEV)
+    bias = (torch.randn(N, generator=g) * 0.5).bfloat16().to(DEV)
+    pos = (torch.arange(M, dtype=torch.int32) + 3).to(DEV)
+    table = ref.rope_cos_sin(torch.arange(0, M + 8, device=DEV), D)
+    slots = (torch.randperm(M + 20, generator=g)[:M]).long().to(DEV)
+    ss = (torch.rand(M, generator=g) * K * 2 + 1).to(DEV)
+    eps = 1e-6
+
+    def pools():
+        return torch.zeros(M + 20, Hkv, D, device=DEV, dtype=torch.bfloat16), torch.zeros(M + 20, Hkv, D, device=DEV, dtype=torch.bfloat16)
+
+    # two launches: projection (row-RMS factor and bias in its epilogue), then rotate + scatter
+    kp0, vp0 = pools()
+    q0 = torch.zeros(M, Hq * D, device=DEV, dtype=torch.bfloat16)
+    qkv = ops.gemm(x, w, bias=bias, row_scale=ss, row_rms=(K, eps))
+    ops.rope_kv(qkv, Hq, Hkv, D, q0, pos=pos, cos_sin=table, k_pool=kp0, v_pool=vp0, slots=slots)
+    # one launch
+    kp1, vp1 = pools()
+    q1 = torch.zeros_like(q0)
+    scratch = torch.full((2, M), 3.0, device=DEV)
+    desc = ops.rope_epilogue_desc(q1, kp1, vp1, table, pos, slots, Hq, Hkv, D)
+    dummy = torch.zeros(M, N, device=DEV, dtype=torch.bfloat16)
+    ops.gemm(x, ops.permute_rope_rows(w, Hq, Hkv, D), dummy, bias=ops.permute_rope_rows(bias, Hq, Hkv, D),
+             row_scale=ss, row_rms=(K, eps), rope=desc, zero=scratch)
+    _status_ok()
+    assert float(scratch.abs().max()) == 0.0 and float(dummy.abs().max()) == 0.0
+    assert relerr(q1, q0) < 1e-2, relerr(q1, q0)
+    assert relerr(kp1, kp0) < 1e-2 and torch.equal(vp1, vp0)
+
+
 def test_rope_kv_and_small_ops():
     from phyai_b200 import ops
     from phyai_b200.ops import ref
@@ -325,7 +396,7 @@ def test_gemm_fp8_block_scaled(M, N, K, bias):
     assert relerr(y, full) < 0.08          # quantisation error itself
 
 
-@pytest.mark.parametrize("rows,D", [(1024, 1024), (7040, 5120), (3001, 2048)])
+@pytest.mark.parametrize("rows,D", [(1024, 1024), (7040, 5120), (3001, 2048), (2050, 4096), (1500, 8192)])
 def test_norms_many_rows(rows, D):
     """Row counts that take the warp-per-row kernel."""
     from phyai_b200 import ops
