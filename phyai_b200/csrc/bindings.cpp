@@ -354,6 +354,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("reset_launch_counter", [] { pb::reset_launch_counter(); });
   m.def("set_pdl", [](bool on) { pb::set_pdl_enabled(on); });
   m.def("set_gemm_2cta", [](int64_t mode) { pb::set_gemm_2cta(int(mode)); });
+  m.def("gemm_2cta_launches", []() { return int64_t(pb::gemm_2cta_launches()); });
   m.def("pdl_enabled", [] { return pb::pdl_enabled(); });
   register_comm(m);
 }

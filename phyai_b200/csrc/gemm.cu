@@ -475,7 +475,12 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream, int* n_ctas) {
       (reinterpret_cast<uintptr_t>(a.w_scale) & 15))
     return cudaErrorInvalidValue;
   if (a.block_scaled) return cudaErrorInvalidValue;  // handled by gemm_fp8_block_launch
-  if (gemm_2cta_eligible(a)) return gemm_2cta_launch(a, stream);
+  if (gemm_2cta_eligible(a)) {
+    const cudaError_t e = gemm_2cta_launch(a, stream);
+    if (e != cudaErrorInvalidClusterSize) return e;
+    cudaGetLastError();   // pairs cannot be scheduled in this context (e.g. an SM partition): use one CTA per tile set
+    set_gemm_2cta(0);
+  }
   if (gemm_persist_eligible(a)) {
     if (a.push && (a.push->world < 0 || a.push->world > kMaxRanks ||
                    (a.push->world > 0 && (a.glu || a.act || a.bias || a.residual || a.col_gate)) ||

@@ -97,6 +97,7 @@ cudaError_t gemm_persist_launch(const GemmArgs& a, cudaStream_t stream, int* n_c
 bool gemm_2cta_eligible(const GemmArgs& a);
 cudaError_t gemm_2cta_launch(const GemmArgs& a, cudaStream_t stream);
 void set_gemm_2cta(int mode);   // 1 on, 0 off, -1 follow the PHYAI_GEMM_2CTA variable
+unsigned long long gemm_2cta_launches();
 
 // 3-D bf16 tensor map (d, head, row) for the attention kernels (see gemm.cu).
 bool make_tmap_3d_bf16(CUtensorMap* out, const void* ptr, uint64_t D, uint64_t H, uint64_t R,

@@ -95,6 +95,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = int(cluster_ctarank());          // 0: the CTA that issues the MMAs
   const int n_tiles = p_tiles * q_tiles;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;   // clusters are (2, 1, 1): a pair is two neighbours in x
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kCStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -112,11 +113,14 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   const uint32_t tmem = tmem_base_s;
   pdl_launch_dependents();
   pdl_wait();
+  if (ep.zero && blockIdx.x == 0) {
+    for (int i = threadIdx.x; i < ep.zero_n; i += kCThreads) ep.zero[i] = 0.f;   // predecessors are complete, successors wait
+  }
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer (both CTAs)
     int it = 0;
-    for (int t = blockIdx.x; t < n_tiles && !err_s; t += gridDim.x) {
+    for (int t = pair; t < n_tiles && !err_s; t += n_pairs) {
       int p, q;
       grouped_tile_coords(t, p_tiles, q_tiles, p, q);
       for (int kb = 0; kb < total_kb; ++kb, ++it) {
@@ -137,7 +141,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     if (rank == 0) {
       const uint32_t idesc = make_idesc_f16(kCM, kCN, 1);
       int it = 0, ti = 0;
-      for (int t = blockIdx.x; t < n_tiles && !err_s; t += gridDim.x, ++ti) {
+      for (int t = pair; t < n_tiles && !err_s; t += n_pairs, ++ti) {
         const int buf = ti & 1;
         if (ti >= 2 && !mbar_wait(&tempty[buf], uint32_t(((ti >> 1) & 1) ^ 1))) { err_s = kStatusTimeoutAcc; break; }
         tc_fence_after();
@@ -165,7 +169,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     const int quad = warp & 3, row_in_tile = quad * 32 + lane;
     const uint32_t lane_base = tmem + (uint32_t(quad * 32) << 16);
     int ti = 0;
-    for (int t = blockIdx.x; t < n_tiles && !err_s; t += gridDim.x, ++ti) {
+    for (int t = pair; t < n_tiles && !err_s; t += n_pairs, ++ti) {
       int p, q;
       grouped_tile_coords(t, p_tiles, q_tiles, p, q);
       const int buf = ti & 1;
@@ -190,6 +194,8 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   if (warp == 1) tmem_dealloc_pair(tmem, 512);
 }
 
+static unsigned long long g_2cta_launches = 0;
+
 template <int ACT, bool GLU>
 static cudaError_t launch_2cta(const CUtensorMap& tx, const CUtensorMap& tw, const EpiParams& ep, int p_tiles, int q_tiles,
                                int total_kb, int clusters, cudaStream_t st) {
@@ -201,8 +207,29 @@ static cudaError_t launch_2cta(const CUtensorMap& tx, const CUtensorMap& tw, con
     if (e != cudaSuccess) return e;
     attr_done = true;
   }
-  return launch_kernel(kern, dim3(clusters, 1, 2), dim3(kCThreads), smem, st, 2, tx, tw, ep, p_tiles, q_tiles, total_kb,
-                       kernel_status_ptr());
+  // the CTA pair of cta_group::2 is a cluster of two along x
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * clusters);
+  cfg.blockDim = dim3(kCThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attrs[2];
+  int na = 0;
+  attrs[na].id = cudaLaunchAttributeClusterDimension;
+  attrs[na].val.clusterDim.x = 2;
+  attrs[na].val.clusterDim.y = 1;
+  attrs[na].val.clusterDim.z = 1;
+  ++na;
+  if (pdl_enabled()) {
+    attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = na;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tx, tw, ep, p_tiles, q_tiles, total_kb, kernel_status_ptr());
+  if (e == cudaSuccess) { bump_launch_counter(1); ++g_2cta_launches; }
+  return e;
 }
 
 static int sm_count() {
@@ -214,6 +241,7 @@ static int sm_count() {
 
 static int g_2cta_mode = -1;   // -1: PHYAI_GEMM_2CTA decides, 0 / 1: set by the program
 void set_gemm_2cta(int mode) { g_2cta_mode = mode; }
+unsigned long long gemm_2cta_launches() { return g_2cta_launches; }
 
 bool gemm_2cta_eligible(const GemmArgs& a) {
   // PHYAI_GEMM_2CTA=1 (or set_gemm_2cta(1)) routes large plain bf16 problems to the CTA-pair kernel
@@ -221,7 +249,7 @@ bool gemm_2cta_eligible(const GemmArgs& a) {
   const bool on = g_2cta_mode < 0 ? env_on : g_2cta_mode > 0;
   if (!on || a.push) return false;
   if (((a.M + kCM - 1) / kCM) * ((a.N + kCN - 1) / kCN) < sm_count() / 2) return false;
-  return a.M >= 512 && a.N >= 2048 && a.K >= 256 && !a.fp8 && !a.out_fp32 && !a.row_scale && !a.sumsq && !a.rope && !a.zero &&
+  return a.M >= 512 && a.N >= 2048 && a.K >= 256 && !a.fp8 && !a.out_fp32 && !a.rope &&
          !a.a_scale && !a.w_scale && !a.trace && a.force_bn == 0 && a.force_swap == -1 && a.force_splits == 0 &&
          (reinterpret_cast<uintptr_t>(a.bias) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.col_gate) & 15) == 0 &&
          (reinterpret_cast<uintptr_t>(a.residual) & 15) == 0 && (!a.residual || a.ldr % 8 == 0) && a.ldo % 8 == 0;
@@ -235,6 +263,8 @@ cudaError_t gemm_2cta_launch(const GemmArgs& a, cudaStream_t stream) {
   memset(&ep, 0, sizeof(ep));
   ep.out = a.out; ep.ldo = a.ldo; ep.M = a.M; ep.N = a.N; ep.bias = a.bias; ep.residual = a.residual; ep.ldr = a.ldr;
   ep.res_mod = a.res_mod; ep.col_gate = a.col_gate; ep.act = a.act; ep.glu = a.glu;
+  ep.row_scale = a.row_scale; ep.sumsq = a.sumsq; ep.zero = a.zero; ep.zero_n = a.zero_n;
+  ep.rs_inv_dim = a.row_rms_dim > 0 ? 1.f / float(a.row_rms_dim) : 0.f; ep.rs_eps = a.row_rms_eps;
   const int p_tiles = (a.M + kCM - 1) / kCM, q_tiles = (a.N + kCN - 1) / kCN, total_kb = (a.K + kCBK - 1) / kCBK;
   const int pairs = sm_count() / 2;
   const int clusters = p_tiles * q_tiles < pairs ? p_tiles * q_tiles : pairs;

@@ -15,8 +15,8 @@
 // Tiles are taken in the grouped order (8 column tiles per group) so the tiles in flight across
 // the chip form a compact block of the output and both operands are re-read from L2.
 // Same operands, epilogue semantics and result as gemm_kernel; the launcher in gemm.cu routes a
-// call here when the shape qualifies and nothing exotic (fp8, fp32 output, row scales, sum of
-// squares, peer pushes) is requested. Every wait is bounded.
+// call here when the shape qualifies and nothing exotic (fp8, fp32 output, the rotating QKV epilogue)
+// is requested. Every wait is bounded.
 #include <cstdlib>
 #include <cstring>
 #include <type_traits>
@@ -71,6 +71,9 @@ gemm_persist_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
   const uint32_t tmem = tmem_base_s;
   pdl_launch_dependents();
   pdl_wait();
+  if (ep.zero && blockIdx.x == 0) {
+    for (int i = threadIdx.x; i < ep.zero_n; i += kPThreads) ep.zero[i] = 0.f;   // predecessors are complete, successors wait
+  }
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -143,6 +146,11 @@ gemm_persist_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
       const bool live = m < ep.M;
       const __nv_bfloat16* res_row = (ep.residual && live) ? ep.residual + size_t(ep.res_mod > 0 ? (m % ep.res_mod) : m) * ep.ldr : nullptr;
       __nv_bfloat16* out_row = reinterpret_cast<__nv_bfloat16*>(ep.out) + size_t(live ? m : 0) * ep.ldo;
+      float rscale = 1.f, ss = 0.f;
+      if (ep.row_scale && live) {
+        rscale = ep.row_scale[m];
+        if (ep.rs_inv_dim > 0.f) rscale = rsqrtf(rscale * ep.rs_inv_dim + ep.rs_eps);
+      }
 #pragma unroll 1
       for (int c = 0; c < kPN; c += 32) {
         uint32_t r[32];
@@ -172,9 +180,10 @@ gemm_persist_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
             }
             continue;
           }
-          row_epilogue_8<ACT, GLU>(ep, x, n, res_row, out_row);
+          ss += row_epilogue_8<ACT, GLU>(ep, x, n, res_row, out_row, rscale);
         }
       }
+      if (ep.sumsq && live) atomicAdd(ep.sumsq + m, ss);   // one add per row and tile
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[buf]);
@@ -245,7 +254,7 @@ bool gemm_persist_eligible(const GemmArgs& a) {
     if (!comm_on) return false;
   }
   if (a.push && a.push->world > 0 && (a.push->ld % 8 || a.push->slots_off % 8 || a.push->slot_stride % 8)) return false;
-  return a.M >= 512 && a.N >= 2048 && a.K >= 256 && !a.fp8 && !a.out_fp32 && !a.row_scale && !a.sumsq && !a.rope && !a.zero && !a.a_scale &&
+  return a.M >= 512 && a.N >= 2048 && a.K >= 256 && !a.fp8 && !a.out_fp32 && !a.rope && !a.a_scale && !(a.push && (a.row_scale || a.sumsq)) &&
          !a.w_scale && !a.trace && a.force_bn == 0 && a.force_swap == -1 && a.force_splits == 0 &&
          (reinterpret_cast<uintptr_t>(a.bias) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.col_gate) & 15) == 0 &&
          (reinterpret_cast<uintptr_t>(a.residual) & 15) == 0 && (!a.residual || a.ldr % 8 == 0) && a.ldo % 8 == 0;
@@ -258,6 +267,8 @@ cudaError_t gemm_persist_launch(const GemmArgs& a, cudaStream_t stream, int* n_c
   memset(&ep, 0, sizeof(ep));
   ep.out = a.out; ep.ldo = a.ldo; ep.M = a.M; ep.N = a.N; ep.bias = a.bias; ep.residual = a.residual; ep.ldr = a.ldr;
   ep.res_mod = a.res_mod; ep.col_gate = a.col_gate; ep.act = a.act; ep.glu = a.glu;
+  ep.row_scale = a.row_scale; ep.sumsq = a.sumsq; ep.zero = a.zero; ep.zero_n = a.zero_n;
+  ep.rs_inv_dim = a.row_rms_dim > 0 ? 1.f / float(a.row_rms_dim) : 0.f; ep.rs_eps = a.row_rms_eps;
   const int p_tiles = (a.M + kPM - 1) / kPM, q_tiles = (a.N + kPN - 1) / kPN, total_kb = (a.K + kPBK - 1) / kPBK;
   int sms = 148;
   {

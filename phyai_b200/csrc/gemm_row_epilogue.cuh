@@ -29,9 +29,13 @@ __device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float (&f)[8]) {
 }
 
 // Eight consecutive accumulator columns [n, n + 8) of row m (x holds them); n < ep.N, n % 8 == 0.
+// `rscale` multiplies the accumulator before the bias; the return value is the sum of squares of the
+// stored (rounded) values.
 template <int ACT, bool GLU>
-__device__ __forceinline__ void row_epilogue_8(const EpiParams& ep, float (&x)[8], int n, const __nv_bfloat16* res_row,
-                                               __nv_bfloat16* out_row) {
+__device__ __forceinline__ float row_epilogue_8(const EpiParams& ep, float (&x)[8], int n, const __nv_bfloat16* res_row,
+                                                __nv_bfloat16* out_row, float rscale = 1.f) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) x[j] *= rscale;
   if (ep.bias) {
     float b[8];
     unpack_bf16x8(*reinterpret_cast<const uint4*>(ep.bias + n), b);
@@ -60,6 +64,8 @@ __device__ __forceinline__ void row_epilogue_8(const EpiParams& ep, float (&x)[8
     o.x = *reinterpret_cast<const uint32_t*>(&o0);
     o.y = *reinterpret_cast<const uint32_t*>(&o1);
     *reinterpret_cast<uint2*>(out_row + no) = o;
+    const float q0 = __bfloat162float(o0.x), q1 = __bfloat162float(o0.y), q2 = __bfloat162float(o1.x), q3 = __bfloat162float(o1.y);
+    return q0 * q0 + q1 * q1 + q2 * q2 + q3 * q3;
   } else {
     if constexpr (ACT != 0) {
 #pragma unroll
@@ -82,6 +88,13 @@ __device__ __forceinline__ void row_epilogue_8(const EpiParams& ep, float (&x)[8
 #pragma unroll
     for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]);
     *reinterpret_cast<uint4*>(out_row + n) = o;
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float q0 = __bfloat162float(o2[j].x), q1 = __bfloat162float(o2[j].y);
+      ss += q0 * q0 + q1 * q1;
+    }
+    return ss;
   }
 }
 
@@ -93,6 +106,11 @@ __device__ __forceinline__ void row_epilogue_tile(const EpiParams& ep, uint32_t 
   const bool live = m < ep.M;
   const __nv_bfloat16* res_row = (ep.residual && live) ? ep.residual + size_t(ep.res_mod > 0 ? (m % ep.res_mod) : m) * ep.ldr : nullptr;
   __nv_bfloat16* out_row = reinterpret_cast<__nv_bfloat16*>(ep.out) + size_t(live ? m : 0) * ep.ldo;
+  float rscale = 1.f, ss = 0.f;
+  if (ep.row_scale && live) {
+    rscale = ep.row_scale[m];
+    if (ep.rs_inv_dim > 0.f) rscale = rsqrtf(rscale * ep.rs_inv_dim + ep.rs_eps);
+  }
 #pragma unroll 1
   for (int c = 0; c < width; c += 32) {
     uint32_t r[32];
@@ -106,9 +124,10 @@ __device__ __forceinline__ void row_epilogue_tile(const EpiParams& ep, uint32_t 
       float x[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(r[8 * g + j]);
-      row_epilogue_8<ACT, GLU>(ep, x, n, res_row, out_row);
+      ss += row_epilogue_8<ACT, GLU>(ep, x, n, res_row, out_row, rscale);
     }
   }
+  if (ep.sumsq && live) atomicAdd(ep.sumsq + m, ss);   // one add per row and tile
 }
 
 }  // namespace pb

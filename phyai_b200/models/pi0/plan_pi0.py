@@ -54,6 +54,7 @@ class PI0Plan(PI05Plan):
         bias = te @ wt.t() + heads.action_time_mlp_in.bias.float() + wa @ heads.action_in_proj.bias.float()
         self.time_bias = bias.to(torch.bfloat16).contiguous()
         if self.fold_norms:
+            self._fold_prefix()
             # Gemma RMSNorm weights (1 + w) folded into the weights that consume the normed rows; the
             # per-row 1/rms is applied in that GEMM's epilogue from sums of squares accumulated by the
             # epilogue of the GEMM that wrote the rows (the first block of a pass keeps its norm kernel).

@@ -157,6 +157,22 @@ class PI05Plan:
         self.mod_final = stack.norm.project_modulation(conds)
         if self.fold_norms:
             self._fold_modulation(stack)
+            self._fold_prefix()
+
+    def _fold_prefix(self) -> None:
+        """Prefix decoder: Gemma RMSNorm weights (1 + w) folded into the QKV and gate/up weights (one
+        static copy each), QKV rows reordered for the rotating epilogue; block 0 keeps its norm kernel."""
+        t, lm = self.cfg.text, self.model.paligemma_lm
+        Hq, Hkv, D = t.num_attention_heads, t.num_key_value_heads, t.head_dim
+
+        def fold(w, norm_w):
+            return (w.float() * (1.0 + norm_w.float())[None, :]).to(torch.bfloat16).contiguous()
+
+        self.pfold_qkv = [ops.permute_rope_rows(fold(l.attn.qkv.weight, l.input_layernorm.weight) if li > 0
+                                                else l.attn.qkv.weight, Hq, Hkv, D) for li, l in enumerate(lm.layers)]
+        self.pfold_gate_up = [fold(l.mlp.gate_up.weight, l.post_attention_layernorm.weight) for l in lm.layers[:-1]]
+        self.p_rope = self._rope_descs(self.p_q, self.p_pos, self.p_slots)
+        self.p_ss = torch.zeros(2, self.B * self.P, dtype=torch.float32, device=self.device)
 
     def _fold_modulation(self, stack) -> None:
         """Per Euler step, fold each AdaRMS (1 + scale) into the weight that consumes the normed rows
@@ -268,6 +284,25 @@ class PI05Plan:
         qkv, q, attn, act = self.p_qkv[:Mp], self.p_q[:Mp], self.p_attn[:Mp], self.p_act[:Mp]
         q3, a3 = q.unflatten(1, (Hq, D)), attn.unflatten(1, (Hq, D))
         last = len(lm.layers) - 1
+        if self.fold_norms:
+            # five launches per block: norms, rotary embedding and the K/V scatter live in GEMM epilogues
+            ss_in, ss_post = self.p_ss[0], self.p_ss[1]
+            rms = (t.hidden_size, t.rms_norm_eps)
+            for li, layer in enumerate(lm.layers):
+                kpool, vpool = self.pool.layer(li)
+                if li == 0:
+                    ops.norm(h, "gemma_rms", weight=layer.input_layernorm.weight, eps=t.rms_norm_eps, out=x)
+                    ops.gemm(x, self.pfold_qkv[li], qkv, rope=self.p_rope[li])
+                else:
+                    ops.gemm(h, self.pfold_qkv[li], qkv, row_scale=ss_in, row_rms=rms, rope=self.p_rope[li])
+                if li == last:
+                    break  # only this block's K/V are consumed downstream
+                ops.attention(q3, kpool, vpool, a3, self.p_qstart, self.p_qlen, self.p_kvptr, self.p_kvlen,
+                              max_q_len=n_per, splits=self.prefix_splits, sm_scale=D ** -0.5)
+                ops.gemm(attn, layer.attn.o.weight, h, residual=h, sumsq=ss_post, zero=ss_in)
+                ops.gemm(h, self.pfold_gate_up[li], act, row_scale=ss_post, row_rms=rms, act="gelu_tanh", glu=True)
+                ops.gemm(act, layer.mlp.down.weight, h, residual=h, sumsq=ss_in, zero=ss_post)
+            return
         for li, layer in enumerate(lm.layers):
             kpool, vpool = self.pool.layer(li)
             ops.norm(h, "gemma_rms", weight=layer.input_layernorm.weight, eps=t.rms_norm_eps, out=x)

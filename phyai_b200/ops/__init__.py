@@ -75,6 +75,11 @@ def set_gemm_2cta(mode: int | bool | None) -> None:
     ext().set_gemm_2cta(-1 if mode is None else int(bool(mode)))
 
 
+def gemm_2cta_launches() -> int:
+    """How many GEMM calls the CTA-pair kernel has served in this process."""
+    return int(ext().gemm_2cta_launches())
+
+
 def pdl_enabled() -> bool:
     return ext().pdl_enabled()
 

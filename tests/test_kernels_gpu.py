@@ -128,6 +128,7 @@ def test_gemm_cta_pair(M, N, K, act, glu, res):
     bias = torch.randn(N, generator=g).bfloat16().to(DEV)
     r = torch.randn(M, N // 2 if glu else N, generator=g).bfloat16().to(DEV) if res else None
     base = ops.gemm(x, w, bias=bias, residual=r, act=act, glu=glu)
+    n0 = ops.gemm_2cta_launches()
     ops.set_gemm_2cta(True)
     try:
         out = ops.gemm(x, w, bias=bias, residual=r, act=act, glu=glu)
@@ -135,6 +136,7 @@ def test_gemm_cta_pair(M, N, K, act, glu, res):
     finally:
         ops.set_gemm_2cta(None)
     _status_ok()
+    assert ops.gemm_2cta_launches() == n0 + 1
     y = x.float() @ w.float().T + bias.float()
     if glu:
         f = torch.nn.functional.silu if act == "silu" else (lambda t: torch.nn.functional.gelu(t, approximate="tanh"))
@@ -145,6 +147,36 @@ def test_gemm_cta_pair(M, N, K, act, glu, res):
         y = y + r.float()
     assert relerr(out, y) < 2e-2, relerr(out, y)
     assert relerr(out, base) < 1e-2
+
+
+@pytest.mark.parametrize("pair", [False, True])
+def test_gemm_persistent_rms_and_sumsq(pair):
+    """Row-RMS factor, sum of squares and scratch clearing in the persistent kernels (one CTA per SM / CTA pairs)."""
+    from phyai_b200 import ops
+
+    M, K, N, eps = 1300, 1024, 4096, 1e-6
+    g = torch.Generator(device="cpu").manual_seed(5)
+    x = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16().to(DEV)
+    bias = torch.randn(N, generator=g).bfloat16().to(DEV)
+    r = torch.randn(M, N, generator=g).bfloat16().to(DEV)
+    ss_in = x.float().pow(2).sum(-1)
+    ss_out = torch.zeros(M, device=DEV)
+    scratch = torch.full((M,), 2.0, device=DEV)
+    n0 = ops.gemm_2cta_launches()
+    ops.set_gemm_2cta(pair)
+    try:
+        out = ops.gemm(x, w, bias=bias, residual=r, row_scale=ss_in, row_rms=(K, eps), sumsq=ss_out, zero=scratch)
+        torch.cuda.synchronize()
+    finally:
+        ops.set_gemm_2cta(None)
+    _status_ok()
+    assert ops.gemm_2cta_launches() == n0 + int(pair)
+    xf = x.float()
+    y = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)) @ w.float().T + bias.float() + r.float()
+    assert relerr(out, y) < 2e-2, relerr(out, y)
+    assert relerr(ss_out, out.float().pow(2).sum(-1)) < 1e-4
+    assert float(scratch.abs().max()) == 0.0
 
 
 def test_gemm_rejects_misaligned():

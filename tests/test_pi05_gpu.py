@@ -20,6 +20,18 @@ def _mid_config():
         chunk_size=50, max_action_dim=32, num_inference_steps=4, tokenizer_max_length=48)
 
 
+def _perturb_norms(eng, g):
+    """Random init leaves the RMSNorm weights at identity: perturb them so that folding them into the
+    neighbouring GEMM weights is visible, then rebuild the plan's prepared weights."""
+    model = eng.entry.model
+    with torch.no_grad():
+        for mod in (model.paligemma_lm, model.expert_stack):
+            for name, p in mod.named_parameters():
+                if p.dim() == 1 and "norm" in name and "dense" not in name:
+                    p.copy_((torch.randn(p.shape, generator=g) * 0.2).to(p))
+    eng.entry.scheduler.plan.build_modulation_tables()
+
+
 @pytest.mark.parametrize("batch,graph", [(1, True), (2, True), (2, False)])
 def test_plan_matches_eager(batch, graph):
     from phyai_b200 import ops
@@ -33,6 +45,7 @@ def test_plan_matches_eager(batch, graph):
                             EngineConfig(device=DeviceConfig("cuda:0", torch.bfloat16),
                                          runtime=RuntimeConfig(use_cuda_graph=graph))))
     g = torch.Generator().manual_seed(batch)
+    _perturb_norms(eng, g)
     lens = torch.tensor([40, 7][:batch])
     req = PI05Request((torch.rand(batch, 2, 3, 56, 56, generator=g) * 2 - 1).bfloat16().cuda(),
                       torch.randint(0, 1024, (batch, 48), generator=g).cuda(), lens.cuda(),
@@ -72,13 +85,7 @@ def test_pi0_plan_matches_eager(batch):
     eng = Engine(EngineArgs("pi0", PI0Args(config=cfg, max_batch_size=2, inputs_image_shape=[[56, 56, 3]] * 2),
                             EngineConfig(device=DeviceConfig("cuda:0", torch.bfloat16), runtime=RuntimeConfig(use_cuda_graph=True))))
     g = torch.Generator().manual_seed(10 + batch)
-    # random init leaves the RMSNorm weights at identity: perturb them so that folding them into the
-    # neighbouring GEMM weights is visible, then rebuild the plan's prepared weights
-    with torch.no_grad():
-        for name, p in eng.entry.model.expert_stack.named_parameters():
-            if p.dim() == 1 and "norm" in name:
-                p.copy_((torch.randn(p.shape, generator=g) * 0.2).to(p))
-    eng.entry.scheduler.plan.build_modulation_tables()
+    _perturb_norms(eng, g)
     lens = torch.tensor([33, 9][:batch])
     req = PI0Request((torch.rand(batch, 2, 3, 56, 56, generator=g) * 2 - 1).bfloat16().cuda(),
                      torch.randint(0, 1024, (batch, 48), generator=g).cuda(), lens.cuda(),
