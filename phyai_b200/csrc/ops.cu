@@ -12,6 +12,8 @@
 
 #include <cuda_fp8.h>
 
+#include <cstdlib>
+
 #include "gemm.cuh"
 #include "launch.cuh"
 #include "ptx.cuh"
@@ -341,8 +343,147 @@ __global__ void __launch_bounds__(256) norm_rows_reg_kernel(NormArgs a) {
   }
 }
 
+// Streaming variant for tens of thousands of rows: persistent CTAs, a dedicated warp moves groups of
+// eight rows global -> shared memory with bulk asynchronous copies (one instruction per group when the
+// rows are contiguous) into a ring of stages, so the copy engine keeps the DRAM queue full with no
+// per-thread load instructions outstanding. Eight consumer warps take one row each: the row goes from
+// shared memory into registers, the stage is handed back at once, and the warp reduces, scales and
+// stores from registers. No residual input (that variant stays on norm_rows_reg_kernel).
+constexpr int kNormTmaRows = 8;
+template <int MODE, int NVL>
+__global__ void __launch_bounds__(288) norm_rows_tma_kernel(NormArgs a, int stages, int* status) {
+  extern __shared__ uint8_t nsm_raw[];
+  uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(nsm_raw) + 127) & ~uintptr_t(127));
+  __shared__ __align__(8) uint64_t full_bar[4], empty_bar[4];
+  __shared__ volatile int err_s;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row_bytes = a.D * 2, stage_bytes = kNormTmaRows * row_bytes;
+  const int n_groups = (a.rows + kNormTmaRows - 1) / kNormTmaRows;
+  const bool contiguous = a.ldx == a.D;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], kNormTmaRows); }
+    err_s = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  pdl_launch_dependents();
+  pdl_wait();
+  if (warp == kNormTmaRows) {
+    // ------------------------------------------------------------------ copy warp
+    if (lane == 0) {
+      int it = 0;
+      for (int g = blockIdx.x; g < n_groups && !err_s; g += gridDim.x, ++it) {
+        const int s = it % stages;
+        if (it >= stages && !mbar_wait(&empty_bar[s], uint32_t((it / stages) & 1) ^ 1)) { err_s = kStatusTimeoutEmpty; break; }
+        const int r0 = g * kNormTmaRows, nr = min(kNormTmaRows, a.rows - r0);
+        mbar_expect_tx(&full_bar[s], uint32_t(nr * row_bytes));
+        uint8_t* dst = sm + size_t(s) * stage_bytes;
+        if (contiguous) {
+          bulk_load(dst, a.x + size_t(r0) * a.ldx, uint32_t(nr * row_bytes), &full_bar[s]);
+        } else {
+          for (int r = 0; r < nr; ++r) bulk_load(dst + r * row_bytes, a.x + size_t(r0 + r) * a.ldx, uint32_t(row_bytes), &full_bar[s]);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ one row per warp and group
+    const int nv = a.D >> 3;
+    const BF8* wv = a.weight ? reinterpret_cast<const BF8*>(a.weight) : nullptr;
+    int it = 0;
+    for (int g = blockIdx.x; g < n_groups && !err_s; g += gridDim.x, ++it) {
+      const int s = it % stages;
+      if (!mbar_wait(&full_bar[s], uint32_t((it / stages) & 1))) { err_s = kStatusTimeoutFull; break; }
+      const int row = g * kNormTmaRows + warp;
+      const bool live = row < a.rows;
+      BF8 xv[NVL];
+      if (live) {
+        const BF8* xs = reinterpret_cast<const BF8*>(sm + size_t(s) * stage_bytes + size_t(warp) * row_bytes);
+#pragma unroll
+        for (int j = 0; j < NVL; ++j) {
+          const int v = lane + 32 * j;
+          if (v < nv) xv[j] = xs[v];
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[s]);     // the row is in registers: the stage can be refilled
+      if (!live) continue;
+      float s2 = 0.f;
+#pragma unroll
+      for (int j = 0; j < NVL; ++j) {
+        if (lane + 32 * j < nv) {
+          float f[8];
+          unpack8(xv[j], f);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) s2 += f[i] * f[i];
+        }
+      }
+      s2 = warp_sum(s2);
+      const float rstd = rsqrtf(s2 / a.D + a.eps);
+      const BF8* mv = MODE == kNormAdaRms ? reinterpret_cast<const BF8*>(a.mod + size_t(row / a.group) * 3 * a.D) : nullptr;
+      BF8* yr = reinterpret_cast<BF8*>(a.y + size_t(row) * a.ldy);
+#pragma unroll
+      for (int j = 0; j < NVL; ++j) {
+        const int v = lane + 32 * j;
+        if (v < nv) {
+          float f[8], o[8];
+          unpack8(xv[j], f);
+          if (MODE == kNormAdaRms) {
+            float sc[8], sh[8];
+            unpack8(mv[v], sc);
+            unpack8(mv[nv + v], sh);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = f[i] * rstd * (1.f + sc[i]) + sh[i];
+          } else if (MODE == kNormRmsNoWeight) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = f[i] * rstd;
+          } else {
+            float w[8];
+            unpack8(wv[v], w);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = f[i] * rstd * (MODE == kNormGemmaRms ? 1.f + w[i] : w[i]);
+          }
+          yr[v] = pack8(o);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (err_s && threadIdx.x == 0) {
+    if (status) atomicCAS(status, 0, int(err_s));
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);   // let copies in flight land
+  }
+}
+
+template <int MODE, int NVL>
+static cudaError_t launch_norm_tma(const NormArgs& a, cudaStream_t s) {
+  const int stage_bytes = kNormTmaRows * a.D * 2;
+  int stages = (200 * 1024) / stage_bytes;
+  if (stages > 4) stages = 4;
+  const size_t smem = size_t(stages) * stage_bytes + 128;
+  auto kern = norm_rows_tma_kernel<MODE, NVL>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 201 * 1024);
+    if (e != cudaSuccess) return e;
+    attr_done = true;
+  }
+  int sms = 148, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int n_groups = (a.rows + kNormTmaRows - 1) / kNormTmaRows;
+  const int grid = n_groups < sms ? n_groups : sms;
+  return launch_kernel(kern, dim3(grid), dim3(288), smem, s, 1, a, stages, kernel_status_ptr());
+}
+
 template <int MODE>
 static cudaError_t launch_norm_rows(const NormArgs& a, cudaStream_t s) {
+  static const bool tma_off = [] { const char* e = getenv("PHYAI_NORM_TMA"); return e && e[0] == '0'; }();
+  if (!tma_off && !a.residual && a.rows >= 4096 && a.D >= 1024 && a.D <= 6144 && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0) {
+    if (a.D <= 2048) return launch_norm_tma<MODE, 8>(a, s);
+    if (a.D <= 4096) return launch_norm_tma<MODE, 16>(a, s);
+    return launch_norm_tma<MODE, 24>(a, s);
+  }
   const int grid = (a.rows + 7) / 8;
   if (a.D <= 2048) PB_LAUNCH((norm_rows_reg_kernel<MODE, 8>), grid, 256, s, a);
   else if (a.D <= 4096) PB_LAUNCH((norm_rows_reg_kernel<MODE, 16>), grid, 256, s, a);

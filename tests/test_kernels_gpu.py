@@ -428,7 +428,8 @@ def test_gemm_fp8_block_scaled(M, N, K, bias):
     assert relerr(y, full) < 0.08          # quantisation error itself
 
 
-@pytest.mark.parametrize("rows,D", [(1024, 1024), (7040, 5120), (3001, 2048), (2050, 4096), (1500, 8192)])
+@pytest.mark.parametrize("rows,D", [(1024, 1024), (7040, 5120), (3001, 2048), (2050, 4096), (1500, 8192), (4099, 2048),
+                                    (4100, 4096), (9001, 1024)])
 def test_norms_many_rows(rows, D):
     """Row counts that take the warp-per-row kernel."""
     from phyai_b200 import ops
@@ -440,6 +441,8 @@ def test_norms_many_rows(rows, D):
     assert relerr(ops.norm(x, "gemma_rms", weight=w), ref.rms_norm(x, w, gemma=True)) < TOL
     modr = (torch.randn(rows // 7 + 1, 3 * D, device=DEV) * 0.2).bfloat16()
     assert relerr(ops.norm(x, "ada_rms", mod=modr, group=7), ref.ada_rms_norm(x, modr.repeat_interleave(7, 0)[:rows])[0]) < TOL
+    wide = torch.randn(rows, D + 64, device=DEV).bfloat16()          # rows that are not back to back in memory
+    assert relerr(ops.norm(wide[:, :D], "rms", weight=w), ref.rms_norm(wide[:, :D], w)) < TOL
     r = torch.randn(rows, D, device=DEV).bfloat16()
     r2 = r.clone()
     y = ops.norm(x, "rms", weight=w, residual=r2)
