@@ -21,15 +21,9 @@ import torch
 sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
 
 
-def main() -> None:
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--batch", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--lang-len", type=int, default=48)
-    ap.add_argument("--model", default="base", choices=["base", "tiny"])
-    a = ap.parse_args()
-
+def measure_stages(batch: int = 1, steps: int = 20, warmup: int = 3, lang_len: int = 48, model: str = "base") -> dict:
+    """Median milliseconds of each stage (and of the whole request) for one batch size; see the module docstring."""
+    a = argparse.Namespace(batch=batch, steps=steps, warmup=warmup, lang_len=lang_len, model=model)
     from phyai_b200.engine import Engine, EngineArgs
     from phyai_b200.engine_config import DeviceConfig, EngineConfig, RuntimeConfig
     from phyai_b200.models.pi05.configuration_pi05 import PI05Config, tiny_pi05_config
@@ -72,10 +66,20 @@ def main() -> None:
             torch.cuda.synchronize()
             ts.append(e0.elapsed_time(e1))
         out[name] = round(statistics.median(ts), 4)
-    print(json.dumps({"bench": "pi05_stages", "batch": B, "lang_bucket": bucket, "model": a.model,
-                      "median_ms": out, "steps": a.steps, "warmup": a.warmup, "l2": "flushed before every replay",
-                      "dtype": "bf16", "data": "synthetic"}))
     eng.close()
+    return {"bench": "pi05_stages", "batch": B, "lang_bucket": bucket, "model": a.model, "median_ms": out, "steps": a.steps,
+            "warmup": a.warmup, "l2": "flushed before every replay", "dtype": "bf16", "data": "synthetic"}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--lang-len", type=int, default=48)
+    ap.add_argument("--model", default="base", choices=["base", "tiny"])
+    a = ap.parse_args()
+    print(json.dumps(measure_stages(a.batch, a.steps, a.warmup, a.lang_len, a.model)))
 
 
 if __name__ == "__main__":

@@ -144,5 +144,8 @@ def build_all(verbose: bool = False) -> list[Path]:
 
 
 if __name__ == "__main__":
-    for p in build_all("-v" in sys.argv):
-        print("built", p)
+    if "--radix-only" in sys.argv:      # host-only C++ (no nvcc): what a CPU-only checkout can build
+        print("built", build_radix("-v" in sys.argv))
+    else:
+        for p in build_all("-v" in sys.argv):
+            print("built", p)
