@@ -97,6 +97,21 @@ def main() -> None:
             gbs = 2 * R * D * 2 / t_o / 1e6
             rows.append(dict(kernel="rms_norm", shape=name, ours_ms=round(t_o, 4), eager_ms=round(t_e, 4), gbs=round(gbs, 1),
                              frac_of_measured_hbm=round(gbs / peaks["hbm_gbs"], 3)))
+        # AdaRMS (scale | shift | gate rows shared by a group of tokens) at the action-expert and Cosmos-sized shapes,
+        # against the eager fp32 formula (counterpart of phyai-kernel/benchmark/bench_adarmsnorm.py)
+        for name, (R, D, G) in {"ada_rms.50x1024": (50, 1024, 50), "ada_rms.800x1024": (800, 1024, 50), "ada_rms.8192x4096": (8192, 4096, 1024)}.items():
+            if a.only and name != a.only:
+                continue
+            from phyai_b200.ops import ref
+
+            x = torch.randn(R, D, device=dev, dtype=bf)
+            mod = (torch.randn(R // G, 3 * D, device=dev, dtype=bf) * 0.1).contiguous()
+            y = torch.empty_like(x)
+            t_o = bench(lambda: ops.norm(x, "ada_rms", mod=mod, group=G, out=y))
+            t_e = float("nan") if a.no_baselines else bench(lambda: ref.ada_rms_norm(x, mod.repeat_interleave(G, 0)))
+            gbs = 2 * R * D * 2 / t_o / 1e6
+            rows.append(dict(kernel="ada_rms_norm", shape=name, ours_ms=round(t_o, 4), eager_ms=round(t_e, 4), gbs=round(gbs, 1),
+                             frac_of_measured_hbm=round(gbs / peaks["hbm_gbs"], 3)))
     for r in rows:
         print(json.dumps(r), flush=True)
 
