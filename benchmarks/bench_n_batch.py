@@ -57,12 +57,46 @@ def summarize(model: str, bs: int, lat: list[float]) -> BenchResult:
 
 
 class NBatchBenchRunner:
-    def __init__(self, model: str, *, device: str = "cuda:0", lang_len: int = 1, use_cuda_graph: bool = True) -> None:
+    def __init__(self, model: str, *, device: str = "cuda:0", lang_len: int = 1, use_cuda_graph: bool = True,
+                 impl: str = "ours") -> None:
         self.model, self.device, self.lang_len, self.use_cuda_graph = model, device, lang_len, use_cuda_graph
+        self.impl = impl
+
+    def build_reference(self, bs: int):
+        """The unmodified reference package (installed under ``baseline/_ref``) through its own Engine and plugins,
+        bf16 everywhere (its Pi0 plugin defaults the vision tower to fp32; both arms are timed in bf16)."""
+        import torch
+
+        sys.path.insert(0, str(Path(__file__).resolve().parents[1] / "baseline" / "_ref"))
+        from phyai.engine import Engine, EngineArgs
+        from phyai.engine_config import DeviceConfig, EngineConfig, RuntimeConfig
+
+        cfg = EngineConfig(device=DeviceConfig(target=self.device, params_dtype=torch.bfloat16),
+                           runtime=RuntimeConfig(use_cuda_graph=self.use_cuda_graph))
+        px = (torch.rand(bs, 3, 3, 224, 224, device=self.device) * 2 - 1).to(torch.bfloat16)
+        noise = torch.randn(bs, 50, 32, device=self.device, dtype=torch.bfloat16)
+        if self.model == "pi05":
+            from phyai.models.pi05.main_pi05 import PI05Args
+            from phyai.models.pi05.scheduler_ws1_pi05 import PI05Request
+
+            eng = Engine(EngineArgs("pi05", PI05Args(checkpoint_dir=None, max_batch_size=bs, inputs_image_shape=[[224, 224, 3]] * 3), cfg))
+            ids = torch.zeros(bs, 200, dtype=torch.long, device=self.device)
+            ids[:, 0] = 2
+            return eng, PI05Request(pixel_values=px, input_ids=ids, lang_lens=torch.full((bs,), self.lang_len, device=self.device), noise=noise)
+        from phyai.models.pi0.main_pi0 import PI0Args
+        from phyai.models.pi0.scheduler_ws1_pi0 import PI0Request
+
+        eng = Engine(EngineArgs("pi0", PI0Args(checkpoint_dir=None, max_batch_size=bs, vision_params_dtype=torch.bfloat16), cfg))
+        ids = torch.zeros(bs, 48, dtype=torch.long, device=self.device)
+        ids[:, 0] = 2
+        return eng, PI0Request(pixel_values=px, input_ids=ids, lang_lens=torch.full((bs,), min(self.lang_len, 48), device=self.device),
+                               state=torch.randn(bs, 32, device=self.device, dtype=torch.bfloat16), noise=noise)
 
     def build(self, bs: int):
         import torch
 
+        if self.impl == "reference":
+            return self.build_reference(bs)
         from phyai_b200.engine import Engine, EngineArgs
         from phyai_b200.engine_config import DeviceConfig, EngineConfig, RuntimeConfig
 
@@ -106,7 +140,7 @@ class NBatchBenchRunner:
             e1.synchronize()
             lat.append(e0.elapsed_time(e1))
         eng.close()
-        return summarize(self.model, bs, lat)
+        return summarize(self.model if self.impl == "ours" else f"{self.model} (reference)", bs, lat)
 
 
 def main() -> None:
@@ -118,8 +152,9 @@ def main() -> None:
     ap.add_argument("--lang-len", type=int, default=1)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--jsonl", type=str, default=None)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     a = ap.parse_args()
-    runner = NBatchBenchRunner(a.model, lang_len=a.lang_len, use_cuda_graph=not a.no_graph)
+    runner = NBatchBenchRunner(a.model, lang_len=a.lang_len, use_cuda_graph=not a.no_graph, impl=a.impl)
     for bs in a.batch_sizes:
         t0 = time.time()
         r = runner.run(bs, a.n_warmup, a.n_timed)
