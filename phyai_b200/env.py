@@ -109,6 +109,12 @@ class envs:
     PHYAI_USE_PYNCCL = EnvField("PHYAI_USE_PYNCCL", False, parse_bool)   # register the ctypes NCCL backend ahead of torch's
     PHYAI_PEER_COMM = EnvField("PHYAI_PEER_COMM", True, parse_bool)    # fused peer-memory collectives (0: NCCL only)
     PHYAI_PEER_HEAP_MB = EnvField("PHYAI_PEER_HEAP_MB", 0, int)          # symmetric heap size override
+    # kernel routing (read by the native library itself on first use: listed here so they show up with the rest)
+    PHYAI_GEMM_PERSIST = EnvField("PHYAI_GEMM_PERSIST", True, parse_bool)        # 0: one tile per CTA for large GEMMs too
+    PHYAI_GEMM_PERSIST_COMM = EnvField("PHYAI_GEMM_PERSIST_COMM", True, parse_bool)  # 0: peer modes stay off the persistent kernel
+    PHYAI_GEMM_2CTA = EnvField("PHYAI_GEMM_2CTA", False, parse_bool)            # 1: CTA-pair (cta_group::2) kernel for large plain GEMMs
+    PHYAI_NORM_TMA = EnvField("PHYAI_NORM_TMA", False, parse_bool)              # 1: many-row norms through bulk copies into shared memory
+    PHYAI_PI05_OVERLAP = EnvField("PHYAI_PI05_OVERLAP", False, parse_bool)      # 1: first Euler step on a second stream under the prefix
     # debug / tensor dump
     PHYAI_DEBUG_TENSOR_DUMP_DIR = EnvField("PHYAI_DEBUG_TENSOR_DUMP_DIR", None, str)
     PHYAI_DEBUG_TENSOR_DUMP_FILTER = EnvField("PHYAI_DEBUG_TENSOR_DUMP_FILTER", None, parse_regex_list)

@@ -29,6 +29,7 @@ import torch
 
 from ... import ops
 from ...cache import KVCachePool
+from ...env import envs
 from .modeling_pi05 import PI05Model
 
 
@@ -50,6 +51,9 @@ class PI05Plan:
     suffix_extra = 0
     #: fold the expert's AdaRMS norms into the neighbouring GEMMs (one weight copy per Euler step)
     fold_norms = True
+    #: run the first Euler step on a second stream under the prefix decoder (PHYAI_PI05_OVERLAP=1)
+    overlap_first_step = bool(envs.PHYAI_PI05_OVERLAP.get())
+    _side_stream = None
 
     def __init__(self, model: PI05Model, *, max_batch_size: int = 1, num_images: int = 3,
                  device: torch.device | str = "cuda") -> None:
@@ -269,7 +273,7 @@ class PI05Plan:
         ops.norm(self.v_h, "layer", weight=m.post_layernorm.weight, bias=m.post_layernorm.bias,
                  eps=v.layer_norm_eps, out=self.v_x)
 
-    def prefix(self, lang_bucket: int) -> None:
+    def prefix(self, lang_bucket: int, kv_events=None) -> None:
         cfg, t, lm = self.cfg, self.cfg.text, self.model.paligemma_lm
         n_per = self.img_tokens + lang_bucket
         Mp = self.B * n_per
@@ -295,6 +299,8 @@ class PI05Plan:
                     ops.gemm(x, self.pfold_qkv[li], qkv, rope=self.p_rope[li])
                 else:
                     ops.gemm(h, self.pfold_qkv[li], qkv, row_scale=ss_in, row_rms=rms, rope=self.p_rope[li])
+                if kv_events is not None:
+                    kv_events[li].record(torch.cuda.current_stream())     # this block's prefix K / V are in the pool
                 if li == last:
                     break  # only this block's K/V are consumed downstream
                 ops.attention(q3, kpool, vpool, a3, self.p_qstart, self.p_qlen, self.p_kvptr, self.p_kvlen,
@@ -347,9 +353,11 @@ class PI05Plan:
             ops.axpy(self.x_t, self.e_v, self.dt)
         self.out.view(Me, -1).copy_(self.x_t)
 
-    def _expert_folded(self) -> None:
+    def _expert_folded(self, steps=None, before_attn=None, finish: bool = True) -> None:
         """Five launches per block: the two AdaRMS kernels live in the GEMM epilogues around them, rotary
-        embedding and the K/V scatter in the epilogue of the QKV GEMM."""
+        embedding and the K/V scatter in the epilogue of the QKV GEMM. ``steps``: which Euler steps to issue
+        (default all); ``before_attn(li)`` runs before block ``li``'s attention is issued (the overlapped
+        schedule waits there for the prefix K/V of that block); ``finish`` copies the result out."""
         cfg, e, t = self.cfg, self.cfg.expert, self.cfg.text
         heads, stack = self.model.heads, self.model.expert_stack
         Hq, Hkv, D, He, Me = t.num_attention_heads, t.num_key_value_heads, t.head_dim, e.hidden_size, self.Me
@@ -357,7 +365,7 @@ class PI05Plan:
         q3, a3 = self.e_q.unflatten(1, (Hq, D)), self.e_attn.unflatten(1, (Hq, D))
         ss_in, ss_post = self.e_ss[0], self.e_ss[1]
         rms = (He, e.rms_norm_eps)
-        for i in range(cfg.num_inference_steps):
+        for i in (range(cfg.num_inference_steps) if steps is None else steps):
             ops.gemm(self.x_t, heads.action_in_proj.weight, h, bias=heads.action_in_proj.bias)
             for li, layer in enumerate(stack.layers):
                 kpool, vpool = self.pool.layer(li)
@@ -369,6 +377,8 @@ class PI05Plan:
                     ops.gemm(x, w, self.e_qkv, rope=self.rope_desc[li])
                 else:
                     ops.gemm(h, w[i], self.e_qkv, bias=b[i], row_scale=ss_in, row_rms=rms, rope=self.rope_desc[li])
+                if before_attn is not None:
+                    before_attn(li)
                 ops.attention(q3, kpool, vpool, a3, self.e_qstart, self.e_qlen, self.e_kvptr, self.e_kvlen,
                               max_q_len=self.C, splits=self.expert_splits, sm_scale=D ** -0.5)
                 # each accumulating GEMM clears the other accumulator, which is idle at that point
@@ -381,13 +391,41 @@ class PI05Plan:
             w, b = self.fold_out
             ops.gemm(h, w[i], self.e_v, bias=b[i], row_scale=ss_in, row_rms=rms)
             ops.axpy(self.x_t, self.e_v, self.dt)
-        self.out.view(Me, -1).copy_(self.x_t)
+        if finish:
+            self.out.view(Me, -1).copy_(self.x_t)
 
     def run(self, lang_bucket: int) -> torch.Tensor:
         """The whole request; inputs are ``pixels``, ``input_ids``, ``noise``; result in ``out``."""
+        if self.overlap_first_step and self.fold_norms and type(self).expert is PI05Plan.expert and self.device.type == "cuda":
+            return self._run_overlapped(lang_bucket)
         self.vision()
         self.prefix(lang_bucket)
         self.expert()
+        return self.out
+
+    def _run_overlapped(self, lang_bucket: int) -> torch.Tensor:
+        """Same request with the first Euler step on a second stream. Block ``li`` of the expert only needs
+        the prefix K/V of block ``li``, so the first step (launch-bound, a few CTAs per kernel) runs under the
+        compute-bound prefix decoder: it waits, block by block, on an event recorded after the prefix QKV
+        GEMM that wrote that block's K/V. The streams join before the second step. Works eagerly and inside
+        a stream capture (the event edges become graph dependencies)."""
+        main = torch.cuda.current_stream()
+        if self._side_stream is None:
+            self._side_stream = torch.cuda.Stream(device=self.device)
+        side = self._side_stream
+        n_layers = self.cfg.num_layers
+        fork, join = torch.cuda.Event(), torch.cuda.Event()
+        kv_ready = [torch.cuda.Event() for _ in range(n_layers)]
+        fork.record(main)
+        self.vision()
+        self.prefix(lang_bucket, kv_events=kv_ready)
+        with torch.cuda.stream(side):
+            side.wait_event(fork)
+            self.x_t.copy_(self.noise.view(self.Me, -1))
+            self._expert_folded(steps=[0], before_attn=lambda li: side.wait_event(kv_ready[li]), finish=False)
+            join.record(side)
+        main.wait_event(join)
+        self._expert_folded(steps=range(1, self.cfg.num_inference_steps))
         return self.out
 
 

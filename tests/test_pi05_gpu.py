@@ -32,8 +32,11 @@ def _perturb_norms(eng, g):
     eng.entry.scheduler.plan.build_modulation_tables()
 
 
-@pytest.mark.parametrize("batch,graph", [(1, True), (2, True), (2, False)])
-def test_plan_matches_eager(batch, graph):
+@pytest.mark.parametrize("batch,graph,overlap", [(1, True, False), (2, True, False), (2, False, False), (1, True, True), (2, False, True)])
+def test_plan_matches_eager(batch, graph, overlap, monkeypatch):
+    from phyai_b200.models.pi05.plan_pi05 import PI05Plan
+
+    monkeypatch.setattr(PI05Plan, "overlap_first_step", overlap)   # first Euler step on a second stream under the prefix
     from phyai_b200 import ops
     from phyai_b200.engine import Engine, EngineArgs
     from phyai_b200.engine_config import DeviceConfig, EngineConfig, RuntimeConfig
