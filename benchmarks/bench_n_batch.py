@@ -65,8 +65,12 @@ class NBatchBenchRunner:
     def build_reference(self, bs: int):
         """The unmodified reference package (installed under ``baseline/_ref``) through its own Engine and plugins,
         bf16 everywhere (its Pi0 plugin defaults the vision tower to fp32; both arms are timed in bf16)."""
+        import os
+
         import torch
 
+        # the reference's own knob: its default 128 MiB FlashInfer workspace overflows from batch 8 (Pi0.5) / batch 1 (Pi0)
+        os.environ.setdefault("PHYAI_FLASHINFER_WORKSPACE_BYTES", str(1 << 30))
         sys.path.insert(0, str(Path(__file__).resolve().parents[1] / "baseline" / "_ref"))
         from phyai.engine import Engine, EngineArgs
         from phyai.engine_config import DeviceConfig, EngineConfig, RuntimeConfig

@@ -24,6 +24,8 @@
 // Capability parity: the reference runs its diffusion attention through FlashInfer
 // (phyai/src/phyai/layers/attention/backends/flashinfer_diffusion.py) and the prefix
 // attention through FlashInfer prefill (.../flashinfer_ar.py).
+#include <cstdlib>
+
 #include "attention.cuh"
 #include "gemm.cuh"
 #include "launch.cuh"
@@ -57,7 +59,8 @@ __device__ __forceinline__ float exp2_fma(float x) {
 
 }  // namespace
 
-template <int DB>  // head dim padded to 64 * DB, DB in {1, 2}
+// DB: head dim padded to 64 * DB, DB in {1, 2}. NP: how many of every four probabilities take exp2_fma (0..2).
+template <int DB, int NP>
 __global__ void __launch_bounds__(kPPThreads, 1)
 attn_pp_kernel(AttnParams p, int* status, const __grid_constant__ CUtensorMap tmQ,
                const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV) {
@@ -249,9 +252,10 @@ attn_pp_kernel(AttnParams p, int* status, const __grid_constant__ CUtensorMap tm
 #pragma unroll
         for (int c = 0; c < kT; c += 4) {
           const float p0 = exp2f(__uint_as_float(sv[c]) * scale_log2 - m_use);
-          const float p1 = exp2f(__uint_as_float(sv[c + 1]) * scale_log2 - m_use);
+          const float x1 = __uint_as_float(sv[c + 1]) * scale_log2 - m_use, x3 = __uint_as_float(sv[c + 3]) * scale_log2 - m_use;
+          const float p1 = NP >= 2 ? exp2_fma(x1) : exp2f(x1);
           const float p2 = exp2f(__uint_as_float(sv[c + 2]) * scale_log2 - m_use);
-          const float p3 = exp2_fma(__uint_as_float(sv[c + 3]) * scale_log2 - m_use);
+          const float p3 = NP >= 1 ? exp2_fma(x3) : exp2f(x3);
           sum += (p0 + p1) + (p2 + p3);
           const __nv_bfloat162 h0 = __floats2bfloat162_rn(p0, p1), h1 = __floats2bfloat162_rn(p2, p3);
           pk[c >> 1] = *reinterpret_cast<const uint32_t*>(&h0);
@@ -336,9 +340,9 @@ attn_pp_kernel(AttnParams p, int* status, const __grid_constant__ CUtensorMap tm
   if (warp == 8) tmem_dealloc(tmem, 512);
 }
 
-template <int DB>
+template <int DB, int NP>
 static cudaError_t attn_pp_launch_db(const AttnParams& p, cudaStream_t stream) {
-  auto kern = attn_pp_kernel<DB>;
+  auto kern = attn_pp_kernel<DB, NP>;
   const size_t smem = size_t(6 * DB) * kBlk + 1024;
   static bool attr_done = false;
   if (!attr_done) {
@@ -365,7 +369,10 @@ bool attn_pp_supported(const AttnParams& p) {
 
 cudaError_t attn_pp_launch(const AttnParams& p, cudaStream_t stream) {
   if (!attn_pp_supported(p) || p.batch <= 0 || p.max_q_len <= 0 || p.group <= 0) return cudaErrorInvalidValue;
-  return p.head_dim <= 64 ? attn_pp_launch_db<1>(p, stream) : attn_pp_launch_db<2>(p, stream);
+  // PHYAI_ATTN_POLY = 0 / 1 / 2: how many of every four exponentials go to the FMA pipe (default 1)
+  static const int np = [] { const char* e = getenv("PHYAI_ATTN_POLY"); return e && e[0] >= '0' && e[0] <= '2' ? e[0] - '0' : 1; }();
+  if (p.head_dim <= 64) return np == 0 ? attn_pp_launch_db<1, 0>(p, stream) : np == 2 ? attn_pp_launch_db<1, 2>(p, stream) : attn_pp_launch_db<1, 1>(p, stream);
+  return np == 0 ? attn_pp_launch_db<2, 0>(p, stream) : np == 2 ? attn_pp_launch_db<2, 2>(p, stream) : attn_pp_launch_db<2, 1>(p, stream);
 }
 
 }  // namespace pb

@@ -51,7 +51,7 @@ class PI05Plan:
     suffix_extra = 0
     #: fold the expert's AdaRMS norms into the neighbouring GEMMs (one weight copy per Euler step)
     fold_norms = True
-    #: run the first Euler step on a second stream under the prefix decoder (PHYAI_PI05_OVERLAP=1)
+    #: run the first Euler step on a second stream under the prefix decoder (PHYAI_PI05_OVERLAP=0 turns it off)
     overlap_first_step = bool(envs.PHYAI_PI05_OVERLAP.get())
     _side_stream = None
 
@@ -353,11 +353,13 @@ class PI05Plan:
             ops.axpy(self.x_t, self.e_v, self.dt)
         self.out.view(Me, -1).copy_(self.x_t)
 
-    def _expert_folded(self, steps=None, before_attn=None, finish: bool = True) -> None:
+    def _expert_folded(self, steps=None, before_block=None, finish: bool = True) -> None:
         """Five launches per block: the two AdaRMS kernels live in the GEMM epilogues around them, rotary
         embedding and the K/V scatter in the epilogue of the QKV GEMM. ``steps``: which Euler steps to issue
-        (default all); ``before_attn(li)`` runs before block ``li``'s attention is issued (the overlapped
-        schedule waits there for the prefix K/V of that block); ``finish`` copies the result out."""
+        (default all); ``before_block(li)`` runs before block ``li`` is issued (the overlapped schedule waits
+        there for the prefix K/V of that block: the wait has to precede this block's own K/V scatter, because
+        the padded prompt rows of the prefix land in the pool slots the action tokens use); ``finish`` copies
+        the result out."""
         cfg, e, t = self.cfg, self.cfg.expert, self.cfg.text
         heads, stack = self.model.heads, self.model.expert_stack
         Hq, Hkv, D, He, Me = t.num_attention_heads, t.num_key_value_heads, t.head_dim, e.hidden_size, self.Me
@@ -370,6 +372,8 @@ class PI05Plan:
             for li, layer in enumerate(stack.layers):
                 kpool, vpool = self.pool.layer(li)
                 m_in, m_post = self.mod_in[li][i:i + 1], self.mod_post[li][i:i + 1]
+                if before_block is not None:
+                    before_block(li)
                 # the QKV epilogue rotates q / k and writes k / v into this block's pool rows
                 w, b = self.fold_qkv[li]
                 if li == 0:
@@ -377,8 +381,6 @@ class PI05Plan:
                     ops.gemm(x, w, self.e_qkv, rope=self.rope_desc[li])
                 else:
                     ops.gemm(h, w[i], self.e_qkv, bias=b[i], row_scale=ss_in, row_rms=rms, rope=self.rope_desc[li])
-                if before_attn is not None:
-                    before_attn(li)
                 ops.attention(q3, kpool, vpool, a3, self.e_qstart, self.e_qlen, self.e_kvptr, self.e_kvlen,
                               max_q_len=self.C, splits=self.expert_splits, sm_scale=D ** -0.5)
                 # each accumulating GEMM clears the other accumulator, which is idle at that point
@@ -422,7 +424,7 @@ class PI05Plan:
         with torch.cuda.stream(side):
             side.wait_event(fork)
             self.x_t.copy_(self.noise.view(self.Me, -1))
-            self._expert_folded(steps=[0], before_attn=lambda li: side.wait_event(kv_ready[li]), finish=False)
+            self._expert_folded(steps=[0], before_block=lambda li: side.wait_event(kv_ready[li]), finish=False)
             join.record(side)
         main.wait_event(join)
         self._expert_folded(steps=range(1, self.cfg.num_inference_steps))
