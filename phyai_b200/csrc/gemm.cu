@@ -86,7 +86,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
   constexpr int P_BYTES = kTileP * kRowBytes;        // 16 KB
   constexpr int Q_BYTES = BN * kRowBytes;
   constexpr int STAGE_BYTES = P_BYTES + Q_BYTES;
-  constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+  constexpr int TMEM_COLS = BN < 32 ? 32 : (BN == 192 ? 256 : BN);   // allocations are powers of two
   constexpr int TM = SWAP ? BN : kTileP;             // tile rows in output orientation
   constexpr int TN = SWAP ? kTileP : BN;             // tile cols in output orientation
   constexpr int LDS = TN + 4;                        // staging row stride (floats)
@@ -444,6 +444,9 @@ static cudaError_t launch_bn(int bn, const CUtensorMap& tmP, const CUtensorMap& 
     case 32: return launch_inst<32, SWAP, FP8>(tmP, tmQ, ep, push, grid, total_kb, kbps, stages, smem, st, tr);
     case 64: return launch_inst<64, SWAP, FP8>(tmP, tmQ, ep, push, grid, total_kb, kbps, stages, smem, st, tr);
     case 128: return launch_inst<128, SWAP, FP8>(tmP, tmQ, ep, push, grid, total_kb, kbps, stages, smem, st, tr);
+    case 192:
+      if constexpr (!SWAP && !FP8) return launch_inst<192, SWAP, FP8>(tmP, tmQ, ep, push, grid, total_kb, kbps, stages, smem, st, tr);
+      else return cudaErrorInvalidValue;
     case 256: return launch_inst<256, SWAP, FP8>(tmP, tmQ, ep, push, grid, total_kb, kbps, stages, smem, st, tr);
     default: return cudaErrorInvalidValue;
   }
@@ -490,6 +493,20 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream, int* n_ctas) {
     return gemm_persist_launch(a, stream, n_ctas);
   }
 
+  // K split over a cluster when the tiles alone leave more than half of the SMs idle
+  const auto pick_splits = [](int ctas, int total_kb) {
+    int splits = 1;
+    if (ctas * 2 <= num_sms()) {
+      splits = 8;
+      while (splits > 1 && (ctas * splits > num_sms() || total_kb / splits < 2)) splits >>= 1;
+    }
+    int kbps = (total_kb + splits - 1) / splits;
+    while (splits > 1 && (total_kb + kbps - 1) / kbps != splits) {
+      splits >>= 1;
+      kbps = (total_kb + splits - 1) / splits;
+    }
+    return splits;
+  };
   bool swap = a.M <= 256;
   if (a.force_swap == 0) swap = false;
   if (a.force_swap == 1) swap = true;
@@ -501,6 +518,24 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream, int* n_ctas) {
     bn = a.N >= 2048 && a.M >= 512 ? 256 : 128;
     if (a.N <= 64) bn = 64;
     if (a.N <= 32) bn = 32;
+    if (a.M >= 512 && a.N >= 512 && !a.fp8 && a.force_bn == 0 && a.force_splits == 0) {
+      // Mid-size problems are a wave or two of tiles: pick the tile width (128 / 192 / 256) whose
+      // waves x K blocks per CTA x cycles per K block is smallest, i.e. the one that wastes the fewest
+      // SM-cycles on a partial last wave (768 x 3456: 84 tiles of 256 or 162 of 128 cost about the same,
+      // 108 of 192 a sixth less). Cycles per K block: the slower of the MMAs (2 cycles per column) and the
+      // operand ingest ((128 + width) x 128 bytes at about 96 bytes per cycle), so narrow tiles pay for
+      // their lower arithmetic intensity.
+      const int p_t = (a.M + kTileP - 1) / kTileP, kb = (a.K + BK - 1) / BK;
+      long best = -1;
+      for (int cand : {256, 192, 128}) {
+        const int ctas_c = p_t * ((a.N + cand - 1) / cand);
+        const int sp = pick_splits(ctas_c, kb);
+        const int waves = (ctas_c * sp + num_sms() - 1) / num_sms();
+        const int per_kb = cand == 256 ? 512 : cand == 192 ? 427 : 341;
+        const long cost = long(waves) * ((kb + sp - 1) / sp + (sp > 1 ? 3 : 1)) * per_kb;   // + fixed per-CTA work (cluster reduce when split)
+        if (best < 0 || cost < best) { best = cost; bn = cand; }
+      }
+    }
   }
   if (a.force_bn) bn = a.force_bn;
   if (a.glu && !swap && bn < 16) return cudaErrorInvalidValue;
@@ -511,13 +546,7 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream, int* n_ctas) {
   const int total_kb = (a.K + BK - 1) / BK;
   const int ctas = p_tiles * q_tiles;
 
-  int splits = 1;
-  if (a.force_splits > 0) {
-    splits = a.force_splits;
-  } else if (ctas * 2 <= num_sms()) {
-    splits = 8;
-    while (splits > 1 && (ctas * splits > num_sms() || total_kb / splits < 2)) splits >>= 1;
-  }
+  int splits = a.force_splits > 0 ? a.force_splits : pick_splits(ctas, total_kb);
   int kbps = (total_kb + splits - 1) / splits;
   while (splits > 1 && (total_kb + kbps - 1) / kbps != splits) {
     splits >>= 1;

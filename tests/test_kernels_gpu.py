@@ -40,6 +40,9 @@ GEMM_CASES = [
     dict(M=400, N=2048, K=1024, glu=True, act="silu"),
     dict(M=300, N=512, K=1024, force_swap=0, force_bn=64),
     dict(M=300, N=512, K=1024, force_swap=0, force_bn=32, out_fp32=True),
+    dict(M=768, N=3456, K=1152, bias=True),                                           # picks the 192-wide tile
+    dict(M=700, N=1000, K=320, force_swap=0, force_bn=192, bias=True, residual=True),  # 192-wide, ragged N and M edges
+    dict(M=640, N=1536, K=512, force_swap=0, force_bn=192, glu=True, act="silu", force_splits=2),
 ]
 
 
@@ -85,6 +88,11 @@ def test_gemm_sumsq_and_determinism():
         _status_ok()
         assert relerr(ss, o.float().pow(2).sum(-1)) < 1e-4
         assert torch.equal(o, o2)
+        if M > 256:      # 192-wide tiles: the last column block of a tile is only half populated
+            ss3 = torch.zeros(M, device=DEV)
+            o3 = ops.gemm(x, w, sumsq=ss3, force_swap=0, force_bn=192)
+            _status_ok()
+            assert relerr(ss3, o3.float().pow(2).sum(-1)) < 1e-4 and relerr(o3, o) < 1e-2
 
 
 @pytest.mark.parametrize("M,glu", [(50, False), (50, True), (1, False), (300, True)])
