@@ -42,11 +42,11 @@ constexpr int kPPThreads = 320;
 constexpr int kBlk = 128 * 128;         // bytes of one [128 rows x 128 B] swizzled block
 constexpr float kRaise = 8.0f;          // raise the running max only beyond this (log2 units)
 
-// 2^x on the FMA pipe: the special-function unit delivers 16 exponentials per clock and SM, which for a
-// 128-wide head costs as many cycles as the two matrix products of the tile; every fourth probability is
-// therefore computed here (round-to-nearest split x = n + f with the 1.5 * 2^23 trick, a cubic for 2^f on
+// 2^x on the FMA pipe (round-to-nearest split x = n + f with the 1.5 * 2^23 trick, a cubic for 2^f on
 // [-0.5, 0.5] with relative error below 6e-4, well under bf16 rounding of P, and n added to the exponent
-// field), which takes a quarter of the load off that unit.
+// field). The special-function unit delivers 16 exponentials per clock and SM, which for a 128-wide head
+// costs as many cycles as the two matrix products of the tile, so a kernel variant can route one or two of
+// every four probabilities through here (template parameter NP); it is off by default because it measured slower.
 __device__ __forceinline__ float exp2_fma(float x) {
   x = fmaxf(x, -125.f);
   const float t = x + 12582912.f;
@@ -369,8 +369,9 @@ bool attn_pp_supported(const AttnParams& p) {
 
 cudaError_t attn_pp_launch(const AttnParams& p, cudaStream_t stream) {
   if (!attn_pp_supported(p) || p.batch <= 0 || p.max_q_len <= 0 || p.group <= 0) return cudaErrorInvalidValue;
-  // PHYAI_ATTN_POLY = 0 / 1 / 2: how many of every four exponentials go to the FMA pipe (default 1)
-  static const int np = [] { const char* e = getenv("PHYAI_ATTN_POLY"); return e && e[0] >= '0' && e[0] <= '2' ? e[0] - '0' : 1; }();
+  // PHYAI_ATTN_POLY = 0 / 1 / 2: how many of every four exponentials go to the FMA pipe. Measured on one box at the
+  // Cosmos3 shape: 0.98 / 1.03 / 1.10 ms, i.e. the FMA pipe, not the special-function unit, is the busier one here: default 0.
+  static const int np = [] { const char* e = getenv("PHYAI_ATTN_POLY"); return e && e[0] >= '0' && e[0] <= '2' ? e[0] - '0' : 0; }();
   if (p.head_dim <= 64) return np == 0 ? attn_pp_launch_db<1, 0>(p, stream) : np == 2 ? attn_pp_launch_db<1, 2>(p, stream) : attn_pp_launch_db<1, 1>(p, stream);
   return np == 0 ? attn_pp_launch_db<2, 0>(p, stream) : np == 2 ? attn_pp_launch_db<2, 2>(p, stream) : attn_pp_launch_db<2, 1>(p, stream);
 }

@@ -42,10 +42,8 @@ __device__ __forceinline__ float epi_act(float v, int act) {
 }
 __device__ __forceinline__ void ld_bf16x4(const __nv_bfloat16* p, float (&f)[4]) {
   const uint2 raw = *reinterpret_cast<const uint2*>(p);
-  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-  const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-  f[0] = __bfloat162float(a.x); f[1] = __bfloat162float(a.y);
-  f[2] = __bfloat162float(b.x); f[3] = __bfloat162float(b.y);
+  f[0] = __uint_as_float(raw.x << 16); f[1] = __uint_as_float(raw.x & 0xffff0000u);
+  f[2] = __uint_as_float(raw.y << 16); f[3] = __uint_as_float(raw.y & 0xffff0000u);
 }
 
 template <int ACT>

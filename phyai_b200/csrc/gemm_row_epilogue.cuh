@@ -23,9 +23,10 @@ __device__ __forceinline__ void grouped_tile_coords(int t, int P, int Q, int& p,
 }
 
 __device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float (&f)[8]) {
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  // bf16 -> fp32 is a shift / mask of the bit pattern (integer pipe; the conversion instruction is a 16-per-clock unit)
+  const uint32_t* u = reinterpret_cast<const uint32_t*>(&raw);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) { f[2 * i] = __bfloat162float(h[i].x); f[2 * i + 1] = __bfloat162float(h[i].y); }
+  for (int i = 0; i < 4; ++i) { f[2 * i] = __uint_as_float(u[i] << 16); f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u); }
 }
 
 // Eight consecutive accumulator columns [n, n + 8) of row m (x holds them); n < ep.N, n % 8 == 0.

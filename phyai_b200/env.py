@@ -114,7 +114,7 @@ class envs:
     PHYAI_GEMM_PERSIST_COMM = EnvField("PHYAI_GEMM_PERSIST_COMM", True, parse_bool)  # 0: peer modes stay off the persistent kernel
     PHYAI_GEMM_2CTA = EnvField("PHYAI_GEMM_2CTA", False, parse_bool)            # 1: CTA-pair (cta_group::2) kernel for large plain GEMMs
     PHYAI_NORM_TMA = EnvField("PHYAI_NORM_TMA", False, parse_bool)              # 1: many-row norms through bulk copies into shared memory
-    PHYAI_ATTN_POLY = EnvField("PHYAI_ATTN_POLY", 1, int)                       # pipelined attention: 0..2 of every 4 exponentials on the FMA pipe
+    PHYAI_ATTN_POLY = EnvField("PHYAI_ATTN_POLY", 0, int)                       # pipelined attention: 0..2 of every 4 exponentials on the FMA pipe
     PHYAI_PI05_OVERLAP = EnvField("PHYAI_PI05_OVERLAP", True, parse_bool)       # 0: no second stream (first Euler step after the prefix)
     # debug / tensor dump
     PHYAI_DEBUG_TENSOR_DUMP_DIR = EnvField("PHYAI_DEBUG_TENSOR_DUMP_DIR", None, str)
