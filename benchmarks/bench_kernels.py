@@ -38,7 +38,7 @@ def bench(fn, n=10, warm=3):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--set", default="all", choices=("gemm", "attention", "norm", "all"))
+    ap.add_argument("--set", default="all", choices=("gemm", "attention", "norm", "fp8", "all"))
     ap.add_argument("--only", default=None, help="run a single named shape (for profiler captures)")
     ap.add_argument("--no-baselines", action="store_true", help="skip the library kernels (keeps a profiler capture small)")
     ap.add_argument("--gemm-2cta", action="store_true", help="also time the CTA-pair (cta_group::2) GEMM kernel")
@@ -72,6 +72,36 @@ def main() -> None:
                 t_2 = bench(lambda: ops.gemm(x, w, out))
                 ops.set_gemm_2cta(None)
                 rows[-1].update(cta_pair_ms=round(t_2, 4), cta_pair_tflops=round(2 * M * N * K / t_2 / 1e9, 1))
+    if a.set in ("fp8", "all"):
+        # block-scaled fp8 (1x128 activation blocks, 128x128 weight blocks) against FlashInfer's groupwise kernel, the
+        # library path the reference serves block-fp8 checkpoints with (layers/linear/backends/flashinfer.py:132-157)
+        from phyai_b200.ops import fp8_block
+
+        for name, (M, K, N) in {"fp8.pi05.prefix.gate_up": (968, 2048, 32768), "fp8.pi05.expert.gate_up": (52, 1024, 8192),
+                                "fp8.cosmos3.qkv": (7040, 5120, 7168)}.items():
+            if a.only and name != a.only:
+                continue
+            x, w = torch.randn(M, K, device=dev) * 0.5, torch.randn(N, K, device=dev) * 0.05
+            xb = x.reshape(M, K // 128, 128)
+            xs = xb.abs().amax(-1).clamp_min(1e-12) / 448.0
+            x8 = (xb / xs[..., None]).clamp(-448, 448).reshape(M, K).to(torch.float8_e4m3fn)
+            w8, ws = fp8_block.quantize_weight_block(w)
+            out = torch.empty(M, N, device=dev, dtype=bf)
+            t_o = bench(lambda: fp8_block.gemm_fp8_block(x8, xs, w8, ws, out))
+            t_f, note = float("nan"), ""
+            if not a.no_baselines:
+                try:
+                    import flashinfer.gemm as fg
+
+                    xs_mn = xs.t().contiguous()                      # MN-major: (K/128, M)
+                    ws_mn = ws.t().contiguous()                      # (K/128, N/128)
+                    t_f = bench(lambda: fg.gemm_fp8_nt_groupwise(x8, w8, xs_mn, ws_mn, scale_granularity_mnk=(1, 128, 128),
+                                                                 scale_major_mode="MN", out_dtype=bf))
+                except Exception as e:  # noqa: BLE001 - a missing or unsupported library path is a result, not a failure
+                    note = f"{type(e).__name__}: {str(e)[:120]}"
+            tf = 2 * M * N * K / t_o / 1e9
+            rows.append(dict(kernel="gemm_fp8_block", shape=name, ours_ms=round(t_o, 4), flashinfer_ms=round(t_f, 4), tflops=round(tf, 1),
+                             note=note))
     if a.set in ("attention", "all"):
         for name, (S, T, hq, hkv, D) in {"cosmos3.gen": (7040, 512, 40, 8, 128), "cosmos3.gen.tp4": (7040, 512, 10, 2, 128)}.items():
             if a.only and name != a.only:

@@ -139,8 +139,8 @@ __global__ void cfg_exchange_kernel(const __nv_bfloat16* mine, long long n, Peer
       __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const float m0 = __bfloat162float(a2[k].x), m1 = __bfloat162float(a2[k].y);
-        const float t0 = __bfloat162float(b2[k].x), t1 = __bfloat162float(b2[k].y);
+        const float m0 = bf2f(a2[k].x), m1 = bf2f(a2[k].y);
+        const float t0 = bf2f(b2[k].x), t1 = bf2f(b2[k].y);
         const float c0 = is_cond ? m0 : t0, c1 = is_cond ? m1 : t1;
         const float u0 = is_cond ? t0 : m0, u1 = is_cond ? t1 : m1;
         const float v0 = u0 + g * (c0 - u0), v1 = u1 + g * (c1 - u1);

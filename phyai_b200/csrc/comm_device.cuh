@@ -115,25 +115,25 @@ __device__ __forceinline__ void reduce_norm_row(const ReduceNormArgs& a, int row
       const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        acc[2 * i] += __bfloat162float(b2[i].x);
-        acc[2 * i + 1] += __bfloat162float(b2[i].y);
+        acc[2 * i] += bf2f(b2[i].x);
+        acc[2 * i + 1] += bf2f(b2[i].y);
       }
     }
     if (a.bias) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] += __bfloat162float(a.bias[v * 8 + i]);
+      for (int i = 0; i < 8; ++i) acc[i] += bf2f(a.bias[v * 8 + i]);
     }
     if (a.col_gate) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] *= __bfloat162float(a.col_gate[v * 8 + i]);
+      for (int i = 0; i < 8; ++i) acc[i] *= bf2f(a.col_gate[v * 8 + i]);
     }
     if (a.residual) {
       const uint4 raw = *reinterpret_cast<const uint4*>(a.residual + size_t(row) * a.ldr + v * 8);
       const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        acc[2 * i] += __bfloat162float(b2[i].x);
-        acc[2 * i + 1] += __bfloat162float(b2[i].y);
+        acc[2 * i] += bf2f(b2[i].x);
+        acc[2 * i + 1] += bf2f(b2[i].y);
       }
     }
     uint4 out;
@@ -141,7 +141,7 @@ __device__ __forceinline__ void reduce_norm_row(const ReduceNormArgs& a, int row
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       o2[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-      const float x0 = __bfloat162float(o2[i].x), x1 = __bfloat162float(o2[i].y);
+      const float x0 = bf2f(o2[i].x), x1 = bf2f(o2[i].y);
       ss += x0 * x0 + x1 * x1;
     }
     if (hrow) *reinterpret_cast<uint4*>(hrow + v * 8) = out;
@@ -167,17 +167,17 @@ __device__ __forceinline__ void reduce_norm_row(const ReduceNormArgs& a, int row
     __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      float x0 = __bfloat162float(b2[i].x) * rstd, x1 = __bfloat162float(b2[i].y) * rstd;
+      float x0 = bf2f(b2[i].x) * rstd, x1 = bf2f(b2[i].y) * rstd;
       const int c = v * 8 + 2 * i;
       if (a.norm_mode == 3) {  // AdaRMS: (1 + scale) and shift from the modulation row
-        x0 = x0 * (1.f + __bfloat162float(a.mod[c])) + __bfloat162float(a.mod[a.N + c]);
-        x1 = x1 * (1.f + __bfloat162float(a.mod[c + 1])) + __bfloat162float(a.mod[a.N + c + 1]);
+        x0 = x0 * (1.f + bf2f(a.mod[c])) + bf2f(a.mod[a.N + c]);
+        x1 = x1 * (1.f + bf2f(a.mod[c + 1])) + bf2f(a.mod[a.N + c + 1]);
       } else if (a.norm_mode == 1) {  // Gemma (1 + w)
-        x0 *= 1.f + __bfloat162float(a.weight[c]);
-        x1 *= 1.f + __bfloat162float(a.weight[c + 1]);
+        x0 *= 1.f + bf2f(a.weight[c]);
+        x1 *= 1.f + bf2f(a.weight[c + 1]);
       } else if (a.norm_mode == 0) {
-        x0 *= __bfloat162float(a.weight[c]);
-        x1 *= __bfloat162float(a.weight[c + 1]);
+        x0 *= bf2f(a.weight[c]);
+        x1 *= bf2f(a.weight[c + 1]);
       }
       o2[i] = __floats2bfloat162_rn(x0, x1);
     }

@@ -83,7 +83,7 @@ __device__ __forceinline__ void epilogue_pass_t(const EpiParams& ep, const float
       if (ep.col_gate) {
         if constexpr (GLU) {
           const __nv_bfloat162 g = *reinterpret_cast<const __nv_bfloat162*>(ep.col_gate + (n >> 1));
-          gate4[0] = __bfloat162float(g.x); gate4[1] = __bfloat162float(g.y);
+          gate4[0] = bf2f(g.x); gate4[1] = bf2f(g.y);
         } else {
           ld_bf16x4(ep.col_gate + n, gate4);
         }
@@ -137,7 +137,7 @@ __device__ __forceinline__ void epilogue_pass_t(const EpiParams& ep, const float
             y0 *= gate4[0]; y1 *= gate4[1];
             if (res_row) {
               const __nv_bfloat162 r2 = *reinterpret_cast<const __nv_bfloat162*>(res_row + no);
-              y0 += __bfloat162float(r2.x); y1 += __bfloat162float(r2.y);
+              y0 += bf2f(r2.x); y1 += bf2f(r2.y);
             }
           }
           if (AUX && ep.out_fp32) {
@@ -146,7 +146,7 @@ __device__ __forceinline__ void epilogue_pass_t(const EpiParams& ep, const float
           } else {
             const __nv_bfloat162 o = __floats2bfloat162_rn(y0, y1);
             *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(ep.out) + size_t(m) * ep.ldo + no) = o;
-            const float q0 = __bfloat162float(o.x), q1 = __bfloat162float(o.y);
+            const float q0 = bf2f(o.x), q1 = bf2f(o.y);
             ss = q0 * q0 + q1 * q1;
           }
         } else {
@@ -176,8 +176,8 @@ __device__ __forceinline__ void epilogue_pass_t(const EpiParams& ep, const float
             *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(ep.out) + size_t(m) * ep.ldo + n) = raw;
             if constexpr (AUX) {
               // a norm consuming the sum of squares sees the rounded values
-              const float q0 = __bfloat162float(o01.x), q1 = __bfloat162float(o01.y);
-              const float q2 = __bfloat162float(o23.x), q3 = __bfloat162float(o23.y);
+              const float q0 = bf2f(o01.x), q1 = bf2f(o01.y);
+              const float q2 = bf2f(o23.x), q3 = bf2f(o23.y);
               ss = q0 * q0 + q1 * q1 + q2 * q2 + q3 * q3;
             }
           }
@@ -296,8 +296,8 @@ __device__ __forceinline__ void epilogue_rope(const EpiParams& ep, const float* 
       const float* cs = rp.cos_sin + size_t(rp.pos[m]) * rp.D;
       const float2 cc = *reinterpret_cast<const float2*>(cs + i0), sn = *reinterpret_cast<const float2*>(cs + half + i0);
       // the projection is rounded to bf16 before the rotation, as the separate kernels would see it
-      const float a0 = __bfloat162float(__float2bfloat16(x[0])), b0 = __bfloat162float(__float2bfloat16(x[1]));
-      const float a1 = __bfloat162float(__float2bfloat16(x[2])), b1 = __bfloat162float(__float2bfloat16(x[3]));
+      const float a0 = bf2f(__float2bfloat16(x[0])), b0 = bf2f(__float2bfloat16(x[1]));
+      const float a1 = bf2f(__float2bfloat16(x[2])), b1 = bf2f(__float2bfloat16(x[3]));
       __nv_bfloat16* dst = is_q ? rp.q_out + size_t(m) * rp.ldq + size_t(head) * rp.D
                                 : rp.k_pool + size_t(rp.slots[m]) * rp.pool_stride + size_t(head - rp.Hq) * rp.D;
       *reinterpret_cast<__nv_bfloat162*>(dst + i0) = __floats2bfloat162_rn(a0 * cc.x - b0 * sn.x, a1 * cc.y - b1 * sn.y);

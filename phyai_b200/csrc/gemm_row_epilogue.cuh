@@ -51,21 +51,21 @@ __device__ __forceinline__ float row_epilogue_8(const EpiParams& ep, float (&x)[
     if (ep.col_gate) {
       const uint2 gr = *reinterpret_cast<const uint2*>(ep.col_gate + no);
       const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gr);
-      y[0] *= __bfloat162float(g2[0].x); y[1] *= __bfloat162float(g2[0].y);
-      y[2] *= __bfloat162float(g2[1].x); y[3] *= __bfloat162float(g2[1].y);
+      y[0] *= bf2f(g2[0].x); y[1] *= bf2f(g2[0].y);
+      y[2] *= bf2f(g2[1].x); y[3] *= bf2f(g2[1].y);
     }
     if (res_row) {
       const uint2 rr = *reinterpret_cast<const uint2*>(res_row + no);
       const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rr);
-      y[0] += __bfloat162float(r2[0].x); y[1] += __bfloat162float(r2[0].y);
-      y[2] += __bfloat162float(r2[1].x); y[3] += __bfloat162float(r2[1].y);
+      y[0] += bf2f(r2[0].x); y[1] += bf2f(r2[0].y);
+      y[2] += bf2f(r2[1].x); y[3] += bf2f(r2[1].y);
     }
     const __nv_bfloat162 o0 = __floats2bfloat162_rn(y[0], y[1]), o1 = __floats2bfloat162_rn(y[2], y[3]);
     uint2 o;
     o.x = *reinterpret_cast<const uint32_t*>(&o0);
     o.y = *reinterpret_cast<const uint32_t*>(&o1);
     *reinterpret_cast<uint2*>(out_row + no) = o;
-    const float q0 = __bfloat162float(o0.x), q1 = __bfloat162float(o0.y), q2 = __bfloat162float(o1.x), q3 = __bfloat162float(o1.y);
+    const float q0 = bf2f(o0.x), q1 = bf2f(o0.y), q2 = bf2f(o1.x), q3 = bf2f(o1.y);
     return q0 * q0 + q1 * q1 + q2 * q2 + q3 * q3;
   } else {
     if constexpr (ACT != 0) {
@@ -92,7 +92,7 @@ __device__ __forceinline__ float row_epilogue_8(const EpiParams& ep, float (&x)[
     float ss = 0.f;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float q0 = __bfloat162float(o2[j].x), q1 = __bfloat162float(o2[j].y);
+      const float q0 = bf2f(o2[j].x), q1 = bf2f(o2[j].y);
       ss += q0 * q0 + q1 * q1;
     }
     return ss;

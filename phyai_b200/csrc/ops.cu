@@ -589,7 +589,7 @@ __global__ void rope_kv_kernel(RopeKvArgs a) {
   if (nw) {
     float ss = 0.f;
     for (int i = lane; i < D; i += 32) {
-      const float v = __bfloat162float(src[i]);
+      const float v = bf2f(src[i]);
       ss += v * v;
     }
     ss = warp_sum(ss);
@@ -600,11 +600,11 @@ __global__ void rope_kv_kernel(RopeKvArgs a) {
   for (int i = lane; i < (D >> 1); i += 32) {
     // pair (i, i + half_rot) inside the rotated span; dims past rot_dim pass through
     if (i < half_rot) {
-      float x1 = __bfloat162float(src[i]), x2 = __bfloat162float(src[i + half_rot]);
+      float x1 = bf2f(src[i]), x2 = bf2f(src[i + half_rot]);
       if (nw) {
         // norm output is rounded to bf16 before the rotation, as separate kernels would
-        x1 = __bfloat162float(__float2bfloat16(x1 * rstd * __bfloat162float(nw[i])));
-        x2 = __bfloat162float(__float2bfloat16(x2 * rstd * __bfloat162float(nw[i + half_rot])));
+        x1 = bf2f(__float2bfloat16(x1 * rstd * bf2f(nw[i])));
+        x2 = bf2f(__float2bfloat16(x2 * rstd * bf2f(nw[i + half_rot])));
       }
       float c = 1.f, s = 0.f;
       if (cs) { c = cs[i]; s = cs[half_rot + i]; }
@@ -613,8 +613,8 @@ __global__ void rope_kv_kernel(RopeKvArgs a) {
     }
   }
   for (int i = 2 * half_rot + lane; i < D; i += 32) {
-    float x = __bfloat162float(src[i]);
-    if (nw) x = x * rstd * __bfloat162float(nw[i]);
+    float x = bf2f(src[i]);
+    if (nw) x = x * rstd * bf2f(nw[i]);
     dst[i] = __float2bfloat16(x);
   }
 }
@@ -704,8 +704,8 @@ __global__ void gated_act_kernel(const __nv_bfloat16* x, __nv_bfloat16* y, int M
   if (idx >= (long long)M * I) return;
   const int m = int(idx / I), j = int(idx % I);
   const __nv_bfloat16* r = x + size_t(m) * 2 * I;
-  const float g = __bfloat162float(interleaved ? r[2 * j] : r[j]);
-  const float u = __bfloat162float(interleaved ? r[2 * j + 1] : r[I + j]);
+  const float g = bf2f(interleaved ? r[2 * j] : r[j]);
+  const float u = bf2f(interleaved ? r[2 * j + 1] : r[I + j]);
   y[size_t(m) * I + j] = __float2bfloat16(act_f(g, act) * u);
 }
 cudaError_t gated_act_launch(const __nv_bfloat16* x, __nv_bfloat16* y, int M, int I, int act,
@@ -720,7 +720,7 @@ __global__ void unary_kernel(const __nv_bfloat16* x, __nv_bfloat16* y, long long
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   pdl_launch_dependents();
   pdl_wait();
-  if (i < n) y[i] = __float2bfloat16(act_f(__bfloat162float(x[i]), act));
+  if (i < n) y[i] = __float2bfloat16(act_f(bf2f(x[i]), act));
 }
 cudaError_t unary_launch(const __nv_bfloat16* x, __nv_bfloat16* y, long long n, int act,
                          cudaStream_t s) {
@@ -737,10 +737,10 @@ __global__ void axpy_kernel(void* x, int x_fp32, const __nv_bfloat16* v, float d
   if (i >= n) return;
   if (x_fp32) {
     float* xf = reinterpret_cast<float*>(x);
-    xf[i] += dt * __bfloat162float(v[i]);
+    xf[i] += dt * bf2f(v[i]);
   } else {
     __nv_bfloat16* xb = reinterpret_cast<__nv_bfloat16*>(x);
-    xb[i] = __float2bfloat16(__bfloat162float(xb[i]) + dt * __bfloat162float(v[i]));
+    xb[i] = __float2bfloat16(bf2f(xb[i]) + dt * bf2f(v[i]));
   }
 }
 cudaError_t axpy_launch(void* x, int x_fp32, const __nv_bfloat16* v, float dt, long long n,
@@ -756,7 +756,7 @@ __global__ void cfg_combine_kernel(const __nv_bfloat16* c, const __nv_bfloat16* 
   pdl_launch_dependents();
   pdl_wait();
   if (i >= n) return;
-  const float vc = __bfloat162float(c[i]), vu = __bfloat162float(u[i]);
+  const float vc = bf2f(c[i]), vu = bf2f(u[i]);
   const float v = vu + g * (vc - vu);
   if (out) out[i] = __float2bfloat16(v);
   if (x) x[i] += dt * v;
