@@ -57,11 +57,36 @@ __device__ __forceinline__ float exp2_fma(float x) {
   return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
 }
 
+// Packed fp32 pairs (one 64-bit register): sm_100 issues fma / add on both halves with one instruction, which
+// halves the scale-subtract and row-sum instructions of the softmax; the three-input max halves the max pass.
+// The softmax warps are issue-bound (two warps per scheduler next to 128 scores per thread and chunk).
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 }  // namespace
 
 // DB: head dim padded to 64 * DB, DB in {1, 2}. NP: how many of every four probabilities take exp2_fma (0..2).
 template <int DB, int NP>
-__global__ void __launch_bounds__(kPPThreads, 1)
+__global__ void __maxnreg__(192)
 attn_pp_kernel(AttnParams p, int* status, const __grid_constant__ CUtensorMap tmQ,
                const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV) {
   constexpr int DP = 64 * DB;
@@ -232,7 +257,7 @@ attn_pp_kernel(AttnParams p, int* status, const __grid_constant__ CUtensorMap tm
       float mx = -INFINITY;
       if (lim >= kT) {
 #pragma unroll
-        for (int c = 0; c < kT; ++c) mx = fmaxf(mx, __uint_as_float(sv[c]));
+        for (int c = 0; c < kT; c += 2) mx = max3(mx, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]));
       } else {
 #pragma unroll
         for (int c = 0; c < kT; ++c) mx = fmaxf(mx, c < lim ? __uint_as_float(sv[c]) : -INFINITY);
@@ -248,7 +273,22 @@ attn_pp_kernel(AttnParams p, int* status, const __grid_constant__ CUtensorMap tm
       const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
       float sum = 0.f;
       uint32_t pk[kT / 2];
-      if (lim >= kT) {
+      if (NP == 0 && lim >= kT) {
+        const uint64_t sc2 = pack2(scale_log2, scale_log2), nm2 = pack2(-m_use, -m_use);
+        uint64_t sum2 = pack2(0.f, 0.f);
+#pragma unroll
+        for (int c = 0; c < kT; c += 2) {
+          float x0, x1;
+          unpack2(fma2(pack2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), sc2, nm2), x0, x1);
+          const float p0 = exp2f(x0), p1 = exp2f(x1);
+          sum2 = add2(sum2, pack2(p0, p1));
+          const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+          pk[c >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        float s0, s1;
+        unpack2(sum2, s0, s1);
+        sum = s0 + s1;
+      } else if (lim >= kT) {
 #pragma unroll
         for (int c = 0; c < kT; c += 4) {
           const float p0 = exp2f(__uint_as_float(sv[c]) * scale_log2 - m_use);
