@@ -11,8 +11,10 @@
 // promoted. For skinny problems the operands are swapped (weights fill the 128-row operand, the
 // activation rows become the MMA N), which moves the per-row activation scale from "one per
 // thread" to "one per column": those BN x KB factors are staged in shared memory once.
-// Roles (192 threads): warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 promotion; afterwards all
-// threads run the shared epilogue (bias / activation / gated activation / gate / residual).
+// Roles: warp 0 TMA producer, warp 1 MMA issuer, then PW promotion warps (4, or 8 for the 256-wide tile
+// of large problems: two warps per tensor-memory lane quadrant, each folding half of the columns, so the
+// promotion of a block (128 columns per thread) takes less time than its MMAs); afterwards all threads run
+// the shared epilogue (bias / activation / gated activation / gate / residual).
 //
 // Capability parity: phyai/src/phyai/layers/linear/backends/flashinfer.py:132-172
 // (gemm_fp8_nt_groupwise) and the dequantise + matmul fallback in backends/torch.py:139-176.
@@ -26,20 +28,21 @@
 namespace pb {
 
 namespace {
-constexpr int kBThreads = 192;
 constexpr int kBStagesMax = 6;
 constexpr int kP = 128;         // rows of the 128-row operand
 constexpr int kRowB = 128;      // bytes of one operand row per K block (128 e4m3)
 }  // namespace
 
-template <int BN, bool SWAP>
-__global__ void __launch_bounds__(kBThreads)
+template <int BN, bool SWAP, int PW>
+__global__ void __launch_bounds__(64 + 32 * PW)
 gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ, EpiParams ep,
                       const float* __restrict__ a_scale, const float* __restrict__ w_scale, int total_kb, int stages,
                       int* status) {
   constexpr int P_BYTES = kP * kRowB, Q_BYTES = BN * kRowB, STAGE_BYTES = P_BYTES + Q_BYTES;
   constexpr int TM = SWAP ? BN : kP, TN = SWAP ? kP : BN, LDS = TN + 4;
   constexpr int TCOLS = 2 * BN < 32 ? 32 : 2 * BN;
+  constexpr int NTHREADS = 64 + 32 * PW;
+  constexpr int CW = BN / (PW / 4);            // accumulator columns one promotion thread owns
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -53,7 +56,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_cons
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&tfull[b], 1); mbar_init(&tempty[b], 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&tfull[b], 1); mbar_init(&tempty[b], PW); }
     err_s = 0;
     mbar_fence_init();
     prefetch_tmap(&tmP);
@@ -70,7 +73,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_cons
   if constexpr (SWAP) {
     // activation rows of this tile are the MMA N: stage their per-K-block scales (0 past M)
     const int m0 = q_tile * BN;
-    for (int i = threadIdx.x; i < total_kb * BN; i += kBThreads) {
+    for (int i = threadIdx.x; i < total_kb * BN; i += NTHREADS) {
       const int kb = i / BN, c = i % BN;
       colscale[i] = (m0 + c < ep.M) ? a_scale[size_t(m0 + c) * total_kb + kb] : 0.f;
     }
@@ -110,29 +113,30 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_cons
   } else {
     // ---------------------------------------------------------------- promotion
     const int quad = warp & 3, i = quad * 32 + lane;        // row of the P operand = tensor-memory lane
-    float acc[BN];
+    const int cb = ((warp - 2) >> 2) * CW;                  // first accumulator column of this thread
+    float acc[CW];
 #pragma unroll
-    for (int c = 0; c < BN; ++c) acc[c] = 0.f;
+    for (int c = 0; c < CW; ++c) acc[c] = 0.f;
     const int p_global = p_tile * kP + i;
     // the P operand's own scale: activation row (1 x 128 blocks) or weight block row (128 x 128)
     const float* my_scale = SWAP ? w_scale + size_t(p_tile) * total_kb
                                  : a_scale + size_t(min(p_global, ep.M - 1)) * total_kb;
-    const float* w_blk = SWAP ? nullptr : w_scale + size_t((q_tile * BN) / 128) * total_kb;
+    const float* w_blk = SWAP ? nullptr : w_scale + size_t((q_tile * BN + cb) / 128) * total_kb;
     bool ok = true;
     for (int kb = 0; kb < total_kb && !err_s; ++kb) {
       const int buf = kb & 1;
       if (!mbar_wait(&tfull[buf], uint32_t((kb >> 1) & 1))) { err_s = kStatusTimeoutAcc; ok = false; break; }
       tc_fence_after();
       const float f = SWAP ? my_scale[kb] : my_scale[kb] * w_blk[kb];
-      constexpr int CH = BN >= 32 ? 32 : 16;
+      constexpr int CH = CW >= 32 ? 32 : 16;
 #pragma unroll
-      for (int c = 0; c < BN; c += CH) {
+      for (int c = 0; c < CW; c += CH) {
         uint32_t r[CH];
-        const uint32_t taddr = tmem + (uint32_t(quad * 32) << 16) + uint32_t(buf * BN + c);
+        const uint32_t taddr = tmem + (uint32_t(quad * 32) << 16) + uint32_t(buf * BN + cb + c);
         if constexpr (CH == 32) tmem_ld_32x32(taddr, r); else tmem_ld_32x16(taddr, r);
         tmem_ld_wait();
         if constexpr (SWAP) {
-          const float* cs = colscale + kb * BN + c;
+          const float* cs = colscale + kb * BN + cb + c;
 #pragma unroll
           for (int j = 0; j < CH; ++j) acc[c + j] = fmaf(f * cs[j], __uint_as_float(r[j]), acc[c + j]);
         } else {
@@ -150,11 +154,11 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_cons
       float* stg = reinterpret_cast<float*>(smem);
       if constexpr (!SWAP) {
 #pragma unroll
-        for (int c = 0; c < BN; c += 4)
-          *reinterpret_cast<float4*>(stg + i * LDS + c) = make_float4(acc[c], acc[c + 1], acc[c + 2], acc[c + 3]);
+        for (int c = 0; c < CW; c += 4)
+          *reinterpret_cast<float4*>(stg + i * LDS + cb + c) = make_float4(acc[c], acc[c + 1], acc[c + 2], acc[c + 3]);
       } else {
 #pragma unroll
-        for (int c = 0; c < BN; ++c) stg[c * LDS + i] = acc[c];
+        for (int c = 0; c < CW; ++c) stg[(cb + c) * LDS + i] = acc[c];
       }
     }
   }
@@ -164,7 +168,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_cons
   if (err == 0) {
     const int m0 = SWAP ? q_tile * BN : p_tile * kP;
     const int n0 = SWAP ? p_tile * kP : q_tile * BN;
-    epilogue_pass<TN>(ep, reinterpret_cast<const float*>(smem), smem_u32(smem), LDS, m0, n0, 0, TM, 1, warp, lane, kBThreads / 32);
+    epilogue_pass<TN>(ep, reinterpret_cast<const float*>(smem), smem_u32(smem), LDS, m0, n0, 0, TM, 1, warp, lane, NTHREADS / 32);
   } else if (threadIdx.x == 0) {
     if (status) atomicCAS(status, 0, err);
     const uint64_t t0 = globaltimer_ns();
@@ -175,17 +179,17 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_cons
   if (warp == 1) tmem_dealloc(tmem, TCOLS);
 }
 
-template <int BN, bool SWAP>
+template <int BN, bool SWAP, int PW = 4>
 static cudaError_t launch_block(const CUtensorMap& tmP, const CUtensorMap& tmQ, const EpiParams& ep, const float* a_scale,
                                 const float* w_scale, dim3 grid, int total_kb, int stages, size_t smem, cudaStream_t st) {
-  auto kern = gemm_fp8_block_kernel<BN, SWAP>;
+  auto kern = gemm_fp8_block_kernel<BN, SWAP, PW>;
   static bool attr_done = false;
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return e;
     attr_done = true;
   }
-  return launch_kernel(kern, grid, dim3(kBThreads), smem, st, 1, tmP, tmQ, ep, a_scale, w_scale, total_kb, stages,
+  return launch_kernel(kern, grid, dim3(64 + 32 * PW), smem, st, 1, tmP, tmQ, ep, a_scale, w_scale, total_kb, stages,
                        kernel_status_ptr());
 }
 
@@ -196,7 +200,9 @@ cudaError_t gemm_fp8_block_launch(const GemmArgs& a, cudaStream_t stream) {
       (reinterpret_cast<uintptr_t>(a.col_gate) & 7) || (reinterpret_cast<uintptr_t>(a.residual) & 7) || (a.residual && a.ldr % 4))
     return cudaErrorInvalidValue;
   const bool swap = a.M <= 64;
-  const int bn = swap ? (a.M <= 16 ? 16 : (a.M <= 32 ? 32 : 64)) : 128;
+  // large problems: 256-wide tiles with eight promotion warps (MMA-bound); otherwise 128-wide with four
+  const bool wide = !swap && a.M > 256 && a.N >= 512 && a.N % 128 == 0;
+  const int bn = swap ? (a.M <= 16 ? 16 : (a.M <= 32 ? 32 : 64)) : (wide ? 256 : 128);
   const int total_kb = a.K / 128;
   const int p_rows = swap ? a.N : a.M, q_rows = swap ? a.M : a.N;
   const int p_tiles = (p_rows + kP - 1) / kP, q_tiles = (q_rows + bn - 1) / bn;
@@ -228,6 +234,7 @@ cudaError_t gemm_fp8_block_launch(const GemmArgs& a, cudaStream_t stream) {
       default: return launch_block<64, true>(tmP, tmQ, ep, a.a_scale, a.w_scale, grid, total_kb, stages, smem, stream);
     }
   }
+  if (wide) return launch_block<256, false, 8>(tmP, tmQ, ep, a.a_scale, a.w_scale, grid, total_kb, stages, smem, stream);
   return launch_block<128, false>(tmP, tmQ, ep, a.a_scale, a.w_scale, grid, total_kb, stages, smem, stream);
 }
 

@@ -182,3 +182,15 @@ def test_heartbeat_and_status_translation():
     time.sleep(0.05)
     live.stop()
     assert live._n >= 2
+
+
+def test_show_env_cli(capsys):
+    from phyai_b200.__main__ import main
+
+    assert main(["show-env"]) == 0
+    out = capsys.readouterr().out
+    import json as _json
+
+    info = _json.loads(out)
+    assert "torch" in info and "PHYAI_PEER_COMM" in info["env"] and "jit_cache_dir" in info
+    assert main(["nope"]) == 2
