@@ -86,7 +86,7 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 
 // DB: head dim padded to 64 * DB, DB in {1, 2}. NP: how many of every four probabilities take exp2_fma (0..2).
 template <int DB, int NP>
-__global__ void __maxnreg__(192)
+__global__ void __launch_bounds__(kPPThreads, 1)
 attn_pp_kernel(AttnParams p, int* status, const __grid_constant__ CUtensorMap tmQ,
                const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV) {
   constexpr int DP = 64 * DB;
