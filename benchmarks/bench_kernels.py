@@ -77,8 +77,9 @@ def main() -> None:
         # library path the reference serves block-fp8 checkpoints with (layers/linear/backends/flashinfer.py:132-157)
         from phyai_b200.ops import fp8_block
 
-        for name, (M, K, N) in {"fp8.pi05.prefix.gate_up": (968, 2048, 32768), "fp8.pi05.expert.gate_up": (52, 1024, 8192),
-                                "fp8.cosmos3.qkv": (7040, 5120, 7168)}.items():
+        fp8_shapes = {"fp8.pi05.prefix.gate_up": (968, 2048, 32768), "fp8.pi05.expert.gate_up": (52, 1024, 8192),
+                      "fp8.cosmos3.qkv": (7040, 5120, 7168)}
+        for name, (M, K, N) in fp8_shapes.items():
             if a.only and name != a.only:
                 continue
             x, w = torch.randn(M, K, device=dev) * 0.5, torch.randn(N, K, device=dev) * 0.05
@@ -88,8 +89,11 @@ def main() -> None:
             w8, ws = fp8_block.quantize_weight_block(w)
             out = torch.empty(M, N, device=dev, dtype=bf)
             t_o = bench(lambda: fp8_block.gemm_fp8_block(x8, xs, w8, ws, out))
-            t_f, note = float("nan"), ""
+            row = dict(kernel="gemm_fp8_block", shape=name, ours_ms=round(t_o, 4), tflops=round(2 * M * N * K / t_o / 1e9, 1),
+                       kernel_status=ops.kernel_status())
+            print(json.dumps(row), flush=True)          # before the library call: its first use may compile for minutes
             if not a.no_baselines:
+                t_f, note = float("nan"), ""
                 try:
                     import flashinfer.gemm as fg
 
@@ -99,9 +103,7 @@ def main() -> None:
                                                                  scale_major_mode="MN", out_dtype=bf))
                 except Exception as e:  # noqa: BLE001 - a missing or unsupported library path is a result, not a failure
                     note = f"{type(e).__name__}: {str(e)[:120]}"
-            tf = 2 * M * N * K / t_o / 1e9
-            rows.append(dict(kernel="gemm_fp8_block", shape=name, ours_ms=round(t_o, 4), flashinfer_ms=round(t_f, 4), tflops=round(tf, 1),
-                             note=note))
+                print(json.dumps(dict(kernel="flashinfer.gemm_fp8_nt_groupwise", shape=name, flashinfer_ms=round(t_f, 4), note=note)), flush=True)
     if a.set in ("attention", "all"):
         for name, (S, T, hq, hkv, D) in {"cosmos3.gen": (7040, 512, 40, 8, 128), "cosmos3.gen.tp4": (7040, 512, 10, 2, 128)}.items():
             if a.only and name != a.only:
