@@ -5,7 +5,7 @@ heads and MLP columns are sharded by the parallel linear layers (the single KV h
 stacks is replicated); the row-parallel products are summed with ``parallel.all_reduce``, which on
 CUDA goes to the peer-memory backend for these small messages (one push kernel + one reduce kernel,
 no NCCL launch). The model runs its eager path here: the single-GPU plugin's captured plan assumes
-whole weights, and one B200 already serves the batch-1 case faster than a TP group can (18.9 ms;
+whole weights, and one B200 already serves the batch-1 case faster than a TP group can (about 17 ms;
 a TP step adds 2 x 36 reductions per denoise step), so this entry exists for checkpoints that do
 not fit one GPU and for parity with TP-capable layers.
 

@@ -6,13 +6,18 @@ CUDA graph per prompt-length bucket:
 
 * ``vision``  all cameras of all robots in one batch (the reference runs one robot at a
   time, phyai/src/phyai/models/pi05/scheduler_ws1_pi05.py:449-462);
-* ``prefix``  18 Gemma blocks over [image | prompt] rows; K/V go straight from the RoPE
-  kernel into the paged pool; the last block stops after its K/V write because nothing
-  reads its output (the reference computes it, scheduler_ws1_pi05.py:505-511);
-* ``expert``  the 10-step Euler loop, 8 kernels per block: AdaRMSNorm, qkv GEMM,
-  RoPE+KV write, joint attention (KV split over a cluster), o-proj GEMM with gated
-  residual epilogue, AdaRMSNorm, gate-up GEMM with GeGLU epilogue, down GEMM with gated
-  residual epilogue (the reference needs ~13, modeling_pi05.py:801-835).
+* ``prefix``  18 Gemma blocks over [image | prompt] rows; K/V go straight from the epilogue
+  of the QKV GEMM into the paged pool; the last block stops after its K/V write because
+  nothing reads its output (the reference computes it, scheduler_ws1_pi05.py:505-511);
+* ``expert``  the 10-step Euler loop, 5 kernels per block: QKV GEMM (AdaRMS factor, RoPE and
+  K/V write in its epilogue), joint attention (KV split over a cluster), o-proj GEMM with
+  gated residual and sum-of-squares epilogue, gate-up GEMM with AdaRMS factor and GeGLU
+  epilogue, down GEMM with gated residual and sum-of-squares epilogue (the reference needs
+  ~13, modeling_pi05.py:801-835). With ``fold_norms = False`` the unfused 8-kernel sequence
+  (separate AdaRMSNorm and RoPE kernels) runs instead.
+
+The first Euler step runs on a second stream underneath the prefix decoder (``_run_overlapped``):
+block ``li`` of the expert only needs the prefix K/V of block ``li``.
 
 KV pool layout: robot ``b`` owns the slab of slots ``1 + b*(P+C) + [0, P+C)`` (``P`` = max
 prefix rows, ``C`` = chunk; slot 0 is unused padding). Its real prefix rows fill the start of
