@@ -252,6 +252,12 @@ bool gemm_persist_eligible(const GemmArgs& a) {
     // peer variants of this kernel: PHYAI_GEMM_PERSIST_COMM=0 keeps them on the one-tile-per-CTA kernel
     static const bool comm_on = [] { const char* e = getenv("PHYAI_GEMM_PERSIST_COMM"); return !(e && e[0] == '0'); }();
     if (!comm_on) return false;
+    // Push / scatter from here are row-per-thread 16-byte stores: fine when half of the rows stay local (2 ranks:
+    // 233.0 -> 213.9 ms per Cosmos3 step), but at 4 ranks three quarters of them cross NVLink in 64-byte pieces and the
+    // step got slower (77.4 -> 83.8 ms on 8 GPUs), so larger groups keep the one-tile kernel, whose push epilogue
+    // writes 256 contiguous bytes per warp. The wait mode only reads local memory and stays here.
+    static const int push_max_world = [] { const char* e = getenv("PHYAI_GEMM_PERSIST_PUSH_WORLD"); return e ? atoi(e) : 2; }();
+    if (a.push->world > push_max_world) return false;
   }
   if (a.push && a.push->world > 0 && (a.push->ld % 8 || a.push->slots_off % 8 || a.push->slot_stride % 8)) return false;
   return a.M >= 512 && a.N >= 2048 && a.K >= 256 && !a.fp8 && !a.out_fp32 && !a.rope && !a.a_scale && !(a.push && (a.row_scale || a.sumsq)) &&
