@@ -148,8 +148,9 @@ class PI05Plan:
         self.mod_post: list[torch.Tensor] = []
         self.mod_final: torch.Tensor | None = None
         self.dt = -1.0 / cfg.num_inference_steps
-        self.expert_splits = 8
-        self.prefix_splits = 2 if B == 1 else 1
+        # KV splits of the attention calls (a cluster of that many CTAs per head and query tile)
+        self.expert_splits = int(envs.PHYAI_PI05_EXPERT_SPLITS.get() or 8)
+        self.prefix_splits = int(envs.PHYAI_PI05_PREFIX_SPLITS.get() or (4 if B == 1 else 1))
         self._layout_key = None
 
     # ------------------------------------------------------------------ setup
