@@ -114,15 +114,47 @@ class PI0Plan(PI05Plan):
         ops.gemm(act, layer.mlp.down.weight, h, residual=h)
 
     def expert(self) -> None:
-        cfg, heads, stack = self.cfg, self.model.heads, self.model.expert_stack
-        Me, fold = self.Me, self.fold_norms
-        # ---- state token, once per request
+        self.state_pass()
+        self.euler_loop()
+
+    def state_pass(self, before_block=None) -> None:
+        """The state token of every robot through the expert, once per request. ``before_block(li)`` runs before
+        block ``li`` is issued (the overlapped schedule waits there for the prefix K/V of that block: the padded
+        prompt rows of the prefix land in the pool slot the state token uses, so the wait precedes the block)."""
+        heads, stack, fold = self.model.heads, self.model.expert_stack, self.fold_norms
         ops.gemm(self.state, heads.state_proj.weight, self.s_h, bias=heads.state_proj.bias)
         for li, layer in enumerate(stack.layers):
+            if before_block is not None:
+                before_block(li)
             self._block(layer, li, self.s_h, self.s_x, self.s_qkv, self.s_q, self.s_attn, self.s_act, self.s_pos,
                         self.s_slots, self.s_qstart, self.s_qlen, self.s_kvlen, 1, self.expert_splits,
                         ss=self.s_ss if fold else None, rope=self.s_rope if fold else None)
-        # ---- Euler loop over the action tokens
+
+    def run(self, lang_bucket: int) -> torch.Tensor:
+        """As the Pi0.5 plan; with the overlapped schedule the state-token pass (90 small launches) runs on a second
+        stream underneath the prefix decoder, block by block behind the prefix K/V it attends to."""
+        if not (self.overlap_first_step and self.fold_norms and self.device.type == "cuda"):
+            return super().run(lang_bucket)
+        main = torch.cuda.current_stream()
+        if self._side_stream is None:
+            self._side_stream = torch.cuda.Stream(device=self.device)
+        side = self._side_stream
+        fork, join = torch.cuda.Event(), torch.cuda.Event()
+        kv_ready = [torch.cuda.Event() for _ in range(self.cfg.num_layers)]
+        fork.record(main)
+        self.vision()
+        self.prefix(lang_bucket, kv_events=kv_ready)
+        with torch.cuda.stream(side):
+            side.wait_event(fork)
+            self.state_pass(before_block=lambda li: side.wait_event(kv_ready[li]))
+            join.record(side)
+        main.wait_event(join)
+        self.euler_loop()
+        return self.out
+
+    def euler_loop(self) -> None:
+        cfg, heads, stack = self.cfg, self.model.heads, self.model.expert_stack
+        Me, fold = self.Me, self.fold_norms
         self.x_t.copy_(self.noise.view(Me, -1))
         for i in range(cfg.num_inference_steps):
             ops.gemm(self.x_t, self.w_fold, self.e_t, bias=self.time_bias[i], act="silu")

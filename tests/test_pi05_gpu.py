@@ -70,8 +70,11 @@ def test_plan_matches_eager(batch, graph, overlap, monkeypatch):
     eng.close()
 
 
-@pytest.mark.parametrize("batch", [1, 2])
-def test_pi0_plan_matches_eager(batch):
+@pytest.mark.parametrize("batch,overlap", [(1, True), (2, True), (1, False)])
+def test_pi0_plan_matches_eager(batch, overlap, monkeypatch):
+    from phyai_b200.models.pi05.plan_pi05 import PI05Plan
+
+    monkeypatch.setattr(PI05Plan, "overlap_first_step", overlap)   # state-token pass on a second stream under the prefix
     from phyai_b200 import ops
     from phyai_b200.engine import Engine, EngineArgs
     from phyai_b200.engine_config import DeviceConfig, EngineConfig, RuntimeConfig
