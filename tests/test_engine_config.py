@@ -69,3 +69,19 @@ def test_env_parsers(monkeypatch):
     with pytest.raises(ValueError):
         envs.PHYAI_WORLD_SIZE.get()
     assert "PHYAI_TP_SIZE" in envs.fields()
+
+
+def test_native_env_switches_are_registered():
+    """Every PHYAI_* variable the native sources read with getenv() is listed in the env catalogue."""
+    import re
+    from pathlib import Path
+
+    from phyai_b200.env import envs
+
+    root = Path(__file__).resolve().parents[1] / "phyai_b200" / "csrc"
+    used = set()
+    for src in list(root.glob("*.cu")) + list(root.glob("*.cuh")) + list(root.glob("*.cpp")):
+        used |= set(re.findall(r'getenv\("(PHYAI_[A-Z0-9_]+)"\)', src.read_text()))
+    assert used, "expected the kernels to read at least one switch"
+    missing = used - set(envs.fields())
+    assert not missing, f"register in phyai_b200/env.py: {sorted(missing)}"
