@@ -1,6 +1,6 @@
 """Cosmos3 policy request: per-phase latency against the roofline, over a batch sweep.
 
-    python -m benchmarks.roofline.profile_cosmos3_policy --model nano --batches 1 2 4 8 --out-dir gpurun_out/roofline_c3
+    python -m benchmarks.roofline.profile_cosmos3_policy --model nano --batches 1 2 4 8 --out-dir out/roofline_c3
 
 Each batch size runs ``benchmarks/bench_cosmos3.py --policy`` in a child process (so every size starts from a clean
 allocator) and reads its JSON line: the median denoise step (CUDA events) and the whole request. The request splits into

@@ -1,6 +1,6 @@
 """Pi0.5 per-stage latency against the roofline, over a batch sweep.
 
-    python -m benchmarks.roofline.profile_pi05 --batches 1 2 4 8 --out-dir gpurun_out/roofline_pi05
+    python -m benchmarks.roofline.profile_pi05 --batches 1 2 4 8 --out-dir out/roofline_pi05
 
 For every batch size: vision / prefix / expert / whole-request medians (``benchmarks/bench_pi05_stages.py``:
 one CUDA graph per stage, CUDA events, L2 flushed before every replay) joined with the FLOP and traffic model of

@@ -8,6 +8,7 @@
 
 #include "attention.cuh"
 #include "comm.cuh"
+#include "expert_stack.cuh"
 #include "gemm.cuh"
 #include "launch.cuh"
 #include "ops.cuh"
@@ -306,6 +307,96 @@ void quant_fp8(const Tensor& x, Tensor& y, Tensor& scale, int64_t block) {
         "quant_fp8_launch");
 }
 
+// Tensor maps of the persistent action-expert kernel: per layer (qkv, o, gate_up, down) weight maps with
+// 64 x 128 boxes, then the attention-output buffer with a 64 x 64 box; returned as a device byte tensor
+// that the caller keeps alive together with the tensors named here.
+Tensor expert_stack_tmaps(const std::vector<Tensor>& weights, const Tensor& attn) {
+  TORCH_CHECK(!weights.empty() && weights.size() % 4 == 0, "expert_stack_tmaps: four weights per layer");
+  const size_t n = weights.size() + 1;
+  Tensor host = at::empty({int64_t(n * sizeof(CUtensorMap))}, at::TensorOptions().dtype(at::kByte));
+  CUtensorMap* maps = reinterpret_cast<CUtensorMap*>(host.data_ptr());
+  for (size_t i = 0; i < weights.size(); ++i) {
+    const Tensor& w = weights[i];
+    TORCH_CHECK(w.is_cuda() && w.scalar_type() == at::kBFloat16 && w.dim() == 2 && w.stride(1) == 1 &&
+                w.size(0) % 128 == 0 && w.size(1) % 64 == 0, "expert_stack_tmaps: weight ", i, " must be bf16 [128a, 64b]");
+    TORCH_CHECK(pb::make_tmap_2d(&maps[i], w.data_ptr(), uint64_t(w.size(0)), uint64_t(w.size(1)), uint64_t(w.stride(0)), 128, 2),
+                "expert_stack_tmaps: cuTensorMapEncodeTiled failed");
+  }
+  TORCH_CHECK(attn.is_cuda() && attn.scalar_type() == at::kBFloat16 && attn.dim() == 2 && attn.size(0) == 64 &&
+              attn.is_contiguous(), "expert_stack_tmaps: attn must be bf16 [64, Hq * D]");
+  TORCH_CHECK(pb::make_tmap_2d(&maps[n - 1], attn.data_ptr(), 64, uint64_t(attn.size(1)), uint64_t(attn.stride(0)), 64, 2),
+              "expert_stack_tmaps: cuTensorMapEncodeTiled failed");
+  // cudaMalloc'ed storage is 256-byte aligned, which covers the 64-byte alignment a tensor map needs
+  return host.to(attn.device());
+}
+
+int64_t expert_stack_grid() { return pb::expert_stack_grid(); }
+
+void expert_stack_run(const Tensor& tmaps, int64_t M, int64_t H, int64_t I, int64_t Hq, int64_t D, int64_t A,
+                      int64_t n_layers, int64_t step_begin, int64_t step_end, int64_t att_splits, double eps,
+                      double dt, double sm_scale, const Tensor& in_scale, const Tensor& post_scale,
+                      const Tensor& gate_in, const Tensor& gate_post, const Tensor& qkv_bias, const Tensor& gu_bias,
+                      const Tensor& fin_scale, const Tensor& out_bias, const Tensor& w_in, const Tensor& b_in,
+                      const Tensor& w_out, const Tensor& k_pool, const Tensor& v_pool, const Tensor& kv_ptr,
+                      const Tensor& kv_len, const Tensor& pos, const Tensor& cos_sin, const Tensor& x0, Tensor& out,
+                      Tensor& scratch_f32, Tensor& attn, Tensor& barrier, const OptT& trace) {
+  pb::ExpertStackParams p;
+  p.M = int(M); p.H = int(H); p.I = int(I); p.Hq = int(Hq); p.D = int(D); p.A = int(A);
+  p.n_layers = int(n_layers); p.step_begin = int(step_begin); p.step_end = int(step_end);
+  p.att_splits = int(att_splits);
+  p.eps = float(eps); p.dt = float(dt); p.sm_scale = float(sm_scale);
+  TORCH_CHECK(tmaps.is_cuda() && tmaps.scalar_type() == at::kByte && tmaps.is_contiguous() &&
+              tmaps.numel() == int64_t((n_layers * 4 + 1) * sizeof(CUtensorMap)), "expert_stack_run: tmaps");
+  p.tmaps = reinterpret_cast<const CUtensorMap*>(tmaps.data_ptr());
+  const int64_t SL = step_end * n_layers, Nqkv = (Hq + 2) * D;
+  const auto vec = [](const Tensor& t, int64_t min_numel, const char* name) {
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kFloat && t.is_contiguous() && t.numel() >= min_numel,
+                "expert_stack_run: ", name, " must be a contiguous CUDA fp32 tensor of at least ", min_numel, " elements");
+    return reinterpret_cast<const float*>(t.data_ptr());
+  };
+  p.in_scale = vec(in_scale, SL * H, "in_scale"); p.post_scale = vec(post_scale, SL * H, "post_scale");
+  p.gate_in = vec(gate_in, SL * H, "gate_in"); p.gate_post = vec(gate_post, SL * H, "gate_post");
+  p.qkv_bias = vec(qkv_bias, SL * Nqkv, "qkv_bias"); p.gu_bias = vec(gu_bias, SL * 2 * I, "gu_bias");
+  p.fin_scale = vec(fin_scale, step_end * H, "fin_scale"); p.out_bias = vec(out_bias, step_end * A, "out_bias");
+  TORCH_CHECK(w_in.is_contiguous() && w_in.numel() == H * A && b_in.numel() == H && w_out.is_contiguous() &&
+              w_out.numel() == A * H, "expert_stack_run: input / output projection shapes");
+  p.w_in = bf(w_in); p.b_in = bf(b_in); p.w_out = bf(w_out);
+  TORCH_CHECK(k_pool.dim() == 4 && k_pool.size(2) == 1 && k_pool.size(3) == D && k_pool.stride(3) == 1 &&
+              k_pool.size(0) >= n_layers && k_pool.strides() == v_pool.strides(), "expert_stack_run: pools must be [layers, slots, 1, D]");
+  p.k_pool = bf(k_pool); p.v_pool = bf(v_pool);
+  p.pool_layer_stride = k_pool.stride(0); p.pool_row_stride = k_pool.stride(1);
+  TORCH_CHECK(p.pool_row_stride % 8 == 0 && p.pool_layer_stride % 8 == 0, "expert_stack_run: pool strides");
+  p.kv_ptr = i32(OptT(kv_ptr)); p.kv_len = i32(OptT(kv_len)); p.pos = i32(OptT(pos));
+  TORCH_CHECK(pos.numel() >= M && cos_sin.is_contiguous() && cos_sin.size(-1) == D, "expert_stack_run: pos / cos_sin");
+  p.cos_sin = f32(OptT(cos_sin));
+  TORCH_CHECK(x0.is_contiguous() && x0.numel() >= M * A && out.is_contiguous() && out.numel() >= M * A, "expert_stack_run: x0 / out");
+  p.x0 = bf(x0); p.out = bfm(out);
+  // fp32 scratch: x_t | h | acc_qkv | acc_gu | ss | part_o | part_ml, every block 64 rows
+  const int64_t need = 64 * (A + H + Nqkv + 2 * I + 2) + Hq * att_splits * 64 * (D + 2);
+  TORCH_CHECK(scratch_f32.is_cuda() && scratch_f32.scalar_type() == at::kFloat && scratch_f32.is_contiguous() &&
+              scratch_f32.numel() >= need, "expert_stack_run: scratch_f32 needs ", need, " floats");
+  float* s = reinterpret_cast<float*>(scratch_f32.data_ptr());
+  p.x_t = s; s += 64 * A;
+  p.h = s; s += 64 * H;
+  p.acc_qkv = s; s += 64 * Nqkv;
+  p.acc_gu = s; s += 64 * 2 * I;
+  p.ss = s; s += 128;
+  p.part_o = s; s += Hq * att_splits * 64 * D;
+  p.part_ml = s;
+  TORCH_CHECK(attn.is_cuda() && attn.scalar_type() == at::kBFloat16 && attn.is_contiguous() && attn.numel() == 64 * Hq * D,
+              "expert_stack_run: attn must be bf16 [64, Hq * D]");
+  p.attn = bfm(attn);
+  TORCH_CHECK(barrier.is_cuda() && barrier.scalar_type() == at::kInt && barrier.numel() >= 1, "expert_stack_run: barrier");
+  p.barrier = reinterpret_cast<unsigned*>(barrier.data_ptr());
+  p.status = pb::kernel_status_ptr();
+  if (trace.has_value() && trace->defined()) {
+    TORCH_CHECK(trace->is_cuda() && trace->scalar_type() == at::kLong && trace->is_contiguous() &&
+                trace->numel() >= 64 * pb::expert_stack_grid(), "expert_stack_run: trace needs 64 int64 per CTA");
+    p.trace = reinterpret_cast<unsigned long long*>(trace->data_ptr());
+  }
+  check(pb::expert_stack_launch(p, cur_stream()), "expert_stack_launch");
+}
+
 }  // namespace
 
 void register_comm(pybind11::module_& m);
@@ -356,5 +447,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("set_gemm_2cta", [](int64_t mode) { pb::set_gemm_2cta(int(mode)); });
   m.def("gemm_2cta_launches", []() { return int64_t(pb::gemm_2cta_launches()); });
   m.def("pdl_enabled", [] { return pb::pdl_enabled(); });
+  m.def("expert_stack_tmaps", &expert_stack_tmaps);
+  m.def("expert_stack_grid", &expert_stack_grid);
+  m.def("expert_stack_run", &expert_stack_run, py::arg("tmaps"), py::arg("M"), py::arg("H"), py::arg("I"), py::arg("Hq"),
+        py::arg("D"), py::arg("A"), py::arg("n_layers"), py::arg("step_begin"), py::arg("step_end"), py::arg("att_splits"),
+        py::arg("eps"), py::arg("dt"), py::arg("sm_scale"), py::arg("in_scale"), py::arg("post_scale"), py::arg("gate_in"),
+        py::arg("gate_post"), py::arg("qkv_bias"), py::arg("gu_bias"), py::arg("fin_scale"), py::arg("out_bias"),
+        py::arg("w_in"), py::arg("b_in"), py::arg("w_out"), py::arg("k_pool"), py::arg("v_pool"), py::arg("kv_ptr"),
+        py::arg("kv_len"), py::arg("pos"), py::arg("cos_sin"), py::arg("x0"), py::arg("out"), py::arg("scratch_f32"),
+        py::arg("attn"), py::arg("barrier"), py::arg("trace") = py::none());
   register_comm(m);
 }

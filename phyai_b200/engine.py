@@ -136,6 +136,12 @@ class Engine:
             raise RuntimeError("Engine.step after close()")
         t0 = time.perf_counter()
         out = self.entry.step(request)
+        if self.device.type == "cuda":
+            # the step's sync point: a device wait that gave up (a late or lost peer) must surface here,
+            # with the channels reset, not as stale rows in the next step
+            from .parallel.health import check_step_status
+
+            check_step_status(what=f"{self.plugin_name}.step")
         if self._dumper is not None:
             self._dumper.flush()
         m = metrics()

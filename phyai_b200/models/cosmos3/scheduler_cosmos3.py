@@ -125,12 +125,28 @@ class _GuidanceMixin:
         self._peer = None
 
     def _peer_exchange(self):
+        """The guidance pair's peer group, or None when it cannot be had. Opening it is a collective, so the two
+        ranks agree on the outcome before either uses it: a rank whose mapping failed while its partner's
+        succeeded would otherwise call NCCL against a partner that waits in the peer kernel."""
         if self._peer is None and self.cfg_size == 2 and self.device.type == "cuda":
+            import logging
+
+            import torch.distributed as dist
+
+            pg = None
             try:
                 from ...parallel.symm import PeerGroup
 
-                self._peer = PeerGroup.for_axis(self.mesh, "cfg")
-            except Exception:
+                pg = PeerGroup.for_axis(self.mesh, "cfg")
+            except Exception as e:     # noqa: BLE001 - any failure means "use NCCL", but it is said out loud
+                logging.getLogger(__name__).warning("cfg peer exchange unavailable on this rank: %s", e)
+            ok = torch.tensor([1 if pg is not None else 0], dtype=torch.int32, device=self.device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.mesh.axis_group("cfg"))
+            if int(ok.item()) == 1:
+                self._peer = pg
+            else:
+                if pg is not None:
+                    pg._closed = True      # the partner never opened its side: drop the handle without the collective close
                 self._peer = False
         return self._peer or None
 

@@ -35,6 +35,7 @@ import torch
 from ... import ops
 from ...cache import KVCachePool
 from ...env import envs
+from ...ops.expert_stack import ExpertGeometry, ExpertStack
 from .modeling_pi05 import PI05Model
 
 
@@ -58,6 +59,8 @@ class PI05Plan:
     fold_norms = True
     #: run the first Euler step on a second stream under the prefix decoder (PHYAI_PI05_OVERLAP=0 turns it off)
     overlap_first_step = bool(envs.PHYAI_PI05_OVERLAP.get())
+    #: run the Euler loop as one persistent kernel (``csrc/expert_stack.cu``) where the geometry allows it
+    use_expert_kernel = bool(envs.PHYAI_PI05_EXPERT_KERNEL.get())
     _side_stream = None
 
     def __init__(self, model: PI05Model, *, max_batch_size: int = 1, num_images: int = 3,
@@ -154,6 +157,7 @@ class PI05Plan:
         self._prefix_splits_env = envs.PHYAI_PI05_PREFIX_SPLITS.get()
         self.prefix_splits = int(self._prefix_splits_env or (2 if B == 1 else 1))
         self._layout_key = None
+        self.stack: ExpertStack | None = None
 
     # ------------------------------------------------------------------ setup
     @torch.no_grad()
@@ -168,8 +172,52 @@ class PI05Plan:
         self.mod_post = [l.post_attention_layernorm.project_modulation(conds) for l in stack.layers]
         self.mod_final = stack.norm.project_modulation(conds)
         if self.fold_norms:
+            self._build_expert_kernel(stack)
             self._fold_modulation(stack)
             self._fold_prefix()
+
+    def _expert_geometry(self) -> ExpertGeometry:
+        cfg, e, t = self.cfg, self.cfg.expert, self.cfg.text
+        return ExpertGeometry(rows=self.Me, hidden=e.hidden_size, inter=e.intermediate_size, q_heads=t.num_attention_heads,
+                              head_dim=t.head_dim, action_dim=cfg.max_action_dim, layers=cfg.num_layers,
+                              steps=cfg.num_inference_steps)
+
+    def _build_expert_kernel(self, stack) -> None:
+        """Tables of the persistent expert kernel: the AdaRMS modulation of every (step, block) as fp32
+        column factors, branch gates and ``shift @ W^T`` biases; the weights stay as loaded (one copy)."""
+        self.stack = None
+        t = self.cfg.text
+        if not (self.use_expert_kernel and self.device.type == "cuda" and self.B == 1 and t.num_key_value_heads == 1
+                and self.suffix_extra == 0):
+            return
+        geo = self._expert_geometry()
+        if not ExpertStack.supports(geo, self.slab):
+            return
+        He, heads = geo.hidden, self.model.heads
+        st = ExpertStack(geo, device=self.device)
+        st.set_weights([(l.attn.qkv.weight, l.attn.o.weight, l.mlp.gate_up.weight, l.mlp.down.weight) for l in stack.layers])
+
+        def cols(mods, a, b):          # [layers][steps, 3He] -> [steps, layers, He]
+            return torch.stack([m[:, a:b].float() for m in mods], dim=1)
+
+        def biases(mods, weights):     # shift @ W^T -> [steps, layers, N]
+            return torch.stack([m[:, He:2 * He].float() @ w.float().t() for m, w in zip(mods, weights)], dim=1)
+
+        st.set_tables(in_scale=1.0 + cols(self.mod_in, 0, He), post_scale=1.0 + cols(self.mod_post, 0, He),
+                      gate_in=cols(self.mod_in, 2 * He, 3 * He), gate_post=cols(self.mod_post, 2 * He, 3 * He),
+                      qkv_bias=biases(self.mod_in, [l.attn.qkv.weight for l in stack.layers]),
+                      gu_bias=biases(self.mod_post, [l.mlp.gate_up.weight for l in stack.layers]),
+                      fin_scale=1.0 + self.mod_final[:, :He].float(),
+                      out_bias=self.mod_final[:, He:2 * He].float() @ heads.action_out_proj.weight.float().t()
+                      + heads.action_out_proj.bias.float()[None, :])
+        self.stack = st
+
+    def _run_expert_kernel(self, step_begin: int, step_end: int) -> None:
+        cfg, e, t, heads = self.cfg, self.cfg.expert, self.cfg.text, self.model.heads
+        self.stack.run(w_in=heads.action_in_proj.weight, b_in=heads.action_in_proj.bias, w_out=heads.action_out_proj.weight,
+                       k_pool=self.pool.k, v_pool=self.pool.v, kv_ptr=self.e_kvptr, kv_len=self.e_kvlen, pos=self.e_pos,
+                       cos_sin=self.cos_sin, x0=self.x_t, out=self.x_t, eps=e.rms_norm_eps, dt=self.dt,
+                       sm_scale=t.head_dim ** -0.5, step_begin=step_begin, step_end=step_end)
 
     def _fold_prefix(self) -> None:
         """Prefix decoder: Gemma RMSNorm weights (1 + w) folded into the QKV and gate/up weights (one
@@ -207,16 +255,20 @@ class PI05Plan:
 
         t = self.cfg.text
         Hq, Hkv, D = t.num_attention_heads, t.num_key_value_heads, t.head_dim
+        # with the persistent kernel serving the loop, only the first step (the one that may run on the
+        # second stream under the prefix decoder) still goes launch by launch: one folded copy, not one per step
+        keep = 1 if self.stack is not None else self.cfg.num_inference_steps
+        self.folded_steps = keep
         self.fold_qkv, self.fold_gate_up = [], []
         for li, layer in enumerate(stack.layers):
             # q / k head rows reordered for the rotating epilogue of the QKV GEMM. The first block of a
             # step keeps its norm kernel (nothing upstream accumulates its sums): plain weight, no bias.
             wq = ops.permute_rope_rows(layer.attn.qkv.weight, Hq, Hkv, D)
-            self.fold_qkv.append(fold(wq, self.mod_in[li]) if li > 0 else (wq, None))
-            self.fold_gate_up.append(fold(layer.mlp.gate_up.weight, self.mod_post[li]))
+            self.fold_qkv.append(fold(wq, self.mod_in[li][:keep]) if li > 0 else (wq, None))
+            self.fold_gate_up.append(fold(layer.mlp.gate_up.weight, self.mod_post[li][:keep]))
         self.rope_desc = self._rope_descs(self.e_q, self.e_pos, self.e_slots)
         heads = self.model.heads
-        self.fold_out = fold(heads.action_out_proj.weight, self.mod_final, heads.action_out_proj.bias)
+        self.fold_out = fold(heads.action_out_proj.weight, self.mod_final[:keep], heads.action_out_proj.bias)
         self.e_ss = torch.zeros(2, self.Me, dtype=torch.float32, device=self.device)
 
     def _rope_descs(self, q_out: torch.Tensor, pos: torch.Tensor, slots: torch.Tensor) -> list[torch.Tensor]:
@@ -377,7 +429,16 @@ class PI05Plan:
         q3, a3 = self.e_q.unflatten(1, (Hq, D)), self.e_attn.unflatten(1, (Hq, D))
         ss_in, ss_post = self.e_ss[0], self.e_ss[1]
         rms = (He, e.rms_norm_eps)
-        for i in (range(cfg.num_inference_steps) if steps is None else steps):
+        steps = list(range(cfg.num_inference_steps) if steps is None else steps)
+        if self.stack is not None and before_block is None and steps:
+            # the whole range in one persistent launch (the per-block hook needs launch boundaries)
+            if steps != list(range(steps[0], steps[-1] + 1)):
+                raise ValueError("the persistent expert kernel runs a contiguous range of Euler steps")
+            self._run_expert_kernel(steps[0], steps[-1] + 1)
+            steps = []
+        for i in steps:
+            if i >= self.folded_steps:
+                raise RuntimeError(f"Euler step {i} has no folded weights (only {self.folded_steps} kept)")
             ops.gemm(self.x_t, heads.action_in_proj.weight, h, bias=heads.action_in_proj.bias)
             for li, layer in enumerate(stack.layers):
                 kpool, vpool = self.pool.layer(li)

@@ -8,7 +8,8 @@ Backends: ``nccl`` / ``gloo`` (``torch.distributed``, plumbing and fallback) and
 on CUDA, ``peer`` — this repository's own kernels over IPC-mapped peer memory
 (one-shot all-reduce, CFG exchange), preferred for small messages because they
 avoid the NCCL launch path and are captured into CUDA graphs. The kernels that
-fuse a GEMM with its collective live in ``phyai_b200.parallel.fused``.
+fuse a GEMM with its collective are reached through ``phyai_b200.parallel.symm`` (``PeerStream.linear_reduce``,
+``ops.gemm(wait=...)``).
 
 Reference: phyai/src/phyai/parallel/__init__.py:78-249.
 """

@@ -19,11 +19,14 @@ from ..backend import Call, Op
 class PeerBackend:
     name = "peer"
     max_bytes = 4 << 20
+    #: every call is laid out as rows of this many bf16 values, so one slot geometry serves all shapes
+    COLS = 1024
 
     def __init__(self, mesh) -> None:
         self.mesh = mesh
         self._groups: dict[str, Any] = {}
-        self._streams: dict[tuple[str, int, int], Any] = {}
+        self._streams: dict[str, Any] = {}
+        self._failed: set[str] = set()
 
     @classmethod
     def create(cls, mesh) -> "PeerBackend | None":
@@ -35,6 +38,10 @@ class PeerBackend:
             return None
         return cls(mesh)
 
+    @property
+    def max_rows(self) -> int:
+        return -(-(self.max_bytes // 2) // self.COLS)
+
     def can_handle(self, call: Call) -> bool:
         if call.op is not Op.ALL_REDUCE or call.device_type != "cuda" or call.dtype != torch.bfloat16:
             return False
@@ -42,44 +49,68 @@ class PeerBackend:
             return False
         n = call.mesh.axis_size(call.axis)
         # decisions are cached per power-of-two size bucket, so the limit sits on a bucket edge
-        return 1 < n <= 8 and call.nbytes < self.max_bytes and call.mesh is self.mesh
+        if not (1 < n <= 8 and call.nbytes < self.max_bytes and call.mesh is self.mesh):
+            return False
+        # the stream is created here (every rank asks in the same order), so that a heap or channel
+        # shortage sends the call to the next backend instead of failing in the middle of a forward
+        return self._stream(call.axis) is not None
 
     def supports_capture(self) -> bool:
         return True
 
-    def _stream(self, axis: str, rows: int, cols: int):
-        key = (axis, rows, cols)
-        st = self._streams.get(key)
-        if st is None:
-            from ..symm import PeerGroup
+    def _open_group(self, axis: str):
+        from ..symm import PeerGroup
 
+        return PeerGroup.for_axis(self.mesh, axis, heap_bytes=256 << 20)
+
+    def _stream(self, axis: str):
+        """The one stream of an axis: ``max_rows x COLS`` slots, which every call up to ``max_bytes`` fits."""
+        st = self._streams.get(axis)
+        if st is not None or axis in self._failed:
+            return st
+        try:
             pg = self._groups.get(axis)
             if pg is None:
-                pg = PeerGroup.for_axis(self.mesh, axis, heap_bytes=256 << 20)
+                pg = self._open_group(axis)
                 self._groups[axis] = pg
-            st = pg.stream(f"ar:{rows}x{cols}", rows, cols)
-            self._streams[key] = st
+            st = pg.stream(f"ar:{axis}", self.max_rows, self.COLS)
+        except (MemoryError, RuntimeError) as e:
+            import logging
+
+            logging.getLogger(__name__).warning("peer backend unavailable on axis %r (%s): calls go to the next backend", axis, e)
+            self._failed.add(axis)
+            return None
+        self._streams[axis] = st
         return st
+
+    @classmethod
+    def flatten(cls, x: torch.Tensor) -> torch.Tensor:
+        """``x`` as rows of ``COLS`` values (a view when the size divides, else a zero-padded copy)."""
+        n = x.numel()
+        x = x.contiguous()
+        if n % cls.COLS == 0:
+            return x.view(-1, cls.COLS)
+        flat = x.new_zeros(-(-n // cls.COLS), cls.COLS)
+        flat.view(-1)[:n] = x.view(-1)
+        return flat
 
     def execute(self, call: Call, *tensors: torch.Tensor, **kw: Any):
         if kw.get("reduce", "sum") != "sum":
             raise NotImplementedError("peer backend reduces with sum only")
-        x = tensors[0].contiguous()
-        n = x.numel()
-        if n % 8:  # the kernels move 16-byte vectors: pad the tail
-            flat = x.new_zeros((n + 7) // 8, 8)
-            flat.view(-1)[:n] = x.view(-1)
-        else:
-            cols = x.shape[-1] if x.dim() > 1 and x.shape[-1] % 8 == 0 else 8
-            flat = x.view(-1, cols)
-        out = self._stream(call.axis, flat.shape[0], flat.shape[1]).all_reduce(flat)
-        return out.view(-1)[:n].view(x.shape)
+        x = tensors[0]
+        st = self._stream(call.axis)
+        if st is None:
+            raise RuntimeError(f"peer backend has no stream on axis {call.axis!r}")
+        flat = self.flatten(x)
+        out = st.all_reduce(flat)
+        return out.view(-1)[: x.numel()].view(x.shape)
 
     def close(self) -> None:
         for pg in self._groups.values():
             pg.close()
         self._groups.clear()
         self._streams.clear()
+        self._failed.clear()
 
 
 __all__ = ["PeerBackend"]

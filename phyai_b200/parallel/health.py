@@ -38,6 +38,41 @@ def raise_for_kernel_status(status: int | None = None, *, what: str = "step") ->
     raise RuntimeError(msg)
 
 
+def check_step_status(*, what: str = "step", force: bool = False) -> None:
+    """The per-step sync point of a serving loop: read the device status word where the step's outputs
+    leave the device anyway and turn a device-wait time-out into an exception BEFORE the next step runs
+    on stale data.
+
+    With peer groups open the ranks first agree on the worst status (one tiny all-reduce over each group),
+    so that either every rank raises or none does; on a non-zero status every rank resets the channel
+    state of its groups (:meth:`PeerGroup.reset_channels`, a collective) and raises. Without peer groups
+    nothing is read unless ``force`` (or ``PHYAI_CHECK_KERNEL_STATUS=1``) asks for it: single-GPU
+    kernels wait only on their own copies."""
+    import os
+
+    import torch
+
+    from .symm import PeerGroup
+
+    groups = PeerGroup.open_groups() if torch.cuda.is_available() else []
+    if not groups and not force and os.environ.get("PHYAI_CHECK_KERNEL_STATUS", "0") in ("0", "", "false", "off"):
+        return
+    from .. import ops
+
+    status = int(ops.kernel_status())
+    if groups:
+        import torch.distributed as dist
+
+        t = torch.tensor([status], dtype=torch.int32, device=groups[0].device)
+        for g in groups:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=g.group)
+        status = int(t.item())
+        if status != 0:
+            for g in groups:
+                g.reset_channels()
+    raise_for_kernel_status(status, what=what)
+
+
 class DictStore:
     """In-process stand-in for a TCPStore (tests, single-process runs)."""
 
@@ -122,4 +157,4 @@ class Heartbeat:
             raise PeerLostError(f"rank {self.rank}: no heartbeat from ranks {lost} within {deadline_s:.1f} s")
 
 
-__all__ = ["Heartbeat", "DictStore", "raise_for_kernel_status", "STATUS_TEXT"]
+__all__ = ["Heartbeat", "DictStore", "raise_for_kernel_status", "check_step_status", "STATUS_TEXT"]

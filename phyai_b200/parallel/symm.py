@@ -94,6 +94,21 @@ class PeerGroup:
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
 
+    @classmethod
+    def open_groups(cls) -> list["PeerGroup"]:
+        """Every peer group of this process that has not been closed."""
+        return [g for g in cls._registry.values() if not g._closed]
+
+    def reset_channels(self) -> None:
+        """Collective: bring every channel back to its initial state after a device wait gave up.
+
+        A consumer that timed out has already closed its call (counter cleared, epoch bumped), so an
+        arrival that lands afterwards would be counted for a later call. All ranks drain their streams,
+        meet on the host, clear their signal words, and meet again before anyone launches."""
+        self.sync()
+        self.slab[: self.sig_bytes].zero_()
+        self.sync()
+
     def close(self) -> None:
         if self._closed:
             return

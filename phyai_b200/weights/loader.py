@@ -6,10 +6,15 @@ the layers (reference protocol: phyai/src/phyai/weights/loader.py:174-318):
 * ``param.hf_keys``      ``{checkpoint_key: shard_id}`` (or a list of keys, shard_id None)
 * ``param.weight_loader`` ``loader(param, tensor, shard_id)`` (default: replicated copy)
 * ``param.optional``     missing keys are reported separately and never fail ``strict``
+* ``param.hf_alternatives`` the keys are alternative spellings of one tensor: at least one of them
+  must be present, the others are not reported as missing
 
-Parameters without ``hf_keys`` claim their dotted module path. After all shards
-are consumed every module's ``post_load()`` hook runs (quantisation fan-out,
-packed layouts, exponentiated Snake parameters ...).
+Parameters without ``hf_keys`` are looked up under their dotted module path but, as in the
+reference (which skips them), never count as missing. ``remap`` is a callable (``None`` drops the
+key) or a dict of ordered substring rewrites (reference loader.py:87-110); ``source`` is a
+checkpoint folder, a hub repo id, one safetensors file or an iterable of files. After all shards
+are consumed every module's ``post_load()`` hook runs (quantisation fan-out, packed layouts,
+exponentiated Snake parameters ...).
 """
 
 from __future__ import annotations
@@ -53,11 +58,34 @@ def _apply_remap(remap: Remap, key: str) -> str | None:
         return key
     if callable(remap):
         return remap(key)
-    return remap.get(key, key)
+    if not isinstance(remap, Mapping):
+        raise TypeError(f"remap must be callable, a dict or None; got {type(remap).__name__}")
+    for src, dst in remap.items():          # ordered substring rewrites; a None target drops the key
+        if src in key:
+            if dst is None:
+                return None
+            key = key.replace(src, dst)
+    return key
+
+
+def _resolve_source(source: "str | Path | Iterable[str | Path]", stem: str) -> tuple[list[Path], str]:
+    """Shard files of ``source`` (folder / repo id / one file / iterable of files) and a label for the log."""
+    if isinstance(source, (str, Path)):
+        p = Path(source).expanduser()
+        if p.is_file():
+            return [p], p.name
+        directory = resolve_checkpoint(source)
+        return find_safetensors(directory, stem=stem), str(directory)
+    files = [Path(f) for f in source]
+    if not files:
+        raise FileNotFoundError("load_pretrained: empty list of safetensors files")
+    return files, "weights"
 
 
 def build_index(model: torch.nn.Module) -> tuple[dict[str, tuple[torch.nn.Parameter, object, str]], set[str]]:
-    """``checkpoint_key -> (param, shard_id, param_name)`` plus the set of optional keys."""
+    """``checkpoint_key -> (param, shard_id, param_name)`` plus the set of keys whose absence is not an error
+    by itself (optional parameters, parameters without ``hf_keys``, alternative spellings: for the latter
+    :func:`load_pretrained` still wants one spelling per parameter)."""
     index: dict[str, tuple[torch.nn.Parameter, object, str]] = {}
     optional: set[str] = set()
     tensors: Iterable[tuple[str, torch.Tensor]] = list(model.named_parameters()) + [
@@ -74,17 +102,16 @@ def build_index(model: torch.nn.Module) -> tuple[dict[str, tuple[torch.nn.Parame
             if k in index and index[k][0] is not p:
                 raise ValueError(f"checkpoint key {k!r} is claimed by both {index[k][2]!r} and {name!r}")
             index[k] = (p, sid, name)
-            if getattr(p, "optional", False) or getattr(p, "hf_alternatives", False):
+            if keys is None or getattr(p, "optional", False) or getattr(p, "hf_alternatives", False):
                 optional.add(k)
     return index, optional
 
 
-def load_pretrained(model: torch.nn.Module, source: str | Path, *, remap: Remap = None, strict: bool = True,
-                    stem: str = "model", progress: bool = False) -> LoadReport:
+def load_pretrained(model: torch.nn.Module, source: "str | Path | Iterable[str | Path]", *, remap: Remap = None,
+                    strict: bool = True, stem: str = "model", progress: bool = False) -> LoadReport:
     from safetensors import safe_open
 
-    directory = resolve_checkpoint(source)
-    files = find_safetensors(directory, stem=stem)
+    files, directory = _resolve_source(source, stem)
     index, optional = build_index(model)
     report = LoadReport()
     seen: set[str] = set()
@@ -119,9 +146,18 @@ def load_pretrained(model: torch.nn.Module, source: str | Path, *, remap: Remap 
                         raise type(e)(f"while loading {raw!r} -> {key!r}: {e}") from e
                     seen.add(key)
                     report.loaded.append(key)
+    # alternative spellings: a parameter none of whose keys showed up is missing after all
+    unmet: set[str] = set()
+    by_param: dict[int, list[str]] = {}
+    for k, (p, _, _) in index.items():
+        if getattr(p, "hf_alternatives", False) and not getattr(p, "optional", False):
+            by_param.setdefault(id(p), []).append(k)
+    for ks in by_param.values():
+        if not any(k in seen for k in ks):
+            unmet.add(ks[0])
     for k in index:
         if k not in seen:
-            (report.optional_missing if k in optional else report.missing).append(k)
+            (report.missing if k in unmet or k not in optional else report.optional_missing).append(k)
     this_rank_log(logger, logging.INFO, "%s: %s", directory, report.summary())
     if strict and not report.ok:
         raise RuntimeError(f"strict load failed: missing={report.missing[:8]} unexpected={report.unexpected[:8]} "

@@ -1,0 +1,96 @@
+"""Host-side bookkeeping of the peer-memory all-reduce backend and of the per-step status check (no GPU)."""
+
+import pytest
+import torch
+
+from phyai_b200.parallel.backend import Call, Mode, Op
+from phyai_b200.parallel.backends.peer import PeerBackend
+from phyai_b200.parallel.exceptions import CommTimeoutError
+
+
+class _FakeStream:
+    def __init__(self, rows, cols):
+        self.max_rows, self.max_cols, self.calls = rows, cols, []
+
+    def all_reduce(self, flat):
+        assert flat.dim() == 2 and flat.shape[1] == self.max_cols and flat.shape[0] <= self.max_rows
+        self.calls.append(tuple(flat.shape))
+        return flat * 2          # "sum over two ranks holding the same tensor"
+
+
+class _FakeGroup:
+    def __init__(self, heap_bytes):
+        self.heap_bytes, self.used, self.streams, self.closed = heap_bytes, 0, {}, False
+
+    def stream(self, name, rows, cols):
+        if name not in self.streams:
+            need = 2 * 2 * rows * cols * 2          # two parities x two ranks x bf16
+            if self.used + need > self.heap_bytes:
+                raise MemoryError("symmetric heap exhausted")
+            self.used += need
+            self.streams[name] = _FakeStream(rows, cols)
+        return self.streams[name]
+
+    def close(self):
+        self.closed = True
+
+
+class _Mesh:
+    device_type = "cuda"
+
+    def axis_size(self, axis):
+        return 2
+
+
+def _call(mesh, x, axis="tp"):
+    return Call(op=Op.ALL_REDUCE, axis=axis, mesh=mesh, dtype=x.dtype, device_type="cuda", nbytes=x.numel() * 2, mode=Mode.EAGER, extra=("sum",))
+
+
+def test_fifty_shapes_share_one_stream(monkeypatch):
+    mesh = _Mesh()
+    be = PeerBackend(mesh)
+    group = _FakeGroup(256 << 20)
+    monkeypatch.setattr(be, "_open_group", lambda axis: group)
+    for L in range(1, 51):                      # one distinct (768 + L) x 2048 prefix shape per prompt length
+        x = torch.randn(7 + L, 264, dtype=torch.float32).bfloat16()
+        call = _call(mesh, x)
+        assert be.can_handle(call)
+        out = be.execute(call, x)
+        assert out.shape == x.shape and torch.equal(out, x * 2)
+    assert len(group.streams) == 1              # slots are sized once, for max_bytes
+    st = next(iter(group.streams.values()))
+    assert len(st.calls) == 50 and group.used == 2 * 2 * be.max_rows * be.COLS * 2
+    be.close()
+    assert group.closed
+
+
+def test_exhausted_heap_declines_instead_of_raising(monkeypatch):
+    mesh = _Mesh()
+    be = PeerBackend(mesh)
+    monkeypatch.setattr(be, "_open_group", lambda axis: _FakeGroup(1 << 20))   # too small for the stream
+    x = torch.zeros(64, 1024, dtype=torch.bfloat16)
+    assert not be.can_handle(_call(mesh, x))    # the dispatcher moves on to NCCL
+    assert not be.can_handle(_call(mesh, x))    # and the failure is remembered, not retried per call
+    with pytest.raises(RuntimeError):
+        be.execute(_call(mesh, x), x)
+
+
+def test_flatten_pads_the_tail():
+    x = torch.arange(3000, dtype=torch.float32).bfloat16()
+    flat = PeerBackend.flatten(x)
+    assert flat.shape == (3, 1024) and torch.equal(flat.view(-1)[:3000], x) and float(flat.view(-1)[3000:].abs().sum()) == 0
+    y = torch.zeros(4, 512, dtype=torch.bfloat16)
+    assert PeerBackend.flatten(y).data_ptr() == y.data_ptr()      # a view when the size divides
+
+
+def test_step_status_check_raises_and_is_silent_when_clean(monkeypatch):
+    from phyai_b200 import ops
+    from phyai_b200.parallel import health
+
+    seen = iter([0, 4, 3])
+    monkeypatch.setattr(ops, "kernel_status", lambda: next(seen))
+    health.check_step_status(force=True)                       # 0: nothing
+    with pytest.raises(CommTimeoutError):
+        health.check_step_status(what="cosmos3.step", force=True)
+    with pytest.raises(RuntimeError):
+        health.check_step_status(force=True)

@@ -141,3 +141,63 @@ def test_synthetic_checkpoint_roundtrip(tmp_path):
     pre = "paligemma_with_expert.paligemma.model.language_model.layers.0"
     assert torch.equal(l0.mlp.gate_up.weight.data[0::2], state[f"{pre}.mlp.gate_proj.weight"])
     assert torch.equal(l0.attn.qkv.weight.data[-32:], state[f"{pre}.self_attn.v_proj.weight"])
+
+
+# ---- the loader's public contract, as the reference states it (phyai/tests/weights/test_loader.py)
+def _two_param_model():
+    m = nn.Module()
+    m.a = nn.Parameter(torch.zeros(2, 3), requires_grad=False)
+    m.a.hf_keys = {"model.layers.0.a.weight": None}
+    m.b = nn.Parameter(torch.zeros(4), requires_grad=False)      # no hf_keys: never "missing"
+    return m
+
+
+def test_dict_remap_is_an_ordered_substring_rewrite(tmp_path):
+    from safetensors.torch import save_file
+
+    from phyai_b200.weights.loader import load_pretrained
+
+    f = tmp_path / "model.safetensors"
+    save_file({"transformer.h.0.a.weight": torch.ones(2, 3), "transformer.drop.me": torch.zeros(1)}, str(f))
+    m = _two_param_model()
+    rep = load_pretrained(m, tmp_path, remap={"transformer.": "model.", ".h.": ".layers.", "drop.me": None})
+    assert rep.ok and rep.loaded == ["model.layers.0.a.weight"] and rep.dropped == ["transformer.drop.me"]
+    assert torch.equal(m.a, torch.ones(2, 3)) and "b" in rep.optional_missing
+
+
+def test_source_may_be_one_file_or_a_list_of_files(tmp_path):
+    from safetensors.torch import save_file
+
+    from phyai_b200.weights.loader import load_pretrained
+
+    f1, f2 = tmp_path / "part1.safetensors", tmp_path / "part2.safetensors"
+    save_file({"model.layers.0.a.weight": torch.full((2, 3), 2.0)}, str(f1))
+    save_file({"b": torch.full((4,), 3.0)}, str(f2))
+    m = _two_param_model()
+    assert load_pretrained(m, f1).ok and float(m.a[0, 0]) == 2.0
+    m = _two_param_model()
+    rep = load_pretrained(m, [f1, f2])
+    assert rep.ok and float(m.b[0]) == 3.0 and not rep.optional_missing
+
+
+def test_alternative_spellings_need_one_hit(tmp_path):
+    from safetensors.torch import save_file
+
+    from phyai_b200.weights.loader import load_pretrained
+
+    def model():
+        m = nn.Module()
+        m.w = nn.Parameter(torch.zeros(3), requires_grad=False)
+        m.w.hf_keys = {"conv.weight": None, "conv.parametrizations.weight.original1": None}
+        m.w.hf_alternatives = True
+        return m
+
+    save_file({"conv.parametrizations.weight.original1": torch.ones(3)}, str(tmp_path / "model.safetensors"))
+    m = model()
+    rep = load_pretrained(m, tmp_path)
+    assert rep.ok and rep.optional_missing == ["conv.weight"] and float(m.w[0]) == 1.0
+    other = tmp_path / "empty"
+    other.mkdir()
+    save_file({"unrelated": torch.ones(1)}, str(other / "model.safetensors"))
+    with pytest.raises(RuntimeError):
+        load_pretrained(model(), other, remap=lambda k: None if k == "unrelated" else k)

@@ -27,18 +27,29 @@ def test_matches_the_torch_facing_op_twice_in_a_row(rows, cols):
     x = torch.randn(rows, cols, device="cuda", generator=g).bfloat16()
     w = (torch.randn(cols, device="cuda", generator=g) * 0.2 + 1.0).bfloat16()
     stream = torch.cuda.current_stream().cuda_stream
+    # first contact loads the kernels' module and resolves the scratch symbol (the driver may take memory for that once)
+    warm = torch.zeros_like(x)
+    assert fn(x.data_ptr(), warm.data_ptr(), w.data_ptr(), torch.empty_like(x).data_ptr(), rows, cols, 1e-6, stream) == 0
     for call in range(2):       # the second call reuses the scratch the first one dirtied
         r = torch.randn(rows, cols, device="cuda", generator=g).bfloat16()
         r_new, r_old = r.clone(), r.clone()
         y_new = torch.empty_like(x)
-        before = torch.cuda.memory_allocated()
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()          # the driver's view: a cudaMalloc inside the call would show here
+        held_before = torch.cuda.memory_allocated()
         rc = fn(x.data_ptr(), r_new.data_ptr(), w.data_ptr(), y_new.data_ptr(), rows, cols, 1e-6, stream)
-        assert rc == 0 and torch.cuda.memory_allocated() == before
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        assert rc == 0 and torch.cuda.memory_allocated() == held_before and free_after == free_before
         y_old = ops.norm(x, "rms", weight=w, residual=r_old, eps=1e-6)
         torch.cuda.synchronize()
         assert torch.equal(r_new, r_old), call                                  # the bf16 residual sum is exact either way
-        scale = y_old.float().abs().max().item()
-        assert (y_new.float() - y_old.float()).abs().max().item() <= 1e-2 * scale, call
+        torch.testing.assert_close(y_new.float(), y_old.float(), atol=2e-2, rtol=2e-2)
+        # and against the plain fp32 statement of the op
+        h = (x.float() + r.float()).bfloat16().float()
+        y_ref = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()
+        torch.testing.assert_close(r_new.float(), h, atol=0, rtol=0)
+        torch.testing.assert_close(y_new.float(), y_ref, atol=2e-2, rtol=2e-2)
     assert ops.kernel_status() == 0
 
 
