@@ -15,8 +15,14 @@ Two measurements per run:
 * ``e2e``: the same call fed from pinned host memory, including the host->device
   copies of that step's inputs and the device->host read of the action chunk.
 
+A second block, ``cosmos3``, rides on the same JSON line: one guided denoise step of the
+Cosmos3-Super geometry (7040 video + 512 text tokens, 40 blocks, guidance 7.0) over the N GPUs
+of the run as a CFG x TP mesh (1: cfg1 x tp1, 2: cfg1 x tp2, 4: cfg1 x tp4, 8: cfg2 x tp4), i.e.
+strong scaling of a fixed request, timed on the device between consecutive sampler updates,
+max over ranks (``benchmarks/bench_cosmos3.py`` holds the measurement). ``--no-cosmos3`` skips it.
+
 ``--impl reference`` runs the unmodified reference package installed under
-``baseline/_ref`` through its own ``Engine`` with the same request.
+``baseline/_ref`` through its own ``Engine`` / schedulers with the same requests.
 """
 
 from __future__ import annotations
@@ -43,7 +49,33 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--lang-len", type=int, default=200, help="real prompt tokens per robot")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-cosmos3", action="store_true", help="skip the Cosmos3 TP / CFG block")
+    ap.add_argument("--cosmos3-model", default="super", help="geometry of the Cosmos3 block (super | nano | small)")
+    ap.add_argument("--cosmos3-steps", type=int, default=6)
+    ap.add_argument("--cosmos3-warmup", type=int, default=3)
     return ap.parse_args()
+
+
+COSMOS3_LAYOUT = {1: (1, 1), 2: (1, 2), 4: (1, 4), 8: (2, 4)}   # n_gpus -> (cfg, tp)
+
+
+def cosmos3_block(args: argparse.Namespace) -> dict:
+    """The Cosmos3 denoise step of this run's arm over all N GPUs; a failure is reported, not raised."""
+    import argparse as _ap
+
+    if args.gpus not in COSMOS3_LAYOUT:
+        return {"skipped": f"no CFG x TP layout for {args.gpus} GPUs (have {sorted(COSMOS3_LAYOUT)})"}
+    try:
+        from benchmarks.bench_cosmos3 import run_block
+
+        cfg, tp = COSMOS3_LAYOUT[args.gpus]
+        ns = _ap.Namespace(model=args.cosmos3_model, tp=tp, cfg=cfg, steps=args.cosmos3_steps, warmup=max(args.cosmos3_warmup, 3),
+                           impl=args.impl, policy=False, batch=1, layers=0)
+        rec = run_block(ns, keep_process_group=True)
+        rec["scaling"] = "strong"
+        return rec
+    except Exception as e:  # noqa: BLE001 - the headline line must still be printed
+        return {"error": f"{type(e).__name__}: {e}".replace("\n", " ")[:300]}
 
 
 def percentile(xs: list[float], q: float) -> float:
@@ -127,6 +159,14 @@ def run(args: argparse.Namespace) -> dict:
     torch.cuda.set_device(local_rank)
     device = f"cuda:{local_rank}"
     N = args.gpus
+    if N > 1 and not dist.is_initialized():
+        # one process group for the whole run: the engines and the Cosmos3 block find it initialised and leave it alone
+        if args.impl == "reference":
+            dist.init_process_group("nccl", device_id=torch.device(device))
+        else:
+            from phyai_b200.parallel.dist import init_dist
+
+            init_dist(N, "cuda")
 
     if args.impl == "reference":
         sys.path.insert(0, str(ROOT / "baseline" / "_ref"))
@@ -226,6 +266,11 @@ def run(args: argparse.Namespace) -> dict:
     p50, p99, mean, e50, e99 = (float(v) for v in stats.tolist())
     h2d = sum(t.numel() * t.element_size() for t in host)
     d2h = N * 50 * 32 * 2
+    last = step_dev().float()
+    finite = bool(torch.isfinite(last).all().item())
+    checksum = float(last.abs().mean().item())
+    if not finite:
+        raise RuntimeError("the action chunk holds non-finite values")
     result = {
         "metric": "pi05_action_chunk_latency_p50_ms", "value": round(p50, 4), "unit": "ms", "n_gpus": N,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(mean, 4),
@@ -244,8 +289,16 @@ def run(args: argparse.Namespace) -> dict:
         "gpu_launches": int(per_step_launches * args.steps),
         "gpu_launches_per_step": int(per_step_launches),
         "timed_region_s": round(region_s, 3),
+        "output": {"finite": finite, "abs_mean": round(checksum, 6)},
     }
     engine.close()
+    del engine, req_dev, dev_in, flush
+    torch.cuda.empty_cache()
+    if not args.no_cosmos3:
+        result["cosmos3"] = cosmos3_block(args)
+    if N > 1 and dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
     return result if rank == 0 else {}
 
 

@@ -282,6 +282,30 @@ void axpy(Tensor& x, const Tensor& v, double dt) {
         "axpy_launch");
 }
 
+Tensor gdn_decode(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& g, const Tensor& beta,
+                  Tensor& state_pool, const Tensor& state_indices, double scale, bool l2norm) {
+  TORCH_CHECK(q.dim() == 3 && k.sizes() == q.sizes() && v.dim() == 3 && v.size(0) == q.size(0) && v.size(1) == q.size(1),
+              "gdn_decode: q, k [B, H, Dk], v [B, H, Dv]");
+  const auto dt = q.scalar_type();
+  TORCH_CHECK((dt == at::kBFloat16 || dt == at::kFloat) && k.scalar_type() == dt && v.scalar_type() == dt &&
+              g.scalar_type() == dt && beta.scalar_type() == dt, "gdn_decode: inputs must all be fp32 or all bf16");
+  TORCH_CHECK(q.is_cuda() && q.is_contiguous() && k.is_contiguous() && v.is_contiguous() && g.is_contiguous() &&
+              beta.is_contiguous(), "gdn_decode: contiguous CUDA inputs");
+  const int B = int(q.size(0)), H = int(q.size(1)), Dk = int(q.size(2)), Dv = int(v.size(2));
+  TORCH_CHECK(g.numel() == int64_t(B) * H && beta.numel() == int64_t(B) * H, "gdn_decode: g, beta [B, H]");
+  TORCH_CHECK(state_pool.is_cuda() && state_pool.scalar_type() == at::kFloat && state_pool.is_contiguous() &&
+              state_pool.dim() == 4 && state_pool.size(1) == H && state_pool.size(2) == Dk && state_pool.size(3) == Dv,
+              "gdn_decode: state_pool must be fp32 [slots, H, Dk, Dv]");
+  TORCH_CHECK(state_indices.is_cuda() && state_indices.scalar_type() == at::kLong && state_indices.numel() == B,
+              "gdn_decode: state_indices int64 [B]");
+  Tensor out = at::empty_like(v);
+  check(pb::gdn_decode_launch(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), dt == at::kBFloat16,
+                              reinterpret_cast<float*>(state_pool.data_ptr()), i64(OptT(state_indices)), out.data_ptr(),
+                              dt == at::kBFloat16, B, H, Dk, Dv, float(scale), l2norm ? 1 : 0, cur_stream()),
+        "gdn_decode_launch");
+  return out;
+}
+
 void cfg_combine(const Tensor& cond, const Tensor& uncond, double g, const OptT& out,
                  const OptT& x_fp32, double dt) {
   TORCH_CHECK(cond.is_contiguous() && uncond.is_contiguous() && cond.numel() == uncond.numel(), "cfg_combine: layout");
@@ -339,7 +363,7 @@ void expert_stack_run(const Tensor& tmaps, int64_t M, int64_t H, int64_t I, int6
                       const Tensor& fin_scale, const Tensor& out_bias, const Tensor& w_in, const Tensor& b_in,
                       const Tensor& w_out, const Tensor& k_pool, const Tensor& v_pool, const Tensor& kv_ptr,
                       const Tensor& kv_len, const Tensor& pos, const Tensor& cos_sin, const Tensor& x0, Tensor& out,
-                      Tensor& scratch_f32, Tensor& attn, Tensor& barrier, const OptT& trace) {
+                      Tensor& scratch_f32, Tensor& attn, Tensor& barrier, const OptT& trace, int64_t debug) {
   pb::ExpertStackParams p;
   p.M = int(M); p.H = int(H); p.I = int(I); p.Hq = int(Hq); p.D = int(D); p.A = int(A);
   p.n_layers = int(n_layers); p.step_begin = int(step_begin); p.step_end = int(step_end);
@@ -394,6 +418,7 @@ void expert_stack_run(const Tensor& tmaps, int64_t M, int64_t H, int64_t I, int6
                 trace->numel() >= 64 * pb::expert_stack_grid(), "expert_stack_run: trace needs 64 int64 per CTA");
     p.trace = reinterpret_cast<unsigned long long*>(trace->data_ptr());
   }
+  p.debug = int(debug);
   check(pb::expert_stack_launch(p, cur_stream()), "expert_stack_launch");
 }
 
@@ -440,6 +465,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("out") = py::none(), py::arg("x_fp32") = py::none(), py::arg("dt") = 0.0);
   m.def("scatter_rows", &scatter_rows, py::arg("src"), py::arg("dst"), py::arg("rows") = py::none());
   m.def("quant_fp8", &quant_fp8);
+  m.def("gdn_decode", &gdn_decode, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("g"), py::arg("beta"),
+        py::arg("state_pool"), py::arg("state_indices"), py::arg("scale"), py::arg("l2norm") = true);
   m.def("kernel_status", [] { return pb::read_and_clear_kernel_status(); });
   m.def("launch_counter", [] { return pb::launch_counter(); });
   m.def("reset_launch_counter", [] { pb::reset_launch_counter(); });
@@ -455,6 +482,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("gate_post"), py::arg("qkv_bias"), py::arg("gu_bias"), py::arg("fin_scale"), py::arg("out_bias"),
         py::arg("w_in"), py::arg("b_in"), py::arg("w_out"), py::arg("k_pool"), py::arg("v_pool"), py::arg("kv_ptr"),
         py::arg("kv_len"), py::arg("pos"), py::arg("cos_sin"), py::arg("x0"), py::arg("out"), py::arg("scratch_f32"),
-        py::arg("attn"), py::arg("barrier"), py::arg("trace") = py::none());
+        py::arg("attn"), py::arg("barrier"), py::arg("trace") = py::none(), py::arg("debug") = 0);
   register_comm(m);
 }

@@ -118,6 +118,291 @@ __device__ __forceinline__ void pair_range(const Geo& g, int cta, int G, int& p0
   p1 = int((long long)total * (cta + 1) / G);
 }
 
+
+// ------------------------------------------------------------------ worker routines
+// The loaders below are separate functions on purpose: inlined into the kernel they share its register
+// budget (168 per thread at 320 threads), a batch of loads gets spilled as it is issued, and a spilled load
+// has to arrive before the spill can store it: the batch degenerates into one L2 round trip per load.
+// As functions of their own each has room to keep a whole batch in flight.
+struct WCtx {
+  const ExpertStackParams* p;
+  int cta, G, wtid, lane, M, H, Nqkv, N2I;
+  uint32_t sA;           // shared-memory address of the phase-private region
+  float inv_H;
+};
+
+// Thread mapping of the two activation loaders: a worker owns one 4-column group (c4 = wtid & 15) of rows
+// r0, r0 + 16, r0 + 32, r0 + 48 (r0 = wtid >> 4) in every K block of the CTA, so the index arithmetic is a few
+// adds per element (no division by run-time values: eight warps per SM leave ~1000 instructions per
+// microsecond per warp, and a software division costs a hundred cycles of dependent latency).
+
+// activation operand = rows of h times a per-column factor (bf16, swizzled K-major blocks, one per pair);
+// optionally the row sums of squares of the K blocks of weight tile 0 (each K block exactly once per grid)
+__device__ __noinline__ void es_load_h(const WCtx& c, int kbs, int p0, int p1, const float* scale, float* ss) {
+  constexpr int UP = 4;                       // pairs per batch of loads
+  const ExpertStackParams& p = *c.p;
+  const int c4 = c.wtid & 15, r0 = c.wtid >> 4, np = p1 - p0;
+  int kb = p0 % kbs, nt = p0 / kbs;
+  const float* hrow[4];
+  uint32_t soff[4];
+  bool ok[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int m = r0 + 16 * j;
+    ok[j] = m < c.M;
+    hrow[j] = p.h + size_t(ok[j] ? m : 0) * c.H + c4 * 4;
+    soff[j] = c.sA + sw64(m, c4 * 4);
+  }
+  for (int pr = 0; pr < np; pr += UP) {
+    float4 hv[UP][4], sc[UP];
+    bool t0[UP];
+#pragma unroll
+    for (int b = 0; b < UP; ++b) {
+      t0[b] = false;
+      if (pr + b < np) {
+        const int k = kb * 64;
+        t0[b] = nt == 0;
+        sc[b] = __ldg(reinterpret_cast<const float4*>(scale + k + c4 * 4));
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          hv[b][j] = ok[j] ? __ldcg(reinterpret_cast<const float4*>(hrow[j] + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (++kb == kbs) { kb = 0; ++nt; }
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < UP; ++b) {
+      if (pr + b < np) {
+        const uint32_t blk = uint32_t(pr + b) * kActBlk;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float4 h4 = hv[b][j];
+          if (ok[j]) st_shared_v2(blk + soff[j], pack_bf16(h4.x * sc[b].x, h4.y * sc[b].y), pack_bf16(h4.z * sc[b].z, h4.w * sc[b].w));
+          if (ss != nullptr && t0[b]) {                    // uniform over the CTA: the shuffles see full warps
+            float sq = h4.x * h4.x + h4.y * h4.y + h4.z * h4.z + h4.w * h4.w;
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            if (c4 == 0 && ok[j]) atomicAdd(ss + r0 + 16 * j, sq);
+          }
+        }
+      }
+    }
+  }
+}
+
+// activation operand of the down projection: GeGLU of the gate / up sums (row 1/rms and bias applied on the way)
+__device__ __noinline__ void es_load_glu(const WCtx& c, int kbs, int p0, int p1, const float* bias, const float* ss) {
+  constexpr int UP = 2;
+  const ExpertStackParams& p = *c.p;
+  const int c4 = c.wtid & 15, r0 = c.wtid >> 4, np = p1 - p0;
+  int kb = p0 % kbs;
+  const float* grow[4];
+  uint32_t soff[4];
+  float rms[4];
+  bool ok[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int m = r0 + 16 * j;
+    ok[j] = m < c.M;
+    grow[j] = p.acc_gu + size_t(ok[j] ? m : 0) * c.N2I + c4 * 8;
+    soff[j] = c.sA + sw64(m, c4 * 4);
+    rms[j] = ok[j] ? __ldcg(ss + m) : 1.f;
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) rms[j] = rsqrtf(rms[j] * c.inv_H + p.eps);
+  for (int pr = 0; pr < np; pr += UP) {
+    float4 a0[UP][4], a1[UP][4], b0[UP], b1[UP];
+#pragma unroll
+    for (int b = 0; b < UP; ++b) {
+      if (pr + b < np) {
+        const int k2 = kb * 128;                           // gate / up interleaved: two values per intermediate column
+        b0[b] = __ldg(reinterpret_cast<const float4*>(bias + k2 + c4 * 8));
+        b1[b] = __ldg(reinterpret_cast<const float4*>(bias + k2 + c4 * 8 + 4));
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (ok[j]) {
+            a0[b][j] = __ldcg(reinterpret_cast<const float4*>(grow[j] + k2));
+            a1[b][j] = __ldcg(reinterpret_cast<const float4*>(grow[j] + k2 + 4));
+          }
+        }
+        if (++kb == kbs) kb = 0;
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < UP; ++b) {
+      if (pr + b < np) {
+        const uint32_t blk = uint32_t(pr + b) * kActBlk;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (ok[j]) {
+            const float r = rms[j];
+            const float4 x0 = a0[b][j], x1 = a1[b][j];
+            const float y0 = gelu_tanh_f(x0.x * r + b0[b].x) * (x0.y * r + b0[b].y);
+            const float y1 = gelu_tanh_f(x0.z * r + b0[b].z) * (x0.w * r + b0[b].w);
+            const float y2 = gelu_tanh_f(x1.x * r + b1[b].x) * (x1.y * r + b1[b].y);
+            const float y3 = gelu_tanh_f(x1.z * r + b1[b].z) * (x1.w * r + b1[b].w);
+            st_shared_v2(blk + soff[j], pack_bf16(y0, y1), pack_bf16(y2, y3));
+          }
+        }
+      }
+    }
+  }
+}
+
+// one q or k head row group of the fused projection: 1/rms, bias, rounding to bf16, rotation; 4 + 4 values
+__device__ __forceinline__ void rope_store(float4 a, float4 b, float4 ba, float4 bb, float4 c, float4 s, float rms,
+                                           uint32_t tile, int r, int d0) {
+  const float xa[4] = {round_bf16(a.x * rms + ba.x), round_bf16(a.y * rms + ba.y), round_bf16(a.z * rms + ba.z), round_bf16(a.w * rms + ba.w)};
+  const float xb[4] = {round_bf16(b.x * rms + bb.x), round_bf16(b.y * rms + bb.y), round_bf16(b.z * rms + bb.z), round_bf16(b.w * rms + bb.w)};
+  const float cc[4] = {c.x, c.y, c.z, c.w}, sn[4] = {s.x, s.y, s.z, s.w};
+  float lo[4], hi[4];
+#pragma unroll
+  for (int t = 0; t < 4; ++t) { lo[t] = xa[t] * cc[t] - xb[t] * sn[t]; hi[t] = xb[t] * cc[t] + xa[t] * sn[t]; }
+  st_shared_v2(tile + sw64(r, d0), pack_bf16(lo[0], lo[1]), pack_bf16(lo[2], lo[3]));
+  st_shared_v2(tile + sw64(r, 128 + d0), pack_bf16(hi[0], hi[1]), pack_bf16(hi[2], hi[3]));
+}
+
+struct AttUnit { int head, split, p0, np, q0, nq, kv_ptr; };   // pool rows [p0, p0 + np), action rows [q0, q0 + nq)
+
+// Q / K / V tiles of one attention unit: pool rows by cp.async (zero fill past the unit's rows), q rows of the
+// head and the unit's share of the freshly projected rows from the fp32 sums. A worker owns one 4-wide
+// dimension group d0 (and its rotation partner d0 + 128) of rows r0, r0 + 8, ...: biases are read once.
+__device__ __noinline__ void es_load_att(const WCtx& c, const AttUnit& u, int layer, const float* bias) {
+  const ExpertStackParams& p = *c.p;
+  const uint32_t sQ = c.sA + 8192, sK = sQ + 32768, sV = sK + 32768;
+  const int kn = u.np + u.nq;
+  const int cg = c.wtid & 31, r0 = c.wtid >> 5, d0 = cg * 4;
+  const __nv_bfloat16* kpl = p.k_pool + size_t(layer) * p.pool_layer_stride + cg * 8;
+  const __nv_bfloat16* vpl = p.v_pool + size_t(layer) * p.pool_layer_stride + cg * 8;
+  {
+    // thread (cg, r0): 16-byte chunk cg of rows r0, r0 + 8, ..., r0 + 56
+    const uint32_t cbase = uint32_t(cg >> 3) * kActBlk;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int r = r0 + 8 * j;
+      const bool in_pool = r < u.np;
+      if (in_pool || r >= kn) {
+        const size_t row = size_t(in_pool ? u.kv_ptr + u.p0 + r : 0) * p.pool_row_stride;
+        const uint32_t off = cbase + uint32_t(r) * 128u + uint32_t(((cg & 7) ^ (r & 7)) << 4);
+        cp16(sK + off, kpl + row, in_pool);
+        cp16(sV + off, vpl + row, in_pool);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  {
+    const float* src0 = p.acc_qkv + u.head * kD + d0;
+    const float* bs = bias + u.head * kD + d0;
+    const float4 ba = __ldg(reinterpret_cast<const float4*>(bs)), bb = __ldg(reinterpret_cast<const float4*>(bs + 128));
+#pragma unroll 1
+    for (int jb = 0; jb < 8; jb += 4) {
+      float4 a[4], b[4], cc[4], sn[4];
+      float ssv[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const int m = r0 + 8 * (jb + t);
+        if (m < c.M) {
+          const float* cs = p.cos_sin + size_t(__ldg(p.pos + m)) * kD + d0;
+          ssv[t] = __ldcg(p.ss + m);
+          a[t] = __ldcg(reinterpret_cast<const float4*>(src0 + size_t(m) * c.Nqkv));
+          b[t] = __ldcg(reinterpret_cast<const float4*>(src0 + size_t(m) * c.Nqkv + 128));
+          cc[t] = __ldg(reinterpret_cast<const float4*>(cs));
+          sn[t] = __ldg(reinterpret_cast<const float4*>(cs + 128));
+        }
+      }
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const int m = r0 + 8 * (jb + t);
+        if (m < c.M) rope_store(a[t], b[t], ba, bb, cc[t], sn[t], rsqrtf(ssv[t] * c.inv_H + p.eps), sQ, m, d0);
+      }
+    }
+  }
+  if (r0 < u.nq) {                                           // nq <= 8 (ceil(M / S)): one row per thread
+    const int m = u.q0 + r0, r = u.np + r0;
+    const float* src = p.acc_qkv + size_t(m) * c.Nqkv + p.Hq * kD + d0;
+    const float* bs = bias + p.Hq * kD + d0;
+    const float* cs = p.cos_sin + size_t(__ldg(p.pos + m)) * kD + d0;
+    const float ssv = __ldcg(p.ss + m);
+    const float4 a = __ldcg(reinterpret_cast<const float4*>(src)), b = __ldcg(reinterpret_cast<const float4*>(src + 128));
+    const float4 v0 = __ldcg(reinterpret_cast<const float4*>(src + kD)), v1 = __ldcg(reinterpret_cast<const float4*>(src + kD + 128));
+    const float4 ba = __ldg(reinterpret_cast<const float4*>(bs)), bb = __ldg(reinterpret_cast<const float4*>(bs + 128));
+    const float4 b0 = __ldg(reinterpret_cast<const float4*>(bs + kD)), b1 = __ldg(reinterpret_cast<const float4*>(bs + kD + 128));
+    const float4 cc = __ldg(reinterpret_cast<const float4*>(cs)), sn = __ldg(reinterpret_cast<const float4*>(cs + 128));
+    const float rms = rsqrtf(ssv * c.inv_H + p.eps);
+    rope_store(a, b, ba, bb, cc, sn, rms, sK, r, d0);
+    st_shared_v2(sV + sw64(r, d0), pack_bf16(v0.x * rms + b0.x, v0.y * rms + b0.y), pack_bf16(v0.z * rms + b0.z, v0.w * rms + b0.w));
+    st_shared_v2(sV + sw64(r, 128 + d0), pack_bf16(v1.x * rms + b1.x, v1.y * rms + b1.y), pack_bf16(v1.z * rms + b1.z, v1.w * rms + b1.w));
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+// Merge the KV splits of every (row, head): all partial slots hold finite numbers (zeros until a unit first
+// wrote them), so the loads of all splits go out together and a weight of zero removes the slots of empty units.
+__device__ __noinline__ void es_merge(const WCtx& c, int S, int QW) {
+  constexpr int kMaxS = 18;
+  const ExpertStackParams& p = *c.p;
+  const int total = c.M * p.Hq * 64;
+  for (int i = c.cta * kWorkers + c.wtid; i < total; i += c.G * kWorkers) {
+    const int m = i / (p.Hq * 64), rem = i - m * (p.Hq * 64), hh = rem >> 6, d4 = rem & 63;
+    const float* ml = p.part_ml + (size_t(hh) * S * kRows + m) * 2;
+    const float* po = p.part_o + (size_t(hh) * S * kRows + m) * kD + d4 * 4;
+    float2 mlv[kMaxS];
+    float4 ov[kMaxS];
+#pragma unroll
+    for (int s2 = 0; s2 < kMaxS; ++s2) {
+      mlv[s2] = make_float2(-INFINITY, 0.f);
+      ov[s2] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (s2 < S) {
+        mlv[s2] = __ldcg(reinterpret_cast<const float2*>(ml + size_t(s2) * kRows * 2));
+        ov[s2] = __ldcg(reinterpret_cast<const float4*>(po + size_t(s2) * kRows * kD));
+      }
+    }
+    float mmax = -INFINITY;
+#pragma unroll
+    for (int s2 = 0; s2 < kMaxS; ++s2) mmax = fmaxf(mmax, mlv[s2].y > 0.f ? mlv[s2].x : -INFINITY);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float lsum = 0.f;
+#pragma unroll
+    for (int s2 = 0; s2 < kMaxS; ++s2) {
+      const float w = mlv[s2].y > 0.f ? exp2f(mlv[s2].x - mmax) : 0.f;
+      lsum += w * mlv[s2].y;
+      acc.x += w * ov[s2].x; acc.y += w * ov[s2].y; acc.z += w * ov[s2].z; acc.w += w * ov[s2].w;
+    }
+    const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+    uint2 raw;
+    raw.x = pack_bf16(acc.x * inv, acc.y * inv);
+    raw.y = pack_bf16(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(p.attn + size_t(m) * QW + hh * kD + d4 * 4) = raw;
+  }
+}
+
+// Second half of a projection's drain: the staged tiles (shared memory, [tile][64][132] fp32) go to L2 as
+// 16-byte reductions, 512 contiguous bytes per warp, starting at a row that differs from CTA to CTA.
+constexpr int kLds = 132;
+__device__ __noinline__ void es_reduce_out(const WCtx& c, const float* stg, int nt0, int na, float* out, int ldo,
+                                           const float* gate) {
+  const ExpertStackParams& p = *c.p;
+  const int n4 = c.wtid & 31, r0 = c.wtid >> 5;           // a warp covers one row of a tile, 8 rows in flight per CTA
+  const int rot = (c.cta * 3) % c.M;
+  for (int a = 0; a < na; ++a) {
+    const int n = (nt0 + a) * 128 + n4 * 4;
+    float4 g = make_float4(1.f, 1.f, 1.f, 1.f);
+    if (gate) g = __ldg(reinterpret_cast<const float4*>(gate + n));
+    const float* src = stg + a * kRows * kLds + n4 * 4;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int mi = r0 + 8 * j;
+      if (mi < c.M) {
+        int m = mi + rot;
+        if (m >= c.M) m -= c.M;
+        float4 v = *reinterpret_cast<const float4*>(src + m * kLds);
+        v.x *= g.x; v.y *= g.y; v.z *= g.z; v.w *= g.w;
+        if (p.debug & 1) *reinterpret_cast<float4*>(out + size_t(m) * ldo + n) = v;   // timing experiment: no reductions
+        else red_add_v4(out + size_t(m) * ldo + n, v);
+      }
+    }
+  }
+}
+
 }  // namespace
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -178,7 +463,7 @@ expert_stack_kernel(const __grid_constant__ ExpertStackParams p) {
   const int att_q0 = att_split * kq, att_nq = att_unit ? max(0, min(kq, M - att_q0)) : 0;    // action rows of the unit
   const int att_kn = att_np + att_nq;
   const bool att_live = att_unit && att_kn > 0;
-  if (tid == 0 && (kp + kq > kKeys || Lp < 0)) fail(kStatusBadArg);
+  if (tid == 0 && (kp + kq > kKeys || kq > 8 || Lp < 0)) fail(kStatusBadArg);
   __syncthreads();
 
   if (warp == 0) {
@@ -286,6 +571,8 @@ expert_stack_kernel(const __grid_constant__ ExpertStackParams p) {
     const uint32_t sA = smem_u32(regA);
     const uint32_t sP = sA, sQ = sA + 8192, sK = sQ + 32768, sV = sK + 32768;
     const float inv_H = 1.f / float(H);
+    const WCtx wc{&p, cta, G, wtid, lane, M, H, Nqkv, N2I, sA, inv_H};
+    const AttUnit au{att_head, att_split, att_p0, att_np, att_q0, att_nq, kv_ptr};
     uint32_t epoch = 0, acc_par = 0, s_par = 0;
     unsigned long long* tr = p.trace ? p.trace + 64 * cta : nullptr;
     int tr_i = 0;
@@ -316,12 +603,10 @@ expert_stack_kernel(const __grid_constant__ ExpertStackParams p) {
       return go_s != 0;
     };
     auto zero_rows = [&](float* base, int width) {
-      // rows [0, M) of a [64, width] fp32 buffer, spread over every worker of the grid
-      const int per_row = width >> 2, total = M * per_row;
-      for (int i = cta * kWorkers + wtid; i < total; i += G * kWorkers) {
-        const int m = i / per_row, c = i - m * per_row;
-        *reinterpret_cast<float4*>(base + size_t(m) * width + 4 * c) = make_float4(0.f, 0.f, 0.f, 0.f);
-      }
+      // rows [0, M) of a [64, width] fp32 buffer (contiguous), spread over every worker of the grid
+      const int total = (M * width) >> 2;
+      float4* b4 = reinterpret_cast<float4*>(base);
+      for (int i = cta * kWorkers + wtid; i < total; i += G * kWorkers) b4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     };
     auto arrive_act = [&]() {
       fence_proxy_async_smem();
@@ -334,7 +619,6 @@ expert_stack_kernel(const __grid_constant__ ExpertStackParams p) {
     // so that a thread owns four consecutive columns: one 16-byte reduction instead of four, a warp covers
     // 512 contiguous bytes, and the row order can start anywhere: CTAs that share a weight tile add into the
     // same rows, and each starts at another row so that they do not queue up on one address.
-    constexpr int kLds = 132;
     auto drain = [&](const Geo& geo, int p0, int p1, float* out, int ldo, const float* gate) {
       const bool any = p1 > p0;
       const int nt0 = any ? p0 / geo.kbs : 0, na = any ? (p1 - 1) / geo.kbs - nt0 + 1 : 0;
@@ -354,85 +638,8 @@ expert_stack_kernel(const __grid_constant__ ExpertStackParams p) {
         acc_par ^= 1u;
       }
       worker_sync();
-      if (any) {
-        const int rot = (cta * 3) % M, per = M * 32, total = na * per;
-        for (int i = wtid; i < total; i += kWorkers) {
-          const int a = i / per, rem = i - a * per, n4 = rem & 31;
-          int m = (rem >> 5) + rot;
-          if (m >= M) m -= M;
-          float4 v = *reinterpret_cast<const float4*>(stg + (a * kRows + m) * kLds + n4 * 4);
-          const int n = (nt0 + a) * 128 + n4 * 4;
-          if (gate) {
-            const float4 g = __ldg(reinterpret_cast<const float4*>(gate + n));
-            v.x *= g.x; v.y *= g.y; v.z *= g.z; v.w *= g.w;
-          }
-          red_add_v4(out + size_t(m) * ldo + n, v);
-        }
-      }
+      if (any) es_reduce_out(wc, stg, nt0, na, out, ldo, gate);
     };
-    // activation operand = rows of h times a per-column factor; optionally the row sums of squares.
-    // Loads are issued in batches before the first store (the stores are volatile asm and would fence them).
-    auto load_h = [&](const Geo& geo, int p0, int p1, const float* scale, float* ss) {
-      constexpr int U = 8;
-      const int per_pair = M * 16, limit = (p1 - p0) * per_pair;
-      for (int base = 0; base < limit; base += kWorkers * U) {
-        float4 hv[U], sc[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int i = base + u * kWorkers + wtid;
-          hv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-          sc[u] = hv[u];
-          if (i < limit) {
-            const int pr = i / per_pair, rem = i - pr * per_pair;
-            const int k = ((p0 + pr) % geo.kbs) * 64 + (rem & 15) * 4;
-            hv[u] = __ldcg(reinterpret_cast<const float4*>(p.h + size_t(rem >> 4) * H + k));
-            sc[u] = __ldg(reinterpret_cast<const float4*>(scale + k));
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int i = base + u * kWorkers + wtid;
-          if (base + u * kWorkers < limit) {                   // warp-uniform: the shuffles below see full warps
-            const bool valid = i < limit;
-            const int pr = valid ? i / per_pair : 0, rem = i - pr * per_pair, m = valid ? rem >> 4 : 0, c4 = rem & 15;
-            if (valid)
-              st_shared_v2(sA + uint32_t(pr) * kActBlk + sw64(m, c4 * 4), pack_bf16(hv[u].x * sc[u].x, hv[u].y * sc[u].y),
-                           pack_bf16(hv[u].z * sc[u].z, hv[u].w * sc[u].w));
-            // 16 consecutive lanes hold one row of one K block
-            float sq = hv[u].x * hv[u].x + hv[u].y * hv[u].y + hv[u].z * hv[u].z + hv[u].w * hv[u].w;
-#pragma unroll
-            for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-            if (valid && ss != nullptr && (p0 + pr) / geo.kbs == 0 && (lane & 15) == 0) atomicAdd(ss + m, sq);
-          }
-        }
-      }
-    };
-    // one q or k head row group of the fused projection: 1/rms, bias, rounding, rotation; 4 + 4 values
-    struct RopeIn { float4 a, b, ba, bb, c, s; float rms; };
-    auto rope_load = [&](const float* src, const float* bs, int m, int d0) {
-      RopeIn x;
-      x.rms = __ldcg(p.ss + m);
-      x.a = __ldcg(reinterpret_cast<const float4*>(src + d0));
-      x.b = __ldcg(reinterpret_cast<const float4*>(src + 128 + d0));
-      x.ba = __ldg(reinterpret_cast<const float4*>(bs + d0));
-      x.bb = __ldg(reinterpret_cast<const float4*>(bs + 128 + d0));
-      const float* cs = p.cos_sin + size_t(__ldg(p.pos + m)) * kD;
-      x.c = __ldg(reinterpret_cast<const float4*>(cs + d0));
-      x.s = __ldg(reinterpret_cast<const float4*>(cs + 128 + d0));
-      return x;
-    };
-    auto rope_store = [&](const RopeIn& x, uint32_t tile, int r, int d0) {
-      const float rms = rsqrtf(x.rms * inv_H + p.eps);
-      const float xa[4] = {round_bf16(x.a.x * rms + x.ba.x), round_bf16(x.a.y * rms + x.ba.y), round_bf16(x.a.z * rms + x.ba.z), round_bf16(x.a.w * rms + x.ba.w)};
-      const float xb[4] = {round_bf16(x.b.x * rms + x.bb.x), round_bf16(x.b.y * rms + x.bb.y), round_bf16(x.b.z * rms + x.bb.z), round_bf16(x.b.w * rms + x.bb.w)};
-      const float cc[4] = {x.c.x, x.c.y, x.c.z, x.c.w}, sn[4] = {x.s.x, x.s.y, x.s.z, x.s.w};
-      float lo[4], hi[4];
-#pragma unroll
-      for (int t = 0; t < 4; ++t) { lo[t] = xa[t] * cc[t] - xb[t] * sn[t]; hi[t] = xb[t] * cc[t] + xa[t] * sn[t]; }
-      st_shared_v2(tile + sw64(r, d0), pack_bf16(lo[0], lo[1]), pack_bf16(lo[2], lo[3]));
-      st_shared_v2(tile + sw64(r, 128 + d0), pack_bf16(hi[0], hi[1]), pack_bf16(hi[2], hi[3]));
-    };
-
     for (int step = p.step_begin; step < p.step_end; ++step) {
       const bool first_step = step == p.step_begin;
       // ------------------------------------------------ input projection (and the first clearing)
@@ -479,7 +686,7 @@ expert_stack_kernel(const __grid_constant__ ExpertStackParams p) {
           const Geo geo = gemm_geo(p, 0);
           int p0, p1;
           pair_range(geo, cta, G, p0, p1);
-          load_h(geo, p0, p1, p.in_scale + sl * H, p.ss);
+          es_load_h(wc, geo.kbs, p0, p1, p.in_scale + sl * H, p.ss);
           arrive_act();
           ES_STAMP();
           if (!(first_step && layer == 0)) {
@@ -494,55 +701,7 @@ expert_stack_kernel(const __grid_constant__ ExpertStackParams p) {
         // ---------------------------------------------------------------- attention units
         if (att_live) {
           const float* bias = p.qkv_bias + sl * Nqkv;
-          // K / V pool rows by cp.async first (they only depend on the prefix), zero fill past the unit's rows
-          const __nv_bfloat16* kpl = p.k_pool + size_t(layer) * p.pool_layer_stride;
-          const __nv_bfloat16* vpl = p.v_pool + size_t(layer) * p.pool_layer_stride;
-          for (int i = wtid; i < kKeys * 32; i += kWorkers) {
-            const int r = i >> 5, c = i & 31;
-            const bool in_pool = r < att_np;
-            if (in_pool || r >= att_kn) {
-              const size_t row = size_t(in_pool ? kv_ptr + att_p0 + r : 0) * p.pool_row_stride + c * 8;
-              const uint32_t off = uint32_t(c >> 3) * kActBlk + uint32_t(r) * 128u + uint32_t(((c & 7) ^ (r & 7)) << 4);
-              cp16(sK + off, kpl + row, in_pool);
-              cp16(sV + off, vpl + row, in_pool);
-            }
-          }
-          asm volatile("cp.async.commit_group;" ::: "memory");
-          // q rows of this head, in two batches of loads
-          {
-            const float* src0 = p.acc_qkv + att_head * kD;
-            const float* bs = bias + att_head * kD;
-            constexpr int U = 3;
-            for (int base = 0; base < M * 32; base += kWorkers * U) {
-              RopeIn x[U];
-#pragma unroll
-              for (int u = 0; u < U; ++u) {
-                const int i = base + u * kWorkers + wtid;
-                if (i < M * 32) x[u] = rope_load(src0 + size_t(i >> 5) * Nqkv, bs, i >> 5, (i & 31) * 4);
-              }
-#pragma unroll
-              for (int u = 0; u < U; ++u) {
-                const int i = base + u * kWorkers + wtid;
-                if (i < M * 32) rope_store(x[u], sQ, i >> 5, (i & 31) * 4);
-              }
-            }
-          }
-          // the unit's share of the rows the projection just produced: k rotated, v as is
-          for (int i = wtid; i < att_nq * 32; i += kWorkers) {
-            const int m = att_q0 + (i >> 5), r = att_np + (i >> 5), d0 = (i & 31) * 4;
-            const float* src = p.acc_qkv + size_t(m) * Nqkv + p.Hq * kD;
-            const float* bs = bias + p.Hq * kD;
-            const RopeIn x = rope_load(src, bs, m, d0);
-            const float4 v0 = __ldcg(reinterpret_cast<const float4*>(src + kD + d0));
-            const float4 v1 = __ldcg(reinterpret_cast<const float4*>(src + kD + 128 + d0));
-            const float4 b0 = __ldg(reinterpret_cast<const float4*>(bs + kD + d0));
-            const float4 b1 = __ldg(reinterpret_cast<const float4*>(bs + kD + 128 + d0));
-            rope_store(x, sK, r, d0);
-            const float rms = rsqrtf(x.rms * inv_H + p.eps);
-            st_shared_v2(sV + sw64(r, d0), pack_bf16(v0.x * rms + b0.x, v0.y * rms + b0.y), pack_bf16(v0.z * rms + b0.z, v0.w * rms + b0.w));
-            st_shared_v2(sV + sw64(r, 128 + d0), pack_bf16(v1.x * rms + b1.x, v1.y * rms + b1.y), pack_bf16(v1.z * rms + b1.z, v1.w * rms + b1.w));
-          }
-          asm volatile("cp.async.wait_group 0;" ::: "memory");
+          es_load_att(wc, au, layer, bias);
           arrive_act();
           ES_STAMP();
           // softmax of the unit: one thread per query row (rows live in lane quadrants 0 and 1)
@@ -615,58 +774,7 @@ expert_stack_kernel(const __grid_constant__ ExpertStackParams p) {
         ES_STAMP();
         // ---------------------------------------------------------------- merge the splits
         {
-          // every partial slot holds finite numbers (zeros until a unit first wrote it), so all S loads go out
-          // together and a weight of zero removes the slots of empty units
-          constexpr int kMaxS = 18;
-          const int total = M * p.Hq * 64;
-          for (int i = cta * kWorkers + wtid; i < total; i += G * kWorkers) {
-            const int m = i / (p.Hq * 64), rem = i - m * (p.Hq * 64), hh = rem >> 6, d4 = rem & 63;
-            const float* ml = p.part_ml + (size_t(hh) * S * kRows + m) * 2;
-            const float* po = p.part_o + (size_t(hh) * S * kRows + m) * kD + d4 * 4;
-            float2 mlv[kMaxS];
-            float4 ov[kMaxS / 2];
-#pragma unroll
-            for (int s2 = 0; s2 < kMaxS; ++s2) {
-              mlv[s2] = make_float2(-INFINITY, 0.f);
-              if (s2 < S) mlv[s2] = __ldcg(reinterpret_cast<const float2*>(ml + size_t(s2) * kRows * 2));
-            }
-#pragma unroll
-            for (int s2 = 0; s2 < kMaxS / 2; ++s2) {
-              ov[s2] = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (s2 < S) ov[s2] = __ldcg(reinterpret_cast<const float4*>(po + size_t(s2) * kRows * kD));
-            }
-            float mmax = -INFINITY;
-#pragma unroll
-            for (int s2 = 0; s2 < kMaxS; ++s2) mmax = fmaxf(mmax, mlv[s2].y > 0.f ? mlv[s2].x : -INFINITY);
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            float lsum = 0.f;
-#pragma unroll
-            for (int s2 = 0; s2 < kMaxS; ++s2) {
-              const float w = mlv[s2].y > 0.f ? exp2f(mlv[s2].x - mmax) : 0.f;
-              lsum += w * mlv[s2].y;
-              mlv[s2].x = w;
-            }
-#pragma unroll
-            for (int s2 = 0; s2 < kMaxS / 2; ++s2) {
-              const float w = mlv[s2].x;
-              acc.x += w * ov[s2].x; acc.y += w * ov[s2].y; acc.z += w * ov[s2].z; acc.w += w * ov[s2].w;
-            }
-#pragma unroll
-            for (int s2 = 0; s2 < kMaxS / 2; ++s2) {
-              ov[s2] = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (s2 + kMaxS / 2 < S) ov[s2] = __ldcg(reinterpret_cast<const float4*>(po + size_t(s2 + kMaxS / 2) * kRows * kD));
-            }
-#pragma unroll
-            for (int s2 = 0; s2 < kMaxS / 2; ++s2) {
-              const float w = mlv[s2 + kMaxS / 2].x;
-              acc.x += w * ov[s2].x; acc.y += w * ov[s2].y; acc.z += w * ov[s2].z; acc.w += w * ov[s2].w;
-            }
-            const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-            uint2 raw;
-            raw.x = pack_bf16(acc.x * inv, acc.y * inv);
-            raw.y = pack_bf16(acc.z * inv, acc.w * inv);
-            *reinterpret_cast<uint2*>(p.attn + size_t(m) * QW + hh * kD + d4 * 4) = raw;
-          }
+          es_merge(wc, S, QW);
           zero_rows(p.acc_qkv, Nqkv);                        // consumed by the attention units
           if (cta == 0 && wtid < kRows) p.ss[wtid] = 0.f;
         }
@@ -697,7 +805,7 @@ expert_stack_kernel(const __grid_constant__ ExpertStackParams p) {
           const Geo geo = gemm_geo(p, 2);
           int p0, p1;
           pair_range(geo, cta, G, p0, p1);
-          load_h(geo, p0, p1, p.post_scale + sl * H, p.ss + kRows);
+          es_load_h(wc, geo.kbs, p0, p1, p.post_scale + sl * H, p.ss + kRows);
           arrive_act();
           ES_STAMP();
           drain(geo, p0, p1, p.acc_gu, N2I, nullptr);
@@ -711,39 +819,7 @@ expert_stack_kernel(const __grid_constant__ ExpertStackParams p) {
           int p0, p1;
           pair_range(geo, cta, G, p0, p1);
           const float* bias = p.gu_bias + sl * N2I;
-          constexpr int U = 4;
-          const int per_pair = M * 16, limit = (p1 - p0) * per_pair;
-          for (int base = 0; base < limit; base += kWorkers * U) {
-            float4 a0[U], a1[U], b0[U], b1[U];
-            float ssv[U];
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-              const int i = base + u * kWorkers + wtid;
-              if (i < limit) {
-                const int pr = i / per_pair, rem = i - pr * per_pair, m = rem >> 4, c4 = rem & 15;
-                const int k = ((p0 + pr) % geo.kbs) * 64 + c4 * 4;
-                const float* src = p.acc_gu + size_t(m) * N2I + 2 * k;
-                ssv[u] = __ldcg(p.ss + kRows + m);
-                a0[u] = __ldcg(reinterpret_cast<const float4*>(src));
-                a1[u] = __ldcg(reinterpret_cast<const float4*>(src + 4));
-                b0[u] = __ldg(reinterpret_cast<const float4*>(bias + 2 * k));
-                b1[u] = __ldg(reinterpret_cast<const float4*>(bias + 2 * k + 4));
-              }
-            }
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-              const int i = base + u * kWorkers + wtid;
-              if (i < limit) {
-                const int pr = i / per_pair, rem = i - pr * per_pair, m = rem >> 4, c4 = rem & 15;
-                const float rms = rsqrtf(ssv[u] * inv_H + p.eps);
-                const float y0 = gelu_tanh_f(a0[u].x * rms + b0[u].x) * (a0[u].y * rms + b0[u].y);
-                const float y1 = gelu_tanh_f(a0[u].z * rms + b0[u].z) * (a0[u].w * rms + b0[u].w);
-                const float y2 = gelu_tanh_f(a1[u].x * rms + b1[u].x) * (a1[u].y * rms + b1[u].y);
-                const float y3 = gelu_tanh_f(a1[u].z * rms + b1[u].z) * (a1[u].w * rms + b1[u].w);
-                st_shared_v2(sA + uint32_t(pr) * kActBlk + sw64(m, c4 * 4), pack_bf16(y0, y1), pack_bf16(y2, y3));
-              }
-            }
-          }
+          es_load_glu(wc, geo.kbs, p0, p1, bias, p.ss + kRows);
           arrive_act();
           ES_STAMP();
           drain(geo, p0, p1, p.h, H, p.gate_post + sl * H);
@@ -828,7 +904,7 @@ cudaError_t expert_stack_launch(const ExpertStackParams& p, cudaStream_t stream)
   if (p.M <= 0 || p.M > kRows || p.D != kD || p.A <= 0 || p.A % 4 || p.H % 128 || p.I % 64 ||
       ((p.Hq + 2) * p.D) % 128 || (2 * p.I) % 128 || p.n_layers <= 0 || p.step_end <= p.step_begin || p.step_begin < 0)
     return cudaErrorInvalidValue;
-  if (p.att_splits <= 0 || p.Hq * p.att_splits > G) return cudaErrorInvalidValue;
+  if (p.att_splits <= 0 || p.Hq * p.att_splits > G || (p.M + p.att_splits - 1) / p.att_splits > 8) return cudaErrorInvalidValue;
   const int nt[4] = {(p.Hq + 2) * p.D / 128, p.H / 128, 2 * p.I / 128, p.H / 128};
   const int kb[4] = {p.H / 64, p.Hq * p.D / 64, p.H / 64, p.I / 64};
   for (int g = 0; g < 4; ++g) {

@@ -50,6 +50,7 @@ struct ExpertStackParams {
   unsigned* barrier = nullptr;         // grid barrier word, cleared before every launch
   int* status = nullptr;
   unsigned long long* trace = nullptr; // optional: 64 globaltimer stamps per CTA
+  int debug = 0;                       // bit 0: plain stores instead of reductions (timing experiments; wrong results)
 };
 
 // Bytes of fp32 / bf16 scratch the kernel needs for a geometry (see the struct): the caller allocates.

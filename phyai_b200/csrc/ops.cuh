@@ -64,6 +64,12 @@ cudaError_t gated_act_launch(const __nv_bfloat16* x, __nv_bfloat16* y, int M, in
                              int interleaved, cudaStream_t s);
 
 // x += dt * v (elementwise; x fp32 or bf16, v bf16)
+// Gated DeltaNet decode step (gdn.cu): q, k [B, H, Dk], v [B, H, Dv], g, beta [B, H] (all fp32 or all bf16),
+// state_pool fp32 [slots, H, Dk, Dv] updated in place at rows state_indices[B]; out [B, H, Dv].
+cudaError_t gdn_decode_launch(const void* q, const void* k, const void* v, const void* g, const void* beta, int in_bf16,
+                              float* state_pool, const long long* state_indices, void* out, int out_bf16, int B, int H,
+                              int Dk, int Dv, float scale, int l2norm, cudaStream_t stream);
+
 cudaError_t axpy_launch(void* x, int x_fp32, const __nv_bfloat16* v, float dt, long long n,
                         cudaStream_t s);
 

@@ -219,6 +219,17 @@ def im2col(pix: torch.Tensor, patch: int, out: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def gdn_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor,
+               state_pool: torch.Tensor, state_indices: torch.Tensor, *, scale: float | None = None,
+               use_qk_l2norm: bool = True) -> torch.Tensor:
+    """One Gated-DeltaNet decode step per sequence (``csrc/gdn.cu``): q, k ``(B, H, Dk)``, v ``(B, H, Dv)``, g, beta
+    ``(B, H)``; the fp32 states ``state_pool[state_indices]`` (``(slots, H, Dk, Dv)``) are updated in place."""
+    sc = q.shape[-1] ** -0.5 if scale is None else scale
+    idx = state_indices.to(torch.int64).contiguous()
+    return ext().gdn_decode(q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous().to(q.dtype),
+                            beta.contiguous().to(q.dtype), state_pool, idx, float(sc), bool(use_qk_l2norm))
+
+
 def gated_act(x: torch.Tensor, act: str, *, interleaved: bool = False,
               out: Optional[torch.Tensor] = None) -> torch.Tensor:
     if out is None:

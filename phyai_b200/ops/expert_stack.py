@@ -52,6 +52,7 @@ class ExpertStack:
         self.tmaps: torch.Tensor | None = None
         self._keep: list[torch.Tensor] = []
         self.tables: dict[str, torch.Tensor] = {}
+        self.debug = 0      # timing experiments only (bit 0: plain stores instead of reductions: wrong results)
 
     # ------------------------------------------------------------------ capability
     @staticmethod
@@ -66,7 +67,9 @@ class ExpertStack:
         if geo.hidden % 128 or geo.inter % 64 or geo.action_dim % 4:
             return False
         splits = min(18, grid // geo.q_heads)
-        if splits <= 0 or max_kv_rows > 64 * splits:
+        # a unit holds ceil(pool rows / splits) + ceil(rows / splits) <= 64 keys, at most 8 of them new
+        pool_rows = max(0, max_kv_rows - geo.rows)
+        if splits <= 0 or -(-geo.rows // splits) > 8 or -(-pool_rows // splits) + -(-geo.rows // splits) > 64:
             return False
         nt = [(geo.q_heads + 2) * geo.head_dim // 128, geo.hidden // 128, 2 * geo.inter // 128, geo.hidden // 128]
         kb = [geo.hidden // 64, geo.q_heads * geo.head_dim // 64, geo.hidden // 64, geo.inter // 64]
@@ -102,7 +105,7 @@ class ExpertStack:
                                self.tables["in_scale"], self.tables["post_scale"], self.tables["gate_in"],
                                self.tables["gate_post"], self.tables["qkv_bias"], self.tables["gu_bias"],
                                self.tables["fin_scale"], self.tables["out_bias"], w_in, b_in, w_out, k_pool, v_pool,
-                               kv_ptr, kv_len, pos, cos_sin, x0, out, self.scratch, self.attn, self.barrier, trace)
+                               kv_ptr, kv_len, pos, cos_sin, x0, out, self.scratch, self.attn, self.barrier, trace, self.debug)
 
 
 __all__ = ["ExpertStack", "ExpertGeometry"]

@@ -457,3 +457,30 @@ def test_norms_many_rows(rows, D):
     h = (x.float() + r.float()).bfloat16()
     assert relerr(r2, h) < 1e-2 and relerr(y, ref.rms_norm(h, w)) < TOL
     _status_ok()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gdn_decode_kernel_matches_the_recurrence(dtype):
+    from phyai_b200 import ops
+    from phyai_b200.layers.attention.gdn import GatedDeltaNetAttention, gated_delta_rule_recurrent
+
+    g0 = torch.Generator().manual_seed(5)
+    B, H, Dk, Dv, steps = 3, 4, 128, 128, 3
+    pool = (torch.randn(6, H, Dk, Dv, generator=g0) * 0.2).to(DEV)
+    idx = torch.tensor([5, 0, 2], device=DEV)
+    ref_state = pool[idx].clone()
+    layer = GatedDeltaNetAttention(H, Dk, Dv)
+    for _ in range(steps):                       # the pool rows are updated in place, step after step
+        q, k = (torch.randn(B, H, Dk, generator=g0).to(DEV, dtype) for _ in range(2))
+        v = torch.randn(B, H, Dv, generator=g0).to(DEV, dtype)
+        g = (-torch.rand(B, H, generator=g0)).to(DEV, dtype)
+        beta = torch.rand(B, H, generator=g0).to(DEV, dtype)
+        o = layer.decode(q, k, v, g, beta, state_pool=pool, state_indices=idx)
+        o_ref, ref_state = gated_delta_rule_recurrent(q[:, None].float(), k[:, None].float(), v[:, None].float(), g[:, None].float(),
+                                                      beta[:, None].float(), ref_state)
+        tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+        torch.testing.assert_close(o.float(), o_ref[:, 0], atol=tol, rtol=tol)
+        torch.testing.assert_close(pool[idx], ref_state, atol=1e-4, rtol=1e-4)
+    untouched = [i for i in range(6) if i not in (5, 0, 2)]
+    assert ops.launch_counter() > 0 and torch.isfinite(pool[untouched]).all()
+    _status_ok()

@@ -162,6 +162,29 @@ def test_gdn_chunked_equals_stepwise_decode():
     assert torch.allclose(torch.stack(outs, 1), o, atol=1e-5) and torch.allclose(pool[idx], S, atol=1e-5)
 
 
+def test_gdn_chunked_prefill_matches_the_token_recurrence():
+    from phyai_b200.layers.attention.gdn import gated_delta_rule_chunked
+
+    g0 = torch.Generator().manual_seed(11)
+    for B, T, H, Dk, Dv, chunk in [(2, 150, 3, 32, 48, 64), (1, 64, 2, 16, 16, 64), (1, 37, 1, 8, 12, 16)]:
+        q, k = torch.randn(B, T, H, Dk, generator=g0), torch.randn(B, T, H, Dk, generator=g0)
+        v = torch.randn(B, T, H, Dv, generator=g0)
+        g, beta = -torch.rand(B, T, H, generator=g0) * 0.7, torch.rand(B, T, H, generator=g0)
+        s0 = torch.randn(B, H, Dk, Dv, generator=g0) * 0.3
+        o1, S1 = gated_delta_rule_recurrent(q, k, v, g, beta, s0)
+        o2, S2 = gated_delta_rule_chunked(q, k, v, g, beta, s0, chunk=chunk)
+        assert torch.allclose(o1, o2, atol=2e-5) and torch.allclose(S1, S2, atol=2e-5)
+    # the layer's prefill takes the chunked path and leaves the same states in the pool
+    layer = GatedDeltaNetAttention(3, 32, 48)
+    pool = torch.zeros(5, 3, 32, 48)
+    idx = torch.tensor([4, 0])
+    q, k, v = torch.randn(2, 70, 3, 32, generator=g0), torch.randn(2, 70, 3, 32, generator=g0), torch.randn(2, 70, 3, 48, generator=g0)
+    g, beta = -torch.rand(2, 70, 3, generator=g0), torch.rand(2, 70, 3, generator=g0)
+    o = layer.prefill(q, k, v, g, beta, state_pool=pool, state_indices=idx)
+    o_ref, S_ref = gated_delta_rule_recurrent(q, k, v, g, beta)
+    assert torch.allclose(o, o_ref, atol=2e-5) and torch.allclose(pool[idx], S_ref, atol=2e-5)
+
+
 def test_vocab_parallel_embedding_masks_other_ranks():
     e0 = VocabParallelEmbedding(100, 8, mesh=fake_mesh(2, 0), prefix="emb")
     e1 = VocabParallelEmbedding(100, 8, mesh=fake_mesh(2, 1), prefix="emb")
