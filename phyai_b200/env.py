@@ -119,7 +119,7 @@ class envs:
     PHYAI_PI05_EXPERT_SPLITS = EnvField("PHYAI_PI05_EXPERT_SPLITS", None, int)  # KV split of the expert's joint attention (default 8)
     PHYAI_PI05_PREFIX_SPLITS = EnvField("PHYAI_PI05_PREFIX_SPLITS", None, int)  # KV split of the prefix attention (default at batch 1: 4 from 896 prefix rows, else 2)
     PHYAI_PI05_OVERLAP = EnvField("PHYAI_PI05_OVERLAP", True, parse_bool)       # 0: no second stream (first Euler step after the prefix)
-    PHYAI_PI05_EXPERT_KERNEL = EnvField("PHYAI_PI05_EXPERT_KERNEL", True, parse_bool)  # 0: Euler loop launch by launch instead of the persistent kernel
+    PHYAI_PI05_EXPERT_KERNEL = EnvField("PHYAI_PI05_EXPERT_KERNEL", False, parse_bool)  # 1: Euler loop as one persistent kernel (measured slower than launch by launch at batch 1)
     PHYAI_CHECK_KERNEL_STATUS = EnvField("PHYAI_CHECK_KERNEL_STATUS", False, parse_bool)  # 1: read the device status word after every Engine.step even without peer groups
     # debug / tensor dump
     PHYAI_DEBUG_TENSOR_DUMP_DIR = EnvField("PHYAI_DEBUG_TENSOR_DUMP_DIR", None, str)

@@ -46,6 +46,14 @@ def resolve_mesh(name: str | None = None) -> Any:
     return _MESHES[key]
 
 
+def mesh_name(mesh: Any) -> str | None:
+    """The name a mesh object is registered under (None for an unregistered mesh)."""
+    for k, v in _MESHES.items():
+        if v is mesh:
+            return k
+    return None
+
+
 def default_mesh() -> Any | None:
     return _MESHES.get(_ACTIVE.get() or _DEFAULT_NAME)
 
@@ -63,5 +71,5 @@ def clear_meshes() -> None:
     _MESHES.clear()
 
 
-__all__ = ["current_mode", "graph_capture", "register_mesh", "unregister_mesh", "resolve_mesh",
+__all__ = ["current_mode", "graph_capture", "register_mesh", "unregister_mesh", "resolve_mesh", "mesh_name",
            "default_mesh", "use_mesh", "clear_meshes"]

@@ -94,3 +94,27 @@ def test_step_status_check_raises_and_is_silent_when_clean(monkeypatch):
         health.check_step_status(what="cosmos3.step", force=True)
     with pytest.raises(RuntimeError):
         health.check_step_status(force=True)
+
+
+def test_collectives_are_registered_ops_with_shape_only_fakes():
+    """The tensor-valued collectives exist as ``torch.ops.phyai_b200.*`` and can be traced with fake tensors."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    from phyai_b200.parallel import state
+    from phyai_b200.parallel.mesh import Mesh
+
+    mesh = Mesh((1, 4), ("cfg", "tp"), rank=1, build_groups=False, device_type="cpu")
+    state.register_mesh("fake_tp4", mesh)
+    try:
+        with FakeTensorMode():
+            x = torch.empty(8, 6)
+            assert tuple(torch.ops.phyai_b200.all_reduce(x, "fake_tp4", "tp", "sum").shape) == (8, 6)
+            assert tuple(torch.ops.phyai_b200.all_gather(x, "fake_tp4", "tp", 1).shape) == (8, 24)
+            assert tuple(torch.ops.phyai_b200.reduce_scatter(x, "fake_tp4", "tp", 0, "sum").shape) == (2, 6)
+            assert tuple(torch.ops.phyai_b200.all_to_all(x, "fake_tp4", "tp", 0, 1).shape) == (2, 24)
+            assert tuple(torch.ops.phyai_b200.broadcast(x, "fake_tp4", "tp", 0).shape) == (8, 6)
+            with pytest.raises(Exception):
+                torch.ops.phyai_b200.reduce_scatter(torch.empty(7, 6), "fake_tp4", "tp", 0, "sum")
+        assert state.mesh_name(mesh) == "fake_tp4"
+    finally:
+        state.unregister_mesh("fake_tp4")

@@ -32,11 +32,14 @@ def _perturb_norms(eng, g):
     eng.entry.scheduler.plan.build_modulation_tables()
 
 
-@pytest.mark.parametrize("batch,graph,overlap", [(1, True, False), (2, True, False), (2, False, False), (1, True, True), (2, False, True)])
-def test_plan_matches_eager(batch, graph, overlap, monkeypatch):
+@pytest.mark.parametrize("batch,graph,overlap,expert_kernel", [(1, True, False, False), (2, True, False, False), (2, False, False, False),
+                                                               (1, True, True, False), (2, False, True, False),
+                                                               (1, True, False, True), (1, True, True, True)])
+def test_plan_matches_eager(batch, graph, overlap, expert_kernel, monkeypatch):
     from phyai_b200.models.pi05.plan_pi05 import PI05Plan
 
     monkeypatch.setattr(PI05Plan, "overlap_first_step", overlap)   # first Euler step on a second stream under the prefix
+    monkeypatch.setattr(PI05Plan, "use_expert_kernel", expert_kernel)   # Euler loop as one persistent kernel
     from phyai_b200 import ops
     from phyai_b200.engine import Engine, EngineArgs
     from phyai_b200.engine_config import DeviceConfig, EngineConfig, RuntimeConfig
@@ -44,11 +47,13 @@ def test_plan_matches_eager(batch, graph, overlap, monkeypatch):
     from phyai_b200.models.pi05.scheduler_ws1_pi05 import PI05Request
 
     cfg = _mid_config()
-    eng = Engine(EngineArgs("pi05", PI05Args(config=cfg, max_batch_size=2, inputs_image_shape=[[56, 56, 3]] * 2),
+    # the persistent kernel serves one robot: its cases build a batch-1 engine
+    eng = Engine(EngineArgs("pi05", PI05Args(config=cfg, max_batch_size=1 if expert_kernel else 2, inputs_image_shape=[[56, 56, 3]] * 2),
                             EngineConfig(device=DeviceConfig("cuda:0", torch.bfloat16),
                                          runtime=RuntimeConfig(use_cuda_graph=graph))))
     g = torch.Generator().manual_seed(batch)
     _perturb_norms(eng, g)
+    assert (eng.entry.scheduler.plan.stack is not None) == expert_kernel
     lens = torch.tensor([40, 7][:batch])
     req = PI05Request((torch.rand(batch, 2, 3, 56, 56, generator=g) * 2 - 1).bfloat16().cuda(),
                       torch.randint(0, 1024, (batch, 48), generator=g).cuda(), lens.cuda(),
@@ -59,7 +64,10 @@ def test_plan_matches_eager(batch, graph, overlap, monkeypatch):
     assert ops.kernel_status() == 0
     ref = eng.entry.model.sample_actions(req.pixel_values, req.input_ids, lens, req.noise)
     rel = (out.float() - ref.float()).abs().max() / ref.float().abs().max()
-    assert torch.equal(out, out_again)
+    if expert_kernel:   # split-K sums are fp32 reductions in L2: their order, hence the last bit, varies from run to run
+        assert (out.float() - out_again.float()).abs().max() <= 2e-2 * ref.float().abs().max()
+    else:
+        assert torch.equal(out, out_again)
     assert rel < 5e-2, rel
     # a different prompt length re-plans the metadata without re-capturing anything it should not
     req2 = PI05Request(req.pixel_values, req.input_ids, torch.tensor([12, 30][:batch]).cuda(), req.noise)
