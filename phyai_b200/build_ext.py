@@ -6,6 +6,14 @@ GPU), the pybind/torch binding unit with the host compiler, and links them into
 ``phyai_b200/_C*.so`` next to the Python sources. Objects are cached under
 ``build/`` keyed by a hash of the source, its headers and the flags, so an
 unchanged file is not recompiled.
+
+Variants (objects are cached per flag set, the output replaces the regular ``.so``):
+
+* ``--debug``     ``-DPHYAI_DEBUG=1``: the kernels' index checks are compiled in (a row / column /
+  slot index outside its tensor is recorded in the status word as ``kStatusBadArg`` and the access is
+  skipped, see ``PB_DEBUG_CHECK`` in ``csrc/ptx.cuh``), device code at ``-O1`` with line info;
+* ``--sanitize``  host-only prefix cache with ``-fsanitize=address,undefined`` (run the cache tests with
+  ``LD_PRELOAD=$(gcc -print-file-name=libasan.so)``); ``--tsan`` the same with ``-fsanitize=thread``.
 """
 
 from __future__ import annotations
@@ -52,7 +60,7 @@ def ext_suffix() -> str:
     return sysconfig.get_config_var("EXT_SUFFIX") or ".so"
 
 
-def build_core(verbose: bool = False) -> Path:
+def build_core(verbose: bool = False, debug: bool = False) -> Path:
     """Build ``phyai_b200/_C`` (CUDA kernels + torch bindings)."""
     BUILD.mkdir(exist_ok=True)
     headers = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
@@ -67,6 +75,8 @@ def build_core(verbose: bool = False) -> Path:
                                  f"-I{p}" for p in inc]
     if verbose:
         cu_flags += ["-Xptxas", "-v"]
+    if debug:
+        cu_flags = [f for f in cu_flags if f != "-O3"] + ["-O1", "-DPHYAI_DEBUG=1"]
     cxx_flags = ["-O2", "-std=c++17", "-fPIC", "-DTORCH_EXTENSION_NAME=_C",
                  "-DTORCH_API_INCLUDE_EXTENSION_H", "-D_GLIBCXX_USE_CXX11_ABI=1",
                  "-I/usr/local/cuda/include"] + common_inc + [f"-I{p}" for p in inc]
@@ -104,8 +114,9 @@ def build_core(verbose: bool = False) -> Path:
     return out
 
 
-def build_radix(verbose: bool = False) -> Path | None:
-    """Build ``phyai_b200/_radix`` (host-only C++ prefix cache, pybind11)."""
+def build_radix(verbose: bool = False, sanitize: str | None = None) -> Path | None:
+    """Build ``phyai_b200/_radix`` (host-only C++ prefix cache, pybind11). ``sanitize``: ``"address"`` (with
+    undefined-behaviour checks) or ``"thread"``."""
     src_dir = CSRC / "radix_cache"
     if not src_dir.exists():
         return None
@@ -117,6 +128,14 @@ def build_radix(verbose: bool = False) -> Path | None:
     pyinc = sysconfig.get_paths()["include"]
     flags = ["-O2", "-std=c++20", "-fPIC", "-pthread", f"-I{src_dir}", f"-I{pyinc}",
              f"-I{pybind11.get_include()}"]
+    san: list[str] = []
+    if sanitize == "address":
+        san = ["-fsanitize=address,undefined", "-fno-omit-frame-pointer", "-g"]
+    elif sanitize == "thread":
+        san = ["-fsanitize=thread", "-fno-omit-frame-pointer", "-g"]
+    elif sanitize:
+        raise ValueError(f"unknown sanitizer {sanitize!r}")
+    flags = [f if f != "-O2" else ("-O1" if san else "-O2") for f in flags] + san
     objs, jobs = [], []
     for s in srcs:
         tag = _hash([s] + hdrs, flags)
@@ -127,25 +146,26 @@ def build_radix(verbose: bool = False) -> Path | None:
     with ThreadPoolExecutor(max_workers=8) as ex:
         list(ex.map(_run, jobs))
     out = ROOT / f"_radix{ext_suffix()}"
-    link_tag = _hash(objs, ["link-radix"])
+    link_tag = _hash(objs, ["link-radix", *san])
     stamp = BUILD / f"_radix.{link_tag}.stamp"
     if not out.exists() or not stamp.exists():
-        _run(["g++", "-shared", "-pthread", "-o", str(out), *map(str, objs)])
+        _run(["g++", "-shared", "-pthread", *san, "-o", str(out), *map(str, objs)])
         stamp.write_text("ok")
     return out
 
 
-def build_all(verbose: bool = False) -> list[Path]:
-    outs = [build_core(verbose)]
-    r = build_radix(verbose)
+def build_all(verbose: bool = False, debug: bool = False, sanitize: str | None = None) -> list[Path]:
+    outs = [build_core(verbose, debug)]
+    r = build_radix(verbose, sanitize)
     if r is not None:
         outs.append(r)
     return outs
 
 
 if __name__ == "__main__":
+    sanitize = "address" if "--sanitize" in sys.argv else ("thread" if "--tsan" in sys.argv else None)
     if "--radix-only" in sys.argv:      # host-only C++ (no nvcc): what a CPU-only checkout can build
-        print("built", build_radix("-v" in sys.argv))
+        print("built", build_radix("-v" in sys.argv, sanitize))
     else:
-        for p in build_all("-v" in sys.argv):
+        for p in build_all("-v" in sys.argv, "--debug" in sys.argv, sanitize):
             print("built", p)

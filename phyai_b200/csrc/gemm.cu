@@ -582,6 +582,9 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream, int* n_ctas) {
   ep.act = a.act; ep.glu = a.glu; ep.out_fp32 = a.out_fp32;
   ep.rs_inv_dim = a.row_rms_dim > 0 ? 1.f / float(a.row_rms_dim) : 0.f; ep.rs_eps = a.row_rms_eps;
   ep.rope = a.rope; ep.zero = a.zero; ep.zero_n = a.zero_n;
+#ifdef PHYAI_DEBUG
+  ep.status = kernel_status_ptr();
+#endif
   if (a.rope && (a.glu || a.act || a.residual || a.col_gate || a.sumsq || a.fp8 || a.out_fp32)) return cudaErrorInvalidValue;
 
   PushParams push;

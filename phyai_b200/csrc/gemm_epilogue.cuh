@@ -30,6 +30,7 @@ struct EpiParams {
   const RopeEpi* rope = nullptr;          // non-null: rotate + scatter instead of storing to `out`
   float* zero = nullptr;                  // optional fp32 scratch cleared by the first CTA (sum-of-squares
   int zero_n = 0;                         // accumulators that a later launch adds into)
+  int* status = nullptr;                  // debug build: where a failed index check is recorded
 };
 
 __device__ __forceinline__ float epi_act(float v, int act) {
@@ -116,6 +117,7 @@ __device__ __forceinline__ void epilogue_pass_t(const EpiParams& ep, const float
         const int rr = row + u * nwarps;
         if (rr >= row_end) continue;
         const int m = m0 + rr;
+        if (!PB_DEBUG_CHECK(m >= 0 && m < ep.M && n >= 0 && n < ep.N && ep.ldo >= (GLU ? ep.N / 2 : ep.N), ep.status)) continue;
         float* x = v[u];
         const __nv_bfloat16* res_row = nullptr;
         if constexpr (AUX) {
@@ -277,6 +279,7 @@ __device__ __forceinline__ void epilogue_rope(const EpiParams& ep, const float* 
           if (r < nsplit) { x[0] += part[r].x; x[1] += part[r].y; x[2] += part[r].z; x[3] += part[r].w; }
       }
       const int m = m0 + rr;
+      if (!PB_DEBUG_CHECK(m >= 0 && m < ep.M && rp.slots[m] >= 0 && rp.pos[m] >= 0, ep.status)) continue;
       float rscale = 1.f;
       if (ep.row_scale) {
         rscale = ep.row_scale[m];

@@ -24,6 +24,15 @@ enum KernelStatus : int {
   kStatusBadArg = 5,
 };
 
+// Index checks of the debug build (`python -m phyai_b200.build_ext --debug`, -DPHYAI_DEBUG=1): a failing
+// check records kStatusBadArg in the status word and evaluates to false so the caller skips the access;
+// nothing traps. In the regular build the macro is the constant `true` and costs nothing.
+#ifdef PHYAI_DEBUG
+#define PB_DEBUG_CHECK(cond, status_ptr) ((cond) ? true : (((status_ptr) != nullptr ? (void)atomicCAS((status_ptr), 0, int(::pb::kStatusBadArg)) : (void)0), false))
+#else
+#define PB_DEBUG_CHECK(cond, status_ptr) (true)
+#endif
+
 // bf16 -> fp32 as a shift of the bit pattern (exact). The conversion instruction the intrinsic can turn into
 // shares the 16-per-clock special-function pipe; a profile of the many-row norm showed that pipe at 140 % of its
 // sustained peak with DRAM at 42 %, and the shift form brought the kernel from 0.55 to 0.83 of the copy bandwidth.

@@ -1,7 +1,7 @@
 """Plugin ``pi0_wn``: data-parallel Pi0 (one replica per GPU, rank 0 routes the batch).
 
-Same routing as the Pi0.5 data-parallel plugin (header broadcast, one grouped point-to-point launch
-per step, all-gather of the action chunks); a Pi0 request carries one more tensor, the state vector.
+Same routing as the Pi0.5 data-parallel plugin (no header exchange, one grouped point-to-point launch
+per step that rank 0 does not wait for, gather of the action chunks); a Pi0 request carries one more tensor, the state vector.
 The reference ships data parallelism for Pi0.5 only (phyai/src/phyai/models/pi05/main_pi05_wn.py:42-138);
 its Pi0 batch sweep runs on one GPU (benchmark/bench_n_batch_ws1_pi0.py).
 """

@@ -6,8 +6,13 @@ occupies that partition's SMs; CUDA graphs captured on it inherit the restrictio
 (``runtime.capture_on_stream``).
 
 The driver calls go through a small ``DriverApi`` object so the partitioning arithmetic and the
-life-cycle are testable without a GPU; the real one binds the green-context entry points of
-cuda-python. Reference: phyai/src/phyai/vgpu/{vgpu,partition,topology,backend,state}.py.
+life-cycle are testable without a GPU. Two real backends: ``CudaDriver`` binds the green-context
+entry points of cuda-python and supports disjoint splits plus a remainder; ``TorchGreenDriver``
+wraps ``torch.cuda.green_contexts`` and, like the reference's torch backend, serves one shard per
+call (several of its contexts may share SMs). ``PHYAI_VGPU_BACKEND`` = ``cuda`` | ``torch`` picks one.
+Every :class:`vGPU` owns a ``torch.cuda.MemPool`` (on CUDA): allocations made inside ``activate()``
+come from that pool, so a partition's activations never fragment its neighbour's.
+Reference: phyai/src/phyai/vgpu/{vgpu,partition,topology,backend,state}.py, backends/torch.py:27-90.
 """
 
 from __future__ import annotations
@@ -120,6 +125,63 @@ class CudaDriver:
         self._ok(self.d.cuGreenCtxDestroy(ctx), "cuGreenCtxDestroy")
 
 
+class TorchGreenDriver:
+    """One shard per call through ``torch.cuda.green_contexts.GreenContext`` (no disjointness guarantee
+    between calls, no remainder: ``split`` with more than one count is refused)."""
+
+    def capability(self, device: int) -> tuple[int, int]:
+        import torch
+
+        return torch.cuda.get_device_capability(device)
+
+    def sm_count(self, device: int) -> int:
+        import torch
+
+        return torch.cuda.get_device_properties(device).multi_processor_count
+
+    def split(self, device: int, counts: Sequence[int]) -> list[tuple[Any, int]]:
+        if len(counts) != 1:
+            raise VGPURuntimeError("the torch backend makes one shard per call (its contexts may share SMs); "
+                                   "use the cuda backend for disjoint splits")
+        return [(("torch", int(counts[0])), int(counts[0])), (None, 0)]
+
+    def make_stream(self, device: int, resource: Any) -> tuple[Any, Any]:
+        import torch
+        from torch.cuda.green_contexts import GreenContext
+
+        _, n = resource
+        g = GreenContext.create(num_sms=n, device_id=device)
+        try:
+            stream = g.Stream()
+        except AttributeError:           # older binding: make a stream while the context is current
+            g.set_context()
+            try:
+                stream = torch.cuda.Stream(device=device)
+            finally:
+                g.pop_context()
+        return g, stream
+
+    def destroy(self, ctx: Any) -> None:
+        return None                      # released with the last reference
+
+
+def default_driver() -> DriverApi:
+    """``PHYAI_VGPU_BACKEND`` = ``torch`` | ``cuda`` (default: cuda-python when importable, else torch)."""
+    from ..env import envs
+
+    want = (envs.PHYAI_VGPU_BACKEND.get() or "").lower()
+    if want == "torch":
+        return TorchGreenDriver()
+    if want in ("", "cuda", "auto"):
+        try:
+            return CudaDriver()
+        except ImportError:
+            if want == "cuda":
+                raise
+            return TorchGreenDriver()
+    raise VGPURuntimeError(f"unknown vGPU backend {want!r} (cuda | torch)")
+
+
 @dataclass(frozen=True)
 class Shard:
     name: str
@@ -139,7 +201,7 @@ def init(device: int = 0, *, driver: DriverApi | None = None, world_size: int = 
     """Once per process, before any split. Refuses multi-rank jobs (each rank owns a whole GPU) and pre-Ampere GPUs."""
     if world_size > 1:
         raise VGPUNotApplicableError("SM partitioning is for single-GPU serving; multi-rank jobs own whole GPUs")
-    drv = driver if driver is not None else CudaDriver()
+    drv = driver if driver is not None else default_driver()
     if drv.capability(device)[0] < 8:
         raise VGPUNotApplicableError(f"green contexts need compute capability >= 8.0, device has {drv.capability(device)}")
     _STATE.update(driver=drv, device=device)
@@ -182,6 +244,14 @@ class vGPU:
 
     def __init__(self, shard: Shard) -> None:
         self.shard, self._closed = shard, False
+        self.mem_pool = None
+        try:
+            import torch
+
+            if isinstance(shard.stream, torch.cuda.Stream) and hasattr(torch.cuda, "MemPool"):
+                self.mem_pool = torch.cuda.MemPool()
+        except ImportError:  # pragma: no cover
+            pass
         _STATE["open"].append(self)
 
     name = property(lambda s: s.shard.name)
@@ -198,21 +268,24 @@ class vGPU:
             raise VGPURuntimeError(f"{self.name} is closed")
         from ..runtime import capture_on_stream
 
-        cm = contextlib.nullcontext()
+        cm, pool = contextlib.nullcontext(), contextlib.nullcontext()
         try:
             import torch
 
             if isinstance(self.stream, torch.cuda.Stream):
                 cm = torch.cuda.stream(self.stream)
+                if self.mem_pool is not None:
+                    pool = torch.cuda.use_mem_pool(self.mem_pool)
         except ImportError:  # pragma: no cover
             pass
-        with cm, capture_on_stream(self.stream):
+        with cm, pool, capture_on_stream(self.stream):
             yield self
 
     def close(self) -> None:
         if self._closed:
             return
         _driver().destroy(self.shard._ctx)
+        self.mem_pool = None
         self._closed = True
         if self in _STATE["open"]:
             _STATE["open"].remove(self)
@@ -232,5 +305,5 @@ def _reset_for_tests() -> None:
 
 
 __all__ = ["VGPUError", "VGPUNotApplicableError", "VGPURuntimeError", "VGPUDriverError", "get_sm_count_constraint", "round_up_sm_count",
-           "validate_total", "DriverApi", "CudaDriver", "Shard", "init", "split_device", "split_device_by_sm_count", "vGPU", "create_vgpus",
+           "validate_total", "DriverApi", "CudaDriver", "TorchGreenDriver", "default_driver", "Shard", "init", "split_device", "split_device_by_sm_count", "vGPU", "create_vgpus",
            "close_all"]
