@@ -191,6 +191,43 @@ def main() -> int:
             got = tp_model(lat, tt, cond)
             check(f"cosmos3.tp{world}{vs}[{it}]", got, want, 0.06)
 
+    # ---- the ctypes NCCL backend against the real library: eager, and replayed from a CUDA graph
+    try:
+        from phyai_b200.parallel.backend import Call, Mode, Op
+        from phyai_b200.parallel.backends.pynccl import PyNcclBackend
+
+        pn = PyNcclBackend(mesh, ["tp"])
+    except Exception as e:  # noqa: BLE001 - e.g. no libnccl that ctypes can load
+        pn = None
+        if rank == 0:
+            print(f"pynccl skipped: {type(e).__name__}: {e}", flush=True)
+    if pn is not None:
+        def call(op, x, extra=()):
+            return Call(op=op, axis="tp", mesh=mesh, dtype=x.dtype, nbytes=x.numel() * x.element_size(), mode=Mode.EAGER,
+                        device_type="cuda", extra=extra)
+
+        x = (torch.arange(24, device=dev, dtype=torch.float32).reshape(4, 6) + rank)
+        got = pn.execute(call(Op.ALL_REDUCE, x, ("sum",)), x, reduce="sum")
+        check("pynccl.all_reduce", got, nccl_sum(x), 1e-6)
+        got = pn.execute(call(Op.ALL_GATHER, x, (0,)), x, dim=0)
+        want = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(want, x)
+        check("pynccl.all_gather", got, torch.cat(want), 1e-6)
+        got = pn.execute(call(Op.BROADCAST, x, (world - 1,)), x, src=world - 1)
+        check("pynccl.broadcast", got, torch.arange(24, device=dev, dtype=torch.float32).reshape(4, 6) + world - 1, 1e-6)
+        xb = torch.ones(64, 128, device=dev, dtype=torch.bfloat16) * (rank + 1)
+        pn.execute(call(Op.ALL_REDUCE, xb, ("sum",)), xb, reduce="sum")        # warm the path before capture
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            yb = pn.execute(call(Op.ALL_REDUCE, xb, ("sum",)), xb, reduce="sum")
+        for k in (1, 2):
+            xb.fill_(float(k * (rank + 1)))
+            graph.replay()
+            torch.cuda.synchronize()
+            check(f"pynccl.graph[{k}]", yb, torch.full((64, 128), float(k * world * (world + 1) // 2)), 1e-2)
+        pn.close()
+
     torch.cuda.synchronize()
     status = ops.kernel_status()
     if status != 0:

@@ -27,7 +27,7 @@ def test_bounded_wait_reports_instead_of_hanging():
     assert torch.ones(4, device="cuda").sum().item() == 4   # the context is still usable
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_peer_collectives(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
