@@ -306,6 +306,17 @@ Tensor gdn_decode(const Tensor& q, const Tensor& k, const Tensor& v, const Tenso
   return out;
 }
 
+Tensor snake(const Tensor& x, const Tensor& alpha, const Tensor& beta) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 3 && x.is_contiguous(), "snake: x must be a contiguous CUDA [B, C, T] tensor");
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kFloat, "snake: bf16 or fp32");
+  TORCH_CHECK(alpha.numel() == x.size(1) && beta.numel() == x.size(1) && alpha.is_contiguous() && beta.is_contiguous(),
+              "snake: alpha, beta [C]");
+  Tensor out = at::empty_like(x);
+  check(pb::snake_launch(x.data_ptr(), out.data_ptr(), x.scalar_type() == at::kBFloat16, f32(OptT(alpha)), f32(OptT(beta)),
+                         int(x.size(1)), x.size(2), x.numel(), cur_stream()), "snake_launch");
+  return out;
+}
+
 void cfg_combine(const Tensor& cond, const Tensor& uncond, double g, const OptT& out,
                  const OptT& x_fp32, double dt) {
   TORCH_CHECK(cond.is_contiguous() && uncond.is_contiguous() && cond.numel() == uncond.numel(), "cfg_combine: layout");
@@ -465,6 +476,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("out") = py::none(), py::arg("x_fp32") = py::none(), py::arg("dt") = 0.0);
   m.def("scatter_rows", &scatter_rows, py::arg("src"), py::arg("dst"), py::arg("rows") = py::none());
   m.def("quant_fp8", &quant_fp8);
+  m.def("snake", &snake);
   m.def("gdn_decode", &gdn_decode, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("g"), py::arg("beta"),
         py::arg("state_pool"), py::arg("state_indices"), py::arg("scale"), py::arg("l2norm") = true);
   m.def("kernel_status", [] { return pb::read_and_clear_kernel_status(); });

@@ -851,4 +851,39 @@ cudaError_t quant_fp8_launch(const __nv_bfloat16* x, int rows, int D, int ldx, u
   return cudaGetLastError();
 }
 
+
+// ---------------------------------------------------------------------- snake
+// y[b, c, t] = x + sin^2(alpha[c] x) / (beta[c] + 1e-9), x of shape [B, C, T] (T contiguous). One pass,
+// fp32 math; the reference composes it from five elementwise ATen kernels on an fp32 copy
+// (phyai/src/phyai/layers/activation.py:40-67).
+template <typename T>
+__global__ void snake_kernel(const T* x, T* y, const float* alpha, const float* beta, int C, long long Tn, long long total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int c = int((i / Tn) % C);
+    const float a = alpha[c], ib = 1.f / (beta[c] + 1e-9f);
+    float v;
+    if constexpr (sizeof(T) == 2) v = bf2f(reinterpret_cast<const __nv_bfloat16*>(x)[i]);
+    else v = reinterpret_cast<const float*>(x)[i];
+    const float sn = sinf(a * v);
+    const float o = v + sn * sn * ib;
+    if constexpr (sizeof(T) == 2) reinterpret_cast<__nv_bfloat16*>(y)[i] = __float2bfloat16(o);
+    else reinterpret_cast<float*>(y)[i] = o;
+  }
+}
+cudaError_t snake_launch(const void* x, void* y, int is_bf16, const float* alpha, const float* beta, int C, long long T,
+                         long long total, cudaStream_t s) {
+  if (total <= 0) return cudaSuccess;
+  if (C <= 0 || T <= 0) return cudaErrorInvalidValue;
+  const int threads = 256;
+  long long blocks = (total + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (is_bf16) PB_LAUNCH(snake_kernel<__nv_bfloat16>, unsigned(blocks), threads, s, reinterpret_cast<const __nv_bfloat16*>(x),
+                         reinterpret_cast<__nv_bfloat16*>(y), alpha, beta, C, T, total);
+  else PB_LAUNCH(snake_kernel<float>, unsigned(blocks), threads, s, reinterpret_cast<const float*>(x),
+                 reinterpret_cast<float*>(y), alpha, beta, C, T, total);
+  return cudaGetLastError();
+}
+
 }  // namespace pb

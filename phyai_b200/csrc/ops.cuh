@@ -70,6 +70,10 @@ cudaError_t gdn_decode_launch(const void* q, const void* k, const void* v, const
                               float* state_pool, const long long* state_indices, void* out, int out_bf16, int B, int H,
                               int Dk, int Dv, float scale, int l2norm, cudaStream_t stream);
 
+// Snake activation over [B, C, T] (alpha, beta fp32 [C], already exponentiated).
+cudaError_t snake_launch(const void* x, void* y, int is_bf16, const float* alpha, const float* beta, int C, long long T,
+                         long long total, cudaStream_t s);
+
 cudaError_t axpy_launch(void* x, int x_fp32, const __nv_bfloat16* v, float dt, long long n,
                         cudaStream_t s);
 

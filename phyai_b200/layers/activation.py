@@ -1,7 +1,8 @@
 """Snake activation ``x + sin^2(alpha x) / beta`` with per-channel log-scale parameters.
 
-The checkpoint stores ``log alpha`` / ``log beta``; ``post_load`` exponentiates them once.
-Reference: phyai/src/phyai/layers/activation.py:12-67.
+The checkpoint stores ``log alpha`` / ``log beta``; ``post_load`` exponentiates them once. On CUDA
+(bf16 / fp32, ``(B, C, T)``) the forward is one launch of ``snake_kernel`` (``csrc/ops.cu``); elsewhere the
+PyTorch statement below. Reference: phyai/src/phyai/layers/activation.py:12-67.
 """
 
 from __future__ import annotations
@@ -34,6 +35,11 @@ class Snake1d(nn.Module):
         a, b = self.alpha.float(), self.beta.float()
         if self.logscale and not self._ready:
             a, b = a.exp(), b.exp()
+        if x.is_cuda and x.dim() == 3 and x.dtype in (torch.bfloat16, torch.float32):
+            from .. import ops
+
+            if ops.available():
+                return ops.snake(x, a, b)
         xf = x.float()
         return (xf + torch.sin(a * xf).pow(2) / (b + 1e-9)).to(x.dtype)
 

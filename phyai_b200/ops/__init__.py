@@ -230,6 +230,12 @@ def gdn_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tenso
                             beta.contiguous().to(q.dtype), state_pool, idx, float(sc), bool(use_qk_l2norm))
 
 
+def snake(x: torch.Tensor, alpha: torch.Tensor, beta: torch.Tensor) -> torch.Tensor:
+    """``x + sin^2(alpha x) / (beta + 1e-9)`` over ``(B, C, T)`` in one pass; ``alpha`` / ``beta`` are the
+    per-channel scales (already exponentiated), any shape with C elements."""
+    return ext().snake(x.contiguous(), alpha.reshape(-1).float().contiguous(), beta.reshape(-1).float().contiguous())
+
+
 def gated_act(x: torch.Tensor, act: str, *, interleaved: bool = False,
               out: Optional[torch.Tensor] = None) -> torch.Tensor:
     if out is None:

@@ -484,3 +484,23 @@ def test_gdn_decode_kernel_matches_the_recurrence(dtype):
     untouched = [i for i in range(6) if i not in (5, 0, 2)]
     assert ops.launch_counter() > 0 and torch.isfinite(pool[untouched]).all()
     _status_ok()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_snake_kernel(dtype):
+    from phyai_b200.layers.activation import Snake1d
+
+    g0 = torch.Generator().manual_seed(3)
+    layer = Snake1d(96, dtype=torch.float32, device=DEV)
+    with torch.no_grad():
+        layer.alpha.copy_(torch.randn(1, 96, 1, generator=g0) * 0.3)
+        layer.beta.copy_(torch.randn(1, 96, 1, generator=g0) * 0.3)
+    layer.post_load()
+    x = torch.randn(2, 96, 1001, generator=g0).to(DEV, dtype)
+    y = layer(x)
+    a, b = layer.alpha.float(), layer.beta.float()
+    want = x.float() + torch.sin(a * x.float()).pow(2) / (b + 1e-9)
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+    torch.testing.assert_close(y.float(), want, atol=tol, rtol=tol)
+    assert y.dtype == dtype
+    _status_ok()
