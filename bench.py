@@ -49,6 +49,8 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--lang-len", type=int, default=200, help="real prompt tokens per robot")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--dtype", choices=("bf16", "fp8_block"), default="bf16",
+                    help="fp8_block: prefix decoder and action expert in block-scaled fp8 (ours arm; not the headline dtype)")
     ap.add_argument("--no-cosmos3", action="store_true", help="skip the Cosmos3 TP / CFG block")
     ap.add_argument("--cosmos3-model", default="super", help="geometry of the Cosmos3 block (super | nano | small)")
     ap.add_argument("--cosmos3-steps", type=int, default=6)
@@ -189,11 +191,17 @@ def run(args: argparse.Namespace) -> dict:
                        parallel=ParallelConfig(world_size=N, dp_size=N),
                        runtime=RuntimeConfig(use_cuda_graph=not args.no_graph))
     shape = [[224, 224, 3]] * 3
+    qkw = {}
+    if args.dtype == "fp8_block":
+        if args.impl == "reference":
+            # the reference reads its quantisation from a checkpoint's config; this benchmark builds random weights in memory
+            raise RuntimeError("the reference arm serves fp8 only from an fp8 checkpoint on disk; none is generated here")
+        qkw = {"quantization": "fp8_block"}
     if N == 1:
-        engine = Engine(EngineArgs("pi05", PI05Args(checkpoint_dir=None, max_batch_size=1, inputs_image_shape=shape), cfg))
+        engine = Engine(EngineArgs("pi05", PI05Args(checkpoint_dir=None, max_batch_size=1, inputs_image_shape=shape, **qkw), cfg))
     else:
         engine = Engine(EngineArgs("pi05_wn", PI05WNArgs(checkpoint_dir=None, max_batch_size=N,
-                                                         inputs_image_shape=shape), cfg))
+                                                         inputs_image_shape=shape, **qkw), cfg))
 
     host = make_request_tensors(torch, N, args.lang_len)
     dev_in = [t.to(device) for t in host]
@@ -276,7 +284,7 @@ def run(args: argparse.Namespace) -> dict:
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(mean, 4),
         "higher_is_better": False, "scaling": "weak",
         "vs_baseline": (p50 / BASELINE_P50_MS) if BASELINE_P50_MS else None,
-        "dtype": "bf16", "data": "synthetic (uniform pixels, uniform prompt ids, N(0,1) noise; random-init weights)",
+        "dtype": args.dtype, "data": "synthetic (uniform pixels, uniform prompt ids, N(0,1) noise; random-init weights)",
         "impl": args.impl, "p99_ms": round(p99, 4), "samples_per_s": round(N / (p50 * 1e-3), 2),
         "config": {"model": "pi05_base geometry (SigLIP-So400m + Gemma-2B prefix + Gemma-300M expert)",
                    "global_batch": N, "per_gpu_batch": 1, "seq_len": 768 + args.lang_len, "prompt_tokens": args.lang_len,

@@ -118,6 +118,19 @@ def main() -> None:
             tf = 4 * S * (S + T) * D * hq / t_o / 1e9
             rows.append(dict(kernel="attention", shape=name, ours_ms=round(t_o, 4), sdpa_ms=round(t_s, 4), tflops=round(tf, 1),
                              frac_of_measured_bf16=round(tf / peaks["bf16_tflops"], 3)))
+        # the action expert's joint attention: 50 query tokens x 8 heads on one KV head of 256, 968 + 50 KV rows,
+        # KV split over a cluster of 8 (the latency kernel, attention_tc.cu)
+        if not a.only or a.only == "pi05.expert.joint":
+            S, T, hq, hkv, D = 50, 1018, 8, 1, 256
+            q = torch.randn(S, hq, D, device=dev, dtype=bf)
+            k, v = torch.randn(T, hkv, D, device=dev, dtype=bf), torch.randn(T, hkv, D, device=dev, dtype=bf)
+            o, z = torch.empty_like(q), torch.zeros(1, dtype=torch.int32, device=dev)
+            ql, kl = torch.full((1,), S, dtype=torch.int32, device=dev), torch.full((1,), T, dtype=torch.int32, device=dev)
+            t_o = bench(lambda: ops.attention(q, k, v, o, z, ql, z, kl, max_q_len=S, splits=8, sm_scale=D ** -0.5))
+            qq, kk, vv = (t.transpose(0, 1)[None] for t in (q, k, v))
+            t_s = float("nan") if a.no_baselines else bench(lambda: torch.nn.functional.scaled_dot_product_attention(qq, kk, vv, enable_gqa=True))
+            rows.append(dict(kernel="attention", shape="pi05.expert.joint", ours_ms=round(t_o, 4), sdpa_ms=round(t_s, 4),
+                             kv_bytes=2 * T * D * 2, gbs=round(2 * T * D * 2 / t_o / 1e6, 1)))
     if a.set in ("norm", "all"):
         for name, (R, D) in {"rms.7040x5120": (7040, 5120), "rms.65536x4096": (65536, 4096)}.items():
             if a.only and name != a.only:

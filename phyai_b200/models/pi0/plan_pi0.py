@@ -20,8 +20,10 @@ from .modeling_pi0 import PI0Model
 class PI0Plan(PI05Plan):
     suffix_extra = 1
 
-    def __init__(self, model: PI0Model, *, max_batch_size: int = 1, num_images: int = 3, device="cuda") -> None:
-        super().__init__(model, max_batch_size=max_batch_size, num_images=num_images, device=device)
+    def __init__(self, model: PI0Model, *, max_batch_size: int = 1, num_images: int = 3, device="cuda",
+                 quantization: str | None = None) -> None:
+        # block-scaled fp8 covers the shared prefix decoder; the Pi0 expert keeps its bf16 launch sequence
+        super().__init__(model, max_batch_size=max_batch_size, num_images=num_images, device=device, quantization=quantization)
         cfg, dev, B = self.cfg, self.device, self.B
         He = cfg.expert.hidden_size
         bf = torch.bfloat16
@@ -53,6 +55,8 @@ class PI0Plan(PI05Plan):
         te = heads.time_embedding(ts).to(torch.bfloat16).float()
         bias = te @ wt.t() + heads.action_time_mlp_in.bias.float() + wa @ heads.action_in_proj.bias.float()
         self.time_bias = bias.to(torch.bfloat16).contiguous()
+        if self.fp8:
+            self._build_fp8_weights(expert=False)
         if self.fold_norms:
             self._fold_prefix()
             # Gemma RMSNorm weights (1 + w) folded into the weights that consume the normed rows; the

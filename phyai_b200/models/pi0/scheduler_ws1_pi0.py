@@ -38,7 +38,7 @@ class PI0WS1Scheduler(PI05WS1Scheduler):
 
         ops.set_pdl(os.environ.get("PHYAI_PDL", "1") not in ("0", "false", "off"))
         self.plan = PI0Plan(self.model, max_batch_size=self.max_batch_size, num_images=self.num_images,
-                            device=self.device)
+                            device=self.device, quantization=getattr(self, "quantization", None))
         self.plan.build_modulation_tables()
 
     def _validate(self, r: PI0Request) -> int:  # type: ignore[override]

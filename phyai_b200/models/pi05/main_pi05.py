@@ -55,6 +55,7 @@ class PI05Args(EntryArgs):
     vision_params_dtype: torch.dtype | None = None  # torch.float32 = vision tower parity path
     inputs_image_shape: list[list[int]] | None = None  # one [H, W, C] per camera; None = 3 cameras
     random_init_seed: int | None = 0               # used only when checkpoint_dir is None
+    quantization: str | None = None                # "fp8_block": serve prefix decoder + expert in block-scaled fp8
 
 
 def resolve_num_images(inputs_image_shape, num_channels: int) -> int:
@@ -103,7 +104,8 @@ class PI05Entry(Entry):
         self.model = self.build_model(args)
         n_img = resolve_num_images(args.inputs_image_shape, self.model.config.vision.num_channels)
         self.scheduler = PI05WS1Scheduler(self.model, max_batch_size=args.max_batch_size, num_images=n_img,
-                                          device=eng.device.target, use_cuda_graph=eng.runtime.use_cuda_graph)
+                                          device=eng.device.target, use_cuda_graph=eng.runtime.use_cuda_graph,
+                                          quantization=args.quantization)
         self.scheduler.setup()
 
     def step(self, request: PI05Request) -> torch.Tensor:  # type: ignore[override]

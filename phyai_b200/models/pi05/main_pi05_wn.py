@@ -35,7 +35,7 @@ class PI05WNEntry(PI05Entry):
         self.model = self.build_model(args)
         n_img = resolve_num_images(args.inputs_image_shape, self.model.config.vision.num_channels)
         local = PI05WS1Scheduler(self.model, max_batch_size=per_rank, num_images=n_img, device=eng.device.target,
-                                 use_cuda_graph=eng.runtime.use_cuda_graph)
+                                 use_cuda_graph=eng.runtime.use_cuda_graph, quantization=args.quantization)
         self.scheduler = PI05WNScheduler(local, device=eng.device.target)
         self.scheduler.setup()
 

@@ -62,13 +62,23 @@ class PI05Plan:
     #: run the Euler loop as one persistent kernel (``csrc/expert_stack.cu``) where the geometry allows it; off by
     #: default: at batch 1 it measured 16.5 ms for the ten steps against 9.3 ms launch by launch
     use_expert_kernel = bool(envs.PHYAI_PI05_EXPERT_KERNEL.get())
+    #: serve the prefix decoder and the action expert in block-scaled fp8 (``PHYAI_PI05_FP8=1`` or
+    #: ``quantization="fp8_block"``): e4m3 weights with 128 x 128 scales, activations quantised per 1 x 128 block
+    #: by the norm kernels / a quantiser in front of every GEMM; the vision tower (4304-wide MLP) stays bf16
+    serve_fp8 = bool(envs.PHYAI_PI05_FP8.get())
     _side_stream = None
 
     def __init__(self, model: PI05Model, *, max_batch_size: int = 1, num_images: int = 3,
-                 device: torch.device | str = "cuda") -> None:
+                 device: torch.device | str = "cuda", quantization: str | None = None) -> None:
         cfg = model.config
         self.model, self.cfg = model, cfg
         self.device = torch.device(device)
+        if quantization not in (None, "bf16", "fp8_block"):
+            raise ValueError(f"unknown quantization {quantization!r} (bf16 | fp8_block)")
+        self.fp8 = quantization == "fp8_block" or (quantization is None and self.serve_fp8)
+        if self.fp8:
+            # the fp8 GEMM has no norm / rotary epilogues: the unfolded launch sequence, no second stream
+            self.fold_norms, self.overlap_first_step, self.use_expert_kernel = False, False, False
         self.B, self.n_img = max_batch_size, num_images
         dt = torch.bfloat16
         if model.params_dtype != dt or model.vision.compute_dtype != dt:
@@ -148,6 +158,19 @@ class PI05Plan:
         self.e_kvptr = torch.tensor([1 + b * self.slab for b in range(B)], dtype=torch.int32, device=dev)
         self.e_kvlen = torch.zeros(B, dtype=torch.int32, device=dev)
         self.out = buf(B, self.C, cfg.max_action_dim)
+        if self.fp8:
+            f8 = torch.float8_e4m3fn
+            for name, width in (("H", H), ("Q", t.num_attention_heads * t.head_dim), ("I", t.intermediate_size)):
+                if width % 128:
+                    raise ValueError(f"block-scaled fp8 needs widths that are multiples of 128, got {width}")
+                setattr(self, f"p8_{name}", torch.zeros(Mp, width, dtype=f8, device=dev))
+                setattr(self, f"p8s_{name}", torch.zeros(Mp, width // 128, dtype=torch.float32, device=dev))
+            for name, width in (("H", He), ("Q", t.num_attention_heads * t.head_dim), ("I", e.intermediate_size)):
+                if width % 128:
+                    raise ValueError(f"block-scaled fp8 needs widths that are multiples of 128, got {width}")
+                setattr(self, f"e8_{name}", torch.zeros(Me, width, dtype=f8, device=dev))
+                setattr(self, f"e8s_{name}", torch.zeros(Me, width // 128, dtype=torch.float32, device=dev))
+            self.w8: dict[str, list[tuple[torch.Tensor, torch.Tensor]]] = {}
         self.mod_in: list[torch.Tensor] = []
         self.mod_post: list[torch.Tensor] = []
         self.mod_final: torch.Tensor | None = None
@@ -176,6 +199,19 @@ class PI05Plan:
             self._build_expert_kernel(stack)
             self._fold_modulation(stack)
             self._fold_prefix()
+        if self.fp8:
+            self._build_fp8_weights(expert=True)
+
+    def _build_fp8_weights(self, *, expert: bool) -> None:
+        """Block-scaled e4m3 copies (or the stored tensors of an fp8 checkpoint) of the decoder projections."""
+        from ...ops.fp8_block import layer_weight_fp8
+
+        groups = [("p", self.model.paligemma_lm.layers)] + ([("e", self.model.expert_stack.layers)] if expert else [])
+        for tag, layers in groups:
+            self.w8[f"{tag}.qkv"] = [layer_weight_fp8(l.attn.qkv) for l in layers]
+            self.w8[f"{tag}.o"] = [layer_weight_fp8(l.attn.o) for l in layers]
+            self.w8[f"{tag}.gate_up"] = [layer_weight_fp8(l.mlp.gate_up) for l in layers]
+            self.w8[f"{tag}.down"] = [layer_weight_fp8(l.mlp.down) for l in layers]
 
     def _expert_geometry(self) -> ExpertGeometry:
         cfg, e, t = self.cfg, self.cfg.expert, self.cfg.text
@@ -372,6 +408,33 @@ class PI05Plan:
                 ops.gemm(h, self.pfold_gate_up[li], act, row_scale=ss_post, row_rms=rms, act="gelu_tanh", glu=True)
                 ops.gemm(act, layer.mlp.down.weight, h, residual=h, sumsq=ss_in, zero=ss_post)
             return
+        if self.fp8:
+            from ...ops.fp8_block import gemm_fp8_block as g8, quantize_rows_into as q8
+
+            x8, xs = self.p8_H[:Mp], self.p8s_H[:Mp]
+            a8, as_ = self.p8_Q[:Mp], self.p8s_Q[:Mp]
+            m8, ms = self.p8_I[:Mp], self.p8s_I[:Mp]
+            W = self.w8
+            for li, layer in enumerate(lm.layers):
+                kpool, vpool = self.pool.layer(li)
+                ops.norm(h, "gemma_rms", weight=layer.input_layernorm.weight, eps=t.rms_norm_eps, out=x, y8=x8, y8_scale=xs, y8_block=128)
+                g8(x8, xs, *W["p.qkv"][li], qkv)
+                ops.rope_kv(qkv, Hq, Hkv, D, q, pos=self.p_pos[:Mp], cos_sin=self.cos_sin, k_pool=kpool, v_pool=vpool,
+                            slots=self.p_slots[:Mp])
+                if kv_events is not None:
+                    kv_events[li].record(torch.cuda.current_stream())
+                if li == last:
+                    break
+                ops.attention(q3, kpool, vpool, a3, self.p_qstart, self.p_qlen, self.p_kvptr, self.p_kvlen,
+                              max_q_len=n_per, splits=self.prefix_splits, sm_scale=D ** -0.5)
+                q8(attn, a8, as_)
+                g8(a8, as_, *W["p.o"][li], h, residual=h)
+                ops.norm(h, "gemma_rms", weight=layer.post_attention_layernorm.weight, eps=t.rms_norm_eps, out=x, y8=x8, y8_scale=xs,
+                         y8_block=128)
+                g8(x8, xs, *W["p.gate_up"][li], act, act="gelu_tanh", glu=True)
+                q8(act, m8, ms)
+                g8(m8, ms, *W["p.down"][li], h, residual=h)
+            return
         for li, layer in enumerate(lm.layers):
             kpool, vpool = self.pool.layer(li)
             ops.norm(h, "gemma_rms", weight=layer.input_layernorm.weight, eps=t.rms_norm_eps, out=x)
@@ -396,6 +459,8 @@ class PI05Plan:
         self.x_t.copy_(self.noise.view(Me, -1))
         if self.fold_norms:
             return self._expert_folded()
+        if self.fp8:
+            return self._expert_fp8()
         for i in range(cfg.num_inference_steps):
             ops.gemm(self.x_t, heads.action_in_proj.weight, h, bias=heads.action_in_proj.bias)
             for li, layer in enumerate(stack.layers):
@@ -411,6 +476,40 @@ class PI05Plan:
                 ops.norm(h, "ada_rms", mod=m_post, group=Me, eps=e.rms_norm_eps, out=x)
                 ops.gemm(x, layer.mlp.gate_up.weight, self.e_act, act="gelu_tanh", glu=True)
                 ops.gemm(self.e_act, layer.mlp.down.weight, h, residual=h, col_gate=m_post[0, 2 * He:])
+            ops.norm(h, "ada_rms", mod=self.mod_final[i:i + 1], group=Me, eps=e.rms_norm_eps, out=x)
+            ops.gemm(x, heads.action_out_proj.weight, self.e_v, bias=heads.action_out_proj.bias)
+            ops.axpy(self.x_t, self.e_v, self.dt)
+        self.out.view(Me, -1).copy_(self.x_t)
+
+    def _expert_fp8(self) -> None:
+        """The Euler loop with block-scaled fp8 projections: the AdaRMS kernels emit the e4m3 rows and their
+        1 x 128 scales directly, attention output and the GeGLU product pass through the quantiser; gates and
+        residual adds stay in the GEMM epilogues. Ten launches per block."""
+        from ...ops.fp8_block import gemm_fp8_block as g8, quantize_rows_into as q8
+
+        cfg, e, t = self.cfg, self.cfg.expert, self.cfg.text
+        heads, stack = self.model.heads, self.model.expert_stack
+        Hq, Hkv, D, He, Me = t.num_attention_heads, t.num_key_value_heads, t.head_dim, e.hidden_size, self.Me
+        h, x, W = self.e_h, self.e_x, self.w8
+        q3, a3 = self.e_q.unflatten(1, (Hq, D)), self.e_attn.unflatten(1, (Hq, D))
+        x8, xs, a8, as_, m8, ms = self.e8_H, self.e8s_H, self.e8_Q, self.e8s_Q, self.e8_I, self.e8s_I
+        for i in range(cfg.num_inference_steps):
+            ops.gemm(self.x_t, heads.action_in_proj.weight, h, bias=heads.action_in_proj.bias)
+            for li, layer in enumerate(stack.layers):
+                kpool, vpool = self.pool.layer(li)
+                m_in, m_post = self.mod_in[li][i:i + 1], self.mod_post[li][i:i + 1]
+                ops.norm(h, "ada_rms", mod=m_in, group=Me, eps=e.rms_norm_eps, out=x, y8=x8, y8_scale=xs, y8_block=128)
+                g8(x8, xs, *W["e.qkv"][li], self.e_qkv)
+                ops.rope_kv(self.e_qkv, Hq, Hkv, D, self.e_q, pos=self.e_pos, cos_sin=self.cos_sin, k_pool=kpool,
+                            v_pool=vpool, slots=self.e_slots)
+                ops.attention(q3, kpool, vpool, a3, self.e_qstart, self.e_qlen, self.e_kvptr, self.e_kvlen,
+                              max_q_len=self.C, splits=self.expert_splits, sm_scale=D ** -0.5)
+                q8(self.e_attn, a8, as_)
+                g8(a8, as_, *W["e.o"][li], h, residual=h, col_gate=m_in[0, 2 * He:])
+                ops.norm(h, "ada_rms", mod=m_post, group=Me, eps=e.rms_norm_eps, out=x, y8=x8, y8_scale=xs, y8_block=128)
+                g8(x8, xs, *W["e.gate_up"][li], self.e_act, act="gelu_tanh", glu=True)
+                q8(self.e_act, m8, ms)
+                g8(m8, ms, *W["e.down"][li], h, residual=h, col_gate=m_post[0, 2 * He:])
             ops.norm(h, "ada_rms", mod=self.mod_final[i:i + 1], group=Me, eps=e.rms_norm_eps, out=x)
             ops.gemm(x, heads.action_out_proj.weight, self.e_v, bias=heads.action_out_proj.bias)
             ops.axpy(self.x_t, self.e_v, self.dt)

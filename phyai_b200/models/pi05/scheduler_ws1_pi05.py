@@ -40,7 +40,8 @@ class PI05Request:
 
 class PI05WS1Scheduler(Scheduler):
     def __init__(self, model: PI05Model, *, max_batch_size: int = 1, num_images: int = 3,
-                 device: torch.device | str | None = None, use_cuda_graph: bool = True) -> None:
+                 device: torch.device | str | None = None, use_cuda_graph: bool = True,
+                 quantization: str | None = None) -> None:
         if max_batch_size <= 0 or num_images <= 0:
             raise ValueError("max_batch_size and num_images must be positive")
         self.model, self.cfg = model, model.config
@@ -53,6 +54,7 @@ class PI05WS1Scheduler(Scheduler):
                          and model.vision.compute_dtype == torch.bfloat16)
         self.use_cuda_graph = bool(use_cuda_graph) and self.use_plan
         self.plan: PI05Plan | None = None
+        self.quantization = quantization          # None | "bf16" | "fp8_block" (see PI05Plan)
         self.graphs = CudaGraphRegistry()
         self.generator: torch.Generator | None = None
 
@@ -65,7 +67,7 @@ class PI05WS1Scheduler(Scheduler):
 
         ops.set_pdl(os.environ.get("PHYAI_PDL", "1") not in ("0", "false", "off"))
         self.plan = PI05Plan(self.model, max_batch_size=self.max_batch_size, num_images=self.num_images,
-                             device=self.device)
+                             device=self.device, quantization=self.quantization)
         self.plan.build_modulation_tables()
 
     def bucket_for(self, max_lang: int) -> int:

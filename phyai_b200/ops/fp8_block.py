@@ -44,4 +44,24 @@ def quantize_weight_block(w: torch.Tensor, block: int = 128) -> tuple[torch.Tens
     return q, scale
 
 
-__all__ = ["gemm_fp8_block", "ref_gemm_fp8_block", "quantize_weight_block"]
+def quantize_rows_into(x: torch.Tensor, y8: torch.Tensor, scale: torch.Tensor, block: int = 128) -> None:
+    """bf16 rows -> e4m3 with one scale per 1 x ``block`` group, into caller-owned buffers (no allocation:
+    what a captured serving plan calls between a bf16 producer and a block-scaled GEMM)."""
+    ext().quant_fp8(x, y8, scale, block)
+
+
+def layer_weight_fp8(layer) -> tuple[torch.Tensor, torch.Tensor]:
+    """Block-scaled e4m3 weight and scales of a linear layer: taken as stored when the layer was built from a
+    block-fp8 checkpoint, quantised here (128 x 128 blocks, amax / 448) when it holds bf16 / fp16 / fp32."""
+    w = layer.weight
+    if w.dtype == torch.float8_e4m3fn:
+        ws = getattr(layer, "weight_scale", None)
+        if ws is None or ws.dim() != 2:
+            raise ValueError("fp8 layer without 2-D block scales: only fp8_block_128_128 weights can be served as stored")
+        return w.data, ws.data.float().contiguous()
+    if w.shape[1] % 128:
+        raise ValueError(f"block-scaled fp8 needs in_features % 128 == 0, got {w.shape[1]}")
+    return quantize_weight_block(w.data)
+
+
+__all__ = ["gemm_fp8_block", "ref_gemm_fp8_block", "quantize_weight_block", "quantize_rows_into", "layer_weight_fp8"]

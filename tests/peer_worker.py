@@ -226,6 +226,12 @@ def main() -> int:
             graph.replay()
             torch.cuda.synchronize()
             check(f"pynccl.graph[{k}]", yb, torch.full((64, 128), float(k * world * (world + 1) // 2)), 1e-2)
+        # NCCL counts a captured collective as a reference on its communicator: the graph goes first,
+        # otherwise destroying the communicator waits for it forever
+        graph.reset()
+        del graph, yb
+        torch.cuda.synchronize()
+        dist.barrier()
         pn.close()
 
     torch.cuda.synchronize()

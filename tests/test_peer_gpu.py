@@ -1,6 +1,7 @@
 """Peer-memory collectives on real GPUs: bounded waits on one GPU, the fused kernels on two or more."""
 
 import os
+import signal
 import subprocess
 import sys
 from pathlib import Path
@@ -35,6 +36,14 @@ def test_peer_collectives(world):
     port = 29600 + world
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
            "127.0.0.1", "--master-port", str(port), str(ROOT / "tests" / "peer_worker.py")]
-    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
-    tail = (r.stdout + r.stderr)[-4000:]
-    assert r.returncode == 0 and "PEER_OK" in r.stdout, tail
+    # own process group: if the ranks ever stall, the whole tree (launcher + workers) is ended, not just the launcher,
+    # and the pipes close so that the failure is reported at once
+    proc = subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, start_new_session=True)
+    try:
+        out, err = proc.communicate(timeout=420)
+    except subprocess.TimeoutExpired:
+        os.killpg(proc.pid, signal.SIGKILL)
+        out, err = proc.communicate()
+        pytest.fail("peer worker did not finish within 420 s: " + (out + err)[-3000:])
+    tail = (out + err)[-4000:]
+    assert proc.returncode == 0 and "PEER_OK" in out, tail

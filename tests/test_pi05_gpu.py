@@ -112,3 +112,40 @@ def test_pi0_plan_matches_eager(batch, overlap, monkeypatch):
     rel = (out.float() - ref.float()).abs().max() / ref.float().abs().max()
     assert rel < 5e-2, rel
     eng.close()
+
+
+@pytest.mark.parametrize("batch", [1, 2])
+def test_fp8_block_plan_tracks_the_bf16_plan(batch):
+    """Prefix decoder and action expert served in block-scaled fp8 (weights quantised at plan build, activations by
+    the norm kernels / the quantiser): the action chunk stays within fp8 noise of the bf16 plan and of the eager oracle."""
+    from phyai_b200 import ops
+    from phyai_b200.engine import Engine, EngineArgs
+    from phyai_b200.engine_config import DeviceConfig, EngineConfig, RuntimeConfig
+    from phyai_b200.models.pi05.main_pi05 import PI05Args
+    from phyai_b200.models.pi05.scheduler_ws1_pi05 import PI05Request
+
+    cfg = _mid_config()
+    ecfg = EngineConfig(device=DeviceConfig("cuda:0", torch.bfloat16), runtime=RuntimeConfig(use_cuda_graph=True))
+    g = torch.Generator().manual_seed(40 + batch)
+    lens = torch.tensor([31, 5][:batch])
+    req = PI05Request((torch.rand(batch, 2, 3, 56, 56, generator=g) * 2 - 1).bfloat16().cuda(),
+                      torch.randint(0, 1024, (batch, 48), generator=g).cuda(), lens.cuda(),
+                      torch.randn(batch, 50, 32, generator=g).bfloat16().cuda())
+    outs = {}
+    for q in ("fp8_block", None):
+        eng = Engine(EngineArgs("pi05", PI05Args(config=cfg, max_batch_size=2, inputs_image_shape=[[56, 56, 3]] * 2, quantization=q), ecfg))
+        plan = eng.entry.scheduler.plan
+        assert plan.fp8 == (q == "fp8_block")
+        if q:
+            assert plan.w8["p.qkv"][0][0].dtype == torch.float8_e4m3fn and not plan.fold_norms
+        outs[q] = eng.step(req).float()
+        again = eng.step(req).float()
+        torch.cuda.synchronize()
+        assert ops.kernel_status() == 0 and torch.equal(outs[q], again)
+        if q is None:
+            ref = eng.entry.model.sample_actions(req.pixel_values, req.input_ids, lens, req.noise).float()
+        eng.close()
+    scale = ref.abs().max()
+    assert torch.isfinite(outs["fp8_block"]).all()
+    assert (outs["fp8_block"] - outs[None]).abs().max() < 0.12 * scale       # e4m3 has 3 mantissa bits; 6 blocks x 4 steps deep
+    assert (outs["fp8_block"] - ref).abs().mean() < 0.03 * scale
