@@ -27,9 +27,31 @@ def main() -> None:
     req = PI05Request(pixel_values=(torch.rand(1, 3, 3, 224, 224, generator=g) * 2 - 1).to(dev, torch.bfloat16),
                       input_ids=torch.randint(0, 1000, (1, 200), generator=g).to(dev), lang_lens=torch.tensor([200], device=dev),
                       noise=torch.randn(1, 50, 32, generator=g).to(dev, torch.bfloat16))
+    import json
+    import statistics
+
+    import torch.distributed as dist
+
     out = engine.step(req)
+    for _ in range(2):
+        engine.step(req)
+    ms = []
+    for _ in range(int(os.environ.get("PI05_TP_TIMED_STEPS", "8"))):
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        engine.step(req)
+        e1.record()
+        e1.synchronize()
+        ms.append(e0.elapsed_time(e1))
+    t = torch.tensor([statistics.median(ms)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)       # the slowest rank defines the latency
     if rank == 0:
-        print("action chunk", tuple(out.shape), "finite:", bool(torch.isfinite(out.float()).all()))
+        print(json.dumps({"plugin": "pi05_tp", "tp": world, "p50_ms_max_over_ranks": round(float(t), 3), "steps": len(ms),
+                          "action_chunk": list(out.shape), "finite": bool(torch.isfinite(out.float()).all()),
+                          "path": "eager layers, row-parallel sums over peer memory (<= 4 MB) / NCCL"}))
     engine.close()
 
 

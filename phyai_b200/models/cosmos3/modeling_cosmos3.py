@@ -205,6 +205,8 @@ class Cosmos3GenDecoderLayer(nn.Module):
         B, S = ws.B, ws.S
         Hq, Hkv, D = ca.num_local_heads, ca.num_local_kv_heads, ca.head_dim
         kbuf, vbuf = kv_buf
+        if ws.fp8 is not None:
+            return self._forward_fused_fp8(h, kv_buf, cos_sin, ws)
         ops.norm(h, "rms", weight=self.input_layernorm.weight, eps=cfg.rms_norm_eps, out=ws.x)
         ops.gemm(ws.x, ca.qkv_proj.weight, ws.qkv)
         ops.rope_kv(ws.qkv, Hq, Hkv, D, ws.q, cos_sin=cos_sin, q_norm_w=ca.norm_q.weight, k_norm_w=ca.norm_k.weight,
@@ -223,6 +225,52 @@ class Cosmos3GenDecoderLayer(nn.Module):
             h = h + P.all_reduce(part, axis=self.mlp.down_proj.axis)
         else:
             ops.gemm(ws.act, self.mlp.down_proj.weight, h, residual=h)
+        return h
+
+    def _fp8_weights(self) -> dict:
+        """Block-scaled e4m3 weights of this layer's four projections (stored ones of an fp8 checkpoint, else
+        quantised once from the bf16 tensors)."""
+        w = getattr(self, "_w8", None)
+        if w is None:
+            from ...ops.fp8_block import layer_weight_fp8
+
+            ca = self.cross_attention
+            w = {"qkv": layer_weight_fp8(ca.qkv_proj), "o": layer_weight_fp8(ca.to_out),
+                 "gate_up": layer_weight_fp8(self.mlp.gate_up_proj), "down": layer_weight_fp8(self.mlp.down_proj)}
+            self._w8 = w
+        return w
+
+    def _forward_fused_fp8(self, h: torch.Tensor, kv_buf, cos_sin: torch.Tensor, ws: "GenWorkspace") -> torch.Tensor:
+        """The same layer with block-scaled fp8 projections (reference: every linear through
+        ``gemm_fp8_nt_groupwise`` with per-token activation quantisation, layers/linear/backends/flashinfer.py:132-157).
+        The norm kernels emit the e4m3 rows and their 1 x 128 scales; attention output and the gated product pass
+        through the quantiser; residual adds stay in the GEMM epilogues. Row-parallel sums over ``tp`` use NCCL."""
+        from ...ops.fp8_block import gemm_fp8_block as g8, quantize_rows_into as q8
+
+        ca, cfg, W, f = self.cross_attention, self.cfg, self._fp8_weights(), ws.fp8
+        S = ws.S
+        Hq, Hkv, D = ca.num_local_heads, ca.num_local_kv_heads, ca.head_dim
+        kbuf, vbuf = kv_buf
+        x8, xs, a8, as_, m8, ms = f["x"], f["xs"], f["attn"], f["attns"], f["act"], f["acts"]
+        ops.norm(h, "rms", weight=self.input_layernorm.weight, eps=cfg.rms_norm_eps, out=ws.x, y8=x8, y8_scale=xs, y8_block=128)
+        g8(x8, xs, *W["qkv"], ws.qkv)
+        ops.rope_kv(ws.qkv, Hq, Hkv, D, ws.q, cos_sin=cos_sin, q_norm_w=ca.norm_q.weight, k_norm_w=ca.norm_k.weight,
+                    norm_eps=cfg.rms_norm_eps, k_pool=kbuf, v_pool=vbuf, slots=ws.slots)
+        ops.attention(ws.q.unflatten(1, (Hq, D)), kbuf, vbuf, ws.attn.unflatten(1, (Hq, D)), ws.q_start, ws.q_len,
+                      ws.kv_ptr, ws.kv_len, max_q_len=S, sm_scale=D ** -0.5)
+        q8(ws.attn, a8, as_)
+        if ca.to_out.tp_size > 1:
+            h = h + P.all_reduce(g8(a8, as_, *W["o"], ws.part), axis=ca.to_out.axis)
+        else:
+            g8(a8, as_, *W["o"], h, residual=h)
+        ops.norm(h, "rms", weight=self.post_attention_layernorm.weight, eps=cfg.rms_norm_eps, out=ws.x, y8=x8, y8_scale=xs,
+                 y8_block=128)
+        g8(x8, xs, *W["gate_up"], ws.act, act=self.mlp.activation, glu=True)
+        q8(ws.act, m8, ms)
+        if self.mlp.down_proj.tp_size > 1:
+            h = h + P.all_reduce(g8(m8, ms, *W["down"], ws.part), axis=self.mlp.down_proj.axis)
+        else:
+            g8(m8, ms, *W["down"], h, residual=h)
         return h
 
     def forward_fused_tp(self, h: torch.Tensor, y_in: torch.Tensor, wait, kv_buf, s_text: int, cos_sin: torch.Tensor,
@@ -269,6 +317,7 @@ class GenWorkspace:
     kv_ptr: torch.Tensor
     kv_len: torch.Tensor
     stream: object | None = None   # PeerStream of the tensor-parallel group (None: single rank or NCCL fallback)
+    fp8: dict | None = None        # block-scaled fp8 serving: e4m3 row buffers and 1 x 128 scales ("x", "attn", "act")
 
 
 class Cosmos3LanguageModel(nn.Module):

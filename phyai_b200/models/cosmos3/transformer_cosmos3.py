@@ -52,6 +52,9 @@ class Cosmos3Transformer(nn.Module):
         self.use_fused = (torch.device(device).type == "cuda" and dtype == torch.bfloat16
                           and get_engine_config().resolved_backend("attn") == "b200")
         self.use_peer = envs.PHYAI_PEER_COMM.get()   # tensor-parallel GEN layers over peer memory (else NCCL all-reduce)
+        # generation tower in block-scaled fp8 (e4m3 weights with 128 x 128 scales, activations per 1 x 128 block);
+        # the peer-memory tensor-parallel layer is bf16 only, so fp8 + tp sums its row-parallel products over NCCL
+        self.serve_fp8 = bool(envs.PHYAI_COSMOS3_FP8.get())
 
     @torch.no_grad()
     def init_random(self, seed: int = 0, std: float = 0.02) -> "Cosmos3Transformer":
@@ -167,7 +170,16 @@ class Cosmos3Transformer(nn.Module):
                           z(B * S, self.gen_layers[0].mlp.down_proj.input_size_per_partition), z(B * S, cfg.hidden_size),
                           slots.long(), ar * S, torch.full_like(ar, S), ar * tot, torch.full_like(ar, tot))
         tp = self.gen_layers[0].mlp.down_proj.tp_size
-        if tp > 1 and self.use_peer:
+        if self.serve_fp8:
+            f8, f32 = torch.float8_e4m3fn, torch.float32
+            widths = {"x": cfg.hidden_size, "attn": Hq * D, "act": self.gen_layers[0].mlp.down_proj.input_size_per_partition}
+            if any(w % 128 for w in widths.values()):
+                raise ValueError(f"block-scaled fp8 needs per-rank widths that are multiples of 128, got {widths}")
+            ws.fp8 = {}
+            for name, w in widths.items():
+                ws.fp8[name] = torch.empty(B * S, w, dtype=f8, device=device)
+                ws.fp8[name + "s"] = torch.empty(B * S, w // 128, dtype=f32, device=device)
+        if tp > 1 and self.use_peer and not self.serve_fp8:
             from ...parallel.symm import PeerGroup
 
             rows, H = B * S, cfg.hidden_size

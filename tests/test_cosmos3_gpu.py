@@ -66,6 +66,36 @@ def test_fused_gen_path_matches_eager(engine_cuda, variant):
         assert torch.equal(a, a2)
 
 
+def test_fp8_block_gen_path_tracks_bf16(engine_cuda):
+    """The generation tower with block-scaled fp8 projections (weights quantised from the bf16 tensors on first use)
+    stays within e4m3 noise of the bf16 fused path and of the eager PyTorch path."""
+    from phyai_b200 import ops
+    from phyai_b200.models.cosmos3 import Cosmos3Transformer
+
+    cfg = small_real_config()
+    model = Cosmos3Transformer(cfg, params_dtype=torch.bfloat16, device="cuda").eval().init_random(2, std=0.05)
+    g = torch.Generator().manual_seed(1)
+    B, vs = 1, (3, 16, 24)
+    ids = torch.randint(0, 512, (B, 20), generator=g).cuda()
+    mask = torch.ones(B, 20, dtype=torch.long, device="cuda")
+    lat = torch.randn(B, 16, *vs, generator=g).cuda().bfloat16()
+    t = torch.full((B,), 500.0, device="cuda")
+    bf16_out = model(lat, t, model.encode_condition(ids, mask, vs, 24.0)).float()
+    model.serve_fp8 = True
+    fp8_out = model(lat, t, model.encode_condition(ids, mask, vs, 24.0)).float()
+    fp8_again = model(lat, t, model.encode_condition(ids, mask, vs, 24.0)).float()
+    model.serve_fp8, model.use_fused = False, False
+    eager = model(lat, t, model.encode_condition(ids, mask, vs, 24.0)).float()
+    torch.cuda.synchronize()
+    assert ops.kernel_status() == 0
+    assert model.gen_layers[0]._w8["qkv"][0].dtype == torch.float8_e4m3fn
+    scale = eager.abs().max().item()
+    assert torch.isfinite(fp8_out).all() and torch.equal(fp8_out, fp8_again)
+    assert (fp8_out - bf16_out).abs().max().item() <= 0.12 * scale
+    assert (fp8_out - eager).abs().mean().item() <= 0.03 * scale
+    assert (fp8_out - bf16_out).abs().max().item() > 0          # it is a different computation
+
+
 def test_policy_scheduler_and_vae_on_gpu(engine_cuda):
     from phyai_b200.models.cosmos3 import Cosmos3ActionRequest, Cosmos3PolicyScheduler, Cosmos3Transformer, Cosmos3WanVAEConfig
     from phyai_b200.models.cosmos3.vae_wan import Cosmos3WanVAE
