@@ -33,7 +33,7 @@ class PI0Plan(PI05Plan):
         self.s_qkv = torch.zeros(B, self.e_qkv.shape[1], dtype=bf, device=dev)
         self.s_q = torch.zeros(B, self.e_q.shape[1], dtype=bf, device=dev)
         self.s_attn = torch.zeros(B, self.e_q.shape[1], dtype=bf, device=dev)
-        self.s_act = torch.zeros(B, cfg.expert.intermediate_size, dtype=bf, device=dev)
+        self.s_act = torch.zeros(B, self.I_e, dtype=bf, device=dev)
         self.s_pos = torch.zeros(B, dtype=torch.int32, device=dev)
         self.s_slots = torch.zeros(B, dtype=torch.int64, device=dev)
         self.s_qstart = torch.arange(B, dtype=torch.int32, device=dev)
@@ -67,7 +67,7 @@ class PI0Plan(PI05Plan):
 
             stack = self.model.expert_stack
             t = cfg.text
-            Hq, Hkv, D = t.num_attention_heads, t.num_key_value_heads, t.head_dim
+            Hq, Hkv, D = self.Hq, self.Hkv, t.head_dim
             # QKV rows reordered for the rotating epilogue; block 0 keeps its norm kernel and the plain weight
             self.fold_qkv = [ops.permute_rope_rows(fold(l.attn.qkv.weight, l.input_layernorm.weight) if li > 0
                                                    else l.attn.qkv.weight, Hq, Hkv, D)
@@ -91,7 +91,7 @@ class PI0Plan(PI05Plan):
     def _block(self, layer, li, h, x, qkv, q, attn, act, pos, slots, qstart, qlen, kvlen, max_q, splits,
                ss=None, rope=None) -> None:
         t, e = self.cfg.text, self.cfg.expert
-        Hq, Hkv, D = t.num_attention_heads, t.num_key_value_heads, t.head_dim
+        Hq, Hkv, D = self.Hq, self.Hkv, t.head_dim
         kpool, vpool = self.pool.layer(li)
         if ss is not None:
             rms = (e.hidden_size, e.rms_norm_eps)

@@ -78,6 +78,8 @@ def resolve_num_images(inputs_image_shape, num_channels: int) -> int:
 class PI05Entry(Entry):
     name: ClassVar[str] = "pi05"
     args_cls: ClassVar[type[EntryArgs]] = PI05Args
+    #: mesh axis the vision encoder blocks are sharded over (``None``: whole tower on every rank)
+    vision_axis: ClassVar[str | None] = "tp"
 
     def __init__(self) -> None:
         self.model: PI05Model | None = None
@@ -92,7 +94,8 @@ class PI05Entry(Entry):
         else:
             config = PI05Config()
         with use_quant_plan(load_quant_plan(args.checkpoint_dir)):
-            model = PI05Model(config, vision_params_dtype=args.vision_params_dtype, device=eng.device.target)
+            model = PI05Model(config, vision_params_dtype=args.vision_params_dtype, device=eng.device.target,
+                              vision_axis=self.vision_axis)
         if args.checkpoint_dir is not None:
             load_pretrained(model, args.checkpoint_dir, remap=compose_remap(args.weight_remap), strict=args.weight_strict)
         elif args.random_init_seed is not None:

@@ -1,13 +1,12 @@
 """Plugin ``pi05_tp``: tensor-parallel Pi0.5 (every rank holds a slice of each projection).
 
-All ranks of the ``tp`` axis take the same request and return the same action chunk. The attention
-heads and MLP columns are sharded by the parallel linear layers (the single KV head of the Gemma
-stacks is replicated); the row-parallel products are summed with ``parallel.all_reduce``, which on
-CUDA goes to the peer-memory backend for these small messages (one push kernel + one reduce kernel,
-no NCCL launch). The model runs its eager path here: the single-GPU plugin's captured plan assumes
-whole weights, and one B200 already serves the batch-1 case faster than a TP group can (about 17 ms;
-a TP step adds 2 x 36 reductions per denoise step), so this entry exists for checkpoints that do
-not fit one GPU and for parity with TP-capable layers.
+All ranks of the ``tp`` axis take the same request and return the same action chunk. On CUDA bf16 the
+request runs through :class:`PI05TPPlan`, captured as one CUDA graph per prompt bucket: q heads and
+MLP columns are sharded (the single KV head of the Gemma stacks is replicated), every row-parallel
+product leaves its GEMM through the epilogue into the peers' memory and is summed by the kernel that also
+applies the gate, the residual and the next (Ada)RMS norm, and the cameras (not the vision weights) are
+split over the ranks. Elsewhere (CPU, fp32, a single rank) the eager model path runs, with the
+row-parallel products summed by ``parallel.all_reduce``.
 
 The reference has TP-capable Pi0.5 layers and no scheduler that drives them
 (phyai/src/phyai/models/pi05/modeling_pi05.py:388-1008; its schedulers are scheduler_ws1_pi05.py and scheduler_wn_pi05.py, single GPU and data parallel).
@@ -15,6 +14,7 @@ The reference has TP-capable Pi0.5 layers and no scheduler that drives them
 
 from __future__ import annotations
 
+import dataclasses
 from dataclasses import dataclass
 from typing import ClassVar
 
@@ -23,42 +23,55 @@ import torch
 from ... import parallel as P
 from ...engine import Engine, EntryArgs
 from ...engine_config import get_engine_config
-from ...runtime import Scheduler
 from .main_pi05 import PI05Args, PI05Entry, resolve_num_images
 from .modeling_pi05 import PI05Model
-from .scheduler_ws1_pi05 import PI05Request
+from .plan_pi05 import PI05Plan
+from .scheduler_ws1_pi05 import PI05Request, PI05WS1Scheduler
 
 
-class PI05TPScheduler(Scheduler):
-    def __init__(self, model: PI05Model, *, max_batch_size: int, num_images: int, device) -> None:
-        self.model, self.max_batch_size, self.num_images = model, max_batch_size, num_images
-        self.device = torch.device(device)
+class PI05TPScheduler(PI05WS1Scheduler):
+    """The single-GPU scheduler with the tensor-parallel plan behind it. Noise that the request does not
+    carry is drawn on the host from a generator every rank seeds alike, so the ranks stay identical."""
+
+    def __init__(self, model: PI05Model, *, max_batch_size: int, num_images: int, device, use_cuda_graph: bool = True,
+                 axis: str = "tp") -> None:
+        super().__init__(model, max_batch_size=max_batch_size, num_images=num_images, device=device,
+                         use_cuda_graph=use_cuda_graph)
+        self.axis = axis
         mesh = P.default_mesh()
-        self.tp_size = mesh.axis_size("tp") if mesh is not None else 1
-        self.tp_rank = mesh.axis_local_rank("tp") if mesh is not None else 0
+        self.tp_size = mesh.axis_size(axis) if mesh is not None else 1
+        self.tp_rank = mesh.axis_local_rank(axis) if mesh is not None else 0
+        self._noise_gen = torch.Generator(device="cpu").manual_seed(0)
+        # the plan splits the cameras over the ranks and needs the whole vision tower on each of them
+        if self.tp_size > 1 and model.vision.blocks[0].out.tp_size > 1:
+            self.use_plan = self.use_cuda_graph = False
 
     def setup(self) -> None:
+        super().setup()
+        if self.tp_size > 1 and not self.use_plan:
+            P.warmup((self.axis,))
+
+    def _make_plan(self) -> PI05Plan:
+        if self.tp_size == 1:
+            return super()._make_plan()
+        from .plan_tp_pi05 import PI05TPPlan
+
+        return PI05TPPlan(self.model, max_batch_size=self.max_batch_size, num_images=self.num_images, device=self.device,
+                          axis=self.axis)
+
+    def _captured(self, bucket: int) -> None:
+        # capture time differs between ranks; the first replay's bounded waits start together
         if self.tp_size > 1:
-            P.warmup(("tp",))
+            self.plan.pg.sync()
 
     @torch.no_grad()
     def step(self, request: PI05Request) -> torch.Tensor:
-        B = request.pixel_values.shape[0]
-        if B > self.max_batch_size:
-            raise ValueError(f"batch of {B} exceeds max_batch_size={self.max_batch_size}")
-        if request.pixel_values.shape[1] != self.num_images:
-            raise ValueError(f"{request.pixel_values.shape[1]} cameras, the plugin was set up for {self.num_images}")
-        cfg = self.model.config
-        noise = request.noise
-        if noise is None:
-            g = torch.Generator(device="cpu").manual_seed(0)     # identical on every rank
-            noise = torch.randn(B, cfg.chunk_size, cfg.max_action_dim, generator=g)
-        dt = next(self.model.parameters()).dtype
-        return self.model.sample_actions(request.pixel_values.to(self.device, dt), request.input_ids.to(self.device),
-                                         request.lang_lens.to(self.device), noise.to(self.device, dt))
-
-    def close(self) -> None:
-        return None
+        if request.noise is None:
+            cfg = self.cfg
+            B = request.pixel_values.shape[0]
+            noise = torch.randn(B, cfg.chunk_size, cfg.max_action_dim, generator=self._noise_gen)
+            request = dataclasses.replace(request, noise=noise)
+        return super().step(request)
 
 
 @dataclass
@@ -70,6 +83,8 @@ class PI05TPArgs(PI05Args):
 class PI05TPEntry(PI05Entry):
     name: ClassVar[str] = "pi05_tp"
     args_cls: ClassVar[type[EntryArgs]] = PI05TPArgs
+    #: the encoder blocks of the vision tower stay whole on every rank (see PI05TPPlan)
+    vision_axis: ClassVar[str | None] = None
 
     def setup(self, args: PI05TPArgs) -> None:  # type: ignore[override]
         eng = get_engine_config()

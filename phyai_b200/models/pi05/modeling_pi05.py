@@ -47,17 +47,17 @@ def dense_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal
 
 # ------------------------------------------------------------------- vision
 class SiglipBlock(nn.Module):
-    def __init__(self, cfg: SiglipVisionConfig, dtype, prefix: str) -> None:
+    def __init__(self, cfg: SiglipVisionConfig, dtype, prefix: str, axis: str | None = "tp") -> None:
         super().__init__()
         H, I = cfg.hidden_size, cfg.intermediate_size
         self.num_heads, self.head_dim = cfg.num_attention_heads, cfg.head_dim
         self.ln1 = LayerNorm(H, cfg.layer_norm_eps, dtype=dtype, prefix=f"{prefix}.layer_norm1")
         self.qkv = QKVParallelLinear(H, cfg.head_dim, cfg.num_attention_heads, bias=True, params_dtype=dtype,
-                                     prefix=f"{prefix}.self_attn.qkv_proj")
-        self.out = RowParallelLinear(H, H, bias=True, params_dtype=dtype, prefix=f"{prefix}.self_attn.out_proj")
+                                     prefix=f"{prefix}.self_attn.qkv_proj", axis=axis)
+        self.out = RowParallelLinear(H, H, bias=True, params_dtype=dtype, prefix=f"{prefix}.self_attn.out_proj", axis=axis)
         self.ln2 = LayerNorm(H, cfg.layer_norm_eps, dtype=dtype, prefix=f"{prefix}.layer_norm2")
-        self.fc1 = ColumnParallelLinear(H, I, bias=True, params_dtype=dtype, prefix=f"{prefix}.mlp.fc1")
-        self.fc2 = RowParallelLinear(I, H, bias=True, params_dtype=dtype, prefix=f"{prefix}.mlp.fc2")
+        self.fc1 = ColumnParallelLinear(H, I, bias=True, params_dtype=dtype, prefix=f"{prefix}.mlp.fc1", axis=axis)
+        self.fc2 = RowParallelLinear(I, H, bias=True, params_dtype=dtype, prefix=f"{prefix}.mlp.fc2", axis=axis)
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         """h: (n_img, patches, H)."""
@@ -77,10 +77,14 @@ class SiglipBlock(nn.Module):
 
 
 class PI05VisionTower(nn.Module):
-    """SigLIP-So400m + multi-modal projector; output ``(n_img, patches, text_hidden)``."""
+    """SigLIP-So400m + multi-modal projector; output ``(n_img, patches, text_hidden)``. ``axis``: mesh axis the
+    encoder blocks are sharded over; ``None`` keeps the whole tower on every rank (the tensor-parallel plan
+    then splits the cameras over the ranks instead of the 72-wide heads and the 4304-wide MLP)."""
 
-    def __init__(self, cfg: SiglipVisionConfig, *, params_dtype=None, prefix: str = f"{PALIGEMMA}.model") -> None:
+    def __init__(self, cfg: SiglipVisionConfig, *, params_dtype=None, prefix: str = f"{PALIGEMMA}.model",
+                 axis: str | None = "tp") -> None:
         super().__init__()
+        self.axis = axis
         dtype, _, _ = resolve_engine_defaults(params_dtype, None, None)
         dev = get_engine_config().device.target
         self.config, self.compute_dtype = cfg, dtype
@@ -95,7 +99,7 @@ class PI05VisionTower(nn.Module):
                                                requires_grad=False)
         self.position_embedding.hf_keys = {f"{vp}.embeddings.position_embedding.weight": None}
         self.patch_k = k
-        self.blocks = nn.ModuleList([SiglipBlock(cfg, dtype, f"{vp}.encoder.layers.{i}")
+        self.blocks = nn.ModuleList([SiglipBlock(cfg, dtype, f"{vp}.encoder.layers.{i}", axis)
                                      for i in range(cfg.num_hidden_layers)])
         self.post_layernorm = LayerNorm(cfg.hidden_size, cfg.layer_norm_eps, dtype=dtype, prefix=f"{vp}.post_layernorm")
         self.projector = ReplicatedLinear(cfg.hidden_size, cfg.projection_dim, bias=True, params_dtype=dtype,
@@ -250,11 +254,11 @@ class ActionTimeHeads(nn.Module):
 
 class PI05Model(nn.Module):
     def __init__(self, config: PI05Config, *, vision_params_dtype: torch.dtype | None = None,
-                 device: str | None = None, params_dtype: torch.dtype | None = None) -> None:
+                 device: str | None = None, params_dtype: torch.dtype | None = None, vision_axis: str | None = "tp") -> None:
         super().__init__()
         dtype, _, _ = resolve_engine_defaults(params_dtype, None, None)
         self.config, self.params_dtype = config, dtype
-        self.vision = PI05VisionTower(config.vision, params_dtype=vision_params_dtype or dtype)
+        self.vision = PI05VisionTower(config.vision, params_dtype=vision_params_dtype or dtype, axis=vision_axis)
         self.paligemma_lm = PaliGemmaLanguageModel(config.text, params_dtype=dtype)
         self.expert_stack = PI05ExpertStack(config.expert, params_dtype=dtype)
         self.heads = ActionTimeHeads(config, params_dtype=dtype)

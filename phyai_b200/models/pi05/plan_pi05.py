@@ -66,6 +66,8 @@ class PI05Plan:
     #: ``quantization="fp8_block"``): e4m3 weights with 128 x 128 scales, activations quantised per 1 x 128 block
     #: by the norm kernels / a quantiser in front of every GEMM; the vision tower (4304-wide MLP) stays bf16
     serve_fp8 = bool(envs.PHYAI_PI05_FP8.get())
+    #: True in the subclass whose stages reduce the row-parallel products over a peer group
+    tensor_parallel = False
     _side_stream = None
 
     def __init__(self, model: PI05Model, *, max_batch_size: int = 1, num_images: int = 3,
@@ -84,6 +86,13 @@ class PI05Plan:
         if model.params_dtype != dt or model.vision.compute_dtype != dt:
             raise ValueError("PI05Plan runs bf16 weights; use the eager path for other dtypes")
         v, t, e = cfg.vision, cfg.text, cfg.expert
+        # widths of this rank's slice of every projection (the whole projection on one GPU)
+        lm0, ex0 = model.paligemma_lm.layers[0], model.expert_stack.layers[0]
+        self.tp = int(lm0.attn.o.tp_size)
+        self.Hq, self.Hkv = lm0.attn.qkv.q_size // t.head_dim, lm0.attn.qkv.kv_size // t.head_dim
+        self.I_p, self.I_e = lm0.mlp.down.input_size_per_partition, ex0.mlp.down.input_size_per_partition
+        if self.tp > 1 and not self.tensor_parallel:
+            raise ValueError("the model is sharded over a tensor-parallel axis: build PI05TPPlan for it")
         self.img_tokens = v.num_patches * num_images
         self.P = self.img_tokens + cfg.tokenizer_max_length          # max prefix rows per robot
         self.C = cfg.chunk_size
@@ -120,15 +129,15 @@ class PI05Plan:
         # ---------------- prefix buffers (sized for the largest bucket)
         Mp = B * self.P
         H = t.hidden_size
-        qkv_w = (t.num_attention_heads + 2 * t.num_key_value_heads) * t.head_dim
+        qkv_w = (self.Hq + 2 * self.Hkv) * t.head_dim
         self.p_h = buf(Mp, H)
         self.p_x = buf(Mp, H)
         self.p_qkv = buf(Mp, qkv_w)
-        self.p_q = buf(Mp, t.num_attention_heads * t.head_dim)
-        self.p_attn = buf(Mp, t.num_attention_heads * t.head_dim)
-        self.p_act = buf(Mp, t.intermediate_size)
+        self.p_q = buf(Mp, self.Hq * t.head_dim)
+        self.p_attn = buf(Mp, self.Hq * t.head_dim)
+        self.p_act = buf(Mp, self.I_p)
         self.input_ids = torch.zeros(B, cfg.tokenizer_max_length, dtype=torch.int64, device=dev)
-        self.pool = KVCachePool(cfg.num_layers, 1 + B * self.slab, t.num_key_value_heads, t.head_dim, dtype=dt, device=dev)
+        self.pool = KVCachePool(cfg.num_layers, 1 + B * self.slab, self.Hkv, t.head_dim, dtype=dt, device=dev)
         # per-bucket metadata (filled by set_layout)
         self.p_pos = torch.zeros(Mp, dtype=torch.int32, device=dev)
         self.p_slots = torch.zeros(Mp, dtype=torch.int64, device=dev)
@@ -147,9 +156,9 @@ class PI05Plan:
         self.e_h = buf(Me, He)
         self.e_x = buf(Me, He)
         self.e_qkv = buf(Me, qkv_w)
-        self.e_q = buf(Me, t.num_attention_heads * t.head_dim)
-        self.e_attn = buf(Me, t.num_attention_heads * t.head_dim)
-        self.e_act = buf(Me, e.intermediate_size)
+        self.e_q = buf(Me, self.Hq * t.head_dim)
+        self.e_attn = buf(Me, self.Hq * t.head_dim)
+        self.e_act = buf(Me, self.I_e)
         self.e_v = buf(Me, cfg.max_action_dim)
         self.e_pos = torch.zeros(Me, dtype=torch.int32, device=dev)
         self.e_slots = torch.zeros(Me, dtype=torch.int64, device=dev)
@@ -160,12 +169,12 @@ class PI05Plan:
         self.out = buf(B, self.C, cfg.max_action_dim)
         if self.fp8:
             f8 = torch.float8_e4m3fn
-            for name, width in (("H", H), ("Q", t.num_attention_heads * t.head_dim), ("I", t.intermediate_size)):
+            for name, width in (("H", H), ("Q", self.Hq * t.head_dim), ("I", self.I_p)):
                 if width % 128:
                     raise ValueError(f"block-scaled fp8 needs widths that are multiples of 128, got {width}")
                 setattr(self, f"p8_{name}", torch.zeros(Mp, width, dtype=f8, device=dev))
                 setattr(self, f"p8s_{name}", torch.zeros(Mp, width // 128, dtype=torch.float32, device=dev))
-            for name, width in (("H", He), ("Q", t.num_attention_heads * t.head_dim), ("I", e.intermediate_size)):
+            for name, width in (("H", He), ("Q", self.Hq * t.head_dim), ("I", self.I_e)):
                 if width % 128:
                     raise ValueError(f"block-scaled fp8 needs widths that are multiples of 128, got {width}")
                 setattr(self, f"e8_{name}", torch.zeros(Me, width, dtype=f8, device=dev))
@@ -215,7 +224,7 @@ class PI05Plan:
 
     def _expert_geometry(self) -> ExpertGeometry:
         cfg, e, t = self.cfg, self.cfg.expert, self.cfg.text
-        return ExpertGeometry(rows=self.Me, hidden=e.hidden_size, inter=e.intermediate_size, q_heads=t.num_attention_heads,
+        return ExpertGeometry(rows=self.Me, hidden=e.hidden_size, inter=e.intermediate_size, q_heads=self.Hq,
                               head_dim=t.head_dim, action_dim=cfg.max_action_dim, layers=cfg.num_layers,
                               steps=cfg.num_inference_steps)
 
@@ -224,7 +233,7 @@ class PI05Plan:
         column factors, branch gates and ``shift @ W^T`` biases; the weights stay as loaded (one copy)."""
         self.stack = None
         t = self.cfg.text
-        if not (self.use_expert_kernel and self.device.type == "cuda" and self.B == 1 and t.num_key_value_heads == 1
+        if not (self.use_expert_kernel and self.device.type == "cuda" and self.B == 1 and t.num_key_value_heads == 1 and self.tp == 1
                 and self.suffix_extra == 0):
             return
         geo = self._expert_geometry()
@@ -260,7 +269,7 @@ class PI05Plan:
         """Prefix decoder: Gemma RMSNorm weights (1 + w) folded into the QKV and gate/up weights (one
         static copy each), QKV rows reordered for the rotating epilogue; block 0 keeps its norm kernel."""
         t, lm = self.cfg.text, self.model.paligemma_lm
-        Hq, Hkv, D = t.num_attention_heads, t.num_key_value_heads, t.head_dim
+        Hq, Hkv, D = self.Hq, self.Hkv, t.head_dim
 
         def fold(w, norm_w):
             return (w.float() * (1.0 + norm_w.float())[None, :]).to(torch.bfloat16).contiguous()
@@ -291,7 +300,7 @@ class PI05Plan:
             return folded, b.to(dt).contiguous()
 
         t = self.cfg.text
-        Hq, Hkv, D = t.num_attention_heads, t.num_key_value_heads, t.head_dim
+        Hq, Hkv, D = self.Hq, self.Hkv, t.head_dim
         # with the persistent kernel serving the loop, only the first step (the one that may run on the
         # second stream under the prefix decoder) still goes launch by launch: one folded copy, not one per step
         keep = 1 if self.stack is not None else self.cfg.num_inference_steps
@@ -311,8 +320,7 @@ class PI05Plan:
     def _rope_descs(self, q_out: torch.Tensor, pos: torch.Tensor, slots: torch.Tensor) -> list[torch.Tensor]:
         """One rotate-and-scatter destination per layer (its K/V pool) for the QKV GEMM epilogue."""
         t = self.cfg.text
-        return [ops.rope_epilogue_desc(q_out, *self.pool.layer(li), self.cos_sin, pos, slots, t.num_attention_heads,
-                                       t.num_key_value_heads, t.head_dim) for li in range(self.cfg.num_layers)]
+        return [ops.rope_epilogue_desc(q_out, *self.pool.layer(li), self.cos_sin, pos, slots, self.Hq, self.Hkv, t.head_dim) for li in range(self.cfg.num_layers)]
 
     def set_layout(self, layout: PI05Layout) -> bool:
         """Write the metadata of a request shape into the static buffers. Returns True if it changed."""
@@ -348,27 +356,33 @@ class PI05Plan:
         return True
 
     # ----------------------------------------------------------------- stages
-    def vision(self) -> None:
+    def vision(self, img_lo: int = 0, img_hi: int | None = None) -> None:
+        """Cameras ``[img_lo, img_hi)`` of the batch (all of them by default) through the tower; their rows
+        land at the start of ``v_x``."""
         cfg, v, m = self.cfg, self.cfg.vision, self.model.vision
-        ops.im2col(self.pixels, v.patch_size, self.v_cols)
-        ops.gemm(self.v_cols, self.patch_w, self.v_h, bias=m.patch_bias, residual=m.position_embedding,
-                 res_mod=v.num_patches)
+        hi = self.B * self.n_img if img_hi is None else img_hi
+        n = hi - img_lo
+        if n <= 0:
+            return
+        M = n * v.num_patches
+        cols, h, x, qkv, attn, mlp = (b[:M] for b in (self.v_cols, self.v_h, self.v_x, self.v_qkv, self.v_attn, self.v_mlp))
+        qstart, qlen = self.v_qstart[:n], self.v_qlen[:n]
+        ops.im2col(self.pixels[img_lo:hi], v.patch_size, cols)
+        ops.gemm(cols, self.patch_w, h, bias=m.patch_bias, residual=m.position_embedding, res_mod=v.num_patches)
         H, hd, nh = v.hidden_size, v.head_dim, v.num_attention_heads
-        q3 = self.v_qkv[:, :H].unflatten(1, (nh, hd))
-        k3 = self.v_qkv[:, H:2 * H].unflatten(1, (nh, hd))
-        v3 = self.v_qkv[:, 2 * H:].unflatten(1, (nh, hd))
-        a3 = self.v_attn.unflatten(1, (nh, hd))
+        q3 = qkv[:, :H].unflatten(1, (nh, hd))
+        k3 = qkv[:, H:2 * H].unflatten(1, (nh, hd))
+        v3 = qkv[:, 2 * H:].unflatten(1, (nh, hd))
+        a3 = attn.unflatten(1, (nh, hd))
         for blk in m.blocks:
-            ops.norm(self.v_h, "layer", weight=blk.ln1.weight, bias=blk.ln1.bias, eps=v.layer_norm_eps, out=self.v_x)
-            ops.gemm(self.v_x, blk.qkv.weight, self.v_qkv, bias=blk.qkv.bias)
-            ops.attention(q3, k3, v3, a3, self.v_qstart, self.v_qlen, self.v_qstart, self.v_qlen,
-                          max_q_len=v.num_patches, sm_scale=hd ** -0.5)
-            ops.gemm(self.v_attn, blk.out.weight, self.v_h, bias=blk.out.bias, residual=self.v_h)
-            ops.norm(self.v_h, "layer", weight=blk.ln2.weight, bias=blk.ln2.bias, eps=v.layer_norm_eps, out=self.v_x)
-            ops.gemm(self.v_x, blk.fc1.weight, self.v_mlp, bias=blk.fc1.bias, act="gelu_tanh")
-            ops.gemm(self.v_mlp, blk.fc2.weight, self.v_h, bias=blk.fc2.bias, residual=self.v_h)
-        ops.norm(self.v_h, "layer", weight=m.post_layernorm.weight, bias=m.post_layernorm.bias,
-                 eps=v.layer_norm_eps, out=self.v_x)
+            ops.norm(h, "layer", weight=blk.ln1.weight, bias=blk.ln1.bias, eps=v.layer_norm_eps, out=x)
+            ops.gemm(x, blk.qkv.weight, qkv, bias=blk.qkv.bias)
+            ops.attention(q3, k3, v3, a3, qstart, qlen, qstart, qlen, max_q_len=v.num_patches, sm_scale=hd ** -0.5)
+            ops.gemm(attn, blk.out.weight, h, bias=blk.out.bias, residual=h)
+            ops.norm(h, "layer", weight=blk.ln2.weight, bias=blk.ln2.bias, eps=v.layer_norm_eps, out=x)
+            ops.gemm(x, blk.fc1.weight, mlp, bias=blk.fc1.bias, act="gelu_tanh")
+            ops.gemm(mlp, blk.fc2.weight, h, bias=blk.fc2.bias, residual=h)
+        ops.norm(h, "layer", weight=m.post_layernorm.weight, bias=m.post_layernorm.bias, eps=v.layer_norm_eps, out=x)
 
     def prefix(self, lang_bucket: int, kv_events=None) -> None:
         cfg, t, lm = self.cfg, self.cfg.text, self.model.paligemma_lm
@@ -383,7 +397,7 @@ class PI05Plan:
             ops.gemm(self.v_x[b * self.img_tokens:(b + 1) * self.img_tokens], proj.weight,
                      h[b * n_per: b * n_per + self.img_tokens], bias=proj.bias)
         ops.embedding(self.input_ids.view(-1), lm.embed_tokens, h, scale=lm.embed_scale, dst_rows=self.lang_rows)
-        Hq, Hkv, D = t.num_attention_heads, t.num_key_value_heads, t.head_dim
+        Hq, Hkv, D = self.Hq, self.Hkv, t.head_dim
         qkv, q, attn, act = self.p_qkv[:Mp], self.p_q[:Mp], self.p_attn[:Mp], self.p_act[:Mp]
         q3, a3 = q.unflatten(1, (Hq, D)), attn.unflatten(1, (Hq, D))
         last = len(lm.layers) - 1
@@ -453,7 +467,7 @@ class PI05Plan:
     def expert(self) -> None:
         cfg, e, t = self.cfg, self.cfg.expert, self.cfg.text
         heads, stack = self.model.heads, self.model.expert_stack
-        Hq, Hkv, D, He, Me = t.num_attention_heads, t.num_key_value_heads, t.head_dim, e.hidden_size, self.Me
+        Hq, Hkv, D, He, Me = self.Hq, self.Hkv, t.head_dim, e.hidden_size, self.Me
         h, x = self.e_h, self.e_x
         q3, a3 = self.e_q.unflatten(1, (Hq, D)), self.e_attn.unflatten(1, (Hq, D))
         self.x_t.copy_(self.noise.view(Me, -1))
@@ -489,7 +503,7 @@ class PI05Plan:
 
         cfg, e, t = self.cfg, self.cfg.expert, self.cfg.text
         heads, stack = self.model.heads, self.model.expert_stack
-        Hq, Hkv, D, He, Me = t.num_attention_heads, t.num_key_value_heads, t.head_dim, e.hidden_size, self.Me
+        Hq, Hkv, D, He, Me = self.Hq, self.Hkv, t.head_dim, e.hidden_size, self.Me
         h, x, W = self.e_h, self.e_x, self.w8
         q3, a3 = self.e_q.unflatten(1, (Hq, D)), self.e_attn.unflatten(1, (Hq, D))
         x8, xs, a8, as_, m8, ms = self.e8_H, self.e8s_H, self.e8_Q, self.e8s_Q, self.e8_I, self.e8s_I
@@ -524,7 +538,7 @@ class PI05Plan:
         the result out."""
         cfg, e, t = self.cfg, self.cfg.expert, self.cfg.text
         heads, stack = self.model.heads, self.model.expert_stack
-        Hq, Hkv, D, He, Me = t.num_attention_heads, t.num_key_value_heads, t.head_dim, e.hidden_size, self.Me
+        Hq, Hkv, D, He, Me = self.Hq, self.Hkv, t.head_dim, e.hidden_size, self.Me
         h, x = self.e_h, self.e_x
         q3, a3 = self.e_q.unflatten(1, (Hq, D)), self.e_attn.unflatten(1, (Hq, D))
         ss_in, ss_post = self.e_ss[0], self.e_ss[1]

@@ -66,9 +66,15 @@ class PI05WS1Scheduler(Scheduler):
         from ... import ops
 
         ops.set_pdl(os.environ.get("PHYAI_PDL", "1") not in ("0", "false", "off"))
-        self.plan = PI05Plan(self.model, max_batch_size=self.max_batch_size, num_images=self.num_images,
-                             device=self.device, quantization=self.quantization)
+        self.plan = self._make_plan()
         self.plan.build_modulation_tables()
+
+    def _make_plan(self) -> PI05Plan:
+        return PI05Plan(self.model, max_batch_size=self.max_batch_size, num_images=self.num_images,
+                        device=self.device, quantization=self.quantization)
+
+    def _captured(self, bucket: int) -> None:
+        """Called once after a bucket's graph has been captured, before its first replay."""
 
     def bucket_for(self, max_lang: int) -> int:
         for b in self.lang_buckets:
@@ -119,6 +125,7 @@ class PI05WS1Scheduler(Scheduler):
                 g = self.graphs.get_or_create(bucket)
                 if not g.captured:
                     g.capture(lambda: plan.run(bucket), {})
+                    self._captured(bucket)
                 g.replay()
             else:
                 plan.run(bucket)
