@@ -1,5 +1,6 @@
-"""Tensor-parallel Pi0.5: every rank holds a shard of each linear layer and receives the same request (eager path; the
-single-GPU CUDA-graph plan is the low-latency default, this plugin is for checkpoints that should not be replicated).
+"""Tensor-parallel Pi0.5: every rank holds a shard of each decoder projection and receives the same request. On CUDA
+bf16 the request runs as one captured graph whose row-parallel GEMMs store into the peers' memory (``PI05TPPlan``); the
+single-GPU plan stays the low-latency default at batch 1, this plugin is for checkpoints that should not be replicated.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 examples/pi05/run_pi05_tp.py
 """
@@ -51,7 +52,7 @@ def main() -> None:
     if rank == 0:
         print(json.dumps({"plugin": "pi05_tp", "tp": world, "p50_ms_max_over_ranks": round(float(t), 3), "steps": len(ms),
                           "action_chunk": list(out.shape), "finite": bool(torch.isfinite(out.float()).all()),
-                          "path": "eager layers, row-parallel sums over peer memory (<= 4 MB) / NCCL"}))
+                          "path": type(engine.entry.scheduler.plan).__name__}))
     engine.close()
 
 

@@ -59,6 +59,11 @@ class PI05TPScheduler(PI05WS1Scheduler):
         return PI05TPPlan(self.model, max_batch_size=self.max_batch_size, num_images=self.num_images, device=self.device,
                           axis=self.axis)
 
+    def _before_capture(self, bucket: int) -> None:
+        # the warm-up runs execute the peer kernels for real, and their waits on peers are bounded: start together
+        if self.tp_size > 1:
+            self.plan.pg.sync()
+
     def _captured(self, bucket: int) -> None:
         # capture time differs between ranks; the first replay's bounded waits start together
         if self.tp_size > 1:
@@ -90,7 +95,8 @@ class PI05TPEntry(PI05Entry):
         eng = get_engine_config()
         self.model = self.build_model(args)
         n_img = resolve_num_images(args.inputs_image_shape, self.model.config.vision.num_channels)
-        self.scheduler = PI05TPScheduler(self.model, max_batch_size=args.max_batch_size, num_images=n_img, device=eng.device.target)
+        self.scheduler = PI05TPScheduler(self.model, max_batch_size=args.max_batch_size, num_images=n_img, device=eng.device.target,
+                                         use_cuda_graph=eng.runtime.use_cuda_graph)
         self.scheduler.setup()
 
 

@@ -73,6 +73,9 @@ class PI05WS1Scheduler(Scheduler):
         return PI05Plan(self.model, max_batch_size=self.max_batch_size, num_images=self.num_images,
                         device=self.device, quantization=self.quantization)
 
+    def _before_capture(self, bucket: int) -> None:
+        """Called before the warm-up runs and the capture of a bucket's graph."""
+
     def _captured(self, bucket: int) -> None:
         """Called once after a bucket's graph has been captured, before its first replay."""
 
@@ -124,6 +127,7 @@ class PI05WS1Scheduler(Scheduler):
             if self.use_cuda_graph:
                 g = self.graphs.get_or_create(bucket)
                 if not g.captured:
+                    self._before_capture(bucket)
                     g.capture(lambda: plan.run(bucket), {})
                     self._captured(bucket)
                 g.replay()
