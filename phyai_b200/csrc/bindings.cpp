@@ -327,6 +327,38 @@ void cfg_combine(const Tensor& cond, const Tensor& uncond, double g, const OptT&
         "cfg_combine_launch");
 }
 
+void unipc_step(const Tensor& v, const OptT& v_uncond, double g, Tensor& x, Tensor& x_last, Tensor& m1, Tensor& m2,
+                double sigma, bool has_corr, std::vector<double> corr, std::vector<double> pred, const OptT& keep,
+                const OptT& cond, int64_t C, int64_t T, int64_t inner, int64_t live_inner) {
+  TORCH_CHECK(v.is_cuda() && v.is_contiguous() && x.is_contiguous() && v.numel() == x.numel(), "unipc_step: v / x layout");
+  TORCH_CHECK(v.scalar_type() == at::kBFloat16 && x.scalar_type() == at::kBFloat16, "unipc_step: bf16 velocity and sample");
+  for (const Tensor* t : {&x_last, &m1, &m2})
+    TORCH_CHECK(t->is_contiguous() && t->scalar_type() == at::kFloat && t->numel() == x.numel(), "unipc_step: fp32 state of the sample's size");
+  TORCH_CHECK(corr.size() == 4 && pred.size() == 3, "unipc_step: corr (c_x, c_0, c_1, c_t), pred (p_x, p_0, p_1)");
+  TORCH_CHECK(C > 0 && T > 0 && inner > 0 && x.numel() % (C * T * inner) == 0, "unipc_step: [B, C, T, inner] view");
+  pb::UniPCStepArgs a;
+  a.v = bf(v); a.v_uncond = nullptr; a.g = float(g);
+  if (v_uncond.has_value() && v_uncond->defined()) {
+    TORCH_CHECK(v_uncond->is_contiguous() && v_uncond->scalar_type() == at::kBFloat16 && v_uncond->numel() == v.numel(), "unipc_step: v_uncond");
+    a.v_uncond = bf(*v_uncond);
+  }
+  a.x = bfm(x); a.x_last = reinterpret_cast<float*>(x_last.data_ptr());
+  a.m1 = reinterpret_cast<float*>(m1.data_ptr()); a.m2 = reinterpret_cast<float*>(m2.data_ptr());
+  a.sigma = float(sigma); a.has_corr = has_corr ? 1 : 0;
+  a.c_x = float(corr[0]); a.c_0 = float(corr[1]); a.c_1 = float(corr[2]); a.c_t = float(corr[3]);
+  a.p_x = float(pred[0]); a.p_0 = float(pred[1]); a.p_1 = float(pred[2]);
+  a.keep = nullptr; a.cond = nullptr;
+  if (keep.has_value() && keep->defined()) {
+    TORCH_CHECK(cond.has_value() && cond->defined() && cond->is_contiguous() && cond->scalar_type() == at::kBFloat16 &&
+                cond->numel() == x.numel(), "unipc_step: cond must match the sample");
+    TORCH_CHECK(keep->is_contiguous() && keep->element_size() == 1 && keep->numel() == x.numel() / (C * inner), "unipc_step: keep is [B, T] bytes");
+    a.keep = reinterpret_cast<const unsigned char*>(keep->data_ptr());
+    a.cond = bf(*cond);
+  }
+  a.n = x.numel(); a.inner = inner; a.T = T; a.C = C; a.live_inner = live_inner > 0 ? live_inner : inner;
+  check(pb::unipc_step_launch(a, cur_stream()), "unipc_step_launch");
+}
+
 void scatter_rows(const Tensor& src, Tensor& dst, const OptT& rows) {
   TORCH_CHECK(src.dim() == 2 && dst.dim() == 2 && src.stride(1) == 1 && dst.stride(1) == 1, "scatter_rows: layout");
   check(pb::scatter_rows_launch(bf(src), int(src.size(0)), int(src.size(1)), int(src.stride(0)),
@@ -477,6 +509,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("scatter_rows", &scatter_rows, py::arg("src"), py::arg("dst"), py::arg("rows") = py::none());
   m.def("quant_fp8", &quant_fp8);
   m.def("snake", &snake);
+  m.def("unipc_step", &unipc_step);
   m.def("gdn_decode", &gdn_decode, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("g"), py::arg("beta"),
         py::arg("state_pool"), py::arg("state_indices"), py::arg("scale"), py::arg("l2norm") = true);
   m.def("kernel_status", [] { return pb::read_and_clear_kernel_status(); });

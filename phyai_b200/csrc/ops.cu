@@ -769,6 +769,52 @@ cudaError_t cfg_combine_launch(const __nv_bfloat16* cond, const __nv_bfloat16* u
   return cudaGetLastError();
 }
 
+// ------------------------------------------------------------ UniPC sampler step
+// One multistep update of a flow-matching latent, element by element, with everything the host loop used to
+// issue as separate tensor ops: guidance combine, x0 prediction, corrector, predictor, history rotation and the
+// re-imposition of clean (conditioning) frames. The tensor is viewed as [B][C][T][inner]; `keep` flags (b, t)
+// pairs whose elements are overwritten with `cond` after the update; columns >= `live_inner` of the innermost
+// dimension carry no signal (padding of an action vector) and get a zero velocity.
+__global__ void unipc_step_kernel(UniPCStepArgs a) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
+  if (i >= a.n) return;
+  float v = bf2f(a.v[i]);
+  if (a.v_uncond) {
+    const float vu = bf2f(a.v_uncond[i]);
+    v = vu + a.g * (v - vu);
+  }
+  const long long col = i % a.inner;
+  if (col >= a.live_inner) v = 0.f;
+  const float x = bf2f(a.x[i]);
+  const float m_t = x - a.sigma * v;
+  const float m1 = a.m1[i];
+  float xs = x;
+  if (a.has_corr) {
+    xs = a.c_x * a.x_last[i] + a.c_0 * m1 + a.c_t * m_t;
+    if (a.c_1 != 0.f) xs += a.c_1 * a.m2[i];
+    xs = bf2f(__float2bfloat16(xs));          // the corrected sample is what a bf16 model input would have seen
+  }
+  float out = a.p_x * xs + a.p_0 * m_t;
+  if (a.p_1 != 0.f) out += a.p_1 * m1;
+  a.x_last[i] = xs;
+  a.m2[i] = m1;
+  a.m1[i] = m_t;
+  __nv_bfloat16 o = __float2bfloat16(out);
+  if (a.keep) {
+    const long long frame = (i / a.inner) % a.T;
+    const long long b = i / (a.inner * a.T * a.C);
+    if (a.keep[b * a.T + frame]) o = a.cond[i];
+  }
+  a.x[i] = o;
+}
+cudaError_t unipc_step_launch(const UniPCStepArgs& a, cudaStream_t s) {
+  if (a.n <= 0) return cudaSuccess;
+  PB_LAUNCH(unipc_step_kernel, unsigned((a.n + 255) / 256), 256, s, a);
+  return cudaGetLastError();
+}
+
 // --------------------------------------------------------------- row scatter
 __global__ void scatter_rows_kernel(const __nv_bfloat16* src, int D, int lds, __nv_bfloat16* dst,
                                     int ldd, const int* rows) {

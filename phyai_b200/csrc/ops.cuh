@@ -82,6 +82,28 @@ cudaError_t cfg_combine_launch(const __nv_bfloat16* cond, const __nv_bfloat16* u
                                __nv_bfloat16* out, float* x_fp32, float dt, long long n,
                                cudaStream_t s);
 
+// One UniPC (order <= 2, flow prediction) update of a latent viewed as [B][C][T][inner]:
+//   v = v_uncond + g (v - v_uncond)        when v_uncond is given
+//   m_t = x - sigma v;  x_s = c_x x_last + c_0 m1 + c_1 m2 + c_t m_t (has_corr) else x
+//   x <- p_x x_s + p_0 m_t + p_1 m1;  x_last <- x_s;  m2 <- m1;  m1 <- m_t
+//   x[b, :, t, :] <- cond[b, :, t, :] where keep[b, t]
+struct UniPCStepArgs {
+  const __nv_bfloat16* v;
+  const __nv_bfloat16* v_uncond;   // null: v is already guided
+  float g;
+  __nv_bfloat16* x;                // sample, in and out
+  float* x_last;                   // state (fp32, same numel)
+  float* m1;                       // x0 prediction of the previous step
+  float* m2;                       // ... of the step before
+  float sigma;
+  int has_corr;
+  float c_x, c_0, c_1, c_t, p_x, p_0, p_1;
+  const unsigned char* keep;       // [B, T] or null
+  const __nv_bfloat16* cond;       // same shape as x (read where keep is set)
+  long long n, inner, T, C, live_inner;
+};
+cudaError_t unipc_step_launch(const UniPCStepArgs& a, cudaStream_t s);
+
 // dst[rows[i], :] = src[i, :]   (row scatter of 16-byte aligned rows)
 cudaError_t scatter_rows_launch(const __nv_bfloat16* src, int n, int D, int lds,
                                 __nv_bfloat16* dst, int ldd, const int* rows, cudaStream_t s);

@@ -187,4 +187,50 @@ class UniPCMultistepSampler:
         return out.to(sample.dtype)
 
 
-__all__ = ["UniPCMultistepSampler", "StepCoeffs", "resolve_use_karras_sigmas"]
+class FusedUniPCStream:
+    """One latent stream of a denoise loop updated on the device by ``ops.unipc_step``: a single kernel per step
+    in place of the dozen tensor ops of :meth:`UniPCMultistepSampler.step` (and of the guidance combine and the
+    clean-frame copy around it). State (last corrected sample, two x0 predictions) is fp32; the sample stays bf16.
+
+    ``sample`` is read as ``[B, C, T, inner]`` (``view`` = (C, T, inner)); ``keep`` ``[B, T]`` marks frames that are
+    put back from ``cond`` after every update; innermost columns from ``live_inner`` on get a zero velocity.
+    The coefficient table is the sampler's (reference update: phyai/src/phyai/models/cosmos3/sampler_unipc.py:145-288)."""
+
+    def __init__(self, sampler: UniPCMultistepSampler, sample: torch.Tensor, *, view: tuple[int, int, int] | None = None,
+                 keep: torch.Tensor | None = None, cond: torch.Tensor | None = None, live_inner: int = 0) -> None:
+        if not (sample.is_cuda and sample.dtype == torch.bfloat16 and sample.is_contiguous()):
+            raise ValueError("the fused sampler updates a contiguous bf16 CUDA sample in place")
+        if sampler.num_inference_steps is None:
+            raise RuntimeError("call set_timesteps() on the sampler first")
+        self.table, self.sample, self.i = sampler.table, sample, 0
+        self.view = view if view is not None else (1, 1, sample.shape[-1])
+        self.live_inner = int(live_inner)
+        z = lambda: torch.zeros(sample.shape, dtype=torch.float32, device=sample.device)  # noqa: E731
+        self.x_last, self.m1, self.m2 = z(), z(), z()
+        self.keep = self.cond = None
+        if keep is not None:
+            if cond is None:
+                raise ValueError("keep needs the clean values")
+            self.keep = keep.to(device=sample.device, dtype=torch.uint8).contiguous()
+            self.cond = cond.to(device=sample.device, dtype=torch.bfloat16).expand_as(sample).contiguous()
+
+    @staticmethod
+    def usable(sample: torch.Tensor) -> bool:
+        return sample.is_cuda and sample.dtype == torch.bfloat16
+
+    def step(self, velocity: torch.Tensor, *, uncond: torch.Tensor | None = None, g: float = 1.0) -> torch.Tensor:
+        """``velocity`` already guided, or the conditional one with ``uncond`` and ``g`` for an in-kernel combine."""
+        from ... import ops
+
+        if self.i >= len(self.table):
+            raise RuntimeError("more sampler steps than timesteps")
+        c = self.table[self.i]
+        v = velocity.to(torch.bfloat16).contiguous()
+        u = None if uncond is None else uncond.to(torch.bfloat16).contiguous()
+        ops.unipc_step(v, self.sample, self.x_last, self.m1, self.m2, sigma=c.sigma, corr=c.corr, pred=c.pred, v_uncond=u, g=g,
+                       keep=self.keep, cond=self.cond, view=self.view, live_inner=self.live_inner)
+        self.i += 1
+        return self.sample
+
+
+__all__ = ["UniPCMultistepSampler", "StepCoeffs", "FusedUniPCStream", "resolve_use_karras_sigmas"]

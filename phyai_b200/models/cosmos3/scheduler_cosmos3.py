@@ -23,10 +23,11 @@ import torch
 
 from ... import ops
 from ... import parallel as P
+from ...env import envs
 from ...runtime import Scheduler
 from ...utils.profile import event_scope
 from .modeling_cosmos3 import Cosmos3Condition
-from .sampler_unipc import UniPCMultistepSampler
+from .sampler_unipc import FusedUniPCStream, UniPCMultistepSampler
 from .transformer_cosmos3 import Cosmos3Transformer
 
 
@@ -115,6 +116,9 @@ class Cosmos3Runner:
 class _GuidanceMixin:
     """CFG over one or two ``cfg`` ranks."""
 
+    #: UniPC update, guidance combine and clean frames as one kernel per step on CUDA bf16 (PHYAI_COSMOS3_FUSED_SAMPLER=0: tensor ops)
+    fused_sampler = bool(envs.PHYAI_COSMOS3_FUSED_SAMPLER.get())
+
     def _init_guidance(self) -> None:
         mesh = P.default_mesh()
         self.mesh = mesh
@@ -168,6 +172,13 @@ class _GuidanceMixin:
                 out.append((pair[1].float() + g * (pair[0].float() - pair[1].float())).to(v.dtype))
         return tuple(out)
 
+    def guided_pair(self, run_branch, g: float, do_cfg: bool):
+        """As :meth:`guided`, for a consumer that can combine the two branches itself (the fused sampler kernel):
+        returns ``(velocities, uncond velocities or None)``; the second is set only when both branches ran here."""
+        if do_cfg and self.cfg_size == 1:
+            return run_branch("cond"), run_branch("uncond")
+        return self.guided(run_branch, g, do_cfg), None
+
     @staticmethod
     def _combine_local(c: torch.Tensor, u: torch.Tensor, g: float) -> torch.Tensor:
         if c.is_cuda and c.dtype == torch.bfloat16:
@@ -203,7 +214,7 @@ class Cosmos3T2VScheduler(_GuidanceMixin, Scheduler):
         dev, dt = self.device, self.dtype
         t_lat, h_lat, w_lat = request.video_shape
         with_sound = request.sound_frames is not None
-        video = (request.noise.to(dev, dt) if request.noise is not None
+        video = (request.noise.to(dev, dt).clone() if request.noise is not None
                  else seeded_normal((1, self.latent_channel, t_lat, h_lat, w_lat), request.seed, dev, dt))
         sound = None
         if with_sound:
@@ -223,6 +234,15 @@ class Cosmos3T2VScheduler(_GuidanceMixin, Scheduler):
         uni_s = self._new_sampler(request.num_inference_steps) if with_sound else None
         self.runner.reset()
         scope = "cosmos3.t2av_denoise_loop" if with_sound else "cosmos3.denoise_loop"
+        fused_v = fused_s = None
+        if self.fused_sampler and FusedUniPCStream.usable(video):
+            # one kernel per stream and step: guidance combine, UniPC update and the clean frames in one pass
+            video = video.contiguous()
+            keep = None if frame_mask is None else ~frame_mask
+            fused_v = FusedUniPCStream(uni_v, video, view=(video.shape[1], t_lat, h_lat * w_lat), keep=keep,
+                                       cond=cond_latents if keep is not None else None)
+            if with_sound:
+                fused_s = FusedUniPCStream(uni_s, sound)
         with event_scope(scope):
             for timestep in uni_v.timesteps:
                 tval = timestep.to(dev).reshape(1).to(dt)
@@ -234,6 +254,12 @@ class Cosmos3T2VScheduler(_GuidanceMixin, Scheduler):
                                               sound_latents=sound, sound_fps=sfps)
                     return out if with_sound else (out,)
 
+                if fused_v is not None:
+                    vel, unc = self.guided_pair(run, request.guidance_scale, do_cfg)
+                    fused_v.step(vel[0], uncond=None if unc is None else unc[0], g=request.guidance_scale)
+                    if with_sound:
+                        fused_s.step(vel[1], uncond=None if unc is None else unc[1], g=request.guidance_scale)
+                    continue
                 vel = self.guided(run, request.guidance_scale, do_cfg)
                 video = uni_v.step(vel[0], timestep, video)
                 if with_sound:
@@ -332,6 +358,15 @@ class Cosmos3PolicyScheduler(_GuidanceMixin, Scheduler):
         uni_v.set_timesteps(request.num_inference_steps, device=dev)
         uni_a.set_timesteps(request.num_inference_steps, device=dev)
         self.runner.reset()
+        fused_v = fused_a = None
+        if self.fused_sampler and FusedUniPCStream.usable(video):
+            video, action = video.contiguous(), action.contiguous()
+            fused_v = FusedUniPCStream(uni_v, video, view=(video.shape[1], t_lat, h_lat * w_lat),
+                                       keep=None if cond_video is None else ~vmask, cond=cond_video)
+            held = action_clean and cond_action is not None     # forward dynamics: the action stream stays the given one
+            fused_a = FusedUniPCStream(uni_a, action, view=(1, chunk, ad), live_inner=raw,
+                                       keep=torch.ones(B, chunk, dtype=torch.bool, device=dev) if held else None,
+                                       cond=action.clone() if held else None)
         with event_scope("cosmos3.policy_denoise_loop"):
             for timestep in uni_v.timesteps:
                 tval = timestep.to(dev).reshape(1).to(dt)
@@ -342,6 +377,11 @@ class Cosmos3PolicyScheduler(_GuidanceMixin, Scheduler):
                                                video_shape=request.video_shape, fps=request.fps, noisy_frame_mask=vmask,
                                                action_latents=action, action_domain_id=domain, action_noisy_mask=amask)
 
+                if fused_v is not None:
+                    vel, unc = self.guided_pair(run, request.guidance_scale, do_cfg)
+                    fused_v.step(vel[0], uncond=None if unc is None else unc[0], g=request.guidance_scale)
+                    fused_a.step(vel[1], uncond=None if unc is None else unc[1], g=request.guidance_scale)
+                    continue
                 v_vel, a_vel = self.guided(run, request.guidance_scale, do_cfg)
                 a_vel = a_vel.clone()
                 a_vel[:, :, raw:] = 0.0

@@ -27,6 +27,7 @@ import torch
 
 from ... import ops
 from ... import parallel as P
+from ...env import envs
 from .modeling_pi05 import PI05Model
 from .plan_pi05 import PI05Plan
 
@@ -38,6 +39,8 @@ class PI05TPPlan(PI05Plan):
     fold_norms = False
     overlap_first_step = False
     use_expert_kernel = False
+    #: prefix reductions switch from "push the whole partial" to scatter / gather at this many rows (groups of 4+)
+    scatter_min_rows = int(envs.PHYAI_PI05_TP_SCATTER_ROWS.get())
 
     def __init__(self, model: PI05Model, *, max_batch_size: int = 1, num_images: int = 3, device="cuda",
                  quantization: str | None = None, axis: str = "tp", mesh=None) -> None:
@@ -63,10 +66,17 @@ class PI05TPPlan(PI05Plan):
         self.img_lo = min(self.rank * self.per, n_all)
         self.img_hi = min(self.img_lo + self.per, n_all)
         img_rows = self.per * v.num_patches
-        need = 2 * self.tp * (rows + img_rows) * H * 2 + (8 << 20)
+        # prefix rows at or above the threshold go reduce-scatter -> norm -> all-gather (each rank sums and norms
+        # only the rows it owns and every wire carries 1 / tp of the matrix twice, instead of the whole partial
+        # to every peer); the 50-row expert calls always push the whole partial
+        p_rows = self.B * self.P
+        self.scatter = self.tp >= 4 and p_rows >= self.scatter_min_rows
+        per = -(-p_rows // self.tp)
+        need = 2 * self.tp * (rows + img_rows + (per if self.scatter else 0)) * H * 2 + p_rows * H * 2 + (8 << 20)
         pg = PeerGroup.for_axis(self.mesh, axis, heap_bytes=max(need, 256 << 20))
         self.pg = pg
         self.st = pg.stream(f"pi05.tp:{rows}", rows, H)
+        self.st_sc = pg.stream(f"pi05.tp.sc:{p_rows}", per, H, gather_rows=p_rows, gather_cols=H) if self.scatter else None
         self.st_img = pg.stream(f"pi05.tp.img:{img_rows}", img_rows, H)
         self.v_proj = torch.zeros(img_rows, H, dtype=torch.bfloat16, device=self.device)
         self.v_all = torch.zeros(self.tp * img_rows, H, dtype=torch.bfloat16, device=self.device)
@@ -115,6 +125,8 @@ class PI05TPPlan(PI05Plan):
         last = len(lm.layers) - 1
         eps = t.rms_norm_eps
         ops.norm(h, "gemma_rms", weight=lm.layers[0].input_layernorm.weight, eps=eps, out=x)
+        if self.scatter:
+            return self._prefix_scatter(h, x, qkv, q3, attn, a3, act, n_per)
         for li, layer in enumerate(lm.layers):
             kpool, vpool = self.pool.layer(li)
             ops.gemm(x, self.tp_pqkv[li], qkv, rope=self.p_rope[li])
@@ -125,6 +137,28 @@ class PI05TPPlan(PI05Plan):
             self._reduce(attn, layer.attn.o.weight, h, x, norm="gemma_rms", weight=layer.post_attention_layernorm.weight, eps=eps)
             ops.gemm(x, layer.mlp.gate_up.weight, act, act="gelu_tanh", glu=True)
             self._reduce(act, layer.mlp.down.weight, h, x, norm="gemma_rms", weight=lm.layers[li + 1].input_layernorm.weight, eps=eps)
+
+    def _prefix_scatter(self, h, x, qkv, q3, attn, a3, act, n_per) -> None:
+        """Prefix blocks with a sequence-parallel residual: each product's tiles go to the rank that owns the rows,
+        which sums them, adds its residual rows, applies the next norm and stores the normalised rows into every
+        rank's gathered matrix; the next GEMM waits for those rows in its loader (all-gather fused into the GEMM)."""
+        t, lm, st = self.cfg.text, self.model.paligemma_lm, self.st_sc
+        D, eps = t.head_dim, t.rms_norm_eps
+        last = len(lm.layers) - 1
+        y, wait = x, None
+        for li, layer in enumerate(lm.layers):
+            kpool, vpool = self.pool.layer(li)
+            ops.gemm(y, self.tp_pqkv[li], qkv, rope=self.p_rope[li], wait=wait)
+            if li == last:
+                break
+            ops.attention(q3, kpool, vpool, a3, self.p_qstart, self.p_qlen, self.p_kvptr, self.p_kvlen,
+                          max_q_len=n_per, splits=self.prefix_splits, sm_scale=D ** -0.5)
+            t1 = st.linear_reduce(attn, layer.attn.o.weight, scatter=True, residual=h, norm="gemma_rms",
+                                  weight=layer.post_attention_layernorm.weight, eps=eps, gather=True)
+            ops.gemm(t1.y, layer.mlp.gate_up.weight, act, act="gelu_tanh", glu=True, wait=t1.wait)
+            t2 = st.linear_reduce(act, layer.mlp.down.weight, scatter=True, residual=h, norm="gemma_rms",
+                                  weight=lm.layers[li + 1].input_layernorm.weight, eps=eps, gather=True)
+            y, wait = t2.y, t2.wait
 
     def expert(self) -> None:
         cfg, e, t = self.cfg, self.cfg.expert, self.cfg.text

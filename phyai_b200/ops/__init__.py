@@ -267,6 +267,19 @@ def cfg_combine(cond: torch.Tensor, uncond: torch.Tensor, g: float, *,
     return out
 
 
+def unipc_step(v: torch.Tensor, x: torch.Tensor, x_last: torch.Tensor, m1: torch.Tensor, m2: torch.Tensor, *, sigma: float,
+               corr: Optional[tuple], pred: tuple, v_uncond: Optional[torch.Tensor] = None, g: float = 1.0,
+               keep: Optional[torch.Tensor] = None, cond: Optional[torch.Tensor] = None, view: tuple[int, int, int] | None = None,
+               live_inner: int = 0) -> torch.Tensor:
+    """One UniPC update of the bf16 sample ``x`` in place (guidance combine, x0 prediction, corrector, predictor,
+    history rotation, clean frames re-imposed); ``x_last`` / ``m1`` / ``m2`` are fp32 state of the same size.
+    ``view`` = (C, T, inner) of the ``[B, C, T, inner]`` reading that ``keep`` ``[B, T]`` and ``live_inner`` refer to."""
+    C, T, inner = view if view is not None else (1, 1, x.shape[-1])
+    ext().unipc_step(v, v_uncond, float(g), x, x_last, m1, m2, float(sigma), corr is not None,
+                     [float(c) for c in (corr or (0.0, 0.0, 0.0, 0.0))], [float(c) for c in pred], keep, cond, C, T, inner, live_inner)
+    return x
+
+
 def scatter_rows(src: torch.Tensor, dst: torch.Tensor,
                  rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     ext().scatter_rows(src, dst, rows)

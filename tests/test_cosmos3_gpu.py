@@ -121,3 +121,42 @@ def test_policy_scheduler_and_vae_on_gpu(engine_cuda):
     assert pix.shape == (1, 3, 5, 256, 384) and torch.isfinite(pix.float()).all()
     chunked = vae.decode(out["video"], frames_per_chunk=1)
     assert (pix.float() - chunked.float()).abs().max().item() < 0.1
+
+
+@pytest.mark.parametrize("mode", ["t2v_cond_frames", "policy", "forward_dynamics"])
+def test_fused_sampler_matches_tensor_op_sampler(engine_cuda, mode, monkeypatch):
+    """Whole requests with the one-kernel UniPC update against the same requests with the tensor-op sampler."""
+    from phyai_b200.models.cosmos3 import (Cosmos3ActionRequest, Cosmos3PolicyScheduler, Cosmos3T2VRequest, Cosmos3T2VScheduler,
+                                           Cosmos3Transformer)
+
+    policy = mode != "t2v_cond_frames"
+    cfg = small_real_config(action_gen=policy)
+    model = Cosmos3Transformer(cfg, params_dtype=torch.bfloat16, device="cuda").eval().init_random(2, std=0.05)
+    g = torch.Generator().manual_seed(0)
+    ids, nids = torch.randint(0, 512, (1, 20), generator=g), torch.randint(0, 512, (1, 20), generator=g)
+    mask = torch.ones(1, 20, dtype=torch.long)
+    outs = []
+    for fused in (True, False):
+        if policy:
+            sch = Cosmos3PolicyScheduler(model, device="cuda")
+            monkeypatch.setattr(sch, "fused_sampler", fused, raising=False)
+            sch.setup()
+            req = Cosmos3ActionRequest(ids, mask, nids, mask, video_shape=(2, 16, 24), mode=mode if mode != "policy" else "policy",
+                                       domain_id=1, action_chunk=8, raw_action_dim=7, action_dim=32,
+                                       cond_video_latents=torch.randn(1, 16, 2, 16, 24, generator=torch.Generator().manual_seed(1)),
+                                       cond_action=torch.randn(1, 8, 32, generator=torch.Generator().manual_seed(2)),
+                                       num_inference_steps=4, guidance_scale=3.0)
+            out = sch.step(req)
+            outs.append((out["video"].float().cpu(), out["action"].float().cpu()))
+        else:
+            sch = Cosmos3T2VScheduler(model, device="cuda")
+            monkeypatch.setattr(sch, "fused_sampler", fused, raising=False)
+            sch.setup()
+            req = Cosmos3T2VRequest(ids, mask, nids, mask, video_shape=(3, 16, 24), num_inference_steps=4, guidance_scale=4.0,
+                                    cond_latents=torch.randn(1, 16, 3, 16, 24, generator=torch.Generator().manual_seed(1)),
+                                    cond_frame_indexes=(0,))
+            outs.append((sch.step(req).float().cpu(),))
+    for a, b in zip(*outs):
+        assert torch.isfinite(a).all()
+        scale = b.abs().mean().item()
+        assert (a - b).abs().mean().item() <= 0.03 * scale, ((a - b).abs().mean().item(), scale)

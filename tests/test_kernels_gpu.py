@@ -504,3 +504,66 @@ def test_snake_kernel(dtype):
     torch.testing.assert_close(y.float(), want, atol=tol, rtol=tol)
     assert y.dtype == dtype
     _status_ok()
+
+
+@pytest.mark.parametrize("guided,with_keep", [(False, False), (True, True)])
+def test_unipc_step_kernel_matches_fp32_sampler(guided, with_keep):
+    """The fused sampler kernel over six steps against the tensor-op sampler run in fp32 on the same velocities."""
+    from phyai_b200.models.cosmos3.sampler_unipc import FusedUniPCStream, UniPCMultistepSampler
+
+    g = torch.Generator().manual_seed(3)
+    B, C, T, H, W = 2, 4, 5, 6, 8
+    n_steps, scale = 6, 3.0
+    x0 = torch.randn(B, C, T, H, W, generator=g).bfloat16()
+    cond = torch.randn(B, C, T, H, W, generator=g).bfloat16()
+    keep = torch.zeros(B, T, dtype=torch.bool)
+    keep[:, 0] = keep[1, 3] = True
+    vc = [torch.randn(B, C, T, H, W, generator=g).bfloat16() for _ in range(n_steps)]
+    vu = [torch.randn(B, C, T, H, W, generator=g).bfloat16() for _ in range(n_steps)]
+
+    ref = UniPCMultistepSampler()
+    ref.set_timesteps(n_steps)
+    x = x0.float().clone()
+    if with_keep:
+        x[keep[:, None, :].expand(B, C, T)] = cond.float()[keep[:, None, :].expand(B, C, T)]
+    start = x.clone()
+    for i in range(n_steps):
+        v = vu[i].float() + scale * (vc[i].float() - vu[i].float()) if guided else vc[i].float()
+        x = ref.step(v, None, x)
+        x = x.bfloat16().float()                    # the sample the model would see is bf16
+        if with_keep:
+            m = keep[:, None, :].expand(B, C, T)
+            x[m] = cond.float()[m]
+
+    fused = UniPCMultistepSampler()
+    fused.set_timesteps(n_steps)
+    xs = start.bfloat16().cuda().contiguous()
+    st = FusedUniPCStream(fused, xs, view=(C, T, H * W), keep=keep.cuda() if with_keep else None, cond=cond.cuda() if with_keep else None)
+    for i in range(n_steps):
+        if guided:
+            st.step(vc[i].cuda(), uncond=vu[i].cuda(), g=scale)
+        else:
+            st.step(vc[i].cuda())
+    _status_ok()
+    got = xs.float().cpu()
+    assert torch.allclose(got, x, atol=0.06, rtol=0.03), float((got - x).abs().max())
+    if with_keep:
+        m = keep[:, None, :].expand(B, C, T)
+        assert torch.equal(xs.cpu()[m], cond[m])
+
+
+def test_unipc_step_kernel_zero_tail_columns():
+    """Action vectors padded beyond the real action width: the padding columns get no velocity and stay zero."""
+    from phyai_b200.models.cosmos3.sampler_unipc import FusedUniPCStream, UniPCMultistepSampler
+
+    g = torch.Generator().manual_seed(4)
+    s = UniPCMultistepSampler()
+    s.set_timesteps(3)
+    a = torch.randn(2, 8, 32, generator=g).bfloat16()
+    a[:, :, 7:] = 0
+    xs = a.cuda().contiguous()
+    st = FusedUniPCStream(s, xs, view=(1, 8, 32), live_inner=7)
+    for _ in range(3):
+        st.step(torch.randn(2, 8, 32, generator=g).bfloat16().cuda())
+    _status_ok()
+    assert float(xs[:, :, 7:].abs().max()) == 0.0 and float(xs[:, :, :7].abs().max()) > 0.0
