@@ -91,6 +91,12 @@ def main() -> None:
             t = st.linear_reduce(x, w, scatter=scatter, residual=h, norm="rms", weight=wn, gather=True)
             ops.gemm(t.y, w2, z, wait=t.wait)
 
+        def single():
+            # whole partial to every peer, reduce + residual + norm in the GEMM's own CTAs (few rows) or in one
+            # reduce kernel, normalised rows local: what the Pi0.5 tensor-parallel plan issues
+            st.linear_reduce(x, w, residual=h, y=y, norm="rms", weight=wn)
+            ops.gemm(y, w2, z)
+
         def baseline():
             ops.gemm(x, w, part)
             dist.all_reduce(part)
@@ -109,6 +115,11 @@ def main() -> None:
             g_f = g_b = float("nan")
             if rank == 0:
                 print(f"# graph timing unavailable for {name}: {type(e).__name__}: {e}", flush=True)
+        one = {}
+        if not scatter:
+            before = st.single_launches
+            one = {"local_y_ms": round(timed(single), 4), "graph_local_y_ms": round(timed(single, graph=True), 4)}
+            one["single_launch"] = st.single_launches > before
         flops = 2.0 * M * N * K + 2.0 * M * N2 * N
         # per GPU over NVLink: scatter sends (w-1)/w of its partial and gathers (w-1)/w of the normed rows; one-shot sends w-1 partials
         link_bytes = (2.0 * (world - 1) / world * M * N * 2) if scatter else ((world - 1) * M * N * 2.0 + (world - 1) * M * N * 2.0)
@@ -117,7 +128,7 @@ def main() -> None:
                              nccl_composition_ms=round(t_b, 4), compute_only_ms=round(t_c, 4), graph_fused_ms=round(g_f, 4),
                              graph_nccl_composition_ms=round(g_b, 4), roofline_ms=round(roof_ms, 4),
                              frac_of_roofline=round(roof_ms / min(t_f, g_f if g_f == g_f else t_f), 3),
-                             speedup_vs_nccl=round(t_b / t_f, 3), graph_speedup_vs_nccl=round(g_b / g_f, 3) if g_f == g_f else None))
+                             speedup_vs_nccl=round(t_b / t_f, 3), graph_speedup_vs_nccl=round(g_b / g_f, 3) if g_f == g_f else None, **one))
     if world == 2:
         for name, n in (("cfg.cosmos3.super_latent", 16 * 8 * 44 * 80), ("cfg.cosmos3.720p_latent", 48 * 24 * 45 * 80)):
             v = torch.randn(n, device=dev, dtype=bf)

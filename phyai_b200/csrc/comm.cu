@@ -25,6 +25,8 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <torch/extension.h>
 
+#include <cstdlib>
+#include <cstring>
 #include <string>
 
 #include "comm_device.cuh"
@@ -259,12 +261,11 @@ pb::PeerPtrs to_ptrs(const std::vector<uintptr_t>& v, int64_t byte_off = 0) {
 // residual / h_out / y are indexed by global row. With y_gather_off >= 0 the normalised rows
 // go to that element offset of every rank's slab and y_channel is signalled; the return
 // value is then the number of arrivals a consumer of the gathered matrix waits for.
-int64_t reduce_norm(const std::vector<uintptr_t>& data_ptrs, int64_t rank, int64_t slots_off_elems,
-                 int64_t slot_stride, int64_t M, int64_t N, int64_t ld, int64_t sig_off_bytes,
-                 int64_t channel, int64_t expect, const OptT& residual, const OptT& col_gate,
-                 const OptT& bias, const OptT& h_out, const OptT& y, int64_t norm_mode,
-                 const OptT& weight, const OptT& mod, double eps, int64_t max_ctas,
-                 int64_t rows_per_rank, int64_t y_gather_off, int64_t y_ld, int64_t y_channel) {
+static pb::ReduceNormArgs make_reduce_args(const std::vector<uintptr_t>& data_ptrs, int64_t rank, int64_t slots_off_elems,
+                                           int64_t slot_stride, int64_t M, int64_t N, int64_t ld, const OptT& residual,
+                                           const OptT& col_gate, const OptT& bias, const OptT& h_out, const OptT& y,
+                                           int64_t norm_mode, const OptT& weight, const OptT& mod, double eps,
+                                           int64_t rows_per_rank, int64_t y_gather_off, int64_t y_ld, int64_t y_channel) {
   pb::ReduceNormArgs a;
   const int world = int(data_ptrs.size());
   a.slots = reinterpret_cast<const __nv_bfloat16*>(data_ptrs[rank]) + slots_off_elems;
@@ -292,15 +293,32 @@ int64_t reduce_norm(const std::vector<uintptr_t>& data_ptrs, int64_t rank, int64
     TORCH_CHECK(y_ld % 8 == 0 && y_gather_off % 8 == 0, "reduce_norm: gathered rows must be 16-byte aligned");
     a.y_world = world; a.y_off = y_gather_off; a.ldy = int(y_ld); a.y_channel = int(y_channel);
   }
+  return a;
+}
+
+static int64_t launch_reduce(const pb::ReduceNormArgs& a, const std::vector<uintptr_t>& data_ptrs, int64_t rank,
+                             int64_t sig_off_bytes, int64_t channel, int64_t expect, int64_t max_ctas) {
   auto* sig = reinterpret_cast<pb::ChannelSig*>(data_ptrs[rank] + sig_off_bytes);
-  int threads = int(((N / 8) + 31) / 32 * 32);
+  int threads = int(((a.N / 8) + 31) / 32 * 32);
   threads = threads > 512 ? 512 : (threads < 64 ? 64 : threads);
   int grid = int(a.nrows < max_ctas ? a.nrows : max_ctas);
   if (grid < 1) grid = 1;
   PB_LAUNCH(pb::reduce_norm_kernel, grid, threads, cur_stream(), a, sig, int(channel), unsigned(expect),
             to_ptrs(data_ptrs, sig_off_bytes), pb::kernel_status_ptr());
   throw_on(cudaGetLastError(), "reduce_norm_kernel");
-  return int64_t(grid) * world;
+  return int64_t(grid) * int64_t(data_ptrs.size());
+}
+
+int64_t reduce_norm(const std::vector<uintptr_t>& data_ptrs, int64_t rank, int64_t slots_off_elems,
+                 int64_t slot_stride, int64_t M, int64_t N, int64_t ld, int64_t sig_off_bytes,
+                 int64_t channel, int64_t expect, const OptT& residual, const OptT& col_gate,
+                 const OptT& bias, const OptT& h_out, const OptT& y, int64_t norm_mode,
+                 const OptT& weight, const OptT& mod, double eps, int64_t max_ctas,
+                 int64_t rows_per_rank, int64_t y_gather_off, int64_t y_ld, int64_t y_channel) {
+  const pb::ReduceNormArgs a = make_reduce_args(data_ptrs, rank, slots_off_elems, slot_stride, M, N, ld, residual, col_gate,
+                                                bias, h_out, y, norm_mode, weight, mod, eps, rows_per_rank, y_gather_off,
+                                                y_ld, y_channel);
+  return launch_reduce(a, data_ptrs, rank, sig_off_bytes, channel, expect, max_ctas);
 }
 
 int64_t push_partial(const Tensor& x, const std::vector<uintptr_t>& data_ptrs, int64_t rank,
@@ -329,6 +347,7 @@ int64_t gemm_push(const Tensor& x, const Tensor& w, const std::vector<uintptr_t>
   TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16, "gemm_push: bf16 operands");
   TORCH_CHECK(x.size(1) == w.size(1), "gemm_push: K mismatch");
   pb::PushParams pp;
+  memset(&pp, 0, sizeof(pp));
   pp.data = to_ptrs(data_ptrs);
   pp.sig = to_ptrs(data_ptrs, sig_off_bytes);
   pp.local_sig = reinterpret_cast<const void*>(data_ptrs[rank] + sig_off_bytes);
@@ -347,6 +366,43 @@ int64_t gemm_push(const Tensor& x, const Tensor& w, const std::vector<uintptr_t>
   int ctas = 0;
   throw_on(pb::gemm_launch(a, cur_stream(), &ctas), "gemm_launch (push)");
   return int64_t(ctas) * pp.world;
+}
+
+// Row-parallel linear + all-reduce + residual (* gate) + norm over the peer group. On few rows the GEMM's own CTAs
+// do the consumer half after their arrival (one launch); otherwise the product is pushed and the reduce kernel
+// follows. Returns 1 when it was a single launch.
+int64_t linear_reduce(const Tensor& x, const Tensor& w, const std::vector<uintptr_t>& data_ptrs, int64_t rank,
+                      int64_t slots_off_elems, int64_t slot_stride, int64_t ld, int64_t sig_off_bytes, int64_t channel,
+                      const OptT& residual, const OptT& col_gate, const OptT& bias, const OptT& h_out, const OptT& y,
+                      int64_t norm_mode, const OptT& weight, const OptT& mod, double eps, int64_t max_ctas, bool allow_tail) {
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1, "linear_reduce: layout");
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16, "linear_reduce: bf16 operands");
+  TORCH_CHECK(x.size(1) == w.size(1), "linear_reduce: K mismatch");
+  const int64_t M = x.size(0), N = w.size(0);
+  pb::PushParams pp;
+  memset(&pp, 0, sizeof(pp));
+  pp.data = to_ptrs(data_ptrs);
+  pp.sig = to_ptrs(data_ptrs, sig_off_bytes);
+  pp.local_sig = reinterpret_cast<const void*>(data_ptrs[rank] + sig_off_bytes);
+  pp.slots_off = slots_off_elems; pp.slot_stride = slot_stride; pp.ld = int(ld);
+  pp.world = int(data_ptrs.size()); pp.rank = int(rank); pp.channel = int(channel);
+  pp.rows_per_rank = 0; pp.wait_channel = -1; pp.wait_expect = 0;
+  pp.red = make_reduce_args(data_ptrs, rank, slots_off_elems, slot_stride, M, N, ld, residual, col_gate, bias, h_out, y,
+                            norm_mode, weight, mod, eps, 0, -1, 0, 0);
+  static const bool tail_env = [] { const char* e = getenv("PHYAI_COMM_FUSED_TAIL"); return !e || atoi(e) != 0; }();
+  pp.tail = (allow_tail && tail_env && M <= 256) ? 1 : 0;
+  pb::GemmArgs a;
+  a.x = x.data_ptr(); a.w = w.data_ptr(); a.out = nullptr;
+  a.M = int(M); a.N = int(N); a.K = int(x.size(1));
+  a.ldx = int(x.stride(0)); a.ldw = int(w.stride(0)); a.ldo = int(ld);
+  TORCH_CHECK(M * ld <= slot_stride && N <= ld, "linear_reduce: product does not fit a slot");
+  a.push = &pp;
+  int ctas = 0, tail_done = 0;
+  a.tail_done = &tail_done;
+  throw_on(pb::gemm_launch(a, cur_stream(), &ctas), "gemm_launch (linear_reduce)");
+  if (tail_done) return 1;
+  launch_reduce(pp.red, data_ptrs, rank, sig_off_bytes, channel, int64_t(ctas) * pp.world, max_ctas);
+  return 0;
 }
 
 void cfg_exchange(const Tensor& mine, const std::vector<uintptr_t>& data_ptrs, int64_t my_pos,
@@ -405,6 +461,7 @@ void register_comm(py::module_& m) {
   m.def("reduce_norm", &reduce_norm);
   m.def("push_partial", &push_partial);
   m.def("gemm_push", &gemm_push);
+  m.def("linear_reduce", &linear_reduce);
   m.def("cfg_exchange", &cfg_exchange);
   m.def("gather_consume", &gather_consume);
   m.def("flag_wait_probe", &flag_wait_probe);

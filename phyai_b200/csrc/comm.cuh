@@ -15,6 +15,33 @@ struct PeerPtrs {
   void* p[kMaxRanks];
 };
 
+// What the consumer of a pushed product does with it: h = residual + (sum of the ranks' slots + bias) * gate,
+// y = norm(h). Used by the stand-alone reduce kernel and by the tail of a push-mode GEMM (see PushParams::tail).
+struct ReduceNormArgs {
+  const __nv_bfloat16* slots;   // local: [world][M][ld] partials of this call's parity
+  long long slot_stride;        // elements between consecutive ranks' slots
+  int world, M, N, ld;
+  __nv_bfloat16* residual;      // [M, ldr] in/out: h = residual + sum * gate; may be null
+  int ldr;
+  const __nv_bfloat16* col_gate;  // [N] or null
+  const __nv_bfloat16* bias;      // [N] or null (added once)
+  __nv_bfloat16* h_out;         // where h goes when residual is null (may be null)
+  int ldh;
+  __nv_bfloat16* y;             // [M, ldy] normalised output (null: no norm)
+  int ldy;
+  int norm_mode;                // NormMode from ops.cuh; -1 = none
+  const __nv_bfloat16* weight;  // rms / gemma weight
+  const __nv_bfloat16* mod;     // AdaRMS row (scale | shift | gate), shared by all rows
+  float eps;
+  int row0, nrows;              // rows this rank reduces ([0, M) unless the producer scattered)
+  int slot_row0;                // global row stored at slot row 0 (row0 when scattered, else 0)
+  // all-gather of the normalised rows: y_world > 0 stores each y row at element offset
+  // y_off + row * ldy of EVERY rank's slab instead of `y`, then signals y_channel
+  PeerPtrs y_dst;
+  long long y_off;
+  int y_world, y_channel;
+};
+
 // Where a GEMM epilogue in push mode sends its tiles: slots[parity][rank] of every
 // rank's symmetric slab, then one arrival per CTA on every rank's channel counter.
 // world == 0 means "not pushing" (the kernel stores to its ordinary output).
@@ -34,6 +61,12 @@ struct PushParams {
   int rows_per_rank;
   int wait_channel;
   unsigned int wait_expect;
+  // tail != 0 (push mode on few rows, every CTA of the grid resident at once): after its arrival each CTA
+  // waits for tail_expect arrivals on the channel and reduces its share of the rows (`red`), so the product,
+  // the all-reduce, the residual and the norm are one launch and one peer round trip
+  int tail;
+  unsigned int tail_expect;
+  ReduceNormArgs red;
 };
 
 }  // namespace pb

@@ -75,30 +75,6 @@ __device__ __forceinline__ void channel_signal_all(const PeerPtrs& sig, int chan
   }
 }
 
-struct ReduceNormArgs {
-  const __nv_bfloat16* slots;   // local: [world][M][ld] partials of this call's parity
-  long long slot_stride;        // elements between consecutive ranks' slots
-  int world, M, N, ld;
-  __nv_bfloat16* residual;      // [M, ldr] in/out: h = residual + sum * gate; may be null
-  int ldr;
-  const __nv_bfloat16* col_gate;  // [N] or null
-  const __nv_bfloat16* bias;      // [N] or null (added once)
-  __nv_bfloat16* h_out;         // where h goes when residual is null (may be null)
-  int ldh;
-  __nv_bfloat16* y;             // [M, ldy] normalised output (null: no norm)
-  int ldy;
-  int norm_mode;                // NormMode from ops.cuh; -1 = none
-  const __nv_bfloat16* weight;  // rms / gemma weight
-  const __nv_bfloat16* mod;     // AdaRMS row (scale | shift | gate), shared by all rows
-  float eps;
-  int row0, nrows;              // rows this rank reduces ([0, M) unless the producer scattered)
-  int slot_row0;                // global row stored at slot row 0 (row0 when scattered, else 0)
-  // all-gather of the normalised rows: y_world > 0 stores each y row at element offset
-  // y_off + row * ldy of EVERY rank's slab instead of `y`, then signals y_channel
-  PeerPtrs y_dst;
-  long long y_off;
-  int y_world, y_channel;
-};
 
 // One CTA reduces row `row`: h = residual + (sum_r slot_r + bias) * gate, y = norm(h).
 // `red` is 32 floats of shared memory. N must be a multiple of 8.

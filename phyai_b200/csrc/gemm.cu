@@ -77,6 +77,9 @@ constexpr int kRowBytes = 128;     // one swizzle-128B row: 64 bf16 or 128 e4m3
 // activation loads). The plain variant does not even carry the parameter block, which keeps
 // the launch descriptor of the thousands of ordinary GEMMs in a captured step small.
 struct NoComm { int wait_channel, world; };
+// Largest grid whose CTAs are taken to be resident at once (148 SMs, one CTA each; clusters of up to eight
+// fragment over the GPCs, hence the margin).
+constexpr int kTailMaxCtas = 128;
 template <int BN, bool SWAP, bool FP8, bool COMM>
 __global__ void __launch_bounds__(kThreads)
 gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
@@ -282,6 +285,30 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
                         m0, n0, split * rows_per_cta, rows_per_cta, nsplit, warp, lane, kThreads / 32);
       __syncthreads();
       if (threadIdx.x == 0) channel_signal_all(push.sig, push.channel, parity, push.world);
+      if (push.tail) {
+        // consumer half in the same launch: all CTAs of the grid are resident, so waiting here for every
+        // rank's tiles (this rank's other CTAs included) cannot starve a CTA that has not pushed yet
+        __shared__ float tail_red[32];
+        __shared__ int tail_ok;
+        ChannelSig* lsm = const_cast<ChannelSig*>(ls);
+        if (threadIdx.x == 0) {
+          const bool ok = wait_counter_ge(&ls->arrive[parity], push.tail_expect);
+          tail_ok = ok ? 1 : 0;
+          if (!ok && status) atomicCAS(status, 0, kStatusTimeoutPeer);
+        }
+        __syncthreads();
+        const int n_cta = gridDim.x * gridDim.y * gridDim.z;
+        if (tail_ok) {
+          ReduceNormArgs b = push.red;
+          b.slots = push.red.slots + size_t(parity) * b.world * b.slot_stride;
+          const int lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+          for (int row = lin; row < b.M; row += n_cta) {
+            reduce_norm_row(b, row, tail_red);
+            __syncthreads();
+          }
+        }
+        channel_finish(lsm, parity, unsigned(n_cta));
+      }
     }
     if (!pushed) {
       epilogue_pass<TN>(ep, reinterpret_cast<const float*>(smem), smem_u32(smem), LDS, m0, n0,
@@ -467,6 +494,7 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream, int* n_ctas) {
   const int eb = a.fp8 ? 1 : 2;
   const int BK = a.fp8 ? 128 : 64;
   if (a.M <= 0 || a.N <= 0 || a.K <= 0) return cudaErrorInvalidValue;
+  if (a.tail_done) *a.tail_done = 0;
   // TMA: 16-byte aligned base and row strides; vector epilogue: N multiple of 8.
   if ((reinterpret_cast<uintptr_t>(a.x) & 15) || (reinterpret_cast<uintptr_t>(a.w) & 15) ||
       (size_t(a.ldx) * eb) % 16 || (size_t(a.ldw) * eb) % 16 || (a.N % 8) ||
@@ -603,6 +631,12 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream, int* n_ctas) {
   }
   dim3 grid(p_tiles, q_tiles, splits);
   if (n_ctas) *n_ctas = p_tiles * q_tiles * splits;
+  if (push.tail) {
+    // the tail waits on this grid's own CTAs: only when all of them (clusters included) are resident together
+    if (p_tiles * q_tiles * splits > kTailMaxCtas || push.world <= 0 || push.rows_per_rank > 0) push.tail = 0;
+    else push.tail_expect = unsigned(p_tiles * q_tiles * splits) * unsigned(push.world);
+  }
+  if (a.tail_done) *a.tail_done = push.tail;
   if (swap) {
     return a.fp8 ? launch_bn<true, true>(bn, tmP, tmQ, ep, push, grid, total_kb, kbps, stages, smem, stream, a.trace)
                  : launch_bn<true, false>(bn, tmP, tmQ, ep, push, grid, total_kb, kbps, stages, smem, stream, a.trace);

@@ -71,6 +71,8 @@ struct GemmArgs {
   // Push mode (row-parallel linear fused with its all-reduce): the raw bf16 product goes to
   // every rank's slots instead of `out`; bias/act/residual belong to the consumer kernel.
   const PushParams* push = nullptr;
+  // receives 1 when the launch also ran the consumer half (push->tail asked for it and the grid allowed it)
+  int* tail_done = nullptr;
 };
 
 // Launches on `stream`. Returns cudaSuccess or the launch error; argument

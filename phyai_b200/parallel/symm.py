@@ -183,6 +183,7 @@ class PeerStream:
         self.channel = pg.new_channel()
         self.y_off = pg.alloc(self.gather_rows * self.gather_cols * 2) if gather_rows else -1
         self.y_channel = pg.new_channel() if gather_rows else -1
+        self.single_launches = 0          # linear_reduce calls served by one launch (GEMM with the reduce tail)
 
     # ---- producers
     def _check(self, rows: int, cols: int, scatter: bool) -> int:
@@ -242,8 +243,23 @@ class PeerStream:
 
     # ---- composed collectives
     def linear_reduce(self, x: torch.Tensor, w: torch.Tensor, *, scatter: bool = False, **kw):
+        """Row-parallel ``x @ w.T`` summed over the ranks, with the residual / gate / norm of :meth:`reduce`.
+        Whole-partial calls that gather nothing go through one native entry, which on few rows runs the
+        consumer half in the GEMM's own CTAs (one launch, one peer round trip)."""
+        if not scatter and not kw.get("gather", False):
+            return self._linear_reduce_local(x, w, **kw)
         expect, per = self.gemm_push(x, w, scatter=scatter)
         return self.reduce(expect, x.shape[0], w.shape[0], rows_per_rank=per, **kw)
+
+    def _linear_reduce_local(self, x: torch.Tensor, w: torch.Tensor, *, residual=None, col_gate=None, bias=None, h_out=None,
+                             y=None, norm: str | None = None, weight=None, mod=None, eps: float = 1e-6, gather: bool = False,
+                             max_ctas: int = 592, allow_tail: bool = True) -> None:
+        self._check(x.shape[0], w.shape[0], False)
+        pg = self.pg
+        mode = _NORM_NONE if norm is None else ops.NORM[norm]
+        self.single_launches += int(pg.ext.linear_reduce(x, w, pg.ptrs, pg.pos, self.slots_off // 2, self.slot_stride, self.max_cols, 0,
+                                                         self.channel, residual, col_gate, bias, h_out, y, mode, weight, mod, eps,
+                                                         max_ctas, allow_tail))
 
     def all_reduce(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """Sum of a (rows, cols) bf16 matrix over the ranks."""

@@ -63,6 +63,26 @@ def main() -> int:
         h_ref = res.float() + part * gate.float()
         check(f"linear_reduce.h[{it}]", h, h_ref, 0.03)
         check(f"linear_reduce.y[{it}]", y, ref.rms_norm(h.float(), wn.float(), 1e-6, gemma=True), 0.03)
+    if stl.single_launches != 3:
+        fails.append(f"50-row linear_reduce ran as {stl.single_launches} single launches of 3 (the reduce tail did not engage)")
+    # the same shape as two launches (push GEMM, reduce kernel), AdaRMS this time, and a many-row call that never takes the tail
+    mod, _ = rnd(3 * N, per_rank=False, scale=0.2)
+    for it, (rows, tail) in enumerate([(M, False), (300, True)]):
+        x, _ = rnd(rows, K, scale=0.5)
+        w, _ = rnd(N, K, scale=0.1)
+        res, _ = rnd(rows, N, per_rank=False)
+        h = res.clone()
+        y = torch.empty_like(h)
+        before = stl.single_launches
+        stl.linear_reduce(x, w, residual=h, col_gate=mod[2 * N:], y=y, norm="ada_rms", mod=mod, eps=1e-6, allow_tail=tail)
+        if stl.single_launches != before:
+            fails.append(f"linear_reduce case {it} took the single-launch path")
+        part = nccl_sum(x.float() @ w.float().t())
+        h_ref = res.float() + part * mod[2 * N:].float()
+        check(f"linear_reduce.two_launch.h[{it}]", h, h_ref, 0.03)
+        hb = h.float()
+        y_ref = hb * torch.rsqrt(hb.pow(2).mean(-1, keepdim=True) + 1e-6) * (1 + mod[:N].float()) + mod[N:2 * N].float()
+        check(f"linear_reduce.two_launch.y[{it}]", y, y_ref, 0.03)
 
     # ---- 3. two-step: scatter to row owners, reduce + norm there, gather into every rank, GEMM waits
     M, K, N, N2 = 777, 512, 1024, 768
