@@ -23,7 +23,8 @@ def main() -> None:
     torch.cuda.set_device(local)
     dev = f"cuda:{local}"
     cfg = EngineConfig(device=DeviceConfig(dev, torch.bfloat16), parallel=ParallelConfig(world_size=world, tp_size=world))
-    engine = Engine(EngineArgs("pi05_tp", PI05TPArgs(checkpoint_dir=None, max_batch_size=1, inputs_image_shape=[[224, 224, 3]] * 3), cfg))
+    engine = Engine(EngineArgs("pi05_tp", PI05TPArgs(checkpoint_dir=None, max_batch_size=1, inputs_image_shape=[[224, 224, 3]] * 3,
+                                                     shard_expert=os.environ.get("PI05_TP_SHARD_EXPERT", "0") == "1"), cfg))
     g = torch.Generator().manual_seed(0)                     # the same request on every rank
     req = PI05Request(pixel_values=(torch.rand(1, 3, 3, 224, 224, generator=g) * 2 - 1).to(dev, torch.bfloat16),
                       input_ids=torch.randint(0, 1000, (1, 200), generator=g).to(dev), lang_lens=torch.tensor([200], device=dev),
@@ -52,7 +53,8 @@ def main() -> None:
     if rank == 0:
         print(json.dumps({"plugin": "pi05_tp", "tp": world, "p50_ms_max_over_ranks": round(float(t), 3), "steps": len(ms),
                           "action_chunk": list(out.shape), "finite": bool(torch.isfinite(out.float()).all()),
-                          "path": type(engine.entry.scheduler.plan).__name__}))
+                          "path": type(engine.entry.scheduler.plan).__name__,
+                          "expert": "whole on every rank" if getattr(engine.entry.scheduler.plan, "expert_replicated", True) else "sharded"}))
     engine.close()
 
 

@@ -67,13 +67,13 @@ class PI0Plan(PI05Plan):
 
             stack = self.model.expert_stack
             t = cfg.text
-            Hq, Hkv, D = self.Hq, self.Hkv, t.head_dim
+            Hq, Hkv, D = self.Hq_e, self.Hkv, t.head_dim
             # QKV rows reordered for the rotating epilogue; block 0 keeps its norm kernel and the plain weight
             self.fold_qkv = [ops.permute_rope_rows(fold(l.attn.qkv.weight, l.input_layernorm.weight) if li > 0
                                                    else l.attn.qkv.weight, Hq, Hkv, D)
                              for li, l in enumerate(stack.layers)]
-            self.e_rope = self._rope_descs(self.e_q, self.e_pos, self.e_slots)
-            self.s_rope = self._rope_descs(self.s_q, self.s_pos, self.s_slots)
+            self.e_rope = self._rope_descs(self.e_q, self.e_pos, self.e_slots, self.Hq_e)
+            self.s_rope = self._rope_descs(self.s_q, self.s_pos, self.s_slots, self.Hq_e)
             self.fold_gate_up = [fold(l.mlp.gate_up.weight, l.post_attention_layernorm.weight) for l in stack.layers]
             self.fold_out = fold(heads.action_out_proj.weight, stack.norm.weight)
             self.e_ss = torch.zeros(2, self.Me, dtype=torch.float32, device=self.device)
@@ -91,7 +91,7 @@ class PI0Plan(PI05Plan):
     def _block(self, layer, li, h, x, qkv, q, attn, act, pos, slots, qstart, qlen, kvlen, max_q, splits,
                ss=None, rope=None) -> None:
         t, e = self.cfg.text, self.cfg.expert
-        Hq, Hkv, D = self.Hq, self.Hkv, t.head_dim
+        Hq, Hkv, D = self.Hq_e, self.Hkv, t.head_dim
         kpool, vpool = self.pool.layer(li)
         if ss is not None:
             rms = (e.hidden_size, e.rms_norm_eps)
@@ -120,6 +120,9 @@ class PI0Plan(PI05Plan):
     def expert(self) -> None:
         self.state_pass()
         self.euler_loop()
+
+    def _first_step_overlappable(self) -> bool:
+        return False           # this plan's own run() puts the state-token pass on the second stream
 
     def state_pass(self, before_block=None) -> None:
         """The state token of every robot through the expert, once per request. ``before_block(li)`` runs before

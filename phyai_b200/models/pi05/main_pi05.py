@@ -81,6 +81,10 @@ class PI05Entry(Entry):
     #: mesh axis the vision encoder blocks are sharded over (``None``: whole tower on every rank)
     vision_axis: ClassVar[str | None] = "tp"
 
+    def expert_axis_for(self, args) -> str | None:
+        """Mesh axis the action expert is sharded over (``None``: whole on every rank)."""
+        return "tp"
+
     def __init__(self) -> None:
         self.model: PI05Model | None = None
         self.scheduler: PI05WS1Scheduler | None = None
@@ -95,7 +99,7 @@ class PI05Entry(Entry):
             config = PI05Config()
         with use_quant_plan(load_quant_plan(args.checkpoint_dir)):
             model = PI05Model(config, vision_params_dtype=args.vision_params_dtype, device=eng.device.target,
-                              vision_axis=self.vision_axis)
+                              vision_axis=self.vision_axis, expert_axis=self.expert_axis_for(args))
         if args.checkpoint_dir is not None:
             load_pretrained(model, args.checkpoint_dir, remap=compose_remap(args.weight_remap), strict=args.weight_strict)
         elif args.random_init_seed is not None:

@@ -2,10 +2,10 @@
 
 All ranks of the ``tp`` axis take the same request and return the same action chunk. On CUDA bf16 the
 request runs through :class:`PI05TPPlan`, captured as one CUDA graph per prompt bucket: q heads and
-MLP columns are sharded (the single KV head of the Gemma stacks is replicated), every row-parallel
-product leaves its GEMM through the epilogue into the peers' memory and is summed by the kernel that also
-applies the gate, the residual and the next (Ada)RMS norm, and the cameras (not the vision weights) are
-split over the ranks. Elsewhere (CPU, fp32, a single rank) the eager model path runs, with the
+MLP columns of the prefix decoder are sharded (the single KV head of the Gemma stacks is replicated), every
+row-parallel product leaves its GEMM through the epilogue into the peers' memory and is summed by the kernel
+that also applies the residual and the next RMS norm, the cameras (not the vision weights) are split over the
+ranks, and the action expert stays whole on every rank unless ``shard_expert`` asks otherwise. Elsewhere (CPU, fp32, a single rank) the eager model path runs, with the
 row-parallel products summed by ``parallel.all_reduce``.
 
 The reference has TP-capable Pi0.5 layers and no scheduler that drives them
@@ -81,7 +81,9 @@ class PI05TPScheduler(PI05WS1Scheduler):
 
 @dataclass
 class PI05TPArgs(PI05Args):
-    pass
+    #: shard the action expert too. Off by default: at 0.6 GB it is kept whole on every rank, which lets the Euler
+    #: loop run without communication (the latency-bound part of a request); on, its blocks reduce over peer memory
+    shard_expert: bool = False
 
 
 @Engine.register
@@ -90,6 +92,9 @@ class PI05TPEntry(PI05Entry):
     args_cls: ClassVar[type[EntryArgs]] = PI05TPArgs
     #: the encoder blocks of the vision tower stay whole on every rank (see PI05TPPlan)
     vision_axis: ClassVar[str | None] = None
+
+    def expert_axis_for(self, args) -> str | None:
+        return "tp" if getattr(args, "shard_expert", False) else None
 
     def setup(self, args: PI05TPArgs) -> None:  # type: ignore[override]
         eng = get_engine_config()

@@ -129,11 +129,11 @@ class PI05VisionTower(nn.Module):
 
 # ------------------------------------------------------------------ prefix LM
 class GemmaMLP(nn.Module):
-    def __init__(self, hidden: int, inter: int, dtype, prefix: str) -> None:
+    def __init__(self, hidden: int, inter: int, dtype, prefix: str, axis: str | None = "tp") -> None:
         super().__init__()
         self.gate_up = MergedColumnParallelLinear(hidden, [inter, inter], bias=False, params_dtype=dtype,
-                                                  interleave=True, prefix=f"{prefix}.gate_up_proj")
-        self.down = RowParallelLinear(inter, hidden, bias=False, params_dtype=dtype, prefix=f"{prefix}.down_proj")
+                                                  interleave=True, prefix=f"{prefix}.gate_up_proj", axis=axis)
+        self.down = RowParallelLinear(inter, hidden, bias=False, params_dtype=dtype, prefix=f"{prefix}.down_proj", axis=axis)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         gu, _ = self.gate_up(x)
@@ -144,12 +144,12 @@ class GemmaMLP(nn.Module):
 class GemmaAttentionProj(nn.Module):
     """q/k/v + o projections of one Gemma block (the attention itself is the caller's)."""
 
-    def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, dtype, prefix: str) -> None:
+    def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, dtype, prefix: str, axis: str | None = "tp") -> None:
         super().__init__()
         self.head_dim = head_dim
         self.qkv = QKVParallelLinear(hidden, head_dim, heads, kv_heads, bias=False, params_dtype=dtype,
-                                     prefix=f"{prefix}.qkv_proj")
-        self.o = RowParallelLinear(heads * head_dim, hidden, bias=False, params_dtype=dtype, prefix=f"{prefix}.o_proj")
+                                     prefix=f"{prefix}.qkv_proj", axis=axis)
+        self.o = RowParallelLinear(heads * head_dim, hidden, bias=False, params_dtype=dtype, prefix=f"{prefix}.o_proj", axis=axis)
 
     def project_qkv(self, x: torch.Tensor):
         qkv, _ = self.qkv(x)
@@ -198,15 +198,15 @@ class PaliGemmaLanguageModel(nn.Module):
 
 # ------------------------------------------------------------- action expert
 class PI05ExpertLayer(nn.Module):
-    def __init__(self, cfg: GemmaExpertConfig, dtype, prefix: str) -> None:
+    def __init__(self, cfg: GemmaExpertConfig, dtype, prefix: str, axis: str | None = "tp") -> None:
         super().__init__()
         self.input_layernorm = AdaRMSNorm(cfg.hidden_size, cfg.adarms_cond_dim, cfg.rms_norm_eps, dtype=dtype,
                                           prefix=f"{prefix}.input_layernorm")
         self.attn = GemmaAttentionProj(cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
-                                       dtype, f"{prefix}.self_attn")
+                                       dtype, f"{prefix}.self_attn", axis)
         self.post_attention_layernorm = AdaRMSNorm(cfg.hidden_size, cfg.adarms_cond_dim, cfg.rms_norm_eps, dtype=dtype,
                                                    prefix=f"{prefix}.post_attention_layernorm")
-        self.mlp = GemmaMLP(cfg.hidden_size, cfg.intermediate_size, dtype, f"{prefix}.mlp")
+        self.mlp = GemmaMLP(cfg.hidden_size, cfg.intermediate_size, dtype, f"{prefix}.mlp", axis)
 
     def forward(self, h: torch.Tensor, cond: torch.Tensor, cos_sin: torch.Tensor, k_prefix: torch.Tensor,
                 v_prefix: torch.Tensor) -> torch.Tensor:
@@ -221,11 +221,14 @@ class PI05ExpertLayer(nn.Module):
 
 
 class PI05ExpertStack(nn.Module):
-    def __init__(self, cfg: GemmaExpertConfig, *, params_dtype=None, prefix: str = f"{EXPERT}.model") -> None:
+    """The action expert. ``axis``: mesh axis its projections are sharded over; ``None`` keeps the whole expert
+    (0.6 GB in bf16) on every rank, so that a tensor-parallel group runs the Euler loop without communication."""
+
+    def __init__(self, cfg: GemmaExpertConfig, *, params_dtype=None, prefix: str = f"{EXPERT}.model", axis: str | None = "tp") -> None:
         super().__init__()
         dtype, _, _ = resolve_engine_defaults(params_dtype, None, None)
-        self.config = cfg
-        self.layers = nn.ModuleList([PI05ExpertLayer(cfg, dtype, f"{prefix}.layers.{i}")
+        self.config, self.axis = cfg, axis
+        self.layers = nn.ModuleList([PI05ExpertLayer(cfg, dtype, f"{prefix}.layers.{i}", axis)
                                      for i in range(cfg.num_hidden_layers)])
         self.norm = AdaRMSNorm(cfg.hidden_size, cfg.adarms_cond_dim, cfg.rms_norm_eps, dtype=dtype, prefix=f"{prefix}.norm")
 
@@ -254,13 +257,14 @@ class ActionTimeHeads(nn.Module):
 
 class PI05Model(nn.Module):
     def __init__(self, config: PI05Config, *, vision_params_dtype: torch.dtype | None = None,
-                 device: str | None = None, params_dtype: torch.dtype | None = None, vision_axis: str | None = "tp") -> None:
+                 device: str | None = None, params_dtype: torch.dtype | None = None, vision_axis: str | None = "tp",
+                 expert_axis: str | None = "tp") -> None:
         super().__init__()
         dtype, _, _ = resolve_engine_defaults(params_dtype, None, None)
         self.config, self.params_dtype = config, dtype
         self.vision = PI05VisionTower(config.vision, params_dtype=vision_params_dtype or dtype, axis=vision_axis)
         self.paligemma_lm = PaliGemmaLanguageModel(config.text, params_dtype=dtype)
-        self.expert_stack = PI05ExpertStack(config.expert, params_dtype=dtype)
+        self.expert_stack = PI05ExpertStack(config.expert, params_dtype=dtype, axis=expert_axis)
         self.heads = ActionTimeHeads(config, params_dtype=dtype)
         self.rope = RotaryEmbedding(config.text.head_dim, config.text.max_position_embeddings, config.text.rope_theta,
                                     device=get_engine_config().device.target)

@@ -91,6 +91,11 @@ class PI05Plan:
         self.tp = int(lm0.attn.o.tp_size)
         self.Hq, self.Hkv = lm0.attn.qkv.q_size // t.head_dim, lm0.attn.qkv.kv_size // t.head_dim
         self.I_p, self.I_e = lm0.mlp.down.input_size_per_partition, ex0.mlp.down.input_size_per_partition
+        # the expert may be whole on every rank while the prefix decoder is sharded (its K/V head is replicated either way)
+        self.tp_e = int(ex0.attn.o.tp_size)
+        self.Hq_e = ex0.attn.qkv.q_size // t.head_dim
+        if ex0.attn.qkv.kv_size // t.head_dim != self.Hkv:
+            raise ValueError("prefix decoder and action expert must hold the same K/V heads per rank (they share the pool)")
         if self.tp > 1 and not self.tensor_parallel:
             raise ValueError("the model is sharded over a tensor-parallel axis: build PI05TPPlan for it")
         self.img_tokens = v.num_patches * num_images
@@ -155,9 +160,9 @@ class PI05Plan:
         self.noise = buf(B, self.C, cfg.max_action_dim)
         self.e_h = buf(Me, He)
         self.e_x = buf(Me, He)
-        self.e_qkv = buf(Me, qkv_w)
-        self.e_q = buf(Me, self.Hq * t.head_dim)
-        self.e_attn = buf(Me, self.Hq * t.head_dim)
+        self.e_qkv = buf(Me, (self.Hq_e + 2 * self.Hkv) * t.head_dim)
+        self.e_q = buf(Me, self.Hq_e * t.head_dim)
+        self.e_attn = buf(Me, self.Hq_e * t.head_dim)
         self.e_act = buf(Me, self.I_e)
         self.e_v = buf(Me, cfg.max_action_dim)
         self.e_pos = torch.zeros(Me, dtype=torch.int32, device=dev)
@@ -174,7 +179,7 @@ class PI05Plan:
                     raise ValueError(f"block-scaled fp8 needs widths that are multiples of 128, got {width}")
                 setattr(self, f"p8_{name}", torch.zeros(Mp, width, dtype=f8, device=dev))
                 setattr(self, f"p8s_{name}", torch.zeros(Mp, width // 128, dtype=torch.float32, device=dev))
-            for name, width in (("H", He), ("Q", self.Hq * t.head_dim), ("I", self.I_e)):
+            for name, width in (("H", He), ("Q", self.Hq_e * t.head_dim), ("I", self.I_e)):
                 if width % 128:
                     raise ValueError(f"block-scaled fp8 needs widths that are multiples of 128, got {width}")
                 setattr(self, f"e8_{name}", torch.zeros(Me, width, dtype=f8, device=dev))
@@ -224,7 +229,7 @@ class PI05Plan:
 
     def _expert_geometry(self) -> ExpertGeometry:
         cfg, e, t = self.cfg, self.cfg.expert, self.cfg.text
-        return ExpertGeometry(rows=self.Me, hidden=e.hidden_size, inter=e.intermediate_size, q_heads=self.Hq,
+        return ExpertGeometry(rows=self.Me, hidden=e.hidden_size, inter=e.intermediate_size, q_heads=self.Hq_e,
                               head_dim=t.head_dim, action_dim=cfg.max_action_dim, layers=cfg.num_layers,
                               steps=cfg.num_inference_steps)
 
@@ -233,7 +238,7 @@ class PI05Plan:
         column factors, branch gates and ``shift @ W^T`` biases; the weights stay as loaded (one copy)."""
         self.stack = None
         t = self.cfg.text
-        if not (self.use_expert_kernel and self.device.type == "cuda" and self.B == 1 and t.num_key_value_heads == 1 and self.tp == 1
+        if not (self.use_expert_kernel and self.device.type == "cuda" and self.B == 1 and t.num_key_value_heads == 1 and self.tp_e == 1
                 and self.suffix_extra == 0):
             return
         geo = self._expert_geometry()
@@ -300,7 +305,7 @@ class PI05Plan:
             return folded, b.to(dt).contiguous()
 
         t = self.cfg.text
-        Hq, Hkv, D = self.Hq, self.Hkv, t.head_dim
+        Hq, Hkv, D = self.Hq_e, self.Hkv, t.head_dim
         # with the persistent kernel serving the loop, only the first step (the one that may run on the
         # second stream under the prefix decoder) still goes launch by launch: one folded copy, not one per step
         keep = 1 if self.stack is not None else self.cfg.num_inference_steps
@@ -312,15 +317,16 @@ class PI05Plan:
             wq = ops.permute_rope_rows(layer.attn.qkv.weight, Hq, Hkv, D)
             self.fold_qkv.append(fold(wq, self.mod_in[li][:keep]) if li > 0 else (wq, None))
             self.fold_gate_up.append(fold(layer.mlp.gate_up.weight, self.mod_post[li][:keep]))
-        self.rope_desc = self._rope_descs(self.e_q, self.e_pos, self.e_slots)
+        self.rope_desc = self._rope_descs(self.e_q, self.e_pos, self.e_slots, self.Hq_e)
         heads = self.model.heads
         self.fold_out = fold(heads.action_out_proj.weight, self.mod_final[:keep], heads.action_out_proj.bias)
         self.e_ss = torch.zeros(2, self.Me, dtype=torch.float32, device=self.device)
 
-    def _rope_descs(self, q_out: torch.Tensor, pos: torch.Tensor, slots: torch.Tensor) -> list[torch.Tensor]:
+    def _rope_descs(self, q_out: torch.Tensor, pos: torch.Tensor, slots: torch.Tensor, q_heads: int | None = None) -> list[torch.Tensor]:
         """One rotate-and-scatter destination per layer (its K/V pool) for the QKV GEMM epilogue."""
         t = self.cfg.text
-        return [ops.rope_epilogue_desc(q_out, *self.pool.layer(li), self.cos_sin, pos, slots, self.Hq, self.Hkv, t.head_dim) for li in range(self.cfg.num_layers)]
+        Hq = self.Hq if q_heads is None else q_heads
+        return [ops.rope_epilogue_desc(q_out, *self.pool.layer(li), self.cos_sin, pos, slots, Hq, self.Hkv, t.head_dim) for li in range(self.cfg.num_layers)]
 
     def set_layout(self, layout: PI05Layout) -> bool:
         """Write the metadata of a request shape into the static buffers. Returns True if it changed."""
@@ -467,7 +473,7 @@ class PI05Plan:
     def expert(self) -> None:
         cfg, e, t = self.cfg, self.cfg.expert, self.cfg.text
         heads, stack = self.model.heads, self.model.expert_stack
-        Hq, Hkv, D, He, Me = self.Hq, self.Hkv, t.head_dim, e.hidden_size, self.Me
+        Hq, Hkv, D, He, Me = self.Hq_e, self.Hkv, t.head_dim, e.hidden_size, self.Me
         h, x = self.e_h, self.e_x
         q3, a3 = self.e_q.unflatten(1, (Hq, D)), self.e_attn.unflatten(1, (Hq, D))
         self.x_t.copy_(self.noise.view(Me, -1))
@@ -503,7 +509,7 @@ class PI05Plan:
 
         cfg, e, t = self.cfg, self.cfg.expert, self.cfg.text
         heads, stack = self.model.heads, self.model.expert_stack
-        Hq, Hkv, D, He, Me = self.Hq, self.Hkv, t.head_dim, e.hidden_size, self.Me
+        Hq, Hkv, D, He, Me = self.Hq_e, self.Hkv, t.head_dim, e.hidden_size, self.Me
         h, x, W = self.e_h, self.e_x, self.w8
         q3, a3 = self.e_q.unflatten(1, (Hq, D)), self.e_attn.unflatten(1, (Hq, D))
         x8, xs, a8, as_, m8, ms = self.e8_H, self.e8s_H, self.e8_Q, self.e8s_Q, self.e8_I, self.e8s_I
@@ -538,7 +544,7 @@ class PI05Plan:
         the result out."""
         cfg, e, t = self.cfg, self.cfg.expert, self.cfg.text
         heads, stack = self.model.heads, self.model.expert_stack
-        Hq, Hkv, D, He, Me = self.Hq, self.Hkv, t.head_dim, e.hidden_size, self.Me
+        Hq, Hkv, D, He, Me = self.Hq_e, self.Hkv, t.head_dim, e.hidden_size, self.Me
         h, x = self.e_h, self.e_x
         q3, a3 = self.e_q.unflatten(1, (Hq, D)), self.e_attn.unflatten(1, (Hq, D))
         ss_in, ss_post = self.e_ss[0], self.e_ss[1]
@@ -583,12 +589,20 @@ class PI05Plan:
 
     def run(self, lang_bucket: int) -> torch.Tensor:
         """The whole request; inputs are ``pixels``, ``input_ids``, ``noise``; result in ``out``."""
-        if self.overlap_first_step and self.fold_norms and type(self).expert is PI05Plan.expert and self.device.type == "cuda":
+        if self.overlap_first_step and self.fold_norms and self._first_step_overlappable() and self.device.type == "cuda":
             return self._run_overlapped(lang_bucket)
-        self.vision()
+        self.encode_images()
         self.prefix(lang_bucket)
         self.expert()
         return self.out
+
+    def encode_images(self) -> None:
+        """Everything in front of the prefix decoder (a tensor-parallel plan splits the cameras over its ranks here)."""
+        self.vision()
+
+    def _first_step_overlappable(self) -> bool:
+        """Whether ``_expert_folded(steps=[0])`` is this plan's first Euler step (subclasses with their own expert say no)."""
+        return type(self).expert is PI05Plan.expert
 
     def _run_overlapped(self, lang_bucket: int) -> torch.Tensor:
         """Same request with the first Euler step on a second stream. Block ``li`` of the expert only needs
@@ -604,7 +618,7 @@ class PI05Plan:
         fork, join = torch.cuda.Event(), torch.cuda.Event()
         kv_ready = [torch.cuda.Event() for _ in range(n_layers)]
         fork.record(main)
-        self.vision()
+        self.encode_images()
         self.prefix(lang_bucket, kv_events=kv_ready)
         with torch.cuda.stream(side):
             side.wait_event(fork)

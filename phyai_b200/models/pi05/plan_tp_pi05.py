@@ -16,6 +16,12 @@ The vision tower is not sharded: 72-wide heads and a 4304-wide MLP split badly, 
 independent, so each rank encodes ``ceil(cameras / tp)`` of them with whole weights and the projected
 rows are exchanged once (a peer-memory all-gather of 256 x 2048 rows per camera).
 
+The action expert (0.6 GB) is normally kept whole on every rank (``expert_axis=None`` on the model): each rank then runs
+the ten Euler steps of the single-GPU plan on its own copy of the K/V pool with no communication at all, first step
+under the prefix decoder on a second stream, and tensor parallelism shortens what is big (the 2 B-parameter prefix
+decoder, the cameras) without taxing what is latency-bound. A sharded expert is served too (two fused reductions per
+block, AdaRMS applied by the reducing kernel).
+
 Every rank must be given the same request; all ranks finish with bit-identical action chunks (each sums
 the partials in rank order). The request is captured as one CUDA graph per prompt bucket like the
 single-GPU plan; waits on peers are bounded, so ranks have to enter a replay within a second of each other.
@@ -34,10 +40,6 @@ from .plan_pi05 import PI05Plan
 
 class PI05TPPlan(PI05Plan):
     tensor_parallel = True
-    # the fused reduce kernel already writes the next norm; the folded-weight epilogues, the second stream
-    # (both stages would share one signal channel) and the one-GPU expert kernel do not apply
-    fold_norms = False
-    overlap_first_step = False
     use_expert_kernel = False
     #: prefix reductions switch from "push the whole partial" to scatter / gather at this many rows (groups of 4+)
     scatter_min_rows = int(envs.PHYAI_PI05_TP_SCATTER_ROWS.get())
@@ -49,6 +51,11 @@ class PI05TPPlan(PI05Plan):
         super().__init__(model, max_batch_size=max_batch_size, num_images=num_images, device=device, quantization="bf16")
         self.axis = axis
         self.mesh = mesh if mesh is not None else P.default_mesh()
+        # a whole expert on every rank runs the single-GPU Euler loop (folded norms, first step on the second stream);
+        # a sharded one reduces over the same signal channel as the prefix decoder, so it cannot run beside it
+        self.expert_replicated = self.tp_e == 1
+        self.fold_norms = self.expert_replicated
+        self.overlap_first_step = self.expert_replicated and type(self).overlap_first_step
         self.rank = int(model.paligemma_lm.layers[0].attn.o.tp_rank)
         cfg, v, t = self.cfg, self.cfg.vision, self.cfg.text
         n_all = self.B * self.n_img
@@ -88,12 +95,22 @@ class PI05TPPlan(PI05Plan):
         Hq, Hkv, D = self.Hq, self.Hkv, t.head_dim
         # q / k rows of this rank's QKV slice reordered for the rotating epilogue
         self.tp_pqkv = [ops.permute_rope_rows(l.attn.qkv.weight, Hq, Hkv, D) for l in self.model.paligemma_lm.layers]
-        self.tp_eqkv = [ops.permute_rope_rows(l.attn.qkv.weight, Hq, Hkv, D) for l in self.model.expert_stack.layers]
         self.p_rope = self._rope_descs(self.p_q, self.p_pos, self.p_slots)
-        self.rope_desc = self._rope_descs(self.e_q, self.e_pos, self.e_slots)
+        if not self.expert_replicated:
+            self.tp_eqkv = [ops.permute_rope_rows(l.attn.qkv.weight, self.Hq_e, Hkv, D) for l in self.model.expert_stack.layers]
+            self.rope_desc = self._rope_descs(self.e_q, self.e_pos, self.e_slots, self.Hq_e)
         for m in (*self.mod_in, *self.mod_post, self.mod_final):
             if m.dtype != torch.bfloat16 or not m.is_contiguous():
                 raise ValueError("modulation rows must be contiguous bf16 for the reduce kernel")
+
+    def _fold_prefix(self) -> None:
+        """Nothing to fold: the reducing kernel of the previous product applies each prefix norm."""
+
+    def _first_step_overlappable(self) -> bool:
+        return self.expert_replicated
+
+    def encode_images(self) -> None:
+        self.images()
 
     # ----------------------------------------------------------------- stages
     def _reduce(self, x_part: torch.Tensor, w: torch.Tensor, h: torch.Tensor, y: torch.Tensor, **norm) -> None:
@@ -126,10 +143,12 @@ class PI05TPPlan(PI05Plan):
         eps = t.rms_norm_eps
         ops.norm(h, "gemma_rms", weight=lm.layers[0].input_layernorm.weight, eps=eps, out=x)
         if self.scatter:
-            return self._prefix_scatter(h, x, qkv, q3, attn, a3, act, n_per)
+            return self._prefix_scatter(h, x, qkv, q3, attn, a3, act, n_per, kv_events)
         for li, layer in enumerate(lm.layers):
             kpool, vpool = self.pool.layer(li)
             ops.gemm(x, self.tp_pqkv[li], qkv, rope=self.p_rope[li])
+            if kv_events is not None:
+                kv_events[li].record(torch.cuda.current_stream())     # this block's prefix K / V are in the pool
             if li == last:
                 break  # only this block's K/V are consumed downstream
             ops.attention(q3, kpool, vpool, a3, self.p_qstart, self.p_qlen, self.p_kvptr, self.p_kvlen,
@@ -138,7 +157,7 @@ class PI05TPPlan(PI05Plan):
             ops.gemm(x, layer.mlp.gate_up.weight, act, act="gelu_tanh", glu=True)
             self._reduce(act, layer.mlp.down.weight, h, x, norm="gemma_rms", weight=lm.layers[li + 1].input_layernorm.weight, eps=eps)
 
-    def _prefix_scatter(self, h, x, qkv, q3, attn, a3, act, n_per) -> None:
+    def _prefix_scatter(self, h, x, qkv, q3, attn, a3, act, n_per, kv_events=None) -> None:
         """Prefix blocks with a sequence-parallel residual: each product's tiles go to the rank that owns the rows,
         which sums them, adds its residual rows, applies the next norm and stores the normalised rows into every
         rank's gathered matrix; the next GEMM waits for those rows in its loader (all-gather fused into the GEMM)."""
@@ -149,6 +168,8 @@ class PI05TPPlan(PI05Plan):
         for li, layer in enumerate(lm.layers):
             kpool, vpool = self.pool.layer(li)
             ops.gemm(y, self.tp_pqkv[li], qkv, rope=self.p_rope[li], wait=wait)
+            if kv_events is not None:
+                kv_events[li].record(torch.cuda.current_stream())
             if li == last:
                 break
             ops.attention(q3, kpool, vpool, a3, self.p_qstart, self.p_qlen, self.p_kvptr, self.p_kvlen,
@@ -161,9 +182,11 @@ class PI05TPPlan(PI05Plan):
             y, wait = t2.y, t2.wait
 
     def expert(self) -> None:
+        if self.expert_replicated:
+            return PI05Plan.expert(self)
         cfg, e, t = self.cfg, self.cfg.expert, self.cfg.text
         heads, stack = self.model.heads, self.model.expert_stack
-        Hq, D, He, Me = self.Hq, t.head_dim, e.hidden_size, self.Me
+        Hq, D, He, Me = self.Hq_e, t.head_dim, e.hidden_size, self.Me
         h, x = self.e_h, self.e_x
         q3, a3 = self.e_q.unflatten(1, (Hq, D)), self.e_attn.unflatten(1, (Hq, D))
         n_layers, eps = len(stack.layers), e.rms_norm_eps
@@ -185,11 +208,6 @@ class PI05TPPlan(PI05Plan):
             ops.axpy(self.x_t, self.e_v, self.dt)
         self.out.view(Me, -1).copy_(self.x_t)
 
-    def run(self, lang_bucket: int) -> torch.Tensor:
-        self.images()
-        self.prefix(lang_bucket)
-        self.expert()
-        return self.out
 
 
 __all__ = ["PI05TPPlan"]

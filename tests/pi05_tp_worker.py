@@ -62,11 +62,13 @@ def main() -> int:
                 state[k] = (torch.randn(state[k].shape, generator=g0) * 0.2).to(state[k].dtype)
         write_checkpoint(ckpt, state)
     dist.barrier()
-    eng = Engine(EngineArgs("pi05_tp", PI05TPArgs(config=cfg, checkpoint_dir=str(ckpt), max_batch_size=2,
+    shard_expert = os.environ.get("PI05_TP_SHARD_EXPERT", "0") == "1"
+    eng = Engine(EngineArgs("pi05_tp", PI05TPArgs(config=cfg, checkpoint_dir=str(ckpt), max_batch_size=2, shard_expert=shard_expert,
                                                   inputs_image_shape=[[56, 56, 3]] * 2, weight_strict=False), ec))
     sch = eng.entry.scheduler
-    if not isinstance(sch.plan, PI05TPPlan) or sch.plan.tp != world:
-        fails.append(f"plan is {type(sch.plan).__name__}, tp={getattr(sch.plan, 'tp', None)}")
+    if not isinstance(sch.plan, PI05TPPlan) or sch.plan.tp != world or sch.plan.expert_replicated == shard_expert:
+        fails.append(f"plan is {type(sch.plan).__name__}, tp={getattr(sch.plan, 'tp', None)}, "
+                     f"expert whole={getattr(sch.plan, 'expert_replicated', None)}")
     P.register_mesh("single", Mesh((1,), ("tp",), rank=0, build_groups=False, device_type="cuda"))
     with P.use_mesh("single"):
         whole = PI05Model(cfg).eval()
