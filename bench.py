@@ -21,6 +21,9 @@ of the run as a CFG x TP mesh (1: cfg1 x tp1, 2: cfg1 x tp2, 4: cfg1 x tp4, 8: c
 strong scaling of a fixed request, timed on the device between consecutive sampler updates,
 max over ranks (``benchmarks/bench_cosmos3.py`` holds the measurement). ``--no-cosmos3`` skips it.
 
+For N > 1 a third block, ``pi05_tp``, serves the headline request (one robot) with all N GPUs as one tensor-parallel
+group (``Engine(plugin="pi05_tp")``): strong scaling of the batch-1 latency. The reference has no such scheduler.
+
 ``--impl reference`` runs the unmodified reference package installed under
 ``baseline/_ref`` through its own ``Engine`` / schedulers with the same requests.
 """
@@ -52,6 +55,7 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--dtype", choices=("bf16", "fp8_block"), default="bf16",
                     help="fp8_block: prefix decoder and action expert in block-scaled fp8 (ours arm; not the headline dtype)")
     ap.add_argument("--no-cosmos3", action="store_true", help="skip the Cosmos3 TP / CFG block")
+    ap.add_argument("--no-pi05-tp", action="store_true", help="skip the tensor-parallel Pi0.5 block (N > 1)")
     ap.add_argument("--cosmos3-model", default="super", help="geometry of the Cosmos3 block (super | nano | small)")
     ap.add_argument("--cosmos3-steps", type=int, default=6)
     ap.add_argument("--cosmos3-warmup", type=int, default=3)
@@ -75,6 +79,59 @@ def cosmos3_block(args: argparse.Namespace) -> dict:
                            impl=args.impl, policy=False, batch=1, layers=0)
         rec = run_block(ns, keep_process_group=True)
         rec["scaling"] = "strong"
+        return rec
+    except Exception as e:  # noqa: BLE001 - the headline line must still be printed
+        return {"error": f"{type(e).__name__}: {e}".replace("\n", " ")[:300]}
+
+
+def pi05_tp_block(args: argparse.Namespace, device: str) -> dict:
+    """The headline request (one robot, batch 1) served by ALL N GPUs as one tensor-parallel group: strong scaling of
+    the latency, through ``Engine(plugin="pi05_tp")``. Device time per step, L2 flushed, p50, max over ranks."""
+    import torch
+    import torch.distributed as dist
+
+    N = args.gpus
+    if N == 1:
+        return {"skipped": "one GPU: the headline value is this request"}
+    if args.impl == "reference":
+        return {"unavailable": "the reference ships no tensor-parallel Pi0.5 scheduler (single-GPU and data-parallel only)"}
+    if args.dtype != "bf16":
+        return {"skipped": "the tensor-parallel plan serves bf16"}
+    try:
+        from phyai_b200.engine import Engine, EngineArgs
+        from phyai_b200.engine_config import DeviceConfig, EngineConfig, ParallelConfig, RuntimeConfig
+        from phyai_b200.models.pi05.main_pi05_tp import PI05TPArgs
+        from phyai_b200.models.pi05.scheduler_ws1_pi05 import PI05Request
+
+        cfg = EngineConfig(device=DeviceConfig(target=device, params_dtype=torch.bfloat16),
+                           parallel=ParallelConfig(world_size=N, tp_size=N), runtime=RuntimeConfig(use_cuda_graph=not args.no_graph))
+        engine = Engine(EngineArgs("pi05_tp", PI05TPArgs(checkpoint_dir=None, max_batch_size=1, inputs_image_shape=[[224, 224, 3]] * 3), cfg))
+        host = make_request_tensors(torch, 1, args.lang_len)            # the same request on every rank
+        t = [x.to(device) for x in host]
+        req = PI05Request(pixel_values=t[0], input_ids=t[1], lang_lens=t[2], noise=t[3])
+        flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
+        for _ in range(max(args.warmup, 3)):
+            out = engine.step(req)
+        ms = []
+        for _ in range(args.steps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            dist.barrier()
+            e0.record()
+            out = engine.step(req)
+            e1.record()
+            e1.synchronize()
+            ms.append(e0.elapsed_time(e1))
+        st = torch.tensor([percentile(ms, 0.5), percentile(ms, 0.99)], device=device, dtype=torch.float64)
+        dist.all_reduce(st, op=dist.ReduceOp.MAX)
+        plan = engine.entry.scheduler.plan
+        rec = {"metric": "pi05_action_chunk_latency_p50_ms", "value": round(float(st[0]), 4), "p99_ms": round(float(st[1]), 4), "unit": "ms",
+               "parallelism": f"tp{N}", "scaling": "strong", "global_batch": 1, "steps": args.steps,
+               "plan": type(plan).__name__, "expert": "whole on every rank" if getattr(plan, "expert_replicated", True) else "sharded",
+               "finite": bool(torch.isfinite(out.float()).all().item()), "abs_mean": round(float(out.float().abs().mean().item()), 6)}
+        engine.close()
+        del engine, flush
+        torch.cuda.empty_cache()
         return rec
     except Exception as e:  # noqa: BLE001 - the headline line must still be printed
         return {"error": f"{type(e).__name__}: {e}".replace("\n", " ")[:300]}
@@ -302,6 +359,8 @@ def run(args: argparse.Namespace) -> dict:
     engine.close()
     del engine, req_dev, dev_in, flush
     torch.cuda.empty_cache()
+    if not args.no_pi05_tp:
+        result["pi05_tp"] = pi05_tp_block(args, device)
     if not args.no_cosmos3:
         result["cosmos3"] = cosmos3_block(args)
     if N > 1 and dist.is_initialized():

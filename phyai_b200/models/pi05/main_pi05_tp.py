@@ -69,6 +69,14 @@ class PI05TPScheduler(PI05WS1Scheduler):
         if self.tp_size > 1:
             self.plan.pg.sync()
 
+    def close(self) -> None:
+        """Drops the graphs, then (collectively) the peer mappings: a later engine of the same process gets a fresh group."""
+        pg = getattr(self.plan, "pg", None)
+        super().close()
+        if pg is not None:
+            torch.cuda.synchronize()
+            pg.close()
+
     @torch.no_grad()
     def step(self, request: PI05Request) -> torch.Tensor:
         if request.noise is None:

@@ -99,6 +99,16 @@ def init(layout: Sequence[int] = (1,), mesh_dim_names: Sequence[str] = ("tp",), 
 
 
 def shutdown(name: str = "model") -> None:
+    """Collective: closes the backends and the peer-memory groups of this process (their process groups belong to the
+    mesh that goes away here: a group left open would be asked to agree on the step status by the next engine), then
+    forgets the mesh."""
+    from .symm import PeerGroup
+
+    for g in PeerGroup.open_groups():
+        try:
+            g.close()
+        except Exception:  # noqa: BLE001 - a rank that lost its peers still has to get through shutdown
+            g._closed = True
     d = get_dispatcher()
     if d is not None:
         for n in d.registry.names():
