@@ -327,6 +327,28 @@ void cfg_combine(const Tensor& cond, const Tensor& uncond, double g, const OptT&
         "cfg_combine_launch");
 }
 
+Tensor linear_simt(const Tensor& x, const Tensor& w, const OptT& bias) {
+  auto code = [](const Tensor& t) {
+    switch (t.scalar_type()) {
+      case at::kFloat: return 0;
+      case at::kBFloat16: return 1;
+      case at::kHalf: return 2;
+      default: TORCH_CHECK(false, "linear_simt: fp32 / bf16 / fp16 only"); return -1;
+    }
+  };
+  TORCH_CHECK(x.is_cuda() && w.is_cuda() && x.dim() == 2 && w.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1 &&
+              x.size(1) == w.size(1), "linear_simt: x [M, K], w [N, K], unit inner strides");
+  const void* b = nullptr;
+  if (bias.has_value() && bias->defined()) {
+    TORCH_CHECK(bias->is_contiguous() && bias->numel() == w.size(0) && bias->scalar_type() == w.scalar_type(), "linear_simt: bias [N] of the weight's dtype");
+    b = bias->data_ptr();
+  }
+  Tensor y = at::empty({x.size(0), w.size(0)}, x.options());
+  check(pb::linear_simt_launch(x.data_ptr(), code(x), w.data_ptr(), code(w), b, y.data_ptr(), int(x.size(0)), int(w.size(0)),
+                               int(x.size(1)), int(x.stride(0)), int(w.stride(0)), int(y.stride(0)), cur_stream()), "linear_simt_launch");
+  return y;
+}
+
 void unipc_step(const Tensor& v, const OptT& v_uncond, double g, Tensor& x, Tensor& x_last, Tensor& m1, Tensor& m2,
                 double sigma, bool has_corr, std::vector<double> corr, std::vector<double> pred, const OptT& keep,
                 const OptT& cond, int64_t C, int64_t T, int64_t inner, int64_t live_inner) {
@@ -510,6 +532,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("quant_fp8", &quant_fp8);
   m.def("snake", &snake);
   m.def("unipc_step", &unipc_step);
+  m.def("linear_simt", &linear_simt);
   m.def("gdn_decode", &gdn_decode, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("g"), py::arg("beta"),
         py::arg("state_pool"), py::arg("state_indices"), py::arg("scale"), py::arg("l2norm") = true);
   m.def("kernel_status", [] { return pb::read_and_clear_kernel_status(); });

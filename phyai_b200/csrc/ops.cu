@@ -769,6 +769,79 @@ cudaError_t cfg_combine_launch(const __nv_bfloat16* cond, const __nv_bfloat16* u
   return cudaGetLastError();
 }
 
+// ------------------------------------------------------------ small / odd linears
+// y = x @ w^T + bias for the shapes the tensor-core GEMM does not take (fp32 or fp16 operands, K or N not a
+// multiple of 8): one warp per output column and group of four rows, fp32 accumulation, lanes stride K.
+// These are the tiny projections around a model (timestep embedders, action heads), not its hot path.
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return bf2f(v); }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16(v); }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half(v); }
+
+template <typename TX, typename TW>
+__global__ void linear_simt_kernel(const TX* x, const TW* w, const TW* bias, TX* y, int M, int N, int K, int ldx, int ldw, int ldy) {
+  constexpr int R = 4;
+  const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * warps + (threadIdx.x >> 5);
+  const int m0 = blockIdx.y * R;
+  pdl_launch_dependents();
+  pdl_wait();
+  if (n >= N) return;
+  float acc[R] = {0.f, 0.f, 0.f, 0.f};
+  const TW* wr = w + size_t(n) * ldw;
+  for (int k = lane; k < K; k += 32) {
+    const float wv = to_f32<TW>(wr[k]);
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+      if (m0 + r < M) acc[r] += wv * to_f32<TX>(x[size_t(m0 + r) * ldx + k]);
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], o);
+  }
+  if (lane == 0) {
+    const float b = bias ? to_f32<TW>(bias[n]) : 0.f;
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+      if (m0 + r < M) y[size_t(m0 + r) * ldy + n] = from_f32<TX>(acc[r] + b);
+  }
+}
+
+template <typename TX, typename TW>
+static cudaError_t linear_simt_typed(const void* x, const void* w, const void* bias, void* y, int M, int N, int K, int ldx,
+                                     int ldw, int ldy, cudaStream_t s) {
+  const int warps = 8;
+  dim3 grid((N + warps - 1) / warps, (M + 3) / 4);
+  PB_LAUNCH((linear_simt_kernel<TX, TW>), grid, warps * 32, s, reinterpret_cast<const TX*>(x), reinterpret_cast<const TW*>(w),
+            reinterpret_cast<const TW*>(bias), reinterpret_cast<TX*>(y), M, N, K, ldx, ldw, ldy);
+  return cudaGetLastError();
+}
+
+// dtype codes: 0 = fp32, 1 = bf16, 2 = fp16 (bias has the weight's type, y has x's type)
+cudaError_t linear_simt_launch(const void* x, int x_type, const void* w, int w_type, const void* bias, void* y, int M, int N,
+                               int K, int ldx, int ldw, int ldy, cudaStream_t s) {
+  if (M <= 0 || N <= 0 || K <= 0) return cudaSuccess;
+#define PB_LS(TX, TW) return linear_simt_typed<TX, TW>(x, w, bias, y, M, N, K, ldx, ldw, ldy, s)
+  switch (x_type * 3 + w_type) {
+    case 0: PB_LS(float, float);
+    case 1: PB_LS(float, __nv_bfloat16);
+    case 2: PB_LS(float, __half);
+    case 3: PB_LS(__nv_bfloat16, float);
+    case 4: PB_LS(__nv_bfloat16, __nv_bfloat16);
+    case 5: PB_LS(__nv_bfloat16, __half);
+    case 6: PB_LS(__half, float);
+    case 7: PB_LS(__half, __nv_bfloat16);
+    case 8: PB_LS(__half, __half);
+  }
+#undef PB_LS
+  return cudaErrorInvalidValue;
+}
+
 // ------------------------------------------------------------ UniPC sampler step
 // One multistep update of a flow-matching latent, element by element, with everything the host loop used to
 // issue as separate tensor ops: guidance combine, x0 prediction, corrector, predictor, history rotation and the

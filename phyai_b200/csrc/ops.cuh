@@ -82,6 +82,10 @@ cudaError_t cfg_combine_launch(const __nv_bfloat16* cond, const __nv_bfloat16* u
                                __nv_bfloat16* out, float* x_fp32, float dt, long long n,
                                cudaStream_t s);
 
+// y = x @ w^T + bias on CUDA cores for operands the tensor-core GEMM does not take (dtype codes 0 fp32, 1 bf16, 2 fp16).
+cudaError_t linear_simt_launch(const void* x, int x_type, const void* w, int w_type, const void* bias, void* y, int M, int N,
+                               int K, int ldx, int ldw, int ldy, cudaStream_t s);
+
 // One UniPC (order <= 2, flow prediction) update of a latent viewed as [B][C][T][inner]:
 //   v = v_uncond + g (v - v_uncond)        when v_uncond is given
 //   m_t = x - sigma v;  x_s = c_x x_last + c_0 m1 + c_1 m2 + c_t m_t (has_corr) else x

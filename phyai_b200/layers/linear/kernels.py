@@ -87,9 +87,13 @@ class B200Kernel:
             x2 = x2.contiguous()
         spec = layer.spec
         if spec.spec_id == "bf16":
-            if x2.dtype != torch.bfloat16 or x2.shape[1] % 8 or layer.weight.shape[0] % 8:
-                return F.linear(x, layer.weight, bias)
-            y = ops.gemm(x2, layer.weight, bias=bias)
+            w = layer.weight
+            if x2.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x2.shape[1] % 8 or w.shape[0] % 8:
+                # fp32 / fp16 operands or odd widths (timestep embedders, action heads): the CUDA-core kernel
+                b = bias if bias is None or bias.dtype == w.dtype else bias.to(w.dtype)
+                y = ops.linear_simt(x2, w, b)
+            else:
+                y = ops.gemm(x2, w, bias=bias)
         elif spec.granularity is Granularity.BLOCK:
             from ...ops import fp8_block
 

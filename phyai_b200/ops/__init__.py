@@ -267,6 +267,12 @@ def cfg_combine(cond: torch.Tensor, uncond: torch.Tensor, g: float, *,
     return out
 
 
+def linear_simt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ w.T + bias`` on CUDA cores with fp32 accumulation, for what :func:`gemm` does not take: fp32 / fp16
+    operands, mixed operand types, K or N that is not a multiple of 8. ``x`` (M, K), ``w`` (N, K)."""
+    return ext().linear_simt(x, w, bias)
+
+
 def unipc_step(v: torch.Tensor, x: torch.Tensor, x_last: torch.Tensor, m1: torch.Tensor, m2: torch.Tensor, *, sigma: float,
                corr: Optional[tuple], pred: tuple, v_uncond: Optional[torch.Tensor] = None, g: float = 1.0,
                keep: Optional[torch.Tensor] = None, cond: Optional[torch.Tensor] = None, view: tuple[int, int, int] | None = None,

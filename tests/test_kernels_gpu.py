@@ -567,3 +567,42 @@ def test_unipc_step_kernel_zero_tail_columns():
         st.step(torch.randn(2, 8, 32, generator=g).bfloat16().cuda())
     _status_ok()
     assert float(xs[:, :, 7:].abs().max()) == 0.0 and float(xs[:, :, :7].abs().max()) > 0.0
+
+
+@pytest.mark.parametrize("xdt,wdt,M,K,N", [(torch.float32, torch.float32, 1, 256, 5120), (torch.bfloat16, torch.bfloat16, 50, 7, 33),
+                                           (torch.float16, torch.float16, 5, 100, 12), (torch.float32, torch.bfloat16, 9, 31, 64)])
+def test_linear_simt_matches_fp32(xdt, wdt, M, K, N):
+    """The CUDA-core linear that takes what the tensor-core GEMM refuses (fp32 / fp16 operands, odd K or N)."""
+    from phyai_b200 import ops
+
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(M, K, generator=g).to(xdt).cuda()
+    w = (torch.randn(N, K, generator=g) * 0.2).to(wdt).cuda()
+    b = torch.randn(N, generator=g).to(wdt).cuda()
+    y = ops.linear_simt(x, w, b)
+    _status_ok()
+    want = x.float() @ w.float().t() + b.float()
+    assert y.dtype == xdt and y.shape == (M, N)
+    tol = 1e-4 if xdt == torch.float32 else 2e-2
+    assert torch.allclose(y.float(), want, atol=tol * float(want.abs().max()), rtol=tol)
+
+
+def test_odd_linear_layer_runs_own_kernel():
+    """A ReplicatedLinear with fp32 weights on the b200 kernel path: served by linear_simt, not by a library GEMM."""
+    from phyai_b200 import ops
+    from phyai_b200.engine_config import DeviceConfig, EngineConfig, init_engine_config
+    from phyai_b200.layers import linear as L
+    from phyai_b200.layers.linear import ReplicatedLinear
+
+    init_engine_config(EngineConfig(device=DeviceConfig("cuda", torch.bfloat16)))
+    L.init()
+    lin = ReplicatedLinear(256, 40, bias=True, params_dtype=torch.float32)
+    with torch.no_grad():
+        lin.weight.normal_(0, 0.1)
+        lin.bias.normal_(0, 0.1)
+    x = torch.randn(3, 256, device="cuda")
+    c0 = ops.launch_counter()
+    y, _ = lin(x)
+    assert ops.launch_counter() == c0 + 1
+    want = x @ lin.weight.t() + lin.bias
+    assert torch.allclose(y, want, atol=1e-4, rtol=1e-4)
