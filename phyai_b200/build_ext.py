@@ -154,11 +154,63 @@ def build_radix(verbose: bool = False, sanitize: str | None = None) -> Path | No
     return out
 
 
+def cutlass_include_dirs() -> list[Path]:
+    """CUTLASS / CuTe header trees vendored by Python packages of this environment (none: empty list)."""
+    import site
+
+    found: list[Path] = []
+    for sp in site.getsitepackages():
+        for rel in ("flashinfer/data/cutlass", "tilelang/3rdparty/cutlass"):
+            inc = Path(sp) / rel / "include"
+            if (inc / "cutlass" / "detail" / "sm100_blockscaled_layout.hpp").is_file():
+                found = [inc] + ([inc.parent / "tools" / "util" / "include"] if (inc.parent / "tools" / "util" / "include").is_dir() else [])
+                return found
+    return found
+
+
+def build_nvfp4(verbose: bool = False) -> Path | None:
+    """Build ``phyai_b200/_nvfp4`` (block-scaled NVFP4 GEMM: CUTLASS sm100 collective inside ``csrc/cutlass/gemm_nvfp4.cu``
+    plus this repository's quantisation kernels). Skipped, with a note, where no CUTLASS header tree is found."""
+    src = CSRC / "cutlass" / "gemm_nvfp4.cu"
+    if not src.is_file():
+        return None
+    cut = cutlass_include_dirs()
+    if not cut:
+        sys.stderr.write("build_ext: no CUTLASS headers found, phyai_b200/_nvfp4 not built (NVFP4 layers use the dequantising path)\n")
+        return None
+    BUILD.mkdir(exist_ok=True)
+    inc, libdirs = _torch_paths()
+    pyinc = sysconfig.get_paths()["include"]
+    import pybind11
+
+    flags = ARCH_FLAGS + ["-O3", "-std=c++17", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "--expt-extended-lambda",
+                          "-diag-suppress", "20012", "-DTORCH_EXTENSION_NAME=_nvfp4", "-DTORCH_API_INCLUDE_EXTENSION_H",
+                          "-D_GLIBCXX_USE_CXX11_ABI=1", f"-I{pyinc}", f"-I{pybind11.get_include()}"] + [f"-I{p}" for p in cut] + [
+                              f"-I{p}" for p in inc]
+    if verbose:
+        flags += ["-Xptxas", "-v"]
+    tag = _hash([src], flags)
+    obj = BUILD / f"gemm_nvfp4.{tag}.o"
+    if not obj.exists():
+        _run([NVCC, *flags, "-c", str(src), "-o", str(obj)])
+    out = ROOT / f"_nvfp4{ext_suffix()}"
+    stamp = BUILD / f"_nvfp4.{tag}.stamp"
+    if not out.exists() or not stamp.exists():
+        libs = ["-lc10", "-ltorch", "-ltorch_cpu", "-ltorch_python", "-lc10_cuda", "-ltorch_cuda"]
+        _run([NVCC, "-shared", *ARCH_FLAGS, "-o", str(out), str(obj), *[f"-L{p}" for p in libdirs], *libs,
+              *[f"-Xlinker=-rpath={p}" for p in libdirs]])
+        stamp.write_text("ok")
+    return out
+
+
 def build_all(verbose: bool = False, debug: bool = False, sanitize: str | None = None) -> list[Path]:
     outs = [build_core(verbose, debug)]
     r = build_radix(verbose, sanitize)
     if r is not None:
         outs.append(r)
+    n = build_nvfp4(verbose)
+    if n is not None:
+        outs.append(n)
     return outs
 
 
