@@ -189,15 +189,22 @@ def build_nvfp4(verbose: bool = False) -> Path | None:
                               f"-I{p}" for p in inc]
     if verbose:
         flags += ["-Xptxas", "-v"]
-    tag = _hash([src], flags)
-    obj = BUILD / f"gemm_nvfp4.{tag}.o"
-    if not obj.exists():
-        _run([NVCC, *flags, "-c", str(src), "-o", str(obj)])
+    flags += [f"-I{src.parent}"]
+    hdrs = sorted(src.parent.glob("*.cuh"))
+    objs, jobs = [], []
+    for cu in sorted(src.parent.glob("*.cu")):          # one tile shape per translation unit: they compile side by side
+        tag = _hash([cu] + hdrs, flags)
+        obj = BUILD / f"{cu.stem}.{tag}.o"
+        objs.append(obj)
+        if not obj.exists():
+            jobs.append([NVCC, *flags, "-c", str(cu), "-o", str(obj)])
+    with ThreadPoolExecutor(max_workers=max(1, len(jobs))) as ex:
+        list(ex.map(_run, jobs))
     out = ROOT / f"_nvfp4{ext_suffix()}"
-    stamp = BUILD / f"_nvfp4.{tag}.stamp"
+    stamp = BUILD / f"_nvfp4.{_hash(objs, ['link-nvfp4'])}.stamp"
     if not out.exists() or not stamp.exists():
         libs = ["-lc10", "-ltorch", "-ltorch_cpu", "-ltorch_python", "-lc10_cuda", "-ltorch_cuda"]
-        _run([NVCC, "-shared", *ARCH_FLAGS, "-o", str(out), str(obj), *[f"-L{p}" for p in libdirs], *libs,
+        _run([NVCC, "-shared", *ARCH_FLAGS, "-o", str(out), *map(str, objs), *[f"-L{p}" for p in libdirs], *libs,
               *[f"-Xlinker=-rpath={p}" for p in libdirs]])
         stamp.write_text("ok")
     return out
