@@ -1,6 +1,6 @@
 """Micro-benchmarks of this repository's kernels against library baselines, with roofline fractions.
 
-    python benchmarks/bench_kernels.py [--set gemm|attention|norm|all] [--peaks MEASURED_PEAKS.json]
+    python benchmarks/bench_kernels.py [--set gemm|attention|norm|fp8|nvfp4|all] [--peaks MEASURED_PEAKS.json]
 
 GEMMs are compared with ``torch.matmul`` (cuBLAS), attention with ``scaled_dot_product_attention``
 and, when importable, FlashInfer / flash-attn; norms with an eager PyTorch expression. Each timing is
@@ -38,7 +38,7 @@ def bench(fn, n=10, warm=3):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--set", default="all", choices=("gemm", "attention", "norm", "fp8", "all"))
+    ap.add_argument("--set", default="all", choices=("gemm", "attention", "norm", "fp8", "nvfp4", "all"))
     ap.add_argument("--only", default=None, help="run a single named shape (for profiler captures)")
     ap.add_argument("--no-baselines", action="store_true", help="skip the library kernels (keeps a profiler capture small)")
     ap.add_argument("--gemm-2cta", action="store_true", help="also time the CTA-pair (cta_group::2) GEMM kernel")
@@ -104,6 +104,45 @@ def main() -> None:
                 except Exception as e:  # noqa: BLE001 - a missing or unsupported library path is a result, not a failure
                     note = f"{type(e).__name__}: {str(e)[:120]}"
                 print(json.dumps(dict(kernel="flashinfer.gemm_fp8_nt_groupwise", shape=name, flashinfer_ms=round(t_f, 4), note=note)), flush=True)
+    if a.set in ("nvfp4", "all"):
+        # NVFP4 (e2m1 operands, ue4m3 scale per 16, fp32 global scales) against FlashInfer's mm_fp4, the call the reference
+        # serves NVFP4 checkpoints with (layers/linear/backends/flashinfer.py:163-200); both include nothing but the GEMM,
+        # the activation quantiser is timed on its own
+        from phyai_b200.layers.quant.specs import Nvfp4Spec
+        from phyai_b200.ops import nvfp4
+
+        if not nvfp4.available():
+            print(json.dumps(dict(kernel="gemm_nvfp4", skipped="phyai_b200/_nvfp4 is not built")), flush=True)
+        else:
+            for name, (M, K, N) in {"nvfp4.pi05.prefix.gate_up": (968, 2048, 32768), "nvfp4.pi05.expert.gate_up": (52, 1024, 8192),
+                                    "nvfp4.cosmos3.qkv": (7040, 5120, 7168), "nvfp4.cosmos3.gate_up": (7040, 5120, 27648)}.items():
+                if a.only and name != a.only:
+                    continue
+                x = (torch.randn(M, K, device=dev) * 0.5).to(bf)
+                w = torch.randn(N, K, device=dev) * 0.05
+                w4, wsf, wg = Nvfp4Spec.quantize(w)
+                sfw = nvfp4.swizzle_scales(wsf, K)
+                t_q = bench(lambda: nvfp4.quantize_activation(x, 1.0))
+                x4, sfx = nvfp4.quantize_activation(x, 1.0)
+                out = torch.empty(M, N, device=dev, dtype=bf)
+                alpha = float(wg)
+                t_o = bench(lambda: nvfp4.gemm_nvfp4(x4, sfx, w4, sfw, alpha, out=out))
+                row = dict(kernel="gemm_nvfp4", shape=name, ours_ms=round(t_o, 4), tflops=round(2 * M * N * K / t_o / 1e9, 1),
+                           quantize_act_ms=round(t_q, 4))
+                print(json.dumps(row), flush=True)
+                if not a.no_baselines:
+                    t_f, note = float("nan"), ""
+                    try:
+                        import flashinfer
+
+                        one = torch.ones(1, device=dev)
+                        fa, fsa = flashinfer.nvfp4_quantize(x, one)
+                        fb, fsb = flashinfer.nvfp4_quantize(w.to(bf), one)
+                        al = torch.tensor([1.0], device=dev)
+                        t_f = bench(lambda: flashinfer.mm_fp4(fa, fb.t(), fsa, fsb.t(), al, bf))
+                    except Exception as e:  # noqa: BLE001 - a missing or unsupported library path is a result, not a failure
+                        note = f"{type(e).__name__}: {str(e)[:160]}"
+                    print(json.dumps(dict(kernel="flashinfer.mm_fp4", shape=name, flashinfer_ms=round(t_f, 4), note=note)), flush=True)
     if a.set in ("attention", "all"):
         for name, (S, T, hq, hkv, D) in {"cosmos3.gen": (7040, 512, 40, 8, 128), "cosmos3.gen.tp4": (7040, 512, 10, 2, 128)}.items():
             if a.only and name != a.only:

@@ -73,7 +73,7 @@ class B200Kernel:
     """tcgen05 GEMM with fused bias; fp8 specs quantise the activation with the CUDA quant kernel."""
 
     name = "b200"
-    specs = frozenset({"bf16", "fp8_per_tensor", "fp8_per_channel", "fp8_block_128_128"})
+    specs = frozenset({"bf16", "fp8_per_tensor", "fp8_per_channel", "fp8_block_128_128", "nvfp4_block_16"})
     min_sm = 100
     device_types = frozenset({"cuda"})
 
@@ -94,6 +94,12 @@ class B200Kernel:
                 y = ops.linear_simt(x2, w, b)
             else:
                 y = ops.gemm(x2, w, bias=bias)
+        elif spec.spec_id == "nvfp4_block_16":
+            from ...ops import nvfp4
+
+            if not nvfp4.available() or x2.shape[1] % 32 or layer.weight.shape[0] % 8:
+                return spec.reference_apply(layer, x, bias)     # the block-scaled GEMM module is not built here
+            y = nvfp4.linear(x2.to(torch.bfloat16), layer, bias).to(x.dtype)
         elif spec.granularity is Granularity.BLOCK:
             from ...ops import fp8_block
 
