@@ -186,7 +186,8 @@ def main() -> int:
 
     L.init()
     P.register_mesh("single", Mesh((1,), ("tp",), rank=0, build_groups=False, device_type="cuda"))
-    mc = Cosmos3Config(hidden_size=512, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+    kvh = max(2, world)                      # the towers shard their K/V heads: at least one per rank
+    mc = Cosmos3Config(hidden_size=512, num_hidden_layers=2, num_attention_heads=2 * kvh, num_key_value_heads=kvh, head_dim=128,
                        intermediate_size=1024, vocab_size=512, mrope_section=(24, 20, 20), latent_channel=16,
                        latent_patch_size=2, patch_latent_dim=64)
     with P.use_mesh("single"):
