@@ -4,8 +4,8 @@
 //                                                      sfx, sfw: one ue4m3 scale per 16 elements of K
 //
 // The GEMM is the CUTLASS sm100 block-scaled collective (tcgen05.mma kind::mxf4nvf4 with the scale factors
-// staged into tensor memory, TMA operand loads, no cluster: loads are per CTA) instantiated for three tile
-// shapes; the kernels around it are this file's own: activation quantisation (bf16 rows -> e2m1 + ue4m3
+// staged into tensor memory, TMA operand loads, no cluster: loads are per CTA) instantiated for three one-CTA tile
+// shapes and one CTA-pair shape; the kernels around it are this file's own: activation quantisation (bf16 rows -> e2m1 + ue4m3
 // scales written directly in the 128 x 4 interleaved scale layout the MMA reads), the re-layout of a
 // checkpoint's row-major weight scales into that layout, and the bias add.
 //
@@ -25,6 +25,7 @@ namespace nvfp4 {
 int run_tile64(const void*, const void*, const void*, const void*, void*, int, int, int, float, void*, size_t, cudaStream_t);
 int run_tile128(const void*, const void*, const void*, const void*, void*, int, int, int, float, void*, size_t, cudaStream_t);
 int run_tile256(const void*, const void*, const void*, const void*, void*, int, int, int, float, void*, size_t, cudaStream_t);
+int run_tile2sm(const void*, const void*, const void*, const void*, void*, int, int, int, float, void*, size_t, cudaStream_t);
 
 // ------------------------------------------------------------------ own kernels
 __host__ __device__ inline size_t sf_offset(int row, int kb, int kb_padded) {
@@ -130,7 +131,7 @@ Tensor swizzle_scales(const Tensor& sf_linear, int64_t K) {
   return out;
 }
 
-// x4 [M, K/2], w4 [N, K/2] packed e2m1; sfx / sfw in the interleaved layout; out bf16 [M, N]. tile: 0 auto, 64 / 128 / 256.
+// x4 [M, K/2], w4 [N, K/2] packed e2m1; sfx / sfw in the interleaved layout; out bf16 [M, N]. tile: 0 auto, 64 / 128 / 256 (one CTA per tile), 512 (256 x 256 on a CTA pair).
 void gemm(const Tensor& x4, const Tensor& sfx, const Tensor& w4, const Tensor& sfw, Tensor& out, double alpha,
           const c10::optional<Tensor>& bias, Tensor& workspace, int64_t tile) {
   TORCH_CHECK(x4.is_cuda() && w4.is_cuda() && x4.is_contiguous() && w4.is_contiguous() && x4.scalar_type() == at::kByte &&
@@ -146,12 +147,15 @@ void gemm(const Tensor& x4, const Tensor& sfx, const Tensor& w4, const Tensor& s
     // fill the 148 SMs: the widest tile that still gives about a wave of CTAs
     const long m_t = (M + 127) / 128;
     tile = m_t * ((N + 255) / 256) >= 120 ? 256 : (m_t * ((N + 127) / 128) >= 100 ? 128 : 64);
+    // several waves of 256-wide tiles: CTA pairs halve the B traffic per SM
+    if (tile == 256 && ((M + 255) / 256) * ((N + 255) / 256) >= 148) tile = 512;
   }
   const void *A = x4.data_ptr(), *B = w4.data_ptr(), *SA = sfx.data_ptr(), *SB = sfw.data_ptr();
   void* ws = workspace.data_ptr();
   const size_t wsb = size_t(workspace.numel()) * workspace.element_size();
   int rc;
-  if (tile == 256) rc = run_tile256(A, SA, B, SB, out.data_ptr(), M, N, K, float(alpha), ws, wsb, cur());
+  if (tile == 512) rc = run_tile2sm(A, SA, B, SB, out.data_ptr(), M, N, K, float(alpha), ws, wsb, cur());
+  else if (tile == 256) rc = run_tile256(A, SA, B, SB, out.data_ptr(), M, N, K, float(alpha), ws, wsb, cur());
   else if (tile == 128) rc = run_tile128(A, SA, B, SB, out.data_ptr(), M, N, K, float(alpha), ws, wsb, cur());
   else rc = run_tile64(A, SA, B, SB, out.data_ptr(), M, N, K, float(alpha), ws, wsb, cur());
   TORCH_CHECK(rc == 0, "nvfp4 gemm: stage ", rc, " failed (1 shape not supported, 2 workspace, 3 initialise, 4 launch)");

@@ -36,7 +36,7 @@ def test_activation_quantiser(nv, M, K):
     assert int(sf.sum().item()) == int(sfl.view(torch.uint8).sum().item())
 
 
-@pytest.mark.parametrize("M,K,N,tile", [(50, 1024, 2560, 0), (300, 2048, 1000, 128), (1000, 512, 4096, 256), (129, 96, 72, 64)])
+@pytest.mark.parametrize("M,K,N,tile", [(50, 1024, 2560, 0), (300, 2048, 1000, 128), (1000, 512, 4096, 256), (129, 96, 72, 64), (700, 768, 1024, 512)])
 def test_gemm_matches_dequantised_fp32(nv, M, K, N, tile):
     from phyai_b200.layers.quant.specs import Nvfp4Spec
 
