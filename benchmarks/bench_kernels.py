@@ -78,7 +78,7 @@ def main() -> None:
         from phyai_b200.ops import fp8_block
 
         fp8_shapes = {"fp8.pi05.prefix.gate_up": (968, 2048, 32768), "fp8.pi05.expert.gate_up": (52, 1024, 8192),
-                      "fp8.cosmos3.qkv": (7040, 5120, 7168)}
+                      "fp8.cosmos3.qkv": (7040, 5120, 7168), "fp8.cosmos3.gate_up": (7040, 5120, 27648), "fp8.cosmos3.down": (7040, 13824, 5120)}
         for name, (M, K, N) in fp8_shapes.items():
             if a.only and name != a.only:
                 continue
@@ -88,9 +88,18 @@ def main() -> None:
             x8 = (xb / xs[..., None]).clamp(-448, 448).reshape(M, K).to(torch.float8_e4m3fn)
             w8, ws = fp8_block.quantize_weight_block(w)
             out = torch.empty(M, N, device=dev, dtype=bf)
+            keep, fp8_block.TILE_MODULE_MIN_ROWS = fp8_block.TILE_MODULE_MIN_ROWS, 0        # the in-tree kernel first
             t_o = bench(lambda: fp8_block.gemm_fp8_block(x8, xs, w8, ws, out))
+            fp8_block.TILE_MODULE_MIN_ROWS = keep
             row = dict(kernel="gemm_fp8_block", shape=name, ours_ms=round(t_o, 4), tflops=round(2 * M * N * K / t_o / 1e9, 1),
                        kernel_status=ops.kernel_status())
+            from phyai_b200.ops import nvfp4 as _bs
+
+            if _bs.available() and M >= 128:
+                # the CUTLASS blockwise collective of phyai_b200._blockscaled: 128 x 128, 256 x 128 pair, 256 x 256 pair
+                for tid, tname in ((1, "tile_1sm_128x128_ms"), (2, "tile_2sm_256x128_ms"), (3, "tile_2sm_256x256_ms")):
+                    row[tname] = round(bench(lambda: fp8_block.gemm_fp8_blockwise_tiles(x8, xs, w8, ws, out, tile=tid)), 4)
+                row["routed_ms"] = round(bench(lambda: fp8_block.gemm_fp8_block(x8, xs, w8, ws, out)), 4)
             print(json.dumps(row), flush=True)          # before the library call: its first use may compile for minutes
             if not a.no_baselines:
                 t_f, note = float("nan"), ""
@@ -112,7 +121,7 @@ def main() -> None:
         from phyai_b200.ops import nvfp4
 
         if not nvfp4.available():
-            print(json.dumps(dict(kernel="gemm_nvfp4", skipped="phyai_b200/_nvfp4 is not built")), flush=True)
+            print(json.dumps(dict(kernel="gemm_nvfp4", skipped="phyai_b200/_blockscaled is not built")), flush=True)
         else:
             for name, (M, K, N) in {"nvfp4.pi05.prefix.gate_up": (968, 2048, 32768), "nvfp4.pi05.expert.gate_up": (52, 1024, 8192),
                                     "nvfp4.cosmos3.qkv": (7040, 5120, 7168), "nvfp4.cosmos3.gate_up": (7040, 5120, 27648)}.items():

@@ -168,15 +168,16 @@ def cutlass_include_dirs() -> list[Path]:
     return found
 
 
-def build_nvfp4(verbose: bool = False) -> Path | None:
-    """Build ``phyai_b200/_nvfp4`` (block-scaled NVFP4 GEMM: CUTLASS sm100 collective inside ``csrc/cutlass/gemm_nvfp4.cu``
-    plus this repository's quantisation kernels). Skipped, with a note, where no CUTLASS header tree is found."""
-    src = CSRC / "cutlass" / "gemm_nvfp4.cu"
+def build_blockscaled(verbose: bool = False) -> Path | None:
+    """Build ``phyai_b200/_blockscaled`` (NVFP4 and block-scaled fp8 GEMMs: CUTLASS sm100 collectives instantiated in
+    ``csrc/cutlass/``, one translation unit per tile shape, plus this repository's quantisation kernels and bindings in
+    ``blockscaled_module.cu``). Skipped, with a note, where no CUTLASS header tree is found."""
+    src = CSRC / "cutlass" / "blockscaled_module.cu"
     if not src.is_file():
         return None
     cut = cutlass_include_dirs()
     if not cut:
-        sys.stderr.write("build_ext: no CUTLASS headers found, phyai_b200/_nvfp4 not built (NVFP4 layers use the dequantising path)\n")
+        sys.stderr.write("build_ext: no CUTLASS headers found, phyai_b200/_blockscaled not built (NVFP4 layers dequantise, block-scaled fp8 keeps the in-tree kernel)\n")
         return None
     BUILD.mkdir(exist_ok=True)
     inc, libdirs = _torch_paths()
@@ -184,7 +185,7 @@ def build_nvfp4(verbose: bool = False) -> Path | None:
     import pybind11
 
     flags = ARCH_FLAGS + ["-O3", "-std=c++17", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "--expt-extended-lambda",
-                          "-diag-suppress", "20012", "-DTORCH_EXTENSION_NAME=_nvfp4", "-DTORCH_API_INCLUDE_EXTENSION_H",
+                          "-diag-suppress", "20012", "-DTORCH_EXTENSION_NAME=_blockscaled", "-DTORCH_API_INCLUDE_EXTENSION_H",
                           "-D_GLIBCXX_USE_CXX11_ABI=1", f"-I{pyinc}", f"-I{pybind11.get_include()}"] + [f"-I{p}" for p in cut] + [
                               f"-I{p}" for p in inc]
     if verbose:
@@ -200,8 +201,8 @@ def build_nvfp4(verbose: bool = False) -> Path | None:
             jobs.append([NVCC, *flags, "-c", str(cu), "-o", str(obj)])
     with ThreadPoolExecutor(max_workers=max(1, len(jobs))) as ex:
         list(ex.map(_run, jobs))
-    out = ROOT / f"_nvfp4{ext_suffix()}"
-    stamp = BUILD / f"_nvfp4.{_hash(objs, ['link-nvfp4'])}.stamp"
+    out = ROOT / f"_blockscaled{ext_suffix()}"
+    stamp = BUILD / f"_blockscaled.{_hash(objs, ['link-blockscaled'])}.stamp"
     if not out.exists() or not stamp.exists():
         libs = ["-lc10", "-ltorch", "-ltorch_cpu", "-ltorch_python", "-lc10_cuda", "-ltorch_cuda"]
         _run([NVCC, "-shared", *ARCH_FLAGS, "-o", str(out), *map(str, objs), *[f"-L{p}" for p in libdirs], *libs,
@@ -216,9 +217,9 @@ def build_all(verbose: bool = False, debug: bool = False, sanitize: str | None =
     if r is not None:
         outs.append(r)
     try:
-        n = build_nvfp4(verbose)
+        n = build_blockscaled(verbose)
     except RuntimeError as e:        # optional module (its header tree is not this repository's): say so and go on
-        sys.stderr.write(f"build_ext: phyai_b200/_nvfp4 not built: {e}\n")
+        sys.stderr.write(f"build_ext: phyai_b200/_blockscaled not built: {e}\n")
         n = None
     if n is not None:
         outs.append(n)

@@ -1,5 +1,5 @@
 """NVFP4 linear on the block-scaled tensor cores: e2m1 operands, one ue4m3 scale per 16 elements of K, fp32 global
-scales. Kernels: ``csrc/cutlass/gemm_nvfp4.cu`` (built into ``phyai_b200/_nvfp4``; optional: without it NVFP4 layers
+scales. Kernels: ``csrc/cutlass/`` (built into ``phyai_b200/_blockscaled``; optional: without it NVFP4 layers
 run through the dequantising reference path).
 
 Reference: FlashInfer ``mm_fp4`` + ``nvfp4_quantize`` (phyai/src/phyai/layers/linear/backends/flashinfer.py:163-200).
@@ -23,7 +23,7 @@ def ext():
     if not _TRIED:
         _TRIED = True
         try:
-            from .. import _nvfp4 as m  # type: ignore[attr-defined]
+            from .. import _blockscaled as m  # type: ignore[attr-defined]
 
             _EXT = m
         except ImportError:

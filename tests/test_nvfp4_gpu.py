@@ -11,7 +11,7 @@ def nv():
     from phyai_b200.ops import nvfp4
 
     if not nvfp4.available():
-        pytest.skip("phyai_b200/_nvfp4 is not built in this checkout (needs a CUTLASS header tree at build time)")
+        pytest.skip("phyai_b200/_blockscaled is not built in this checkout (needs a CUTLASS header tree at build time)")
     return nvfp4
 
 
