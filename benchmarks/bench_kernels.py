@@ -88,18 +88,9 @@ def main() -> None:
             x8 = (xb / xs[..., None]).clamp(-448, 448).reshape(M, K).to(torch.float8_e4m3fn)
             w8, ws = fp8_block.quantize_weight_block(w)
             out = torch.empty(M, N, device=dev, dtype=bf)
-            keep, fp8_block.TILE_MODULE_MIN_ROWS = fp8_block.TILE_MODULE_MIN_ROWS, 0        # the in-tree kernel first
             t_o = bench(lambda: fp8_block.gemm_fp8_block(x8, xs, w8, ws, out))
-            fp8_block.TILE_MODULE_MIN_ROWS = keep
             row = dict(kernel="gemm_fp8_block", shape=name, ours_ms=round(t_o, 4), tflops=round(2 * M * N * K / t_o / 1e9, 1),
                        kernel_status=ops.kernel_status())
-            from phyai_b200.ops import nvfp4 as _bs
-
-            if _bs.available() and M >= 128:
-                # the CUTLASS blockwise collective of phyai_b200._blockscaled: 128 x 128, 256 x 128 pair, 256 x 256 pair
-                for tid, tname in ((1, "tile_1sm_128x128_ms"), (2, "tile_2sm_256x128_ms"), (3, "tile_2sm_256x256_ms")):
-                    row[tname] = round(bench(lambda: fp8_block.gemm_fp8_blockwise_tiles(x8, xs, w8, ws, out, tile=tid)), 4)
-                row["routed_ms"] = round(bench(lambda: fp8_block.gemm_fp8_block(x8, xs, w8, ws, out)), 4)
             print(json.dumps(row), flush=True)          # before the library call: its first use may compile for minutes
             if not a.no_baselines:
                 t_f, note = float("nan"), ""

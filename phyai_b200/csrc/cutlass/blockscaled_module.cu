@@ -1,12 +1,7 @@
-// Module ``phyai_b200._blockscaled``: the two block-scaled linears whose GEMM is a CUTLASS sm100 collective
-// instantiated in this directory (one translation unit per tile shape), with this repository's kernels around them.
-//
-// (1) Block-scaled fp8 (e4m3 operands, fp32 scale per 1 x 128 activation block and per 128 x 128 weight block, scales
-//     applied in software between K blocks): gemm_fp8_blockwise_*.cu. The in-tree kernel csrc/gemm_fp8_block.cu serves the
-//     same contract with fused epilogues and wins on few rows; these tiles win from a few hundred rows up.
-//     Reference call: FlashInfer gemm_fp8_nt_groupwise (phyai/src/phyai/layers/linear/backends/flashinfer.py:132-157).
-//
-// (2) NVFP4 linear on the block-scaled tensor-core path of sm_100a.
+// Module ``phyai_b200._blockscaled``: NVFP4 linear on the block-scaled tensor-core path of sm_100a. The GEMM is a CUTLASS
+// sm100 collective instantiated in this directory (one translation unit per tile shape), with this repository's kernels
+// around it. (The blockwise fp8 collective of the same library was measured here too: at 128 x 128 and 256 x 128-pair
+// tiles it ran level with csrc/gemm_fp8_block.cu on every shape, so block-scaled fp8 stays on the in-tree kernel.)
 //
 //   y[M, N] = alpha * (x4 . sfx) @ (w4 . sfw)^T        x4, w4: e2m1 packed two per byte (K-major),
 //                                                      sfx, sfw: one ue4m3 scale per 16 elements of K
@@ -34,15 +29,6 @@ int run_tile64(const void*, const void*, const void*, const void*, void*, int, i
 int run_tile128(const void*, const void*, const void*, const void*, void*, int, int, int, float, void*, size_t, cudaStream_t);
 int run_tile256(const void*, const void*, const void*, const void*, void*, int, int, int, float, void*, size_t, cudaStream_t);
 int run_tile2sm(const void*, const void*, const void*, const void*, void*, int, int, int, float, void*, size_t, cudaStream_t);
-}  // namespace nvfp4
-
-namespace fp8bw {
-int run_1sm128(const void*, const float*, const void*, const float*, const void*, void*, int, int, int, void*, size_t, cudaStream_t);
-int run_2sm128(const void*, const float*, const void*, const float*, const void*, void*, int, int, int, void*, size_t, cudaStream_t);
-int run_2sm256(const void*, const float*, const void*, const float*, const void*, void*, int, int, int, void*, size_t, cudaStream_t);
-}  // namespace fp8bw
-
-namespace nvfp4 {
 
 // ------------------------------------------------------------------ own kernels
 __host__ __device__ inline size_t sf_offset(int row, int kb, int kb_padded) {
@@ -186,46 +172,8 @@ void gemm(const Tensor& x4, const Tensor& sfx, const Tensor& w4, const Tensor& s
 
 }  // namespace nvfp4
 
-namespace fp8bw {
-using torch::Tensor;
-
-// x8 [M, K] e4m3 with x_scale [M, K/128]; w8 [N, K] e4m3 with w_scale [ceil(N/128), K/128]; out bf16 [M, N];
-// residual (bf16 [M, N], may be `out`) is added when given. tile: 0 auto, 1 = 128 x 128, 2 = 256 x 128 pair, 3 = 256 x 256 pair.
-void gemm(const Tensor& x8, const Tensor& x_scale, const Tensor& w8, const Tensor& w_scale, Tensor& out,
-          const c10::optional<Tensor>& residual, Tensor& workspace, int64_t tile) {
-  TORCH_CHECK(x8.is_cuda() && w8.is_cuda() && x8.is_contiguous() && w8.is_contiguous() && x8.element_size() == 1 && w8.element_size() == 1 &&
-              x8.dim() == 2 && w8.dim() == 2 && x8.size(1) == w8.size(1), "fp8 blockwise gemm: e4m3 [M, K] and [N, K]");
-  const int M = int(x8.size(0)), N = int(w8.size(0)), K = int(x8.size(1));
-  TORCH_CHECK(K % 128 == 0 && N % 8 == 0, "fp8 blockwise gemm: K % 128 and N % 8");
-  TORCH_CHECK(x_scale.is_contiguous() && x_scale.scalar_type() == at::kFloat && x_scale.numel() == int64_t(M) * (K / 128),
-              "fp8 blockwise gemm: x_scale fp32 [M, K/128]");
-  TORCH_CHECK(w_scale.is_contiguous() && w_scale.scalar_type() == at::kFloat && w_scale.numel() == int64_t((N + 127) / 128) * (K / 128),
-              "fp8 blockwise gemm: w_scale fp32 [ceil(N/128), K/128]");
-  TORCH_CHECK(out.is_contiguous() && out.scalar_type() == at::kBFloat16 && out.size(0) == M && out.size(1) == N, "fp8 blockwise gemm: out bf16 [M, N]");
-  const void* C = nullptr;
-  if (residual.has_value() && residual->defined()) {
-    TORCH_CHECK(residual->is_contiguous() && residual->scalar_type() == at::kBFloat16 && residual->numel() == out.numel(), "fp8 blockwise gemm: residual");
-    C = residual->data_ptr();
-  }
-  if (M == 0) return;
-  if (tile == 0) {
-    const long t256 = long((M + 255) / 256) * ((N + 255) / 256), t128 = long((M + 255) / 256) * ((N + 127) / 128);
-    tile = t256 >= 74 ? 3 : (t128 >= 60 ? 2 : 1);
-  }
-  void* ws = workspace.data_ptr();
-  const size_t wsb = size_t(workspace.numel()) * workspace.element_size();
-  cudaStream_t st = at::cuda::getCurrentCUDAStream().stream();
-  const float *sa = reinterpret_cast<const float*>(x_scale.data_ptr()), *sb = reinterpret_cast<const float*>(w_scale.data_ptr());
-  int rc;
-  if (tile == 3) rc = run_2sm256(x8.data_ptr(), sa, w8.data_ptr(), sb, C, out.data_ptr(), M, N, K, ws, wsb, st);
-  else if (tile == 2) rc = run_2sm128(x8.data_ptr(), sa, w8.data_ptr(), sb, C, out.data_ptr(), M, N, K, ws, wsb, st);
-  else rc = run_1sm128(x8.data_ptr(), sa, w8.data_ptr(), sb, C, out.data_ptr(), M, N, K, ws, wsb, st);
-  TORCH_CHECK(rc == 0, "fp8 blockwise gemm: stage ", rc, " failed (1 shape not supported, 2 workspace, 3 initialise, 4 launch)");
-}
-}  // namespace fp8bw
-
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
-  m.def("fp8_blockwise_gemm", &fp8bw::gemm);
+
   m.def("scale_bytes", &nvfp4::scale_bytes);
   m.def("quantize_act", &nvfp4::quantize_act);
   m.def("swizzle_scales", &nvfp4::swizzle_scales);

@@ -112,7 +112,6 @@ class envs:
     # kernel routing (read by the native library itself on first use: listed here so they show up with the rest)
     PHYAI_GEMM_PERSIST = EnvField("PHYAI_GEMM_PERSIST", True, parse_bool)        # 0: one tile per CTA for large GEMMs too
     PHYAI_GEMM_PERSIST_COMM = EnvField("PHYAI_GEMM_PERSIST_COMM", True, parse_bool)  # 0: peer modes stay off the persistent kernel
-    PHYAI_FP8_BLOCK_TILES_MIN_ROWS = EnvField("PHYAI_FP8_BLOCK_TILES_MIN_ROWS", 256, int)  # block-scaled fp8 GEMMs of at least this many rows use the CUTLASS pair tiles of _blockscaled (0: never)
     PHYAI_COMM_FUSED_TAIL = EnvField("PHYAI_COMM_FUSED_TAIL", True, parse_bool)  # 0: row-parallel products of few rows as two launches (push GEMM, reduce) instead of one
     PHYAI_GEMM_PERSIST_PUSH_WORLD = EnvField("PHYAI_GEMM_PERSIST_PUSH_WORLD", 2, int)  # largest group whose push / scatter GEMMs run persistent
     PHYAI_GEMM_2CTA = EnvField("PHYAI_GEMM_2CTA", False, parse_bool)            # 1: CTA-pair (cta_group::2) kernel for large plain GEMMs

@@ -8,30 +8,6 @@ from typing import Optional
 import torch
 
 from . import ACT, ext
-from ..env import envs
-
-_SCRATCH: dict[tuple, torch.Tensor] = {}
-_WORKSPACE: dict[torch.device, torch.Tensor] = {}
-#: rows from which the CUTLASS tiles of ``phyai_b200._blockscaled`` take over from the in-tree kernel (0: never)
-TILE_MODULE_MIN_ROWS = int(envs.PHYAI_FP8_BLOCK_TILES_MIN_ROWS.get())
-
-
-def _tile_module():
-    from . import nvfp4
-
-    return nvfp4.ext()
-
-
-def gemm_fp8_blockwise_tiles(x8: torch.Tensor, x_scale: torch.Tensor, w8: torch.Tensor, w_scale: torch.Tensor, out: torch.Tensor, *,
-                             residual: Optional[torch.Tensor] = None, tile: int = 0) -> torch.Tensor:
-    """The same product on the CUTLASS sm100 blockwise collective (``csrc/cutlass/gemm_fp8_blockwise_*.cu``): plain or
-    with a residual add; ``tile`` 0 auto, 1 = 128 x 128, 2 = 256 x 128 on a CTA pair, 3 = 256 x 256 on a CTA pair."""
-    dev = x8.device
-    ws = _WORKSPACE.get(dev)
-    if ws is None:
-        ws = _WORKSPACE[dev] = torch.zeros(32 << 20, dtype=torch.uint8, device=dev)
-    _tile_module().fp8_blockwise_gemm(x8, x_scale.contiguous(), w8, w_scale.contiguous(), out, residual, ws, tile)
-    return out
 
 
 def gemm_fp8_block(x8: torch.Tensor, x_scale: torch.Tensor, w8: torch.Tensor, w_scale: torch.Tensor, out: Optional[torch.Tensor] = None, *,
@@ -41,20 +17,6 @@ def gemm_fp8_block(x8: torch.Tensor, x_scale: torch.Tensor, w8: torch.Tensor, w_
     M, N = x8.shape[0], w8.shape[0]
     if out is None:
         out = torch.empty((M, N // 2 if glu else N), dtype=out_dtype, device=x8.device)
-    if (TILE_MODULE_MIN_ROWS and M >= TILE_MODULE_MIN_ROWS and bias is None and col_gate is None and out.dtype == torch.bfloat16
-            and out.is_contiguous() and x8.is_contiguous() and w8.is_contiguous() and (glu or act in (None, "none"))
-            and (residual is None or (residual.is_contiguous() and not glu)) and _tile_module() is not None):
-        # many rows: the pair-tile collective is ahead of the in-tree kernel; a gated activation becomes a second pass
-        if not glu:
-            return gemm_fp8_blockwise_tiles(x8, x_scale, w8, w_scale, out, residual=residual)
-        key = (x8.device, M, N)
-        tmp = _SCRATCH.get(key)
-        if tmp is None:
-            tmp = _SCRATCH[key] = torch.empty(M, N, dtype=torch.bfloat16, device=x8.device)
-        gemm_fp8_blockwise_tiles(x8, x_scale, w8, w_scale, tmp)
-        from . import gated_act
-
-        return gated_act(tmp, act or "none", interleaved=True, out=out)
     ext().gemm_fp8_block(x8, w8, out, x_scale.contiguous(), w_scale.contiguous(), bias, residual, col_gate, ACT[act], glu)
     return out
 
@@ -102,4 +64,4 @@ def layer_weight_fp8(layer) -> tuple[torch.Tensor, torch.Tensor]:
     return quantize_weight_block(w.data)
 
 
-__all__ = ["gemm_fp8_block", "gemm_fp8_blockwise_tiles", "ref_gemm_fp8_block", "quantize_weight_block", "quantize_rows_into", "layer_weight_fp8"]
+__all__ = ["gemm_fp8_block", "ref_gemm_fp8_block", "quantize_weight_block", "quantize_rows_into", "layer_weight_fp8"]
