@@ -24,6 +24,8 @@ struct AttnParams {
   int causal = 0;                     // q token i sees kv j <= i + (kv_len - q_len)
   int splits = 1;                     // KV split over a cluster (1, 2, 4 or 8)
   float sm_scale = 1.0f;
+  int window = 0;                     // > 0: q token i sees only the last `window` kv entries up to its own position (tcgen05 latency kernel)
+  float soft_cap = 0.f;               // > 0: scores become cap * tanh(score / cap) before the softmax (same kernel)
   unsigned long long* trace = nullptr;  // optional: 16 globaltimer stamps per CTA (debugging)
   long long q_rows = 0, kv_rows = 0;  // extents of the q and k/v tensors (rows), for TMA maps
 };

@@ -49,7 +49,9 @@ __device__ __forceinline__ uint32_t sw_off(int r, int c) {
 
 }  // namespace
 
-template <int DB>  // head dim padded to 64 * DB
+// EXTRA: the instantiation that also applies a sliding window (`p.window`) and / or a logit soft cap (`p.soft_cap`);
+// the plain one carries neither the compares nor the tanh.
+template <int DB, bool EXTRA = false>  // head dim padded to 64 * DB
 __global__ void __launch_bounds__(kTcThreads)
 attn_tc_kernel(AttnParams p, int* status, const __grid_constant__ CUtensorMap tmQ,
                const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -208,6 +210,19 @@ attn_tc_kernel(AttnParams p, int* status, const __grid_constant__ CUtensorMap tm
         const int jbase = ch * kTK;
         int jlim = kv_len;                                 // first masked kv index for this row
         if (p.causal) jlim = min(jlim, my_tok + causal_off + 1);
+        int jlo = 0;                                       // first visible kv index (sliding window)
+        if constexpr (EXTRA) {
+          if (p.window > 0) jlo = max(0, my_tok + causal_off - p.window + 1);
+        }
+        // score in the log2 domain; with a soft cap: cap * tanh(score / cap) first
+        const float cap = EXTRA ? p.soft_cap : 0.f, inv_cap = cap > 0.f ? 1.f / cap : 0.f;
+        auto score = [&](uint32_t raw) {
+          if constexpr (EXTRA) {
+            if (cap > 0.f) return cap * tanhf(__uint_as_float(raw) * p.sm_scale * inv_cap) * 1.4426950408889634f;
+          }
+          return __uint_as_float(raw) * scale_log2;
+        };
+        auto seen = [&](int j) { return EXTRA ? (j < jlim && j >= jlo) : j < jlim; };
         float mx = -INFINITY;
 #pragma unroll 1
         for (int c = 0; c < kTK; c += 32) {
@@ -216,7 +231,7 @@ attn_tc_kernel(AttnParams p, int* status, const __grid_constant__ CUtensorMap tm
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            if (jbase + c + j < jlim) mx = fmaxf(mx, __uint_as_float(r[j]) * scale_log2);
+            if (seen(jbase + c + j)) mx = fmaxf(mx, score(r[j]));
         }
         const float m_new = fmaxf(m_run, mx);
         const float m_use = m_new == -INFINITY ? 0.f : m_new;
@@ -233,8 +248,8 @@ attn_tc_kernel(AttnParams p, int* status, const __grid_constant__ CUtensorMap tm
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const int j0 = c + q8 * 8 + 2 * e;
-              const float p0 = jbase + j0 < jlim ? exp2f(__uint_as_float(r[q8 * 8 + 2 * e]) * scale_log2 - m_use) : 0.f;
-              const float p1 = jbase + j0 + 1 < jlim ? exp2f(__uint_as_float(r[q8 * 8 + 2 * e + 1]) * scale_log2 - m_use) : 0.f;
+              const float p0 = seen(jbase + j0) ? exp2f(score(r[q8 * 8 + 2 * e]) - m_use) : 0.f;
+              const float p1 = seen(jbase + j0 + 1) ? exp2f(score(r[q8 * 8 + 2 * e + 1]) - m_use) : 0.f;
               sum += p0 + p1;
               __nv_bfloat162 pb2 = __floats2bfloat162_rn(p0, p1);
               pk[e] = *reinterpret_cast<uint32_t*>(&pb2);
@@ -427,9 +442,9 @@ attn_tc_kernel(AttnParams p, int* status, const __grid_constant__ CUtensorMap tm
   if (warp == 4) tmem_dealloc(tmem, TMEM_COLS);
 }
 
-template <int DB>
+template <int DB, bool EXTRA>
 static cudaError_t attn_tc_launch_db(const AttnParams& p, cudaStream_t stream) {
-  auto kern = attn_tc_kernel<DB>;
+  auto kern = attn_tc_kernel<DB, EXTRA>;
   const size_t smem = size_t(3 * DB + 2) * kBlkBytes + 1024;
   static bool attr_done = false;
   if (!attr_done) {
@@ -464,9 +479,14 @@ cudaError_t attn_tc_launch(const AttnParams& p, cudaStream_t stream) {
   if ((p.q_tok_stride | p.q_head_stride | p.kv_row_stride | p.kv_head_stride | p.o_tok_stride |
        p.o_head_stride) % 8)
     return cudaErrorInvalidValue;
-  if (p.head_dim <= 64) return attn_tc_launch_db<1>(p, stream);
-  if (p.head_dim <= 128) return attn_tc_launch_db<2>(p, stream);
-  return attn_tc_launch_db<4>(p, stream);
+  if (p.window > 0 || p.soft_cap > 0.f) {
+    if (p.head_dim <= 64) return attn_tc_launch_db<1, true>(p, stream);
+    if (p.head_dim <= 128) return attn_tc_launch_db<2, true>(p, stream);
+    return attn_tc_launch_db<4, true>(p, stream);
+  }
+  if (p.head_dim <= 64) return attn_tc_launch_db<1, false>(p, stream);
+  if (p.head_dim <= 128) return attn_tc_launch_db<2, false>(p, stream);
+  return attn_tc_launch_db<4, false>(p, stream);
 }
 
 }  // namespace pb

@@ -138,7 +138,7 @@ void gemm_fp8_block(const Tensor& x, const Tensor& w, Tensor& out, const Tensor&
 void attention(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& out,
                const Tensor& q_start, const Tensor& q_len, const Tensor& kv_indptr,
                const Tensor& kv_len, const OptT& kv_indices, int64_t max_q_len, bool causal,
-               int64_t splits, double sm_scale, int64_t impl, const OptT& trace) {
+               int64_t splits, double sm_scale, int64_t impl, const OptT& trace, int64_t window, double soft_cap) {
   // q/out: [tokens, Hq, D]; k/v: [rows, Hkv, D]; innermost dim contiguous
   TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3 && out.dim() == 3, "attention: 3-D tensors");
   TORCH_CHECK(q.stride(2) == 1 && k.stride(2) == 1 && v.stride(2) == 1 && out.stride(2) == 1,
@@ -160,6 +160,8 @@ void attention(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& out,
   p.causal = causal ? 1 : 0;
   p.splits = int(splits);
   p.sm_scale = float(sm_scale);
+  p.window = int(window); p.soft_cap = float(soft_cap);
+  TORCH_CHECK((window <= 0 && soft_cap <= 0) || impl == 1, "attention: sliding window / soft cap are served by the tcgen05 latency kernel (impl 1)");
   p.q_rows = q.size(0); p.kv_rows = k.size(0);
   if (trace.has_value() && trace->defined()) p.trace = reinterpret_cast<unsigned long long*>(trace->data_ptr());
   // impl: 0 = mma.sync, 1 = tcgen05 (latency variant), 2 = tcgen05 pipelined (throughput variant)
@@ -509,7 +511,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attention", &attention, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"),
         py::arg("q_start"), py::arg("q_len"), py::arg("kv_indptr"), py::arg("kv_len"),
         py::arg("kv_indices") = py::none(), py::arg("max_q_len"), py::arg("causal") = false,
-        py::arg("splits") = 1, py::arg("sm_scale") = 1.0, py::arg("impl") = 1, py::arg("trace") = py::none());
+        py::arg("splits") = 1, py::arg("sm_scale") = 1.0, py::arg("impl") = 1, py::arg("trace") = py::none(),
+        py::arg("window") = 0, py::arg("soft_cap") = 0.0);
   m.def("norm", &norm, py::arg("x"), py::arg("y"), py::arg("mode"), py::arg("weight") = py::none(),
         py::arg("bias") = py::none(), py::arg("mod") = py::none(), py::arg("group") = 1,
         py::arg("residual") = py::none(), py::arg("sumsq") = py::none(), py::arg("eps") = 1e-6,

@@ -48,28 +48,43 @@ class Attention(nn.Module):
     def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, meta: RaggedMeta | None = None,
                 mask: torch.Tensor | None = None) -> torch.Tensor:
         plain = self.sliding_window is None and self.logits_soft_cap is None and mask is None
+        # a sliding window (on a causal layer) and a logit soft cap are served by the tcgen05 kernel too; an explicit mask is not
+        kern = mask is None and (self.sliding_window is None or self.causal)
+        extra = dict(window=int(self.sliding_window or 0), soft_cap=float(self.logits_soft_cap or 0.0))
         if q.dim() == 3:                                   # ragged (T, H, D)
             if meta is None:
                 raise ValueError("ragged attention needs RaggedMeta")
             cu = meta.cu_seqlens.to(torch.int32)
             start, lens = cu[:-1].contiguous(), (cu[1:] - cu[:-1]).contiguous()
-            if plain and _kernel_ok(self.backend, q):
+            if kern and _kernel_ok(self.backend, q):
                 return ops.attention(q, k, v, None, start, lens, start, lens, max_q_len=meta.max_len,
-                                     causal=self.causal, sm_scale=self.scale)
+                                     causal=self.causal, sm_scale=self.scale, **extra)
+            if not plain:
+                if mask is not None:
+                    raise NotImplementedError("ragged attention takes no explicit mask")
+                # window / soft cap off the kernel path: one sequence at a time through the eager statement
+                outs = [self._eager(q[s:s + n][None], k[s:s + n][None], v[s:s + n][None], None)[0]
+                        for s, n in zip(start.tolist(), lens.tolist())]
+                return torch.cat(outs)
             return ref.attention(q, k, v, start, lens, start, lens, causal=self.causal, sm_scale=self.scale)
         B, Sq, Hq, D = q.shape
         Sk = k.shape[1]
-        if plain and _kernel_ok(self.backend, q) and q.is_contiguous() and k.is_contiguous() and v.is_contiguous():
+        if kern and _kernel_ok(self.backend, q) and q.is_contiguous() and k.is_contiguous() and v.is_contiguous():
             ar = torch.arange(B, device=q.device, dtype=torch.int32)
             out = ops.attention(q.view(B * Sq, Hq, D), k.view(B * Sk, -1, D), v.view(B * Sk, -1, D), None, ar * Sq,
                                 torch.full_like(ar, Sq), ar * Sk, torch.full_like(ar, Sk), max_q_len=Sq,
-                                causal=self.causal, sm_scale=self.scale)
+                                causal=self.causal, sm_scale=self.scale, **extra)
             return out.view(B, Sq, Hq, D)
         if plain and self.backend == "torch" and q.device.type != "cpu":
             o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
                                                is_causal=self.causal and Sq == Sk, scale=self.scale,
                                                enable_gqa=self.num_kv_heads != self.num_heads)
             return o.transpose(1, 2)
+        return self._eager(q, k, v, mask)
+
+    def _eager(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.Tensor | None) -> torch.Tensor:
+        """(B, S, H, D) statement in PyTorch with every option (mask, window, soft cap)."""
+        Sq, Sk = q.shape[1], k.shape[1]
         m = mask
         if self.sliding_window is not None:
             qi = torch.arange(Sq, device=q.device)[:, None] + (Sk - Sq)

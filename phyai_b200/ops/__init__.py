@@ -145,7 +145,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[t
               kv_len: torch.Tensor, *, kv_indices: Optional[torch.Tensor] = None,
               max_q_len: int, causal: bool = False, splits: int = 1,
               sm_scale: Optional[float] = None, impl: Optional[str] = None,
-              trace: Optional[torch.Tensor] = None) -> torch.Tensor:
+              trace: Optional[torch.Tensor] = None, window: int = 0, soft_cap: float = 0.0) -> torch.Tensor:
     """Ragged / paged attention (see ``csrc/attention.cuh``).
 
     ``q`` ``(tokens, Hq, D)``; ``k``/``v`` ``(rows, Hkv, D)`` pools; sequence ``b`` owns
@@ -155,10 +155,15 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[t
     ``"pp"`` (tcgen05, two query tiles per CTA in ping-pong with P kept in tensor memory: the
     throughput variant for long dense sequences, head_dim <= 128) or ``"mma"`` (mma.sync). By
     default long unpaged calls take ``"pp"`` and everything else ``"tc"``.
+    ``window`` > 0: a query at position ``i`` (counted from the end of its KV range) sees KV entries ``i - window + 1 .. i``
+    only; ``soft_cap`` > 0: scores become ``soft_cap * tanh(score / soft_cap)`` before the softmax. Both run on ``"tc"``.
     """
+    extra = window > 0 or soft_cap > 0
     if impl is None:
         impl = ATTN_IMPL
-        if (impl == "tc" and max_q_len >= 512 and kv_indices is None and splits == 1 and q.shape[-1] <= 128
+        if extra:
+            impl = "tc"
+        elif (impl == "tc" and max_q_len >= 512 and kv_indices is None and splits == 1 and q.shape[-1] <= 128
                 and q.shape[-1] % 8 == 0):
             impl = "pp"
     if out is None:
@@ -166,7 +171,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[t
     if sm_scale is None:
         sm_scale = q.shape[-1] ** -0.5
     ext().attention(q, k, v, out, q_start, q_len, kv_indptr, kv_len, kv_indices, max_q_len,
-                    causal, splits, sm_scale, {"mma": 0, "tc": 1, "pp": 2}[impl], trace)
+                    causal, splits, sm_scale, {"mma": 0, "tc": 1, "pp": 2}[impl], trace, int(window), float(soft_cap))
     return out
 
 

@@ -606,3 +606,26 @@ def test_odd_linear_layer_runs_own_kernel():
     assert ops.launch_counter() == c0 + 1
     want = x @ lin.weight.t() + lin.bias
     assert torch.allclose(y, want, atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize("window,cap,D,Hq,Hkv", [(37, 0.0, 128, 4, 2), (0, 30.0, 64, 4, 4), (100, 50.0, 256, 8, 1)])
+def test_attention_window_and_soft_cap(window, cap, D, Hq, Hkv):
+    """Sliding window and logit soft cap in the tcgen05 latency kernel against the eager statement of the layer."""
+    from phyai_b200.engine_config import DeviceConfig, EngineConfig, init_engine_config
+    from phyai_b200.layers.attention.layers import Attention
+
+    init_engine_config(EngineConfig(device=DeviceConfig("cuda", torch.bfloat16)))
+    g = torch.Generator().manual_seed(D + window)
+    B, Sq, Sk = 2, 150, 333
+    q = torch.randn(B, Sq, Hq, D, generator=g).bfloat16().cuda()
+    k = torch.randn(B, Sk, Hkv, D, generator=g).bfloat16().cuda()
+    v = torch.randn(B, Sk, Hkv, D, generator=g).bfloat16().cuda()
+    layer = Attention(Hq, D, Hkv, causal=True, sliding_window=window or None, logits_soft_cap=cap or None, backend="b200")
+    from phyai_b200 import ops
+
+    c0 = ops.launch_counter()
+    got = layer(q, k, v)
+    assert ops.launch_counter() == c0 + 1                      # the kernel ran, not the eager statement
+    _status_ok()
+    want = layer._eager(q.float(), k.float(), v.float(), None)
+    assert torch.allclose(got.float(), want, atol=2e-2, rtol=2e-2), float((got.float() - want).abs().max())
