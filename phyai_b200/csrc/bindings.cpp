@@ -58,7 +58,7 @@ void gemm(const Tensor& x, const Tensor& w, Tensor& out, const OptT& bias, const
           int64_t act, bool glu, const OptT& a_scale, const OptT& w_scale, int64_t force_bn,
           int64_t force_swap, int64_t force_splits, const OptT& trace, int64_t wait_sig_ptr,
           int64_t wait_channel, int64_t wait_expect, int64_t row_rms_dim, double row_rms_eps,
-          const OptT& rope, const OptT& zero) {
+          const OptT& rope, const OptT& zero, const OptT& out2, const OptT& col_scale2) {
   TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2, "gemm: 2-D tensors expected");
   TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1 && out.stride(1) == 1, "gemm: rows must be contiguous");
   TORCH_CHECK(x.size(1) == w.size(1), "gemm: K mismatch");
@@ -93,6 +93,13 @@ void gemm(const Tensor& x, const Tensor& w, Tensor& out, const OptT& bias, const
     a.zero = const_cast<float*>(f32(zero)); a.zero_n = int(zero->numel());
   }
   a.sumsq = const_cast<float*>(f32(sumsq));
+  if (out2.has_value() && out2->defined()) {
+    TORCH_CHECK(out2->dim() == 2 && out2->stride(1) == 1 && out2->scalar_type() == at::kBFloat16 && out2->size(0) == out.size(0) &&
+                out2->size(1) == out.size(1), "gemm: out2 must be bf16 of out's shape");
+    TORCH_CHECK(col_scale2.has_value() && col_scale2->defined() && col_scale2->is_contiguous() && col_scale2->numel() == out.size(1),
+                "gemm: out2 needs col_scale2 [N]");
+    a.out2 = bfm(*out2); a.ldo2 = int(out2->stride(0)); a.col_scale2 = bf(col_scale2);
+  }
   a.act = int(act); a.glu = glu ? 1 : 0; a.fp8 = fp8 ? 1 : 0;
   a.a_scale = f32(a_scale); a.w_scale = f32(w_scale);
   TORCH_CHECK(!fp8 || (a.a_scale && a.w_scale), "gemm: fp8 needs a_scale [M] and w_scale [N]");
@@ -502,7 +509,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("force_bn") = 0, py::arg("force_swap") = -1, py::arg("force_splits") = 0,
         py::arg("trace") = py::none(), py::arg("wait_sig_ptr") = 0, py::arg("wait_channel") = -1,
         py::arg("wait_expect") = 0, py::arg("row_rms_dim") = 0, py::arg("row_rms_eps") = 0.0,
-        py::arg("rope") = py::none(), py::arg("zero") = py::none());
+        py::arg("rope") = py::none(), py::arg("zero") = py::none(), py::arg("out2") = py::none(),
+        py::arg("col_scale2") = py::none());
   m.def("rope_epilogue_desc", &rope_epilogue_desc, py::arg("q_out"), py::arg("k_pool"), py::arg("v_pool"),
         py::arg("cos_sin"), py::arg("pos"), py::arg("slots"), py::arg("Hq"), py::arg("Hkv"), py::arg("D"));
   m.def("gemm_fp8_block", &gemm_fp8_block, py::arg("x"), py::arg("w"), py::arg("out"), py::arg("a_scale"), py::arg("w_scale"),

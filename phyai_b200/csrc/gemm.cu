@@ -506,13 +506,13 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream, int* n_ctas) {
       (reinterpret_cast<uintptr_t>(a.w_scale) & 15))
     return cudaErrorInvalidValue;
   if (a.block_scaled) return cudaErrorInvalidValue;  // handled by gemm_fp8_block_launch
-  if (gemm_2cta_eligible(a)) {
+  if (!a.out2 && gemm_2cta_eligible(a)) {
     const cudaError_t e = gemm_2cta_launch(a, stream);
     if (e != cudaErrorInvalidClusterSize) return e;
     cudaGetLastError();   // pairs cannot be scheduled in this context (e.g. an SM partition): use one CTA per tile set
     set_gemm_2cta(0);
   }
-  if (gemm_persist_eligible(a)) {
+  if (!a.out2 && gemm_persist_eligible(a)) {
     if (a.push && (a.push->world < 0 || a.push->world > kMaxRanks ||
                    (a.push->world > 0 && (a.glu || a.act || a.bias || a.residual || a.col_gate)) ||
                    (a.push->world > 0 && a.push->rows_per_rank > 0 &&
@@ -610,6 +610,10 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream, int* n_ctas) {
   ep.act = a.act; ep.glu = a.glu; ep.out_fp32 = a.out_fp32;
   ep.rs_inv_dim = a.row_rms_dim > 0 ? 1.f / float(a.row_rms_dim) : 0.f; ep.rs_eps = a.row_rms_eps;
   ep.rope = a.rope; ep.zero = a.zero; ep.zero_n = a.zero_n;
+  ep.out2 = a.out2; ep.col_scale2 = a.col_scale2; ep.ldo2 = a.ldo2;
+  if (a.out2 && (a.glu || a.out_fp32 || a.rope || a.push || !a.col_scale2 || (a.ldo2 % 4) ||
+                 (reinterpret_cast<uintptr_t>(a.out2) & 7) || (reinterpret_cast<uintptr_t>(a.col_scale2) & 7)))
+    return cudaErrorInvalidValue;
 #ifdef PHYAI_DEBUG
   ep.status = kernel_status_ptr();
 #endif

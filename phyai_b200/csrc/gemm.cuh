@@ -59,6 +59,9 @@ struct GemmArgs {
   int row_rms_dim = 0;                      // > 0: row_scale is the sum of squares of a row of that width
   float row_rms_eps = 0.f;
   float* sumsq = nullptr;                   // [M]
+  __nv_bfloat16* out2 = nullptr;            // [M, ldo2] second bf16 output: stored value * (1 + col_scale2[n]) (one-tile kernel, no glu)
+  const __nv_bfloat16* col_scale2 = nullptr;  // [N]
+  int ldo2 = 0;
   int act = kActNone;
   int glu = 0;
   int out_fp32 = 0;

@@ -31,6 +31,11 @@ struct EpiParams {
   float* zero = nullptr;                  // optional fp32 scratch cleared by the first CTA (sum-of-squares
   int zero_n = 0;                         // accumulators that a later launch adds into)
   int* status = nullptr;                  // debug build: where a failed index check is recorded
+  // second output of a plain (non-gated) bf16 store: out2[m, n] = bf16(stored value * (1 + col_scale2[n])), the input
+  // of a norm whose column factor is applied here and whose per-row factor the consuming GEMM applies (row_rms)
+  __nv_bfloat16* out2 = nullptr;
+  const __nv_bfloat16* col_scale2 = nullptr;
+  int ldo2 = 0;
 };
 
 __device__ __forceinline__ float epi_act(float v, int act) {
@@ -75,8 +80,12 @@ __device__ __forceinline__ void epilogue_pass_t(const EpiParams& ep, const float
     const int n = n0 + c;
     if (n >= ep.N) continue;
     float bias4[4] = {0.f, 0.f, 0.f, 0.f}, gate4[4] = {1.f, 1.f, 1.f, 1.f}, ws4[4] = {1.f, 1.f, 1.f, 1.f};
+    float cs4[4] = {0.f, 0.f, 0.f, 0.f};
     if constexpr (AUX) {
       if (ep.bias) ld_bf16x4(ep.bias + n, bias4);
+      if constexpr (!GLU) {
+        if (ep.out2) ld_bf16x4(ep.col_scale2 + n, cs4);
+      }
       if (ep.w_scale) {
         const float4 w = *reinterpret_cast<const float4*>(ep.w_scale + n);
         ws4[0] = w.x; ws4[1] = w.y; ws4[2] = w.z; ws4[3] = w.w;
@@ -181,6 +190,14 @@ __device__ __forceinline__ void epilogue_pass_t(const EpiParams& ep, const float
               const float q0 = bf2f(o01.x), q1 = bf2f(o01.y);
               const float q2 = bf2f(o23.x), q3 = bf2f(o23.y);
               ss = q0 * q0 + q1 * q1 + q2 * q2 + q3 * q3;
+              if (ep.out2) {
+                const __nv_bfloat162 s01 = __floats2bfloat162_rn(q0 * (1.f + cs4[0]), q1 * (1.f + cs4[1]));
+                const __nv_bfloat162 s23 = __floats2bfloat162_rn(q2 * (1.f + cs4[2]), q3 * (1.f + cs4[3]));
+                uint2 raw2;
+                raw2.x = *reinterpret_cast<const uint32_t*>(&s01);
+                raw2.y = *reinterpret_cast<const uint32_t*>(&s23);
+                *reinterpret_cast<uint2*>(ep.out2 + size_t(m) * ep.ldo2 + n) = raw2;
+              }
             }
           }
         }
@@ -324,7 +341,7 @@ __device__ __forceinline__ void epilogue_pass(const EpiParams& ep, const float* 
     return;
   }
   const bool aux = ep.bias || ep.residual || ep.col_gate || ep.row_scale || ep.sumsq || ep.a_scale ||
-                   ep.w_scale || ep.out_fp32;
+                   ep.w_scale || ep.out_fp32 || ep.out2;
   if (ep.glu) {
     switch (ep.act) {
       case 1: PB_EPI(1, true); break;

@@ -9,11 +9,12 @@ CUDA graph per prompt-length bucket:
 * ``prefix``  18 Gemma blocks over [image | prompt] rows; K/V go straight from the epilogue
   of the QKV GEMM into the paged pool; the last block stops after its K/V write because
   nothing reads its output (the reference computes it, scheduler_ws1_pi05.py:505-511);
-* ``expert``  the 10-step Euler loop, 5 kernels per block: QKV GEMM (AdaRMS factor, RoPE and
+* ``expert``  the 10-step Euler loop, 5 kernels per block: QKV GEMM (AdaRMS row factor, RoPE and
   K/V write in its epilogue), joint attention (KV split over a cluster), o-proj GEMM with
-  gated residual and sum-of-squares epilogue, gate-up GEMM with AdaRMS factor and GeGLU
-  epilogue, down GEMM with gated residual and sum-of-squares epilogue (the reference needs
-  ~13, modeling_pi05.py:801-835). With ``fold_norms = False`` the unfused 8-kernel sequence
+  gated residual, sum-of-squares and the next norm's column factor in its epilogue, gate-up GEMM
+  with AdaRMS row factor and GeGLU epilogue, down GEMM with gated residual, sum-of-squares and
+  column-factor epilogue (the reference needs ~13, modeling_pi05.py:801-835); one copy of the
+  expert weights serves every step. With ``fold_norms = False`` the unfused 8-kernel sequence
   (separate AdaRMSNorm and RoPE kernels) runs instead.
 
 The first Euler step runs on a second stream underneath the prefix decoder (``_run_overlapped``):
@@ -55,7 +56,7 @@ class PI05Layout:
 class PI05Plan:
     #: suffix tokens in front of the action tokens (Pi0 puts one state token there)
     suffix_extra = 0
-    #: fold the expert's AdaRMS norms into the neighbouring GEMMs (one weight copy per Euler step)
+    #: fold the expert's AdaRMS norms into the epilogues of the neighbouring GEMMs (one shared weight copy)
     fold_norms = True
     #: run the first Euler step on a second stream under the prefix decoder (PHYAI_PI05_OVERLAP=0 turns it off)
     overlap_first_step = bool(envs.PHYAI_PI05_OVERLAP.get())
@@ -286,41 +287,34 @@ class PI05Plan:
         self.p_ss = torch.zeros(2, self.B * self.P, dtype=torch.float32, device=self.device)
 
     def _fold_modulation(self, stack) -> None:
-        """Per Euler step, fold each AdaRMS (1 + scale) into the weight that consumes the normed rows
-        and (shift @ W^T) into a bias, so that ``norm(h) @ W^T`` becomes one GEMM on the raw rows with
-        a per-row ``rsqrt(mean(h^2) + eps)`` factor in its epilogue. The row sums of squares come from
-        the epilogue of the GEMM that wrote ``h``. Costs one weight copy per step (a few GB)."""
+        """AdaRMS without a norm kernel and with ONE copy of the weights: ``norm(h) @ W^T`` is evaluated as
+        ``((h * (1 + scale)) @ W^T) * rsqrt(mean(h^2) + eps) + shift @ W^T``. The column factor is applied by the
+        epilogue of the GEMM that produces ``h`` (its second output, ``out2``), together with the row sums of squares;
+        the row factor by the epilogue of the consuming GEMM; ``shift @ W^T`` is a bias row per Euler step (kilobytes)."""
         He = self.cfg.expert.hidden_size
         dt = torch.bfloat16
 
-        def fold(w: torch.Tensor, mod: torch.Tensor, bias: torch.Tensor | None = None):
-            scale, shift = mod[:, :He].float(), mod[:, He:2 * He].float()
-            wf = w.float()
-            folded = torch.empty(mod.shape[0], *w.shape, dtype=dt, device=w.device)
-            for i in range(mod.shape[0]):                       # one step at a time: bounded fp32 scratch
-                folded[i] = (wf * (1.0 + scale[i])[None, :]).to(dt)
-            b = shift @ wf.T
+        def shift_bias(w: torch.Tensor, mod: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+            b = mod[:, He:2 * He].float() @ w.float().T                      # (steps, N)
             if bias is not None:
                 b = b + bias.float()[None, :]
-            return folded, b.to(dt).contiguous()
+            return b.to(dt).contiguous()
 
         t = self.cfg.text
         Hq, Hkv, D = self.Hq_e, self.Hkv, t.head_dim
-        # with the persistent kernel serving the loop, only the first step (the one that may run on the
-        # second stream under the prefix decoder) still goes launch by launch: one folded copy, not one per step
-        keep = 1 if self.stack is not None else self.cfg.num_inference_steps
-        self.folded_steps = keep
+        self.folded_steps = self.cfg.num_inference_steps
         self.fold_qkv, self.fold_gate_up = [], []
         for li, layer in enumerate(stack.layers):
             # q / k head rows reordered for the rotating epilogue of the QKV GEMM. The first block of a
-            # step keeps its norm kernel (nothing upstream accumulates its sums): plain weight, no bias.
+            # step keeps its norm kernel (nothing upstream produces its scaled rows): no bias.
             wq = ops.permute_rope_rows(layer.attn.qkv.weight, Hq, Hkv, D)
-            self.fold_qkv.append(fold(wq, self.mod_in[li][:keep]) if li > 0 else (wq, None))
-            self.fold_gate_up.append(fold(layer.mlp.gate_up.weight, self.mod_post[li][:keep]))
+            self.fold_qkv.append((wq, shift_bias(wq, self.mod_in[li]) if li > 0 else None))
+            self.fold_gate_up.append((layer.mlp.gate_up.weight, shift_bias(layer.mlp.gate_up.weight, self.mod_post[li])))
         self.rope_desc = self._rope_descs(self.e_q, self.e_pos, self.e_slots, self.Hq_e)
         heads = self.model.heads
-        self.fold_out = fold(heads.action_out_proj.weight, self.mod_final[:keep], heads.action_out_proj.bias)
+        self.fold_out = (heads.action_out_proj.weight, shift_bias(heads.action_out_proj.weight, self.mod_final, heads.action_out_proj.bias))
         self.e_ss = torch.zeros(2, self.Me, dtype=torch.float32, device=self.device)
+        self.e_x2 = torch.zeros(self.Me, He, dtype=dt, device=self.device)      # h * (1 + scale) of the norm that comes next
 
     def _rope_descs(self, q_out: torch.Tensor, pos: torch.Tensor, slots: torch.Tensor, q_heads: int | None = None) -> list[torch.Tensor]:
         """One rotate-and-scatter destination per layer (its K/V pool) for the QKV GEMM epilogue."""
@@ -556,13 +550,15 @@ class PI05Plan:
                 raise ValueError("the persistent expert kernel runs a contiguous range of Euler steps")
             self._run_expert_kernel(steps[0], steps[-1] + 1)
             steps = []
+        x2, n_layers = self.e_x2, len(stack.layers)
         for i in steps:
             if i >= self.folded_steps:
-                raise RuntimeError(f"Euler step {i} has no folded weights (only {self.folded_steps} kept)")
+                raise RuntimeError(f"Euler step {i} has no folded biases (only {self.folded_steps} kept)")
             ops.gemm(self.x_t, heads.action_in_proj.weight, h, bias=heads.action_in_proj.bias)
             for li, layer in enumerate(stack.layers):
                 kpool, vpool = self.pool.layer(li)
                 m_in, m_post = self.mod_in[li][i:i + 1], self.mod_post[li][i:i + 1]
+                nxt = self.mod_in[li + 1][i] if li + 1 < n_layers else self.mod_final[i]
                 if before_block is not None:
                     before_block(li)
                 # the QKV epilogue rotates q / k and writes k / v into this block's pool rows
@@ -571,18 +567,19 @@ class PI05Plan:
                     ops.norm(h, "ada_rms", mod=m_in, group=Me, eps=e.rms_norm_eps, out=x)
                     ops.gemm(x, w, self.e_qkv, rope=self.rope_desc[li])
                 else:
-                    ops.gemm(h, w[i], self.e_qkv, bias=b[i], row_scale=ss_in, row_rms=rms, rope=self.rope_desc[li])
+                    ops.gemm(x2, w, self.e_qkv, bias=b[i], row_scale=ss_in, row_rms=rms, rope=self.rope_desc[li])
                 ops.attention(q3, kpool, vpool, a3, self.e_qstart, self.e_qlen, self.e_kvptr, self.e_kvlen,
                               max_q_len=self.C, splits=self.expert_splits, sm_scale=D ** -0.5)
-                # each accumulating GEMM clears the other accumulator, which is idle at that point
+                # each accumulating GEMM clears the other accumulator, which is idle at that point, and leaves the rows
+                # scaled by the next norm's column factor beside the residual stream
                 ops.gemm(self.e_attn, layer.attn.o.weight, h, residual=h, col_gate=m_in[0, 2 * He:], sumsq=ss_post,
-                         zero=ss_in)
+                         zero=ss_in, out2=x2, col_scale2=m_post[0, :He])
                 w, b = self.fold_gate_up[li]
-                ops.gemm(h, w[i], self.e_act, bias=b[i], row_scale=ss_post, row_rms=rms, act="gelu_tanh", glu=True)
+                ops.gemm(x2, w, self.e_act, bias=b[i], row_scale=ss_post, row_rms=rms, act="gelu_tanh", glu=True)
                 ops.gemm(self.e_act, layer.mlp.down.weight, h, residual=h, col_gate=m_post[0, 2 * He:], sumsq=ss_in,
-                         zero=ss_post)
+                         zero=ss_post, out2=x2, col_scale2=nxt[:He])
             w, b = self.fold_out
-            ops.gemm(h, w[i], self.e_v, bias=b[i], row_scale=ss_in, row_rms=rms)
+            ops.gemm(x2, w, self.e_v, bias=b[i], row_scale=ss_in, row_rms=rms)
             ops.axpy(self.x_t, self.e_v, self.dt)
         if finish:
             self.out.view(Me, -1).copy_(self.x_t)

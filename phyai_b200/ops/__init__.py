@@ -93,7 +93,8 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *
          force_bn: int = 0, force_swap: int = -1, force_splits: int = 0,
          trace: Optional[torch.Tensor] = None, wait: Optional[tuple[int, int, int]] = None,
          row_rms: Optional[tuple[int, float]] = None, rope: Optional[torch.Tensor] = None,
-         zero: Optional[torch.Tensor] = None) -> torch.Tensor:
+         zero: Optional[torch.Tensor] = None, out2: Optional[torch.Tensor] = None,
+         col_scale2: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out = epilogue(x @ w.T)`` on tcgen05 tensor cores (see ``csrc/gemm.cuh``).
 
     ``wait=(signal_array_ptr, channel, arrivals)``: ``x`` lives in symmetric memory and is being
@@ -108,6 +109,8 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *
     rows were permuted with :func:`permute_rope_rows`, and instead of storing ``out`` (untouched) the
     epilogue rotates q and k and writes q to its buffer and k / v to their KV-pool rows.
     ``zero``: an fp32 scratch tensor this launch clears (never one it reads or accumulates into).
+    ``out2`` / ``col_scale2``: a second bf16 output ``out * (1 + col_scale2[n])`` of a plain (non-gated) store: the
+    column half of an (Ada)RMS norm applied where the rows are produced; the consumer applies the row half (``row_rms``).
 
     ``x`` is ``(M, K)``, ``w`` is ``(N, K)`` (the ``nn.Linear`` layout), both bf16 or
     both float8_e4m3fn (then ``a_scale`` (M,) and ``w_scale`` (N,) dequantise). With
@@ -119,7 +122,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *
         out = torch.empty((M, N // 2 if glu else N), dtype=out_dtype, device=x.device)
     ext().gemm(x, w, out, bias, residual, res_mod, col_gate, row_scale, sumsq, ACT[act], glu,
                a_scale, w_scale, force_bn, force_swap, force_splits, trace,
-               *((0, -1, 0) if wait is None else wait), *((0, 0.0) if row_rms is None else row_rms), rope, zero)
+               *((0, -1, 0) if wait is None else wait), *((0, 0.0) if row_rms is None else row_rms), rope, zero, out2, col_scale2)
     return out
 
 

@@ -629,3 +629,27 @@ def test_attention_window_and_soft_cap(window, cap, D, Hq, Hkv):
     _status_ok()
     want = layer._eager(q.float(), k.float(), v.float(), None)
     assert torch.allclose(got.float(), want, atol=2e-2, rtol=2e-2), float((got.float() - want).abs().max())
+
+
+@pytest.mark.parametrize("M,K,N", [(50, 1024, 1024), (300, 256, 520), (7, 4096, 1024)])
+def test_gemm_second_output_with_column_factor(M, K, N):
+    """``out2 = out * (1 + col_scale2)`` beside a gated-residual store with row sums of squares (the producer half of
+    an AdaRMS norm folded into GEMM epilogues) against fp32."""
+    from phyai_b200 import ops
+
+    g = torch.Generator().manual_seed(K + M)
+    x = (torch.randn(M, K, generator=g) * 0.3).bfloat16().cuda()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16().cuda()
+    res = torch.randn(M, N, generator=g).bfloat16().cuda()
+    gate = torch.randn(N, generator=g).bfloat16().cuda()
+    cs = (torch.randn(N, generator=g) * 0.3).bfloat16().cuda()
+    h = res.clone()
+    ss = torch.zeros(M, dtype=torch.float32, device="cuda")
+    out2 = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    ops.gemm(x, w, h, residual=h, col_gate=gate, sumsq=ss, out2=out2, col_scale2=cs)
+    _status_ok()
+    want_h = res.float() + (x.float() @ w.float().t()) * gate.float()
+    assert torch.allclose(h.float(), want_h, atol=2e-2 * float(want_h.abs().max()), rtol=2e-2)
+    hb = h.float()                                   # the second output and the sums are taken from the stored (rounded) rows
+    assert torch.allclose(out2.float(), hb * (1 + cs.float()), atol=1e-2 * float(hb.abs().max()), rtol=1e-2)
+    assert torch.allclose(ss, hb.pow(2).sum(-1), rtol=1e-3, atol=1e-3)
