@@ -336,6 +336,20 @@ void cfg_combine(const Tensor& cond, const Tensor& uncond, double g, const OptT&
         "cfg_combine_launch");
 }
 
+Tensor domain_linear(const Tensor& x, const Tensor& w, const Tensor& bias, const Tensor& domain) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 3 && x.is_contiguous() && x.scalar_type() == at::kBFloat16, "domain_linear: x bf16 [B, T, K]");
+  const int64_t B = x.size(0), T = x.size(1), K = x.size(2);
+  TORCH_CHECK(w.is_contiguous() && w.scalar_type() == at::kBFloat16 && w.dim() == 2 && w.size(1) % K == 0, "domain_linear: w bf16 [domains, K * N]");
+  const int64_t N = w.size(1) / K;
+  TORCH_CHECK(bias.is_contiguous() && bias.scalar_type() == at::kBFloat16 && bias.dim() == 2 && bias.size(0) == w.size(0) && bias.size(1) == N,
+              "domain_linear: bias bf16 [domains, N]");
+  TORCH_CHECK(domain.is_cuda() && domain.is_contiguous() && domain.scalar_type() == at::kLong && domain.numel() == B, "domain_linear: domain int64 [B]");
+  Tensor y = at::empty({B, T, N}, x.options());
+  check(pb::domain_linear_launch(bf(x), bf(w), bf(bias), i64(OptT(domain)), bfm(y), int(B), int(T), int(K), int(N), cur_stream()),
+        "domain_linear_launch");
+  return y;
+}
+
 Tensor linear_simt(const Tensor& x, const Tensor& w, const OptT& bias) {
   auto code = [](const Tensor& t) {
     switch (t.scalar_type()) {
@@ -544,6 +558,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("snake", &snake);
   m.def("unipc_step", &unipc_step);
   m.def("linear_simt", &linear_simt);
+  m.def("domain_linear", &domain_linear);
   m.def("gdn_decode", &gdn_decode, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("g"), py::arg("beta"),
         py::arg("state_pool"), py::arg("state_indices"), py::arg("scale"), py::arg("l2norm") = true);
   m.def("kernel_status", [] { return pb::read_and_clear_kernel_status(); });

@@ -842,6 +842,42 @@ cudaError_t linear_simt_launch(const void* x, int x_type, const void* w, int w_t
   return cudaErrorInvalidValue;
 }
 
+// ------------------------------------------------------------ per-domain linear
+// y[b, t, :] = x[b, t, :] @ W[domain[b]] + bias[domain[b]] with W stored [domains][in][out] (the checkpoint layout of
+// the embodiment-specific action projections): one thread per output column and four rows, the domain read on the
+// device so the caller never synchronises. A few MFLOP per call; CUDA cores.
+__global__ void domain_linear_kernel(const __nv_bfloat16* x, const __nv_bfloat16* w, const __nv_bfloat16* bias,
+                                     const long long* domain, __nv_bfloat16* y, int T, int K, int N) {
+  constexpr int R = 4;
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  const int b = blockIdx.z, t0 = blockIdx.y * R;
+  pdl_launch_dependents();
+  pdl_wait();
+  if (n >= N) return;
+  const long long d = domain[b];
+  const __nv_bfloat16* wd = w + size_t(d) * K * N + n;
+  const __nv_bfloat16* xb = x + (size_t(b) * T + t0) * K;
+  float acc[R] = {0.f, 0.f, 0.f, 0.f};
+  for (int k = 0; k < K; ++k) {
+    const float wv = bf2f(wd[size_t(k) * N]);
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+      if (t0 + r < T) acc[r] += wv * bf2f(xb[size_t(r) * K + k]);
+  }
+  const float bv = bf2f(bias[size_t(d) * N + n]);
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+    if (t0 + r < T) y[(size_t(b) * T + t0 + r) * N + n] = __float2bfloat16(acc[r] + bv);
+}
+cudaError_t domain_linear_launch(const __nv_bfloat16* x, const __nv_bfloat16* w, const __nv_bfloat16* bias, const long long* domain,
+                                 __nv_bfloat16* y, int B, int T, int K, int N, cudaStream_t s) {
+  if (B <= 0 || T <= 0 || N <= 0) return cudaSuccess;
+  const int threads = N >= 256 ? 256 : ((N + 31) / 32 * 32);
+  dim3 grid((N + threads - 1) / threads, (T + 3) / 4, B);
+  PB_LAUNCH(domain_linear_kernel, grid, threads, s, x, w, bias, domain, y, T, K, N);
+  return cudaGetLastError();
+}
+
 // ------------------------------------------------------------ UniPC sampler step
 // One multistep update of a flow-matching latent, element by element, with everything the host loop used to
 // issue as separate tensor ops: guidance combine, x0 prediction, corrector, predictor, history rotation and the

@@ -86,6 +86,10 @@ cudaError_t cfg_combine_launch(const __nv_bfloat16* cond, const __nv_bfloat16* u
 cudaError_t linear_simt_launch(const void* x, int x_type, const void* w, int w_type, const void* bias, void* y, int M, int N,
                                int K, int ldx, int ldw, int ldy, cudaStream_t s);
 
+// y[b, t, :] = x[b, t, :] @ W[domain[b]] + bias[domain[b]]; W is [domains][K][N], bias [domains][N], all bf16.
+cudaError_t domain_linear_launch(const __nv_bfloat16* x, const __nv_bfloat16* w, const __nv_bfloat16* bias, const long long* domain,
+                                 __nv_bfloat16* y, int B, int T, int K, int N, cudaStream_t s);
+
 // One UniPC (order <= 2, flow prediction) update of a latent viewed as [B][C][T][inner]:
 //   v = v_uncond + g (v - v_uncond)        when v_uncond is given
 //   m_t = x - sigma v;  x_s = c_x x_last + c_0 m1 + c_1 m2 + c_t m_t (has_corr) else x

@@ -281,6 +281,12 @@ def linear_simt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] =
     return ext().linear_simt(x, w, bias)
 
 
+def domain_linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor, domain: torch.Tensor) -> torch.Tensor:
+    """``x[b] @ W[domain[b]] + bias[domain[b]]`` for ``x`` (B, T, K) bf16, ``w`` (domains, K * N) in ``[K][N]`` order,
+    ``bias`` (domains, N), ``domain`` int64 (B,) on the device (read by the kernel: no host synchronisation)."""
+    return ext().domain_linear(x, w, bias, domain)
+
+
 def unipc_step(v: torch.Tensor, x: torch.Tensor, x_last: torch.Tensor, m1: torch.Tensor, m2: torch.Tensor, *, sigma: float,
                corr: Optional[tuple], pred: tuple, v_uncond: Optional[torch.Tensor] = None, g: float = 1.0,
                keep: Optional[torch.Tensor] = None, cond: Optional[torch.Tensor] = None, view: tuple[int, int, int] | None = None,

@@ -653,3 +653,20 @@ def test_gemm_second_output_with_column_factor(M, K, N):
     hb = h.float()                                   # the second output and the sums are taken from the stored (rounded) rows
     assert torch.allclose(out2.float(), hb * (1 + cs.float()), atol=1e-2 * float(hb.abs().max()), rtol=1e-2)
     assert torch.allclose(ss, hb.pow(2).sum(-1), rtol=1e-3, atol=1e-3)
+
+
+def test_domain_linear_matches_fp32():
+    """Per-sample weight selection by an on-device domain id (the embodiment-specific action projections of Cosmos3)."""
+    from phyai_b200 import ops
+
+    g = torch.Generator().manual_seed(11)
+    B, T, K, N, D = 3, 33, 64, 520, 5
+    x = torch.randn(B, T, K, generator=g).bfloat16().cuda()
+    w = (torch.randn(D, K * N, generator=g) * 0.1).bfloat16().cuda()
+    bias = torch.randn(D, N, generator=g).bfloat16().cuda()
+    dom = torch.tensor([4, 0, 2], dtype=torch.int64, device="cuda")
+    y = ops.domain_linear(x, w, bias, dom)
+    _status_ok()
+    want = torch.bmm(x.float(), w[dom].float().view(B, K, N)) + bias[dom].float()[:, None]
+    assert y.shape == (B, T, N)
+    assert torch.allclose(y.float(), want, atol=2e-2 * float(want.abs().max()), rtol=2e-2)
