@@ -121,6 +121,7 @@ class envs:
     PHYAI_PI05_PREFIX_SPLITS = EnvField("PHYAI_PI05_PREFIX_SPLITS", None, int)  # KV split of the prefix attention (default at batch 1: 4 from 896 prefix rows, else 2)
     PHYAI_PI05_OVERLAP = EnvField("PHYAI_PI05_OVERLAP", True, parse_bool)       # 0: no second stream (first Euler step after the prefix)
     PHYAI_COSMOS3_FP8 = EnvField("PHYAI_COSMOS3_FP8", False, parse_bool)        # 1: Cosmos3 generation tower in block-scaled fp8
+    PHYAI_COSMOS3_NVFP4 = EnvField("PHYAI_COSMOS3_NVFP4", False, parse_bool)    # 1: Cosmos3 generation tower in NVFP4 (one GPU; needs the _blockscaled module)
     PHYAI_COSMOS3_FUSED_SAMPLER = EnvField("PHYAI_COSMOS3_FUSED_SAMPLER", True, parse_bool)  # 0: UniPC update as host-issued tensor ops
     PHYAI_PI05_FP8 = EnvField("PHYAI_PI05_FP8", False, parse_bool)              # 1: Pi0.5 / Pi0 prefix decoder and action expert in block-scaled fp8
     PHYAI_PI05_TP_SCATTER_ROWS = EnvField("PHYAI_PI05_TP_SCATTER_ROWS", 512, int)  # prefix rows from which a 4+ rank Pi0.5 TP group reduce-scatters instead of pushing whole partials

@@ -212,6 +212,8 @@ class Cosmos3GenDecoderLayer(nn.Module):
         kbuf, vbuf = kv_buf
         if ws.fp8 is not None:
             return self._forward_fused_fp8(h, kv_buf, cos_sin, ws)
+        if ws.nvfp4 is not None:
+            return self._forward_fused_nvfp4(h, kv_buf, cos_sin, ws)
         ops.norm(h, "rms", weight=self.input_layernorm.weight, eps=cfg.rms_norm_eps, out=ws.x)
         ops.gemm(ws.x, ca.qkv_proj.weight, ws.qkv)
         ops.rope_kv(ws.qkv, Hq, Hkv, D, ws.q, cos_sin=cos_sin, q_norm_w=ca.norm_q.weight, k_norm_w=ca.norm_k.weight,
@@ -244,6 +246,61 @@ class Cosmos3GenDecoderLayer(nn.Module):
                  "gate_up": layer_weight_fp8(self.mlp.gate_up_proj), "down": layer_weight_fp8(self.mlp.down_proj)}
             self._w8 = w
         return w
+
+    #: global scale of the activations on the NVFP4 path: block scales (ue4m3) are taken relative to it, which puts block
+    #: maxima from 0.0015 to 336 inside their range
+    NVFP4_ACT_GLOBAL = 0.125
+
+    def _nvfp4_weights(self) -> dict:
+        """e2m1 weights of the four projections with ue4m3 scales per 16 inputs in the interleaved layout and one fp32
+        global scale each: taken from an NVFP4 checkpoint's layer as stored, else quantised once from bf16 by the same
+        kernel that quantises activations."""
+        w = getattr(self, "_w4", None)
+        if w is None:
+            from ...ops import nvfp4
+
+            def prep(layer):
+                if getattr(layer.spec, "spec_id", "") == "nvfp4_block_16":
+                    K = layer.weight.shape[1] * 2
+                    return layer.weight.data, nvfp4.swizzle_scales(layer.weight_scale.data, K), float(layer.weight_global_scale.item())
+                wt = layer.weight.data.to(torch.bfloat16)
+                g = max(float(wt.float().abs().amax().item()) / (6.0 * 448.0), 1e-12)
+                q, sf = nvfp4.quantize_activation(wt.contiguous(), g, cached=False)
+                return q, sf, g
+
+            ca = self.cross_attention
+            w = {"qkv": prep(ca.qkv_proj), "o": prep(ca.to_out), "gate_up": prep(self.mlp.gate_up_proj), "down": prep(self.mlp.down_proj)}
+            self._w4 = w
+        return w
+
+    def _forward_fused_nvfp4(self, h: torch.Tensor, kv_buf, cos_sin: torch.Tensor, ws: "GenWorkspace") -> torch.Tensor:
+        """The same layer with NVFP4 projections on the block-scaled tensor cores (reference: every linear of an NVFP4
+        checkpoint through ``nvfp4_quantize`` + ``mm_fp4``, layers/linear/backends/flashinfer.py:163-200). Activations are
+        quantised in front of each GEMM; the GEMM has no fused epilogue, so the residual add and the gated activation
+        are passes of their own. Single GPU."""
+        from ...ops import nvfp4
+
+        ca, cfg, W = self.cross_attention, self.cfg, self._nvfp4_weights()
+        S, ga = ws.S, self.NVFP4_ACT_GLOBAL
+        Hq, Hkv, D = ca.num_local_heads, ca.num_local_kv_heads, ca.head_dim
+        kbuf, vbuf = kv_buf
+
+        def lin(x, name, out):
+            q, sf = nvfp4.quantize_activation(x, ga)
+            w4, sfw, gw = W[name]
+            return nvfp4.gemm_nvfp4(q, sf, w4, sfw, ga * gw, out=out)
+
+        ops.norm(h, "rms", weight=self.input_layernorm.weight, eps=cfg.rms_norm_eps, out=ws.x)
+        lin(ws.x, "qkv", ws.qkv)
+        ops.rope_kv(ws.qkv, Hq, Hkv, D, ws.q, cos_sin=cos_sin, q_norm_w=ca.norm_q.weight, k_norm_w=ca.norm_k.weight,
+                    norm_eps=cfg.rms_norm_eps, k_pool=kbuf, v_pool=vbuf, slots=ws.slots)
+        ops.attention(ws.q.unflatten(1, (Hq, D)), kbuf, vbuf, ws.attn.unflatten(1, (Hq, D)), ws.q_start, ws.q_len,
+                      ws.kv_ptr, ws.kv_len, max_q_len=S, sm_scale=D ** -0.5)
+        ops.axpy(h, lin(ws.attn, "o", ws.part), 1.0)
+        ops.norm(h, "rms", weight=self.post_attention_layernorm.weight, eps=cfg.rms_norm_eps, out=ws.x)
+        ops.gated_act(lin(ws.x, "gate_up", ws.nvfp4["gu"]), self.mlp.activation, interleaved=True, out=ws.act)
+        ops.axpy(h, lin(ws.act, "down", ws.part), 1.0)
+        return h
 
     def _forward_fused_fp8(self, h: torch.Tensor, kv_buf, cos_sin: torch.Tensor, ws: "GenWorkspace") -> torch.Tensor:
         """The same layer with block-scaled fp8 projections (reference: every linear through
@@ -323,6 +380,7 @@ class GenWorkspace:
     kv_len: torch.Tensor
     stream: object | None = None   # PeerStream of the tensor-parallel group (None: single rank or NCCL fallback)
     fp8: dict | None = None        # block-scaled fp8 serving: e4m3 row buffers and 1 x 128 scales ("x", "attn", "act")
+    nvfp4: dict | None = None      # NVFP4 serving: the un-gated gate/up product ("gu")
 
 
 class Cosmos3LanguageModel(nn.Module):

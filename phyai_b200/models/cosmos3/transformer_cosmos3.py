@@ -55,6 +55,8 @@ class Cosmos3Transformer(nn.Module):
         # generation tower in block-scaled fp8 (e4m3 weights with 128 x 128 scales, activations per 1 x 128 block);
         # the peer-memory tensor-parallel layer is bf16 only, so fp8 + tp sums its row-parallel products over NCCL
         self.serve_fp8 = bool(envs.PHYAI_COSMOS3_FP8.get())
+        # generation tower in NVFP4 (e2m1 with ue4m3 scales per 16 inputs) on the block-scaled tensor cores; one GPU only
+        self.serve_nvfp4 = bool(envs.PHYAI_COSMOS3_NVFP4.get())
 
     @torch.no_grad()
     def init_random(self, seed: int = 0, std: float = 0.02) -> "Cosmos3Transformer":
@@ -179,6 +181,14 @@ class Cosmos3Transformer(nn.Module):
             for name, w in widths.items():
                 ws.fp8[name] = torch.empty(B * S, w, dtype=f8, device=device)
                 ws.fp8[name + "s"] = torch.empty(B * S, w // 128, dtype=f32, device=device)
+        if self.serve_nvfp4 and not self.serve_fp8:
+            from ...ops import nvfp4
+
+            if tp > 1 or not nvfp4.available():
+                raise RuntimeError("NVFP4 serving needs the phyai_b200._blockscaled module and a single tensor-parallel rank")
+            if cfg.hidden_size % 32 or (Hq * D) % 32 or self.gen_layers[0].mlp.down_proj.input_size_per_partition % 32:
+                raise ValueError("NVFP4 needs projection inputs that are multiples of 32")
+            ws.nvfp4 = {"gu": torch.empty(B * S, 2 * self.gen_layers[0].mlp.down_proj.input_size_per_partition, dtype=bf, device=device)}
         if tp > 1 and self.use_peer and not self.serve_fp8:
             from ...parallel.symm import PeerGroup
 

@@ -96,6 +96,38 @@ def test_fp8_block_gen_path_tracks_bf16(engine_cuda):
     assert (fp8_out - bf16_out).abs().max().item() > 0          # it is a different computation
 
 
+def test_nvfp4_gen_path_tracks_bf16(engine_cuda):
+    """The generation tower with NVFP4 projections on the block-scaled GEMM (weights and activations quantised by this
+    package's kernel) stays within four-bit noise of the bf16 fused path."""
+    from phyai_b200 import ops
+    from phyai_b200.models.cosmos3 import Cosmos3Transformer
+    from phyai_b200.ops import nvfp4
+
+    if not nvfp4.available():
+        pytest.skip("phyai_b200/_blockscaled is not built in this checkout")
+    cfg = small_real_config()
+    model = Cosmos3Transformer(cfg, params_dtype=torch.bfloat16, device="cuda").eval().init_random(2, std=0.05)
+    g = torch.Generator().manual_seed(1)
+    B, vs = 1, (3, 16, 24)
+    ids = torch.randint(0, 512, (B, 20), generator=g).cuda()
+    mask = torch.ones(B, 20, dtype=torch.long, device="cuda")
+    lat = torch.randn(B, 16, *vs, generator=g).cuda().bfloat16()
+    t = torch.full((B,), 500.0, device="cuda")
+    bf16_out = model(lat, t, model.encode_condition(ids, mask, vs, 24.0)).float()
+    model.serve_nvfp4 = True
+    out = model(lat, t, model.encode_condition(ids, mask, vs, 24.0)).float()
+    again = model(lat, t, model.encode_condition(ids, mask, vs, 24.0)).float()
+    torch.cuda.synchronize()
+    assert ops.kernel_status() == 0
+    assert model.gen_layers[0]._w4["qkv"][0].dtype == torch.uint8
+    scale = bf16_out.abs().max().item()
+    assert torch.isfinite(out).all() and torch.equal(out, again)
+    cos = torch.nn.functional.cosine_similarity(out.flatten(), bf16_out.flatten(), dim=0).item()
+    assert cos > 0.97, cos
+    assert (out - bf16_out).abs().mean().item() <= 0.08 * scale
+    assert (out - bf16_out).abs().max().item() > 0
+
+
 def test_policy_scheduler_and_vae_on_gpu(engine_cuda):
     from phyai_b200.models.cosmos3 import Cosmos3ActionRequest, Cosmos3PolicyScheduler, Cosmos3Transformer, Cosmos3WanVAEConfig
     from phyai_b200.models.cosmos3.vae_wan import Cosmos3WanVAE
