@@ -521,8 +521,10 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream, int* n_ctas) {
     return gemm_persist_launch(a, stream, n_ctas);
   }
 
-  // K split over a cluster when the tiles alone leave more than half of the SMs idle
-  const auto pick_splits = [](int ctas, int total_kb) {
+  // K split over a cluster when the tiles alone leave more than half of the SMs idle. Tiles of up to 128 columns keep
+  // their stages under 100 KB, so two CTAs fit on an SM: there one more doubling is taken while every CTA still gets
+  // four K blocks (50 x 1024 -> 8192: 9.8 -> 8.2 us with 256 CTAs instead of 128).
+  const auto pick_splits = [](int ctas, int total_kb, int bn) {
     int splits = 1;
     if (ctas * 2 <= num_sms()) {
       splits = 8;
@@ -533,6 +535,9 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream, int* n_ctas) {
       splits >>= 1;
       kbps = (total_kb + splits - 1) / splits;
     }
+    if (bn <= 128 && splits < 8 && ctas * 2 <= num_sms() && ctas * splits * 2 <= 2 * num_sms() && total_kb / (splits * 2) >= 4 &&
+        total_kb % (splits * 2) == 0)
+      splits *= 2;
     return splits;
   };
   int mid_splits = 0;      // > 0: K split chosen together with the tile width for mid-size problems
@@ -570,7 +575,7 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream, int* n_ctas) {
         long best = -1;
         for (int cand : {256, 192, 128}) {
           const int ctas_c = p_t * ((a.N + cand - 1) / cand);
-          const int sp = pick_splits(ctas_c, kb);
+          const int sp = pick_splits(ctas_c, kb, cand);
           const int waves = (ctas_c * sp + num_sms() - 1) / num_sms();
           const int per_kb = cand == 256 ? 512 : cand == 192 ? 427 : 341;
           const long cost = long(waves) * ((kb + sp - 1) / sp + (sp > 1 ? 3 : 1)) * per_kb;   // + fixed per-CTA work (cluster reduce when split)
@@ -588,7 +593,7 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream, int* n_ctas) {
   const int total_kb = (a.K + BK - 1) / BK;
   const int ctas = p_tiles * q_tiles;
 
-  int splits = a.force_splits > 0 ? a.force_splits : (mid_splits > 0 && !a.force_bn ? mid_splits : pick_splits(ctas, total_kb));
+  int splits = a.force_splits > 0 ? a.force_splits : (mid_splits > 0 && !a.force_bn ? mid_splits : pick_splits(ctas, total_kb, bn));
   int kbps = (total_kb + splits - 1) / splits;
   while (splits > 1 && (total_kb + kbps - 1) / kbps != splits) {
     splits >>= 1;
