@@ -244,10 +244,14 @@ void set_gemm_2cta(int mode) { g_2cta_mode = mode; }
 unsigned long long gemm_2cta_launches() { return g_2cta_launches; }
 
 bool gemm_2cta_eligible(const GemmArgs& a) {
-  // PHYAI_GEMM_2CTA=1 (or set_gemm_2cta(1)) routes large plain bf16 problems to the CTA-pair kernel
-  static const bool env_on = [] { const char* e = getenv("PHYAI_GEMM_2CTA"); return e && e[0] == '1'; }();
-  const bool on = g_2cta_mode < 0 ? env_on : g_2cta_mode > 0;
-  if (!on || a.push) return false;
+  // PHYAI_GEMM_2CTA=1 (or set_gemm_2cta(1)) routes every large plain bf16 problem to the CTA-pair kernel, 0 none.
+  // Unset: the shapes where it measured ahead of the persistent kernel inside a CUDA graph, i.e. very wide outputs
+  // (968 x 2048 -> 32768: 117.5 -> 111.4 us; 7040 x 5120 -> 27648: 1758 -> 1636 us) and long-K products of many rows
+  // (7040 x 13824 -> 5120: 818 -> 783 us); it was level or behind elsewhere (7040 x 5120 -> 7168: 417 -> 423 us).
+  static const int env_mode = [] { const char* e = getenv("PHYAI_GEMM_2CTA"); return !e || !e[0] ? -1 : (e[0] == '1' ? 1 : 0); }();
+  const int mode = g_2cta_mode < 0 ? env_mode : g_2cta_mode;
+  if (mode == 0 || a.push) return false;
+  if (mode < 0 && !(a.N >= 16384 || (a.K >= 8192 && a.N >= 4096 && a.M >= 4096))) return false;
   if (((a.M + kCM - 1) / kCM) * ((a.N + kCN - 1) / kCN) < sm_count() / 2) return false;
   return a.M >= 512 && a.N >= 2048 && a.K >= 256 && !a.fp8 && !a.out_fp32 && !a.rope &&
          !a.a_scale && !a.w_scale && !a.trace && a.force_bn == 0 && a.force_swap == -1 && a.force_splits == 0 &&

@@ -114,7 +114,7 @@ class envs:
     PHYAI_GEMM_PERSIST_COMM = EnvField("PHYAI_GEMM_PERSIST_COMM", True, parse_bool)  # 0: peer modes stay off the persistent kernel
     PHYAI_COMM_FUSED_TAIL = EnvField("PHYAI_COMM_FUSED_TAIL", True, parse_bool)  # 0: row-parallel products of few rows as two launches (push GEMM, reduce) instead of one
     PHYAI_GEMM_PERSIST_PUSH_WORLD = EnvField("PHYAI_GEMM_PERSIST_PUSH_WORLD", 2, int)  # largest group whose push / scatter GEMMs run persistent
-    PHYAI_GEMM_2CTA = EnvField("PHYAI_GEMM_2CTA", False, parse_bool)            # 1: CTA-pair (cta_group::2) kernel for large plain GEMMs
+    PHYAI_GEMM_2CTA = EnvField("PHYAI_GEMM_2CTA", None, parse_bool)             # CTA-pair (cta_group::2) GEMM: 1 every large plain problem, 0 never, unset: very wide / long-K shapes only
     PHYAI_NORM_TMA = EnvField("PHYAI_NORM_TMA", False, parse_bool)              # 1: many-row norms through bulk copies into shared memory
     PHYAI_ATTN_POLY = EnvField("PHYAI_ATTN_POLY", 0, int)                       # pipelined attention: 0..2 of every 4 exponentials on the FMA pipe
     PHYAI_PI05_EXPERT_SPLITS = EnvField("PHYAI_PI05_EXPERT_SPLITS", None, int)  # KV split of the expert's joint attention (default 8)
