@@ -560,16 +560,19 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream, int* n_ctas) {
       // operand ingest ((128 + width) x 128 bytes at about 96 bytes per cycle), so narrow tiles pay for
       // their lower arithmetic intensity.
       const int p_t = (a.M + kTileP - 1) / kTileP, kb = (a.K + BK - 1) / BK;
-      if (p_t <= 8 && a.K < 8192) {
+      if (p_t <= 8 && a.K < 8192 && !a.push) {
         // Up to about a thousand rows with a short or medium K (vision tower, prefix QKV / o-proj): measured sweep of
         // tile width x K split inside a CUDA graph. 128-wide tiles win throughout: their stages fit twice on an SM, so
         // up to 2 x 148 CTAs are resident at once, and where the tiles alone leave that under-filled K is split over a
         // cluster until they fill it (768 x 1152 -> 1152: 20.3 -> 10.1 us; 768 x 4304 -> 1152: 29.6 -> 16.7 us;
-        // 968 x 2048 -> 2048: 17.1 -> 14.1 us; the wide shapes gain 1.5-2 us from the narrower tile alone).
+        // 968 x 2048 -> 2048: 17.1 -> 14.1 us; the wide shapes gain 1.5-2 us from the narrower tile alone). Every split
+        // keeps at least eight K blocks. Products that leave through the peer epilogue keep the wave model below: on
+        // tensor-parallel shards (K of 512-4096 per rank, one arrival per CTA and rank) the extra CTAs cost more than
+        // they hide (a four-GPU request went from 15.9 to 16.3 ms with them).
         bn = 128;
         const int tiles = p_t * ((a.N + 127) / 128);
         int sp = 1;
-        while (sp < 8 && tiles * sp * 2 <= 2 * num_sms() && kb / (sp * 2) >= 4) sp *= 2;
+        while (sp < 8 && tiles * sp * 2 <= 2 * num_sms() && kb / (sp * 2) >= 8) sp *= 2;
         mid_splits = sp;
       } else {
         long best = -1;
