@@ -38,6 +38,15 @@ from .modeling_pi05 import PI05Model
 from .plan_pi05 import PI05Plan
 
 
+def split_cameras(n_cameras: int, world: int, rank: int) -> tuple[int, int, int]:
+    """``(per_rank, first, last)``: contiguous blocks of ``ceil(n / world)`` cameras per rank, in rank order, so that the
+    all-gather of equally sized (padded) blocks returns the cameras in their original order; ranks past the end get
+    an empty range."""
+    per = -(-n_cameras // world)
+    lo = min(rank * per, n_cameras)
+    return per, lo, min(lo + per, n_cameras)
+
+
 class PI05TPPlan(PI05Plan):
     tensor_parallel = True
     use_expert_kernel = False
@@ -69,9 +78,7 @@ class PI05TPPlan(PI05Plan):
 
         H = t.hidden_size
         rows = max(self.B * self.P, self.Me)
-        self.per = -(-n_all // self.tp)
-        self.img_lo = min(self.rank * self.per, n_all)
-        self.img_hi = min(self.img_lo + self.per, n_all)
+        self.per, self.img_lo, self.img_hi = split_cameras(n_all, self.tp, self.rank)
         img_rows = self.per * v.num_patches
         # prefix rows at or above the threshold go reduce-scatter -> norm -> all-gather (each rank sums and norms
         # only the rows it owns and every wire carries 1 / tp of the matrix twice, instead of the whole partial
@@ -210,4 +217,4 @@ class PI05TPPlan(PI05Plan):
 
 
 
-__all__ = ["PI05TPPlan"]
+__all__ = ["PI05TPPlan", "split_cameras"]

@@ -153,3 +153,41 @@ def test_engine_plugins_on_cpu(tmp_path):
     with pytest.raises(TypeError):
         from phyai_b200.models.pi05.main_pi05 import PI05Args
         Engine(EngineArgs("pi0", PI05Args(), ec))
+
+
+def test_tensor_parallel_camera_split_keeps_order_and_covers_all():
+    """The tensor-parallel Pi0.5 plan gives each rank a contiguous block of cameras; equal padded blocks gathered in rank
+    order must list every camera once, in order."""
+    from phyai_b200.models.pi05.plan_tp_pi05 import split_cameras
+
+    for n in (1, 2, 3, 4, 6, 9):
+        for world in (2, 3, 4, 8):
+            seen = []
+            for rank in range(world):
+                per, lo, hi = split_cameras(n, world, rank)
+                assert per == -(-n // world) and 0 <= lo <= hi <= n and hi - lo <= per
+                # position of camera g in the gathered (world * per)-block matrix is rank * per + (g - lo) == g
+                seen += [(rank * per + j, g) for j, g in enumerate(range(lo, hi))]
+            assert [g for _, g in seen] == list(range(n))
+            assert all(pos == g for pos, g in seen)
+
+
+def test_nvfp4_scale_layout_round_trip():
+    """The interleaved 128 x 4 scale layout of the NVFP4 GEMM: the PyTorch inverse used by the tests against a direct
+    statement of the forward map (checked on the GPU against the kernel, and at build time against the collective)."""
+    import torch
+
+    from phyai_b200.ops.nvfp4 import unswizzle_scales
+
+    rows, K = 300, 1056                      # neither a multiple of 128 rows nor of 64 columns
+    nkb, kbp = K // 16, (K + 63) // 64 * 4
+    total = (rows + 127) // 128 * 128 * kbp
+    flat = torch.zeros(total, dtype=torch.uint8)
+    src = torch.randint(1, 255, (rows, nkb), dtype=torch.uint8)
+    for r in range(rows):
+        for kb in range(nkb):
+            off = ((r // 128) * (kbp // 4) + kb // 4) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + kb % 4
+            assert flat[off] == 0            # the map is injective
+            flat[off] = src[r, kb]
+    back = unswizzle_scales(flat, rows, K).view(torch.uint8)
+    assert torch.equal(back, src)
