@@ -118,7 +118,7 @@ class envs:
     PHYAI_NORM_TMA = EnvField("PHYAI_NORM_TMA", False, parse_bool)              # 1: many-row norms through bulk copies into shared memory
     PHYAI_ATTN_POLY = EnvField("PHYAI_ATTN_POLY", 0, int)                       # pipelined attention: 0..2 of every 4 exponentials on the FMA pipe
     PHYAI_PI05_EXPERT_SPLITS = EnvField("PHYAI_PI05_EXPERT_SPLITS", None, int)  # KV split of the expert's joint attention (default 8)
-    PHYAI_PI05_PREFIX_SPLITS = EnvField("PHYAI_PI05_PREFIX_SPLITS", None, int)  # KV split of the prefix attention (default at batch 1: 4 from 896 prefix rows, else 2)
+    PHYAI_PI05_PREFIX_SPLITS = EnvField("PHYAI_PI05_PREFIX_SPLITS", None, int)  # KV split of the prefix attention (default: 2 at batch 1, 1 above; the tensor-parallel plan takes 4 from 896 prefix rows)
     PHYAI_PI05_OVERLAP = EnvField("PHYAI_PI05_OVERLAP", True, parse_bool)       # 0: no second stream (first Euler step after the prefix)
     PHYAI_COSMOS3_FP8 = EnvField("PHYAI_COSMOS3_FP8", False, parse_bool)        # 1: Cosmos3 generation tower in block-scaled fp8
     PHYAI_COSMOS3_NVFP4 = EnvField("PHYAI_COSMOS3_NVFP4", False, parse_bool)    # 1: Cosmos3 generation tower in NVFP4 (one GPU; needs the _blockscaled module)

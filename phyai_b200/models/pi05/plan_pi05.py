@@ -192,7 +192,8 @@ class PI05Plan:
         self.dt = -1.0 / cfg.num_inference_steps
         # KV splits of the attention calls (a cluster of that many CTAs per head and query tile)
         self.expert_splits = int(envs.PHYAI_PI05_EXPERT_SPLITS.get() or 8)
-        # batch 1: 4 for the long prompt bucket (968 rows: 17.48 vs 17.55 ms per request), 2 below (769 rows: 16.96 vs 17.03)
+        # batch 1: two KV splits at every prompt bucket (968 rows: 15.75 ms per request with 2, 15.90 with 4; the kernel
+        # alone, inside a graph: 30.6 / 39.2 us at 968 rows, 30.2 / 38.5 us at 816)
         self._prefix_splits_env = envs.PHYAI_PI05_PREFIX_SPLITS.get()
         self.prefix_splits = int(self._prefix_splits_env or (2 if B == 1 else 1))
         self._layout_key = None
@@ -388,8 +389,6 @@ class PI05Plan:
         cfg, t, lm = self.cfg, self.cfg.text, self.model.paligemma_lm
         n_per = self.img_tokens + lang_bucket
         Mp = self.B * n_per
-        if self.B == 1 and not self._prefix_splits_env:
-            self.prefix_splits = 4 if n_per >= 896 else 2
         h, x = self.p_h[:Mp], self.p_x[:Mp]
         # image rows: projector output lands directly in the packed prefix rows of each robot
         proj = self.model.vision.projector
