@@ -123,6 +123,7 @@ class envs:
     PHYAI_COSMOS3_FP8 = EnvField("PHYAI_COSMOS3_FP8", False, parse_bool)        # 1: Cosmos3 generation tower in block-scaled fp8
     PHYAI_COSMOS3_NVFP4 = EnvField("PHYAI_COSMOS3_NVFP4", False, parse_bool)    # 1: Cosmos3 generation tower in NVFP4 (one GPU; needs the _blockscaled module)
     PHYAI_COSMOS3_FUSED_SAMPLER = EnvField("PHYAI_COSMOS3_FUSED_SAMPLER", True, parse_bool)  # 0: UniPC update as host-issued tensor ops
+    PHYAI_COSMOS3_GRAPH = EnvField("PHYAI_COSMOS3_GRAPH", True, parse_bool)    # 0: every launch of a Cosmos3 denoise step from the host (default: one CUDA graph per request on a single GPU)
     PHYAI_PI05_FP8 = EnvField("PHYAI_PI05_FP8", False, parse_bool)              # 1: Pi0.5 / Pi0 prefix decoder and action expert in block-scaled fp8
     PHYAI_PI05_TP_SCATTER_ROWS = EnvField("PHYAI_PI05_TP_SCATTER_ROWS", 512, int)  # prefix rows from which a 4+ rank Pi0.5 TP group reduce-scatters instead of pushing whole partials
     PHYAI_PI05_EXPERT_KERNEL = EnvField("PHYAI_PI05_EXPERT_KERNEL", False, parse_bool)  # 1: Euler loop as one persistent kernel (measured slower than launch by launch at batch 1)

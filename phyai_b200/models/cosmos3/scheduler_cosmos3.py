@@ -8,6 +8,13 @@ unconditional) and the guided velocity is formed by the peer-memory CFG exchange
 all-gather over ``cfg``. With one rank per branch pair the branches run back to back. The
 transformer itself may be tensor parallel over ``tp``.
 
+On one GPU the branch passes of a denoise step are a CUDA graph (:class:`StepGraph`): the first step of a
+request runs launch by launch (it encodes the prompts and builds the K/V buffers), the second is captured, the
+rest replay it. What changes between steps stays outside the graph or in buffers it reads: the timestep in a
+one-element device buffer, the latents in the tensors the sampler kernel updates in place, the sampler kernel
+itself (its coefficients are launch arguments) after every replay. The reference issues every step eagerly
+(phyai/src/phyai/models/cosmos3/scheduler_ws1_cosmos3_policy.py:102-106 notes graph capture as open).
+
 Reference: phyai/src/phyai/models/cosmos3/scheduler_ws1_cosmos3.py:29-320,
 scheduler_wn_cosmos3.py:54-317, scheduler_ws1_cosmos3_policy.py:25-279,
 scheduler_wn_cosmos3_policy.py:50-303.
@@ -25,6 +32,7 @@ from ... import ops
 from ... import parallel as P
 from ...env import envs
 from ...runtime import Scheduler
+from ...runtime.cuda_graph_manager import CudaGraph
 from ...utils.profile import event_scope
 from .modeling_cosmos3 import Cosmos3Condition
 from .sampler_unipc import FusedUniPCStream, UniPCMultistepSampler
@@ -89,6 +97,42 @@ def seeded_normal(shape, seed: int, device, dtype) -> torch.Tensor:
     return torch.from_numpy(np.random.RandomState(int(seed)).standard_normal(shape).astype("float32")).to(device, dtype)
 
 
+class StepGraph:
+    """The model passes of one denoise step, captured once per request and replayed.
+
+    ``run(fn)``: the first call runs ``fn`` as it is (lazy state is built there), the second captures it into a
+    CUDA graph and replays it, later calls only replay. ``fn`` must read everything that changes between steps
+    from tensors whose storage stays put, and return tensors: they live in the graph's memory pool and are
+    overwritten by the next replay. A capture that fails (an op that cannot be captured) turns the graph off
+    for the rest of the request and runs ``fn`` eagerly; nothing the capture issued has executed by then."""
+
+    def __init__(self, enabled: bool) -> None:
+        self.enabled = bool(enabled)
+        self.graph: CudaGraph | None = None
+        self.calls = self.replays = 0
+        self.launches = 0        # kernels of this package in one replay (``ops.launch_counter`` sees the capture only)
+
+    def run(self, fn):
+        self.calls += 1
+        if not self.enabled or self.calls == 1:
+            return fn()
+        if self.graph is None:
+            graph = CudaGraph("cosmos3.step", warmup_iters=0)      # the eager first step was the warm-up
+            before = ops.launch_counter()
+            try:
+                graph.capture(fn, {})
+            except Exception as e:  # noqa: BLE001 - the request is served eagerly instead, and it is said out loud
+                import logging
+
+                logging.getLogger(__name__).warning("denoise step not captured (%s: %s): running it launch by launch",
+                                                    type(e).__name__, e)
+                self.enabled = False
+                return fn()
+            self.graph, self.launches = graph, ops.launch_counter() - before
+        self.replays += 1
+        return self.graph.replay()
+
+
 class Cosmos3Runner:
     """Holds the per-branch condition (encoded once per request) and runs the per-step GEN pass."""
 
@@ -118,6 +162,23 @@ class _GuidanceMixin:
 
     #: UniPC update, guidance combine and clean frames as one kernel per step on CUDA bf16 (PHYAI_COSMOS3_FUSED_SAMPLER=0: tensor ops)
     fused_sampler = bool(envs.PHYAI_COSMOS3_FUSED_SAMPLER.get())
+
+    #: branch passes of a step as one CUDA graph per request on a single GPU (PHYAI_COSMOS3_GRAPH=0: every launch from the host)
+    graph_steps = bool(envs.PHYAI_COSMOS3_GRAPH.get())
+    #: graph replays of the last request (0: it ran launch by launch) and the kernels of this package in one replay
+    last_graph_replays = 0
+    last_graph_launches = 0
+
+    def _step_graph(self, fused: bool) -> StepGraph:
+        """A graph for this request where its steps can be captured: the fused CUDA path of the transformer on one rank
+        (tensor-parallel and two-rank guidance steps hold peer-memory collectives whose launch arguments change per
+        call), the one-kernel sampler (the tensor-op one rebinds the latents), and graphs allowed by the engine."""
+        from ...engine_config import get_engine_config
+
+        tr = self.transformer
+        ok = (self.graph_steps and fused and self.device.type == "cuda" and tr.use_fused and self.cfg_size == 1
+              and tr.gen_layers[0].mlp.down_proj.tp_size == 1 and get_engine_config().runtime.use_cuda_graph)
+        return StepGraph(ok)
 
     def _init_guidance(self) -> None:
         mesh = P.default_mesh()
@@ -243,9 +304,11 @@ class Cosmos3T2VScheduler(_GuidanceMixin, Scheduler):
                                        cond=cond_latents if keep is not None else None)
             if with_sound:
                 fused_s = FusedUniPCStream(uni_s, sound)
+        graph = self._step_graph(fused_v is not None)
+        tval = torch.empty(1, device=dev, dtype=dt)      # one buffer for all steps: a captured step reads it
         with event_scope(scope):
             for timestep in uni_v.timesteps:
-                tval = timestep.to(dev).reshape(1).to(dt)
+                tval.copy_(timestep.reshape(1))
 
                 def run(branch: str):
                     ids, mask = prompts[branch]
@@ -255,7 +318,7 @@ class Cosmos3T2VScheduler(_GuidanceMixin, Scheduler):
                     return out if with_sound else (out,)
 
                 if fused_v is not None:
-                    vel, unc = self.guided_pair(run, request.guidance_scale, do_cfg)
+                    vel, unc = graph.run(lambda: self.guided_pair(run, request.guidance_scale, do_cfg))
                     fused_v.step(vel[0], uncond=None if unc is None else unc[0], g=request.guidance_scale)
                     if with_sound:
                         fused_s.step(vel[1], uncond=None if unc is None else unc[1], g=request.guidance_scale)
@@ -266,6 +329,7 @@ class Cosmos3T2VScheduler(_GuidanceMixin, Scheduler):
                     sound = uni_s.step(vel[1], timestep, sound)
                 if cond_latents is not None:
                     video[:, :, cond_idx] = cond_latents[:, :, cond_idx]
+        self.last_graph_replays, self.last_graph_launches = graph.replays, graph.launches
         if with_sound:
             return {"video": video, "sound": sound.transpose(1, 2).contiguous()}
         return video
@@ -367,9 +431,11 @@ class Cosmos3PolicyScheduler(_GuidanceMixin, Scheduler):
             fused_a = FusedUniPCStream(uni_a, action, view=(1, chunk, ad), live_inner=raw,
                                        keep=torch.ones(B, chunk, dtype=torch.bool, device=dev) if held else None,
                                        cond=action.clone() if held else None)
+        graph = self._step_graph(fused_v is not None)
+        tval = torch.empty(1, device=dev, dtype=dt)      # one buffer for all steps: a captured step reads it
         with event_scope("cosmos3.policy_denoise_loop"):
             for timestep in uni_v.timesteps:
-                tval = timestep.to(dev).reshape(1).to(dt)
+                tval.copy_(timestep.reshape(1))
 
                 def run(branch: str):
                     ids, mask = prompts[branch]
@@ -378,7 +444,7 @@ class Cosmos3PolicyScheduler(_GuidanceMixin, Scheduler):
                                                action_latents=action, action_domain_id=domain, action_noisy_mask=amask)
 
                 if fused_v is not None:
-                    vel, unc = self.guided_pair(run, request.guidance_scale, do_cfg)
+                    vel, unc = graph.run(lambda: self.guided_pair(run, request.guidance_scale, do_cfg))
                     fused_v.step(vel[0], uncond=None if unc is None else unc[0], g=request.guidance_scale)
                     fused_a.step(vel[1], uncond=None if unc is None else unc[1], g=request.guidance_scale)
                     continue
@@ -392,6 +458,7 @@ class Cosmos3PolicyScheduler(_GuidanceMixin, Scheduler):
                 if action_clean and cond_action is not None:
                     action = cond_action.to(action.dtype).clone()
                     action[:, :, raw:] = 0.0
+        self.last_graph_replays, self.last_graph_launches = graph.replays, graph.launches
         out = {"video": video, "action": action[:, :, :raw]}
         if decode_video:
             if self.vae is None:
@@ -407,5 +474,5 @@ Cosmos3T2VWNScheduler = Cosmos3T2VScheduler
 Cosmos3PolicyWNScheduler = Cosmos3PolicyScheduler
 
 __all__ = ["Cosmos3T2VRequest", "Cosmos3ActionRequest", "ACTION_MODES", "pixel_to_latent_shape", "seeded_normal",
-           "Cosmos3Runner", "Cosmos3T2VScheduler", "Cosmos3PolicyScheduler", "Cosmos3T2VWNScheduler",
+           "Cosmos3Runner", "StepGraph", "Cosmos3T2VScheduler", "Cosmos3PolicyScheduler", "Cosmos3T2VWNScheduler",
            "Cosmos3PolicyWNScheduler"]

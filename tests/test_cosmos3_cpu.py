@@ -182,3 +182,30 @@ def test_policy_plugin_modes(mode):
     with pytest.raises(ValueError):
         eng.entry.scheduler.step(Cosmos3ActionRequest(ids, mask, ids, mask, (2, 4, 6), "dream", 0, 3, 5, 8))
     eng.close()
+
+
+def test_step_graph_first_call_eager_and_capture_failure_falls_back(caplog):
+    """StepGraph: off -> every call runs the function; on -> the first call is eager, and a capture that cannot be
+    made (no CUDA device here) is reported once and the step runs launch by launch from then on."""
+    from phyai_b200.models.cosmos3.scheduler_cosmos3 import StepGraph
+
+    calls = []
+
+    def fn():
+        calls.append(1)
+        return (torch.ones(2),)
+
+    off = StepGraph(False)
+    for _ in range(3):
+        assert off.run(fn)[0].sum() == 2
+    assert len(calls) == 3 and off.replays == 0
+    calls.clear()
+    on = StepGraph(True)
+    on.run(fn)
+    assert on.enabled and len(calls) == 1
+    with caplog.at_level("WARNING"):
+        out = on.run(fn)
+    assert out[0].sum() == 2 and not on.enabled and on.replays == 0 and on.graph is None
+    assert any("not captured" in r.message for r in caplog.records)
+    on.run(fn)
+    assert len(calls) == 3

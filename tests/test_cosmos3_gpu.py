@@ -195,3 +195,45 @@ def test_fused_sampler_matches_tensor_op_sampler(engine_cuda, mode, monkeypatch)
         assert torch.isfinite(a).all()
         scale = b.abs().mean().item()
         assert (a - b).abs().mean().item() <= 0.03 * scale, ((a - b).abs().mean().item(), scale)
+
+
+@pytest.mark.parametrize("mode", ["t2v", "t2v_sound", "policy"])
+def test_step_graph_matches_launch_by_launch(engine_cuda, mode, monkeypatch):
+    """A request whose steps replay one CUDA graph (captured at its second step) against the same request issued launch
+    by launch: same kernels on the same buffers, so the latents are equal bit for bit."""
+    from phyai_b200 import ops
+    from phyai_b200.models.cosmos3 import (Cosmos3ActionRequest, Cosmos3PolicyScheduler, Cosmos3T2VRequest, Cosmos3T2VScheduler,
+                                           Cosmos3Transformer)
+
+    policy = mode == "policy"
+    cfg = small_real_config(action_gen=policy, sound_gen=mode == "t2v_sound")
+    model = Cosmos3Transformer(cfg, params_dtype=torch.bfloat16, device="cuda").eval().init_random(2, std=0.05)
+    g = torch.Generator().manual_seed(0)
+    ids, nids = torch.randint(0, 512, (1, 20), generator=g), torch.randint(0, 512, (1, 20), generator=g)
+    mask = torch.ones(1, 20, dtype=torch.long)
+    steps, outs = 5, []
+    for graphed in (True, False, True):
+        if policy:
+            sch = Cosmos3PolicyScheduler(model, device="cuda")
+            monkeypatch.setattr(sch, "graph_steps", graphed, raising=False)
+            sch.setup()
+            req = Cosmos3ActionRequest(ids, mask, nids, mask, video_shape=(2, 16, 24), mode="policy", domain_id=1, action_chunk=8,
+                                       raw_action_dim=7, action_dim=32, num_inference_steps=steps, guidance_scale=3.0,
+                                       cond_video_latents=torch.randn(1, 16, 2, 16, 24, generator=torch.Generator().manual_seed(1)))
+            out = sch.step(req)
+            outs.append((out["video"].clone(), out["action"].clone()))
+        else:
+            sch = Cosmos3T2VScheduler(model, device="cuda")
+            monkeypatch.setattr(sch, "graph_steps", graphed, raising=False)
+            sch.setup()
+            kw = dict(sound_frames=10, sound_dim=16, sound_latent_fps=25.0) if mode == "t2v_sound" else {}
+            req = Cosmos3T2VRequest(ids, mask, nids, mask, video_shape=(3, 16, 24), num_inference_steps=steps, guidance_scale=4.0, **kw)
+            out = sch.step(req)
+            outs.append((out["video"].clone(), out["sound"].clone()) if isinstance(out, dict) else (out.clone(),))
+        # the first step is eager, the second is captured and replayed, the rest replay
+        assert sch.last_graph_replays == (steps - 1 if graphed else 0)
+    torch.cuda.synchronize()
+    assert ops.kernel_status() == 0
+    for a, b, c in zip(*outs):
+        assert torch.isfinite(a.float()).all()
+        assert torch.equal(a, b) and torch.equal(a, c)
