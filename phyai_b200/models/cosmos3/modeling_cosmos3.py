@@ -415,6 +415,25 @@ class Cosmos3Condition:
     sound_len: int = 0
     fused: dict = field(default_factory=dict)    # lazily built buffers of the CUDA path
 
+    def refresh_from(self, new: "Cosmos3Condition") -> None:
+        """Take over another prompt of the same geometry in place: the rotary table and the text K/V rows of the
+        CUDA path's buffers are overwritten where they are, so that a captured step which reads them serves the
+        new prompt. A different text length or latent geometry is refused (it needs buffers of its own)."""
+        same = (new.video_shape == self.video_shape and new.action_len == self.action_len and new.sound_len == self.sound_len
+                and new.freqs_gen.shape == self.freqs_gen.shape and len(new.cached_kv) == len(self.cached_kv)
+                and new.cached_kv[0][0].shape == self.cached_kv[0][0].shape)
+        if not same:
+            raise ValueError("refresh_from needs a condition of the same text length and latent geometry")
+        self.freqs_gen.copy_(new.freqs_gen)
+        for (k_old, v_old), (k_new, v_new) in zip(self.cached_kv, new.cached_kv):
+            k_old.copy_(k_new)
+            v_old.copy_(v_new)
+        for _, bufs in self.fused.values():
+            for (kb, vb), (k_new, v_new) in zip(bufs, new.cached_kv):
+                B, s_text, Hkv, D = k_new.shape
+                kb.view(B, -1, Hkv, D)[:, :s_text].copy_(k_new)
+                vb.view(B, -1, Hkv, D)[:, :s_text].copy_(v_new)
+
 
 __all__ = ["compute_mrope_position_ids_text", "compute_mrope_position_ids_vision", "local_head_counts",
            "TimestepEmbedder", "DomainAwareLinear", "Cosmos3Attention", "Cosmos3UndDecoderLayer",

@@ -8,12 +8,14 @@ unconditional) and the guided velocity is formed by the peer-memory CFG exchange
 all-gather over ``cfg``. With one rank per branch pair the branches run back to back. The
 transformer itself may be tensor parallel over ``tp``.
 
-On one GPU the branch passes of a denoise step are a CUDA graph (:class:`StepGraph`): the first step of a
-request runs launch by launch (it encodes the prompts and builds the K/V buffers), the second is captured, the
-rest replay it. What changes between steps stays outside the graph or in buffers it reads: the timestep in a
-one-element device buffer, the latents in the tensors the sampler kernel updates in place, the sampler kernel
-itself (its coefficients are launch arguments) after every replay. The reference issues every step eagerly
-(phyai/src/phyai/models/cosmos3/scheduler_ws1_cosmos3_policy.py:102-106 notes graph capture as open).
+On one GPU the branch passes of a denoise step are a CUDA graph kept per request geometry (:class:`LoopSlot`,
+:class:`StepGraph`): the first step of the first request of a geometry runs launch by launch (it builds the
+workspaces and K/V buffers), the second is captured, and every later step, of that request and of the following
+ones, replays it. What changes between steps or requests stays outside the graph or in buffers it reads: the
+timestep in a one-element device buffer, the latents, masks and domain ids in tensors of the slot that a request
+copies its values into, the prompt in the slot's conditions (text K/V and rotary table overwritten in place), the
+sampler kernel (its coefficients are launch arguments) after every replay. The reference issues every step
+eagerly (phyai/src/phyai/models/cosmos3/scheduler_ws1_cosmos3_policy.py:102-106 notes graph capture as open).
 
 Reference: phyai/src/phyai/models/cosmos3/scheduler_ws1_cosmos3.py:29-320,
 scheduler_wn_cosmos3.py:54-317, scheduler_ws1_cosmos3_policy.py:25-279,
@@ -98,13 +100,13 @@ def seeded_normal(shape, seed: int, device, dtype) -> torch.Tensor:
 
 
 class StepGraph:
-    """The model passes of one denoise step, captured once per request and replayed.
+    """The model passes of one denoise step, captured once and replayed.
 
     ``run(fn)``: the first call runs ``fn`` as it is (lazy state is built there), the second captures it into a
     CUDA graph and replays it, later calls only replay. ``fn`` must read everything that changes between steps
     from tensors whose storage stays put, and return tensors: they live in the graph's memory pool and are
     overwritten by the next replay. A capture that fails (an op that cannot be captured) turns the graph off
-    for the rest of the request and runs ``fn`` eagerly; nothing the capture issued has executed by then."""
+    for good and runs ``fn`` eagerly; nothing the capture issued has executed by then."""
 
     def __init__(self, enabled: bool) -> None:
         self.enabled = bool(enabled)
@@ -133,25 +135,73 @@ class StepGraph:
         return self.graph.replay()
 
 
+@dataclass
+class LoopSlot:
+    """Device state of one request geometry that outlives the request, so that one captured step serves all of them:
+    the tensors a step reads (latents, masks, timestep, domain ids), the conditions of the guidance branches with the
+    buffers of the CUDA path inside them, and the graph."""
+
+    graph: StepGraph
+    tensors: dict[str, torch.Tensor] = dataclasses.field(default_factory=dict)
+    conds: dict[str, Cosmos3Condition] = dataclasses.field(default_factory=dict)
+    opened_at: tuple[int, bool] = (0, False)       # replays so far and "already captured" when the current request began
+
+    @property
+    def persistent(self) -> bool:
+        return self.graph.enabled
+
+    def hold(self, name: str, value: torch.Tensor | None) -> torch.Tensor | None:
+        """The slot's tensor ``name`` with the values of ``value`` (a slot without a graph hands ``value`` through)."""
+        if value is None or not self.persistent:
+            return value
+        cur = self.tensors.get(name)
+        if cur is None:
+            cur = self.tensors[name] = value.contiguous().clone()
+        else:
+            cur.copy_(value)
+        return cur
+
+
+def real_text_len(mask: torch.Tensor) -> int:
+    """Longest unpadded prompt of a batch: the text rows a condition keeps."""
+    return int(mask.sum(dim=1).max().item())
+
+
 class Cosmos3Runner:
     """Holds the per-branch condition (encoded once per request) and runs the per-step GEN pass."""
 
     def __init__(self, transformer: Cosmos3Transformer) -> None:
         self.transformer = transformer
         self._cond: dict[str, Cosmos3Condition] = {}
+        self._held: dict[str, Cosmos3Condition] | None = None
 
-    def reset(self) -> None:
+    def reset(self, held: dict[str, Cosmos3Condition] | None = None) -> None:
+        """Forget the last request's prompts. ``held``: conditions that a captured step reads; a new prompt is written
+        into them in place instead of replacing them."""
         self._cond.clear()
+        self._held = held
+
+    def prepare(self, branch: str, *, text_ids, text_mask, video_shape, fps, action_len: int = 0, sound_len: int = 0,
+                sound_fps=None) -> Cosmos3Condition:
+        c = self.transformer.encode_condition(text_ids, text_mask, video_shape, fps, action_len=action_len,
+                                              sound_len=sound_len, sound_fps=sound_fps)
+        if self._held is not None:
+            kept = self._held.get(branch)
+            if kept is None:
+                self._held[branch] = c
+            else:
+                kept.refresh_from(c)
+                c = kept
+        self._cond[branch] = c
+        return c
 
     def forward(self, branch: str, video, t, *, text_ids, text_mask, video_shape, fps, noisy_frame_mask=None,
                 action_latents=None, action_domain_id=None, action_noisy_mask=None, sound_latents=None, sound_fps=None):
         c = self._cond.get(branch)
         if c is None:
-            c = self.transformer.encode_condition(
-                text_ids, text_mask, video_shape, fps,
-                action_len=0 if action_latents is None else action_latents.shape[1],
-                sound_len=0 if sound_latents is None else sound_latents.shape[1], sound_fps=sound_fps)
-            self._cond[branch] = c
+            c = self.prepare(branch, text_ids=text_ids, text_mask=text_mask, video_shape=video_shape, fps=fps,
+                             action_len=0 if action_latents is None else action_latents.shape[1],
+                             sound_len=0 if sound_latents is None else sound_latents.shape[1], sound_fps=sound_fps)
         return self.transformer(video, t.expand(video.shape[0]), c, noisy_frame_mask=noisy_frame_mask,
                                 action_latents=action_latents, action_domain_id=action_domain_id,
                                 action_noisy_mask=action_noisy_mask, sound_latents=sound_latents)
@@ -163,22 +213,57 @@ class _GuidanceMixin:
     #: UniPC update, guidance combine and clean frames as one kernel per step on CUDA bf16 (PHYAI_COSMOS3_FUSED_SAMPLER=0: tensor ops)
     fused_sampler = bool(envs.PHYAI_COSMOS3_FUSED_SAMPLER.get())
 
-    #: branch passes of a step as one CUDA graph per request on a single GPU (PHYAI_COSMOS3_GRAPH=0: every launch from the host)
+    #: branch passes of a step as one CUDA graph per request geometry on a single GPU (PHYAI_COSMOS3_GRAPH=0: every launch from the host)
     graph_steps = bool(envs.PHYAI_COSMOS3_GRAPH.get())
-    #: graph replays of the last request (0: it ran launch by launch) and the kernels of this package in one replay
+    #: request geometries whose buffers and graph are kept (least recently used goes first)
+    max_loop_slots = 2
+    #: graph replays of the last request (0: it ran launch by launch), and how many kernels of this package those replays
+    #: ran that ``ops.launch_counter`` did not see (it counts a capture once and no replay)
     last_graph_replays = 0
-    last_graph_launches = 0
+    last_graph_uncounted = 0
 
-    def _step_graph(self, fused: bool) -> StepGraph:
-        """A graph for this request where its steps can be captured: the fused CUDA path of the transformer on one rank
+    def _graphable(self, fused: bool) -> bool:
+        """Whether the steps of a request can be captured: the fused CUDA path of the transformer on one rank
         (tensor-parallel and two-rank guidance steps hold peer-memory collectives whose launch arguments change per
         call), the one-kernel sampler (the tensor-op one rebinds the latents), and graphs allowed by the engine."""
         from ...engine_config import get_engine_config
 
         tr = self.transformer
-        ok = (self.graph_steps and fused and self.device.type == "cuda" and tr.use_fused and self.cfg_size == 1
-              and tr.gen_layers[0].mlp.down_proj.tp_size == 1 and get_engine_config().runtime.use_cuda_graph)
-        return StepGraph(ok)
+        return bool(self.graph_steps and fused and self.device.type == "cuda" and tr.use_fused and self.cfg_size == 1
+                    and tr.gen_layers[0].mlp.down_proj.tp_size == 1 and get_engine_config().runtime.use_cuda_graph)
+
+    def _loop_slot(self, signature: tuple, fused: bool) -> LoopSlot:
+        """The kept slot of this request geometry where its steps can be captured, else a throw-away slot that keeps
+        nothing."""
+        tr = self.transformer
+        if not self._graphable(fused):
+            return LoopSlot(StepGraph(False))
+        slots = self.__dict__.setdefault("_loop_slots", {})
+        key = (signature, bool(tr.serve_fp8), bool(tr.serve_nvfp4))
+        slot = slots.pop(key, None)
+        if slot is None:
+            slot = LoopSlot(StepGraph(True))
+            while len(slots) >= self.max_loop_slots:
+                slots.pop(next(iter(slots)))
+        slots[key] = slot                      # most recently used last
+        slot.opened_at = (slot.graph.replays, slot.graph.graph is not None)
+        return slot
+
+    def _close_slot(self, slot: LoopSlot) -> None:
+        """Book-keeping after the loop of a request."""
+        g = slot.graph
+        replays0, captured0 = slot.opened_at
+        self.last_graph_replays = g.replays - replays0
+        captured_now = g.graph is not None and not captured0
+        self.last_graph_uncounted = max(self.last_graph_replays - (1 if captured_now else 0), 0) * g.launches
+
+    def drop_loop_slots(self) -> None:
+        """Free the kept request geometries (their buffers and graphs)."""
+        self.__dict__.pop("_loop_slots", None)
+
+    def close(self) -> None:
+        self.drop_loop_slots()
+        super().close()
 
     def _init_guidance(self) -> None:
         mesh = P.default_mesh()
@@ -293,10 +378,20 @@ class Cosmos3T2VScheduler(_GuidanceMixin, Scheduler):
         sfps = request.sound_latent_fps if with_sound else None
         uni_v = self._new_sampler(request.num_inference_steps)
         uni_s = self._new_sampler(request.num_inference_steps) if with_sound else None
-        self.runner.reset()
         scope = "cosmos3.t2av_denoise_loop" if with_sound else "cosmos3.denoise_loop"
+        fused = self.fused_sampler and FusedUniPCStream.usable(video)
+        branches = ("cond", "uncond") if do_cfg else ("cond",)
+        slot = self._loop_slot(("t2v", tuple(video.shape), None if sound is None else tuple(sound.shape), frame_mask is not None,
+                                tuple(real_text_len(prompts[b][1]) for b in branches)), fused)
+        self.runner.reset(slot.conds if slot.persistent else None)
+        if slot.persistent:
+            # a captured step reads the slot's tensors and conditions: this request's values go into them
+            video, sound, frame_mask = slot.hold("video", video), slot.hold("sound", sound), slot.hold("frame_mask", frame_mask)
+            for b in branches:
+                self.runner.prepare(b, text_ids=prompts[b][0], text_mask=prompts[b][1], video_shape=request.video_shape,
+                                    fps=request.fps, sound_len=0 if sound is None else sound.shape[1], sound_fps=sfps)
         fused_v = fused_s = None
-        if self.fused_sampler and FusedUniPCStream.usable(video):
+        if fused:
             # one kernel per stream and step: guidance combine, UniPC update and the clean frames in one pass
             video = video.contiguous()
             keep = None if frame_mask is None else ~frame_mask
@@ -304,8 +399,8 @@ class Cosmos3T2VScheduler(_GuidanceMixin, Scheduler):
                                        cond=cond_latents if keep is not None else None)
             if with_sound:
                 fused_s = FusedUniPCStream(uni_s, sound)
-        graph = self._step_graph(fused_v is not None)
-        tval = torch.empty(1, device=dev, dtype=dt)      # one buffer for all steps: a captured step reads it
+        graph = slot.graph
+        tval = slot.hold("tval", torch.empty(1, device=dev, dtype=dt))      # one buffer for all steps: a captured step reads it
         with event_scope(scope):
             for timestep in uni_v.timesteps:
                 tval.copy_(timestep.reshape(1))
@@ -329,7 +424,9 @@ class Cosmos3T2VScheduler(_GuidanceMixin, Scheduler):
                     sound = uni_s.step(vel[1], timestep, sound)
                 if cond_latents is not None:
                     video[:, :, cond_idx] = cond_latents[:, :, cond_idx]
-        self.last_graph_replays, self.last_graph_launches = graph.replays, graph.launches
+        self._close_slot(slot)
+        if slot.tensors:
+            video = video.clone()              # the slot's tensor is overwritten by the next request
         if with_sound:
             return {"video": video, "sound": sound.transpose(1, 2).contiguous()}
         return video
@@ -421,9 +518,20 @@ class Cosmos3PolicyScheduler(_GuidanceMixin, Scheduler):
         uni_v, uni_a = mk(), mk()
         uni_v.set_timesteps(request.num_inference_steps, device=dev)
         uni_a.set_timesteps(request.num_inference_steps, device=dev)
-        self.runner.reset()
+        fused = self.fused_sampler and FusedUniPCStream.usable(video)
+        branches = ("cond", "uncond") if do_cfg else ("cond",)
+        slot = self._loop_slot(("action", tuple(video.shape), tuple(action.shape),
+                                tuple(real_text_len(prompts[b][1]) for b in branches)), fused)
+        self.runner.reset(slot.conds if slot.persistent else None)
+        if slot.persistent:
+            # a captured step reads the slot's tensors and conditions: this request's values go into them
+            video, action, domain = slot.hold("video", video), slot.hold("action", action), slot.hold("domain", domain)
+            vmask, amask = slot.hold("vmask", vmask), slot.hold("amask", amask)
+            for b in branches:
+                self.runner.prepare(b, text_ids=prompts[b][0], text_mask=prompts[b][1], video_shape=request.video_shape,
+                                    fps=request.fps, action_len=chunk)
         fused_v = fused_a = None
-        if self.fused_sampler and FusedUniPCStream.usable(video):
+        if fused:
             video, action = video.contiguous(), action.contiguous()
             fused_v = FusedUniPCStream(uni_v, video, view=(video.shape[1], t_lat, h_lat * w_lat),
                                        keep=None if cond_video is None else ~vmask, cond=cond_video)
@@ -431,8 +539,8 @@ class Cosmos3PolicyScheduler(_GuidanceMixin, Scheduler):
             fused_a = FusedUniPCStream(uni_a, action, view=(1, chunk, ad), live_inner=raw,
                                        keep=torch.ones(B, chunk, dtype=torch.bool, device=dev) if held else None,
                                        cond=action.clone() if held else None)
-        graph = self._step_graph(fused_v is not None)
-        tval = torch.empty(1, device=dev, dtype=dt)      # one buffer for all steps: a captured step reads it
+        graph = slot.graph
+        tval = slot.hold("tval", torch.empty(1, device=dev, dtype=dt))      # one buffer for all steps: a captured step reads it
         with event_scope("cosmos3.policy_denoise_loop"):
             for timestep in uni_v.timesteps:
                 tval.copy_(timestep.reshape(1))
@@ -458,7 +566,9 @@ class Cosmos3PolicyScheduler(_GuidanceMixin, Scheduler):
                 if action_clean and cond_action is not None:
                     action = cond_action.to(action.dtype).clone()
                     action[:, :, raw:] = 0.0
-        self.last_graph_replays, self.last_graph_launches = graph.replays, graph.launches
+        self._close_slot(slot)
+        if slot.tensors:
+            video, action = video.clone(), action.clone()      # the slot's tensors are overwritten by the next request
         out = {"video": video, "action": action[:, :, :raw]}
         if decode_video:
             if self.vae is None:
@@ -474,5 +584,5 @@ Cosmos3T2VWNScheduler = Cosmos3T2VScheduler
 Cosmos3PolicyWNScheduler = Cosmos3PolicyScheduler
 
 __all__ = ["Cosmos3T2VRequest", "Cosmos3ActionRequest", "ACTION_MODES", "pixel_to_latent_shape", "seeded_normal",
-           "Cosmos3Runner", "StepGraph", "Cosmos3T2VScheduler", "Cosmos3PolicyScheduler", "Cosmos3T2VWNScheduler",
+           "Cosmos3Runner", "StepGraph", "LoopSlot", "Cosmos3T2VScheduler", "Cosmos3PolicyScheduler", "Cosmos3T2VWNScheduler",
            "Cosmos3PolicyWNScheduler"]

@@ -209,3 +209,57 @@ def test_step_graph_first_call_eager_and_capture_failure_falls_back(caplog):
     assert any("not captured" in r.message for r in caplog.records)
     on.run(fn)
     assert len(calls) == 3
+
+
+@pytest.mark.parametrize("kind", ["t2v", "policy"])
+def test_loop_slot_serves_later_requests_from_kept_buffers(kind, monkeypatch):
+    """The request-geometry slot on CPU (the step function itself runs eagerly here: the tensor-op sampler never goes
+    through the graph): a second request with another prompt, noise and masks, written into the slot's tensors and
+    conditions in place, gives what a scheduler without slots gives; results handed out earlier are not overwritten;
+    a prompt of another length gets a slot of its own and the oldest slot is dropped."""
+    from phyai_b200.engine import Engine, EngineArgs
+    from phyai_b200.models.cosmos3 import scheduler_cosmos3 as sc
+    from phyai_b200.models.cosmos3.main_cosmos3 import Cosmos3Args
+    from phyai_b200.models.cosmos3.main_cosmos3_policy import Cosmos3PolicyArgs
+
+    policy = kind == "policy"
+    cfg = tiny_cosmos3_config(action_gen=policy)
+    args = Cosmos3PolicyArgs(config=cfg) if policy else Cosmos3Args(config=cfg, load_vae=False, load_sound=False)
+    eng = Engine(EngineArgs("cosmos3_policy" if policy else "cosmos3", args, CPU_ENGINE()))
+    sch = eng.entry.scheduler
+
+    def request(seed: int, text_len: int = 6):
+        g = torch.Generator().manual_seed(seed)
+        ids = torch.randint(0, cfg.vocab_size, (1, 8), generator=g)
+        nids = torch.randint(0, cfg.vocab_size, (1, 8), generator=g)
+        mask = torch.zeros(1, 8, dtype=torch.long)
+        mask[:, :text_len] = 1
+        if policy:
+            return Cosmos3ActionRequest(ids, mask, nids, mask, video_shape=(2, 4, 6), mode="policy", domain_id=seed % 3, action_chunk=3,
+                                        raw_action_dim=5, action_dim=8, cond_video_latents=torch.randn(1, 4, 2, 4, 6, generator=g),
+                                        num_inference_steps=3, guidance_scale=2.0, seed=seed)
+        return Cosmos3T2VRequest(ids, mask, nids, mask, video_shape=(3, 4, 6), num_inference_steps=3, guidance_scale=2.0,
+                                 cond_latents=torch.randn(1, 4, 3, 4, 6, generator=g), cond_frame_indexes=(seed % 3,), seed=seed)
+
+    def tensors(out):
+        return [out["video"], out["action"]] if isinstance(out, dict) else [out]
+
+    want = [tensors(sch.step(request(s, n))) for s, n in ((1, 6), (2, 6), (3, 5), (4, 7))]
+    assert sch.last_graph_replays == 0 and "_loop_slots" not in sch.__dict__
+
+    monkeypatch.setattr(sch, "_graphable", lambda fused: True)
+    got = [tensors(sch.step(request(1, 6)))]
+    got.append(tensors(sch.step(request(2, 6))))           # same geometry: served from the slot of the first
+    assert len(sch._loop_slots) == 1
+    slot = next(iter(sch._loop_slots.values()))
+    assert set(slot.conds) == {"cond", "uncond"} and "video" in slot.tensors and "tval" in slot.tensors
+    got.append(tensors(sch.step(request(3, 5))))           # another prompt length: a second slot
+    assert len(sch._loop_slots) == 2
+    got.append(tensors(sch.step(request(4, 7))))           # a third: the least recently used one goes
+    assert len(sch._loop_slots) == 2 and slot not in sch._loop_slots.values()
+    for a, b in zip(got, want):
+        for x, y in zip(a, b):
+            assert torch.equal(x, y)
+    sch.drop_loop_slots()
+    assert "_loop_slots" not in sch.__dict__
+    eng.close()

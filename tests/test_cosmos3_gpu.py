@@ -237,3 +237,51 @@ def test_step_graph_matches_launch_by_launch(engine_cuda, mode, monkeypatch):
     for a, b, c in zip(*outs):
         assert torch.isfinite(a.float()).all()
         assert torch.equal(a, b) and torch.equal(a, c)
+
+
+@pytest.mark.parametrize("mode", ["t2v_cond_frames", "policy"])
+def test_step_graph_serves_following_requests(engine_cuda, mode, monkeypatch):
+    """One scheduler, three requests of one geometry with different prompts, noise, clean frames and domain: from the
+    second request on every step is a replay of the graph captured in the first, reading the slot's buffers; each result
+    equals the one of a scheduler that issues every launch from the host."""
+    from phyai_b200 import ops
+    from phyai_b200.models.cosmos3 import (Cosmos3ActionRequest, Cosmos3PolicyScheduler, Cosmos3T2VRequest, Cosmos3T2VScheduler,
+                                           Cosmos3Transformer)
+
+    policy = mode == "policy"
+    cfg = small_real_config(action_gen=policy)
+    model = Cosmos3Transformer(cfg, params_dtype=torch.bfloat16, device="cuda").eval().init_random(2, std=0.05)
+    mask = torch.ones(1, 20, dtype=torch.long)
+
+    def request(seed: int, steps: int):
+        g = torch.Generator().manual_seed(seed)
+        ids, nids = torch.randint(0, 512, (1, 20), generator=g), torch.randint(0, 512, (1, 20), generator=g)
+        if policy:
+            return Cosmos3ActionRequest(ids, mask, nids, mask, video_shape=(2, 16, 24), mode="policy", domain_id=seed % 4, action_chunk=8,
+                                        raw_action_dim=7, action_dim=32, num_inference_steps=steps, guidance_scale=3.0, seed=seed,
+                                        cond_video_latents=torch.randn(1, 16, 2, 16, 24, generator=g))
+        return Cosmos3T2VRequest(ids, mask, nids, mask, video_shape=(3, 16, 24), num_inference_steps=steps, guidance_scale=4.0,
+                                 seed=seed, cond_latents=torch.randn(1, 16, 3, 16, 24, generator=g), cond_frame_indexes=(seed % 3,))
+
+    def tensors(out):
+        return [out["video"], out["action"]] if isinstance(out, dict) else [out]
+
+    cls = Cosmos3PolicyScheduler if policy else Cosmos3T2VScheduler
+    plan = [(1, 4), (2, 5), (3, 3)]
+    graphed, eager = cls(model, device="cuda"), cls(model, device="cuda")
+    monkeypatch.setattr(eager, "graph_steps", False, raising=False)
+    graphed.setup()
+    eager.setup()
+    got = []
+    for i, (seed, steps) in enumerate(plan):
+        got.append(tensors(graphed.step(request(seed, steps))))
+        assert graphed.last_graph_replays == (steps - 1 if i == 0 else steps)
+    want = [tensors(eager.step(request(seed, steps))) for seed, steps in plan]
+    assert eager.last_graph_replays == 0
+    torch.cuda.synchronize()
+    assert ops.kernel_status() == 0
+    assert len(graphed._loop_slots) == 1
+    for a, b in zip(got, want):
+        for x, y in zip(a, b):
+            assert torch.isfinite(x.float()).all()
+            assert torch.equal(x, y), (x.float() - y.float()).abs().max().item()
