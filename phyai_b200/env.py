@@ -108,6 +108,7 @@ class envs:
     PHYAI_HEARTBEAT_S = EnvField("PHYAI_HEARTBEAT_S", 0.0, float)
     PHYAI_USE_PYNCCL = EnvField("PHYAI_USE_PYNCCL", False, parse_bool)   # register the ctypes NCCL backend ahead of torch's
     PHYAI_PEER_COMM = EnvField("PHYAI_PEER_COMM", True, parse_bool)    # fused peer-memory collectives (0: NCCL only)
+    PHYAI_PEER_GUARD = EnvField("PHYAI_PEER_GUARD", False, parse_bool)  # 1: guard bands around every symmetric-heap allocation (PeerGroup.check_guards reads them back)
     PHYAI_PEER_HEAP_MB = EnvField("PHYAI_PEER_HEAP_MB", 0, int)          # symmetric heap size override
     # kernel routing (read by the native library itself on first use: listed here so they show up with the rest)
     PHYAI_GEMM_PERSIST = EnvField("PHYAI_GEMM_PERSIST", True, parse_bool)        # 0: one tile per CTA for large GEMMs too

@@ -37,6 +37,11 @@ from .. import ops
 
 _ALIGN = 256
 _NORM_NONE = -1
+_GUARD_BYTE = 0xA5
+
+
+class PeerGuardError(RuntimeError):
+    """A guard band of the symmetric heap was written: some kernel, on this rank or on a peer, stored outside its buffer."""
 
 
 def _up(n: int, a: int = _ALIGN) -> int:
@@ -75,6 +80,13 @@ class PeerGroup:
         self._next_channel = 0
         self._streams: dict[str, PeerStream] = {}
         self._closed = False
+        # PHYAI_PEER_GUARD=1: every allocation of the heap sits between two bands of a known byte, which
+        # check_guards() reads back. Peers store into this rank's buffers, so the bands of a rank catch the
+        # overruns of every rank. All ranks must agree on the setting (the offsets are part of the protocol).
+        from ..env import envs
+
+        self.guard_bytes = _ALIGN if envs.PHYAI_PEER_GUARD.get() else 0
+        self._guards: list[tuple[int, int]] = []
         self.sync()
 
     # ------------------------------------------------------------------ construction helpers
@@ -122,11 +134,37 @@ class PeerGroup:
 
     # ------------------------------------------------------------------ allocation (identical on every rank)
     def alloc(self, nbytes: int) -> int:
+        g = self.guard_bytes
+        if g and not self._guards:
+            self._band(self._top)          # in front of the first allocation
+            self._top += g
         off = self._top
-        self._top = _up(off + nbytes)
-        if self._top > self.heap_bytes:
-            raise MemoryError(f"symmetric heap exhausted: {self._top} > {self.heap_bytes} bytes")
+        end = _up(off + nbytes)
+        if end + g > self.heap_bytes:
+            raise MemoryError(f"symmetric heap exhausted: {end + g} > {self.heap_bytes} bytes")
+        if g:
+            self._band(off + nbytes, end + g)   # from the last byte asked for: behind this allocation, in front of the next
+        self._top = end + g
         return off
+
+    def _band(self, lo: int, hi: int | None = None) -> None:
+        hi = lo + self.guard_bytes if hi is None else hi
+        if hi > self.heap_bytes:
+            raise MemoryError("symmetric heap exhausted by a guard band")
+        self.slab[lo:hi].fill_(_GUARD_BYTE)
+        self._guards.append((lo, hi))
+
+    def check_guards(self) -> None:
+        """Raise :class:`PeerGuardError` if a guard band of this rank's heap no longer holds its fill byte
+        (no-op without ``PHYAI_PEER_GUARD=1``). Call it between steps, after ``sync()``."""
+        bad = []
+        for lo, hi in self._guards:
+            wrong = (self.slab[lo:hi] != _GUARD_BYTE).nonzero()
+            if wrong.numel():
+                bad.append((lo + int(wrong[0]), int(wrong.numel())))
+        if bad:
+            raise PeerGuardError("symmetric heap guard bands overwritten on rank position %d: %s"
+                                 % (self.pos, ", ".join(f"{n} byte(s) from offset {o}" for o, n in bad)))
 
     def new_channel(self) -> int:
         c = self._next_channel

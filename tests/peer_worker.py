@@ -260,6 +260,14 @@ def main() -> int:
     if status != 0:
         fails.append(f"kernel status {status}")
     pg.sync()
+    # PHYAI_PEER_GUARD=1 (set by the test): no kernel of any rank stored outside its buffer of this rank's heap
+    if not pg.guard_bytes:
+        fails.append("the symmetric heap has no guard bands")
+    for g in PeerGroup.open_groups():
+        try:
+            g.check_guards()
+        except Exception as e:  # noqa: BLE001
+            fails.append(str(e))
     ok = torch.tensor([0 if fails else 1], device=dev)
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
     for f in fails:

@@ -96,6 +96,18 @@ def main() -> int:
     status = int(ops.kernel_status())
     if status != 0:
         fails.append(f"kernel status {status}")
+    # PHYAI_PEER_GUARD=1 (set by the test): no kernel of any rank stored outside its buffer of this rank's heap
+    from phyai_b200.parallel.symm import PeerGroup
+
+    groups = PeerGroup.open_groups()
+    if not groups or not all(g.guard_bytes for g in groups):
+        fails.append("no peer group with guard bands is open")
+    for g in groups:
+        g.sync()
+        try:
+            g.check_guards()
+        except Exception as e:  # noqa: BLE001
+            fails.append(str(e))
     eng.close()
     t = torch.tensor([len(fails)], device=dev)
     dist.all_reduce(t)

@@ -118,3 +118,41 @@ def test_collectives_are_registered_ops_with_shape_only_fakes():
         assert state.mesh_name(mesh) == "fake_tp4"
     finally:
         state.unregister_mesh("fake_tp4")
+
+
+def test_symmetric_heap_guard_bands():
+    """The heap allocator with guard bands (host arithmetic on a CPU slab): allocations stay aligned and apart, the
+    bands are found intact, and a store one byte past a buffer, or one byte in front of it, is reported with its offset."""
+    from phyai_b200.parallel import symm
+
+    def heap(guard: int):
+        g = object.__new__(symm.PeerGroup)
+        g.pos, g.sig_bytes, g.heap_bytes, g.guard_bytes = 0, 1024, 1024 + 8192, guard
+        g.slab = torch.zeros(g.heap_bytes, dtype=torch.uint8)
+        g._top, g._guards = g.sig_bytes, []
+        return g
+
+    plain = heap(0)
+    assert [plain.alloc(n) for n in (100, 256, 257)] == [1024, 1280, 1536] and plain._top == 2048
+    plain.check_guards()                                   # nothing to check, nothing raised
+
+    g = heap(256)
+    offs = [g.alloc(n) for n in (100, 256, 257)]
+    assert offs == [1280, 1792, 2304] and all(o % 256 == 0 for o in offs)
+    assert g._guards == [(1024, 1280), (1380, 1792), (2048, 2304), (2561, 3072)] and g._top == 3072
+    g.check_guards()
+    g.slab[offs[1]:offs[1] + 256].fill_(7)                 # a full write of the buffer leaves the bands alone
+    g.check_guards()
+    g.slab[offs[1] + 256] = 1                              # one byte behind it
+    with pytest.raises(symm.PeerGuardError, match="offset 2048"):
+        g.check_guards()
+    g.slab[offs[1] + 256] = 0xA5
+    g.slab[offs[2] - 1] = 0                                # one byte in front of the next buffer
+    with pytest.raises(symm.PeerGuardError, match="offset 2303"):
+        g.check_guards()
+    g.slab[offs[2] - 1] = 0xA5
+    g.slab[offs[0] + 100] = 3                              # one byte behind a buffer whose size is not a multiple of the alignment
+    with pytest.raises(symm.PeerGuardError, match="offset 1380"):
+        g.check_guards()
+    with pytest.raises(MemoryError):
+        g.alloc(8192)

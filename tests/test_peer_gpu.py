@@ -32,7 +32,7 @@ def test_bounded_wait_reports_instead_of_hanging():
 def test_peer_collectives(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=f"{ROOT}:{os.environ.get('PYTHONPATH', '')}")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PHYAI_PEER_GUARD="1", PYTHONPATH=f"{ROOT}:{os.environ.get('PYTHONPATH', '')}")
     port = 29600 + world
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
            "127.0.0.1", "--master-port", str(port), str(ROOT / "tests" / "peer_worker.py")]

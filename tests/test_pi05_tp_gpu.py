@@ -20,7 +20,7 @@ def test_tp_plan_matches_single_rank(world, shard_expert):
         pytest.skip(f"needs {world} GPUs")
     # PHYAI_PI05_TP_SCATTER_ROWS: the test geometry has 80-160 prefix rows; groups of four and more take the
     # reduce-scatter / all-gather prefix with it
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=f"{ROOT}:{os.environ.get('PYTHONPATH', '')}",
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PHYAI_PEER_GUARD="1", PYTHONPATH=f"{ROOT}:{os.environ.get('PYTHONPATH', '')}",
                PI05_TP_SHARD_EXPERT="1" if shard_expert else "0", PHYAI_PI05_TP_SCATTER_ROWS="64")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
            "127.0.0.1", "--master-port", str(29650 + world + (20 if shard_expert else 0)), str(ROOT / "tests" / "pi05_tp_worker.py")]
