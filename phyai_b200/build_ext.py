@@ -12,8 +12,13 @@ Variants (objects are cached per flag set, the output replaces the regular ``.so
 * ``--debug``     ``-DPHYAI_DEBUG=1``: the kernels' index checks are compiled in (a row / column /
   slot index outside its tensor is recorded in the status word as ``kStatusBadArg`` and the access is
   skipped, see ``PB_DEBUG_CHECK`` in ``csrc/ptx.cuh``), device code at ``-O1`` with line info;
-* ``--sanitize``  host-only prefix cache with ``-fsanitize=address,undefined`` (run the cache tests with
-  ``LD_PRELOAD=$(gcc -print-file-name=libasan.so)``); ``--tsan`` the same with ``-fsanitize=thread``.
+* ``--sanitize``  host-only prefix cache with ``-fsanitize=address,undefined``; run the cache tests with
+  ``LD_PRELOAD="$(gcc -print-file-name=libasan.so) $(gcc -print-file-name=libstdc++.so)" ASAN_OPTIONS=detect_leaks=0``
+  (the C++ runtime has to be loaded with the sanitizer, or its ``__cxa_throw`` hook finds nothing to call at the first
+  exception); ``--tsan`` the same with ``-fsanitize=thread`` and ``libtsan.so``.
+
+Building a variant and then the regular flavour again relinks: ``build/_C.linked`` / ``build/_radix.linked`` hold the
+link tag of what the output file contains.
 """
 
 from __future__ import annotations
@@ -103,14 +108,14 @@ def build_core(verbose: bool = False, debug: bool = False) -> Path:
 
     out = ROOT / f"_C{ext_suffix()}"
     link_tag = _hash(objs, ["link"])
-    stamp = BUILD / f"_C.{link_tag}.stamp"
-    if not out.exists() or not stamp.exists():
+    stamp = BUILD / "_C.linked"           # the link tag of what the output file holds (variants replace one another)
+    if not out.exists() or not stamp.exists() or stamp.read_text() != link_tag:
         libs = ["-lc10", "-ltorch", "-ltorch_cpu", "-ltorch_python", "-lc10_cuda", "-ltorch_cuda"]
         cmd = [NVCC, "-shared", *ARCH_FLAGS, "-o", str(out), *map(str, objs),
                *[f"-L{p}" for p in libdirs], *libs,
                *[f"-Xlinker=-rpath={p}" for p in libdirs]]
         _run(cmd)
-        stamp.write_text("ok")
+        stamp.write_text(link_tag)
     return out
 
 
@@ -147,10 +152,10 @@ def build_radix(verbose: bool = False, sanitize: str | None = None) -> Path | No
         list(ex.map(_run, jobs))
     out = ROOT / f"_radix{ext_suffix()}"
     link_tag = _hash(objs, ["link-radix", *san])
-    stamp = BUILD / f"_radix.{link_tag}.stamp"
-    if not out.exists() or not stamp.exists():
+    stamp = BUILD / "_radix.linked"       # the link tag of what the output file holds (variants replace one another)
+    if not out.exists() or not stamp.exists() or stamp.read_text() != link_tag:
         _run(["g++", "-shared", "-pthread", *san, "-o", str(out), *map(str, objs)])
-        stamp.write_text("ok")
+        stamp.write_text(link_tag)
     return out
 
 
