@@ -26,7 +26,9 @@ PRE_JSON, POST_JSON = "policy_preprocessor.json", "policy_postprocessor.json"
 
 
 def discretize_state(state: torch.Tensor, num_bins: int = STATE_NUM_BINS) -> np.ndarray:
-    """[-1, 1] -> bin index in [0, num_bins); values outside clip to the end bins."""
+    """[-1, 1] -> bin index in [0, num_bins). Values above 1 land in the last bin; values below -1 give -1, as the
+    binning of the reference does (phyai-utils-tools/src/phyai_utils_tools/models/pi05/ops_pi05.py:29-31): states are
+    expected to be normalised into range before this step."""
     edges = np.linspace(-1.0, 1.0, num_bins + 1)[:-1]
     return np.digitize(state.detach().to(torch.float32).cpu().numpy(), bins=edges) - 1
 

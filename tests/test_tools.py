@@ -9,7 +9,7 @@ import torch
 from phyai_b200.tools import cosmos3 as c3
 from phyai_b200.tools.pi0 import PI0Processor, PadStateStep
 from phyai_b200.tools.pi05 import ACTION_FEATURE, STATE_FEATURE, PI05Processor, build_prompts, discretize_state
-from phyai_b200.tools.processing import (ACTION, IMAGES, PIXEL_VALUES, STATE, TASK, NormalizerStep, ProcessorPipeline, ProcessorStepError,
+from phyai_b200.tools.processing import (ACTION, IMAGES, PIXEL_VALUES, PROMPT, STATE, TASK, NormalizerStep, ProcessorPipeline, ProcessorStepError,
                                          ProcessorStepRegistry, ResizeWithPadStep, UnnormalizerStep, resize_with_pad)
 from phyai_b200.tools.tokenizer import ByteTokenizer
 
@@ -68,8 +68,11 @@ def test_pipeline_save_load_lerobot_layout(tmp_path):
 
 
 def test_pi05_state_binning_and_prompt():
-    bins = discretize_state(torch.tensor([[-1.0, 0.0, 0.999, 1.5, -3.0]]))
-    assert bins.tolist() == [[0, 128, 255, 255, -1 + 0]] or bins.tolist()[0][:3] == [0, 128, 255]
+    edge = -1 + 2 / 256                                                       # the left edge of bin 1
+    bins = discretize_state(torch.tensor([[-1.0, 0.0, 0.999, 1.0, 1.5, -3.0, edge, edge - 1e-4]]))
+    assert bins.tolist() == [[0, 128, 255, 255, 255, -1, 1, 0]]             # above range: last bin; below range: -1
+    assert discretize_state(torch.tensor([0.25], dtype=torch.bfloat16)).tolist() == [160]     # bf16 states convert cleanly
+    assert discretize_state(torch.tensor([[-1.0, 0.99]]), num_bins=4).tolist() == [[0, 3]]
     assert build_prompts(["a_b"], np.array([[1, 2]])) == ["Task: a b, State: 1 2;\nAction: "]
     with pytest.raises(ValueError):
         build_prompts(["a", "b"], np.array([[1]]))
@@ -131,3 +134,53 @@ def test_cosmos3_policy_processor_and_postprocess(tmp_path):
     assert frames.shape == (5, 16, 24, 3) and frames.dtype == torch.uint8
     f = post.save_npz(frames, tmp_path / "clip.npz")
     assert np.load(f)["frames"].shape == (5, 16, 24, 3)
+
+
+def test_pi05_processor_end_to_end_and_saved_pair(tmp_path):
+    """Images resized, state normalised by quantiles and written into the prompt as bins, tokens right-padded; the action
+    chunk comes back un-normalised and cut to the robot's width; a saved pair rebuilds the same pipelines."""
+    from phyai_b200.tools.pi05 import PI05Processor, StateTokenizerPrepareStep, make_pi05_processors
+
+    stats = {"observation.state": {"q01": [0.0, 0.0], "q99": [2.0, 4.0]}, "action": {"q01": [-1.0] * 3, "q99": [3.0] * 3}}
+    p = PI05Processor(tokenizer=ByteTokenizer(), image_size=16, tokenizer_max_length=160, params_dtype=torch.float32, action_dim=3,
+                      dataset_stats=stats, max_state_dim=4)
+    sample = {IMAGES: torch.rand(1, 2, 3, 8, 16), STATE: torch.tensor([[1.0, 4.0]]), TASK: "pick_up the\ncube "}
+    out = p.preprocess(dict(sample))
+    assert out.pixel_values.shape == (1, 2, 3, 16, 16) and out.input_ids.shape == (1, 160)
+    text = ByteTokenizer().decode(out.input_ids[0, : int(out.lang_lens[0])])
+    # state 1.0 of [0, 2] -> 0 -> bin 128; 4.0 of [0, 4] -> ~1 -> bin 255; two padding columns at 0 -> bin 128
+    assert text == "Task: pick up the cube, State: 128 255 128 128;\nAction: "
+    act = p.postprocess(torch.zeros(1, 5, 32))
+    assert act.shape == (1, 5, 3) and torch.allclose(act, torch.ones(1, 5, 3), atol=1e-5)        # 0 of [-1, 3] -> the middle, 1.0
+    with pytest.raises(ValueError, match="needs 'state' and 'task'"):
+        StateTokenizerPrepareStep()({TASK: "x"})
+    p.save_pretrained(tmp_path)
+    assert (tmp_path / "policy_preprocessor.json").is_file() and (tmp_path / "policy_postprocessor.json").is_file()
+    q = PI05Processor.from_pretrained(tmp_path, tokenizer=ByteTokenizer(), params_dtype=torch.float32)
+    again = q.preprocess(dict(sample))
+    assert torch.equal(again.input_ids, out.input_ids) and torch.equal(again.pixel_values, out.pixel_values)
+    assert torch.allclose(q.postprocess(torch.zeros(1, 5, 32)), act)
+    pre, post = make_pi05_processors(tokenizer=ByteTokenizer(), image_size=16, tokenizer_max_length=32, params_dtype=torch.float32)
+    assert pre.name == "policy_preprocessor" and post.name == "policy_postprocessor" and len(pre) == 5
+
+
+def test_pi0_saved_pair_and_prompt_step_names(tmp_path):
+    from phyai_b200.tools.pi0 import Pi0NewLineProcessor, Pi0PromptPrepareStep
+
+    stats = {"observation.state": {"mean": [1.0] * 5, "std": [2.0] * 5}, "action": {"mean": [0.5] * 7, "std": [2.0] * 7}}
+    p = PI0Processor(tokenizer=ByteTokenizer(), image_size=16, tokenizer_max_length=16, params_dtype=torch.float32, action_dim=7,
+                     dataset_stats=stats)
+    out = p.preprocess({IMAGES: torch.rand(1, 3, 3, 16, 16), STATE: torch.full((1, 5), 3.0), TASK: "Wipe Table"})
+    assert torch.allclose(out.state[0, :5], torch.ones(5), atol=1e-6) and out.state[0, 5:].abs().sum() == 0    # (3 - 1) / 2, then zero padding
+    assert ByteTokenizer().decode(out.input_ids[0, : int(out.lang_lens[0])]) == "Wipe Table\n"                # case is kept
+    assert torch.allclose(p.postprocess(torch.ones(1, 4, 32)), torch.full((1, 4, 7), 2.5), atol=1e-6)
+    p.save_pretrained(tmp_path)
+    q = PI0Processor.from_pretrained(tmp_path, tokenizer=ByteTokenizer(), params_dtype=torch.float32)
+    again = q.preprocess({IMAGES: torch.rand(1, 3, 3, 16, 16), STATE: torch.full((1, 5), 3.0), TASK: "Wipe Table"})
+    assert torch.equal(again.state, out.state) and torch.equal(again.input_ids, out.input_ids)
+    assert Pi0PromptPrepareStep()({TASK: ["a\n", "b"]})[PROMPT] == ["a\n", "b\n"]
+    assert Pi0NewLineProcessor()({TASK: "c"})[PROMPT] == ["c\n"]                                              # the name lerobot checkpoints use
+    with pytest.raises(ValueError, match="needs 'task'"):
+        Pi0PromptPrepareStep()({})
+    with pytest.raises(TypeError, match="must be a tensor"):
+        PadStateStep()({STATE: [1.0]})
