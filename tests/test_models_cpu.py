@@ -191,3 +191,69 @@ def test_nvfp4_scale_layout_round_trip():
             flat[off] = src[r, kb]
     back = unswizzle_scales(flat, rows, K).view(torch.uint8)
     assert torch.equal(back, src)
+
+
+def test_pi05_cached_path_equals_masked_joint_forward():
+    """Pi0.5 (two Euler steps) against one masked joint forward per step written with plain tensor ops on the same
+    weights: rows = [prefix | actions], the prefix runs the PaliGemma weights with the static Gemma norm, the action rows
+    run the expert weights with the time-conditioned norm (scale, shift, gate from a dense layer on the time embedding)."""
+    from phyai_b200.models.pi05.configuration_pi05 import tiny_pi05_config
+    from phyai_b200.models.pi05.modeling_pi05 import PI05Model
+
+    cfg = tiny_pi05_config(num_inference_steps=2)
+    m = PI05Model(cfg).init_random(5)
+    for l in m.paligemma_lm.layers:
+        l.input_layernorm.weight.data.normal_(0, 0.2)
+        l.post_attention_layernorm.weight.data.normal_(0, 0.2)
+    for n_ in [n for l in m.expert_stack.layers for n in (l.input_layernorm, l.post_attention_layernorm)] + [m.expert_stack.norm]:
+        n_.dense.weight.data.normal_(0, 0.05)
+        n_.dense.bias.data.normal_(0, 0.05)
+    g = torch.Generator().manual_seed(2)
+    pix = torch.rand(2, 3, 56, 56, generator=g) * 2 - 1
+    ids = torch.randint(0, 1024, (16,), generator=g)
+    noise = torch.randn(cfg.chunk_size, cfg.max_action_dim, generator=g)
+    L = 9
+    got = m.sample_actions(pix[None], ids[None], torch.tensor([L]), noise[None])[0]
+
+    def ada(x, norm, cond, eps=cfg.expert.rms_norm_eps):
+        scale, shift, gate = (cond @ norm.dense.weight.t() + norm.dense.bias).chunk(3, dim=-1)
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * (1 + scale) + shift, gate
+
+    img = m.vision(pix).reshape(-1, cfg.text.hidden_size)
+    lang = m.paligemma_lm.embed_tokens.data[ids[:L]] * math.sqrt(cfg.text.hidden_size)
+    prefix0 = torch.cat([img, lang])
+    P, C = prefix0.shape[0], cfg.chunk_size
+    n = P + C
+    mask = torch.zeros(n, n, dtype=torch.bool)
+    mask[:P, :P] = True                      # prefix: bidirectional, blind to the actions
+    mask[P:, :] = True                       # actions: the prefix and each other
+    pos = torch.arange(n)
+    H, KV, hd = cfg.text.num_attention_heads, cfg.text.num_key_value_heads, cfg.text.head_dim
+    x = noise.clone()
+    N = cfg.num_inference_steps
+    for i in range(N):
+        t = torch.full((1,), 1.0 - i / N)
+        emb = ref.sinusoidal_time_embedding(t, cfg.expert.hidden_size, cfg.min_period, cfg.max_period)
+        cond = F.silu(F.silu(emb @ m.heads.time_mlp_in.weight.t() + m.heads.time_mlp_in.bias) @ m.heads.time_mlp_out.weight.t()
+                      + m.heads.time_mlp_out.bias)
+        hp = prefix0
+        he = x @ m.heads.action_in_proj.weight.t() + m.heads.action_in_proj.bias
+        for lp, le in zip(m.paligemma_lm.layers, m.expert_stack.layers):
+            wp, we = _weights(lp), _weights(le)
+            xp = _gemma_norm(hp, lp.input_layernorm.weight.data)
+            xe, g1 = ada(he, le.input_layernorm, cond)
+            q = torch.cat([(xp @ wp["wq"].t()), (xe @ we["wq"].t())]).reshape(n, H, hd)
+            k = torch.cat([(xp @ wp["wk"].t()), (xe @ we["wk"].t())]).reshape(n, KV, hd)
+            v = torch.cat([(xp @ wp["wv"].t()), (xe @ we["wv"].t())]).reshape(n, KV, hd)
+            q, k = _rope(q, pos), _rope(k, pos)
+            kk, vv = k.repeat_interleave(H // KV, 1), v.repeat_interleave(H // KV, 1)
+            s = torch.einsum("qhd,khd->hqk", q, kk) / math.sqrt(hd)
+            att = torch.einsum("hqk,khd->qhd", torch.softmax(s.masked_fill(~mask[None], float("-inf")), -1), vv).reshape(n, -1)
+            hp = hp + att[:P] @ wp["wo"].t()
+            he = he + g1 * (att[P:] @ we["wo"].t())
+            hp = hp + _mlp(_gemma_norm(hp, lp.post_attention_layernorm.weight.data), wp)
+            xe, g2 = ada(he, le.post_attention_layernorm, cond)
+            he = he + g2 * _mlp(xe, we)
+        out, _ = ada(he, m.expert_stack.norm, cond)
+        x = x - (out @ m.heads.action_out_proj.weight.t() + m.heads.action_out_proj.bias) / N
+    assert torch.allclose(got, x, atol=2e-4), (got - x).abs().max()
