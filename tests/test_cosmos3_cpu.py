@@ -263,3 +263,118 @@ def test_loop_slot_serves_later_requests_from_kept_buffers(kind, monkeypatch):
     sch.drop_loop_slots()
     assert "_loop_slots" not in sch.__dict__
     eng.close()
+
+
+def test_transformer_matches_a_restatement_from_checkpoint_tensors(tmp_path):
+    """A checkpoint written under the upstream key names (one layer index feeding both towers), loaded through the key
+    remap, against the forward pass written out with plain tensor ops on those same checkpoint tensors: text tower
+    (causal, K/V kept per layer), generation tower over [text K/V | its own], interleaved three-axis rotary positions with
+    the frame-rate rescaling, additive time embedding, patch folding."""
+    from safetensors.torch import save_file
+
+    from phyai_b200.models.cosmos3 import Cosmos3Transformer
+    from phyai_b200.models.cosmos3.transformer_cosmos3 import cosmos3_weight_remap
+    from phyai_b200.weights import load_pretrained
+
+    cfg = tiny_cosmos3_config()
+    H, D, Hq, Hkv, I, nl = cfg.hidden_size, cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.intermediate_size, cfg.num_hidden_layers
+    g = torch.Generator().manual_seed(0)
+    rnd = lambda *s, std=0.2: torch.randn(*s, generator=g) * std  # noqa: E731
+    ck = {"embed_tokens.weight": rnd(cfg.vocab_size, H, std=1.0), "norm.weight": 1 + rnd(H), "lm_head.weight": rnd(4, 4),
+          "proj_in.weight": rnd(H, cfg.patch_latent_dim), "proj_in.bias": rnd(H), "proj_out.weight": rnd(cfg.patch_latent_dim, H),
+          "proj_out.bias": rnd(cfg.patch_latent_dim), "norm_moe_gen.weight": 1 + rnd(H),
+          "time_embedder.linear_1.weight": rnd(H, 256), "time_embedder.linear_1.bias": rnd(H),
+          "time_embedder.linear_2.weight": rnd(H, H), "time_embedder.linear_2.bias": rnd(H)}
+    und = dict(q="self_attn.to_q", k="self_attn.to_k", v="self_attn.to_v", o="self_attn.to_out", nq="self_attn.norm_q", nk="self_attn.norm_k",
+               ln1="input_layernorm", ln2="post_attention_layernorm", gate="mlp.gate_proj", up="mlp.up_proj", down="mlp.down_proj")
+    gen = dict(q="self_attn.add_q_proj", k="self_attn.add_k_proj", v="self_attn.add_v_proj", o="self_attn.to_add_out",
+               nq="self_attn.norm_added_q", nk="self_attn.norm_added_k", ln1="input_layernorm_moe_gen",
+               ln2="post_attention_layernorm_moe_gen", gate="mlp_moe_gen.gate_proj", up="mlp_moe_gen.up_proj", down="mlp_moe_gen.down_proj")
+    shapes = dict(q=(Hq * D, H), k=(Hkv * D, H), v=(Hkv * D, H), o=(H, Hq * D), nq=(D,), nk=(D,), ln1=(H,), ln2=(H,),
+                  gate=(I, H), up=(I, H), down=(H, I))
+    for i in range(nl):
+        for names in (und, gen):
+            for short, leaf in names.items():
+                t = rnd(*shapes[short])
+                ck[f"layers.{i}.{leaf}.weight"] = 1 + t if len(shapes[short]) == 1 else t
+    save_file({k: v.contiguous() for k, v in ck.items()}, str(tmp_path / "model.safetensors"))
+    model = Cosmos3Transformer(cfg, params_dtype=torch.float32, device="cpu").eval()
+    report = load_pretrained(model, tmp_path, remap=cosmos3_weight_remap, strict=True)
+    assert not report.missing and not report.unexpected
+
+    B, L, vs, fps = 1, 6, (3, 4, 6), 12.0
+    ids = torch.randint(0, cfg.vocab_size, (B, L), generator=g)
+    lat = torch.randn(B, cfg.latent_channel, *vs, generator=g)
+    tval = torch.tensor([437.0])
+    got = model(lat, tval, model.encode_condition(ids, torch.ones(B, L, dtype=torch.long), vs, fps))
+
+    # ------------------------------------------------------------------ by hand
+    def rms(x, w):
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + cfg.rms_norm_eps) * w
+
+    def rope(x, pos3):
+        """x (T, heads, D); pos3 (3, T). Band i of the D/2 frequency bands follows the time axis, except bands
+        1, 4, 7, ... (as many as the height section holds) and 2, 5, 8, ... (width section)."""
+        half = D // 2
+        inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+        ang = pos3[0].float()[:, None] * inv[None]
+        for axis in (1, 2):
+            idx = torch.arange(axis, cfg.mrope_section[axis] * 3, 3)
+            ang[:, idx] = pos3[axis].float()[:, None] * inv[None, idx]
+        cos, sin = ang.cos()[:, None], ang.sin()[:, None]
+        x1, x2 = x[..., :half], x[..., half:]
+        return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], -1)
+
+    def block(h, names, i, pos3, extra_kv=None, causal=False):
+        w = lambda s: ck[f"layers.{i}.{names[s]}.weight"]  # noqa: E731
+        x = rms(h, w("ln1"))
+        T = x.shape[0]
+        q = rope(rms((x @ w("q").t()).reshape(T, Hq, D), w("nq")), pos3)
+        k = rope(rms((x @ w("k").t()).reshape(T, Hkv, D), w("nk")), pos3)
+        v = (x @ w("v").t()).reshape(T, Hkv, D)
+        kk, vv = (k, v) if extra_kv is None else (torch.cat([extra_kv[0], k]), torch.cat([extra_kv[1], v]))
+        rep = Hq // Hkv
+        s = torch.einsum("qhd,khd->hqk", q, kk.repeat_interleave(rep, 1)) / math.sqrt(D)
+        if causal:
+            s = s.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1)[None], float("-inf"))
+        a = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), vv.repeat_interleave(rep, 1)).reshape(T, Hq * D)
+        h = h + a @ w("o").t()
+        y = rms(h, w("ln2"))
+        return h + (torch.nn.functional.silu(y @ w("gate").t()) * (y @ w("up").t())) @ w("down").t(), k, v
+
+    text_pos = torch.arange(L)[None].expand(3, -1)
+    h = ck["embed_tokens.weight"][ids[0]]
+    text_kv = []
+    for i in range(nl):
+        h, k, v = block(h, und, i, text_pos, causal=True)
+        text_kv.append((k, v))
+    t_lat, h_lat, w_lat = vs
+    p = cfg.latent_patch_size
+    hp, wp = h_lat // p, w_lat // p
+    first = L + cfg.temporal_modality_margin
+    # frame positions rescaled to the base frame rate: frame f sits at f / (fps / 4) * (24 / 4)
+    tt = torch.arange(t_lat, dtype=torch.float32) / (fps / cfg.temporal_compression_factor) * (cfg.base_fps / cfg.temporal_compression_factor) + first
+    gen_pos = torch.stack([tt[:, None, None].expand(t_lat, hp, wp).reshape(-1),
+                           torch.arange(hp, dtype=torch.float32)[None, :, None].expand(t_lat, hp, wp).reshape(-1),
+                           torch.arange(wp, dtype=torch.float32)[None, None, :].expand(t_lat, hp, wp).reshape(-1)])
+    tokens = torch.zeros(t_lat * hp * wp, p * p * cfg.latent_channel)
+    for f in range(t_lat):
+        for y in range(hp):
+            for x_ in range(wp):
+                patch = lat[0, :, f, y * p:(y + 1) * p, x_ * p:(x_ + 1) * p]            # (c, py, px)
+                tokens[(f * hp + y) * wp + x_] = patch.permute(1, 2, 0).reshape(-1)       # ordered (py, px, c)
+    freqs = torch.exp(-math.log(10000.0) * torch.arange(128, dtype=torch.float32) / 128)
+    a = (tval * cfg.timestep_scale)[:, None] * freqs[None]
+    te = torch.nn.functional.silu(torch.cat([a.cos(), a.sin()], -1) @ ck["time_embedder.linear_1.weight"].t() + ck["time_embedder.linear_1.bias"])
+    te = te @ ck["time_embedder.linear_2.weight"].t() + ck["time_embedder.linear_2.bias"]
+    hg = tokens @ ck["proj_in.weight"].t() + ck["proj_in.bias"] + te
+    for i in range(nl):
+        hg, _, _ = block(hg, gen, i, gen_pos, extra_kv=text_kv[i])
+    out_tok = rms(hg, ck["norm_moe_gen.weight"]) @ ck["proj_out.weight"].t() + ck["proj_out.bias"]
+    want = torch.zeros_like(lat)
+    for f in range(t_lat):
+        for y in range(hp):
+            for x_ in range(wp):
+                want[0, :, f, y * p:(y + 1) * p, x_ * p:(x_ + 1) * p] = out_tok[(f * hp + y) * wp + x_].reshape(p, p, -1).permute(2, 0, 1)
+    assert got.shape == want.shape
+    assert torch.allclose(got, want, atol=2e-4, rtol=1e-4), (got - want).abs().max()
