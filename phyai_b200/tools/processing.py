@@ -240,10 +240,17 @@ def resize_with_pad(images: torch.Tensor, target_h: int, target_w: int, *, mode:
         raise ValueError(f"unsupported image dtype {images.dtype}")
     ratio = max(w / target_w, h / target_h)
     rh, rw = int(h / ratio), int(w / ratio)
-    src = images.float() if images.dtype == torch.uint8 else images
-    out = F.interpolate(src, size=(rh, rw), mode=mode, align_corners=False if mode == "bilinear" else None)
+    kw = dict(size=(rh, rw), mode=mode, align_corners=False if mode == "bilinear" else None)
     if images.dtype == torch.uint8:
+        # bytes are interpolated as bytes where the device has that kernel (the CPU does: same pixels as the reference,
+        # phyai-utils-tools/src/phyai_utils_tools/processing/ops/image_ops.py:56-64), else through fp32
+        try:
+            out = F.interpolate(images, **kw)
+        except (RuntimeError, NotImplementedError):
+            out = F.interpolate(images.float(), **kw)
         out = out.round().clamp(0, 255).to(torch.uint8)
+    else:
+        out = F.interpolate(images, **kw)
     top, rem_h = divmod(target_h - rh, 2)
     left, rem_w = divmod(target_w - rw, 2)
     return F.pad(out, (left, left + rem_w, top, top + rem_h), value=pad_value)

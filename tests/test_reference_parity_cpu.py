@@ -1,0 +1,226 @@
+"""This package against the unmodified reference installed under ``baseline/_ref``, piece by piece on CPU: the parts
+of the reference that import and run without a GPU (sampler, rotary tables and position ids, prompt and bucket helpers,
+state binning, image and normalisation steps). Skipped where the reference is not installed."""
+
+import importlib
+import json
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+REF = ROOT / "baseline" / "_ref"
+pytestmark = pytest.mark.skipif(not (REF / "phyai").is_dir(), reason="the reference is not installed under baseline/_ref")
+
+
+@pytest.fixture()
+def ref():
+    """``ref("phyai.x.y")`` imports a module of the reference; its folder is on the path only inside the test."""
+    sys.path.insert(0, str(REF))
+    try:
+        yield importlib.import_module
+    finally:
+        sys.path.remove(str(REF))
+
+
+@pytest.mark.parametrize("karras,shift,steps", [(True, 1.0, 8), (False, 1.0, 5), (False, 5.0, 12), (True, 3.0, 2), (False, 1.0, 1)])
+def test_unipc_trajectory(ref, karras, shift, steps):
+    from phyai_b200.models.cosmos3 import UniPCMultistepSampler
+
+    theirs = ref("phyai.models.cosmos3.sampler_unipc").UniPCMultistepSampler(flow_shift=shift, use_karras_sigmas=karras)
+    ours = UniPCMultistepSampler(flow_shift=shift, use_karras_sigmas=karras)
+    theirs.set_timesteps(steps)
+    ours.set_timesteps(steps)
+    assert torch.allclose(ours.timesteps.float(), theirs.timesteps.float()) and torch.allclose(ours.sigmas.float(), theirs.sigmas.float(), atol=1e-6)
+    g = torch.Generator().manual_seed(steps)
+    xa = xb = torch.randn(2, 4, 3, 5, generator=g, dtype=torch.float64)
+    w = torch.randn(5, 5, generator=g, dtype=torch.float64) * 0.3
+    for t in theirs.timesteps:
+        va, vb = torch.tanh(xa @ w) + 0.1 * xa, torch.tanh(xb @ w) + 0.1 * xb          # a smooth stand-in for the model
+        xa, xb = theirs.step(va, t, xa), ours.step(vb, t, xb)
+        # the reference holds its sigmas and coefficients in fp32 tensors, this package in Python floats
+        assert torch.allclose(xa, xb, atol=2e-5, rtol=2e-5), (float(t), (xa - xb).abs().max())
+    assert ours.step_index == theirs.step_index == steps
+
+
+def test_position_ids_and_interleaved_rotary_tables(ref):
+    from phyai_b200.layers.rotary_embedding import MRotaryEmbedding
+    from phyai_b200.models.cosmos3 import modeling_cosmos3 as mine
+
+    theirs = ref("phyai.models.cosmos3.modeling_cosmos3")
+    rot = ref("phyai.layers.rotary_embedding")
+    assert torch.equal(mine.compute_mrope_position_ids_text(7, 3)[0], theirs.compute_mrope_position_ids_text(7, 3)[0])
+    cases = [dict(fps=None), dict(fps=24.0), dict(fps=10.0), dict(fps=30.0, temporal_compression_factor=1, base_temporal_compression_factor=4,
+                                                                   start_frame_offset=1), dict(fps=12.0, enable_fps_modulation=False)]
+    for kw in cases:
+        a, na = mine.compute_mrope_position_ids_vision(3, 2, 4, 107, **kw)
+        b, nb = theirs.compute_mrope_position_ids_vision(3, 2, 4, 107, **kw)
+        assert a.dtype == b.dtype and torch.equal(a, b) and na == nb, kw
+    for head_dim, sections, theta in ((128, (24, 20, 20), 5e6), (16, (4, 2, 2), 1e4), (64, (16, 8, 8), 1e6)):
+        pos = torch.stack([torch.rand(9) * 500, torch.randint(0, 40, (9,)).float(), torch.randint(0, 60, (9,)).float()])
+        ours = MRotaryEmbedding(head_dim, sections, theta, interleaved=True)
+        cos, sin = rot.compute_qwen3vl_mrope_cos_sin_from_inv_freq(pos[:, None], ours.inv_freq, sections)
+        got = ours.cos_sin(pos)
+        half = head_dim // 2
+        assert torch.allclose(got[:, :half], cos[0, :, :half], atol=1e-6) and torch.allclose(got[:, half:], sin[0, :, :half], atol=1e-6)
+
+
+def test_pi05_state_bins_and_prompts(ref):
+    from phyai_b200.tools import pi05 as mine
+
+    theirs = ref("phyai_utils_tools.models.pi05.ops_pi05")
+    g = torch.Generator().manual_seed(0)
+    state = torch.cat([torch.rand(4, 9, generator=g) * 2.4 - 1.2, torch.tensor([[-1.0, 1.0, 0.0, -1 + 2 / 256, 1 - 2 / 256, 0.5, -0.5, 2.0, -2.0]])])
+    for s in (state, state.bfloat16()):
+        assert np.array_equal(mine.discretize_state(s), theirs.discretize_state(s))
+    bins = mine.discretize_state(state)
+    tasks = ["pick_up the cube", " fold\nthe towel ", "open__drawer", "x", "Wipe The Table"]
+    assert mine.build_prompts(tasks, bins) == theirs.build_prompts(tasks, bins)
+    assert mine.STATE_NUM_BINS == theirs.STATE_NUM_BINS
+
+
+def test_cosmos3_prompt_and_bucket_helpers(ref):
+    from phyai_b200.tools import cosmos3 as mine
+
+    theirs = ref("phyai_utils_tools.models.cosmos3.steps_cosmos3")
+    assert mine.EMBODIMENT_TO_DOMAIN_ID == theirs.EMBODIMENT_TO_DOMAIN_ID
+    assert mine.EMBODIMENT_TO_RAW_ACTION_DIM == theirs.EMBODIMENT_TO_RAW_ACTION_DIM
+    for h, w in ((720, 1280), (1280, 720), (480, 640), (500, 500), (333, 1000), (1000, 333), (1080, 1920)):
+        for tier in ("256", "480", "704", "768", "1080"):
+            assert mine.find_closest_target_size(h, w, tier) == theirs.find_closest_target_size(h, w, tier), (h, w, tier)
+    for name in ("libero", "LIBERO", " droid_lerobot ", 7):
+        assert mine.resolve_domain_id(name) == theirs.resolve_domain_id(name)
+    for name in ("pusht", "agibotworld", "robomind-franka-dual"):
+        assert mine.resolve_raw_action_dim(name) == theirs.resolve_raw_action_dim(name)
+    for prompt, frames, fps, h, w in (("open the drawer", 33, 10.0, 480, 832), ("Stop!", 125, 30.0, 704, 1280), ("wave", 1, 24.0, 100, 150),
+                                      ("pour water.", 700, 10.0, 544, 736)):
+        for view in ("ego", "wrist", "third_person", "nowhere"):
+            kw = dict(view_point=view, num_frames=frames, fps=fps, height=h, width=w)
+            assert json.loads(mine.cosmos3_action_json_caption(prompt, **kw)) == json.loads(theirs.cosmos3_action_json_caption(prompt, **kw))
+            assert mine.cosmos3_action_json_caption(prompt, **kw) == theirs.cosmos3_action_json_caption(prompt, **kw)
+    for prompt in ("A robot arm", "A robot arm.", '{"scene": "lab"}', '{"scene": "lab", "duration": "2s", "fps": 3}', "[1, 2]", "  spaced  "):
+        for frames, fps in ((93, 24.0), (1, 24.0), (17, 16.0)):
+            for ar in (None, "16,9"):
+                kw = dict(fps=fps, num_frames=frames, height=720, width=1280, aspect_ratio=ar)
+                assert mine.cosmos3_generation_caption(prompt, **kw) == theirs.cosmos3_generation_caption(prompt, **kw), (prompt, kw)
+
+
+def test_image_resize_and_normalisation_steps(ref):
+    from phyai_b200.tools import processing as mine
+
+    ops, types, steps = (ref(f"phyai_utils_tools.processing.{m}") for m in ("ops.image_ops", "types", "steps.normalize_steps"))
+    keys = ref("phyai_utils_tools.processing")
+    g = torch.Generator().manual_seed(1)
+    for shape, target in (((2, 3, 100, 200), (224, 224)), ((1, 3, 200, 100), (224, 224)), ((1, 3, 37, 53), (64, 48)), ((1, 3, 64, 64), (64, 64))):
+        img = torch.rand(*shape, generator=g)
+        assert torch.allclose(mine.resize_with_pad(img, *target), ops.resize_with_pad(img, *target), atol=1e-6), (shape, target)
+        u8 = (img * 255).to(torch.uint8)
+        assert torch.equal(mine.resize_with_pad(u8, *target), ops.resize_with_pad(u8, *target))
+    assert torch.equal(mine.normalize_pixels(img), ops.normalize_pixels(img))
+    stats = {"observation.state": {"mean": [0.5, -1.0, 2.0], "std": [1.5, 0.5, 2.0], "min": [-1.0, -2.0, 0.0], "max": [2.0, 0.0, 4.0],
+                                   "q01": [-0.5, -1.8, 0.2], "q99": [1.5, -0.2, 3.8], "q10": [0.0, -1.5, 1.0], "q90": [1.0, -0.5, 3.0]}}
+    x = torch.randn(4, 3, generator=g)
+    for mode in ("MEAN_STD", "MIN_MAX", "QUANTILES", "QUANTILE10", "IDENTITY"):
+        outs = []
+        for ty, st, key in ((mine, mine, mine.STATE), (types, steps, keys.STATE)):
+            feats = {"observation.state": ty.PolicyFeature(ty.FeatureType.STATE, (3,))}
+            kw = dict(features=feats, norm_map={ty.FeatureType.STATE: ty.NormalizationMode(mode)}, stats=stats)
+            y = st.NormalizerStep(**kw)({key: x.clone()})[key]
+            outs.append((y, st.UnnormalizerStep(**kw)({key: y.clone()})[key]))
+        assert torch.allclose(outs[0][0], outs[1][0], atol=1e-6), mode
+        assert torch.allclose(outs[0][1], outs[1][1], atol=1e-6) and torch.allclose(outs[0][1], x, atol=1e-5), mode
+
+
+class _ChatTokenizer:
+    """Bytes + 3 as ids, with the two calls the Cosmos3 processors make on a tokenizer."""
+
+    eos_token_id = 2
+
+    def convert_tokens_to_ids(self, tok):
+        return 7
+
+    def apply_chat_template(self, chat, tokenize=True, add_generation_prompt=True):
+        text = "".join(f"<{m['role']}>{m['content']}" for m in chat) + "<assistant>"
+        return [b + 3 for b in text.encode()]
+
+
+def test_cosmos3_policy_image_preprocessing(ref):
+    from phyai_b200.tools import cosmos3 as mine
+    from phyai_b200.tools.processing import IMAGES, PIXEL_VALUES
+
+    theirs = ref("phyai_utils_tools.models.cosmos3.steps_cosmos3")
+    rng = np.random.RandomState(0)
+    for h, w in ((96, 128), (480, 640), (720, 1280), (300, 200), (1000, 900)):
+        img = (rng.rand(h, w, 3) * 255).astype("uint8")
+        for th, tw in ((480, 832), (256, 320), (544, 736)):
+            assert np.array_equal(mine.resize_and_pad_action_image(img, th, tw), theirs._resize_and_pad_action_image(img, th, tw)), (h, w, th, tw)
+        for kw in (dict(height=480, width=832, mode="policy"), dict(height=1, width=1, mode="policy", image_size=480),
+                   dict(height=1, width=1, mode="policy", image_size=224)):
+            a, b = mine.Cosmos3ImagePreprocessStep(**kw)({IMAGES: img}), theirs.Cosmos3ImagePreprocessStep(**kw)({IMAGES: img})
+            assert torch.equal(a[PIXEL_VALUES], b[PIXEL_VALUES]) and a[mine.VIDEO_SHAPE] == b[theirs.VIDEO_SHAPE], (h, w, kw)
+            assert (a[mine.META_HEIGHT], a[mine.META_WIDTH]) == (b["meta_height"], b["meta_width"])
+    # the other input forms: channel-first tensors in [0, 1] and in [-1, 1], float arrays, several frames
+    frames = [torch.rand(3, 64, 96), torch.rand(3, 64, 96) * 2 - 1, rng.rand(64, 96, 3).astype("float32")]
+    kw = dict(height=48, width=80, mode="inverse_dynamics")
+    a, b = mine.Cosmos3ImagePreprocessStep(**kw)({IMAGES: frames}), theirs.Cosmos3ImagePreprocessStep(**kw)({IMAGES: frames})
+    assert torch.equal(a[PIXEL_VALUES], b[PIXEL_VALUES]) and a[mine.VIDEO_SHAPE] == b[theirs.VIDEO_SHAPE] == (3, 48, 80)
+    assert mine.Cosmos3ImagePreprocessStep(**kw).get_config() == theirs.Cosmos3ImagePreprocessStep(**kw).get_config()
+
+
+def test_cosmos3_policy_processor_end_to_end(ref, tmp_path, monkeypatch):
+    from phyai_b200.tools import cosmos3 as mine
+
+    theirs = ref("phyai_utils_tools.models.cosmos3.processor_cosmos3")
+    monkeypatch.setattr(theirs, "get_tokenizer", lambda name: _ChatTokenizer())      # no tokenizer files offline
+    stats = tmp_path / "stats.json"
+    stats.write_text(json.dumps({"global": {"mean": [0.1] * 10, "std": [2.0] * 10, "min": [-1.0] * 10, "max": [3.0] * 10, "q01": [-0.5] * 10,
+                                            "q99": [2.5] * 10}, "global_raw": {"q01": [-3.0] * 10, "q99": [5.0] * 10}}))
+    rng = np.random.RandomState(1)
+    img = (rng.rand(240, 320, 3) * 255).astype("uint8")
+    act = rng.rand(5, 10).astype("float32")
+    cases = [dict(mode="policy", prompt_format="plain", image_size=480), dict(mode="policy", prompt_format="json", image_size=480, view_point="wrist_view"),
+             dict(mode="forward_dynamics", prompt_format="plain", append_metadata=False), dict(mode="inverse_dynamics", prompt_format="json", view_point="none"),
+             dict(mode="policy", negative_prompt="bad video", fps=10.0, action_chunk_size=32, cond_frame_indexes=(0, 1))]
+    for kw in cases:
+        common = dict(domain_name="droid_lerobot", **kw)
+        a = mine.Cosmos3PolicyProcessor(tokenizer=_ChatTokenizer(), **common)
+        b = theirs.Cosmos3PolicyProcessor(tokenizer_name_or_path="unused", **common)
+        raw = {"images": img, "task": "put the cup on the plate", "cond_action": act}
+        x, y = a.preprocess(dict(raw)), b.preprocess(dict(raw))
+        for f in ("pixel_values", "text_ids", "text_mask", "neg_text_ids", "neg_text_mask"):
+            assert torch.equal(getattr(x, f), getattr(y, f)), (kw, f)
+        assert (x.cond_action is None) == (y.cond_action is None) and (x.cond_action is None or torch.equal(x.cond_action, y.cond_action))
+        for f in ("domain_id", "mode", "action_chunk", "raw_action_dim", "video_shape", "cond_frame_indexes"):
+            assert getattr(x, f) == getattr(y, f), (kw, f)
+    out = {"action": torch.from_numpy(rng.rand(1, 16, 64).astype("float32")) * 2 - 1, "video": torch.zeros(2), "pixels": torch.ones(2)}
+    for norm in ("meanstd", "minmax", "quantile", "quantile_rot"):
+        common = dict(domain_name="droid_lerobot", action_stats_path=str(stats), action_normalization=norm)
+        a = mine.Cosmos3PolicyProcessor(tokenizer=_ChatTokenizer(), **common).postprocess(out)
+        b = theirs.Cosmos3PolicyProcessor(tokenizer_name_or_path="unused", **common).postprocess(out)
+        assert set(a) == set(b) and torch.allclose(a["action"], b["action"], atol=1e-6) and a["action"].shape == (1, 16, 10), norm
+    a = mine.Cosmos3PolicyProcessor(tokenizer=_ChatTokenizer(), domain_name="pusht").postprocess(out["action"])
+    b = theirs.Cosmos3PolicyProcessor(tokenizer_name_or_path="unused", domain_name="pusht").postprocess(out["action"])
+    assert torch.equal(a["action"], b["action"]) and a["action"].shape == (1, 16, 2)
+
+
+def test_cosmos3_generation_tokenisation(ref, monkeypatch):
+    from phyai_b200.tools import cosmos3 as mine
+
+    theirs = ref("phyai_utils_tools.models.cosmos3.processor_cosmos3")
+    monkeypatch.setattr(theirs, "get_tokenizer", lambda name: _ChatTokenizer())
+    for kw in (dict(), dict(use_system_prompt=True, fps=24.0, num_frames=93, height=720, width=1280),
+               dict(fps=16.0, num_frames=1, height=480, width=832, aspect_ratio="16,9"), dict(fps=24.0, num_frames=93, height=720, width=1280, append_metadata=False),
+               dict(negative_prompt="ugly")):
+        a, b = mine.Cosmos3Processor(tokenizer=_ChatTokenizer(), **kw), theirs.Cosmos3Processor("unused", **kw)
+        for prompt in ("A robot arm stacks cups", '{"scene": "lab"}'):
+            for neg in (None, "", "blurry"):
+                if neg is None and "negative_prompt" not in kw:
+                    continue          # the default negative prompt is a data file of the upstream release, not part of this package
+                (p1, n1), (p2, n2) = a.tokenize_pair(prompt, neg), b.tokenize_pair(prompt, neg)
+                assert torch.equal(p1.text_ids, p2.text_ids) and torch.equal(n1.text_ids, n2.text_ids) and torch.equal(p1.text_mask, p2.text_mask)
+    shipped = REF / "phyai_utils_tools" / "models" / "cosmos3" / "neg_prompts.json"
+    if shipped.is_file():             # given the release's file, the default negative prompt is the reference's byte for byte
+        assert mine.cosmos3_default_negative_prompt(shipped) == ref("phyai_utils_tools.models.cosmos3.steps_cosmos3").cosmos3_default_negative_prompt()

@@ -104,14 +104,14 @@ def test_cosmos3_captions_and_tokenization():
     assert cap == "A robot arm. The video is 3.9 seconds long and is of 24 FPS. This video is of 720x1280 resolution."
     j = json.loads(c3.cosmos3_generation_caption('{"scene": "lab"}', fps=24, num_frames=1, height=480, width=832, aspect_ratio="16,9"))
     assert j == {"scene": "lab", "resolution": {"H": 480, "W": 832}, "aspect_ratio": "16,9"}
-    a = json.loads(c3.cosmos3_action_json_caption("open the drawer", view_point="ego", num_frames=33, fps=10, height=480, width=832))
+    a = json.loads(c3.cosmos3_action_json_caption("open the drawer", view_point="ego_view", num_frames=33, fps=10, height=480, width=832))
     assert a["actions"] == [{"time": "0:00-0:03", "description": "open the drawer."}] and a["duration"] == "3s" and a["aspect_ratio"] == "16,9"
     assert c3.resolve_domain_id("LIBERO") == 5 and c3.resolve_domain_id(3) == 3 and c3.resolve_raw_action_dim("pusht") == 2
     with pytest.raises(ValueError):
         c3.resolve_domain_id("nope")
     with pytest.raises(ValueError):
         c3.resolve_raw_action_dim(4)
-    assert c3.find_closest_target_size(480, 640, "480") == (544, 736) and c3.aspect_ratio_str(30, 20) == "3,2"
+    assert c3.find_closest_target_size(480, 640, "480") == (736, 544) and c3.aspect_ratio_str(30, 20) == "3,2"      # (width, height)
     proc = c3.Cosmos3Processor(tokenizer=FakeChatTokenizer(), fps=24, num_frames=93, height=720, width=1280)
     pos, neg = proc.tokenize_pair("A robot arm")
     assert pos.text_ids.shape[0] == 1 and pos.text_ids[0, -2:].tolist() == [2, 7] and pos.text_mask.all()
@@ -120,15 +120,39 @@ def test_cosmos3_captions_and_tokenization():
 
 
 def test_cosmos3_policy_processor_and_postprocess(tmp_path):
-    p = c3.Cosmos3PolicyProcessor(tokenizer=FakeChatTokenizer(), domain="pusht", mode="forward_dynamics", action_chunk_size=8,
-                                  action_stats={"q01": [-2.0, -4.0], "q99": [2.0, 4.0]})
+    stats = tmp_path / "stats.json"
+    stats.write_text(json.dumps({"global": {"q01": [-2.0, -4.0], "q99": [2.0, 4.0]}}))
+    p = c3.Cosmos3PolicyProcessor(tokenizer=FakeChatTokenizer(), domain_name="pusht", mode="forward_dynamics", action_chunk_size=8,
+                                  image_size=480, prompt_format="json", fps=10.0, action_stats_path=stats, action_normalization="quantile",
+                                  cond_frame_indexes=(0,))
     img = (np.random.rand(96, 128, 3) * 255).astype("uint8")
-    out = p.preprocess({"image": img, "task": "push the T", "cond_action": np.ones((5, 2), dtype="float32")})
-    assert out.video_shape == (3, 34, 46) and out.cond_video_pixels.shape == (1, 3, 1, 544, 736) and float(out.cond_video_pixels.min()) >= -1
+    out = p.preprocess({"images": img, "task": "push the T", "cond_action": np.ones((5, 2), dtype="float32")})
+    # a 4:3 frame scaled to 480 rows falls into the 480 tier, whose 4:3 bucket is 736 x 544; the frame is small, so it is
+    # not enlarged: it sits in the top-left corner and the margins repeat its edge
+    assert out.video_shape == (1, 544, 736) and out.pixel_values.shape == (1, 3, 1, 544, 736)
+    assert -1.0 <= float(out.pixel_values.min()) and float(out.pixel_values.max()) <= 1.0
+    corner = torch.from_numpy(img).permute(2, 0, 1).float() / 127.5 - 1.0
+    assert torch.equal(out.pixel_values[0, :, 0, :96, :128], corner)
+    assert torch.equal(out.pixel_values[0, :, 0, 300, :128], corner[:, -1]) and torch.equal(out.pixel_values[0, :, 0, :96, 500], corner[:, :, -1])
     assert out.domain_id == 4 and out.raw_action_dim == 2 and out.action_chunk == 8 and out.mode == "forward_dynamics"
+    assert out.cond_frame_indexes == (0,)
     assert out.cond_action.shape == (1, 8, 64) and out.cond_action[0, 7, :2].tolist() == [1.0, 1.0] and out.cond_action[0, :, 2:].abs().sum() == 0
-    res = p.postprocess({"action": torch.zeros(1, 8, 64), "video": torch.zeros(1)})
-    assert res["action"].shape == (1, 8, 2) and torch.allclose(res["action"], torch.zeros(1, 8, 2)) and "video" in res
+    text = ByteTokenizer().decode(out.text_ids[0])
+    assert '"actions": [{"time": "0:00-0:01", "description": "push the T."}]' in text and '"resolution": {"H": 544, "W": 736}' in text
+    assert "first-person perspective" in text                                                     # the default view point's sentence
+    res = p.postprocess({"action": torch.zeros(1, 8, 64), "video": torch.zeros(1), "other": 1})
+    assert res["action"].shape == (1, 8, 2) and torch.allclose(res["action"], torch.zeros(1, 8, 2)) and set(res) == {"action", "video"}
+    assert torch.allclose(p.postprocess(torch.ones(1, 8, 64))["action"], torch.tensor([2.0, 4.0]).expand(1, 8, 2))
+    plain = c3.Cosmos3PolicyProcessor(tokenizer=FakeChatTokenizer(), domain_name="libero", raw_action_dim=7, height=32, width=48, fps=8.0,
+                                      action_chunk_size=15)
+    got = plain.preprocess({"images": [torch.rand(3, 32, 48), torch.rand(3, 32, 48)], "prompt": "stack the blocks", "domain_id": 9})
+    assert got.video_shape == (2, 32, 48) and got.cond_action is None and got.domain_id == 9 and got.mode == "policy"
+    assert "stack the blocks. The video is 2.0 seconds long and is of 8 FPS. This video is of 32x48 resolution." in ByteTokenizer().decode(got.text_ids[0])
+    assert plain.postprocess(torch.ones(1, 15, 64))["action"].shape == (1, 15, 7)                 # no statistics: model units
+    with pytest.raises(ValueError, match="conflicts with the 2 on record"):
+        c3.Cosmos3PolicyProcessor(tokenizer=FakeChatTokenizer(), domain_name="pusht", raw_action_dim=3)
+    with pytest.raises(ValueError, match="action_normalization"):
+        c3.Cosmos3PolicyProcessor(tokenizer=FakeChatTokenizer(), domain_name="pusht", action_normalization="zscore")
     post = c3.Cosmos3GenerationPostProcessor(fps=24)
     frames = post.postprocess(torch.rand(1, 3, 5, 16, 24))["frames"]
     assert frames.shape == (5, 16, 24, 3) and frames.dtype == torch.uint8
