@@ -33,7 +33,7 @@ def main() -> None:
     engine = Engine(EngineArgs("pi05", PI05Args(checkpoint_dir=a.checkpoint, max_batch_size=1, inputs_image_shape=[[224, 224, 3]] * 3),
                                EngineConfig(device=DeviceConfig(dev, torch.bfloat16))))
     tok = get_tokenizer(a.tokenizer) if a.tokenizer else ByteTokenizer()
-    proc = (PI05Processor.from_pretrained(a.checkpoint, tokenizer=tok, device=dev) if a.checkpoint and (Path(a.checkpoint) / "policy_preprocessor.json").is_file()
+    proc = (PI05Processor.from_pretrained(a.checkpoint, tokenizer=tok, device=dev, action_dim=7) if a.checkpoint and (Path(a.checkpoint) / "policy_preprocessor.json").is_file()
             else PI05Processor(tokenizer=tok, device=dev, action_dim=7))
     obs = {"images": [torch.rand(1, 3, 480, 640) for _ in range(3)], "state": torch.rand(1, 8) * 2 - 1, "task": [a.task]}
     lat = []

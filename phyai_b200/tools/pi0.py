@@ -16,6 +16,7 @@ from .processing import (ACTION, INPUT_IDS, LANG_LENS, PIXEL_VALUES, PROMPT, STA
                          NormalizationMode, NormalizeImageStep, NormalizerStep, ProcessorPipeline, ProcessorStep,
                          ProcessorStepRegistry, ResizeWithPadStep, SliceActionStep, TokenizerStep, Transition, UnnormalizerStep)
 
+PI0_DEFAULT_TOKENIZER_NAME = "google/paligemma-3b-pt-224"
 PI0_NORM_MAP = {FeatureType.VISUAL: NormalizationMode.IDENTITY, FeatureType.STATE: NormalizationMode.MEAN_STD,
                 FeatureType.ACTION: NormalizationMode.MEAN_STD}
 
@@ -69,13 +70,32 @@ class PI0ProcessedInputs:
     state: torch.Tensor
 
 
+def _is_vision_glue(step: Any) -> bool:
+    return isinstance(step, (ResizeWithPadStep, NormalizeImageStep))
+
+
+def _two_or_three(num_images: int) -> int:
+    if int(num_images) not in (2, 3):
+        raise ValueError(f"pi0 takes exactly 2 or 3 images, got {num_images}")
+    return int(num_images)
+
+
 class PI0Processor(BaseModelProcessor):
-    def __init__(self, *, image_size: int = 224, num_images: int = 3, tokenizer_max_length: int = 48, max_state_dim: int = 32,
-                 action_dim: int | None = None, tokenizer_name: str = "google/paligemma-3b-pt-224", tokenizer: Any = None,
-                 dataset_stats: dict | None = None, normalize_pixels: bool = False, device="cpu", params_dtype=torch.bfloat16) -> None:
-        self.image_size, self.num_images, self.tokenizer_max_length = image_size, num_images, tokenizer_max_length
-        self.max_state_dim, self.action_dim, self.dataset_stats = max_state_dim, action_dim, dataset_stats
-        self.normalize_pixels, self.device, self.params_dtype, self.tokenizer_name = normalize_pixels, device, params_dtype, tokenizer_name
+    """Pi0 pre / post processing in lerobot's conventions: cameras resized with padding and mapped to [-1, 1]
+    (``normalize_pixels``, on by default), state and action normalised by mean / std, the state zero-padded to
+    ``max_state_dim`` and handed over as a tensor, the task newline-terminated and tokenised to 48 tokens; the action
+    chunk cut to ``action_dim``, un-normalised and returned on the CPU. ``save_pretrained`` leaves the resize / pixel
+    steps out of the json; ``from_pretrained`` puts them back (and a state-padding step and an action cut where the files
+    have none). Arguments and behaviour follow phyai-utils-tools/src/phyai_utils_tools/models/pi0/processor_pi0.py:80-300."""
+
+    def __init__(self, *, image_size: int = 224, num_channels: int = 3, num_images: int = 3, tokenizer_max_length: int = 48,
+                 max_state_dim: int = 32, action_dim: int | None = None, tokenizer_name: str = PI0_DEFAULT_TOKENIZER_NAME,
+                 tokenizer: Any = None, dataset_stats: dict | None = None, normalize_pixels: bool = True, image_pad_value: float = 0.0,
+                 device="cpu", params_dtype=torch.bfloat16) -> None:
+        self.image_size, self.num_channels, self.num_images = int(image_size), int(num_channels), _two_or_three(num_images)
+        self.tokenizer_max_length, self.max_state_dim, self.action_dim = int(tokenizer_max_length), int(max_state_dim), action_dim
+        self.tokenizer_name, self.dataset_stats = tokenizer_name, dataset_stats
+        self.normalize_pixels, self.image_pad_value, self.device, self.params_dtype = bool(normalize_pixels), float(image_pad_value), device, params_dtype
         if tokenizer is None:
             from .tokenizer import get_tokenizer
 
@@ -87,38 +107,73 @@ class PI0Processor(BaseModelProcessor):
     def _out(t: Transition) -> PI0ProcessedInputs:
         return PI0ProcessedInputs(t[PIXEL_VALUES], t[INPUT_IDS], t[LANG_LENS], t[STATE])
 
-    def build_preprocessor(self) -> ProcessorPipeline:
-        steps: list[ProcessorStep] = [ResizeWithPadStep(self.image_size, self.image_size)]
+    def _vision_steps(self) -> list[ProcessorStep]:
+        steps: list[ProcessorStep] = [ResizeWithPadStep(self.image_size, self.image_size, self.image_pad_value)]
         if self.normalize_pixels:
             steps.append(NormalizeImageStep())
-        steps += [NormalizerStep(features=_features(self.dataset_stats), norm_map=PI0_NORM_MAP, stats=self.dataset_stats),
-                  PadStateStep(self.max_state_dim), Pi0PromptPrepareStep(),
-                  TokenizerStep(tokenizer=self.tokenizer, max_length=self.tokenizer_max_length, tokenizer_name=self.tokenizer_name),
-                  DeviceStep(device=str(self.device), float_dtype=str(self.params_dtype).replace("torch.", ""))]
-        return ProcessorPipeline(steps, "policy_preprocessor", to_output=self._out)
+        return steps
+
+    def build_preprocessor(self) -> ProcessorPipeline:
+        steps = self._vision_steps() + [
+            NormalizerStep(features=_features(self.dataset_stats), norm_map=PI0_NORM_MAP, stats=self.dataset_stats, device=self.device),
+            PadStateStep(self.max_state_dim), Pi0PromptPrepareStep(),
+            TokenizerStep(tokenizer=self.tokenizer, max_length=self.tokenizer_max_length, tokenizer_name=self.tokenizer_name),
+            DeviceStep(device=self.device, float_dtype=self.params_dtype)]
+        return ProcessorPipeline(steps, "pi0_preprocessor", to_output=self._out)
 
     def build_postprocessor(self) -> ProcessorPipeline:
-        steps = [DeviceStep(device="cpu", float_dtype="float32"),
-                 UnnormalizerStep(features=_features(self.dataset_stats), norm_map=PI0_NORM_MAP, stats=self.dataset_stats),
-                 SliceActionStep(self.action_dim)]
-        return ProcessorPipeline(steps, "policy_postprocessor", to_transition=lambda a: {ACTION: a}, to_output=lambda t: t[ACTION])
+        steps = [SliceActionStep(self.action_dim),
+                 UnnormalizerStep(features=_features(self.dataset_stats), norm_map=PI0_NORM_MAP, stats=self.dataset_stats, device=self.device),
+                 DeviceStep(device="cpu")]
+        return ProcessorPipeline(steps, "pi0_postprocessor", to_transition=lambda a: {ACTION: a}, to_output=lambda t: t[ACTION])
 
     def save_pretrained(self, directory: str | Path) -> None:
-        self.preprocessor.save_pretrained(directory, config_filename=PRE_JSON)
-        self.postprocessor.save_pretrained(directory, config_filename=POST_JSON)
+        ProcessorPipeline([s for s in self.preprocessor.steps if not _is_vision_glue(s)], "policy_preprocessor").save_pretrained(
+            directory, config_filename=PRE_JSON)
+        ProcessorPipeline(list(self.postprocessor.steps), "policy_postprocessor").save_pretrained(directory, config_filename=POST_JSON)
 
     @classmethod
-    def from_pretrained(cls, directory: str | Path, *, tokenizer: Any = None, device="cpu", params_dtype=torch.bfloat16) -> "PI0Processor":
+    def from_pretrained(cls, directory: str | Path, *, tokenizer: Any = None, tokenizer_name: str = PI0_DEFAULT_TOKENIZER_NAME,
+                        image_size: int = 224, num_channels: int = 3, num_images: int = 3, max_state_dim: int = 32,
+                        action_dim: int | None = None, normalize_pixels: bool = True, image_pad_value: float = 0.0, device="cpu",
+                        params_dtype=torch.bfloat16) -> "PI0Processor":
+        if tokenizer is None:
+            from .tokenizer import get_tokenizer
+
+            tokenizer = get_tokenizer(tokenizer_name)
         self = cls.__new__(cls)
-        self.device, self.params_dtype, self.tokenizer = device, params_dtype, tokenizer
-        sk = {"tokenizer_processor": {"tokenizer": tokenizer} if tokenizer is not None else {},
-              "device_processor": {"device": str(device), "float_dtype": str(params_dtype).replace("torch.", "")}}
-        self.preprocessor = ProcessorPipeline.from_pretrained(directory, PRE_JSON, step_kwargs=sk, to_output=cls._out)
-        self.postprocessor = ProcessorPipeline.from_pretrained(
-            directory, POST_JSON, step_kwargs={"device_processor": {"device": "cpu", "float_dtype": "float32"}},
-            to_transition=lambda a: {ACTION: a}, to_output=lambda t: t[ACTION])
+        self.image_size, self.num_channels, self.num_images = int(image_size), int(num_channels), _two_or_three(num_images)
+        self.action_dim, self.tokenizer_name, self.tokenizer, self.dataset_stats = action_dim, tokenizer_name, tokenizer, None
+        self.normalize_pixels, self.image_pad_value, self.device, self.params_dtype = bool(normalize_pixels), float(image_pad_value), device, params_dtype
+        pre = ProcessorPipeline.from_pretrained(directory, PRE_JSON, step_kwargs={
+            "tokenizer_processor": {"tokenizer": tokenizer}, "device_processor": {"device": device, "float_dtype": params_dtype},
+            "normalizer_processor": {"device": device}})
+        post_kw: dict[str, dict] = {"unnormalizer_processor": {"device": device}}
+        if action_dim is not None:
+            post_kw["slice_action_step"] = {"action_dim": action_dim}
+        post = ProcessorPipeline.from_pretrained(directory, POST_JSON, step_kwargs=post_kw)
+        self.tokenizer_max_length = next((s.max_length for s in pre.steps if isinstance(s, TokenizerStep)), 48)
+        self.max_state_dim = next((s.max_state_dim for s in pre.steps if isinstance(s, PadStateStep)), int(max_state_dim))
+        steps = [*self._vision_steps(), *[s for s in pre.steps if not _is_vision_glue(s)]]
+        if not any(isinstance(s, PadStateStep) for s in steps):
+            # behind the last normaliser (statistics cover the real state width), else in front of the prompt / tokenizer steps
+            after_norm = [i + 1 for i, s in enumerate(steps) if isinstance(s, NormalizerStep)]
+            before_text = [i for i, s in enumerate(steps) if isinstance(s, (Pi0PromptPrepareStep, TokenizerStep))]
+            at = after_norm[-1] if after_norm else (before_text[0] if before_text else len(steps))
+            steps.insert(at, PadStateStep(self.max_state_dim))
+        pre.steps, pre.name, pre.to_output = steps, "pi0_preprocessor", cls._out
+        if not any(isinstance(s, SliceActionStep) for s in post.steps):
+            post.steps = [SliceActionStep(action_dim), *post.steps]
+        post.name, post.to_transition, post.to_output = "pi0_postprocessor", (lambda a: {ACTION: a}), (lambda t: t[ACTION])
+        self.preprocessor, self.postprocessor = pre, post
         return self
 
 
-__all__ = ["Pi0PromptPrepareStep", "Pi0NewLineProcessor", "PadStateStep", "PI0ProcessedInputs", "PI0Processor", "PI0_NORM_MAP",
+def make_pi0_processors(**kw) -> tuple[ProcessorPipeline, ProcessorPipeline]:
+    p = PI0Processor(**kw)
+    return p.preprocessor, p.postprocessor
+
+
+__all__ = ["Pi0PromptPrepareStep", "Pi0NewLineProcessor", "PadStateStep", "PI0ProcessedInputs", "PI0Processor", "make_pi0_processors", "PI0_NORM_MAP",
+           "PI0_DEFAULT_TOKENIZER_NAME",
            "STATE_FEATURE", "ACTION_FEATURE"]

@@ -46,25 +46,36 @@ def build_prompts(tasks: list[str], bins: np.ndarray) -> list[str]:
 @ProcessorStepRegistry.register("pi05_prepare_state_tokenizer_processor_step")
 @dataclass
 class StateTokenizerPrepareStep(ProcessorStep):
-    """Normalised state + task text -> the Pi0.5 prompt string (the state enters the model as text)."""
+    """Normalised state + task text -> the Pi0.5 prompt string (the state enters the model as text). Without a state the
+    prompt carries the task alone. ``pad_state`` first pads the state with zeros to ``max_state_dim`` (lerobot's
+    convention: the prompt then always lists that many bins); off by default, as in the reference
+    (phyai-utils-tools/src/phyai_utils_tools/models/pi05/steps_pi05.py:30-68), whose prompt lists the bins of the state
+    it is given. Like lerobot's step of this name it saves no configuration unless padding is on."""
 
+    num_bins: int = STATE_NUM_BINS
     max_state_dim: int = 32
+    pad_state: bool = False
 
     def __call__(self, t: Transition) -> Transition:
-        state, tasks = t.get(STATE), t.get(TASK)
-        if state is None or tasks is None:
-            raise ValueError("the Pi0.5 prompt step needs 'state' and 'task'")
+        tasks = t.get(TASK)
+        if tasks is None:
+            raise ValueError("the Pi0.5 prompt step needs 'task'")
         if isinstance(tasks, str):
             tasks = [tasks]
+        out = dict(t)
+        state = t.get(STATE)
+        if state is None:
+            out[PROMPT] = [f"Task: {s.strip().replace('_', ' ').replace(chr(10), ' ')};\nAction: " for s in tasks]
+            return out
         if state.dim() == 1:
             state = state[None]
-        if state.shape[-1] < self.max_state_dim:
+        if self.pad_state and state.shape[-1] < self.max_state_dim:
             state = torch.nn.functional.pad(state, (0, self.max_state_dim - state.shape[-1]))
-        t[PROMPT] = build_prompts(list(tasks), discretize_state(state))
-        return t
+        out[PROMPT] = build_prompts(list(tasks), discretize_state(state, self.num_bins))
+        return out
 
     def get_config(self):
-        return {"max_state_dim": self.max_state_dim}
+        return {"pad_state": True, "max_state_dim": self.max_state_dim} if self.pad_state else {}
 
 
 @dataclass
@@ -77,23 +88,33 @@ class PI05ProcessedInputs:
 
 
 def _features(stats: dict | None) -> dict:
-    f = {}
-    for name, kind in ((STATE_FEATURE, FeatureType.STATE), (ACTION_FEATURE, FeatureType.ACTION)):
-        if stats and name in stats:
-            width = len(next(iter(stats[name].values())))
-            f[name] = {"type": kind.value, "shape": [width]}
-    return f
+    return {name: {"type": kind.value, "shape": []} for name, kind in ((STATE_FEATURE, FeatureType.STATE), (ACTION_FEATURE, FeatureType.ACTION))
+            if stats and name in stats}
+
+
+def _is_vision_glue(step: Any) -> bool:
+    """Steps that are this package's, not part of a lerobot processor json (lerobot resizes inside the model)."""
+    return isinstance(step, (ResizeWithPadStep, NormalizeImageStep))
 
 
 class PI05Processor(BaseModelProcessor):
-    def __init__(self, *, image_size: int = 224, num_images: int = 3, tokenizer_max_length: int = 200, action_dim: int | None = None,
-                 tokenizer_name: str = PI05_DEFAULT_TOKENIZER_NAME, tokenizer: Any = None, dataset_stats: dict | None = None,
-                 normalize_pixels: bool = False, image_pad_value: float = 0.0, device="cpu", params_dtype: torch.dtype = torch.bfloat16,
-                 max_state_dim: int = 32) -> None:
-        self.image_size, self.num_images, self.tokenizer_max_length = int(image_size), int(num_images), int(tokenizer_max_length)
-        self.action_dim, self.tokenizer_name, self.dataset_stats = action_dim, tokenizer_name, dataset_stats
-        self.normalize_pixels, self.image_pad_value = bool(normalize_pixels), float(image_pad_value)
-        self.device, self.params_dtype, self.max_state_dim = device, params_dtype, max_state_dim
+    """Pi0.5 pre / post processing: cameras resized with padding (optionally to [-1, 1]), state and action normalised by
+    the dataset statistics (quantiles; none given: identity), the state written into the prompt as bins, tokens padded to
+    ``tokenizer_max_length``; the action chunk un-normalised, cut to ``action_dim`` and returned on the CPU.
+
+    ``save_pretrained`` writes the lerobot-portable core (``policy_preprocessor.json`` / ``policy_postprocessor.json``
+    with the statistics beside them): the resize / pixel steps and the action cut are rebuilt from arguments by
+    ``from_pretrained``, which therefore also loads the processor files of a lerobot checkpoint. Arguments and behaviour
+    follow phyai-utils-tools/src/phyai_utils_tools/models/pi05/processor_pi05.py:101-335."""
+
+    def __init__(self, *, image_size: int = 224, num_channels: int = 3, num_images: int = 3, tokenizer_max_length: int = 200,
+                 action_dim: int | None = None, tokenizer_name: str = PI05_DEFAULT_TOKENIZER_NAME, tokenizer: Any = None,
+                 dataset_stats: dict | None = None, normalize_pixels: bool = False, image_pad_value: float = 0.0, device="cpu",
+                 params_dtype: torch.dtype = torch.bfloat16, pad_state: bool = False, max_state_dim: int = 32) -> None:
+        self.image_size, self.num_channels, self.num_images = int(image_size), int(num_channels), int(num_images)
+        self.tokenizer_max_length, self.action_dim, self.tokenizer_name = int(tokenizer_max_length), action_dim, tokenizer_name
+        self.dataset_stats, self.normalize_pixels, self.image_pad_value = dataset_stats, bool(normalize_pixels), float(image_pad_value)
+        self.device, self.params_dtype, self.pad_state, self.max_state_dim = device, params_dtype, bool(pad_state), int(max_state_dim)
         if tokenizer is None:
             from .tokenizer import get_tokenizer
 
@@ -101,40 +122,65 @@ class PI05Processor(BaseModelProcessor):
         self.tokenizer = tokenizer
         self.preprocessor, self.postprocessor = self.build_preprocessor(), self.build_postprocessor()
 
-    def _dtype_name(self) -> str:
-        return str(self.params_dtype).replace("torch.", "")
+    @staticmethod
+    def _inputs(t: Transition) -> PI05ProcessedInputs:
+        return PI05ProcessedInputs(t[PIXEL_VALUES], t[INPUT_IDS], t[LANG_LENS])
 
-    def build_preprocessor(self) -> ProcessorPipeline:
+    def _vision_steps(self) -> list[ProcessorStep]:
         steps: list[ProcessorStep] = [ResizeWithPadStep(self.image_size, self.image_size, self.image_pad_value)]
         if self.normalize_pixels:
             steps.append(NormalizeImageStep())
-        steps += [NormalizerStep(features=_features(self.dataset_stats), norm_map=PI05_NORM_MAP, stats=self.dataset_stats),
-                  StateTokenizerPrepareStep(self.max_state_dim),
-                  TokenizerStep(tokenizer=self.tokenizer, max_length=self.tokenizer_max_length, tokenizer_name=self.tokenizer_name),
-                  DeviceStep(device=str(self.device), float_dtype=self._dtype_name())]
-        return ProcessorPipeline(steps, "policy_preprocessor", to_output=lambda t: PI05ProcessedInputs(t[PIXEL_VALUES], t[INPUT_IDS], t[LANG_LENS]))
+        return steps
+
+    def build_preprocessor(self) -> ProcessorPipeline:
+        steps = self._vision_steps() + [
+            NormalizerStep(features=_features(self.dataset_stats), norm_map=PI05_NORM_MAP, stats=self.dataset_stats, device=self.device),
+            StateTokenizerPrepareStep(max_state_dim=self.max_state_dim, pad_state=self.pad_state),
+            TokenizerStep(tokenizer=self.tokenizer, max_length=self.tokenizer_max_length, tokenizer_name=self.tokenizer_name),
+            DeviceStep(device=self.device, float_dtype=self.params_dtype)]
+        return ProcessorPipeline(steps, "pi05_preprocessor", to_output=self._inputs)
 
     def build_postprocessor(self) -> ProcessorPipeline:
-        steps = [DeviceStep(device="cpu", float_dtype="float32"),
-                 UnnormalizerStep(features=_features(self.dataset_stats), norm_map=PI05_NORM_MAP, stats=self.dataset_stats),
-                 SliceActionStep(self.action_dim)]
-        return ProcessorPipeline(steps, "policy_postprocessor", to_transition=lambda a: {ACTION: a}, to_output=lambda t: t[ACTION])
+        steps = [UnnormalizerStep(features=_features(self.dataset_stats), norm_map=PI05_NORM_MAP, stats=self.dataset_stats, device=self.device),
+                 SliceActionStep(self.action_dim), DeviceStep(device="cpu")]
+        return ProcessorPipeline(steps, "pi05_postprocessor", to_transition=lambda a: {ACTION: a}, to_output=lambda t: t[ACTION])
 
     def save_pretrained(self, directory: str | Path) -> None:
-        self.preprocessor.save_pretrained(directory, config_filename=PRE_JSON)
-        self.postprocessor.save_pretrained(directory, config_filename=POST_JSON)
+        ProcessorPipeline([s for s in self.preprocessor.steps if not _is_vision_glue(s)], "policy_preprocessor").save_pretrained(
+            directory, config_filename=PRE_JSON)
+        ProcessorPipeline([s for s in self.postprocessor.steps if not isinstance(s, SliceActionStep)], "policy_postprocessor").save_pretrained(
+            directory, config_filename=POST_JSON)
 
     @classmethod
-    def from_pretrained(cls, directory: str | Path, *, tokenizer: Any = None, device="cpu", params_dtype=torch.bfloat16, **kw) -> "PI05Processor":
-        """Rebuild from a checkpoint's two processor jsons (statistics come from their sidecars)."""
+    def from_pretrained(cls, directory: str | Path, *, tokenizer: Any = None, tokenizer_name: str = PI05_DEFAULT_TOKENIZER_NAME,
+                        image_size: int = 224, num_channels: int = 3, num_images: int = 3, action_dim: int | None = None,
+                        normalize_pixels: bool = False, image_pad_value: float = 0.0, device="cpu",
+                        params_dtype: torch.dtype = torch.bfloat16) -> "PI05Processor":
+        """Rebuild from a checkpoint's two processor jsons (statistics come from their sidecars). The tokenizer object and
+        the model's device are injected into the steps a json cannot carry; the postprocessor keeps the device the
+        checkpoint names (actions return to the host). Resize / pixel steps go in front and the action cut behind
+        unless the files already hold them."""
+        if tokenizer is None:
+            from .tokenizer import get_tokenizer
+
+            tokenizer = get_tokenizer(tokenizer_name)
         self = cls.__new__(cls)
-        self.device, self.params_dtype, self.tokenizer = device, params_dtype, tokenizer
-        sk = {"tokenizer_processor": {"tokenizer": tokenizer} if tokenizer is not None else {},
-              "device_processor": {"device": str(device), "float_dtype": str(params_dtype).replace("torch.", "")}}
-        pre = ProcessorPipeline.from_pretrained(directory, PRE_JSON, step_kwargs=sk)
-        pre.to_output = lambda t: PI05ProcessedInputs(t[PIXEL_VALUES], t[INPUT_IDS], t[LANG_LENS])
-        post = ProcessorPipeline.from_pretrained(directory, POST_JSON, step_kwargs={"device_processor": {"device": "cpu", "float_dtype": "float32"}})
-        post.to_transition, post.to_output = (lambda a: {ACTION: a}), (lambda t: t[ACTION])
+        self.image_size, self.num_channels, self.num_images = int(image_size), int(num_channels), int(num_images)
+        self.action_dim, self.tokenizer_name, self.tokenizer, self.dataset_stats = action_dim, tokenizer_name, tokenizer, None
+        self.normalize_pixels, self.image_pad_value = bool(normalize_pixels), float(image_pad_value)
+        self.device, self.params_dtype = device, params_dtype
+        pre = ProcessorPipeline.from_pretrained(directory, PRE_JSON, step_kwargs={
+            "tokenizer_processor": {"tokenizer": tokenizer}, "device_processor": {"device": device}})
+        post = ProcessorPipeline.from_pretrained(directory, POST_JSON, step_kwargs={"unnormalizer_processor": {"device": device}})
+        self.tokenizer_max_length = next((s.max_length for s in pre.steps if isinstance(s, TokenizerStep)), 200)
+        prep = next((s for s in pre.steps if isinstance(s, StateTokenizerPrepareStep)), None)
+        self.pad_state, self.max_state_dim = (prep.pad_state, prep.max_state_dim) if prep is not None else (False, 32)
+        if not any(_is_vision_glue(s) for s in pre.steps):
+            pre.steps = [*self._vision_steps(), *pre.steps]
+        if not any(isinstance(s, SliceActionStep) for s in post.steps):
+            post.steps = [*post.steps, SliceActionStep(action_dim)]
+        pre.name, pre.to_output = "pi05_preprocessor", cls._inputs
+        post.name, post.to_transition, post.to_output = "pi05_postprocessor", (lambda a: {ACTION: a}), (lambda t: t[ACTION])
         self.preprocessor, self.postprocessor = pre, post
         return self
 

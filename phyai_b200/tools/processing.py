@@ -371,12 +371,13 @@ class UnnormalizerStep(_NormalizeBase):
 @ProcessorStepRegistry.register("tokenizer_processor")
 @dataclass
 class TokenizerStep(ProcessorStep):
-    """``prompt`` (or ``task``) -> ``input_ids`` (B, max_length) right-padded and ``lang_lens`` (B,)."""
+    """``prompt`` (else ``task``) -> ``input_ids`` (B, max_length) right-padded and ``lang_lens`` (B,). A prompt built by an
+    earlier step always wins; ``task_key`` (``"task"`` in lerobot's json) names the raw text read when there is none."""
 
     tokenizer: Any = None
     tokenizer_name: str | None = None
     max_length: int = 200
-    task_key: str = PROMPT
+    task_key: str = TASK
     padding_side: str = "right"
     padding: str = "max_length"
     truncation: bool = True
@@ -390,7 +391,9 @@ class TokenizerStep(ProcessorStep):
     def __call__(self, t: Transition) -> Transition:
         if self.tokenizer is None:
             raise ProcessorStepError("tokenizer_processor needs a tokenizer (pass step_kwargs={'tokenizer_processor': {'tokenizer': tok}})")
-        texts = t.get(self.task_key) or t.get(TASK)
+        texts = t.get(PROMPT) or t.get(self.task_key) or t.get(TASK)
+        if texts is None:
+            raise ProcessorStepError("tokenizer_processor needs a 'prompt' or 'task' entry")
         if isinstance(texts, str):
             texts = [texts]
         enc = self.tokenizer(list(texts), max_length=self.max_length, padding=self.padding, truncation=self.truncation,
@@ -412,11 +415,13 @@ def _accepts_side(tok) -> bool:
 @ProcessorStepRegistry.register("device_processor")
 @dataclass
 class DeviceStep(ProcessorStep):
-    device: str = "cpu"
-    float_dtype: str | None = None
+    """Tensors (and lists of tensors) to ``device``; floating ones to ``float_dtype`` (a ``torch.dtype`` or its name)."""
+
+    device: Any = "cpu"
+    float_dtype: Any = None
 
     def __call__(self, t: Transition) -> Transition:
-        dt = getattr(torch, self.float_dtype) if self.float_dtype else None
+        dt = getattr(torch, self.float_dtype) if isinstance(self.float_dtype, str) else self.float_dtype
         for k, v in list(t.items()):
             if isinstance(v, torch.Tensor):
                 v = v.to(self.device, non_blocking=True)
@@ -426,7 +431,7 @@ class DeviceStep(ProcessorStep):
         return t
 
     def get_config(self):
-        return {"device": str(self.device), "float_dtype": self.float_dtype}
+        return {"device": str(self.device), "float_dtype": None if self.float_dtype is None else str(self.float_dtype).replace("torch.", "")}
 
 
 @ProcessorStepRegistry.register("to_batch_processor")

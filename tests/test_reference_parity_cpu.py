@@ -224,3 +224,58 @@ def test_cosmos3_generation_tokenisation(ref, monkeypatch):
     shipped = REF / "phyai_utils_tools" / "models" / "cosmos3" / "neg_prompts.json"
     if shipped.is_file():             # given the release's file, the default negative prompt is the reference's byte for byte
         assert mine.cosmos3_default_negative_prompt(shipped) == ref("phyai_utils_tools.models.cosmos3.steps_cosmos3").cosmos3_default_negative_prompt()
+
+
+def _same_inputs(x, y, fields):
+    for f in fields:
+        a, b = getattr(x, f), getattr(y, f)
+        assert a.dtype == b.dtype and a.shape == b.shape and torch.equal(a, b), f
+
+
+@pytest.mark.parametrize("model", ["pi05", "pi0"])
+def test_policy_processors_and_their_saved_files(ref, tmp_path, model):
+    """Same arguments, same sample: the same request tensors and the same actions; and a processor saved by either
+    package loads in the other and behaves the same (the files are lerobot's format)."""
+    from phyai_b200.tools import pi0 as my_pi0
+    from phyai_b200.tools import pi05 as my_pi05
+    from phyai_b200.tools.tokenizer import ByteTokenizer
+
+    if model == "pi05":
+        mine, theirs = my_pi05.PI05Processor, ref("phyai_utils_tools.models.pi05.processor_pi05").PI05Processor
+        # the reference un-normalises before it cuts the action, so its statistics span the model's whole action width
+        stats = {"observation.state": {"q01": [-1.0, 0.0, -2.0], "q99": [1.0, 4.0, 2.0]},
+                 "action": {"q01": [-1.0] * 32, "q99": [3.0, 2.0, 1.0, 0.5] * 8}}
+        fields = ("pixel_values", "input_ids", "lang_lens")
+    else:
+        mine, theirs = my_pi0.PI0Processor, ref("phyai_utils_tools.models.pi0.processor_pi0").PI0Processor
+        stats = {"observation.state": {"mean": [0.5, 1.0, -1.0], "std": [2.0, 0.5, 1.5]}, "action": {"mean": [0.1] * 4, "std": [2.0, 1.0, 0.5, 0.25]}}
+        fields = ("pixel_values", "input_ids", "lang_lens", "state")
+    tok = ByteTokenizer()
+    g = torch.Generator().manual_seed(0)
+    sample = {"images": [torch.rand(2, 3, 40, 64, generator=g), torch.rand(2, 3, 64, 40, generator=g)],
+              "state": torch.rand(2, 3, generator=g) * 2 - 1, "task": ["Pick_up the cube", "fold the\ntowel"]}
+    action = torch.rand(2, 6, 32, generator=g) * 2 - 1
+    for kw in (dict(dataset_stats=stats, action_dim=4, normalize_pixels=True), dict(dataset_stats=None, action_dim=None, normalize_pixels=False),
+               dict(dataset_stats=stats, action_dim=7 if model == "pi05" else 4, image_pad_value=-1.0)):
+        common = dict(tokenizer=tok, image_size=32, num_images=2, tokenizer_max_length=96, params_dtype=torch.float32, **kw)
+        a, b = mine(**common), theirs(**common)
+        _same_inputs(a.preprocess({k: (list(v) if isinstance(v, list) else v) for k, v in sample.items()}),
+                     b.preprocess({k: (list(v) if isinstance(v, list) else v) for k, v in sample.items()}), fields)
+        ya, yb = a.postprocess(action.clone()), b.postprocess(action.clone())
+        assert ya.shape == yb.shape and ya.dtype == yb.dtype and torch.allclose(ya, yb, atol=1e-6), kw
+    # saved by one, loaded by the other
+    common = dict(tokenizer=tok, image_size=32, num_images=2, tokenizer_max_length=96, params_dtype=torch.float32, dataset_stats=stats, action_dim=4)
+    a, b = mine(**common), theirs(**common)
+    a.save_pretrained(tmp_path / "mine")
+    b.save_pretrained(tmp_path / "theirs")
+    load = dict(tokenizer=tok, image_size=32, num_images=2, action_dim=4, params_dtype=torch.float32)
+    if model == "pi0":
+        load["normalize_pixels"] = True
+    want_in, want_out = b.preprocess(dict(sample)), b.postprocess(action.clone())
+    for loader, folder in ((mine, "theirs"), (theirs, "mine"), (mine, "mine")):
+        p = loader.from_pretrained(tmp_path / folder, **load)
+        _same_inputs(p.preprocess(dict(sample)), want_in, fields)
+        assert torch.allclose(p.postprocess(action.clone()), want_out, atol=1e-6), (loader.__module__, folder)
+    for name in ("policy_preprocessor.json", "policy_postprocessor.json"):
+        ja, jb = (json.loads((tmp_path / d / name).read_text()) for d in ("mine", "theirs"))
+        assert [s["registry_name"] for s in ja["steps"]] == [s["registry_name"] for s in jb["steps"]], name

@@ -48,10 +48,15 @@ def test_pipeline_save_load_lerobot_layout(tmp_path):
     p.save_pretrained(tmp_path)
     cfg = json.loads((tmp_path / "policy_preprocessor.json").read_text())
     names = [s["registry_name"] for s in cfg["steps"]]
-    assert names == ["resize_with_pad_step", "normalizer_processor", "pi05_prepare_state_tokenizer_processor_step", "tokenizer_processor", "device_processor"]
-    norm = cfg["steps"][1]
+    # the lerobot-portable core only: the resize step (this package's, lerobot resizes inside the model) is not written
+    assert names == ["normalizer_processor", "pi05_prepare_state_tokenizer_processor_step", "tokenizer_processor", "device_processor"]
+    post_names = [s["registry_name"] for s in json.loads((tmp_path / "policy_postprocessor.json").read_text())["steps"]]
+    assert post_names == ["unnormalizer_processor", "device_processor"]
+    norm = cfg["steps"][0]
     assert norm["config"]["norm_map"]["STATE"] == "QUANTILES" and (tmp_path / norm["state_file"]).is_file() and "stats" not in norm["config"]
-    q = PI05Processor.from_pretrained(tmp_path, tokenizer=ByteTokenizer(), params_dtype=torch.float32)
+    assert cfg["steps"][1]["config"] == {} and cfg["steps"][2]["config"]["task_key"] == "task"
+    q = PI05Processor.from_pretrained(tmp_path, tokenizer=ByteTokenizer(), params_dtype=torch.float32, image_size=32, action_dim=2)
+    assert [type(s).__name__ for s in q.preprocessor.steps][:2] == ["ResizeWithPadStep", "NormalizerStep"] and q.tokenizer_max_length == 256
     raw = {IMAGES: [torch.rand(1, 3, 48, 64)] * 2, STATE: torch.tensor([[0.25, 0.5, 1.0]]), TASK: ["pick_up the\ncube"]}
     a, b = p.preprocess(dict(raw)), q.preprocess(dict(raw))
     assert torch.equal(a.input_ids, b.input_ids) and torch.equal(a.pixel_values, b.pixel_values) and a.pixel_values.shape == (1, 2, 3, 32, 32)
@@ -167,25 +172,31 @@ def test_pi05_processor_end_to_end_and_saved_pair(tmp_path):
 
     stats = {"observation.state": {"q01": [0.0, 0.0], "q99": [2.0, 4.0]}, "action": {"q01": [-1.0] * 3, "q99": [3.0] * 3}}
     p = PI05Processor(tokenizer=ByteTokenizer(), image_size=16, tokenizer_max_length=160, params_dtype=torch.float32, action_dim=3,
-                      dataset_stats=stats, max_state_dim=4)
+                      dataset_stats=stats, max_state_dim=4, pad_state=True)
     sample = {IMAGES: torch.rand(1, 2, 3, 8, 16), STATE: torch.tensor([[1.0, 4.0]]), TASK: "pick_up the\ncube "}
     out = p.preprocess(dict(sample))
     assert out.pixel_values.shape == (1, 2, 3, 16, 16) and out.input_ids.shape == (1, 160)
     text = ByteTokenizer().decode(out.input_ids[0, : int(out.lang_lens[0])])
     # state 1.0 of [0, 2] -> 0 -> bin 128; 4.0 of [0, 4] -> ~1 -> bin 255; two padding columns at 0 -> bin 128
     assert text == "Task: pick up the cube, State: 128 255 128 128;\nAction: "
+    bare = PI05Processor(tokenizer=ByteTokenizer(), image_size=16, tokenizer_max_length=160, params_dtype=torch.float32, dataset_stats=stats)
+    bare_text = ByteTokenizer().decode(bare.preprocess(dict(sample)).input_ids[0])
+    assert "State: 128 255;" in bare_text                                                        # default: the bins of the state given, no padding
     act = p.postprocess(torch.zeros(1, 5, 32))
     assert act.shape == (1, 5, 3) and torch.allclose(act, torch.ones(1, 5, 3), atol=1e-5)        # 0 of [-1, 3] -> the middle, 1.0
-    with pytest.raises(ValueError, match="needs 'state' and 'task'"):
-        StateTokenizerPrepareStep()({TASK: "x"})
+    assert act.device.type == "cpu" and p.postprocess(torch.zeros(1, 5, 32, dtype=torch.bfloat16)).dtype == torch.bfloat16
+    assert StateTokenizerPrepareStep()({TASK: "fold_it"})[PROMPT] == ["Task: fold it;\nAction: "]   # no state: the task alone
+    with pytest.raises(ValueError, match="needs 'task'"):
+        StateTokenizerPrepareStep()({STATE: torch.zeros(1, 2)})
     p.save_pretrained(tmp_path)
     assert (tmp_path / "policy_preprocessor.json").is_file() and (tmp_path / "policy_postprocessor.json").is_file()
-    q = PI05Processor.from_pretrained(tmp_path, tokenizer=ByteTokenizer(), params_dtype=torch.float32)
+    q = PI05Processor.from_pretrained(tmp_path, tokenizer=ByteTokenizer(), params_dtype=torch.float32, image_size=16, action_dim=3)
+    assert q.pad_state and q.max_state_dim == 4                                                  # padding is on: it is saved with the step
     again = q.preprocess(dict(sample))
     assert torch.equal(again.input_ids, out.input_ids) and torch.equal(again.pixel_values, out.pixel_values)
     assert torch.allclose(q.postprocess(torch.zeros(1, 5, 32)), act)
     pre, post = make_pi05_processors(tokenizer=ByteTokenizer(), image_size=16, tokenizer_max_length=32, params_dtype=torch.float32)
-    assert pre.name == "policy_preprocessor" and post.name == "policy_postprocessor" and len(pre) == 5
+    assert pre.name == "pi05_preprocessor" and post.name == "pi05_postprocessor" and len(pre) == 5 and len(post) == 3
 
 
 def test_pi0_saved_pair_and_prompt_step_names(tmp_path):
