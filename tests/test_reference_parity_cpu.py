@@ -279,3 +279,194 @@ def test_policy_processors_and_their_saved_files(ref, tmp_path, model):
     for name in ("policy_preprocessor.json", "policy_postprocessor.json"):
         ja, jb = (json.loads((tmp_path / d / name).read_text()) for d in ("mine", "theirs"))
         assert [s["registry_name"] for s in ja["steps"]] == [s["registry_name"] for s in jb["steps"]], name
+
+
+def test_default_configurations(ref):
+    """Every field of the default model configurations (nested ones included) has the reference's value, so a checkpoint's
+    ``config.json`` that leaves a field out means the same model in both packages."""
+    import dataclasses
+
+    def flat(x, pre=""):
+        out = {}
+        for f in dataclasses.fields(x):
+            v = getattr(x, f.name)
+            if dataclasses.is_dataclass(v):
+                out.update(flat(v, pre + f.name + "."))
+            else:
+                out[pre + f.name] = list(v) if isinstance(v, (tuple, list)) else v
+        return out
+
+    for mod, cls in (("models.pi05.configuration_pi05", "PI05Config"), ("models.pi0.configuration_pi0", "PI0Config"),
+                     ("models.cosmos3.configuration_cosmos3", "Cosmos3Config"), ("models.cosmos3.configuration_cosmos3", "Cosmos3WanVAEConfig"),
+                     ("models.cosmos3.configuration_cosmos3", "Cosmos3AVAESoundConfig")):
+        mine = flat(getattr(importlib.import_module("phyai_b200." + mod), cls)())
+        theirs = flat(getattr(ref("phyai." + mod), cls)())
+        theirs.pop("expert.adarms_cond_dim", None) if cls == "PI0Config" else None      # Pi0 has no time-conditioned norm: the width is unused
+        mine.pop("expert.adarms_cond_dim", None) if cls == "PI0Config" else None
+        assert mine == theirs, (cls, {k: (mine.get(k), theirs.get(k)) for k in set(mine) | set(theirs) if mine.get(k) != theirs.get(k)})
+
+
+@pytest.fixture()
+def ref_single_rank(ref):
+    """The reference's process-level state for building its models on CPU: engine configuration on the CPU in fp32 and a
+    single-rank mesh under its default name (a stand-in for the torch device mesh, as its own unit tests use)."""
+    from unittest.mock import MagicMock
+
+    ec, mesh, state = ref("phyai.engine_config"), ref("phyai.parallel.mesh"), ref("phyai.parallel.state")
+    saved_cfg, saved_meshes = ec.get_engine_config(), dict(state._meshes)
+    ec.set_engine_config(saved_cfg.replace(device=ec.DeviceConfig(target="cpu", params_dtype=torch.float32)))
+    tm = MagicMock()
+    tm.mesh_dim_names = ("dp", "cfg", "ep", "sp", "cp", "tp")
+    tm.size.side_effect = lambda axis: 1
+    tm.get_local_rank.side_effect = lambda axis: 0
+    tm.get_group.side_effect = lambda axis: MagicMock(name=f"pg-{axis}")
+    state.register_mesh(mesh.Mesh(tm, name="model"))
+    try:
+        yield ref
+    finally:
+        ec.set_engine_config(saved_cfg)
+        state._meshes.clear()
+        state._meshes.update(saved_meshes)
+
+
+def _mirror_config(cfg, module):
+    """The reference's configuration object with the field values of this package's (class names and fields coincide)."""
+    import dataclasses
+
+    if dataclasses.is_dataclass(cfg):
+        return getattr(module, type(cfg).__name__)(**{f.name: _mirror_config(getattr(cfg, f.name), module) for f in dataclasses.fields(cfg)})
+    return cfg
+
+
+@pytest.mark.parametrize("what", ["cosmos3", "cosmos3_action", "cosmos3_sound", "pi05", "pi0"])
+def test_checkpoints_written_from_this_package_load_strictly_into_the_reference(ref_single_rank, tmp_path, what):
+    """One tensor per checkpoint key this package's model expects (fused parameters: one per leg), written as a
+    checkpoint, is loaded by the reference's loader into the reference's model with ``strict=True``: the two models
+    expect the same key names and shapes. Parameters that exist under one name in both hold the same values afterwards."""
+    from phyai_b200 import parallel as P
+    from phyai_b200.engine_config import DeviceConfig, EngineConfig, init_engine_config
+    from phyai_b200.weights import synthetic_state_dict, write_checkpoint
+
+    ref = ref_single_rank
+    init_engine_config(EngineConfig(device=DeviceConfig("cpu", torch.float32)))
+    P.init((1,), ("tp",), device="cpu")
+    try:
+        if what.startswith("cosmos3"):
+            from phyai_b200.models.cosmos3 import Cosmos3Transformer, tiny_cosmos3_config
+            from phyai_b200.models.cosmos3.transformer_cosmos3 import cosmos3_inverse_remap
+
+            rm = ref("phyai.models.cosmos3.modeling_cosmos3")
+            cfg = tiny_cosmos3_config(action_gen=what.endswith("action"), sound_gen=what.endswith("sound"))
+            mine = Cosmos3Transformer(cfg, params_dtype=torch.float32, device="cpu")
+            theirs = rm.Cosmos3Transformer(_mirror_config(cfg, rm), params_dtype=torch.float32, device="cpu")
+            state = {cosmos3_inverse_remap(k): v for k, v in synthetic_state_dict(mine, seed=1, std=0.05).items()}
+            remap = rm.cosmos3_weight_remap
+        elif what == "pi05":
+            from phyai_b200.models.pi05.configuration_pi05 import tiny_pi05_config
+            from phyai_b200.models.pi05.modeling_pi05 import PI05Model
+
+            cfg = tiny_pi05_config()
+            mine = PI05Model(cfg)
+            # building the reference's model touches no GPU; its paged attention layers only accept this backend name
+            theirs = ref("phyai.models.pi05.modeling_pi05").PI05Model(_mirror_config(cfg, ref("phyai.models.pi05.configuration_pi05")),
+                                                                      attn_backend="flashinfer", norm_backend="flashinfer", device="cpu")
+            ref("phyai.engine")          # the plugin modules import one another through it
+            state, remap = synthetic_state_dict(mine, seed=1, std=0.05), ref("phyai.models.pi05.main_pi05")._compose_remap(None)
+        else:
+            from phyai_b200.models.pi0.configuration_pi0 import tiny_pi0_config
+            from phyai_b200.models.pi0.main_pi0 import compose_remap
+            from phyai_b200.models.pi0.modeling_pi0 import PI0Model
+
+            cfg = tiny_pi0_config()
+            mine = PI0Model(cfg)
+            theirs = ref("phyai.models.pi0.modeling_pi0").PI0Model(_mirror_config(cfg, ref("phyai.models.pi0.configuration_pi0")),
+                                                                   attn_backend="flashinfer", norm_backend="flashinfer", device="cpu")
+            ref("phyai.engine")
+            state, remap = synthetic_state_dict(mine, seed=1, std=0.05), ref("phyai.models.pi0.main_pi0")._compose_remap(None)
+        gs = torch.Generator().manual_seed(2)
+        state = {k: (torch.randn(v.shape, generator=gs) * 0.1).to(v.dtype) if float(v.float().abs().sum()) == 0 or bool((v == 1).all()) else v
+                 for k, v in state.items()}          # identity norms and zero tables would hide a mix-up: every tensor random
+        write_checkpoint(tmp_path, state, None)
+        report = ref("phyai.weights.loader").load_pretrained(theirs, tmp_path, remap=remap, strict=True)
+        assert not report.missing and not report.unexpected, (report.missing[:5], report.unexpected[:5])
+        theirs_named = dict(theirs.named_parameters())
+        from phyai_b200.weights import load_pretrained
+
+        if what.startswith("cosmos3"):
+            from phyai_b200.models.cosmos3.transformer_cosmos3 import cosmos3_weight_remap
+
+            load_pretrained(mine, tmp_path, remap=cosmos3_weight_remap, strict=True)
+        else:
+            load_pretrained(mine, tmp_path, strict=True)
+        shared = [(n, p) for n, p in mine.named_parameters() if n in theirs_named and theirs_named[n].shape == p.shape]
+        assert len(shared) >= 5
+        for n, p in shared:
+            a, b = p.data.float(), theirs_named[n].data.float()
+            if "gate_up" in n and not torch.equal(a, b):
+                # this package keeps gate and up rows interleaved (the gated epilogue reads them as neighbours), the
+                # reference one block after the other
+                half = b.shape[0] // 2
+                assert torch.equal(a[0::2], b[:half]) and torch.equal(a[1::2], b[half:]), n
+            else:
+                assert torch.equal(a, b), n
+    finally:
+        P.shutdown()
+
+
+def test_video_vae_and_sound_decoder_numerics(ref_single_rank, tmp_path):
+    """The convolutional parts run on the CPU in both packages: one checkpoint (this package's key index, every tensor
+    random), the reference's loader and model on one side, this package's on the other; decoded pixels, encoded latents and
+    the decoded waveform agree to fp32 rounding (the reference walks the clip in chunks of frames with a feature cache,
+    this package in one pass or a stream)."""
+    from phyai_b200.engine_config import DeviceConfig, EngineConfig, init_engine_config
+    from phyai_b200.models.cosmos3 import Cosmos3AVAESoundConfig, Cosmos3WanVAEConfig
+    from phyai_b200.models.cosmos3.avae_sound import Cosmos3AVAESoundDecoder, cosmos3_avae_weight_remap
+    from phyai_b200.models.cosmos3.vae_wan import Cosmos3WanVAE, cosmos3_vae_weight_remap
+    from phyai_b200.weights import load_pretrained, synthetic_state_dict, write_checkpoint
+
+    ref = ref_single_rank
+    init_engine_config(EngineConfig(device=DeviceConfig("cpu", torch.float32)))
+    rcfg, rvae, ravae, rload = (ref(m) for m in ("phyai.models.cosmos3.configuration_cosmos3", "phyai.models.cosmos3.vae_wan",
+                                                 "phyai.models.cosmos3.avae_sound", "phyai.weights.loader"))
+    gs = torch.Generator().manual_seed(0)
+
+    def randomised(model):
+        st = synthetic_state_dict(model, seed=3, std=0.05)
+        return {k: (torch.randn(v.shape, generator=gs) * (0.3 if v.dim() > 1 else 0.1) + (1.0 if v.dim() == 1 and "gamma" in k else 0.0)).to(v.dtype)
+                for k, v in st.items()}
+
+    # ---- video VAE
+    cfg = Cosmos3WanVAEConfig(z_dim=4, decoder_base_dim=8, base_dim=8, dim_mult=(1, 2, 2, 2), num_res_blocks=1,
+                              latents_mean=tuple(0.1 * i for i in range(4)), latents_std=tuple(1.0 + 0.1 * i for i in range(4)))
+    mine = Cosmos3WanVAE(cfg, device="cpu", dtype=torch.float32).eval()
+    d = tmp_path / "vae"
+    write_checkpoint(d, randomised(mine), None)
+    load_pretrained(mine, d, remap=cosmos3_vae_weight_remap, strict=True)
+    theirs = rvae.Cosmos3WanVAE(_mirror_config(cfg, rcfg)).eval()
+    rep = rload.load_pretrained(theirs, d, remap=rvae.cosmos3_vae_weight_remap, strict=True)
+    assert not rep.missing and not rep.unexpected
+    lat = torch.randn(1, 4, 3, 4, 6, generator=gs)
+    with torch.no_grad():
+        a, b = mine.decode(lat), theirs.decode(lat)
+        assert a.shape == b.shape == (1, 3, 9, 64, 96)
+        assert torch.allclose(a, b, atol=2e-4, rtol=1e-4), (a - b).abs().max()
+        assert torch.allclose(mine.decode(lat, frames_per_chunk=1), b, atol=2e-4, rtol=1e-4)
+        pix = torch.rand(1, 3, 5, 32, 48, generator=gs) * 2 - 1
+        ea, eb = mine.encode(pix), theirs.encode(pix)
+        assert ea.shape == eb.shape == (1, 4, 2, 2, 3) and torch.allclose(ea, eb, atol=2e-4, rtol=1e-4), (ea - eb).abs().max()
+
+    # ---- sound decoder
+    acfg = Cosmos3AVAESoundConfig(latent_ch=8, dec_dim=16, dec_c_mults=(1, 2, 4), dec_strides=(2, 4, 5))
+    mine_a = Cosmos3AVAESoundDecoder(acfg, device="cpu", dtype=torch.float32).eval()
+    d = tmp_path / "avae"
+    # this package also accepts the newer spelling of weight-normalised convolutions (parametrizations.weight.original0 / 1);
+    # a checkpoint carries one spelling, here the one the reference knows (weight_g / weight_v)
+    write_checkpoint(d, {k: v for k, v in randomised(mine_a).items() if "parametrizations" not in k}, None)
+    load_pretrained(mine_a, d, remap=cosmos3_avae_weight_remap, strict=True)
+    theirs_a = ravae.Cosmos3AVAESoundDecoder(_mirror_config(acfg, rcfg)).eval()
+    rep = rload.load_pretrained(theirs_a, d, remap=ravae.cosmos3_avae_weight_remap, strict=True)
+    assert not rep.missing and not rep.unexpected
+    z = torch.randn(1, 8, 7, generator=gs)
+    with torch.no_grad():
+        wa, wb = mine_a.decode(z), theirs_a.decode(z)
+    assert wa.shape == wb.shape and wa.shape[-1] == 7 * 40 and torch.allclose(wa, wb, atol=2e-4, rtol=1e-4), (wa - wb).abs().max()
