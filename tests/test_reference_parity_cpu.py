@@ -470,3 +470,88 @@ def test_video_vae_and_sound_decoder_numerics(ref_single_rank, tmp_path):
     with torch.no_grad():
         wa, wb = mine_a.decode(z), theirs_a.decode(z)
     assert wa.shape == wb.shape and wa.shape[-1] == 7 * 40 and torch.allclose(wa, wb, atol=2e-4, rtol=1e-4), (wa - wb).abs().max()
+
+
+@pytest.mark.parametrize("tp,rank", [(2, 1), (4, 2), (8, 5)])
+def test_tensor_parallel_shards_of_one_checkpoint(ref, tmp_path, tp, rank):
+    """The same full-size checkpoint tensors loaded by both packages into their parallel layers on rank ``rank`` of ``tp``
+    (stand-in meshes, no process group): column / row shards, fused q | k | v with fewer KV heads than ranks (replicated
+    KV heads), fused gate / up, vocabulary shards with padding rows."""
+    import torch.nn as nn
+    from unittest.mock import MagicMock
+
+    from phyai_b200.engine_config import DeviceConfig, EngineConfig, init_engine_config
+    from phyai_b200.layers import linear as L
+    from phyai_b200.layers.vocab_embedding import VocabParallelEmbedding
+    from phyai_b200.parallel.mesh import Mesh
+    from phyai_b200.weights import load_pretrained, write_checkpoint
+
+    ec, rmesh, rstate = ref("phyai.engine_config"), ref("phyai.parallel.mesh"), ref("phyai.parallel.state")
+    RL, RV, rload = ref("phyai.layers.linear"), ref("phyai.layers.vocab_embedding"), ref("phyai.weights.loader")
+    saved_cfg, saved_meshes = ec.get_engine_config(), dict(rstate._meshes)
+    ec.set_engine_config(saved_cfg.replace(device=ec.DeviceConfig(target="cpu", params_dtype=torch.float32)))
+    tm = MagicMock()
+    tm.mesh_dim_names = ("tp",)
+    tm.size.side_effect = lambda axis: tp
+    tm.get_local_rank.side_effect = lambda axis: rank
+    tm.get_group.side_effect = lambda axis: MagicMock(name=f"pg-{axis}")
+    rstate.register_mesh(rmesh.Mesh(tm, name="model"))
+    init_engine_config(EngineConfig(device=DeviceConfig("cpu", torch.float32)))
+    my_mesh = Mesh((tp,), ("tp",), rank=rank, build_groups=False)
+    try:
+        H, D, heads, kv_heads, I, V = 64, 8, 16, 2, 48 * tp // 2, 100
+        kw = dict(bias=True, params_dtype=torch.float32)
+
+        class Mine(nn.Module):
+            def __init__(self):
+                super().__init__()
+                self.col = L.ColumnParallelLinear(H, 32 * tp, mesh=my_mesh, prefix="col", **kw)
+                self.row = L.RowParallelLinear(32 * tp, H, mesh=my_mesh, prefix="row", **kw)
+                self.qkv = L.QKVParallelLinear(H, D, heads, kv_heads, mesh=my_mesh, prefix="attn.qkv_proj", hf_legs=("q_proj", "k_proj", "v_proj"), **kw)
+                self.gu = L.MergedColumnParallelLinear(H, [I, I], mesh=my_mesh, prefix="mlp.gate_up_proj", hf_legs=("gate_proj", "up_proj"), **kw)
+                self.emb = VocabParallelEmbedding(V, H, params_dtype=torch.float32, mesh=my_mesh, device="cpu", prefix="emb")
+
+        class Theirs(nn.Module):
+            def __init__(self):
+                super().__init__()
+                self.col = RL.ColumnParallelLinear(H, 32 * tp, prefix="col", **kw)
+                self.row = RL.RowParallelLinear(32 * tp, H, prefix="row", **kw)
+                self.qkv = RL.QKVParallelLinear(H, D, heads, kv_heads, prefix="attn.qkv_proj", hf_legs={"q": "q_proj", "k": "k_proj", "v": "v_proj"}, **kw)
+                self.gu = RL.MergedColumnParallelLinear(H, [I, I], prefix="mlp.gate_up_proj", hf_legs=("gate_proj", "up_proj"), **kw)
+                self.emb = RV.VocabParallelEmbedding(V, H, params_dtype=torch.float32, device="cpu", prefix="emb")
+
+        mine, theirs = Mine(), Theirs()
+        g = torch.Generator().manual_seed(tp * 10 + rank)
+        r = lambda *s: torch.randn(*s, generator=g)  # noqa: E731
+        ck = {"col.weight": r(32 * tp, H), "col.bias": r(32 * tp), "row.weight": r(H, 32 * tp), "row.bias": r(H),
+              "attn.q_proj.weight": r(heads * D, H), "attn.k_proj.weight": r(kv_heads * D, H), "attn.v_proj.weight": r(kv_heads * D, H),
+              "attn.q_proj.bias": r(heads * D), "attn.k_proj.bias": r(kv_heads * D), "attn.v_proj.bias": r(kv_heads * D),
+              "mlp.gate_proj.weight": r(I, H), "mlp.up_proj.weight": r(I, H), "mlp.gate_proj.bias": r(I), "mlp.up_proj.bias": r(I),
+              "emb.weight": r(V, H)}
+        write_checkpoint(tmp_path, ck, None)
+        rep_a = load_pretrained(mine, tmp_path, strict=True)
+        rep_b = rload.load_pretrained(theirs, tmp_path, strict=True)
+        assert not rep_a.missing and not rep_b.missing and not rep_a.unexpected and not rep_b.unexpected
+        for name in ("col", "row", "qkv", "emb"):
+            for pn, p in getattr(mine, name).named_parameters():
+                q = dict(getattr(theirs, name).named_parameters())[pn]
+                assert p.shape == q.shape and torch.equal(p.data, q.data), (name, pn)
+        # gate / up: both hold this rank's gate block and up block; this package may interleave their rows
+        for pn, p in mine.gu.named_parameters():
+            q = dict(theirs.gu.named_parameters())[pn]
+            assert p.shape == q.shape
+            half = q.shape[0] // 2
+            same = torch.equal(p.data, q.data) or (torch.equal(p.data[0::2], q.data[:half]) and torch.equal(p.data[1::2], q.data[half:]))
+            assert same, pn
+        # what the shards must be, said directly
+        per = 32
+        assert torch.equal(mine.col.weight.data, ck["col.weight"][rank * per:(rank + 1) * per]) and torch.equal(mine.row.weight.data, ck["row.weight"][:, rank * per:(rank + 1) * per])
+        hq = heads // tp
+        assert torch.equal(mine.qkv.weight.data[: hq * D], ck["attn.q_proj.weight"][rank * hq * D:(rank + 1) * hq * D])
+        kv_of_rank = rank * kv_heads // tp if tp > kv_heads else None
+        if kv_of_rank is not None:      # more ranks than KV heads: each rank holds one whole KV head, shared by tp / kv_heads ranks
+            assert torch.equal(mine.qkv.weight.data[hq * D: hq * D + D], ck["attn.k_proj.weight"][kv_of_rank * D:(kv_of_rank + 1) * D])
+    finally:
+        ec.set_engine_config(saved_cfg)
+        rstate._meshes.clear()
+        rstate._meshes.update(saved_meshes)
