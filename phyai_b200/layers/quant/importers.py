@@ -19,7 +19,7 @@ def _ignore_rules(names) -> tuple[Rule, ...]:
     rules = []
     for n in names or ():
         if n.startswith("re:"):
-            rules.append(Rule(Matcher(regex=n[3:]), None))
+            rules.append(Rule(Matcher(regex=_from_start(n[3:])), None))
         elif any(ch in n for ch in "*?["):
             rules.append(Rule(Matcher(glob=n), None))
         else:
@@ -31,6 +31,12 @@ def _esc(s: str) -> str:
     import re
 
     return re.escape(s)
+
+
+def _from_start(pattern: str) -> str:
+    """A ``re:`` entry of a checkpoint is matched from the start of the module name (``re.match``), as the libraries
+    that write these files and the reference (phyai/src/phyai/layers/quant/plan.py:25-26) do."""
+    return pattern if pattern.startswith("^") else f"^(?:{pattern})"
 
 
 def import_hf_fp8(blob: Mapping[str, Any]) -> QuantPlan | None:
@@ -45,7 +51,7 @@ def import_hf_fp8(blob: Mapping[str, Any]) -> QuantPlan | None:
             activation=TensorQuant(QDType.FP8_E4M3, Granularity.GROUP, (c,), dynamic=True))
     else:
         scheme = FP8_PER_TENSOR
-    return QuantPlan(rules=_ignore_rules(blob.get("modules_to_not_convert")), default=scheme)
+    return QuantPlan(rules=_ignore_rules(blob.get("ignored_layers") or blob.get("modules_to_not_convert")), default=scheme)
 
 
 def import_compressed_tensors(blob: Mapping[str, Any]) -> QuantPlan | None:
@@ -57,11 +63,13 @@ def import_compressed_tensors(blob: Mapping[str, Any]) -> QuantPlan | None:
         scheme = _ct_scheme(w, group.get("input_activations"))
         for target in group.get("targets", ["Linear"]):
             if target.startswith("re:"):
-                rules.append(Rule(Matcher(regex=target[3:]), scheme))
+                rules.append(Rule(Matcher(regex=_from_start(target[3:])), scheme))
             elif target == "Linear":
                 rules.append(Rule(Matcher(module_cls="LinearBase"), scheme))
-            else:
+            elif "." not in target and target[:1].isupper():          # a bare CamelCase token names a module class
                 rules.append(Rule(Matcher(module_cls=target), scheme))
+            else:                                                     # anything else names modules
+                rules.append(Rule(Matcher(regex=rf"(^|\.){_esc(target)}($|\.)"), scheme))
     return QuantPlan(rules=tuple(rules), default=None)
 
 
@@ -81,7 +89,11 @@ def _ct_scheme(w: Mapping[str, Any], act: Mapping[str, Any] | None) -> QuantSche
 
 
 def import_modelopt(blob: Mapping[str, Any]) -> QuantPlan | None:
+    """``hf_quant_config.json`` (``{"quantization": {"quant_algo": ..., "exclude_modules": [...]}}``) or the same fields
+    inline in ``config.json`` under ``quant_method`` modelopt / modelopt_fp8 / modelopt_fp4."""
     q = blob.get("quantization", blob)
+    if not isinstance(q, Mapping):
+        return None
     algo = q.get("quant_algo")
     if algo is None:
         return None
@@ -89,7 +101,7 @@ def import_modelopt(blob: Mapping[str, Any]) -> QuantPlan | None:
              "FP8_PB_WO": FP8_BLOCK_128, "NVFP4": NVFP4_BLOCK_16}
     if algo not in table:
         raise ValueError(f"ModelOpt quant_algo {algo!r} is not supported")
-    return QuantPlan(rules=_ignore_rules(q.get("exclude_modules")), default=table[algo])
+    return QuantPlan(rules=_ignore_rules(q.get("exclude_modules") or q.get("ignore")), default=table[algo])
 
 
 IMPORTERS: list[Importer] = [import_hf_fp8, import_compressed_tensors, import_modelopt]

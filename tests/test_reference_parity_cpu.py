@@ -555,3 +555,50 @@ def test_tensor_parallel_shards_of_one_checkpoint(ref, tmp_path, tp, rank):
         ec.set_engine_config(saved_cfg)
         rstate._meshes.clear()
         rstate._meshes.update(saved_meshes)
+
+
+def test_quantisation_plans_from_checkpoint_configs(ref, tmp_path):
+    """The three checkpoint dialects (HF fp8, compressed-tensors, ModelOpt) read from a folder by both packages: the same
+    modules are quantised and the same are left alone, with the same weight format (element type, granularity, block
+    shape). Entries are exact module names, last path components, class targets and ``re:`` patterns, which both packages
+    read the same way (this package additionally understands globs and path components inside a dotted name)."""
+    from phyai_b200.layers.linear import LinearBase as MyLinear
+    from phyai_b200.layers.quant import load_quant_plan
+
+    theirs_load = ref("phyai.layers.quant.active").load_quant_plan
+    TheirLinear = ref("phyai.layers.linear").LinearBase
+    cases = {
+        "hf_block": ("config.json", {"quantization_config": {"quant_method": "fp8", "weight_block_size": [128, 128], "modules_to_not_convert": ["lm_head", "fc1"]}}),
+        "hf_plain": ("config.json", {"quantization_config": {"quant_method": "fp8", "ignored_layers": ["model.layers.3.mlp.down_proj"]}}),
+        "ct_channel": ("config.json", {"quantization_config": {"quant_method": "compressed-tensors", "ignore": ["lm_head", "re:.*vision.*"], "config_groups": {"g": {
+            "targets": ["Linear"], "weights": {"num_bits": 8, "type": "float", "strategy": "channel"},
+            "input_activations": {"num_bits": 8, "type": "float", "strategy": "token", "dynamic": True}}}}}),
+        "ct_regex_from_start": ("config.json", {"compression_config": {"quant_method": "compressed-tensors", "config_groups": {"g": {
+            "targets": ["re:model\\\\.layers\\\\.\\\\d+\\\\.mlp", "re:mlp"], "weights": {"num_bits": 8, "type": "float", "strategy": "tensor"}}}}}),
+        "ct_block_named": ("config.json", {"quantization_config": {"quant_method": "compressed-tensors", "config_groups": {"g": {
+            "targets": ["model.layers.0.self_attn.q_proj", "down_proj"], "weights": {"num_bits": 8, "type": "float", "strategy": "block", "block_structure": [128, 128]}}}}}),
+        "modelopt_fp4": ("hf_quant_config.json", {"quantization": {"quant_algo": "NVFP4", "exclude_modules": ["lm_head", "vision.proj"]}}),
+        "modelopt_inline": ("config.json", {"quantization_config": {"quant_method": "modelopt", "quant_algo": "NVFP4", "ignore": ["lm_head"]}}),
+    }
+    names = ["model.layers.0.self_attn.q_proj", "model.layers.3.mlp.down_proj", "lm_head", "model.vision_tower.blocks.0.fc1", "vision.proj", "mlp.up_proj"]
+
+    def weight_format(scheme):
+        if scheme is None:
+            return None
+        w = scheme.weight
+        gran = w.granularity.value if hasattr(w.granularity, "value") else str(w.granularity)
+        return (w.dtype.value, "block" if w.dtype.value == "nvfp4" else gran.lower(), tuple(w.block_shape) if gran.lower() == "block" and w.block_shape else None)
+
+    for tag, (fname, blob) in cases.items():
+        d = tmp_path / tag
+        d.mkdir()
+        (d / "config.json").write_text(json.dumps({"hidden_size": 8, **(blob if fname == "config.json" else {})}))
+        if fname != "config.json":
+            (d / fname).write_text(json.dumps(blob))
+        pa, pb = load_quant_plan(d), theirs_load(d)
+        assert pa is not None and pb is not None, tag
+        for n in names:
+            a, b = weight_format(pa.resolve(n, MyLinear)), weight_format(pb.resolve(n, TheirLinear))
+            if a is not None and b is not None and a[0] == b[0] == "fp8_e4m3" and {a[1], b[1]} == {"per_tensor", "per_channel"}:
+                continue      # one scale per tensor in the file; both packages fan it out per channel after loading
+            assert a == b, (tag, n, a, b)
