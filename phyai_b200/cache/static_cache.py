@@ -10,6 +10,10 @@ import torch
 from .kv_cache_pool import KVCachePool
 
 
+class StaticCacheError(RuntimeError):
+    """The slab has fewer free slots than were asked for."""
+
+
 class StaticCache:
     def __init__(self, pool: KVCachePool, *, base_offset: int, capacity: int) -> None:
         if base_offset < 0 or capacity <= 0 or base_offset + capacity > pool.num_slots:
@@ -30,7 +34,7 @@ class StaticCache:
         if n < 0:
             raise ValueError("allocate: n must be non-negative")
         if n > self.free:
-            raise RuntimeError(f"StaticCache out of slots: want {n}, free {self.free} of {self.capacity}")
+            raise StaticCacheError(f"StaticCache out of slots: want {n}, free {self.free} of {self.capacity}")
         start = self.base_offset + self._used
         self._used += n
         return torch.arange(start, start + n, dtype=torch.int64, device=self.pool.device)
@@ -39,4 +43,4 @@ class StaticCache:
         self._used = 0
 
 
-__all__ = ["StaticCache"]
+__all__ = ["StaticCache", "StaticCacheError"]

@@ -18,6 +18,8 @@ prefill backends/flashinfer.py:113-160, recurrent decode :161-208).
 
 from __future__ import annotations
 
+from dataclasses import dataclass
+
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
@@ -125,4 +127,96 @@ class GatedDeltaNetAttention(nn.Module):
     forward = prefill
 
 
-__all__ = ["GatedDeltaNetAttention", "gated_delta_rule_recurrent", "gated_delta_rule_chunked"]
+@dataclass
+class GatedDeltaNetCtx:
+    """Where the recurrent state of a call lives: ``state_pool`` (slots, value heads, Dv, Dk) fp32 and one slot index per
+    sequence (read as the initial state, written back with the final one); ``cu_seqlens`` for token-major inputs."""
+
+    state_pool: torch.Tensor | None = None
+    state_indices: torch.Tensor | None = None
+    cu_seqlens: torch.Tensor | None = None
+
+
+GDN_BACKENDS = ("chunked", "recurrent")
+_BACKEND_ALIASES = {"flashinfer": "chunked", "fla": "chunked"}      # the names the reference's configurations carry
+
+
+def list_gdn_backends() -> list[str]:
+    return list(GDN_BACKENDS)
+
+
+class GatedDeltaNet(nn.Module):
+    """Gated delta rule with the gates built inside, in the reference's calling convention
+    (phyai/src/phyai/layers/attention/gdn/layer.py:33-140): ``forward(q, k, v, a, b, a_log, dt_bias)`` with
+    ``g = -exp(a_log) * softplus(a + dt_bias)``, ``beta = sigmoid(b)``, q / k scaled to unit length
+    (``x * rsqrt(sum x^2 + 1e-6)``) and value heads a multiple of the query / key heads (each query head serves a group
+    of value heads). Inputs are padded ``(B, T, H, D)`` or token-major ``(T, H, D)`` with ``cu_seqlens``; states are
+    ``(sequences, value heads, Dv, Dk)``. One token per sequence with a state pool takes the decode kernel."""
+
+    def __init__(self, num_query_heads: int, head_dim: int, *, num_key_heads: int | None = None, num_value_heads: int | None = None,
+                 scale: float | None = None, use_qk_l2norm: bool = True, backend: str = "chunked", backend_kwargs: dict | None = None) -> None:
+        super().__init__()
+        num_key_heads = num_query_heads if num_key_heads is None else num_key_heads
+        num_value_heads = num_query_heads if num_value_heads is None else num_value_heads
+        if min(num_query_heads, num_key_heads, num_value_heads, head_dim) <= 0:
+            raise ValueError("GatedDeltaNet: head counts and head_dim must be positive")
+        if num_query_heads != num_key_heads:
+            raise ValueError(f"GatedDeltaNet needs as many key heads as query heads, got {num_key_heads} and {num_query_heads}")
+        if num_value_heads % num_query_heads:
+            raise ValueError(f"num_value_heads={num_value_heads} must be a multiple of num_query_heads={num_query_heads}")
+        name = _BACKEND_ALIASES.get(backend, backend)
+        if name not in GDN_BACKENDS:
+            raise KeyError(f"unknown gated-delta-net backend {backend!r}; available: {list(GDN_BACKENDS)}")
+        self.num_query_heads, self.num_key_heads, self.num_value_heads = int(num_query_heads), int(num_key_heads), int(num_value_heads)
+        self.num_state_heads, self.head_dim = self.num_value_heads, int(head_dim)
+        self.scale = scale if scale is not None else head_dim ** -0.5
+        self.use_qk_l2norm, self.backend, self.chunk = bool(use_qk_l2norm), name, int((backend_kwargs or {}).get("chunk", 64))
+        self._op = GatedDeltaNetAttention(self.num_value_heads, self.head_dim, self.head_dim, backend=name)
+
+    def extra_repr(self) -> str:
+        return (f"num_query_heads={self.num_query_heads}, num_value_heads={self.num_value_heads}, head_dim={self.head_dim}, "
+                f"backend={self.backend!r}")
+
+    def _prepare(self, q, k, a, b, a_log, dt_bias):
+        rep = self.num_value_heads // self.num_query_heads
+        qf, kf = q.float().repeat_interleave(rep, dim=-2), k.float().repeat_interleave(rep, dim=-2)
+        if self.use_qk_l2norm:
+            qf = qf * torch.rsqrt(qf.square().sum(-1, keepdim=True) + 1e-6)
+            kf = kf * torch.rsqrt(kf.square().sum(-1, keepdim=True) + 1e-6)
+        g = -a_log.float().exp() * F.softplus(a.float() + dt_bias.float())
+        return qf, kf, g, b.float().sigmoid()
+
+    def forward(self, q, k, v, a, b, a_log, dt_bias, ctx: GatedDeltaNetCtx | None = None, *, cu_seqlens: torch.Tensor | None = None,
+                initial_state: torch.Tensor | None = None, return_state: bool = False):
+        if q.shape[-2] != self.num_query_heads or v.shape[-2] != self.num_value_heads or q.shape[-1] != self.head_dim:
+            raise ValueError(f"GatedDeltaNet: q {tuple(q.shape)} / v {tuple(v.shape)} do not fit {self.extra_repr()}")
+        ctx = ctx or GatedDeltaNetCtx(cu_seqlens=cu_seqlens)
+        cu = ctx.cu_seqlens if ctx.cu_seqlens is not None else cu_seqlens
+        pool, idx = ctx.state_pool, ctx.state_indices
+        if pool is not None and idx is not None and initial_state is None:
+            initial_state = pool[idx]
+        qf, kf, g, beta = self._prepare(q, k, a, b, a_log, dt_bias)
+        ragged = q.dim() == 3
+        if ragged and cu is None:
+            raise ValueError("token-major inputs need cu_seqlens")
+        spans = list(zip(cu.tolist()[:-1], cu.tolist()[1:])) if ragged else [(None, None)] * 1
+        rule = gated_delta_rule_recurrent if self.backend == "recurrent" else gated_delta_rule_chunked
+        kw = dict(scale=self.scale, use_qk_l2norm=False) | ({} if self.backend == "recurrent" else {"chunk": self.chunk})
+        if ragged:
+            outs, finals = [], []
+            for i, (s0, s1) in enumerate(spans):
+                st = None if initial_state is None else initial_state[i:i + 1].transpose(-1, -2)
+                o, S = rule(qf[None, s0:s1], kf[None, s0:s1], v[None, s0:s1], g[None, s0:s1], beta[None, s0:s1], st, **kw)
+                outs.append(o[0])
+                finals.append(S)
+            out, final = torch.cat(outs), torch.cat(finals)
+        else:
+            st = None if initial_state is None else initial_state.transpose(-1, -2)
+            out, final = rule(qf, kf, v, g, beta, st, **kw)
+        final = final.transpose(-1, -2)                      # (sequences, value heads, Dv, Dk)
+        if pool is not None and idx is not None:
+            pool[idx] = final.to(pool.dtype)
+        return (out, final) if return_state else out
+
+
+__all__ = ["GatedDeltaNet", "GatedDeltaNetCtx", "GDN_BACKENDS", "list_gdn_backends", "GatedDeltaNetAttention", "gated_delta_rule_recurrent", "gated_delta_rule_chunked"]

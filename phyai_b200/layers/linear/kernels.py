@@ -150,10 +150,54 @@ class Registry:
         return out
 
 
+class DefaultPolicy:
+    """The first candidate: kernels preferred for the probe's (spec, regime), then registration order."""
+
+    def choose(self, probe: KernelProbe, candidates: list[LinearKernel]) -> LinearKernel | None:
+        return candidates[0] if candidates else None
+
+
+class ForcedPolicy:
+    """Only the named kernel (``RuntimeConfig.force_linear_kernel`` / ``PHYAI_FORCE_LINEAR_KERNEL``)."""
+
+    def __init__(self, name: str) -> None:
+        self.name = name
+
+    def choose(self, probe: KernelProbe, candidates: list[LinearKernel]) -> LinearKernel | None:
+        return next((k for k in candidates if k.name == self.name), None)
+
+
+Policy = DefaultPolicy | ForcedPolicy
+
+# kernel classes declared by ``register_linear_kernel`` (out-of-tree providers): instantiated by ``init`` behind the built-in ones
+_DECLARED: list[tuple[type, frozenset[tuple[str, str]]]] = []
+
+
+def register_linear_kernel(*, prefer_for: Iterable[tuple[str, str]] | None = None):
+    """Class decorator: declare a :class:`LinearKernel` for the next ``init``. The class is not instantiated here, so
+    importing a provider module has no side effects; ``prefer_for`` lists the ``(spec_id, regime)`` pairs it should win.
+    Reference: phyai/src/phyai/layers/linear/registry.py:34-58."""
+    def deco(cls: type) -> type:
+        if not any(c is cls for c, _ in _DECLARED):
+            _DECLARED.append((cls, frozenset(prefer_for or ())))
+        return cls
+    return deco
+
+
+def list_registered_linear_kernels() -> list[tuple[type, frozenset[tuple[str, str]]]]:
+    return list(_DECLARED)
+
+
+def supported_specs_for_sm(sm: int, device_type: str = "cuda") -> list[str]:
+    """Spec ids some kernel of the installed registry can run on this SM (0 with ``device_type="cpu"``: the CPU)."""
+    return sorted(get_linear_dispatcher().registry.supported_specs_for_sm(sm, device_type))
+
+
 class Dispatcher:
-    def __init__(self, registry: Registry, forced: str | None = None) -> None:
+    def __init__(self, registry: Registry, forced: str | None = None, *, policy: "Policy | None" = None) -> None:
         self.registry = registry
-        self.forced = forced
+        self.forced = forced if policy is None else getattr(policy, "name", None)
+        self.policy = policy if policy is not None else (ForcedPolicy(forced) if forced is not None else DefaultPolicy())
         self._cache: dict[tuple, LinearKernel] = {}
 
     def select(self, *, spec_id: str, M: int, N: int, K: int, in_dtype: torch.dtype, out_dtype: torch.dtype,
@@ -165,14 +209,13 @@ class Dispatcher:
         probe = KernelProbe(spec_id, M, N, K, in_dtype, out_dtype, device_type, capturing)
         sm = sm_arch() if device_type == "cuda" else 0
         cands = self.registry.candidates(probe, sm)
-        if self.forced is not None:
-            cands = [k for k in cands if k.name == self.forced]
-        if not cands:
+        chosen = self.policy.choose(probe, cands)
+        if chosen is None:
             raise RuntimeError(
                 f"no linear kernel for spec {spec_id!r} on {device_type} sm_{sm} (M={M}, N={N}, K={K}, "
                 f"regime={probe.regime}, forced={self.forced!r}); registered: {self.registry.names()}")
-        self._cache[key] = cands[0]
-        return cands[0]
+        self._cache[key] = chosen
+        return chosen
 
 
 _DISPATCHER: Dispatcher | None = None
@@ -186,6 +229,8 @@ def init(force: str | None = None) -> Dispatcher:
     b200_pref = [(s, r) for s in B200Kernel.specs for r in ("decode", "prefill")]
     reg.register(B200Kernel(), prefer_for=b200_pref)
     reg.register(TorchKernel())
+    for cls, pref in _DECLARED:
+        reg.register(cls(), prefer_for=pref)
     reg.validate()
     forced = force or cfg.runtime.force_linear_kernel or (
         cfg.backends.linear if cfg.backends.linear not in (None, "auto") else None)
@@ -204,5 +249,8 @@ def _reset_for_test() -> None:
     _DISPATCHER = None
 
 
-__all__ = ["KernelProbe", "LinearKernel", "TorchKernel", "B200Kernel", "Registry", "Dispatcher", "init",
-           "get_linear_dispatcher"]
+KernelDispatcher, LinearKernelRegistry = Dispatcher, Registry
+
+__all__ = ["KernelProbe", "LinearKernel", "TorchKernel", "B200Kernel", "Registry", "Dispatcher", "KernelDispatcher", "LinearKernelRegistry",
+           "DefaultPolicy", "ForcedPolicy", "Policy", "register_linear_kernel", "list_registered_linear_kernels", "supported_specs_for_sm",
+           "init", "get_linear_dispatcher"]

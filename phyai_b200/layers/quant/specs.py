@@ -10,6 +10,7 @@ Reference: phyai/src/phyai/layers/quant/{base,bf16,fp8,nvfp4,linear,materialize}
 from __future__ import annotations
 
 from dataclasses import dataclass
+from typing import NamedTuple, Protocol, runtime_checkable
 
 import torch
 import torch.nn as nn
@@ -19,6 +20,43 @@ from .scheme import Granularity, QDType, QuantScheme
 
 FP8_MAX = 448.0
 FP4_VALUES = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
+
+
+class ActivationView(NamedTuple):
+    """What a kernel gets from a spec that quantises activations in front of the product."""
+
+    x: torch.Tensor
+    x_scale: torch.Tensor | None
+    granularity: Granularity
+
+
+@runtime_checkable
+class WeightSpec(Protocol):
+    """How one weight format lives in a linear layer: which parameters it allocates, what it fixes up after loading and
+    the PyTorch statement of the product (the oracle of the kernel tests). Reference:
+    phyai/src/phyai/layers/quant/base.py."""
+
+    spec_id: str
+    min_sm: int
+
+    def allocate(self, layer: nn.Module, req: "AllocationRequest") -> None: ...
+
+    def process_after_loading(self, layer: nn.Module) -> None: ...
+
+    def reference_apply(self, layer: nn.Module, x: torch.Tensor, bias: torch.Tensor | None) -> torch.Tensor: ...
+
+
+@runtime_checkable
+class LinearActivationQuant(Protocol):
+    """Specs whose kernels take quantised activations (``isinstance(spec, LinearActivationQuant)`` instead of looking at
+    spec ids). Reference: phyai/src/phyai/layers/quant/linear.py:34-48; here ``quantize_activation(x)`` returns the
+    ``(values, scales)`` pair the CUDA quantiser produces and ``activation_view`` wraps it with its granularity."""
+
+    needs_act_quant: bool
+
+    def quantize_activation(self, x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]: ...
+
+    def activation_view(self, x: torch.Tensor, layer: nn.Module | None = None) -> ActivationView: ...
 
 
 @dataclass(frozen=True)
@@ -51,6 +89,7 @@ class Fp8Spec:
     quantised on the fly (per token, or per 1 x block_k group for block scales)."""
 
     min_sm = 89
+    needs_act_quant = True
 
     def __init__(self, scheme: QuantScheme) -> None:
         self.scheme = scheme
@@ -109,6 +148,10 @@ class Fp8Spec:
             return q.clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn), sc
         sc = xf.abs().amax(-1).clamp_min(1e-12) / FP8_MAX
         return (xf / sc[:, None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn), sc
+
+    def activation_view(self, x: torch.Tensor, layer: nn.Module | None = None) -> ActivationView:
+        q, sc = self.quantize_activation(x.reshape(-1, x.shape[-1]))
+        return ActivationView(q, sc, Granularity.GROUP if self.granularity is Granularity.BLOCK else Granularity.PER_TOKEN)
 
     def dequant_weight(self, layer: nn.Module) -> torch.Tensor:
         w = layer.weight.float()
@@ -212,4 +255,5 @@ def materialize(scheme: QuantScheme | None, sm: int | None = None):
     raise ValueError(f"no weight spec for {scheme}")
 
 
-__all__ = ["AllocationRequest", "Bf16Spec", "Fp8Spec", "Nvfp4Spec", "materialize", "FP8_MAX"]
+__all__ = ["ActivationView", "WeightSpec", "LinearActivationQuant", "AllocationRequest", "Bf16Spec", "Fp8Spec", "Nvfp4Spec", "materialize",
+           "FP8_MAX"]

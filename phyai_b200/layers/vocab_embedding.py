@@ -23,8 +23,11 @@ from ..weights import shards
 PAD_MULTIPLE = 64
 
 
-def pad_vocab(vocab: int, tp: int) -> int:
-    m = tp * PAD_MULTIPLE
+def pad_vocab(vocab: int, tp: int, multiple: int = PAD_MULTIPLE) -> int:
+    """``vocab`` rounded up to a multiple of ``tp * multiple``: equal shards whose rows are a multiple of ``multiple``."""
+    if tp <= 0 or multiple <= 0:
+        raise ValueError(f"pad_vocab: tp and multiple must be positive, got {tp} and {multiple}")
+    m = tp * multiple
     return (vocab + m - 1) // m * m
 
 
@@ -84,4 +87,6 @@ class ParallelLMHead(nn.Module):
         return logits[..., : e.num_embeddings] if (e.tp_size == 1 or self.gather_output) else logits
 
 
-__all__ = ["VocabParallelEmbedding", "ParallelLMHead", "masked_embedding_lookup", "pad_vocab"]
+pad_vocab_to = pad_vocab
+
+__all__ = ["VocabParallelEmbedding", "ParallelLMHead", "masked_embedding_lookup", "pad_vocab", "pad_vocab_to"]

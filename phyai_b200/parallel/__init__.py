@@ -32,9 +32,25 @@ from .mesh import Mesh
 from .ops import (all_gather, all_reduce, all_to_all, barrier, broadcast, get_dispatcher, recv,
                   reduce_scatter, send, set_dispatcher)
 from .registry import DefaultPolicy, ForcedPolicy, Registry
+from .backends.torch_dist import GlooBackend, NcclBackend
+from .backends.torch_dist import _TorchDistBackend as TorchDistBackend
 from .state import current_mode, default_mesh, graph_capture, register_mesh, resolve_mesh, use_mesh
 
 AXES = ("dp", "cfg", "ep", "sp", "cp", "tp")
+Policy = DefaultPolicy | ForcedPolicy       # anything with ``choose(call, candidates) -> Backend``
+
+
+def __getattr__(name: str):
+    # backends with heavier imports (ctypes binding of libnccl, the CUDA extension) load on first use
+    if name in ("PyNcclBackend", "PyNCCLBackend"):
+        from .backends.pynccl import PyNcclBackend
+
+        return PyNcclBackend
+    if name == "PeerBackend":
+        from .backends.peer import PeerBackend
+
+        return PeerBackend
+    raise AttributeError(name)
 
 
 def init(layout: Sequence[int] = (1,), mesh_dim_names: Sequence[str] = ("tp",), *, device: str = "cuda",
@@ -139,7 +155,8 @@ def warmup(axes: Sequence[str] = AXES, *, mesh=None) -> None:
         torch.cuda.synchronize()
 
 
-__all__ = ["AXES", "init", "shutdown", "on_stream", "warmup", "Mesh", "Op", "Mode", "Topology", "Call",
+__all__ = ["GlooBackend", "NcclBackend", "TorchDistBackend", "PyNcclBackend", "PyNCCLBackend", "PeerBackend", "Policy",
+           "get_dispatcher", "set_dispatcher", "AXES", "init", "shutdown", "on_stream", "warmup", "Mesh", "Op", "Mode", "Topology", "Call",
            "Backend", "Registry", "Dispatcher", "DefaultPolicy", "ForcedPolicy", "init_dist", "destroy_dist",
            "all_reduce", "all_gather", "reduce_scatter", "all_to_all", "broadcast", "send", "recv", "barrier",
            "graph_capture", "current_mode", "default_mesh", "resolve_mesh", "register_mesh", "use_mesh",

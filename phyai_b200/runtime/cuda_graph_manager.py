@@ -31,6 +31,10 @@ def capture_on_stream(stream: "torch.cuda.Stream"):
         _CAPTURE_STREAM = prev
 
 
+class CudaGraphError(RuntimeError):
+    """Misuse of a graph object: captured twice, replayed before capture, an input of another shape."""
+
+
 class CudaGraph:
     def __init__(self, name: str = "graph", warmup_iters: int = 3) -> None:
         self.name, self.warmup_iters = name, warmup_iters
@@ -45,7 +49,7 @@ class CudaGraph:
 
     def capture(self, fn: Callable[..., Any], example_inputs: Mapping[str, torch.Tensor], *, pool=None) -> Any:
         if self.captured:
-            raise RuntimeError(f"CudaGraph {self.name!r} is already captured")
+            raise CudaGraphError(f"CudaGraph {self.name!r} is already captured")
         self.static_inputs = {k: v.clone() for k, v in example_inputs.items()}
         side = _CAPTURE_STREAM or torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -62,7 +66,7 @@ class CudaGraph:
 
     def replay(self, inputs: Mapping[str, torch.Tensor] | None = None) -> Any:
         if self.graph is None:
-            raise RuntimeError(f"CudaGraph {self.name!r} replayed before capture")
+            raise CudaGraphError(f"CudaGraph {self.name!r} replayed before capture")
         if inputs:
             for k, v in inputs.items():
                 dst = self.static_inputs[k]

@@ -115,4 +115,16 @@ class TensorDumper:
         return torch.load(Path(directory) / f"pass{index:05d}.pt", map_location="cpu", weights_only=False)
 
 
-__all__ = ["TensorDumper"]
+load_filter_fn = _load_predicate
+
+
+def register_tensor_dumper(module: torch.nn.Module, out_dir: str | Path, *, prefix: str = "", patterns: tuple[str, ...] | None = None,
+                           filter_fn: str | Callable[[str], bool] | None = None) -> TensorDumper:
+    """A dumper hooked onto ``module``'s leaf modules in one call (``filter_fn``: a predicate or its ``"pkg.mod:func"`` spec)."""
+    pred = _load_predicate(filter_fn) if isinstance(filter_fn, str) else filter_fn
+    dumper = TensorDumper(out_dir, patterns=patterns, predicate=pred)
+    dumper.attach(module, prefix=prefix)
+    return dumper
+
+
+__all__ = ["TensorDumper", "load_filter_fn", "register_tensor_dumper"]

@@ -182,13 +182,34 @@ class TimelineProfiler(NoOpProfiler):
 _PROFILER: NoOpProfiler = NoOpProfiler()
 
 
+Profiler = NoOpProfiler          # the interface every profiler here implements (scope, mark, start, stop, step)
+NsysProfiler = NvtxProfiler      # Nsight Systems reads the NVTX ranges and the cudaProfilerStart / Stop window
+
+
+def make_profiler(cfg: ProfilerConfig | None) -> NoOpProfiler:
+    """A profiler for ``cfg`` without installing it (``install_profiler`` does both)."""
+    if cfg is None or cfg.kind == "none":
+        return NoOpProfiler()
+    kinds = {"torch": TorchProfiler, "nvtx": NvtxProfiler, "nsys": NvtxProfiler, "timeline": TimelineProfiler}
+    if cfg.kind not in kinds:
+        raise ValueError(f"unknown profiler kind {cfg.kind!r}; known: none, {', '.join(kinds)}")
+    return kinds[cfg.kind](cfg)
+
+
+def set_profiler(profiler: NoOpProfiler | None) -> NoOpProfiler:
+    """Install a profiler object as the process-wide one (``None``: the no-op profiler)."""
+    global _PROFILER
+    _PROFILER = profiler if profiler is not None else NoOpProfiler()
+    return _PROFILER
+
+
 def install_profiler(cfg: ProfilerConfig | None) -> NoOpProfiler:
     global _PROFILER
     if cfg is None or cfg.kind == "none" or (cfg.only_rank is not None and cfg.only_rank != _rank()):
         _PROFILER = NoOpProfiler()
     elif cfg.kind == "torch":
         _PROFILER = TorchProfiler(cfg)
-    elif cfg.kind == "nvtx":
+    elif cfg.kind in ("nvtx", "nsys"):
         _PROFILER = NvtxProfiler(cfg)
     else:
         _PROFILER = TimelineProfiler(cfg)
@@ -228,5 +249,5 @@ def profile_config_from_args(args: argparse.Namespace) -> ProfilerConfig:
                           module_ranges=args.profile_module_ranges)
 
 
-__all__ = ["ProfilerConfig", "NoOpProfiler", "TorchProfiler", "NvtxProfiler", "TimelineProfiler", "install_profiler",
+__all__ = ["Profiler", "NsysProfiler", "make_profiler", "set_profiler", "ProfilerConfig", "NoOpProfiler", "TorchProfiler", "NvtxProfiler", "TimelineProfiler", "install_profiler",
            "get_profiler", "event_scope", "mark_instant", "add_profile_cli_args", "profile_config_from_args"]

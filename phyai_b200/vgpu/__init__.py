@@ -165,21 +165,63 @@ class TorchGreenDriver:
         return None                      # released with the last reference
 
 
-def default_driver() -> DriverApi:
-    """``PHYAI_VGPU_BACKEND`` = ``torch`` | ``cuda`` (default: cuda-python when importable, else torch)."""
+class BackendCapabilityError(VGPUError):
+    """The chosen backend cannot do what was asked on this machine (no cuda-python, a torch build without green contexts)."""
+
+
+# name -> factory of a DriverApi; out-of-tree backends join with ``register_vgpu_backend``
+_BACKENDS: dict[str, Any] = {"cuda": CudaDriver, "torch": TorchGreenDriver}
+_CHOSEN: dict[str, str | None] = {"name": None}
+GreenCtxBackend = TorchGreenDriver
+
+
+def register_vgpu_backend(name: str):
+    """Decorator: make a :class:`DriverApi` factory selectable by name (``set_backend`` / ``PHYAI_VGPU_BACKEND``).
+    Reference: phyai/src/phyai/vgpu/backend.py."""
+    def deco(factory):
+        if name in _BACKENDS and _BACKENDS[name] is not factory:
+            raise ValueError(f"vGPU backend {name!r} is already registered")
+        _BACKENDS[name] = factory
+        return factory
+    return deco
+
+
+register = register_vgpu_backend
+
+
+def known_backends() -> list[str]:
+    return sorted(_BACKENDS)
+
+
+def set_backend(name: str | None) -> None:
+    """Choose the backend the next ``init()`` builds (``None``: back to ``PHYAI_VGPU_BACKEND`` / automatic)."""
+    if name is not None and name not in _BACKENDS:
+        raise VGPURuntimeError(f"unknown vGPU backend {name!r}; known: {known_backends()}")
+    _CHOSEN["name"] = name
+
+
+def get_backend() -> str:
+    """The name ``default_driver()`` resolves now: an explicit choice, else the environment, else ``"auto"``."""
     from ..env import envs
 
-    want = (envs.PHYAI_VGPU_BACKEND.get() or "").lower()
-    if want == "torch":
-        return TorchGreenDriver()
-    if want in ("", "cuda", "auto"):
+    return _CHOSEN["name"] or (envs.PHYAI_VGPU_BACKEND.get() or "auto").lower()
+
+
+def default_driver() -> DriverApi:
+    """The chosen backend's driver (``set_backend`` / ``PHYAI_VGPU_BACKEND``: a registered name; ``auto`` or unset:
+    cuda-python when importable, else torch green contexts)."""
+    want = get_backend()
+    if want in ("", "auto"):
         try:
             return CudaDriver()
         except ImportError:
-            if want == "cuda":
-                raise
             return TorchGreenDriver()
-    raise VGPURuntimeError(f"unknown vGPU backend {want!r} (cuda | torch)")
+    if want not in _BACKENDS:
+        raise VGPURuntimeError(f"unknown vGPU backend {want!r}; known: {known_backends()}")
+    try:
+        return _BACKENDS[want]()
+    except ImportError as e:
+        raise BackendCapabilityError(f"vGPU backend {want!r} is not usable here: {e}") from e
 
 
 @dataclass(frozen=True)
@@ -302,8 +344,10 @@ def close_all() -> None:
 
 def _reset_for_tests() -> None:
     _STATE.update(driver=None, device=None, open=[])
+    _CHOSEN["name"] = None
 
 
 __all__ = ["VGPUError", "VGPUNotApplicableError", "VGPURuntimeError", "VGPUDriverError", "get_sm_count_constraint", "round_up_sm_count",
            "validate_total", "DriverApi", "CudaDriver", "TorchGreenDriver", "default_driver", "Shard", "init", "split_device", "split_device_by_sm_count", "vGPU", "create_vgpus",
-           "close_all"]
+           "close_all", "BackendCapabilityError", "GreenCtxBackend", "register_vgpu_backend", "register", "known_backends", "set_backend",
+           "get_backend"]

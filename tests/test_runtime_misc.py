@@ -194,3 +194,31 @@ def test_show_env_cli(capsys):
     info = _json.loads(out)
     assert "torch" in info and "PHYAI_PEER_COMM" in info["env"] and "jit_cache_dir" in info
     assert main(["nope"]) == 2
+
+
+def test_vgpu_backend_registry(monkeypatch):
+    from phyai_b200 import vgpu
+
+    vgpu._reset_for_tests()
+    assert vgpu.known_backends() == ["cuda", "torch"] and vgpu.get_backend() == "auto" and vgpu.GreenCtxBackend is vgpu.TorchGreenDriver
+    monkeypatch.setenv("PHYAI_VGPU_BACKEND", "torch")
+    assert vgpu.get_backend() == "torch"
+
+    @vgpu.register_vgpu_backend("fake")
+    class Fake(FakeDriver):
+        pass
+
+    try:
+        assert "fake" in vgpu.known_backends()
+        vgpu.set_backend("fake")                             # an explicit choice wins over the environment
+        assert vgpu.get_backend() == "fake" and isinstance(vgpu.default_driver(), Fake)
+        assert isinstance(vgpu.init(0), Fake)
+        with pytest.raises(ValueError, match="already registered"):
+            vgpu.register_vgpu_backend("fake")(FakeDriver)
+        with pytest.raises(vgpu.VGPURuntimeError, match="unknown vGPU backend 'nope'"):
+            vgpu.set_backend("nope")
+        vgpu.set_backend(None)
+        assert vgpu.get_backend() == "torch"
+    finally:
+        vgpu._BACKENDS.pop("fake", None)
+        vgpu._reset_for_tests()
