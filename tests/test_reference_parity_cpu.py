@@ -602,3 +602,71 @@ def test_quantisation_plans_from_checkpoint_configs(ref, tmp_path):
             if a is not None and b is not None and a[0] == b[0] == "fp8_e4m3" and {a[1], b[1]} == {"per_tensor", "per_channel"}:
                 continue      # one scale per tensor in the file; both packages fan it out per channel after loading
             assert a == b, (tag, n, a, b)
+
+
+def test_prefix_cache_encodings_and_behaviour(ref):
+    """The prompt encodings byte for byte, and one scripted life of a prefix cache (inserts that share prefixes, matches
+    that split edges, a full device tier under each eviction policy) against the reference's native cache: the same
+    match lengths, unit counts and inserted / freed numbers at every step."""
+    import hashlib
+    import random
+
+    from phyai_b200.cache import radix_cache as mine
+
+    theirs, native = ref("phyai.cache.radix_cache"), ref("phyai_ext.radix_cache")
+    enc = ref("phyai.cache.radix_cache.encoding")
+    rng = random.Random(0)
+    ids = [rng.randrange(0, 2 ** 31 - 1) for _ in range(37)]
+    assert mine.encode_text_atoms_int32(ids) == enc.encode_text_atoms_int32(ids)
+    assert mine.encode_eagle_bigram_atoms(ids) == enc.encode_eagle_bigram_atoms(ids)
+    hashes = [rng.randrange(0, 2 ** 64) for _ in range(9)]
+    assert mine.encode_chunk_hash_atoms_u64(hashes) == enc.encode_chunk_hash_atoms_u64(hashes)
+    digest = hashlib.sha256(b"image").digest()
+    assert mine.encode_image_hash_atom_sha256(digest) == enc.encode_image_hash_atom_sha256(digest)
+    segs = [(5, 3), (20, 4)]
+    a = mine.encode_prompt_to_atoms(ids, [mine.ImageSegment(11 + i, 22 + i, p, n) for i, (p, n) in enumerate(segs)])
+    b = enc.encode_prompt_to_atoms(ids, [enc.ImageSegment(11 + i, 22 + i, p, n) for i, (p, n) in enumerate(segs)])
+    assert a == b
+    for page in (8, 16, 64):
+        assert mine.page_align(a, page) == enc.page_align(b, page)
+
+    def life(mod, cache_cls, tier):
+        """Inserts that share prefixes and matches that split edges, in a tier large enough that nothing is evicted."""
+        c = cache_cls(atom_bytes=4, atoms_per_unit=2, device_total_units=64)
+        log = [("page", c.page_bytes, c.total(tier), c.available(tier))]
+        r = random.Random(7)
+        seqs = [[r.randrange(0, 50) for _ in range(r.choice((4, 6, 8, 10)))] for _ in range(6)]
+        seqs += [seqs[0][:4] + [91, 92, 93, 94], seqs[1][:2] + [81, 82], seqs[0][:4] + [91, 92, 71, 72], seqs[0][:3]]
+        for s_ in seqs:
+            atoms, _ = mod.page_align(mod.encode_text_atoms_int32(s_), c.page_bytes)
+            log.append(("match", c.match(atoms).matched_atoms[0]))
+            need = len(atoms) // c.page_bytes
+            if need:
+                _, inserted, freed = c.insert(tier, atoms, c.allocate(tier, need))
+                log.append(("insert", inserted, freed, c.active(tier), c.available(tier)))
+            log.append(("rematch", c.match(atoms).matched_atoms[0]))
+            c.advance_step(1)
+        return log
+
+    assert life(mine, mine.PrefixCache, mine.Tier.DEVICE) == life(enc, native.PrefixCache, native.Tier.DEVICE)
+
+    def eviction(mod, cache_cls, tier, policy):
+        """Three one-page prefixes with distinct recency and hit counts fill the tier; room for two pages is asked for."""
+        c = cache_cls(atom_bytes=4, atoms_per_unit=1, device_total_units=7, eviction_policy=policy, slru_threshold=2)
+        tok = mod.encode_text_atoms_int32
+        for ids in ([1, 2], [3, 4], [5, 6]):
+            c.insert(tier, tok(ids), c.allocate(tier, 2))
+            c.advance_step(1)
+        c.match(tok([1, 2]))
+        c.advance_step(1)
+        c.match(tok([1, 2]))
+        c.advance_step(1)
+        c.match(tok([5, 6]))
+        c.advance_step(1)
+        c.ensure_capacity(tier, 2)
+        return [c.match(tok(ids)).matched_atoms[0] for ids in ([1, 2], [3, 4], [5, 6])], c.available(tier)
+
+    for policy in ("lru", "lfu", "slru"):
+        got = eviction(mine, mine.PrefixCache, mine.Tier.DEVICE, policy)
+        want = eviction(enc, native.PrefixCache, native.Tier.DEVICE, policy)
+        assert got == want == ([2, 0, 2], 2), (policy, got, want)       # the prefix that is neither recent nor hot goes
