@@ -205,6 +205,29 @@ def main() -> int:
         except (ValueError, RuntimeError):
             pass
         eng.entry.scheduler.local.close()
+    elif mode == "seq_parallel":
+        # Megatron-style sequence parallelism on the tensor-parallel axis: activations between the two linears' blocks are
+        # split by tokens; the column-parallel layer gathers the tokens, the row-parallel layer reduce-scatters them back
+        mesh = P.init((world,), ("tp",), device="cpu")
+        L.init()
+        H, I, T = 16, 24 * world, 6 * world
+        g = torch.Generator().manual_seed(3)
+        w1, b1, w2, b2 = torch.randn(I, H, generator=g), torch.randn(I, generator=g), torch.randn(H, I, generator=g), torch.randn(H, generator=g)
+        x = torch.randn(T, H, generator=g)
+        col = L.ColumnParallelLinear(H, I, bias=True, sp_axis="tp", params_dtype=torch.float32)
+        row = L.RowParallelLinear(I, H, bias=True, sp_axis="tp", params_dtype=torch.float32)
+        per_i, per_t = I // world, T // world
+        col.weight.data.copy_(w1[rank * per_i:(rank + 1) * per_i])
+        col.bias.data.copy_(b1[rank * per_i:(rank + 1) * per_i])
+        row.weight.data.copy_(w2[:, rank * per_i:(rank + 1) * per_i])
+        row.bias.data.copy_(b2)
+        h, _ = col(x[rank * per_t:(rank + 1) * per_t].contiguous())            # this rank's tokens in, all tokens x this rank's columns out
+        check("seq_parallel.column", h, (x @ w1.t() + b1)[:, rank * per_i:(rank + 1) * per_i], 1e-5)
+        y, _ = row(torch.relu(h))
+        want = torch.relu(x @ w1.t() + b1) @ w2.t() + b2
+        check("seq_parallel.row", y, want[rank * per_t:(rank + 1) * per_t], 1e-4)   # this rank's tokens of the full result; the bias once
+        if y.shape != (per_t, H):
+            fails.append(f"seq_parallel: output {tuple(y.shape)} is not this rank's token shard")
     else:
         raise SystemExit(f"unknown mode {mode}")
 
