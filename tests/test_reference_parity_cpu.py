@@ -670,3 +670,38 @@ def test_prefix_cache_encodings_and_behaviour(ref):
         got = eviction(mine, mine.PrefixCache, mine.Tier.DEVICE, policy)
         want = eviction(enc, native.PrefixCache, native.Tier.DEVICE, policy)
         assert got == want == ([2, 0, 2], 2), (policy, got, want)       # the prefix that is neither recent nor hot goes
+
+
+def test_environment_catalogue_and_engine_config_fields(ref, monkeypatch):
+    """Every ``PHYAI_*`` variable and every engine configuration field of the reference exists here with the same default
+    (backend names differ: this package's kernels are its own), and the same environment gives the same configuration."""
+    import dataclasses
+
+    from phyai_b200 import engine_config as mine_ec
+    from phyai_b200 import env as mine_env
+
+    their_env, their_ec = ref("phyai.env"), ref("phyai.engine_config")
+    names = lambda mod: {k: v for k, v in vars(mod.envs).items() if k.startswith("PHYAI_")}  # noqa: E731
+    a, b = names(mine_env), names(their_env)
+    assert set(b) <= set(a), sorted(set(b) - set(a))
+    for k in b:
+        assert getattr(a[k], "default", None) == getattr(b[k], "default", None), k
+    for cls in ("BackendConfig", "DeviceConfig", "ParallelConfig", "RuntimeConfig"):
+        fa = {f.name: f.default for f in dataclasses.fields(getattr(mine_ec, cls))}
+        fb = {f.name: f.default for f in dataclasses.fields(getattr(their_ec, cls))}
+        assert set(fb) <= set(fa), (cls, sorted(set(fb) - set(fa)))
+        diff = {k for k in fb if fa[k] != fb[k] and not callable(fa[k])}
+        assert diff <= ({"attn", "norm"} if cls == "BackendConfig" else set()), (cls, diff)
+    for k, v in {"PHYAI_DEVICE": "cpu", "PHYAI_PARAMS_DTYPE": "float16", "PHYAI_FORCE_LINEAR_KERNEL": "torch",
+                 "PHYAI_DEBUG_TENSOR_DUMP_DIR": "/tmp/x", "PHYAI_DEBUG_TENSOR_DUMP_FILTER": "a.*,b$", "PHYAI_FLASHINFER_WORKSPACE_BYTES": "1048576"}.items():
+        monkeypatch.setenv(k, v)
+
+    def flat(x, pre=""):
+        out = {}
+        for f in dataclasses.fields(x):
+            v = getattr(x, f.name)
+            out.update(flat(v, pre + f.name + ".")) if dataclasses.is_dataclass(v) else out.update({pre + f.name: str(v)})
+        return out
+
+    fa, fb = flat(mine_ec.EngineConfig.from_env()), flat(their_ec.EngineConfig.from_env())
+    assert {k for k in fb if fa.get(k) != fb[k]} <= {"backends.attn", "backends.norm"}
