@@ -220,34 +220,65 @@ class Cosmos3Processor:
         return self.tokenize(prompt, device=device, augment=True), self.tokenize(neg, device=device, augment=False)
 
 
+@dataclass
+class Cosmos3GenerationOutput:
+    """Media of one generation request on the CPU: ``frames`` (T, H, W, 3) uint8 RGB, ``video`` as the engine returned
+    it ([0, 1] floats), and for requests with sound the ``waveform`` in [-1, 1] with its ``sample_rate``. Fields can
+    also be read by name like a dict (``out["frames"]``)."""
+
+    frames: torch.Tensor
+    video: torch.Tensor
+    waveform: torch.Tensor | None = None
+    sample_rate: int | None = None
+
+    def __getitem__(self, key: str):
+        if key not in ("frames", "video", "waveform", "sample_rate"):
+            raise KeyError(key)
+        return getattr(self, key)
+
+
 class Cosmos3GenerationPostProcessor:
+    """Output side of the generation plugin (its pixels are already VAE-decoded): tensors to the CPU, pixels to uint8
+    frames, frames (and sound) into an mp4 through PyAV or into an ``.npz``."""
+
     def __init__(self, fps: float) -> None:
         self.fps = float(fps)
 
     @staticmethod
     def to_uint8_frames(video: torch.Tensor) -> torch.Tensor:
-        """(B, 3, T, H, W) or (3, T, H, W) in [0, 1] -> (T, H, W, 3) uint8 of the first sample."""
+        """(1, 3, T, H, W) or (3, T, H, W) in [0, 1] -> (T, H, W, 3) uint8 of the first sample."""
         v = video[0] if video.dim() == 5 else video
+        if v.dim() != 4 or v.shape[0] != 3:
+            raise ValueError(f"a video is (1, 3, T, H, W) or (3, T, H, W), got {tuple(video.shape)}")
         return (v.float().clamp(0, 1) * 255.0).round().to(torch.uint8).permute(1, 2, 3, 0).contiguous().cpu()
 
-    def postprocess(self, output) -> dict[str, Any]:
-        if isinstance(output, dict):
-            res = {"frames": self.to_uint8_frames(output["video"]), "fps": self.fps}
-            if "sound" in output:
-                res["waveform"], res["sample_rate"] = output["sound"][0].float().cpu(), int(output["sample_rate"])
-            return res
-        return {"frames": self.to_uint8_frames(output), "fps": self.fps}
+    def postprocess(self, output) -> Cosmos3GenerationOutput:
+        video, waveform, rate = (output["video"], output.get("sound"), output.get("sample_rate")) if isinstance(output, dict) else (output, None, None)
+        if not isinstance(video, torch.Tensor):
+            raise TypeError(f"expected a video tensor, got {type(video)!r}")
+        wave = waveform.detach().clamp(-1.0, 1.0).float().cpu() if isinstance(waveform, torch.Tensor) else None
+        return Cosmos3GenerationOutput(self.to_uint8_frames(video), video.detach().cpu(), wave, int(rate) if rate is not None else None)
 
-    def save_mp4(self, frames: torch.Tensor, path: str | Path, *, waveform: torch.Tensor | None = None, sample_rate: int | None = None) -> Path:
-        """H.264 (+ AAC) through PyAV when it is installed; otherwise raises and ``save_npz`` is the portable writer."""
+    def save_mp4(self, output, path: str | Path, *, waveform: torch.Tensor | None = None, sample_rate: int | None = None,
+                 crf: str = "18") -> Path:
+        """H.264 (+ AAC when there is a waveform) through PyAV. ``output``: what :meth:`postprocess` returned, or bare
+        frames with ``waveform`` / ``sample_rate`` beside them. Without PyAV this raises; :meth:`save_npz` needs nothing."""
         try:
             import av
         except ImportError as e:
             raise RuntimeError("writing mp4 needs the 'av' package; use save_npz for a dependency-free dump") from e
+        if isinstance(output, Cosmos3GenerationOutput):
+            frames, waveform, sample_rate = output.frames, output.waveform, output.sample_rate
+        else:
+            frames = output
+        if waveform is not None and waveform.dim() == 3:
+            waveform = waveform[0]
         path = Path(path)
+        path.parent.mkdir(parents=True, exist_ok=True)
         with av.open(str(path), mode="w") as c:
             vs = c.add_stream("h264", rate=round(self.fps))
             vs.height, vs.width, vs.pix_fmt = int(frames.shape[1]), int(frames.shape[2]), "yuv420p"
+            vs.options = {"crf": str(crf)}
             aus = None
             if waveform is not None and sample_rate:
                 aus = c.add_stream("aac", rate=int(sample_rate))
@@ -266,7 +297,10 @@ class Cosmos3GenerationPostProcessor:
                     c.mux(pkt)
         return path
 
-    def save_npz(self, frames: torch.Tensor, path: str | Path, **extra) -> Path:
+    def save_npz(self, frames, path: str | Path, **extra) -> Path:
+        if isinstance(frames, Cosmos3GenerationOutput):
+            extra = {**({"waveform": frames.waveform, "sample_rate": frames.sample_rate} if frames.waveform is not None else {}), **extra}
+            frames = frames.frames
         path = Path(path)
         np.savez_compressed(path, frames=frames.numpy(), fps=self.fps, **{k: (v.numpy() if hasattr(v, "numpy") else v) for k, v in extra.items()})
         return path
@@ -567,7 +601,7 @@ class Cosmos3PolicyProcessor(BaseModelProcessor):
         return res
 
 
-__all__ = ["Cosmos3Processor", "Cosmos3TokenizedPrompt", "Cosmos3GenerationPostProcessor", "Cosmos3PolicyProcessor",
+__all__ = ["Cosmos3Processor", "Cosmos3TokenizedPrompt", "Cosmos3GenerationOutput", "Cosmos3GenerationPostProcessor", "Cosmos3PolicyProcessor",
            "Cosmos3PolicyProcessedInputs", "Cosmos3ImagePreprocessStep", "Cosmos3TextTokenizeStep", "Cosmos3ActionPadStep",
            "Cosmos3DomainResolveStep", "EMBODIMENT_TO_DOMAIN_ID", "EMBODIMENT_TO_RAW_ACTION_DIM", "VIDEO_RES_SIZE_INFO",
            "DEFAULT_VIEWPOINT_TEMPLATES", "resolve_domain_id", "resolve_raw_action_dim", "get_vision_data_resolution",

@@ -705,3 +705,23 @@ def test_environment_catalogue_and_engine_config_fields(ref, monkeypatch):
 
     fa, fb = flat(mine_ec.EngineConfig.from_env()), flat(their_ec.EngineConfig.from_env())
     assert {k for k in fb if fa.get(k) != fb[k]} <= {"backends.attn", "backends.norm"}
+
+
+def test_cosmos3_generation_media_output(ref):
+    from phyai_b200.tools import cosmos3 as mine
+
+    theirs = ref("phyai_utils_tools.models.cosmos3.processor_cosmos3")
+    g = torch.Generator().manual_seed(0)
+    video = torch.rand(1, 3, 5, 16, 24, generator=g) * 1.2 - 0.1           # a little outside [0, 1]: clamped
+    sound = torch.randn(1, 2, 480, generator=g)
+    a, b = mine.Cosmos3GenerationPostProcessor(fps=24), theirs.Cosmos3GenerationPostProcessor(fps=24)
+    for out in (video, video[0], {"video": video, "sound": sound, "sample_rate": 48000}):
+        x, y = a.postprocess(out), b.postprocess(out)
+        assert torch.equal(x.frames, y.frames) and x.frames.dtype == torch.uint8 and torch.equal(x.video, y.video)
+        assert (x.waveform is None) == (y.waveform is None) and (x.waveform is None or torch.equal(x.waveform, y.waveform))
+        assert x.sample_rate == y.sample_rate and x["frames"] is x.frames
+    for bad in (torch.rand(3, 16, 24), torch.rand(1, 4, 5, 16, 24)):
+        with pytest.raises(ValueError):
+            a.postprocess(bad)
+        with pytest.raises(ValueError):
+            b.postprocess(bad)

@@ -159,10 +159,16 @@ def test_cosmos3_policy_processor_and_postprocess(tmp_path):
     with pytest.raises(ValueError, match="action_normalization"):
         c3.Cosmos3PolicyProcessor(tokenizer=FakeChatTokenizer(), domain_name="pusht", action_normalization="zscore")
     post = c3.Cosmos3GenerationPostProcessor(fps=24)
-    frames = post.postprocess(torch.rand(1, 3, 5, 16, 24))["frames"]
-    assert frames.shape == (5, 16, 24, 3) and frames.dtype == torch.uint8
+    media = post.postprocess({"video": torch.rand(1, 3, 5, 16, 24), "sound": torch.randn(1, 2, 96) * 3, "sample_rate": 48000})
+    frames = media.frames
+    assert frames.shape == (5, 16, 24, 3) and frames.dtype == torch.uint8 and media["frames"] is frames and media.video.shape == (1, 3, 5, 16, 24)
+    assert media.sample_rate == 48000 and float(media.waveform.abs().max()) <= 1.0                # the waveform is clamped to [-1, 1]
     f = post.save_npz(frames, tmp_path / "clip.npz")
     assert np.load(f)["frames"].shape == (5, 16, 24, 3)
+    saved = np.load(post.save_npz(media, tmp_path / "clip2.npz"))
+    assert saved["frames"].shape == (5, 16, 24, 3) and saved["waveform"].shape == (1, 2, 96) and int(saved["sample_rate"]) == 48000
+    with pytest.raises(KeyError):
+        media["fps"]
 
 
 def test_pi05_processor_end_to_end_and_saved_pair(tmp_path):
