@@ -127,7 +127,8 @@ class PI05Processor(BaseModelProcessor):
         return PI05ProcessedInputs(t[PIXEL_VALUES], t[INPUT_IDS], t[LANG_LENS])
 
     def _vision_steps(self) -> list[ProcessorStep]:
-        steps: list[ProcessorStep] = [ResizeWithPadStep(self.image_size, self.image_size, self.image_pad_value)]
+        steps: list[ProcessorStep] = [ResizeWithPadStep(self.image_size, self.image_size, self.image_pad_value, num_images=self.num_images,
+                                                        num_channels=self.num_channels)]
         if self.normalize_pixels:
             steps.append(NormalizeImageStep())
         return steps

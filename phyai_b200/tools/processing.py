@@ -265,22 +265,51 @@ def normalize_pixels(images: torch.Tensor) -> torch.Tensor:
 @ProcessorStepRegistry.register("resize_with_pad_step")
 @dataclass
 class ResizeWithPadStep(ProcessorStep):
-    """``images`` (list of per-camera (B, C, H, W) or stacked (B, n, C, H, W)) -> ``pixel_values`` (B, n, C, h, w)."""
+    """``images`` (list of per-camera (B, C, H, W) or stacked (B, n, C, H, W)) -> ``pixel_values`` (B, n, C, h, w).
+
+    The target is ``height`` x ``width``, or ``target_size`` squared (the reference's spelling:
+    phyai-utils-tools/src/phyai_utils_tools/processing/steps/image_steps.py:31-45). ``num_images`` / ``num_channels``, when
+    given, are checked against what arrives (a wrong camera count or channel count is an error, not a silent reshape)."""
 
     height: int = 224
     width: int = 224
     pad_value: float = 0.0
     mode: str = "bilinear"
+    target_size: int | None = None
+    num_images: int | None = None
+    num_channels: int | None = None
+
+    def __post_init__(self) -> None:
+        if self.target_size is not None:
+            self.height = self.width = int(self.target_size)
 
     def __call__(self, t: Transition) -> Transition:
         imgs = t[IMAGES]
-        cams = list(imgs.unbind(1)) if isinstance(imgs, torch.Tensor) else list(imgs)
-        t[PIXEL_VALUES] = torch.stack([resize_with_pad(c, self.height, self.width, mode=self.mode, pad_value=self.pad_value)
-                                       for c in cams], dim=1)
-        return t
+        if isinstance(imgs, torch.Tensor):
+            if imgs.dim() != 5:
+                raise ValueError(f"stacked images are (B, num_images, C, H, W), got {tuple(imgs.shape)}")
+            cams = list(imgs.unbind(1))
+        else:
+            cams = list(imgs)
+        if self.num_images is not None and len(cams) != self.num_images:
+            raise ValueError(f"expected {self.num_images} cameras, got {len(cams)}")
+        for i, c in enumerate(cams):
+            if c.dim() != 4:
+                raise ValueError(f"camera {i} is (B, C, H, W), got {tuple(c.shape)}")
+            if self.num_channels is not None and c.shape[1] != self.num_channels:
+                raise ValueError(f"camera {i} has {c.shape[1]} channels, expected {self.num_channels}")
+        out = dict(t)
+        out[PIXEL_VALUES] = torch.stack([resize_with_pad(c, self.height, self.width, mode=self.mode, pad_value=self.pad_value)
+                                         for c in cams], dim=1)
+        return out
 
     def get_config(self):
-        return {"height": self.height, "width": self.width, "pad_value": self.pad_value, "mode": self.mode}
+        cfg = {"height": self.height, "width": self.width, "pad_value": self.pad_value, "mode": self.mode}
+        if self.num_images is not None:
+            cfg["num_images"] = self.num_images
+        if self.num_channels is not None:
+            cfg["num_channels"] = self.num_channels
+        return cfg
 
 
 @ProcessorStepRegistry.register("normalize_image_step")

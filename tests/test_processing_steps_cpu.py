@@ -48,6 +48,14 @@ def test_image_steps_take_lists_or_stacks_and_uint8():
     stacked = pp.ResizeWithPadStep(height=8, width=8)({pp.IMAGES: torch.rand(2, 3, 3, 8, 8)})
     assert stacked[pp.PIXEL_VALUES].shape == (2, 3, 3, 8, 8)
     assert pp.ResizeWithPadStep(4, 6, 0.5, "nearest").get_config() == {"height": 4, "width": 6, "pad_value": 0.5, "mode": "nearest"}
+    # the reference's spelling: a square target and the expected camera / channel counts
+    sq = pp.ResizeWithPadStep(target_size=8, num_images=2, num_channels=3)
+    assert (sq.height, sq.width) == (8, 8) and torch.equal(sq({pp.IMAGES: cams})[pp.PIXEL_VALUES], pp.ResizeWithPadStep(8, 8)({pp.IMAGES: cams})[pp.PIXEL_VALUES])
+    assert sq.get_config() == {"height": 8, "width": 8, "pad_value": 0.0, "mode": "bilinear", "num_images": 2, "num_channels": 3}
+    for bad, msg in (([cams[0]], "expected 2 cameras"), ([cams[0], torch.zeros(2, 1, 4, 4, dtype=torch.uint8)], "has 1 channels"),
+                     (torch.zeros(2, 3, 8, 8), "stacked images are"), ([cams[0], torch.zeros(3, 4, 4)], "camera 1 is")):
+        with pytest.raises(ValueError, match=msg):
+            sq({pp.IMAGES: bad})
 
 
 # ------------------------------------------------------------------ normalisation

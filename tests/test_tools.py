@@ -44,7 +44,7 @@ def test_normalizer_round_trip(mode):
 
 def test_pipeline_save_load_lerobot_layout(tmp_path):
     stats = {ACTION_FEATURE: {"q01": [-1.0, -2.0], "q99": [1.0, 2.0]}, STATE_FEATURE: {"q01": [0.0] * 3, "q99": [1.0] * 3}}
-    p = PI05Processor(tokenizer=ByteTokenizer(), dataset_stats=stats, action_dim=2, image_size=32, tokenizer_max_length=256, params_dtype=torch.float32)
+    p = PI05Processor(tokenizer=ByteTokenizer(), dataset_stats=stats, action_dim=2, image_size=32, num_images=2, tokenizer_max_length=256, params_dtype=torch.float32)
     p.save_pretrained(tmp_path)
     cfg = json.loads((tmp_path / "policy_preprocessor.json").read_text())
     names = [s["registry_name"] for s in cfg["steps"]]
@@ -55,7 +55,7 @@ def test_pipeline_save_load_lerobot_layout(tmp_path):
     norm = cfg["steps"][0]
     assert norm["config"]["norm_map"]["STATE"] == "QUANTILES" and (tmp_path / norm["state_file"]).is_file() and "stats" not in norm["config"]
     assert cfg["steps"][1]["config"] == {} and cfg["steps"][2]["config"]["task_key"] == "task"
-    q = PI05Processor.from_pretrained(tmp_path, tokenizer=ByteTokenizer(), params_dtype=torch.float32, image_size=32, action_dim=2)
+    q = PI05Processor.from_pretrained(tmp_path, tokenizer=ByteTokenizer(), params_dtype=torch.float32, image_size=32, num_images=2, action_dim=2)
     assert [type(s).__name__ for s in q.preprocessor.steps][:2] == ["ResizeWithPadStep", "NormalizerStep"] and q.tokenizer_max_length == 256
     raw = {IMAGES: [torch.rand(1, 3, 48, 64)] * 2, STATE: torch.tensor([[0.25, 0.5, 1.0]]), TASK: ["pick_up the\ncube"]}
     a, b = p.preprocess(dict(raw)), q.preprocess(dict(raw))
@@ -177,7 +177,7 @@ def test_pi05_processor_end_to_end_and_saved_pair(tmp_path):
     from phyai_b200.tools.pi05 import PI05Processor, StateTokenizerPrepareStep, make_pi05_processors
 
     stats = {"observation.state": {"q01": [0.0, 0.0], "q99": [2.0, 4.0]}, "action": {"q01": [-1.0] * 3, "q99": [3.0] * 3}}
-    p = PI05Processor(tokenizer=ByteTokenizer(), image_size=16, tokenizer_max_length=160, params_dtype=torch.float32, action_dim=3,
+    p = PI05Processor(tokenizer=ByteTokenizer(), image_size=16, num_images=2, tokenizer_max_length=160, params_dtype=torch.float32, action_dim=3,
                       dataset_stats=stats, max_state_dim=4, pad_state=True)
     sample = {IMAGES: torch.rand(1, 2, 3, 8, 16), STATE: torch.tensor([[1.0, 4.0]]), TASK: "pick_up the\ncube "}
     out = p.preprocess(dict(sample))
@@ -185,7 +185,7 @@ def test_pi05_processor_end_to_end_and_saved_pair(tmp_path):
     text = ByteTokenizer().decode(out.input_ids[0, : int(out.lang_lens[0])])
     # state 1.0 of [0, 2] -> 0 -> bin 128; 4.0 of [0, 4] -> ~1 -> bin 255; two padding columns at 0 -> bin 128
     assert text == "Task: pick up the cube, State: 128 255 128 128;\nAction: "
-    bare = PI05Processor(tokenizer=ByteTokenizer(), image_size=16, tokenizer_max_length=160, params_dtype=torch.float32, dataset_stats=stats)
+    bare = PI05Processor(tokenizer=ByteTokenizer(), image_size=16, num_images=2, tokenizer_max_length=160, params_dtype=torch.float32, dataset_stats=stats)
     bare_text = ByteTokenizer().decode(bare.preprocess(dict(sample)).input_ids[0])
     assert "State: 128 255;" in bare_text                                                        # default: the bins of the state given, no padding
     act = p.postprocess(torch.zeros(1, 5, 32))
@@ -194,9 +194,13 @@ def test_pi05_processor_end_to_end_and_saved_pair(tmp_path):
     assert StateTokenizerPrepareStep()({TASK: "fold_it"})[PROMPT] == ["Task: fold it;\nAction: "]   # no state: the task alone
     with pytest.raises(ValueError, match="needs 'task'"):
         StateTokenizerPrepareStep()({STATE: torch.zeros(1, 2)})
+    with pytest.raises(ValueError, match="expected 2 cameras, got 3"):
+        p.preprocess({IMAGES: torch.rand(1, 3, 3, 8, 16), STATE: torch.zeros(1, 2), TASK: "x"})
+    with pytest.raises(ValueError, match="has 1 channels, expected 3"):
+        p.preprocess({IMAGES: torch.rand(1, 2, 1, 8, 16), STATE: torch.zeros(1, 2), TASK: "x"})
     p.save_pretrained(tmp_path)
     assert (tmp_path / "policy_preprocessor.json").is_file() and (tmp_path / "policy_postprocessor.json").is_file()
-    q = PI05Processor.from_pretrained(tmp_path, tokenizer=ByteTokenizer(), params_dtype=torch.float32, image_size=16, action_dim=3)
+    q = PI05Processor.from_pretrained(tmp_path, tokenizer=ByteTokenizer(), params_dtype=torch.float32, image_size=16, num_images=2, action_dim=3)
     assert q.pad_state and q.max_state_dim == 4                                                  # padding is on: it is saved with the step
     again = q.preprocess(dict(sample))
     assert torch.equal(again.input_ids, out.input_ids) and torch.equal(again.pixel_values, out.pixel_values)
