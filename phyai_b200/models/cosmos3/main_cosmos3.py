@@ -44,6 +44,10 @@ class Cosmos3Args(EntryArgs):
     avae_config: Cosmos3AVAESoundConfig | None = None
     weight_strict: bool = False
     random_init_seed: int = 0
+    # accepted so that argument bundles written for the reference load: nothing here goes through torch.compile (the GEN
+    # tower runs this package's kernels, on one GPU as a CUDA graph per request geometry), so the two are not acted on
+    torch_compile: bool = False
+    compile_kwargs: dict | None = None
 
 
 def wants_sound(args, config: Cosmos3Config) -> bool:
