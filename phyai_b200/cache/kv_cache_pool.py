@@ -30,6 +30,16 @@ class KVCachePool:
         """``(slots, kv_heads, head_dim)`` views of one layer."""
         return self.k[layer_id], self.v[layer_id]
 
+    def k_buffer(self, layer_id: int) -> torch.Tensor:
+        """The layer's K rows ``(slots, kv_heads, head_dim)``: a view of the pool, writes through it reach the pool."""
+        return self.k[layer_id]
+
+    def v_buffer(self, layer_id: int) -> torch.Tensor:
+        return self.v[layer_id]
+
+    def kv_buffer(self, layer_id: int) -> tuple[torch.Tensor, torch.Tensor]:
+        return self.k[layer_id], self.v[layer_id]
+
     def write_kv(self, layer_id: int, k: torch.Tensor, v: torch.Tensor, write_indices: torch.Tensor) -> None:
         """Scatter ``k``/``v`` rows ``(T, kv_heads, head_dim)`` to the slots in ``write_indices`` (int64)."""
         if write_indices.dtype != torch.int64:

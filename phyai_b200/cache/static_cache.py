@@ -39,6 +39,14 @@ class StaticCache:
         self._used += n
         return torch.arange(start, start + n, dtype=torch.int64, device=self.pool.device)
 
+    def slot_range(self) -> tuple[int, int]:
+        """``(first, one past last)`` slot of the slab in the pool."""
+        return self.base_offset, self.base_offset + self.capacity
+
+    def used_slot_range(self) -> tuple[int, int]:
+        """The slots handed out so far."""
+        return self.base_offset, self.base_offset + self._used
+
     def reset(self) -> None:
         self._used = 0
 

@@ -35,7 +35,9 @@ def _kernel_ok(backend: str, x: torch.Tensor) -> bool:
 class Attention(nn.Module):
     def __init__(self, num_heads: int, head_dim: int, num_kv_heads: int | None = None, *, scale: float | None = None,
                  causal: bool = False, sliding_window: int | None = None, logits_soft_cap: float | None = None,
-                 backend: str | None = None) -> None:
+                 backend: str | None = None, backend_kwargs: dict | None = None) -> None:
+        """``backend_kwargs`` is accepted for argument bundles written for the reference (its backends take workspace sizes
+        and the like); the kernels here need none."""
         super().__init__()
         _, backend, _ = resolve_engine_defaults(None, backend, None)
         self.num_heads, self.head_dim = num_heads, head_dim
@@ -140,7 +142,8 @@ class _PagedAttention(nn.Module):
     default_causal = True
 
     def __init__(self, layer_id: int, num_heads: int, head_dim: int, num_kv_heads: int | None = None, *,
-                 scale: float | None = None, causal: bool | None = None, backend: str | None = None) -> None:
+                 scale: float | None = None, causal: bool | None = None, backend: str | None = None,
+                 backend_kwargs: dict | None = None) -> None:
         super().__init__()
         _, backend, _ = resolve_engine_defaults(None, backend, None)
         self.layer_id, self.num_heads, self.head_dim = layer_id, num_heads, head_dim

@@ -55,17 +55,22 @@ class GemmaRMSNorm(RMSNorm):
 
 
 class LayerNorm(nn.Module):
-    def __init__(self, hidden_size: int, eps: float = 1e-6, *, backend: str | None = None,
+    def __init__(self, hidden_size: int, eps: float = 1e-6, *, bias: bool = True, backend: str | None = None,
                  dtype: torch.dtype | None = None, device=None, prefix: str = "") -> None:
+        """``bias=False``: the shift stays zero and expects no checkpoint tensor."""
         super().__init__()
         dtype, _, backend = resolve_engine_defaults(dtype, None, backend)
         device = device if device is not None else get_engine_config().device.target
         self.hidden_size, self.eps, self.backend, self.prefix = hidden_size, eps, backend, prefix
         self.weight = nn.Parameter(torch.ones(hidden_size, dtype=dtype, device=device), requires_grad=False)
         self.bias = nn.Parameter(torch.zeros(hidden_size, dtype=dtype, device=device), requires_grad=False)
+        self.has_bias = bool(bias)
         if prefix:
             self.weight.hf_keys = {f"{prefix}.weight": None}
-            self.bias.hf_keys = {f"{prefix}.bias": None}
+            if bias:
+                self.bias.hf_keys = {f"{prefix}.bias": None}
+        if not bias:
+            self.bias.optional = True
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if _use_kernel(self.backend, x):

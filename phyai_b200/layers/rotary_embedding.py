@@ -55,8 +55,23 @@ def compute_cos_sin_from_inv_freq(positions: torch.Tensor, inv_freq: torch.Tenso
 
 class RotaryEmbedding(nn.Module):
     def __init__(self, head_dim: int, max_position: int = 8192, theta: float = 10000.0, *, rotary_dim: int | None = None,
-                 scaling: dict | None = None, device=None) -> None:
+                 scaling: dict | None = None, device=None, max_position_embeddings: int | None = None, rope_theta: float | None = None,
+                 rope_type: str = "default", rope_scaling: dict | None = None, partial_rotary_factor: float | None = None,
+                 interleave: bool = False, backend: str | None = None) -> None:
+        """The keyword spellings of the reference (``max_position_embeddings``, ``rope_theta``, ``rope_type`` +
+        ``rope_scaling``, ``partial_rotary_factor``; phyai/src/phyai/layers/rotary_embedding.py:386-398) are taken as
+        well; ``backend`` is accepted and ignored (one implementation here); the pairwise-interleaved layout is not built."""
         super().__init__()
+        if interleave:
+            raise NotImplementedError("RotaryEmbedding rotates halves (the layout of every model here); interleave=True is not built")
+        max_position = max_position if max_position_embeddings is None else int(max_position_embeddings)
+        theta = theta if rope_theta is None else float(rope_theta)
+        if rope_scaling is not None or rope_type != "default":
+            scaling = {**(rope_scaling or {}), "rope_type": (rope_scaling or {}).get("rope_type", rope_type)}
+        if partial_rotary_factor is not None:
+            if not 0.0 < partial_rotary_factor <= 1.0:
+                raise ValueError(f"partial_rotary_factor must be in (0, 1], got {partial_rotary_factor}")
+            rotary_dim = int(head_dim * partial_rotary_factor)
         self.head_dim = head_dim
         self.rotary_dim = rotary_dim or head_dim
         if self.rotary_dim % 2 or self.rotary_dim > head_dim:
@@ -65,6 +80,13 @@ class RotaryEmbedding(nn.Module):
         inv = compute_inv_freq(self.rotary_dim, theta, scaling, device)
         table = compute_cos_sin_from_inv_freq(torch.arange(max_position, device=device), inv)
         self.register_buffer("cos_sin_cache", table, persistent=False)
+
+    def get_cos_sin(self, positions: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """``(cos, sin)`` for ``positions`` (any shape), each ``(*positions.shape, rotary_dim)`` fp32 with the half-width
+        table repeated (the rotate-half layout). Hoist this out of a layer loop when all layers share the positions."""
+        cs = self.cos_sin_cache[positions.long()]
+        half = cs.shape[-1] // 2
+        return torch.cat([cs[..., :half], cs[..., :half]], -1), torch.cat([cs[..., half:], cs[..., half:]], -1)
 
     def forward(self, positions: torch.Tensor, q: torch.Tensor, k: torch.Tensor):
         """q (T, Hq, D), k (T, Hkv, D), positions (T,). Returns rotated copies."""
@@ -106,6 +128,18 @@ class MRotaryEmbedding(nn.Module):
                 axis[o:o + n] = a
                 o += n
         self.register_buffer("band_axis", axis, persistent=False)
+
+    def get_cos_sin(self, position_ids: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """``(cos, sin)`` of shape ``(B, S, head_dim)`` (half-width table repeated) for ``position_ids`` ``(3, B, S)``, or
+        ``(B, S)`` read as the same index on all three axes."""
+        if position_ids.dim() == 2:
+            position_ids = position_ids[None].expand(3, *position_ids.shape)
+        if position_ids.dim() != 3 or position_ids.shape[0] != 3:
+            raise ValueError(f"position ids are (3, B, S) or (B, S), got {tuple(position_ids.shape)}")
+        _, B, S = position_ids.shape
+        cs = self.cos_sin(position_ids.reshape(3, B * S)).reshape(B, S, -1)
+        half = cs.shape[-1] // 2
+        return torch.cat([cs[..., :half], cs[..., :half]], -1), torch.cat([cs[..., half:], cs[..., half:]], -1)
 
     def cos_sin(self, positions: torch.Tensor) -> torch.Tensor:
         """positions (3, T) float -> (T, head_dim) fp32 ``cos | sin``."""

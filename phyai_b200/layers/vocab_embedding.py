@@ -43,7 +43,8 @@ def masked_embedding_lookup(ids: torch.Tensor, table: torch.Tensor, lo: int, hi:
 
 class VocabParallelEmbedding(nn.Module):
     def __init__(self, num_embeddings: int, embedding_dim: int, *, params_dtype: torch.dtype | None = None,
-                 embed_scale: float | None = None, axis: str = "tp", mesh=None, device=None, prefix: str = "") -> None:
+                 embed_scale: float | None = None, axis: str = "tp", mesh=None, device=None, prefix: str = "",
+                 padding_multiple: int = PAD_MULTIPLE) -> None:
         super().__init__()
         cfg = get_engine_config()
         m = mesh if mesh is not None else pstate.default_mesh()
@@ -51,7 +52,7 @@ class VocabParallelEmbedding(nn.Module):
         self.tp_rank = m.axis_local_rank(axis) if m is not None else 0
         self.tp_size = m.axis_size(axis) if m is not None else 1
         self.num_embeddings, self.embedding_dim = num_embeddings, embedding_dim
-        self.padded = pad_vocab(num_embeddings, self.tp_size)
+        self.padded = pad_vocab(num_embeddings, self.tp_size, padding_multiple)
         self.per_rank = self.padded // self.tp_size
         self.lo, self.hi = self.tp_rank * self.per_rank, (self.tp_rank + 1) * self.per_rank
         self.embed_scale = 1.0 if embed_scale is None else float(embed_scale)

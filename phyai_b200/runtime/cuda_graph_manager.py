@@ -36,8 +36,9 @@ class CudaGraphError(RuntimeError):
 
 
 class CudaGraph:
-    def __init__(self, name: str = "graph", warmup_iters: int = 3) -> None:
-        self.name, self.warmup_iters = name, warmup_iters
+    def __init__(self, name: str = "graph", warmup_iters: int = 3, *, num_warmup_iters: int | None = None, mempool=None) -> None:
+        self.name, self.warmup_iters = name, (warmup_iters if num_warmup_iters is None else int(num_warmup_iters))
+        self.mempool = mempool                  # memory pool captures use unless ``capture(pool=...)`` names another
         self.graph: torch.cuda.CUDAGraph | None = None
         self.static_inputs: dict[str, torch.Tensor] = {}
         self.static_output: Any = None
@@ -59,7 +60,7 @@ class CudaGraph:
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
-        with torch.no_grad(), pstate.graph_capture(), torch.cuda.graph(g, pool=pool, stream=_CAPTURE_STREAM):
+        with torch.no_grad(), pstate.graph_capture(), torch.cuda.graph(g, pool=pool if pool is not None else self.mempool, stream=_CAPTURE_STREAM):
             self.static_output = fn(**self.static_inputs)
         self.graph = g
         return self.static_output
@@ -78,6 +79,16 @@ class CudaGraph:
         self.replays += 1
         return self.static_output
 
+    def input_buffer(self, name: str) -> torch.Tensor:
+        """The static tensor the captured graph reads input ``name`` from."""
+        if name not in self.static_inputs:
+            raise KeyError(f"graph {self.name!r} has no input {name!r}; inputs: {sorted(self.static_inputs)}")
+        return self.static_inputs[name]
+
+    @property
+    def input_buffers(self) -> dict[str, torch.Tensor]:
+        return dict(self.static_inputs)
+
     def reset(self) -> None:
         self.graph = None
         self.static_inputs = {}
@@ -94,6 +105,24 @@ class CudaGraphRegistry:
         if key not in self._graphs:
             self._graphs[key] = CudaGraph(name=str(key), **kw)
         return self._graphs[key]
+
+    def register(self, key: Any, graph: CudaGraph) -> CudaGraph:
+        if key in self._graphs and self._graphs[key] is not graph:
+            raise CudaGraphError(f"a graph is already registered under {key!r}")
+        self._graphs[key] = graph
+        return graph
+
+    def deregister(self, key: Any) -> CudaGraph | None:
+        g = self._graphs.pop(key, None)
+        if g is not None:
+            g.reset()
+        return g
+
+    def get(self, key: Any, default: CudaGraph | None = None) -> CudaGraph | None:
+        return self._graphs.get(key, default)
+
+    def has(self, key: Any) -> bool:
+        return key in self._graphs
 
     def __contains__(self, key: Any) -> bool:
         return key in self._graphs
