@@ -205,6 +205,47 @@ def main() -> int:
         except (ValueError, RuntimeError):
             pass
         eng.entry.scheduler.local.close()
+    elif mode in ("cosmos3_wn_engine", "cosmos3_policy_wn_engine"):
+        # the multi-rank plugins through the Engine: guidance branches on two ranks (cfg = world), against the single-rank
+        # plugin's scheduler on a one-rank mesh with the same weights
+        from phyai_b200 import Engine, EngineArgs, ParallelConfig
+        from phyai_b200.models.cosmos3 import (Cosmos3ActionRequest, Cosmos3PolicyScheduler, Cosmos3T2VRequest, Cosmos3T2VScheduler,
+                                               tiny_cosmos3_config)
+        from phyai_b200.models.cosmos3.main_cosmos3_policy_wn import Cosmos3PolicyWNArgs
+        from phyai_b200.models.cosmos3.main_cosmos3_wn import Cosmos3WNArgs
+
+        policy = mode == "cosmos3_policy_wn_engine"
+        ec = EngineConfig(device=DeviceConfig("cpu", torch.float32), parallel=ParallelConfig(world_size=world, cfg_size=world),
+                          runtime=RuntimeConfig(use_cuda_graph=False))
+        cfg = tiny_cosmos3_config(action_gen=policy)
+        args = Cosmos3PolicyWNArgs(config=cfg, random_init_seed=4) if policy else Cosmos3WNArgs(config=cfg, load_vae=False, load_sound=False, random_init_seed=4)
+        eng = Engine(EngineArgs("cosmos3_policy_wn" if policy else "cosmos3_wn", args, ec))
+        sch = eng.entry.scheduler
+        if (sch.cfg_size, sch.cfg_rank) != (world, rank):
+            fails.append(f"plugin scheduler sees cfg {sch.cfg_rank}/{sch.cfg_size}")
+        g = torch.Generator().manual_seed(0)
+        ids, nids = torch.randint(0, 256, (1, 6), generator=g), torch.randint(0, 256, (1, 6), generator=g)
+        mask = torch.ones(1, 6, dtype=torch.long)
+        if policy:
+            req = Cosmos3ActionRequest(ids, mask, nids, mask, video_shape=(2, 4, 6), mode="policy", domain_id=1, action_chunk=3, raw_action_dim=5,
+                                       action_dim=8, cond_video_latents=torch.randn(1, 4, 2, 4, 6, generator=g), num_inference_steps=3, guidance_scale=3.0)
+        else:
+            req = Cosmos3T2VRequest(ids, mask, nids, mask, video_shape=(2, 4, 6), num_inference_steps=3, guidance_scale=4.0)
+        got = eng.step(req)
+        P.register_mesh("single", Mesh((1, 1), ("cfg", "tp"), rank=0, build_groups=False, device_type="cpu"))
+        with P.use_mesh("single"):
+            seq = (Cosmos3PolicyScheduler if policy else Cosmos3T2VScheduler)(eng.entry.transformer, device="cpu", flow_shift=sch._flow_shift,
+                                                                             use_karras_sigmas=sch._karras)      # the plugin's sampler settings
+            seq.setup()
+            want = seq.step(req)
+        if policy:
+            check("policy plugin over cfg ranks", got, want["action"], 1e-4)
+        else:
+            check("generation plugin over cfg ranks", got, want, 1e-4)
+        gathered = [torch.zeros_like(got) for _ in range(world)]
+        dist.all_gather(gathered, got.contiguous())
+        check("every rank returns the same result", gathered[0], gathered[-1], 1e-6)
+        eng.entry.close()
     elif mode == "seq_parallel":
         # Megatron-style sequence parallelism on the tensor-parallel axis: activations between the two linears' blocks are
         # split by tokens; the column-parallel layer gathers the tokens, the row-parallel layer reduce-scatters them back

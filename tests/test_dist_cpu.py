@@ -10,7 +10,8 @@ import pytest
 ROOT = Path(__file__).resolve().parents[1]
 
 
-@pytest.mark.parametrize("mode,port", [("collectives", 29711), ("cosmos3_tp", 29712), ("cosmos3_cfg", 29713), ("pi05_tp", 29714), ("pi05_dp", 29715), ("pi0_dp", 29716), ("vae_tiles", 29717), ("seq_parallel", 29718)])
+@pytest.mark.parametrize("mode,port", [("collectives", 29711), ("cosmos3_tp", 29712), ("cosmos3_cfg", 29713), ("pi05_tp", 29714), ("pi05_dp", 29715), ("pi0_dp", 29716), ("vae_tiles", 29717), ("seq_parallel", 29718), ("cosmos3_wn_engine", 29719),
+                                       ("cosmos3_policy_wn_engine", 29720)])
 def test_two_ranks(mode, port):
     env = dict(os.environ, PYTHONPATH=f"{ROOT}:{os.environ.get('PYTHONPATH', '')}", OMP_NUM_THREADS="2")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
