@@ -215,14 +215,32 @@ def main() -> int:
         from phyai_b200.models.cosmos3.main_cosmos3_wn import Cosmos3WNArgs
 
         policy = mode == "cosmos3_policy_wn_engine"
-        ec = EngineConfig(device=DeviceConfig("cpu", torch.float32), parallel=ParallelConfig(world_size=world, cfg_size=world),
+        cfg_ranks, tp_ranks = (2, world // 2) if world >= 4 else (world, 1)          # four ranks: two guidance branches x two tensor-parallel ranks
+        ec = EngineConfig(device=DeviceConfig("cpu", torch.float32), parallel=ParallelConfig(world_size=world, cfg_size=cfg_ranks, tp_size=tp_ranks),
                           runtime=RuntimeConfig(use_cuda_graph=False))
         cfg = tiny_cosmos3_config(action_gen=policy)
-        args = Cosmos3PolicyWNArgs(config=cfg, random_init_seed=4) if policy else Cosmos3WNArgs(config=cfg, load_vae=False, load_sound=False, random_init_seed=4)
+        # the plugin loads a checkpoint folder in the upstream layout (transformer/ under upstream key names): written once
+        # from a one-rank model's key index, so that sharded and whole models hold the same tensors
+        from phyai_b200.models.cosmos3 import Cosmos3Transformer
+        from phyai_b200.models.cosmos3.transformer_cosmos3 import cosmos3_inverse_remap
+        from phyai_b200.weights import synthetic_state_dict, write_checkpoint
+
+        ckpt = Path(tempfile.gettempdir()) / f"phyai_b200_dist_worker_{os.environ['MASTER_PORT']}"
+        P.register_mesh("single", Mesh((1, 1), ("cfg", "tp"), rank=0, build_groups=False, device_type="cpu"))
+        if rank == 0:
+            with P.use_mesh("single"):
+                probe = Cosmos3Transformer(cfg, params_dtype=torch.float32, device="cpu")
+            write_checkpoint(ckpt / "transformer", {cosmos3_inverse_remap(k): v for k, v in synthetic_state_dict(probe, seed=4, std=0.2).items()},
+                             cfg.to_dict())
+        dist.barrier()
+        kw = dict(checkpoint_dir=ckpt, config=cfg, weight_strict=True)
+        args = Cosmos3PolicyWNArgs(**kw) if policy else Cosmos3WNArgs(load_vae=False, load_sound=False, **kw)
         eng = Engine(EngineArgs("cosmos3_policy_wn" if policy else "cosmos3_wn", args, ec))
         sch = eng.entry.scheduler
-        if (sch.cfg_size, sch.cfg_rank) != (world, rank):
+        if (sch.cfg_size, sch.cfg_rank) != (cfg_ranks, rank // tp_ranks):
             fails.append(f"plugin scheduler sees cfg {sch.cfg_rank}/{sch.cfg_size}")
+        if eng.entry.transformer.gen_layers[0].mlp.down_proj.tp_size != tp_ranks:
+            fails.append("the transformer is not sharded over the tensor-parallel ranks")
         g = torch.Generator().manual_seed(0)
         ids, nids = torch.randint(0, 256, (1, 6), generator=g), torch.randint(0, 256, (1, 6), generator=g)
         mask = torch.ones(1, 6, dtype=torch.long)
@@ -232,9 +250,13 @@ def main() -> int:
         else:
             req = Cosmos3T2VRequest(ids, mask, nids, mask, video_shape=(2, 4, 6), num_inference_steps=3, guidance_scale=4.0)
         got = eng.step(req)
-        P.register_mesh("single", Mesh((1, 1), ("cfg", "tp"), rank=0, build_groups=False, device_type="cpu"))
         with P.use_mesh("single"):
-            seq = (Cosmos3PolicyScheduler if policy else Cosmos3T2VScheduler)(eng.entry.transformer, device="cpu", flow_shift=sch._flow_shift,
+            from phyai_b200.models.cosmos3.transformer_cosmos3 import cosmos3_weight_remap
+            from phyai_b200.weights import load_pretrained
+
+            whole = Cosmos3Transformer(cfg, params_dtype=torch.float32, device="cpu").eval()      # a one-rank copy of the same checkpoint
+            load_pretrained(whole, ckpt / "transformer", remap=cosmos3_weight_remap, strict=True)
+            seq = (Cosmos3PolicyScheduler if policy else Cosmos3T2VScheduler)(whole, device="cpu", flow_shift=sch._flow_shift,
                                                                              use_karras_sigmas=sch._karras)      # the plugin's sampler settings
             seq.setup()
             want = seq.step(req)
