@@ -204,13 +204,22 @@ def get_backend() -> str:
     """The name ``default_driver()`` resolves now: an explicit choice, else the environment, else ``"auto"``."""
     from ..env import envs
 
-    return _CHOSEN["name"] or (envs.PHYAI_VGPU_BACKEND.get() or "auto").lower()
+    if _CHOSEN["name"]:
+        return _CHOSEN["name"]
+    from ..engine_config import get_engine_config
+
+    try:
+        configured = get_engine_config().backends.vgpu          # EngineConfig already overlays PHYAI_VGPU_BACKEND
+    except Exception:  # noqa: BLE001 - no engine configuration installed yet
+        configured = None
+    return (configured or envs.PHYAI_VGPU_BACKEND.get() or "auto").lower()
 
 
 def default_driver() -> DriverApi:
     """The chosen backend's driver (``set_backend`` / ``PHYAI_VGPU_BACKEND``: a registered name; ``auto`` or unset:
     cuda-python when importable, else torch green contexts)."""
     want = get_backend()
+    want = {"driver": "cuda", "green_ctx": "torch", "greenctx": "torch"}.get(want, want)     # spellings of EngineConfig / the reference
     if want in ("", "auto"):
         try:
             return CudaDriver()
