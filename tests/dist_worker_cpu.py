@@ -53,7 +53,7 @@ def main() -> int:
         P.init((world,), ("tp",), device="cpu")
         L.init()
         P.register_mesh("single", Mesh((1,), ("tp",), rank=0, build_groups=False, device_type="cpu"))
-        mc = tiny_cosmos3_config(action_gen=True)
+        mc = tiny_cosmos3_config(action_gen=True, num_key_value_heads=max(2, world))      # one KV head per rank at least
         with P.use_mesh("single"):
             single = Cosmos3Transformer(mc, params_dtype=torch.float32, device="cpu").eval()
         tp_model = Cosmos3Transformer(mc, params_dtype=torch.float32, device="cpu").eval()

@@ -23,3 +23,10 @@ def test_two_ranks(mode, port, world=2):
 @pytest.mark.parametrize("mode,port", [("cosmos3_wn_engine", 29723), ("cosmos3_policy_wn_engine", 29724)])
 def test_four_ranks_two_guidance_branches_of_two_tensor_parallel_ranks(mode, port):
     test_two_ranks(mode, port, world=4)
+
+
+@pytest.mark.parametrize("mode,port", [("pi05_tp", 29725), ("cosmos3_tp", 29726), ("collectives", 29727), ("seq_parallel", 29728)])
+def test_four_ranks(mode, port):
+    """The tensor-parallel paths at four ranks: more ranks than KV heads (replicated heads), cameras that do not divide
+    over the ranks, four-way collectives and token shards."""
+    test_two_ranks(mode, port, world=4)
