@@ -725,3 +725,33 @@ def test_cosmos3_generation_media_output(ref):
             a.postprocess(bad)
         with pytest.raises(ValueError):
             b.postprocess(bad)
+
+
+@pytest.mark.parametrize("variant", ["video", "action", "sound"])
+def test_cosmos3_rotary_tables_for_text_video_action_and_sound_tokens(ref_single_rank, variant):
+    """Positions of a whole request (text with padding, video grid rescaled by the frame rate, action tokens one frame
+    later at their own rate, sound tokens at the sound rate) turned into cos / sin tables by both packages' transformers."""
+    from phyai_b200 import parallel as P
+    from phyai_b200.engine_config import DeviceConfig, EngineConfig, init_engine_config
+    from phyai_b200.models.cosmos3 import Cosmos3Transformer, tiny_cosmos3_config
+
+    ref = ref_single_rank
+    rm = ref("phyai.models.cosmos3.modeling_cosmos3")
+    init_engine_config(EngineConfig(device=DeviceConfig("cpu", torch.float32)))
+    P.init((1,), ("tp",), device="cpu")
+    try:
+        cfg = tiny_cosmos3_config(action_gen=variant == "action", sound_gen=variant == "sound")
+        mine = Cosmos3Transformer(cfg, params_dtype=torch.float32, device="cpu")
+        theirs = rm.Cosmos3Transformer(_mirror_config(cfg, rm), params_dtype=torch.float32, device="cpu")
+        mask = torch.tensor([[1, 1, 1, 1, 1, 0, 0], [1, 1, 1, 0, 0, 0, 0]])          # two prompts of different length, right-padded
+        for fps, sfps in ((None, None), (24.0, 25.0), (10.0, 50.0)):
+            kw = dict(action_len=5 if variant == "action" else 0, sound_len=7 if variant == "sound" else 0, sound_fps=sfps if variant == "sound" else None)
+            und, gen = mine._rope_tables(mask, 3, 2, 3, fps, "cpu", **kw)
+            (cu, su), (cg, sg) = theirs._compute_rope_freqs(mask, 3, 2, 3, fps, torch.device("cpu"), torch.float32, **kw)
+            half = cfg.head_dim // 2
+            for got, cos, sin, what in ((und, cu, su, "text"), (gen, cg, sg, "generated")):
+                assert got.shape[:2] == cos.shape[:2], (variant, fps, what)
+                assert torch.allclose(got[..., :half], cos[:, :, 0, :half], atol=1e-5), (variant, fps, what)
+                assert torch.allclose(got[..., half:], sin[:, :, 0, :half], atol=1e-5), (variant, fps, what)
+    finally:
+        P.shutdown()
