@@ -755,3 +755,56 @@ def test_cosmos3_rotary_tables_for_text_video_action_and_sound_tokens(ref_single
                 assert torch.allclose(got[..., half:], sin[:, :, 0, :half], atol=1e-5), (variant, fps, what)
     finally:
         P.shutdown()
+
+
+def test_cosmos3_adapters_around_the_decoder_stack(ref_single_rank, tmp_path):
+    """The pieces of the Cosmos3 transformer that are plain tensor code in the reference too, run with the same weights:
+    latent <-> token reshapes (grid sizes that need padding included), the timestep embedding, the per-domain action
+    projections and the gate that keeps the timestep off clean frames."""
+    from phyai_b200 import parallel as P
+    from phyai_b200.engine_config import DeviceConfig, EngineConfig, init_engine_config
+    from phyai_b200.models.cosmos3 import Cosmos3Transformer, tiny_cosmos3_config
+    from phyai_b200.models.cosmos3.transformer_cosmos3 import cosmos3_inverse_remap, cosmos3_weight_remap
+    from phyai_b200.weights import load_pretrained, synthetic_state_dict, write_checkpoint
+
+    ref = ref_single_rank
+    rm = ref("phyai.models.cosmos3.modeling_cosmos3")
+    init_engine_config(EngineConfig(device=DeviceConfig("cpu", torch.float32)))
+    P.init((1,), ("tp",), device="cpu")
+    try:
+        cfg = tiny_cosmos3_config(action_gen=True)
+        mine = Cosmos3Transformer(cfg, params_dtype=torch.float32, device="cpu")
+        theirs = rm.Cosmos3Transformer(_mirror_config(cfg, rm), params_dtype=torch.float32, device="cpu")
+        g = torch.Generator().manual_seed(5)
+        state = {cosmos3_inverse_remap(k): torch.randn(v.shape, generator=g) * 0.1 for k, v in synthetic_state_dict(mine, seed=1, std=0.05).items()}
+        write_checkpoint(tmp_path, state, None)
+        ref("phyai.weights.loader").load_pretrained(theirs, tmp_path, remap=rm.cosmos3_weight_remap, strict=True)
+        load_pretrained(mine, tmp_path, remap=cosmos3_weight_remap, strict=True)
+
+        c, p = cfg.latent_channel, cfg.latent_patch_size
+        for t, h, w in ((2, 2 * p, 3 * p), (3, 2 * p + 1, 3 * p - 1), (1, 1, 1)):
+            lat = torch.randn(2, c, t, h, w, generator=g)
+            tok_m, tok_r = mine.patchify(lat, t, h, w), theirs.patchify(lat, t, h, w)
+            assert torch.equal(tok_m, tok_r), (t, h, w)
+            assert torch.equal(mine.unpatchify(tok_m, t, h, w), theirs.unpatchify(tok_r, t, h, w)), (t, h, w)
+            assert torch.equal(mine.unpatchify(tok_m, t, h, w), lat), (t, h, w)
+            assert mine._pad_to_patch_size(h, w) == theirs._pad_to_patch_size(h, w)
+
+        ref("phyai.layers.linear").init(register_flashinfer=False, validate=False)      # its linears pick a kernel per call: the torch one
+        ts = torch.tensor([0.0, 1.0, 37.5, 999.0])
+        assert torch.allclose(mine.time_embedder(ts), theirs.time_embedder(ts), atol=1e-5, rtol=1e-5)
+
+        dom = torch.tensor([0, cfg.num_embodiment_domains - 1, 1])
+        act = torch.randn(3, 5, cfg.action_dim, generator=g)
+        hid = torch.randn(3, 5, cfg.hidden_size, generator=g)
+        assert torch.allclose(mine.action_proj_in(act, dom), theirs.action_proj_in(act, dom), atol=1e-6)
+        assert torch.allclose(mine.action_proj_out(hid, dom), theirs.action_proj_out(hid, dom), atol=1e-6)
+        assert torch.allclose(mine.action_proj_in(act[:, 0], dom), theirs.action_proj_in(act[:, 0], dom), atol=1e-6)
+
+        emb = torch.randn(2, cfg.hidden_size, generator=g)
+        frames = torch.tensor([[0.0, 1.0, 1.0], [1.0, 0.0, 1.0]])
+        for mask in (None, frames):
+            assert torch.equal(mine._gate_timestep(emb, mask, 4), theirs._gate_timestep(emb, mask, 4))
+    finally:
+        ref("phyai.layers.linear")._reset_for_test()
+        P.shutdown()
