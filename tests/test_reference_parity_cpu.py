@@ -808,3 +808,89 @@ def test_cosmos3_adapters_around_the_decoder_stack(ref_single_rank, tmp_path):
     finally:
         ref("phyai.layers.linear")._reset_for_test()
         P.shutdown()
+
+
+def test_pi05_embeddings_and_heads(ref_single_rank, tmp_path):
+    """The ends of the Pi0.5 network that are plain tensor code in the reference too, with the same weights: patch and
+    position embedding of the cameras, scaled token embedding of the prompt, the flow-time embedding that conditions the
+    action expert's norms, and the action projections in and out."""
+    from phyai_b200 import parallel as P
+    from phyai_b200.engine_config import DeviceConfig, EngineConfig, init_engine_config
+    from phyai_b200.models.pi05.configuration_pi05 import tiny_pi05_config
+    from phyai_b200.models.pi05.modeling_pi05 import PI05Model
+    from phyai_b200.weights import load_pretrained, synthetic_state_dict, write_checkpoint
+
+    ref = ref_single_rank
+    init_engine_config(EngineConfig(device=DeviceConfig("cpu", torch.float32)))
+    P.init((1,), ("tp",), device="cpu")
+    try:
+        cfg = tiny_pi05_config()
+        mine = PI05Model(cfg)
+        theirs = ref("phyai.models.pi05.modeling_pi05").PI05Model(_mirror_config(cfg, ref("phyai.models.pi05.configuration_pi05")),
+                                                                  attn_backend="flashinfer", norm_backend="flashinfer", device="cpu")
+        ref("phyai.engine")
+        g = torch.Generator().manual_seed(9)
+        state = {k: torch.randn(v.shape, generator=g) * 0.1 for k, v in synthetic_state_dict(mine, seed=1, std=0.05).items()}
+        write_checkpoint(tmp_path, state, None)
+        ref("phyai.weights.loader").load_pretrained(theirs, tmp_path, remap=ref("phyai.models.pi05.main_pi05")._compose_remap(None), strict=True)
+        load_pretrained(mine, tmp_path, strict=True)
+        ref("phyai.layers.linear").init(register_flashinfer=False, validate=False)
+
+        v = cfg.vision
+        pix = torch.rand(2, v.num_channels, v.image_size, v.image_size, generator=g) * 2 - 1
+        assert torch.allclose(mine.vision.embed_patches(pix), theirs.vision.vision_tower.vision_model.embeddings(pix), atol=1e-5)
+
+        ids = torch.randint(0, cfg.text.vocab_size, (2, 7), generator=g)
+        assert torch.allclose(mine.paligemma_lm.embed_lang(ids), theirs.paligemma_lm.embed_lang(ids), atol=1e-6)
+
+        t = torch.tensor([1.0, 0.9, 0.35, 0.0])
+        assert torch.allclose(mine.heads.embed_time(t), theirs.heads.embed_time(t), atol=1e-5)
+
+        noise = torch.randn(2, cfg.chunk_size, cfg.max_action_dim, generator=g)
+        hid = torch.randn(2, cfg.chunk_size, cfg.expert.hidden_size, generator=g)
+        assert torch.allclose(mine.heads.action_in_proj(noise)[0], theirs.heads.embed_action(noise), atol=1e-5)
+        assert torch.allclose(mine.heads.action_out_proj(hid)[0], theirs.heads.project_action(hid), atol=1e-5)
+    finally:
+        ref("phyai.layers.linear")._reset_for_test()
+        P.shutdown()
+
+
+def test_pi0_state_and_action_time_heads(ref_single_rank, tmp_path):
+    """Pi0 feeds the robot state as one token and mixes the flow time into every action token through a small network
+    (no time-conditioned norms): both, and the projection back to actions, with the same weights in both packages."""
+    from phyai_b200 import parallel as P
+    from phyai_b200.engine_config import DeviceConfig, EngineConfig, init_engine_config
+    from phyai_b200.models.pi0.configuration_pi0 import tiny_pi0_config
+    from phyai_b200.models.pi0.modeling_pi0 import PI0Model
+    from phyai_b200.weights import load_pretrained, synthetic_state_dict, write_checkpoint
+
+    ref = ref_single_rank
+    init_engine_config(EngineConfig(device=DeviceConfig("cpu", torch.float32)))
+    P.init((1,), ("tp",), device="cpu")
+    try:
+        cfg = tiny_pi0_config()
+        mine = PI0Model(cfg)
+        theirs = ref("phyai.models.pi0.modeling_pi0").PI0Model(_mirror_config(cfg, ref("phyai.models.pi0.configuration_pi0")),
+                                                               attn_backend="flashinfer", norm_backend="flashinfer", device="cpu")
+        ref("phyai.engine")
+        g = torch.Generator().manual_seed(11)
+        state = {k: torch.randn(v.shape, generator=g) * 0.1 for k, v in synthetic_state_dict(mine, seed=1, std=0.05).items()}
+        write_checkpoint(tmp_path, state, None)
+        ref("phyai.weights.loader").load_pretrained(theirs, tmp_path, remap=ref("phyai.models.pi0.main_pi0")._compose_remap(None), strict=True)
+        load_pretrained(mine, tmp_path, strict=True)
+        ref("phyai.layers.linear").init(register_flashinfer=False, validate=False)
+
+        robot = torch.randn(1, cfg.max_state_dim, generator=g)
+        assert torch.allclose(mine.heads.state_proj(robot)[0], theirs.heads.embed_state(robot), atol=1e-5)
+        x_t = torch.randn(cfg.chunk_size, cfg.max_action_dim, generator=g)
+        for t in (1.0, 0.6, 0.1):
+            got = mine.heads.embed_action_time(x_t, torch.tensor([t]))
+            want = theirs.heads.embed_action_time(x_t[None], torch.tensor([t]))[0]
+            assert torch.allclose(got, want, atol=1e-5), t
+        hid = torch.randn(cfg.chunk_size, cfg.expert.hidden_size, generator=g)
+        assert torch.allclose(mine.heads.action_out_proj(hid)[0], theirs.heads.project_action(hid[None])[0], atol=1e-5)
+        ids = torch.randint(0, cfg.text.vocab_size, (1, 6), generator=g)
+        assert torch.allclose(mine.paligemma_lm.embed_lang(ids), theirs.paligemma_lm.embed_lang(ids), atol=1e-6)
+    finally:
+        ref("phyai.layers.linear")._reset_for_test()
+        P.shutdown()
