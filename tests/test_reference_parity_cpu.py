@@ -894,3 +894,131 @@ def test_pi0_state_and_action_time_heads(ref_single_rank, tmp_path):
     finally:
         ref("phyai.layers.linear")._reset_for_test()
         P.shutdown()
+
+
+class _StubDenoiser:
+    """Stands in for the network inside both packages' Cosmos3 schedulers: a closed-form "velocity" of everything the
+    loop hands it (latents, timestep, prompt, masks, domain), so the loops can be compared without a GPU."""
+
+    use_cuda_graph = False
+
+    def __init__(self):
+        self.calls = []
+
+    def setup(self):
+        pass
+
+    def reset(self, held=None):
+        self.calls.append("reset")
+
+    def prepare(self, branch, **kw):
+        pass
+
+    def forward(self, branch, video, t, *, text_ids, text_mask, video_shape, fps, noisy_frame_mask=None, action_latents=None,
+                action_domain_id=None, action_noisy_mask=None, sound_latents=None, sound_fps=None):
+        self.calls.append(branch)
+        s = 1.0 if branch == "cond" else 0.55
+        bias = 1e-3 * float(t.float().reshape(-1)[0]) + 1e-2 * float((text_ids * text_mask).float().mean()) / 100.0 + 1e-3 * fps / 24.0
+        v = torch.tanh(video.float() * s) * 0.7 + bias
+        if noisy_frame_mask is not None:
+            v = v * (0.5 + 0.5 * noisy_frame_mask.float())[:, None, :, None, None]
+        if action_latents is not None:
+            a = torch.sin(action_latents.float() * s) + bias + 0.01 * action_domain_id.float()[:, None, None]
+            a = a * (0.25 + 0.75 * action_noisy_mask.float())[..., None] + 0.05 * v.mean()
+            return v.to(video.dtype), a.to(action_latents.dtype)
+        if sound_latents is not None:
+            return v.to(video.dtype), (torch.cos(sound_latents.float()) * s + bias * sound_fps / 25.0).to(sound_latents.dtype)
+        return v.to(video.dtype)
+
+
+def _tiny_prompts(g, B=1):
+    ids = torch.randint(1, 90, (B, 6), generator=g)
+    mask = torch.tensor([[1, 1, 1, 1, 0, 0]] * B)
+    nids = torch.randint(1, 90, (B, 6), generator=g)
+    nmask = torch.tensor([[1, 1, 1, 0, 0, 0]] * B)
+    return dict(text_ids=ids, text_mask=mask, neg_text_ids=nids, neg_text_mask=nmask)
+
+
+@pytest.mark.parametrize("case", ["t2v", "t2v_noguide", "i2v", "sound", "given_noise"])
+def test_cosmos3_generation_loop_around_a_stub_network(ref_single_rank, case):
+    """The whole denoise loop of the generation scheduler (seeded noise, guidance mix, one solver per stream, clean frames
+    written back after every step, sound layout on return) run in both packages around the same stand-in network."""
+    from phyai_b200 import parallel as P
+    from phyai_b200.engine_config import DeviceConfig, EngineConfig, init_engine_config
+    from phyai_b200.models.cosmos3 import Cosmos3Transformer, tiny_cosmos3_config
+    from phyai_b200.models.cosmos3.scheduler_cosmos3 import Cosmos3T2VRequest, Cosmos3T2VScheduler
+
+    ref = ref_single_rank
+    rm, rs = ref("phyai.models.cosmos3.modeling_cosmos3"), ref("phyai.models.cosmos3.scheduler_ws1_cosmos3")
+    init_engine_config(EngineConfig(device=DeviceConfig("cpu", torch.float32)))
+    P.init((1,), ("tp",), device="cpu")
+    try:
+        cfg = tiny_cosmos3_config(sound_gen=case == "sound")
+        mine = Cosmos3T2VScheduler(Cosmos3Transformer(cfg, params_dtype=torch.float32, device="cpu"), device="cpu", flow_shift=3.0, use_karras_sigmas=False)
+        theirs = rs.Cosmos3T2VScheduler(rm.Cosmos3Transformer(_mirror_config(cfg, rm), params_dtype=torch.float32, device="cpu"), device="cpu",
+                                        flow_shift=3.0, use_karras_sigmas=False)
+        mine.setup()
+        mine.runner, theirs.runner = _StubDenoiser(), _StubDenoiser()
+        theirs.setup()
+        g = torch.Generator().manual_seed(3)
+        t, h, w = 3, 4, 6
+        kw = dict(_tiny_prompts(g), video_shape=(t, h, w), fps=16.0, num_inference_steps=6, guidance_scale=1.0 if case == "t2v_noguide" else 4.5, seed=7)
+        if case == "i2v":
+            kw.update(cond_latents=torch.randn(1, cfg.latent_channel, t, h, w, generator=g), cond_frame_indexes=(0, 2))
+        if case == "sound":
+            kw.update(sound_frames=9, sound_dim=cfg.sound_dim, sound_latent_fps=25.0)
+        if case == "given_noise":
+            kw.update(noise=torch.randn(1, cfg.latent_channel, t, h, w, generator=g))
+        got, want = mine.step(Cosmos3T2VRequest(**kw)), theirs.step(rs.Cosmos3T2VRequest(**kw))
+        assert mine.runner.calls == theirs.runner.calls and len(mine.runner.calls) == 1 + 6 * (1 if case == "t2v_noguide" else 2)
+        if case == "sound":
+            assert got["sound"].shape == want["sound"].shape == (1, cfg.sound_dim, 9)
+            assert torch.allclose(got["sound"], want["sound"], atol=2e-5)
+            got, want = got["video"], want["video"]
+        assert torch.allclose(got, want, atol=2e-5), float((got - want).abs().max())
+        if case == "i2v":
+            assert torch.equal(got[:, :, [0, 2]], kw["cond_latents"][:, :, [0, 2]])
+    finally:
+        P.shutdown()
+
+
+@pytest.mark.parametrize("mode,guide,batch,frames", [("policy", 1.0, 1, None), ("policy", 3.0, 2, None), ("forward_dynamics", 1.0, 1, None),
+                                                     ("inverse_dynamics", 2.0, 1, None), ("policy", 1.0, 1, (0, 1))])
+def test_cosmos3_policy_loop_around_a_stub_network(ref_single_rank, mode, guide, batch, frames):
+    """The joint video + action loop in its three modes: which frames and which stream stay clean, the zeroed tail beyond
+    the robot's action width, per-sample noise in a batch, guidance on both streams, in both packages around one stub."""
+    from phyai_b200 import parallel as P
+    from phyai_b200.engine_config import DeviceConfig, EngineConfig, init_engine_config
+    from phyai_b200.models.cosmos3 import Cosmos3Transformer, tiny_cosmos3_config
+    from phyai_b200.models.cosmos3.scheduler_cosmos3 import Cosmos3ActionRequest, Cosmos3PolicyScheduler
+
+    ref = ref_single_rank
+    rm, rs = ref("phyai.models.cosmos3.modeling_cosmos3"), ref("phyai.models.cosmos3.scheduler_ws1_cosmos3_policy")
+    init_engine_config(EngineConfig(device=DeviceConfig("cpu", torch.float32)))
+    P.init((1,), ("tp",), device="cpu")
+    try:
+        cfg = tiny_cosmos3_config(action_gen=True)
+        mine = Cosmos3PolicyScheduler(Cosmos3Transformer(cfg, params_dtype=torch.float32, device="cpu"), device="cpu", flow_shift=2.0, use_karras_sigmas=True)
+        theirs = rs.Cosmos3PolicyScheduler(rm.Cosmos3Transformer(_mirror_config(cfg, rm), params_dtype=torch.float32, device="cpu"), device="cpu",
+                                           flow_shift=2.0, use_karras_sigmas=True, use_cuda_graph=False)
+        mine.setup()
+        mine.runner, theirs.runner = _StubDenoiser(), _StubDenoiser()
+        theirs.setup()
+        g = torch.Generator().manual_seed(4)
+        t, h, w, chunk, raw = 3, 4, 4, 5, 7
+        kw = dict(_tiny_prompts(g, batch), video_shape=(t, h, w), mode=mode, domain_id=2, action_chunk=chunk, raw_action_dim=raw, action_dim=cfg.action_dim,
+                  cond_video_latents=torch.randn(batch, cfg.latent_channel, t, h, w, generator=g), cond_action=torch.randn(batch, chunk, cfg.action_dim, generator=g),
+                  cond_frame_indexes=frames, fps=10.0, num_inference_steps=5, guidance_scale=guide, seed=11)
+        got, want = mine.step(Cosmos3ActionRequest(**kw)), theirs.step(rs.Cosmos3ActionRequest(**kw))
+        assert mine.runner.calls == theirs.runner.calls
+        assert got["action"].shape == want["action"].shape == (batch, chunk, raw)
+        assert torch.allclose(got["action"], want["action"], atol=2e-5), float((got["action"] - want["action"]).abs().max())
+        assert torch.allclose(got["video"], want["video"], atol=2e-5), float((got["video"] - want["video"]).abs().max())
+        if mode == "forward_dynamics":
+            assert torch.equal(got["action"], kw["cond_action"][:, :, :raw])
+        if mode == "inverse_dynamics":
+            assert torch.equal(got["video"], kw["cond_video_latents"])
+        if batch > 1 and mode == "policy":
+            assert not torch.equal(got["action"][0], got["action"][1])
+    finally:
+        P.shutdown()
