@@ -106,3 +106,23 @@ def test_payload_dataclasses():
     l = LLMForwardBatch(hidden_states=torch.zeros(5, 4), position_ids=torch.arange(5), write_indices=torch.arange(5))
     e = ExpertForwardBatch(x_t=torch.zeros(1, 10, 8), time_emb=torch.zeros(1, 16))
     assert v.pixel_values.shape[0] == 3 and l.position_ids[-1] == 4 and e.x_t.shape == (1, 10, 8)
+
+
+def test_tensor_dump_filter_function_from_a_file_sees_the_module(tmp_path):
+    """The filter function named in the runtime configuration is called with the module as well as its name."""
+    from types import SimpleNamespace
+
+    from phyai_b200.runtime.tensor_dump import TensorDumper, load_pass
+
+    src = tmp_path / "pick.py"
+    src.write_text("import torch\n\ndef only_linear(name, module):\n    return isinstance(module, torch.nn.Linear)\n\ndef by_name(name):\n    return name.endswith('1')\n")
+    net = torch.nn.Sequential(torch.nn.Linear(3, 3), torch.nn.ReLU(), torch.nn.Linear(3, 2))
+    for func, want in (("only_linear", ["net.0", "net.2"]), ("by_name", ["net.1"])):
+        rt = SimpleNamespace(debug_tensor_dump_dir=tmp_path / func, debug_tensor_dump_filter=None, debug_tensor_dump_filter_fn=f"{src}:{func}")
+        d = TensorDumper.from_config(rt)
+        assert d.attach(net, prefix="net") == len(want)
+        net(torch.ones(1, 3))
+        assert list(load_pass(d.flush())) == want
+        d.detach()
+    with pytest.raises(FileNotFoundError):
+        TensorDumper.from_config(SimpleNamespace(debug_tensor_dump_dir=tmp_path, debug_tensor_dump_filter=None, debug_tensor_dump_filter_fn=f"{tmp_path}/absent.py:f"))

@@ -1022,3 +1022,64 @@ def test_cosmos3_policy_loop_around_a_stub_network(ref_single_rank, mode, guide,
             assert not torch.equal(got["action"][0], got["action"][1])
     finally:
         P.shutdown()
+
+
+def test_tensor_dump_files_have_the_same_keys_and_values(ref, tmp_path):
+    """One module tree (a module that returns a ``(tensor, None)`` pair, one called twice, one returning no tensor)
+    hooked by both packages' dumpers through the reference's call: the pass files hold the same names and tensors, so a
+    dump taken with one package can be compared key by key with a dump of the other."""
+    from collections import OrderedDict
+
+    from phyai_b200.runtime import tensor_dump as mine_mod
+
+    ref_mod = ref("phyai.runtime.tensor_dump")
+
+    class Pair(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.w = torch.nn.Parameter(torch.eye(4) * 2)
+
+        def forward(self, x):
+            return x @ self.w, None
+
+    class Silent(torch.nn.Module):
+        def forward(self, x):
+            return "nothing to keep"
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.body = torch.nn.Sequential(OrderedDict(lin=torch.nn.Linear(4, 4), act=torch.nn.Tanh()))
+            self.pair, self.silent = Pair(), Silent()
+
+        def forward(self, x):
+            y = self.body(x)
+            y = self.body.act(y)
+            self.silent(y)
+            return self.pair(y)[0]
+
+    torch.manual_seed(0)
+    net, x = Net(), torch.randn(3, 4)
+    results = {}
+    for tag, mod in (("mine", mine_mod), ("theirs", ref_mod)):
+        for flt in (None, [r"body\.", r"^net\.pair$"], lambda name, module: isinstance(module, torch.nn.Tanh)):
+            d = mod.register_tensor_dumper({"net": net}, dump_dir=tmp_path / tag / str(len(results)), filter=flt, rank=3, world_size=4)
+            net(x)
+            first = d.flush_pass()
+            net(x * 2)
+            second = d.flush_pass()
+            assert d.flush_pass() is None
+            d.detach()
+            assert first.parent == d.process_dir and first.parent.name.startswith("rank3_pid") and second.name == "pass00001.pt"
+            results.setdefault(tag, []).append((mod.load_pass(first), mod.load_pass(second)))
+    for (m1, m2), (t1, t2) in zip(results["mine"], results["theirs"]):
+        for a, b in ((m1, t1), (m2, t2)):
+            assert list(a) == list(b)
+            assert all(torch.equal(a[k], b[k]) for k in a)
+    everything = results["mine"][0][0]
+    assert list(everything) == ["net.body.lin", "net.body.act", "net.body.act::call1", "net.pair"] and isinstance(everything["net.pair"], torch.Tensor)
+    assert list(results["mine"][2][0]) == ["net.body.act", "net.body.act::call1"]
+    with pytest.raises(TypeError):
+        mine_mod.TensorDumper({"net": net}, dump_dir=tmp_path / "bad", filter="net")
+    with pytest.raises(ValueError):
+        mine_mod.TensorDumper({}, dump_dir=tmp_path / "bad")
